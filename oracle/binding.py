@@ -1,0 +1,346 @@
+"""ctypes binding of the CPU oracle (TEST INFRASTRUCTURE ONLY).
+
+Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline leg import this
+module; the product package never does.  The shared object is built from
+relux_oracle.cpp by `make -C oracle` (done on demand here).
+"""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "librelux_oracle.so")
+
+FAITHFUL, INTENDED = 0, 1
+FLAG_MLA_BF16_CACHE = 1
+
+MHA_HOOK = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float),
+                       C.POINTER(C.c_float), C.POINTER(C.c_float))
+MLA_HOOK = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float),
+                       C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float))
+
+
+class ModelCfg(C.Structure):
+    _fields_ = [("vocab", C.c_int32), ("dModel", C.c_int32), ("numHeads", C.c_int32), ("numKVHeads", C.c_int32),
+                ("numLayers", C.c_int32), ("dFF", C.c_int32), ("maxSeqLen", C.c_int32), ("ropeBase", C.c_float),
+                ("causal", C.c_int32), ("swiglu", C.c_int32), ("mla", C.c_int32), ("dC", C.c_int32), ("dHR", C.c_int32)]
+
+
+def build(force=False):
+    src = os.path.join(_HERE, "relux_oracle.cpp")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "-s"])
+    return _SO
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = C.CDLL(build())
+        L = _lib
+        L.ro_bf16_from_f32.restype = C.c_uint16
+        L.ro_bf16_from_f32.argtypes = [C.c_float]
+        L.ro_f32_from_bf16.restype = C.c_float
+        L.ro_f32_from_bf16.argtypes = [C.c_uint16]
+        L.ro_fastexp32.restype = C.c_float
+        L.ro_fastexp32.argtypes = [C.c_float]
+        L.ro_gelu.restype = C.c_float
+        L.ro_gelu.argtypes = [C.c_float]
+        for n in ("ro_rope_new", "ro_kvcache_new", "ro_kvcache_new_sized", "ro_mlacache_new", "ro_model_new"):
+            getattr(L, n).restype = C.c_void_p
+        L.ro_rope_new.argtypes = [C.c_int, C.c_float, C.c_int]
+        L.ro_rope_cos.restype = C.POINTER(C.c_float)
+        L.ro_rope_sin.restype = C.POINTER(C.c_float)
+        L.ro_kvcache_view_shape.restype = C.c_int64
+        L.ro_model_weight_count.restype = C.c_int64
+    return _lib
+
+
+def _p(a, t=None):
+    if a is None:
+        return None
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+# ---- scalar / slice helpers -------------------------------------------------
+def bf16_from_f32(a):
+    a = f32(a)
+    out = np.empty(a.shape, np.uint16)
+    lib().ro_bf16_slice_from_f32(_p(a), _p(out), C.c_int64(a.size))
+    return out
+
+
+def f32_from_bf16(a):
+    a = np.ascontiguousarray(a, dtype=np.uint16)
+    out = np.empty(a.shape, np.float32)
+    lib().ro_f32_slice_from_bf16(_p(a), _p(out), C.c_int64(a.size))
+    return out
+
+
+def bf16_from_f64(a):
+    a = np.ascontiguousarray(a, dtype=np.float64)
+    out = np.empty(a.shape, np.uint16)
+    lib().ro_bf16_slice_from_f64(_p(a), _p(out), C.c_int64(a.size))
+    return out
+
+
+def fastexp32(x):
+    return float(lib().ro_fastexp32(C.c_float(x)))
+
+
+def softmax_rows(m):
+    m = f32(m).copy()
+    lib().ro_softmax_rows(_p(m), C.c_int(m.shape[0]), C.c_int(m.shape[1]))
+    return m
+
+
+def matmul(a, b):
+    a, b = f32(a), f32(b)
+    out = np.empty((a.shape[0], b.shape[1]), np.float32)
+    lib().ro_matmul(_p(out), _p(a), _p(b), a.shape[0], a.shape[1], b.shape[1])
+    return out
+
+
+def matmul_transb(a, b):
+    a, b = f32(a), f32(b)
+    out = np.empty((a.shape[0], b.shape[0]), np.float32)
+    lib().ro_matmul_transb(_p(out), _p(a), _p(b), a.shape[0], a.shape[1], b.shape[0])
+    return out
+
+
+def rmsnorm(x, eps):
+    x = f32(x)
+    D = x.shape[-1]
+    out = np.empty_like(x)
+    lib().ro_rmsnorm(_p(out), _p(x), C.c_int(x.size // D), C.c_int(D), C.c_float(eps))
+    return out
+
+
+def greedy(logits):
+    l = f32(logits)
+    return int(lib().ro_greedy(_p(l), C.c_int(l.size)))
+
+
+# ---- RoPE -------------------------------------------------------------------
+class Rope:
+    def __init__(self, head_dim, base, max_seq_len):
+        self.h = lib().ro_rope_new(head_dim, C.c_float(base), max_seq_len)
+        if not self.h:
+            raise ValueError("NewRotaryEmbedding: invalid arguments (the reference panics)")
+        self.head_dim = head_dim
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().ro_rope_free(C.c_void_p(self.h))
+
+    @property
+    def max_seq_len(self):
+        return lib().ro_rope_max_seq_len(C.c_void_p(self.h))
+
+    def cos(self):
+        n = self.max_seq_len * self.head_dim // 2
+        return np.ctypeslib.as_array(lib().ro_rope_cos(C.c_void_p(self.h)), (n,)).copy()
+
+    def sin(self):
+        n = self.max_seq_len * self.head_dim // 2
+        return np.ctypeslib.as_array(lib().ro_rope_sin(C.c_void_p(self.h)), (n,)).copy()
+
+    def extend(self, new_max):
+        if lib().ro_rope_extend(C.c_void_p(self.h), new_max):
+            raise ValueError("ExtendMaxSeqLen: newMax must exceed current (the reference panics)")
+
+    def apply(self, x, start_pos, intended_positions=False):
+        x = f32(x)
+        out = np.empty_like(x)
+        rank1 = x.ndim == 1
+        seq = 1 if rank1 else x.shape[-2]
+        rc = lib().ro_rope_apply(C.c_void_p(self.h), _p(x), _p(out), C.c_int64(x.size // self.head_dim), seq,
+                                 int(rank1), start_pos, int(intended_positions))
+        if rc:
+            raise IndexError("RotaryEmbedding.Apply: position >= maxSeqLen (the reference panics)")
+        return out
+
+
+# ---- KVCache ----------------------------------------------------------------
+class KVCache:
+    F32, BF16 = 0, 1
+
+    def __init__(self, num_layers, dtype, max_len=0, num_kv_heads=0, head_dim=0):
+        if max_len > 0:
+            self.h = lib().ro_kvcache_new_sized(num_layers, max_len, num_kv_heads, head_dim, dtype)
+        else:
+            self.h = lib().ro_kvcache_new(num_layers, dtype)
+        if not self.h:
+            raise ValueError("NewKVCache: invalid arguments (the reference panics)")
+        self.dtype = dtype
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().ro_kvcache_free(C.c_void_p(self.h))
+
+    def append(self, layer, k, v):
+        k, v = f32(k), f32(v)
+        if k.shape != v.shape:
+            raise ValueError("KVCache.Append: K and V shape mismatch")
+        shape = (C.c_int * k.ndim)(*k.shape)
+        rc = lib().ro_kvcache_append(C.c_void_p(self.h), layer, _p(k), _p(v), shape, k.ndim)
+        if rc:
+            raise RuntimeError("KVCache.Append panic code %d" % rc)
+
+    def total_len(self, layer):
+        return lib().ro_kvcache_total_len(C.c_void_p(self.h), layer)
+
+    def view(self, layer, raw_bf16=False):
+        shape = (C.c_int * 8)()
+        rank = C.c_int(0)
+        n = lib().ro_kvcache_view_shape(C.c_void_p(self.h), layer, shape, C.byref(rank))
+        if n < 0:
+            raise IndexError("KVCache.View: layerIdx out of range")
+        if rank.value == 0:
+            return None, None
+        shp = tuple(shape[i] for i in range(rank.value))
+        if raw_bf16:
+            k, v = np.empty(n, np.uint16), np.empty(n, np.uint16)
+            lib().ro_kvcache_read_bf16(C.c_void_p(self.h), layer, _p(k), _p(v), C.c_int64(n))
+        else:
+            k, v = np.empty(n, np.float32), np.empty(n, np.float32)
+            lib().ro_kvcache_read_f32(C.c_void_p(self.h), layer, _p(k), _p(v), C.c_int64(n))
+        return k.reshape(shp), v.reshape(shp)
+
+    def reset(self):
+        lib().ro_kvcache_reset(C.c_void_p(self.h))
+
+
+class MLACache:
+    def __init__(self, num_layers, max_len, dC, dHR, round_bf16=False):
+        self.h = lib().ro_mlacache_new(num_layers, max_len, dC, dHR, int(round_bf16))
+        if not self.h:
+            raise ValueError("NewMLACache: invalid arguments (the reference panics)")
+        self.dC, self.dHR = dC, dHR
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().ro_mlacache_free(C.c_void_p(self.h))
+
+    def append(self, layer, new_c, new_kr):
+        c, r = f32(new_c), f32(new_kr)
+        rc = lib().ro_mlacache_append(C.c_void_p(self.h), layer, _p(c), C.c_int64(c.size), _p(r), C.c_int64(r.size),
+                                      c.shape[-2])
+        if rc:
+            raise RuntimeError("MLACache.Append panic code %d" % rc)
+
+    def total_len(self, layer):
+        return lib().ro_mlacache_total_len(C.c_void_p(self.h), layer)
+
+    def view(self, layer):
+        t = self.total_len(layer)
+        c, r = np.empty((1, t, self.dC), np.float32), np.empty((1, t, self.dHR), np.float32)
+        lib().ro_mlacache_read(C.c_void_p(self.h), layer, _p(c), _p(r))
+        return c, r
+
+    def reset(self):
+        lib().ro_mlacache_reset(C.c_void_p(self.h))
+
+
+# ---- decoder model ----------------------------------------------------------
+class Model:
+    def __init__(self, cfg: ModelCfg, flat_weights_bf16):
+        w = np.ascontiguousarray(flat_weights_bf16, dtype=np.uint16)
+        need = lib().ro_model_weight_count(C.byref(cfg))
+        if w.size != need:
+            raise ValueError("flat weight buffer has %d elements, model needs %d" % (w.size, need))
+        self.cfg = cfg
+        self.h = lib().ro_model_new(C.byref(cfg), _p(w))
+        if not self.h:
+            raise ValueError("NewTransformer: invalid config")
+        self._hooks = None
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().ro_model_free(C.c_void_p(self.h))
+
+    @staticmethod
+    def weight_count(cfg):
+        return int(lib().ro_model_weight_count(C.byref(cfg)))
+
+    def set_mode(self, mode, flags=0):
+        lib().ro_model_set_mode(C.c_void_p(self.h), mode, flags)
+
+    def set_hooks(self, mha=None, mla=None):
+        a = MHA_HOOK(mha) if mha else C.cast(None, MHA_HOOK)
+        b = MLA_HOOK(mla) if mla else C.cast(None, MLA_HOOK)
+        self._hooks = (a, b)  # keep alive
+        lib().ro_model_set_hooks(C.c_void_p(self.h), a, b, None)
+
+    def begin(self):
+        lib().ro_model_begin(C.c_void_p(self.h))
+
+    def forward(self, tokens):
+        t = np.ascontiguousarray(tokens, dtype=np.int32)
+        out = np.empty((t.size, self.cfg.vocab), np.float32)
+        rc = lib().ro_model_forward(C.c_void_p(self.h), _p(t), C.c_int(t.size), _p(out))
+        if rc:
+            raise RuntimeError("Transformer.Forward failed with code %d" % rc)
+        return out
+
+    def generate(self, prompt, max_new):
+        t = np.ascontiguousarray(prompt, dtype=np.int32)
+        out = np.empty(t.size + max_new, np.int32)
+        margins = np.empty(max_new, np.float32)
+        ties = C.c_int(0)
+        rc = lib().ro_model_generate(C.c_void_p(self.h), _p(t), C.c_int(t.size), C.c_int(max_new), _p(out), _p(margins),
+                                     C.byref(ties))
+        if rc:
+            raise RuntimeError("Transformer.Generate failed with code %d" % rc)
+        return out, margins, ties.value
+
+
+# ---- standalone attention ops ----------------------------------------------
+def _i32(a):
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _u16(a):
+    return np.ascontiguousarray(a, dtype=np.uint16)
+
+
+def mla_attend(ckv, kr, ctx, qc, qr, W_UK, W_UV, scale, causal=True, absorbed=False, threads=0):
+    """ckv [B,Tmax,dC] bf16 bits, kr [B,Tmax,dHR] bf16 bits, ctx [B], qc [B,S,H,Dh] f32, qr [B,S,H,dHR] f32."""
+    ckv, kr, qc, qr, ctx = _u16(ckv), _u16(kr), f32(qc), f32(qr), _i32(ctx)
+    W_UK, W_UV = _u16(W_UK), _u16(W_UV)
+    B, Tmax, dC = ckv.shape
+    _, S, H, Dh = qc.shape
+    dHR = kr.shape[2]
+    out = np.empty((B, S, H, Dh), np.float32)
+    fn = lib().ro_mla_attend_absorbed if absorbed else lib().ro_mla_attend_decompress
+    fn(B, S, H, Dh, dC, dHR, Tmax, _p(ctx), _p(ckv), _p(kr), _p(qc), _p(qr), _p(W_UK), _p(W_UV), C.c_float(scale),
+       int(causal), _p(out), threads)
+    return out
+
+
+def gqa_attend(K, V, ctx, q, scale, causal=True, threads=0, reference_cost=False, capacity=0):
+    """K,V [B,Tmax,Hkv,D] bf16 bits, ctx [B], q [B,S,H,D] f32 -> [B,S,H,D] f32."""
+    K, V, q, ctx = _u16(K), _u16(V), f32(q), _i32(ctx)
+    B, Tmax, Hkv, D = K.shape
+    _, S, H, _ = q.shape
+    out = np.empty((B, S, H, D), np.float32)
+    if reference_cost:
+        lib().ro_gqa_attend_reference_cost(B, S, H, Hkv, D, Tmax, max(capacity, Tmax), _p(ctx), _p(K), _p(V), _p(q),
+                                           C.c_float(scale), int(causal), _p(out), threads)
+    else:
+        lib().ro_gqa_attend(B, S, H, Hkv, D, Tmax, _p(ctx), _p(K), _p(V), _p(q), C.c_float(scale), int(causal), _p(out),
+                            threads)
+    return out
+
+
+def num_threads():
+    return int(lib().ro_num_threads())
