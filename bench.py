@@ -1,0 +1,289 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: per-step append + absorbed MLA flash-decode over a paged latent cache.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workload `mla_decode_b64_ctx32k` (default): DeepSeek-V2-like MLA shapes (128 heads, latent 512, rope key 64,
+nope/v 128), batch 64 per GPU, 32768 cached tokens per sequence, 64-token pages in a randomly permuted
+page table; one step = append one new token per sequence, then decode.  Synthetic seeded data.
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank owns its own batch of 64
+sequences and its own pool: sequences are independent, so there is no data-path collective (weak scaling).
+
+One JSON line is printed by rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (kind, batch per GPU, context, heads, head_dim, dC, dHR)
+    "mla_decode_b64_ctx32k": dict(kind="mla", B=64, ctx=32768, H=128, Dh=128, dC=512, dHR=64),
+    "mla_decode_b64_ctx4k": dict(kind="mla", B=64, ctx=4096, H=128, Dh=128, dC=512, dHR=64),
+}
+PAGE = 64
+
+
+def read_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index = index
+        self.samples = []
+        self.stop_flag = False
+        self.proc = None
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            for line in self.proc.stdout:
+                if self.stop_flag:
+                    break
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+        except Exception:
+            pass
+
+    def finish(self):
+        self.stop_flag = True
+        if self.proc:
+            self.proc.terminate()
+        sm = [int(s[0]) for s in self.samples if s[0].isdigit()]
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for s in self.samples for i in range(4) if s[2 + i].lower().startswith("active")})
+        return {"sm_mhz": int(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def dist_setup(n_gpus):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        return world, rank, local, dist
+    return 1, 0, 0, None
+
+
+def barrier(dist):
+    if dist is not None:
+        dist.barrier()
+
+
+def max_over_ranks(dist, x):
+    if dist is None:
+        return x
+    import torch
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+# --------------------------------------------------------------------------------------------------
+def run_mla(args, w, world, rank, local, dist):
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    from oracle import binding as orc  # used only for the bf16 rounding helper of inputs and the CPU baseline leg
+
+    B, ctx0, H, Dh, dC, dHR = w["B"], w["ctx"], w["H"], w["Dh"], w["dC"], w["dHR"]
+    total_steps = 2 * (args.steps + args.warmup) + args.steps + 8
+    pages_per = (ctx0 + total_steps + PAGE - 1) // PAGE + 1
+    dev = rb.Device(local)
+    rng = np.random.default_rng(7 + rank)
+    pool = rb.Pool(dev, L.POOL_MLA, 1, B * pages_per, PAGE, B, pages_per, dC=dC, dHR=dHR)
+    pool.set_tables(rng.permutation(B * pages_per).astype(np.int32).reshape(B, pages_per))
+    # fill the cache: one seeded N(0,1) block of `blk` tokens per sequence, appended ctx0/blk times from device memory
+    blk = min(ctx0, 2048)
+    src_c = orc.bf16_from_f32(rng.standard_normal((B * blk, dC), dtype=np.float32))
+    src_r = orc.bf16_from_f32(rng.standard_normal((B * blk, dHR), dtype=np.float32))
+    d_c, d_r = dev.upload(src_c), dev.upload(src_r)
+    for _ in range(ctx0 // blk):
+        pool.append(0, d_c, d_r, B, n_new=np.full(B, blk, np.int32))
+    dev.sync()
+    d_c.free(); d_r.free()
+    wuk = orc.bf16_from_f32((rng.standard_normal((dC, H * Dh), dtype=np.float32) * 0.02))
+    wuv = orc.bf16_from_f32((rng.standard_normal((dC, H * Dh), dtype=np.float32) * 0.02))
+    d_wuk, d_wuv = dev.upload(wuk), dev.upload(wuv)
+    scale = float(1.0 / np.sqrt(Dh + dHR))
+    # per-step inputs: new latent row + rope key per sequence, queries; resident copies and pinned host copies
+    new_c = rng.standard_normal((B, dC), dtype=np.float32)
+    new_r = rng.standard_normal((B, dHR), dtype=np.float32)
+    qc = rng.standard_normal((B, 1, H, Dh), dtype=np.float32)
+    qr = rng.standard_normal((B, 1, H, dHR), dtype=np.float32)
+    d_new_c, d_new_r = dev.upload(orc.bf16_from_f32(new_c)), dev.upload(orc.bf16_from_f32(new_r))
+    d_qc, d_qr = dev.upload(orc.bf16_from_f32(qc)), dev.upload(orc.bf16_from_f32(qr))
+    d_out = dev.alloc(B * H * Dh * 4, L.DTYPE_F32)
+    pins = [dev.pinned(a.shape, np.float32) for a in (new_c, new_r, qc, qr)]
+    for p_, a in zip(pins, (new_c, new_r, qc, qr)):
+        p_.array[...] = a
+    pin_out = dev.pinned((B, 1, H, Dh), np.float32)
+
+    def step_resident():
+        pool.append(0, d_new_c, d_new_r, B)
+        pool.decode(0, B, d_qc, d_out, H, Dh, scale, q_rope=d_qr, w_uk=d_wuk, w_uv=d_wuv)
+
+    def step_e2e():
+        pool.append(0, pins[0].array, pins[1].array, B)
+        pool.decode(0, B, pins[2].array, pin_out.array, H, Dh, scale, q_rope=pins[3].array, w_uk=d_wuk, w_uv=d_wuv)
+
+    e0, e1 = dev.event(), dev.event()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        dev.sync()
+        barrier(dist)
+        n0 = dev.launch_count()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        dev.sync()
+        ms = e0.elapsed_ms(e1)
+        barrier(dist)
+        return max_over_ranks(dist, ms), dev.launch_count() - n0
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ms_res, launches = timed(step_resident, args.steps, args.warmup)
+    clocks = sampler.finish() if rank == 0 else None
+    ms_e2e, _ = timed(step_e2e, args.steps, args.warmup)
+    # dominant kernel: the split-KV decode kernel, timed alone with CUDA events around its launch
+    kms, ctx_sum = [], []
+    for _ in range(args.steps):
+        step_resident()
+        kms.append(pool.last_kernel_ms())
+        ctx_sum.append(sum(pool.seq_len(0, b) for b in range(B)))
+    assert pool.status() == 0, "device status word is set"
+    kernel_ms = float(np.mean(kms))
+    alg_bytes = float(np.mean(ctx_sum)) * (dC + dHR) * 2
+    peak, peak_src = read_peaks()
+    achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+    tokens = B * world
+    value = tokens * args.steps / (ms_res * 1e-3)
+    e2e = tokens * args.steps / (ms_e2e * 1e-3)
+    h2d = sum(a.nbytes for a in (new_c, new_r, qc, qr))
+    d2h = pin_out.array.nbytes
+    line = {
+        "metric": "mla_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "batch_per_gpu": B, "context": ctx0, "heads": H, "latent": dC, "rope": dHR,
+                   "page_tokens": PAGE, "page_table": "random permutation", "l2": "inputs (%.2f GB of cache rows per GPU) are larger than L2"
+                   % (B * ctx0 * (dC + dHR) * 2 / 1e9)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "peak_source": peak_src, "kernel": "mla split-KV decode", "kernel_ms": kernel_ms,
+                     "algorithmic_bytes_per_launch": alg_bytes, "frac_of_nominal_8TBs": achieved / 8000.0},
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches, "clocks": clocks,
+        "kv_read_gbs_whole_step": alg_bytes * world / (ms_res / args.steps * 1e-3) / 1e9,
+    }
+    if rank == 0 and world == 1:
+        line["cpu_baseline"] = cpu_baseline_mla(w, sample_T=512, threads=1)
+    for b in (d_new_c, d_new_r, d_qc, d_qr, d_out, d_wuk, d_wuv):
+        b.free()
+    pool.destroy()
+    dev.close()
+    return line
+
+
+def cpu_baseline_mla(w, sample_T, threads):
+    """Times the oracle's restatement of the reference's own path (decompress every latent, then attend;
+    mla.go:323-377) on `threads` host threads, one sequence per thread, at a reduced context, and scales the time
+    linearly in context length to the workload's (the work is linear in T)."""
+    from oracle import binding as orc
+    H, Dh, dC, dHR, ctx = w["H"], w["Dh"], w["dC"], w["dHR"], w["ctx"]
+    rng = np.random.default_rng(0)
+    nb = threads
+    ckv = orc.bf16_from_f32(rng.standard_normal((nb, sample_T, dC), dtype=np.float32))
+    kr = orc.bf16_from_f32(rng.standard_normal((nb, sample_T, dHR), dtype=np.float32))
+    qc = rng.standard_normal((nb, 1, H, Dh), dtype=np.float32)
+    qr = rng.standard_normal((nb, 1, H, dHR), dtype=np.float32)
+    wuk = orc.bf16_from_f32(rng.standard_normal((dC, H * Dh), dtype=np.float32) * 0.02)
+    wuv = orc.bf16_from_f32(rng.standard_normal((dC, H * Dh), dtype=np.float32) * 0.02)
+    t0 = time.time()
+    orc.mla_attend(ckv, kr, [sample_T] * nb, qc, qr, wuk, wuv, 0.0722, threads=threads)
+    dt = time.time() - t0
+    return {"value": nb / (dt * (ctx / sample_T)), "unit": "tokens/s",
+            "cores": threads, "kind": "port",
+            "sample": "%d sequence(s) x 1 decode step at context %d (%.1f s), time scaled x%d to context %d; reference-style "
+                      "decompress-then-attend in float32" % (nb, sample_T, dt, ctx // sample_T, ctx)}
+
+
+def run_reference(args, w, world, rank):
+    """--impl reference: the reference's own CPU algorithm (oracle restatement; the Go sources cannot be built
+    here) on all host threads, on the same workload definition."""
+    from oracle import binding as orc
+    if rank != 0:
+        return None
+    threads = orc.num_threads()
+    vals = []
+    for _ in range(args.warmup + args.steps):
+        vals.append(cpu_baseline_mla(w, sample_T=256, threads=threads))
+    vals = vals[args.warmup:]
+    v = float(np.mean([x["value"] for x in vals]))
+    cb = dict(vals[-1])
+    cb["value"] = v
+    B = w["B"]
+    return {"impl": "reference", "metric": "mla_decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": B * world / v * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "batch_per_gpu": B, "context": w["ctx"]},
+            "cpu_baseline": cb, "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="mla_decode_b64_ctx32k", choices=sorted(WORKLOADS))
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        rank = int(os.environ.get("RANK", "0"))
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        line = run_reference(args, w, world, rank)
+        if line is not None:
+            print(json.dumps(line))
+        return
+    world, rank, local, dist = dist_setup(args.gpus)
+    line = run_mla(args, w, world, rank, local, dist)
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

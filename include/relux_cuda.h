@@ -1,0 +1,229 @@
+/*
+ * relux_cuda.h -- C ABI of librelux_cuda.so, the B200 (sm_100a) KV-cache and cached-attention
+ * path for the pure-Go framework relux.
+ *
+ * Design rules of this surface (so that Go can bind it with purego, without cgo):
+ *   - every function is extern "C", returns an int32 status (0 = ok, negative = error), takes
+ *     only integers, floats, pointers, or a pointer to a plain-old-data argument struct;
+ *   - no callbacks, no struct by value, no C++ exceptions cross the boundary;
+ *   - every call selects the handle's CUDA device itself (goroutines migrate between OS threads);
+ *   - calls on one device handle are serialised internally; distinct handles are independent;
+ *   - there is no CPU fallback: when a GPU cannot do the work the call fails with a status.
+ *
+ * "Reference" below is the relux source tree; paths are relative to its root.
+ */
+#ifndef RELUX_CUDA_H_
+#define RELUX_CUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RELUX_CUDA_ABI_VERSION 1
+
+/* ---- status codes ------------------------------------------------------------------------ */
+#define RELUX_OK 0
+#define RELUX_ERR_INVALID_ARG (-1)    /* nil pointer, bad enum, mismatched dims                     */
+#define RELUX_ERR_CUDA (-2)           /* a CUDA runtime/driver call failed; see relux_cuda_last_error */
+#define RELUX_ERR_OUT_OF_MEMORY (-3)  /* device allocation failed                                  */
+#define RELUX_ERR_POOL_EXHAUSTED (-4) /* no free page / sequence slot                              */
+#define RELUX_ERR_OVERFLOW (-5)       /* append past a sequence's page capacity (the reference panics:
+                                         internal/transformer/kvcache.go:282-285, mla_cache.go:164-167) */
+#define RELUX_ERR_BAD_PAGE (-6)       /* a page table holds an id outside the pool (found on device) */
+#define RELUX_ERR_TIMEOUT (-7)        /* a bounded device-side wait ran out                         */
+#define RELUX_ERR_BAD_HANDLE (-8)
+#define RELUX_ERR_UNSUPPORTED (-9)    /* shape outside what the kernels implement                   */
+#define RELUX_ERR_NO_DEVICE (-10)     /* no CUDA device / library built without a usable GPU        */
+
+/* ---- enums ------------------------------------------------------------------------------- */
+#define RELUX_DTYPE_F32 0
+#define RELUX_DTYPE_BF16 1
+#define RELUX_MEM_HOST 0
+#define RELUX_MEM_DEVICE 1
+/* Activation layouts.  TOKEN_MAJOR: [seq][token][head][dim].  HEAD_MAJOR: [seq][head][token][dim],
+ * the layout of the reference's tensors after rearrangeBSNH (internal/transformer/mha.go:789-803). */
+#define RELUX_LAYOUT_TOKEN_MAJOR 0
+#define RELUX_LAYOUT_HEAD_MAJOR 1
+#define RELUX_POOL_MLA 0
+#define RELUX_POOL_GQA 1
+/* Attention arithmetic.
+ * FAST: bf16 tensor-core contractions, online softmax with exp2, split-KV + merge.
+ * REFERENCE: float32 CUDA-core arithmetic in the reference's own operation order
+ *   (k-ascending unfused dot products, full-row softmax with the fastexp32 bit trick of
+ *   internal/transformer/mha.go:823-861, decompress-then-attend for MLA as mla.go:323-377);
+ *   meant for small models where token-id identity with the reference matters. */
+#define RELUX_ATTN_FAST 0
+#define RELUX_ATTN_REFERENCE 1
+
+typedef void* relux_device_t;
+typedef void* relux_pool_t;
+typedef void* relux_event_t;
+
+/* ---- runtime ------------------------------------------------------------------------------
+ * Replaces the backend discovery of internal/compute/factory.go:32-85 (NewComputeBackend) and the
+ * Available()/DeviceInfo() methods of internal/compute/interface.go:13-41 for this path. */
+int32_t relux_cuda_version(void);
+int32_t relux_cuda_device_count(int32_t* count);
+int32_t relux_cuda_device_open(int32_t device_index, relux_device_t* out);
+int32_t relux_cuda_device_close(relux_device_t dev);
+int32_t relux_cuda_sync(relux_device_t dev);
+/* Copies the calling thread's last error message (NUL terminated) into buf. */
+int32_t relux_cuda_last_error(char* buf, int32_t buf_len);
+/* Name, SM count, memory of the device (DeviceInfo() equivalent, interface.go:37-40). */
+int32_t relux_cuda_device_info(relux_device_t dev, char* name, int32_t name_len, int32_t* sm_count,
+                               int64_t* total_mem_bytes);
+/* Number of kernels this library has launched on the handle since it was opened. */
+int32_t relux_cuda_launch_count(relux_device_t dev, int64_t* count);
+/* The CUDA stream (cudaStream_t) all work of this handle is issued on. */
+int32_t relux_cuda_stream(relux_device_t dev, void** stream);
+
+/* ---- device memory ------------------------------------------------------------------------
+ * Replaces internal/alloc/alloc.go:95-117,168-188,375-390 (alloc.Float32 / alloc.Uint16 / alloc.Free)
+ * for buffers that must live on the GPU (weights, activations handed over as device pointers). */
+int32_t relux_cuda_dev_alloc(relux_device_t dev, size_t bytes, void** dptr);
+int32_t relux_cuda_dev_free(relux_device_t dev, void* dptr);
+int32_t relux_cuda_host_alloc(relux_device_t dev, size_t bytes, void** hptr); /* pinned */
+int32_t relux_cuda_host_free(relux_device_t dev, void* hptr);
+/* Asynchronous on the handle's stream when the host side is pinned; ordered with kernel calls. */
+int32_t relux_cuda_h2d(relux_device_t dev, void* dst_dev, const void* src_host, size_t bytes);
+int32_t relux_cuda_d2h(relux_device_t dev, void* dst_host, const void* src_dev, size_t bytes);
+int32_t relux_cuda_memset(relux_device_t dev, void* dst_dev, int32_t value, size_t bytes);
+
+/* ---- timing helpers (CUDA events on the handle's stream) -------------------------------- */
+int32_t relux_cuda_event_create(relux_device_t dev, relux_event_t* ev);
+int32_t relux_cuda_event_record(relux_device_t dev, relux_event_t ev);
+int32_t relux_cuda_event_elapsed_ms(relux_device_t dev, relux_event_t start, relux_event_t stop, float* ms);
+int32_t relux_cuda_event_destroy(relux_device_t dev, relux_event_t ev);
+/* Overwrites a scratch buffer larger than L2 so the next kernel starts cold. */
+int32_t relux_cuda_flush_l2(relux_device_t dev);
+
+/* ---- paged KV pools -----------------------------------------------------------------------
+ * A pool replaces, on the device, both the cache objects and their backing arenas:
+ *   GQA: KVCache / NewKVCacheSized   internal/transformer/kvcache.go:34-49, 66-93
+ *   MLA: MLACache / NewMLACache      internal/transformer/mla_cache.go:21-59
+ *   storage: internal/alloc/alloc.go:95-117,168-188 (64 MiB power-of-two freelist buckets)
+ * Storage is bf16.  One pool serves num_layers layers and up to max_seqs sequences; a sequence
+ * owns a page table of up to max_pages_per_seq physical page ids shared by all layers, and a
+ * length per layer (the reference keeps one cursor per layer: kvcache.go:44-49).
+ * MLA page  : [page_tokens][dC + dHR] (latent row followed by the rotated shared key).
+ * GQA pages : K and V each [num_kv_heads][page_tokens][head_dim]. */
+typedef struct relux_pool_params {
+  int32_t kind;              /* RELUX_POOL_MLA | RELUX_POOL_GQA */
+  int32_t num_layers;
+  int32_t num_pages;         /* physical pages per layer */
+  int32_t page_tokens;       /* tokens per page (64 enables the TMA/tensor-core kernels) */
+  int32_t max_seqs;
+  int32_t max_pages_per_seq;
+  int32_t mla_dc;            /* MLA latent width (kv_lora_rank) */
+  int32_t mla_dhr;           /* MLA decoupled RoPE key width */
+  int32_t gqa_num_kv_heads;
+  int32_t gqa_head_dim;
+  int32_t reserved[6];       /* must be zero */
+} relux_pool_params;
+
+int32_t relux_pool_create(relux_device_t dev, const relux_pool_params* params, relux_pool_t* out);
+int32_t relux_pool_destroy(relux_pool_t pool);
+/* KVCache.Reset / MLACache.Reset (kvcache.go:174-202, mla_cache.go:118-133): every sequence length
+ * becomes 0 and library-allocated sequences are released.  Page contents are left as they are. */
+int32_t relux_pool_reset(relux_pool_t pool);
+/* Caller-owned page tables: table is a host array [n_seqs][stride] of physical page ids, ctx_len a host
+ * array [n_seqs] applied to every layer (NULL = 0).  Sequences 0..n_seqs-1 become live.  Ids are
+ * validated on the host; a bad id is RELUX_ERR_BAD_PAGE. */
+int32_t relux_pool_set_tables(relux_pool_t pool, const int32_t* table, int32_t n_seqs, int32_t stride,
+                              const int32_t* ctx_len);
+/* Library-owned page tables: reserves pages for max_tokens tokens and returns a sequence id. */
+int32_t relux_seq_alloc(relux_pool_t pool, int32_t max_tokens, int32_t* seq_id);
+int32_t relux_seq_free(relux_pool_t pool, int32_t seq_id);
+/* KVCache.TotalLen / MLACache.TotalLen (kvcache.go:383-388, mla_cache.go:236-241). */
+int32_t relux_seq_len(relux_pool_t pool, int32_t layer, int32_t seq_id, int32_t* len);
+/* Sets the length of n_seqs sequences on one layer (layer < 0: on every layer).  Used to commit the accepted
+ * prefix after a speculative verify, or to roll a sequence back.  seq_ids NULL = 0..n_seqs-1. */
+int32_t relux_seq_set_len(relux_pool_t pool, int32_t layer, int32_t n_seqs, const int32_t* seq_ids,
+                          const int32_t* new_len);
+/* Reads the device status word (0, or the first RELUX_ERR_BAD_PAGE / RELUX_ERR_TIMEOUT a kernel recorded)
+ * and clears it.  Synchronises the stream. */
+int32_t relux_pool_status(relux_pool_t pool, int32_t* status);
+/* KVCache.View / MLACache.View equivalent used by the bit-exactness tests (kvcache.go:363-380,
+ * mla_cache.go:222-233): copies n_tokens logical rows starting at token tok0 of one sequence to host memory
+ * as bf16 bit patterns.  MLA: dst_a = latent rows [n][dC], dst_b = rope-key rows [n][dHR].
+ * GQA: dst_a = K rows [n][Hkv][D], dst_b = V rows.  Either destination may be NULL.  Rows past the
+ * sequence length are returned as stored (unspecified content). */
+int32_t relux_pool_read_rows(relux_pool_t pool, int32_t layer, int32_t seq_id, int32_t tok0, int32_t n_tokens,
+                             void* dst_a, void* dst_b);
+
+/* ---- append -------------------------------------------------------------------------------
+ * MLACache.Append (mla_cache.go:152-182) fed by MLA.forwardCached step 4 (mla.go:309-312):
+ * the latent c^KV and the already rotated shared key k^R of n_new[i] tokens per sequence.
+ * KVCache.Append + copyInto (kvcache.go:240-291, 407-438) fed by MHA.forwardCached step 5
+ * (mha.go:283-287): post-RoPE K and V.  float32 inputs are rounded with the reference's own
+ * rule BF16FromF32 (dtype_convert.go:15-24); bf16 inputs are copied bit for bit.
+ * Rows land at logical positions len .. len+n_new-1 of each sequence, i.e. the textbook per-head
+ * placement (the reference's chunk-linear stream for Hkv > 1 is not reproduced). */
+typedef struct relux_append_args {
+  int32_t layer;
+  int32_t n_seqs;
+  const int32_t* seq_ids;   /* host [n_seqs]; NULL = 0..n_seqs-1 */
+  const int32_t* n_new;     /* host [n_seqs]; NULL = 1 token each */
+  const void* a;            /* MLA: c_kv [sum n_new][dC]     GQA: K */
+  const void* b;            /* MLA: k_rope [sum n_new][dHR]  GQA: V */
+  int32_t dtype;            /* RELUX_DTYPE_* of a and b */
+  int32_t mem;              /* RELUX_MEM_* of a and b */
+  int32_t layout;           /* GQA only: TOKEN_MAJOR [tok][Hkv][D] or HEAD_MAJOR [Hkv][n_new_i][D] per sequence */
+  int32_t advance;          /* 1: lengths grow by n_new.  0: rows are written past the cursor, lengths unchanged
+                               (draft rows of a speculative verify; commit with relux_seq_set_len) */
+  int32_t reserved[4];
+} relux_append_args;
+int32_t relux_mla_append(relux_pool_t pool, const relux_append_args* args);
+int32_t relux_gqa_append(relux_pool_t pool, const relux_append_args* args);
+
+/* ---- cached attention ---------------------------------------------------------------------
+ * Each sequence attends over its first (len + extra_tokens) cached rows; its q_tokens query rows are the
+ * LAST q_tokens of those rows.  causal != 0: query row i sees rows j <= T - q_tokens + i (causal inside
+ * the new tokens); causal == 0: every query row sees all T rows (what the reference does for a
+ * multi-token cached call, mha.go:340, mla.go:368).
+ *
+ * relux_mla_decode replaces MLA.forwardCached steps 5-6 (mla.go:317-377) in absorbed form:
+ *   q~ = [W_UK_h q_nope | q_rope], scores over the latent rows, O_lat = P C, out = W_UV_h^T O_lat,
+ * with w_uk / w_uv the reference's bf16 weight matrices [dC][H*head_dim] (mla.go:44-45) on the device.
+ * relux_gqa_decode replaces MHA.forwardCached steps 6-8 (mha.go:292-348).  q_tokens > 1 with causal != 0
+ * and extra_tokens = q_tokens is the verify step of SpeculativeDecoder.verifyPhase (speculative.go:189-207). */
+typedef struct relux_attn_args {
+  int32_t layer;
+  int32_t n_seqs;
+  const int32_t* seq_ids;   /* host [n_seqs]; NULL = 0..n_seqs-1 */
+  int32_t q_tokens;
+  int32_t extra_tokens;
+  int32_t causal;
+  int32_t num_heads;
+  int32_t head_dim;         /* MLA: content (nope) and value head dim; GQA: must equal the pool's */
+  float scale;              /* MLA 1/sqrt(head_dim + dHR) (mla.go:341), GQA 1/sqrt(head_dim) (mha.go:319) */
+  const void* q;            /* MLA: q_nope [n][S][H][head_dim]; GQA: q [n][S][H][head_dim] (post-RoPE) */
+  const void* q_rope;       /* MLA: [n][S][H][dHR] (post-RoPE); GQA: NULL */
+  int32_t q_dtype, q_mem, q_layout;
+  const void* w_uk;         /* MLA: device bf16 [dC][H*head_dim]; GQA: NULL */
+  const void* w_uv;
+  void* out;                /* [n][S][H][head_dim] */
+  int32_t out_dtype, out_mem, out_layout;
+  int32_t mode;             /* RELUX_ATTN_FAST | RELUX_ATTN_REFERENCE */
+  int32_t reserved[5];
+} relux_attn_args;
+int32_t relux_mla_decode(relux_pool_t pool, const relux_attn_args* args);
+int32_t relux_gqa_decode(relux_pool_t pool, const relux_attn_args* args);
+
+/* Speculative verify in one call (speculative.go:189-207 -> mha.go:245-369 with seqQ = k+1): writes the
+ * q_tokens draft K/V rows of every sequence past its cursor (append with advance = 0), then attends with
+ * extra_tokens = q_tokens.  Commit the accepted prefix with relux_seq_set_len afterwards. */
+int32_t relux_gqa_verify(relux_pool_t pool, const relux_attn_args* attn, const relux_append_args* draft_kv);
+int32_t relux_mla_verify(relux_pool_t pool, const relux_attn_args* attn, const relux_append_args* draft_kv);
+
+/* Device-time of the dominant attention kernel of the most recent relux_*_decode / verify call on this
+ * pool, measured with CUDA events around that one launch.  Synchronises the stream. */
+int32_t relux_pool_last_kernel_ms(relux_pool_t pool, float* ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RELUX_CUDA_H_ */

@@ -342,5 +342,18 @@ def gqa_attend(K, V, ctx, q, scale, causal=True, threads=0, reference_cost=False
     return out
 
 
+def set_exact_exp(on):
+    """Test-only: softmaxRows with libm exp instead of fastexp32 (see relux_oracle.cpp)."""
+    lib().ro_set_exact_exp(int(bool(on)))
+
+
+class exact_exp:
+    def __enter__(self):
+        set_exact_exp(True)
+
+    def __exit__(self, *a):
+        set_exact_exp(False)
+
+
 def num_threads():
     return int(lib().ro_num_threads())

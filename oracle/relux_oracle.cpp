@@ -136,7 +136,29 @@ static inline float fastexp32_go(float x) {
 }
 RO_API float ro_fastexp32(float x) { return fastexp32_go(x); }
 
+// Test-only switch: 1 replaces fastexp32 by libm exp (no -20 cut-off) inside softmaxRows, giving the
+// exact softmax.  It separates "the kernel's indexing/masking is right" from "the reference's 3 %
+// exp approximation", which dominates the difference at short contexts.  Default 0 = reference.
+static int g_exact_exp = 0;
+RO_API void ro_set_exact_exp(int on) { g_exact_exp = on; }
+
 static void softmax_rows(float* m, int rows, int cols) {
+  if (g_exact_exp) {
+    for (int r = 0; r < rows; r++) {
+      float* row = m + (size_t)r * cols;
+      float maxV = row[0];
+      for (int j = 1; j < cols; j++)
+        if (row[j] > maxV) maxV = row[j];
+      double sum = 0.0;
+      for (int j = 0; j < cols; j++) {
+        double e = std::exp((double)row[j] - (double)maxV);
+        row[j] = (float)e;
+        sum += e;
+      }
+      for (int j = 0; j < cols; j++) row[j] = (float)((double)row[j] / sum);
+    }
+    return;
+  }
   for (int r = 0; r < rows; r++) {
     float* row = m + (size_t)r * cols;
     float maxV = row[0];

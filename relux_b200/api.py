@@ -1,0 +1,398 @@
+"""Host-side mirror of relux's KV-cache and cached-attention interface over librelux_cuda.so.
+
+Two levels:
+
+* `Pool` -- the batched, paged interface the CUDA library is built around (many sequences, page tables,
+  append / decode / verify on host or device arrays).
+* `KVCache`, `MLACache` -- single-sequence objects with the reference's own method set
+  (Append / View / TotalLen / Reset / DType; internal/transformer/kvcache.go:169-388,
+  internal/transformer/mla_cache.go:118-241) plus `attend`, the replacement for the attention loops of
+  MHA.forwardCached (mha.go:292-348) and MLA.forwardCached (mla.go:317-377).  Misuse that panics in the
+  reference raises here with the same wording.
+
+Arrays are numpy; bf16 travels as uint16 bit patterns.  Nothing here computes on the CPU: every
+operation is a call into the shared library.
+"""
+import ctypes as C
+
+import numpy as np
+
+from . import lib as L
+
+
+def _ptr(a):
+    if a is None:
+        return None
+    if isinstance(a, DeviceBuffer):
+        return a.ptr
+    if isinstance(a, int):
+        return a
+    return a.ctypes.data
+
+
+def _mem(a):
+    return L.MEM_DEVICE if isinstance(a, (DeviceBuffer, int)) else L.MEM_HOST
+
+
+def _dtype_flag(a, explicit=None):
+    if explicit is not None:
+        return explicit
+    if isinstance(a, DeviceBuffer):
+        return a.dtype_flag
+    if a.dtype == np.float32:
+        return L.DTYPE_F32
+    if a.dtype == np.uint16:
+        return L.DTYPE_BF16
+    raise TypeError("arrays must be float32 or uint16 (bf16 bits), got %s" % a.dtype)
+
+
+class Device:
+    """One GPU.  Mirrors compute.NewComputeBackend's role for this path (internal/compute/factory.go:32-85):
+    it either opens a usable sm_100 device or raises -- there is no silent native fallback."""
+
+    def __init__(self, index=0):
+        self.lib = L.load()
+        h = C.c_void_p()
+        L.check(self.lib.relux_cuda_device_open(index, C.byref(h)))
+        self.h = h
+        self.index = index
+
+    def close(self):
+        if self.h:
+            L.check(self.lib.relux_cuda_device_close(self.h))
+            self.h = None
+
+    def sync(self):
+        L.check(self.lib.relux_cuda_sync(self.h))
+
+    def info(self):
+        name = C.create_string_buffer(256)
+        sm = C.c_int32()
+        mem = C.c_int64()
+        L.check(self.lib.relux_cuda_device_info(self.h, name, 256, C.byref(sm), C.byref(mem)))
+        return {"name": name.value.decode(), "sm_count": sm.value, "total_mem": mem.value}
+
+    def launch_count(self):
+        n = C.c_int64()
+        L.check(self.lib.relux_cuda_launch_count(self.h, C.byref(n)))
+        return n.value
+
+    def alloc(self, nbytes, dtype_flag=L.DTYPE_BF16):
+        return DeviceBuffer(self, nbytes, dtype_flag)
+
+    def upload(self, arr):
+        arr = np.ascontiguousarray(arr)
+        b = DeviceBuffer(self, arr.nbytes, L.DTYPE_F32 if arr.dtype == np.float32 else L.DTYPE_BF16)
+        b.upload(arr)
+        return b
+
+    def pinned(self, shape, dtype):
+        """A numpy array over pinned host memory (freed when the returned holder is closed)."""
+        return PinnedArray(self, shape, dtype)
+
+    def flush_l2(self):
+        L.check(self.lib.relux_cuda_flush_l2(self.h))
+
+    def event(self):
+        return Event(self)
+
+
+class Event:
+    def __init__(self, dev):
+        self.dev = dev
+        self.h = C.c_void_p()
+        L.check(dev.lib.relux_cuda_event_create(dev.h, C.byref(self.h)))
+
+    def record(self):
+        L.check(self.dev.lib.relux_cuda_event_record(self.dev.h, self.h))
+
+    def elapsed_ms(self, later):
+        ms = C.c_float()
+        L.check(self.dev.lib.relux_cuda_event_elapsed_ms(self.dev.h, self.h, later.h, C.byref(ms)))
+        return ms.value
+
+    def close(self):
+        if self.h:
+            self.dev.lib.relux_cuda_event_destroy(self.dev.h, self.h)
+            self.h = None
+
+
+class DeviceBuffer:
+    def __init__(self, dev, nbytes, dtype_flag=L.DTYPE_BF16):
+        self.dev = dev
+        self.nbytes = int(nbytes)
+        self.dtype_flag = dtype_flag
+        p = C.c_void_p()
+        L.check(dev.lib.relux_cuda_dev_alloc(dev.h, self.nbytes, C.byref(p)))
+        self.ptr = p.value or 0
+
+    def upload(self, arr, offset=0):
+        arr = np.ascontiguousarray(arr)
+        assert offset + arr.nbytes <= self.nbytes
+        L.check(self.dev.lib.relux_cuda_h2d(self.dev.h, self.ptr + offset, arr.ctypes.data, arr.nbytes))
+        self.dev.sync()  # the source may be pageable and die after this call
+
+    def download(self, shape, dtype, offset=0):
+        out = np.empty(shape, dtype)
+        assert offset + out.nbytes <= self.nbytes
+        L.check(self.dev.lib.relux_cuda_d2h(self.dev.h, out.ctypes.data, self.ptr + offset, out.nbytes))
+        return out
+
+    def zero(self):
+        L.check(self.dev.lib.relux_cuda_memset(self.dev.h, self.ptr, 0, self.nbytes))
+
+    def free(self):
+        if self.ptr:
+            L.check(self.dev.lib.relux_cuda_dev_free(self.dev.h, self.ptr))
+            self.ptr = 0
+
+
+class PinnedArray:
+    def __init__(self, dev, shape, dtype):
+        self.dev = dev
+        n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        p = C.c_void_p()
+        L.check(dev.lib.relux_cuda_host_alloc(dev.h, n, C.byref(p)))
+        self.ptr = p.value
+        buf = (C.c_char * n).from_address(self.ptr)
+        self.array = np.frombuffer(buf, dtype=dtype).reshape(shape)
+
+    def close(self):
+        if self.ptr:
+            self.array = None
+            L.check(self.dev.lib.relux_cuda_host_free(self.dev.h, self.ptr))
+            self.ptr = None
+
+
+class Pool:
+    """Paged bf16 KV pool on one device (see relux_pool_create in include/relux_cuda.h)."""
+
+    def __init__(self, dev, kind, num_layers, num_pages, page_tokens=64, max_seqs=1, max_pages_per_seq=None, dC=0, dHR=0,
+                 num_kv_heads=0, head_dim=0):
+        self.dev = dev
+        self.lib = dev.lib
+        if max_pages_per_seq is None:
+            max_pages_per_seq = num_pages
+        prm = L.PoolParams(kind=kind, num_layers=num_layers, num_pages=num_pages, page_tokens=page_tokens, max_seqs=max_seqs,
+                           max_pages_per_seq=max_pages_per_seq, mla_dc=dC, mla_dhr=dHR, gqa_num_kv_heads=num_kv_heads,
+                           gqa_head_dim=head_dim)
+        self.prm = prm
+        self.kind = kind
+        h = C.c_void_p()
+        L.check(self.lib.relux_pool_create(dev.h, C.byref(prm), C.byref(h)))
+        self.h = h
+        self._keep = []
+
+    def destroy(self):
+        if self.h:
+            L.check(self.lib.relux_pool_destroy(self.h))
+            self.h = None
+
+    def reset(self):
+        L.check(self.lib.relux_pool_reset(self.h))
+
+    def set_tables(self, table, ctx_len=None):
+        table = np.ascontiguousarray(table, dtype=np.int32)
+        cl = None if ctx_len is None else np.ascontiguousarray(ctx_len, dtype=np.int32)
+        L.check(self.lib.relux_pool_set_tables(self.h, table.ctypes.data, table.shape[0], table.shape[1], _ptr(cl)))
+
+    def seq_alloc(self, max_tokens):
+        s = C.c_int32()
+        L.check(self.lib.relux_seq_alloc(self.h, max_tokens, C.byref(s)))
+        return s.value
+
+    def seq_free(self, seq):
+        L.check(self.lib.relux_seq_free(self.h, seq))
+
+    def seq_len(self, layer, seq):
+        n = C.c_int32()
+        L.check(self.lib.relux_seq_len(self.h, layer, seq, C.byref(n)))
+        return n.value
+
+    def set_len(self, layer, new_len, seq_ids=None):
+        nl = np.ascontiguousarray(new_len, dtype=np.int32)
+        ids = None if seq_ids is None else np.ascontiguousarray(seq_ids, dtype=np.int32)
+        L.check(self.lib.relux_seq_set_len(self.h, layer, nl.size, _ptr(ids), nl.ctypes.data))
+
+    def status(self):
+        s = C.c_int32()
+        L.check(self.lib.relux_pool_status(self.h, C.byref(s)))
+        return s.value
+
+    def read_rows(self, layer, seq, tok0, n):
+        p = self.prm
+        if self.kind == L.POOL_MLA:
+            a, b = np.empty((n, p.mla_dc), np.uint16), np.empty((n, p.mla_dhr), np.uint16)
+        else:
+            a = np.empty((n, p.gqa_num_kv_heads, p.gqa_head_dim), np.uint16)
+            b = np.empty_like(a)
+        L.check(self.lib.relux_pool_read_rows(self.h, layer, seq, tok0, n, a.ctypes.data, b.ctypes.data))
+        return a, b
+
+    def _append_args(self, layer, a, b, n_seqs, seq_ids, n_new, layout, advance, dtype):
+        ids = None if seq_ids is None else np.ascontiguousarray(seq_ids, dtype=np.int32)
+        nn = None if n_new is None else np.ascontiguousarray(n_new, dtype=np.int32)
+        self._keep = [ids, nn, a, b]
+        return L.AppendArgs(layer=layer, n_seqs=n_seqs, seq_ids=_ptr(ids), n_new=_ptr(nn), a=_ptr(a), b=_ptr(b),
+                            dtype=_dtype_flag(a, dtype), mem=_mem(a), layout=layout, advance=int(advance))
+
+    def append(self, layer, a, b, n_seqs, seq_ids=None, n_new=None, layout=L.LAYOUT_TOKEN_MAJOR, advance=True, dtype=None):
+        """MLA: a = c_kv [rows, dC], b = k_rope [rows, dHR].  GQA: a = K, b = V."""
+        args = self._append_args(layer, a, b, n_seqs, seq_ids, n_new, layout, advance, dtype)
+        fn = self.lib.relux_mla_append if self.kind == L.POOL_MLA else self.lib.relux_gqa_append
+        L.check(fn(self.h, C.byref(args)))
+
+    def _attn_args(self, layer, n_seqs, q, q_rope, out, num_heads, head_dim, scale, q_tokens, extra_tokens, causal, mode,
+                   w_uk, w_uv, seq_ids, q_layout, out_layout, q_dtype, out_dtype):
+        ids = None if seq_ids is None else np.ascontiguousarray(seq_ids, dtype=np.int32)
+        self._keep2 = [ids, q, q_rope, out]
+        return L.AttnArgs(layer=layer, n_seqs=n_seqs, seq_ids=_ptr(ids), q_tokens=q_tokens, extra_tokens=extra_tokens,
+                          causal=int(causal), num_heads=num_heads, head_dim=head_dim, scale=scale, q=_ptr(q), q_rope=_ptr(q_rope),
+                          q_dtype=_dtype_flag(q, q_dtype), q_mem=_mem(q), q_layout=q_layout, w_uk=_ptr(w_uk), w_uv=_ptr(w_uv),
+                          out=_ptr(out), out_dtype=_dtype_flag(out, out_dtype), out_mem=_mem(out), out_layout=out_layout, mode=mode)
+
+    def decode(self, layer, n_seqs, q, out, num_heads, head_dim, scale, q_rope=None, w_uk=None, w_uv=None, q_tokens=1,
+               extra_tokens=0, causal=True, mode=L.ATTN_FAST, seq_ids=None, q_layout=L.LAYOUT_TOKEN_MAJOR,
+               out_layout=L.LAYOUT_TOKEN_MAJOR, q_dtype=None, out_dtype=None):
+        args = self._attn_args(layer, n_seqs, q, q_rope, out, num_heads, head_dim, scale, q_tokens, extra_tokens, causal, mode,
+                               w_uk, w_uv, seq_ids, q_layout, out_layout, q_dtype, out_dtype)
+        fn = self.lib.relux_mla_decode if self.kind == L.POOL_MLA else self.lib.relux_gqa_decode
+        L.check(fn(self.h, C.byref(args)))
+
+    def verify(self, layer, n_seqs, q, out, draft_a, draft_b, num_heads, head_dim, scale, q_tokens, q_rope=None, w_uk=None,
+               w_uv=None, mode=L.ATTN_FAST, seq_ids=None, kv_layout=L.LAYOUT_TOKEN_MAJOR, q_dtype=None, out_dtype=None,
+               kv_dtype=None):
+        """Speculative verify: draft rows are written past the cursor, q_tokens rows attend causally."""
+        n_new = np.full(n_seqs, q_tokens, np.int32)
+        ap = self._append_args(layer, draft_a, draft_b, n_seqs, seq_ids, n_new, kv_layout, False, kv_dtype)
+        at = self._attn_args(layer, n_seqs, q, q_rope, out, num_heads, head_dim, scale, q_tokens, q_tokens, True, mode, w_uk, w_uv,
+                             seq_ids, L.LAYOUT_TOKEN_MAJOR, L.LAYOUT_TOKEN_MAJOR, q_dtype, out_dtype)
+        fn = self.lib.relux_mla_verify if self.kind == L.POOL_MLA else self.lib.relux_gqa_verify
+        L.check(fn(self.h, C.byref(at), C.byref(ap)))
+
+    def last_kernel_ms(self):
+        ms = C.c_float()
+        L.check(self.lib.relux_pool_last_kernel_ms(self.h, C.byref(ms)))
+        return ms.value
+
+
+BFloat16 = "bf16"
+
+
+class KVCache:
+    """NewKVCacheSized(numLayers, maxLen, numKVHeads, headDim, BFloat16)   kvcache.go:66-93.
+    One sequence, every layer; tensors follow the reference's shapes: K/V [1, numKVHeads, newLen, headDim]."""
+
+    def __init__(self, dev, num_layers, max_len, num_kv_heads, head_dim, page_tokens=64):
+        if num_layers <= 0:
+            raise ValueError("NewKVCacheSized: numLayers=%d, must be > 0" % num_layers)
+        if max_len <= 0:
+            raise ValueError("NewKVCacheSized: maxLen=%d, must be > 0" % max_len)
+        pages = (max_len + page_tokens - 1) // page_tokens
+        self.pool = Pool(dev, L.POOL_GQA, num_layers, pages, page_tokens, 1, pages, num_kv_heads=num_kv_heads, head_dim=head_dim)
+        self.seq = self.pool.seq_alloc(max_len)
+        self.num_layers, self.max_len, self.num_kv_heads, self.head_dim = num_layers, max_len, num_kv_heads, head_dim
+
+    def DType(self):
+        return BFloat16
+
+    def TotalLen(self, layer):
+        return self.pool.seq_len(layer, self.seq)
+
+    def Append(self, layer, new_k, new_v):
+        if not (0 <= layer < self.num_layers):
+            raise IndexError("KVCache.Append: layerIdx=%d out of range [0, %d)" % (layer, self.num_layers))
+        new_k = np.ascontiguousarray(new_k, dtype=np.float32)
+        new_v = np.ascontiguousarray(new_v, dtype=np.float32)
+        if new_k.shape != new_v.shape:
+            raise ValueError("KVCache.Append: K and V shape mismatch: %s vs %s" % (new_k.shape, new_v.shape))
+        if new_k.ndim < 3:
+            raise ValueError("KVCache.Append: K rank=%d, want >= 3 [batch, heads, seq, headDim]" % new_k.ndim)
+        n_new = new_k.shape[-2]
+        try:
+            self.pool.append(layer, new_k, new_v, 1, seq_ids=[self.seq], n_new=[n_new], layout=L.LAYOUT_HEAD_MAJOR)
+        except L.ReluxCudaError as e:
+            if e.code == L.ERR_OVERFLOW:
+                raise OverflowError(str(e))
+            raise
+
+    def View(self, layer):
+        """Returns (K, V) as bf16 bit patterns shaped [1, numKVHeads, total, headDim], or (None, None)."""
+        if not (0 <= layer < self.num_layers):
+            raise IndexError("KVCache.View: layerIdx=%d out of range" % layer)
+        t = self.TotalLen(layer)
+        if t == 0:
+            return None, None
+        k, v = self.pool.read_rows(layer, self.seq, 0, t)  # [t, Hkv, D]
+        return (np.ascontiguousarray(k.transpose(1, 0, 2))[None], np.ascontiguousarray(v.transpose(1, 0, 2))[None])
+
+    def Reset(self):
+        self.pool.set_len(-1, [0], [self.seq])
+
+    def attend(self, layer, q, scale, causal=True, mode=L.ATTN_FAST, extra_tokens=0):
+        """q [1, H, S, D] float32 (post-RoPE) -> attention output [1, H, S, D] float32 over the cached rows;
+        the S query rows are the last S cached rows (append first, then attend: mha.go:287-296)."""
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        _, H, S, D = q.shape
+        out = np.empty_like(q)
+        self.pool.decode(layer, 1, q, out, H, D, scale, q_tokens=S, extra_tokens=extra_tokens, causal=causal, mode=mode,
+                         seq_ids=[self.seq], q_layout=L.LAYOUT_HEAD_MAJOR, out_layout=L.LAYOUT_HEAD_MAJOR)
+        return out
+
+    def close(self):
+        self.pool.destroy()
+
+
+class MLACache:
+    """NewMLACache(numLayers, maxLen, dC, dHR)   mla_cache.go:38-59 (rows are stored as bf16 here)."""
+
+    def __init__(self, dev, num_layers, max_len, dC, dHR, page_tokens=64):
+        if num_layers <= 0:
+            raise ValueError("NewMLACache: numLayers=%d, must be > 0" % num_layers)
+        if max_len <= 0:
+            raise ValueError("NewMLACache: maxLen=%d, must be > 0" % max_len)
+        pages = (max_len + page_tokens - 1) // page_tokens
+        self.pool = Pool(dev, L.POOL_MLA, num_layers, pages, page_tokens, 1, pages, dC=dC, dHR=dHR)
+        self.seq = self.pool.seq_alloc(max_len)
+        self.num_layers, self.max_len, self.dC, self.dHR = num_layers, max_len, dC, dHR
+
+    def TotalLen(self, layer):
+        return self.pool.seq_len(layer, self.seq)
+
+    def Append(self, layer, new_c, new_kr):
+        if not (0 <= layer < self.num_layers):
+            raise IndexError("MLACache.Append: layerIdx=%d out of range [0, %d)" % (layer, self.num_layers))
+        c = np.ascontiguousarray(new_c, dtype=np.float32)
+        r = np.ascontiguousarray(new_kr, dtype=np.float32)
+        n_new = c.shape[-2]
+        try:
+            self.pool.append(layer, c, r, 1, seq_ids=[self.seq], n_new=[n_new])
+        except L.ReluxCudaError as e:
+            if e.code == L.ERR_OVERFLOW:
+                raise OverflowError(str(e))
+            raise
+
+    def View(self, layer):
+        if not (0 <= layer < self.num_layers):
+            raise IndexError("MLACache.View: layerIdx=%d out of range" % layer)
+        t = self.TotalLen(layer)
+        if t == 0:
+            return None, None
+        c, r = self.pool.read_rows(layer, self.seq, 0, t)
+        return c[None], r[None]
+
+    def Reset(self):
+        self.pool.set_len(-1, [0], [self.seq])
+
+    def attend(self, layer, qc, qr, w_uk, w_uv, scale, causal=True, mode=L.ATTN_FAST, extra_tokens=0):
+        """qc [1,H,S,Dh], qr [1,H,S,dHR] float32; w_uk / w_uv device buffers [dC, H*Dh] bf16 -> [1,H,S,Dh] float32."""
+        qc = np.ascontiguousarray(qc, dtype=np.float32)
+        qr = np.ascontiguousarray(qr, dtype=np.float32)
+        _, H, S, Dh = qc.shape
+        out = np.empty_like(qc)
+        self.pool.decode(layer, 1, qc, out, H, Dh, scale, q_rope=qr, w_uk=w_uk, w_uv=w_uv, q_tokens=S, extra_tokens=extra_tokens,
+                         causal=causal, mode=mode, seq_ids=[self.seq], q_layout=L.LAYOUT_HEAD_MAJOR, out_layout=L.LAYOUT_HEAD_MAJOR)
+        return out
+
+    def close(self):
+        self.pool.destroy()

@@ -1,0 +1,216 @@
+// RELUX_ATTN_REFERENCE: cached attention in float32 on CUDA cores with the reference's own
+// operation order, so that its results can be compared bit for bit with a CPU restatement:
+//   * every dot product is a k-ascending chain of unfused multiply-then-add
+//     (internal/transformer/matmul.go:15-44),
+//   * scores are scaled, masked with -Inf, then softmaxRows (mha.go:837-861): exact row max,
+//     weights fastexp32(v - max) with the < -20 cut-off, j-ascending sum, multiply by 1/sum,
+//   * O = P V with j ascending,
+//   * MLA decompresses each latent row with W_UK / W_UV first (mla.go:323-326) instead of absorbing.
+// One CTA per (head, sequence); the score rows live in shared memory, which bounds q_tokens * T.
+// Meant for the small models where greedy token ids are compared, not for speed.
+#include "common.cuh"
+#include "internal.h"
+
+namespace relux {
+
+struct RefGeom {
+  const int32_t* table;
+  int32_t table_stride;
+  const int32_t* len;
+  const int32_t* seq_ids;
+  int32_t num_pages, page_tokens;
+  int32_t* status;
+  int32_t S, extra, causal, H;
+  float scale;
+};
+
+// Shared tail: softmaxRows over w[S][T] and nothing else; all threads of the CTA call it.
+__device__ void softmax_rows_ref(float* w, int S, int T, float* red) {
+  const int tid = threadIdx.x, nt = blockDim.x;
+  for (int s = 0; s < S; s++) {
+    float* row = w + (size_t)s * T;
+    float m = -INFINITY;
+    for (int j = tid; j < T; j += nt) m = fmaxf(m, row[j]);
+    m = warp_max(m);
+    if ((tid & 31) == 0) red[tid >> 5] = m;
+    __syncthreads();
+    if (tid < 32) {
+      float v = (tid < (nt + 31) / 32) ? red[tid] : -INFINITY;
+      v = warp_max(v);
+      if (tid == 0) red[0] = v;
+    }
+    __syncthreads();
+    m = red[0];
+    __syncthreads();
+    for (int j = tid; j < T; j += nt) {
+      float diff = __fsub_rn(row[j], m);
+      row[j] = (diff < -20.0f) ? 0.0f : fastexp32_ref(diff);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      float sum = 0.0f;
+      for (int j = 0; j < T; j++) sum = __fadd_rn(sum, row[j]);
+      red[0] = __fdiv_rn(1.0f, sum);
+    }
+    __syncthreads();
+    const float inv = red[0];
+    for (int j = tid; j < T; j += nt) row[j] = __fmul_rn(row[j], inv);
+    __syncthreads();
+  }
+}
+
+// grid (H, n_seqs).  q, out: [n][S][H][D] f32 token-major.
+__global__ void gqa_reference_kernel(RefGeom g, const uint16_t* __restrict__ k_base, const uint16_t* __restrict__ v_base,
+                                     const float* __restrict__ q, float* __restrict__ out, int Hkv, int D) {
+  extern __shared__ float smem[];
+  __shared__ float red[32];
+  const int h = blockIdx.x, i = blockIdx.y;
+  const int seq = g.seq_ids ? g.seq_ids[i] : i;
+  const int T = g.len[seq] + g.extra;
+  const int S = g.S, kvh = h / (g.H / Hkv);
+  float* w = smem;  // [S][T]
+  const int tid = threadIdx.x, nt = blockDim.x;
+  for (int j = tid; j < T; j += nt) {
+    int32_t pg;
+    bool ok = page_of(g.table, g.table_stride, seq, j / g.page_tokens, g.num_pages, g.status, &pg);
+    const uint16_t* kr = k_base + (size_t)(ok ? pg : 0) * Hkv * g.page_tokens * D + ((size_t)kvh * g.page_tokens + (j % g.page_tokens)) * D;
+    for (int s = 0; s < S; s++) {
+      const float* qv = q + (((size_t)i * S + s) * g.H + h) * D;
+      float sum = 0.0f;
+      for (int d = 0; d < D; d++) sum = __fadd_rn(sum, __fmul_rn(qv[d], f32_from_bf16_bits(kr[d])));
+      float v = __fmul_rn(sum, g.scale);
+      if (g.causal && j > T - S + s) v = -INFINITY;
+      w[(size_t)s * T + j] = ok ? v : -INFINITY;
+    }
+  }
+  __syncthreads();
+  softmax_rows_ref(w, S, T, red);
+  for (int e = tid; e < S * D; e += nt) {
+    const int s = e / D, d = e % D;
+    float o = 0.0f;
+    for (int j = 0; j < T; j++) {
+      int32_t pg = g.table[(size_t)seq * g.table_stride + j / g.page_tokens];
+      if (pg < 0 || pg >= g.num_pages) continue;
+      const uint16_t* vr = v_base + (size_t)pg * Hkv * g.page_tokens * D + ((size_t)kvh * g.page_tokens + (j % g.page_tokens)) * D;
+      o = __fadd_rn(o, __fmul_rn(w[(size_t)s * T + j], f32_from_bf16_bits(vr[d])));
+    }
+    out[(((size_t)i * S + s) * g.H + h) * D + d] = o;
+  }
+}
+
+// grid (H, n_seqs).  qc/out: [n][S][H][Dh], qr: [n][S][H][dHR], W_UK/W_UV: [dC][H*Dh] bf16.
+__global__ void mla_reference_kernel(RefGeom g, const uint16_t* __restrict__ base, const float* __restrict__ qc,
+                                     const float* __restrict__ qr, const uint16_t* __restrict__ W_UK,
+                                     const uint16_t* __restrict__ W_UV, float* __restrict__ out, int Dh, int dC, int dHR) {
+  extern __shared__ float smem[];
+  __shared__ float red[32];
+  const int h = blockIdx.x, i = blockIdx.y;
+  const int seq = g.seq_ids ? g.seq_ids[i] : i;
+  const int T = g.len[seq] + g.extra;
+  const int S = g.S, H = g.H, row = dC + dHR;
+  float* w = smem;  // [S][T]
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const size_t wstride = (size_t)H * Dh;
+  for (int j = tid; j < T; j += nt) {
+    int32_t pg;
+    bool ok = page_of(g.table, g.table_stride, seq, j / g.page_tokens, g.num_pages, g.status, &pg);
+    const uint16_t* cr = base + ((size_t)(ok ? pg : 0) * g.page_tokens + (j % g.page_tokens)) * row;
+    for (int s = 0; s < S; s++) {
+      const float* qcv = qc + (((size_t)i * S + s) * H + h) * Dh;
+      const float* qrv = qr + (((size_t)i * S + s) * H + h) * dHR;
+      // Qc . Kc^T with Kc[j][d] = sum_c C[j][c] * W_UK[c][h*Dh+d]   (mla.go:325, 355)
+      float a = 0.0f;
+      for (int d = 0; d < Dh; d++) {
+        float kc = 0.0f;
+        for (int c = 0; c < dC; c++)
+          kc = __fadd_rn(kc, __fmul_rn(f32_from_bf16_bits(cr[c]), f32_from_bf16_bits(W_UK[(size_t)c * wstride + (size_t)h * Dh + d])));
+        a = __fadd_rn(a, __fmul_rn(qcv[d], kc));
+      }
+      float r = 0.0f;
+      for (int d = 0; d < dHR; d++) r = __fadd_rn(r, __fmul_rn(qrv[d], f32_from_bf16_bits(cr[dC + d])));
+      float v = __fmul_rn(__fadd_rn(a, r), g.scale);
+      if (g.causal && j > T - S + s) v = -INFINITY;
+      w[(size_t)s * T + j] = ok ? v : -INFINITY;
+    }
+  }
+  __syncthreads();
+  softmax_rows_ref(w, S, T, red);
+  for (int e = tid; e < S * Dh; e += nt) {
+    const int s = e / Dh, d = e % Dh;
+    float o = 0.0f;
+    for (int j = 0; j < T; j++) {
+      int32_t pg = g.table[(size_t)seq * g.table_stride + j / g.page_tokens];
+      if (pg < 0 || pg >= g.num_pages) continue;
+      const uint16_t* cr = base + ((size_t)pg * g.page_tokens + (j % g.page_tokens)) * row;
+      float vv = 0.0f;
+      for (int c = 0; c < dC; c++)
+        vv = __fadd_rn(vv, __fmul_rn(f32_from_bf16_bits(cr[c]), f32_from_bf16_bits(W_UV[(size_t)c * wstride + (size_t)h * Dh + d])));
+      o = __fadd_rn(o, __fmul_rn(w[(size_t)s * T + j], vv));
+    }
+    out[(((size_t)i * S + s) * H + h) * Dh + d] = o;
+  }
+}
+
+static int32_t ref_geom(Pool* p, const SeqBatch& sb, const relux_attn_args& a, RefGeom* g, size_t* smem_bytes) {
+  const relux_pool_params& prm = p->prm;
+  int maxT = 0;
+  for (int i = 0; i < sb.n_seqs; i++) maxT = std::max(maxT, p->h_len[(size_t)a.layer * prm.max_seqs + sb.seq[i]] + a.extra_tokens);
+  size_t need = (size_t)a.q_tokens * maxT * sizeof(float);
+  if (need > 200 * 1024) {
+    set_error("RELUX_ATTN_REFERENCE keeps q_tokens*T=%d*%d scores in shared memory; the limit is 51200", a.q_tokens, maxT);
+    return RELUX_ERR_UNSUPPORTED;
+  }
+  *smem_bytes = need;
+  g->table = p->d_table;
+  g->table_stride = prm.max_pages_per_seq;
+  g->len = p->d_len + (size_t)a.layer * prm.max_seqs;
+  g->seq_ids = sb.d_seq_ids;
+  g->num_pages = prm.num_pages;
+  g->page_tokens = prm.page_tokens;
+  g->status = p->d_status;
+  g->S = a.q_tokens;
+  g->extra = a.extra_tokens;
+  g->causal = a.causal;
+  g->H = a.num_heads;
+  g->scale = a.scale;
+  return RELUX_OK;
+}
+
+int32_t launch_attn_reference_gqa(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const float* d_q, float* d_out) {
+  RefGeom g;
+  size_t smem;
+  int32_t rc = ref_geom(p, sb, a, &g, &smem);
+  if (rc) return rc;
+  const uint16_t* kb = p->storage + (size_t)a.layer * p->layer_elems;
+  const uint16_t* vb = kb + p->page_elems * p->prm.num_pages;
+  if (smem > 48 * 1024) RELUX_CUDA_TRY(cudaFuncSetAttribute(gqa_reference_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(a.num_heads, sb.n_seqs);
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev0, p->dev->stream));
+  gqa_reference_kernel<<<grid, 128, smem, p->dev->stream>>>(g, kb, vb, d_q, d_out, p->prm.gqa_num_kv_heads, p->prm.gqa_head_dim);
+  RELUX_CUDA_TRY(cudaGetLastError());
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev1, p->dev->stream));
+  p->timed = true;
+  count_launch(p->dev);
+  return RELUX_OK;
+}
+
+int32_t launch_attn_reference_mla(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const float* d_q, const float* d_qr,
+                                  float* d_out) {
+  RefGeom g;
+  size_t smem;
+  int32_t rc = ref_geom(p, sb, a, &g, &smem);
+  if (rc) return rc;
+  const uint16_t* base = p->storage + (size_t)a.layer * p->layer_elems;
+  if (smem > 48 * 1024) RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_reference_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(a.num_heads, sb.n_seqs);
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev0, p->dev->stream));
+  mla_reference_kernel<<<grid, 128, smem, p->dev->stream>>>(g, base, d_q, d_qr, (const uint16_t*)a.w_uk, (const uint16_t*)a.w_uv, d_out,
+                                                            a.head_dim, p->prm.mla_dc, p->prm.mla_dhr);
+  RELUX_CUDA_TRY(cudaGetLastError());
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev1, p->dev->stream));
+  p->timed = true;
+  count_launch(p->dev);
+  return RELUX_OK;
+}
+
+}  // namespace relux

@@ -1,0 +1,352 @@
+// GQA flash-decode / speculative verify over the paged bf16 K/V pool (RELUX_ATTN_FAST).
+//
+// Bound: HBM bandwidth.  Every cached token costs Hkv * D * 2 (K,V) * 2 B = 4096 B at Hkv=8, D=128,
+// against about 16 flop/B of work, so the kernel is organised around keeping TMA loads in flight:
+//   * one CTA per (sequence chunk, kv head); warp 4 is the producer, warps 0-3 consume;
+//   * the producer streams each 64-token page of this head as four 8 KB TMA boxes (K and V, two 64-wide
+//     halves each, 128-byte swizzle) through a ring of kStages stages guarded by full/empty mbarriers;
+//   * the g query heads sharing the kv head times the S query tokens form the 16-row M dimension of
+//     mma.sync m16n8k16 (bf16 in, f32 accumulate); each consumer warp owns 16 tokens of every page and
+//     keeps its own online-softmax state, so warps never wait on each other inside the loop;
+//   * at the end the four warps' (max, sum, O) are combined through shared memory and written as one
+//     split-KV partial; merge_splits_kernel combines the chunks of a sequence.
+// All mbarrier waits are bounded; a wait that runs out records RELUX_ERR_TIMEOUT and the CTA leaves.
+#include "common.cuh"
+#include "internal.h"
+#include "splitkv.h"
+
+namespace relux {
+
+namespace {
+
+constexpr int kStages = 5;
+constexpr int kPageTok = 64;
+constexpr int kD = 128;
+constexpr int kStageBytes = 4 * 8192;  // K lo, K hi, V lo, V hi
+constexpr int kQStride = kD + 8;       // bf16 elements per Q row in shared memory (272 B, conflict-free ldmatrix)
+constexpr int kConsumerWarps = 4;
+
+struct GqaParams {
+  const WorkItem* items;
+  const int32_t* table;
+  int32_t table_stride;
+  const int32_t* len;
+  int32_t num_pages, Hkv, H, g, S, R, extra, causal;
+  int32_t krow0, vrow0;  // first TMA row of this layer's K block / V block
+  float scale_log2;
+  const void* q;
+  int32_t q_bf16;
+  float* part_o;
+  float* part_ml;
+  int32_t rows_total;  // S * H
+  int32_t* status;
+};
+
+template <int MT>
+__global__ void __launch_bounds__(160, 1) gqa_decode_kernel(const __grid_constant__ CUtensorMap tmap, const GqaParams prm) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // carve: stages (1024-aligned) | Q | barriers
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* stages = smem;
+  uint16_t* qs = (uint16_t*)(smem + kStages * kStageBytes);
+  uint64_t* full = (uint64_t*)(qs + 16 * MT * kQStride);
+  uint64_t* empty = full + kStages;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const WorkItem item = prm.items[blockIdx.x];
+  const int kvh = blockIdx.y;
+  const int T = prm.len[item.seq] + prm.extra;
+  const int npages = item.page_end - item.page_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; s++) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], kConsumerWarps);
+    }
+    fence_mbar_init();
+  }
+  // Q rows of this kv head -> shared memory as bf16; row r = s * g + hq, rows >= R are zero.
+  for (int e = threadIdx.x; e < 16 * MT * (kD / 2); e += blockDim.x) {
+    const int r = e / (kD / 2), c = (e % (kD / 2)) * 2;
+    uint32_t w = 0;
+    if (r < prm.R) {
+      const int s = r / prm.g, hq = r % prm.g;
+      const size_t off = (((size_t)item.seq_index * prm.S + s) * prm.H + (size_t)kvh * prm.g + hq) * kD + c;
+      if (prm.q_bf16) w = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(prm.q) + off);
+      else {
+        float2 f = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(prm.q) + off);
+        w = pack_bf16x2(f.x, f.y);
+      }
+    }
+    *reinterpret_cast<uint32_t*>(qs + r * kQStride + c) = w;
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap);
+      bool ok = true;
+      for (int it = 0; it < npages && ok; it++) {
+        const int st = it % kStages, k = it / kStages;
+        if (k > 0 && !mbar_wait(&empty[st], (k - 1) & 1)) {
+          set_status(prm.status, RELUX_ERR_TIMEOUT);
+          ok = false;
+          break;
+        }
+        int32_t pg = prm.table[(size_t)item.seq * prm.table_stride + item.page_begin + it];
+        if (pg < 0 || pg >= prm.num_pages) {
+          set_status(prm.status, RELUX_ERR_BAD_PAGE);
+          pg = 0;  // keep the pipeline protocol intact; the status word reports the fault
+        }
+        uint8_t* sb = stages + st * kStageBytes;
+        const int32_t krow = prm.krow0 + (pg * prm.Hkv + kvh) * kPageTok;
+        const int32_t vrow = prm.vrow0 + (pg * prm.Hkv + kvh) * kPageTok;
+        mbar_expect_tx(&full[st], kStageBytes);
+        tma_load_2d(sb, &tmap, 0, krow, &full[st]);
+        tma_load_2d(sb + 8192, &tmap, 64, krow, &full[st]);
+        tma_load_2d(sb + 16384, &tmap, 0, vrow, &full[st]);
+        tma_load_2d(sb + 24576, &tmap, 64, vrow, &full[st]);
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  uint32_t qa[MT][8][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+    for (int ks = 0; ks < 8; ks++) {
+      const int m = lane >> 3;
+      const int row = mt * 16 + (m & 1) * 8 + (lane & 7);
+      const int col = ks * 16 + (m >> 1) * 8;
+      ldmatrix_x4(qa[mt][ks][0], qa[mt][ks][1], qa[mt][ks][2], qa[mt][ks][3], smem_u32(qs + row * kQStride + col));
+    }
+
+  float oacc[MT][16][4];
+  float m_run[MT][2], l_run[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; mt++) {
+#pragma unroll
+    for (int nt = 0; nt < 16; nt++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) oacc[mt][nt][e] = 0.f;
+    m_run[mt][0] = m_run[mt][1] = -INFINITY;
+    l_run[mt][0] = l_run[mt][1] = 0.f;
+  }
+  const int tb = warp * 16;  // this warp's tokens inside every page
+  bool alive = true;
+
+  for (int it = 0; it < npages; it++) {
+    const int st = it % kStages;
+    if (!mbar_wait(&full[st], (it / kStages) & 1)) {
+      set_status(prm.status, RELUX_ERR_TIMEOUT);
+      alive = false;
+      break;
+    }
+    const uint32_t kt = smem_u32(stages + st * kStageBytes);
+    const uint32_t vt = kt + 16384;
+    float sacc[MT][2][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+      for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+        for (int e = 0; e < 4; e++) sacc[mt][nt][e] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 8; ks++) {
+      const int m = lane >> 3;
+      const uint32_t row = tb + (m >> 1) * 8 + (lane & 7);
+      const uint32_t chunk = (ks & 3) * 2 + (m & 1);
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4(b0, b1, b2, b3, kt + (ks >> 2) * 8192 + swz128(row, chunk));
+#pragma unroll
+      for (int mt = 0; mt < MT; mt++) {
+        mma_bf16_16816(sacc[mt][0], qa[mt][ks], b0, b1);
+        mma_bf16_16816(sacc[mt][1], qa[mt][ks], b2, b3);
+      }
+    }
+    // scale to the log2 domain, mask the tail of the sequence and the causal part of the draft
+    const int tok0 = (item.page_begin + it) * kPageTok + tb;
+    const bool need_mask = (tok0 + 16 > T - (prm.causal ? prm.S : 0));
+    uint32_t pa[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; mt++) {
+#pragma unroll
+      for (int hf = 0; hf < 2; hf++) {
+        const int row = mt * 16 + hf * 8 + (lane >> 2);
+        const int limit = prm.causal ? (T - prm.S + row / prm.g) : (T - 1);  // last visible token
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            float v = sacc[mt][nt][hf * 2 + e] * prm.scale_log2;
+            if (need_mask) {
+              const int tok = tok0 + nt * 8 + 2 * (lane & 3) + e;
+              if (tok > limit || tok >= T) v = -INFINITY;
+            }
+            sacc[mt][nt][hf * 2 + e] = v;
+            mx = fmaxf(mx, v);
+          }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[mt][hf], mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = exp2f(m_run[mt][hf] - m_use);
+        m_run[mt][hf] = m_new;
+        float ps = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; nt++)
+#pragma unroll
+          for (int e = 0; e < 2; e++) {
+            const float pv = exp2f(sacc[mt][nt][hf * 2 + e] - m_use);
+            sacc[mt][nt][hf * 2 + e] = pv;
+            ps += pv;
+          }
+        l_run[mt][hf] = l_run[mt][hf] * alpha + ps;
+#pragma unroll
+        for (int nt = 0; nt < 16; nt++) {
+          oacc[mt][nt][hf * 2] *= alpha;
+          oacc[mt][nt][hf * 2 + 1] *= alpha;
+        }
+      }
+      pa[mt][0] = pack_bf16x2(sacc[mt][0][0], sacc[mt][0][1]);
+      pa[mt][1] = pack_bf16x2(sacc[mt][0][2], sacc[mt][0][3]);
+      pa[mt][2] = pack_bf16x2(sacc[mt][1][0], sacc[mt][1][1]);
+      pa[mt][3] = pack_bf16x2(sacc[mt][1][2], sacc[mt][1][3]);
+    }
+    // O += P V
+#pragma unroll
+    for (int n2 = 0; n2 < 8; n2++) {
+      const int m = lane >> 3;
+      const uint32_t row = tb + (m & 1) * 8 + (lane & 7);
+      const uint32_t chunk = n2 * 2 + (m >> 1);  // 16 chunks of 8 dims
+      uint32_t b0, b1, b2, b3;
+      ldmatrix_x4_trans(b0, b1, b2, b3, vt + (chunk >> 3) * 8192 + swz128(row, chunk & 7));
+#pragma unroll
+      for (int mt = 0; mt < MT; mt++) {
+        mma_bf16_16816(oacc[mt][2 * n2], pa[mt], b0, b1);
+        mma_bf16_16816(oacc[mt][2 * n2 + 1], pa[mt], b2, b3);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[st]);
+  }
+
+  // ---------------- combine the four warps, write the split-KV partial ----------------
+  // every load this CTA issued has completed once all consumers passed their last full-barrier wait
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  constexpr int kMStride = kD + 2;
+  float* mb = reinterpret_cast<float*>(stages);  // [4 warps][16*MT rows][kD + 2]
+#pragma unroll
+  for (int mt = 0; mt < MT; mt++)
+#pragma unroll
+    for (int hf = 0; hf < 2; hf++) {
+      float l = l_run[mt][hf];
+      l += __shfl_xor_sync(0xffffffffu, l, 1);
+      l += __shfl_xor_sync(0xffffffffu, l, 2);
+      const int row = mt * 16 + hf * 8 + (lane >> 2);
+      float* dst = mb + ((size_t)warp * 16 * MT + row) * kMStride;
+#pragma unroll
+      for (int nt = 0; nt < 16; nt++) {
+        dst[nt * 8 + 2 * (lane & 3)] = oacc[mt][nt][hf * 2];
+        dst[nt * 8 + 2 * (lane & 3) + 1] = oacc[mt][nt][hf * 2 + 1];
+      }
+      if ((lane & 3) == 0) {
+        dst[kD] = alive ? m_run[mt][hf] : -INFINITY;
+        dst[kD + 1] = alive ? l : 0.f;
+      }
+    }
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  const int d = threadIdx.x;  // 128 consumer threads, one output dim each
+  for (int r = 0; r < prm.R; r++) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; w++) M = fmaxf(M, mb[((size_t)w * 16 * MT + r) * kMStride + kD]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; w++) {
+      const float* src = mb + ((size_t)w * 16 * MT + r) * kMStride;
+      const float f = (src[kD] == -INFINITY) ? 0.f : exp2f(src[kD] - M);
+      L += src[kD + 1] * f;
+      O += src[d] * f;
+    }
+    const int s = r / prm.g, hq = r % prm.g;
+    const size_t grow = (size_t)blockIdx.x * prm.rows_total + (size_t)s * prm.H + (size_t)kvh * prm.g + hq;
+    prm.part_o[grow * kD + d] = O;
+    if (d == 0) {
+      prm.part_ml[grow * 2] = M;
+      prm.part_ml[grow * 2 + 1] = L;
+    }
+  }
+}
+
+template <int MT>
+constexpr size_t gqa_smem_bytes() {
+  return 1024 + (size_t)kStages * kStageBytes + (size_t)16 * MT * kQStride * 2 + 2 * kStages * 8 + 64;
+}
+
+}  // namespace
+
+int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, void* d_out) {
+  const relux_pool_params& prm = p->prm;
+  const int g = a.num_heads / prm.gqa_num_kv_heads, R = g * a.q_tokens;
+  if (!p->has_tmap || prm.page_tokens != kPageTok || prm.gqa_head_dim != kD || R > 32) {
+    set_error("GQA FAST kernel needs page_tokens=64, head_dim=128 and (num_heads/num_kv_heads)*q_tokens <= 32 "
+              "(got page_tokens=%d head_dim=%d rows=%d); use RELUX_ATTN_REFERENCE for other shapes",
+              prm.page_tokens, prm.gqa_head_dim, R);
+    return RELUX_ERR_UNSUPPORTED;
+  }
+  SplitPlan plan;
+  int32_t rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, prm.gqa_num_kv_heads, 2, &plan);
+  if (rc) return rc;
+  const int rows_total = a.q_tokens * a.num_heads;
+  rc = grow(p->dev, p->part_o, (size_t)plan.num_items * rows_total * kD * sizeof(float));
+  if (rc) return rc;
+  rc = grow(p->dev, p->part_ml, (size_t)plan.num_items * rows_total * 2 * sizeof(float));
+  if (rc) return rc;
+  GqaParams k;
+  k.items = plan.items;
+  k.table = p->d_table;
+  k.table_stride = prm.max_pages_per_seq;
+  k.len = p->d_len + (size_t)a.layer * prm.max_seqs;
+  k.num_pages = prm.num_pages;
+  k.Hkv = prm.gqa_num_kv_heads;
+  k.H = a.num_heads;
+  k.g = g;
+  k.S = a.q_tokens;
+  k.R = R;
+  k.extra = a.extra_tokens;
+  k.causal = a.causal;
+  const int64_t rows_per_block = (int64_t)prm.num_pages * prm.gqa_num_kv_heads * kPageTok;
+  k.krow0 = (int32_t)((int64_t)a.layer * 2 * rows_per_block);
+  k.vrow0 = (int32_t)((int64_t)a.layer * 2 * rows_per_block + rows_per_block);
+  k.scale_log2 = a.scale * 1.4426950408889634f;
+  k.q = d_q;
+  k.q_bf16 = a.q_dtype == RELUX_DTYPE_BF16;
+  k.part_o = (float*)p->part_o.p;
+  k.part_ml = (float*)p->part_ml.p;
+  k.rows_total = rows_total;
+  k.status = p->d_status;
+  dim3 grid(plan.num_items, prm.gqa_num_kv_heads);
+  cudaStream_t st = p->dev->stream;
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev0, st));
+  if (R <= 16) {
+    constexpr size_t smem = gqa_smem_bytes<1>();
+    RELUX_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    gqa_decode_kernel<1><<<grid, 160, smem, st>>>(p->tmap_gqa, k);
+  } else {
+    constexpr size_t smem = gqa_smem_bytes<2>();
+    RELUX_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    gqa_decode_kernel<2><<<grid, 160, smem, st>>>(p->tmap_gqa, k);
+  }
+  RELUX_CUDA_TRY(cudaGetLastError());
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev1, st));
+  p->timed = true;
+  count_launch(p->dev);
+  return launch_merge(p, plan, sb.n_seqs, rows_total, kD, (float*)d_out, nullptr);
+}
+
+}  // namespace relux

@@ -1,0 +1,127 @@
+// Host-side structures of librelux_cuda: device handle, paged pool, per-call staging.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "relux_cuda.h"
+
+namespace relux {
+
+constexpr uint32_t kDeviceMagic = 0x52444556u;  // "RDEV"
+constexpr uint32_t kPoolMagic = 0x52504F4Cu;    // "RPOL"
+
+void set_error(const char* fmt, ...);
+int32_t cuda_fail(cudaError_t e, const char* what);
+
+#define RELUX_CUDA_TRY(expr)                                  \
+  do {                                                        \
+    cudaError_t e__ = (expr);                                 \
+    if (e__ != cudaSuccess) return ::relux::cuda_fail(e__, #expr); \
+  } while (0)
+
+struct Device {
+  uint32_t magic = kDeviceMagic;
+  int index = 0;
+  int sm_count = 0;
+  size_t total_mem = 0;
+  char name[256] = {0};
+  cudaStream_t stream = nullptr;
+  std::mutex mu;
+  int64_t launches = 0;
+  void* flush_buf = nullptr;
+  size_t flush_bytes = 0;
+};
+
+// A device buffer that grows on demand (never shrinks) for inputs that arrive in host memory
+// and for kernel scratch.  Growth synchronises the stream before the old block is freed.
+struct GrowBuf {
+  void* p = nullptr;
+  size_t cap = 0;
+};
+
+struct Pool {
+  uint32_t magic = kPoolMagic;
+  Device* dev = nullptr;
+  relux_pool_params prm{};
+  int row_elems_a = 0;  // MLA: dC + dHR (one fused row); GQA: head_dim
+  size_t page_elems = 0;    // elements per page per tensor (MLA: P*(dC+dHR); GQA: Hkv*P*D for K, same for V)
+  size_t layer_elems = 0;   // elements per layer (GQA: K then V)
+  uint16_t* storage = nullptr;  // bf16 bits
+  int32_t* d_table = nullptr;   // [max_seqs][max_pages_per_seq]
+  int32_t* d_len = nullptr;     // [num_layers][max_seqs]
+  int32_t* d_status = nullptr;
+  std::vector<int32_t> h_table, h_len;
+  std::vector<int32_t> seq_pages;  // pages reserved per sequence (capacity), 0 = slot not live
+  std::vector<uint8_t> seq_owned;  // 1 = table rows were filled by relux_seq_alloc
+  std::vector<int32_t> free_pages;
+  // per-call staging of small host arrays (seq ids, row offsets)
+  int32_t* d_seq_ids = nullptr;  // [max_seqs]
+  int32_t* d_row_off = nullptr;  // [max_seqs + 1]
+  int32_t* h_stage = nullptr;    // pinned [2 * (max_seqs + 1)]
+  cudaEvent_t stage_ev = nullptr;
+  bool stage_busy = false;
+  // staging of activations that arrive in host memory, and outputs that leave to it
+  GrowBuf in_a, in_b, out_buf, q_conv;
+  // attention scratch
+  GrowBuf q_abs;     // MLA absorbed queries, bf16 [n][S][H][dC+dHR]
+  GrowBuf part_o;    // split-KV partial accumulators, f32
+  GrowBuf part_ml;   // split-KV partial (max, sum), f32 pairs
+  GrowBuf work;      // int32 work list + per-sequence chunk offsets
+  GrowBuf o_lat;     // MLA merged latent output, f32/bf16
+  // TMA descriptors over the pool storage (built at create when the shape allows it)
+  CUtensorMap tmap_mla{};   // 2-D [rows][dC+dHR], box 64 x 64, 128-byte swizzle
+  CUtensorMap tmap_gqa{};   // 2-D [rows][D],      box 64 x 64, 128-byte swizzle
+  bool has_tmap = false;
+  // timing of the dominant kernel
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  bool timed = false;
+};
+
+inline Device* as_device(relux_device_t h) {
+  Device* d = (Device*)h;
+  return (d && d->magic == kDeviceMagic) ? d : nullptr;
+}
+inline Pool* as_pool(relux_pool_t h) {
+  Pool* p = (Pool*)h;
+  return (p && p->magic == kPoolMagic && p->dev && p->dev->magic == kDeviceMagic) ? p : nullptr;
+}
+
+int32_t grow(Device* dev, GrowBuf& b, size_t bytes);
+
+// Resolved view of one call's sequences on the device.
+struct SeqBatch {
+  int32_t n_seqs = 0;
+  const int32_t* d_seq_ids = nullptr;  // nullptr = identity
+  const int32_t* d_row_off = nullptr;  // nullptr = one row per sequence
+  int32_t total_rows = 0;
+  int32_t max_rows = 0;
+  std::vector<int32_t> seq;  // host copy of ids
+  std::vector<int32_t> rows; // host copy of rows per sequence
+};
+int32_t stage_batch(Pool* p, int32_t n_seqs, const int32_t* seq_ids, const int32_t* n_rows, int32_t uniform_rows,
+                    SeqBatch* out);
+
+// kernels (defined in the .cu files of this directory)
+int32_t launch_mla_append(Pool* p, const SeqBatch& sb, int layer, const void* ckv, const void* kr, int dtype, int advance);
+int32_t launch_gqa_append(Pool* p, const SeqBatch& sb, int layer, const void* k, const void* v, int dtype, int layout,
+                          int advance);
+int32_t launch_set_len(Pool* p, const SeqBatch& sb, int layer, const int32_t* d_new_len);
+int32_t launch_gather_rows(Pool* p, int layer, int seq, int tok0, int n, uint16_t* d_a, uint16_t* d_b);
+int32_t launch_attn_reference_gqa(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const float* d_q, float* d_out);
+int32_t launch_attn_reference_mla(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const float* d_q, const float* d_qr,
+                                  float* d_out);
+int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, void* d_out);
+int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, const void* d_qr,
+                               void* d_out);
+
+inline void count_launch(Device* d, int n = 1) { d->launches += n; }
+
+}  // namespace relux

@@ -1,0 +1,824 @@
+// Runtime half of librelux_cuda: handles, errors, memory, paged pools, page tables, and the
+// C-ABI entry points that validate arguments and dispatch to the kernels.
+#include <algorithm>
+#include <new>
+
+#include "internal.h"
+
+namespace relux {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+int32_t cuda_fail(cudaError_t e, const char* what) {
+  set_error("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+  if (e == cudaErrorMemoryAllocation) return RELUX_ERR_OUT_OF_MEMORY;
+  if (e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver) return RELUX_ERR_NO_DEVICE;
+  return RELUX_ERR_CUDA;
+}
+
+int32_t grow(Device* dev, GrowBuf& b, size_t bytes) {
+  if (bytes <= b.cap) return RELUX_OK;
+  size_t want = std::max(bytes, b.cap + b.cap / 2);
+  want = (want + 255) & ~(size_t)255;
+  if (b.p) {
+    RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+    RELUX_CUDA_TRY(cudaFree(b.p));
+    b.p = nullptr;
+    b.cap = 0;
+  }
+  RELUX_CUDA_TRY(cudaMalloc(&b.p, want));
+  b.cap = want;
+  return RELUX_OK;
+}
+
+// Copies the call's sequence ids / rows-per-sequence to the device when they are not the
+// trivial (identity, uniform) case, through one pinned staging block guarded by an event.
+int32_t stage_batch(Pool* p, int32_t n_seqs, const int32_t* seq_ids, const int32_t* n_rows, int32_t uniform_rows,
+                    SeqBatch* out) {
+  const relux_pool_params& prm = p->prm;
+  if (n_seqs <= 0 || n_seqs > prm.max_seqs) {
+    set_error("n_seqs=%d outside [1, max_seqs=%d]", n_seqs, prm.max_seqs);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  out->n_seqs = n_seqs;
+  out->seq.resize(n_seqs);
+  out->rows.resize(n_seqs);
+  out->total_rows = 0;
+  out->max_rows = 0;
+  bool uniform = true;
+  for (int i = 0; i < n_seqs; i++) {
+    int s = seq_ids ? seq_ids[i] : i;
+    if (s < 0 || s >= prm.max_seqs || p->seq_pages[s] == 0) {
+      set_error("sequence id %d is not live in this pool", s);
+      return RELUX_ERR_INVALID_ARG;
+    }
+    int r = n_rows ? n_rows[i] : uniform_rows;
+    if (r < 0) {
+      set_error("negative row count for sequence %d", s);
+      return RELUX_ERR_INVALID_ARG;
+    }
+    if (r != uniform_rows) uniform = false;
+    out->seq[i] = s;
+    out->rows[i] = r;
+    out->total_rows += r;
+    out->max_rows = std::max(out->max_rows, r);
+  }
+  if (seq_ids) {
+    for (int i = 0; i < n_seqs; i++)
+      for (int j = i + 1; j < n_seqs && n_seqs <= 64; j++)
+        if (out->seq[i] == out->seq[j]) {
+          set_error("sequence id %d appears twice in one call", out->seq[i]);
+          return RELUX_ERR_INVALID_ARG;
+        }
+  }
+  out->d_seq_ids = nullptr;
+  out->d_row_off = nullptr;
+  if (!seq_ids && uniform) return RELUX_OK;
+  Device* dev = p->dev;
+  if (p->stage_busy) {
+    RELUX_CUDA_TRY(cudaEventSynchronize(p->stage_ev));
+    p->stage_busy = false;
+  }
+  int32_t* h_ids = p->h_stage;
+  int32_t* h_off = p->h_stage + prm.max_seqs;
+  if (seq_ids) {
+    memcpy(h_ids, out->seq.data(), sizeof(int32_t) * n_seqs);
+    RELUX_CUDA_TRY(cudaMemcpyAsync(p->d_seq_ids, h_ids, sizeof(int32_t) * n_seqs, cudaMemcpyHostToDevice, dev->stream));
+    out->d_seq_ids = p->d_seq_ids;
+  }
+  if (!uniform) {
+    int32_t acc = 0;
+    for (int i = 0; i < n_seqs; i++) {
+      h_off[i] = acc;
+      acc += out->rows[i];
+    }
+    h_off[n_seqs] = acc;
+    RELUX_CUDA_TRY(cudaMemcpyAsync(p->d_row_off, h_off, sizeof(int32_t) * (n_seqs + 1), cudaMemcpyHostToDevice, dev->stream));
+    out->d_row_off = p->d_row_off;
+  }
+  RELUX_CUDA_TRY(cudaEventRecord(p->stage_ev, dev->stream));
+  p->stage_busy = true;
+  return RELUX_OK;
+}
+
+struct DeviceGuard {
+  std::unique_lock<std::mutex> lk;
+  int32_t rc;
+  explicit DeviceGuard(Device* d) : lk(d->mu) {
+    cudaError_t e = cudaSetDevice(d->index);
+    rc = (e == cudaSuccess) ? RELUX_OK : cuda_fail(e, "cudaSetDevice");
+  }
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+// 2-D bf16 tensor [rows][cols] (cols contiguous), box = box_cols x box_rows, 128-byte swizzle.
+static bool make_tmap_2d(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+static void pool_free_all(Pool* p) {
+  auto fr = [](void* q) { if (q) cudaFree(q); };
+  fr(p->storage); fr(p->d_table); fr(p->d_len); fr(p->d_status); fr(p->d_seq_ids); fr(p->d_row_off);
+  fr(p->in_a.p); fr(p->in_b.p); fr(p->out_buf.p); fr(p->q_abs.p); fr(p->part_o.p); fr(p->part_ml.p); fr(p->work.p);
+  fr(p->o_lat.p); fr(p->q_conv.p);
+  if (p->h_stage) cudaFreeHost(p->h_stage);
+  if (p->stage_ev) cudaEventDestroy(p->stage_ev);
+  if (p->ev0) cudaEventDestroy(p->ev0);
+  if (p->ev1) cudaEventDestroy(p->ev1);
+  p->magic = 0;
+  delete p;
+}
+
+static int32_t check_layer(Pool* p, int layer) {
+  if (layer < 0 || layer >= p->prm.num_layers) {
+    set_error("layerIdx=%d out of range [0, %d)", layer, p->prm.num_layers);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  return RELUX_OK;
+}
+
+// Moves an activation that arrives in host memory to the device staging block.
+static int32_t stage_in(Pool* p, GrowBuf& buf, const void* src, size_t bytes, int mem, const void** dptr) {
+  if (mem == RELUX_MEM_DEVICE) {
+    *dptr = src;
+    return RELUX_OK;
+  }
+  int32_t rc = grow(p->dev, buf, bytes);
+  if (rc) return rc;
+  RELUX_CUDA_TRY(cudaMemcpyAsync(buf.p, src, bytes, cudaMemcpyHostToDevice, p->dev->stream));
+  *dptr = buf.p;
+  return RELUX_OK;
+}
+
+static size_t dtype_size(int dt) { return dt == RELUX_DTYPE_BF16 ? 2 : 4; }
+
+static int32_t do_append(Pool* p, const relux_append_args* a, int kind) {
+  if (!a) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
+  if (p->prm.kind != kind) { set_error("pool kind does not match this append call"); return RELUX_ERR_INVALID_ARG; }
+  int32_t rc = check_layer(p, a->layer);
+  if (rc) return rc;
+  if (!a->a || !a->b) { set_error("nil input pointer"); return RELUX_ERR_INVALID_ARG; }
+  if ((a->dtype != RELUX_DTYPE_F32 && a->dtype != RELUX_DTYPE_BF16) || (a->mem != RELUX_MEM_HOST && a->mem != RELUX_MEM_DEVICE)) {
+    set_error("bad dtype/mem flag");
+    return RELUX_ERR_INVALID_ARG;
+  }
+  SeqBatch sb;
+  rc = stage_batch(p, a->n_seqs, a->seq_ids, a->n_new, 1, &sb);
+  if (rc) return rc;
+  // capacity check on the host shadow: the reference panics on overflow (kvcache.go:282-285)
+  const relux_pool_params& prm = p->prm;
+  for (int i = 0; i < sb.n_seqs; i++) {
+    int s = sb.seq[i];
+    int len = p->h_len[(size_t)a->layer * prm.max_seqs + s];
+    int cap = p->seq_pages[s] * prm.page_tokens;
+    if (len + sb.rows[i] > cap) {
+      set_error("Append: layer %d overflow: total=%d + newLen=%d > capacity=%d (sequence %d)", a->layer, len, sb.rows[i], cap, s);
+      return RELUX_ERR_OVERFLOW;
+    }
+  }
+  if (sb.total_rows == 0) return RELUX_OK;
+  size_t es = dtype_size(a->dtype);
+  const void *da = nullptr, *db = nullptr;
+  if (kind == RELUX_POOL_MLA) {
+    rc = stage_in(p, p->in_a, a->a, (size_t)sb.total_rows * prm.mla_dc * es, a->mem, &da);
+    if (rc) return rc;
+    rc = stage_in(p, p->in_b, a->b, (size_t)sb.total_rows * prm.mla_dhr * es, a->mem, &db);
+    if (rc) return rc;
+    rc = launch_mla_append(p, sb, a->layer, da, db, a->dtype, a->advance);
+  } else {
+    size_t bytes = (size_t)sb.total_rows * prm.gqa_num_kv_heads * prm.gqa_head_dim * es;
+    rc = stage_in(p, p->in_a, a->a, bytes, a->mem, &da);
+    if (rc) return rc;
+    rc = stage_in(p, p->in_b, a->b, bytes, a->mem, &db);
+    if (rc) return rc;
+    rc = launch_gqa_append(p, sb, a->layer, da, db, a->dtype, a->layout, a->advance);
+  }
+  if (rc) return rc;
+  if (a->advance)
+    for (int i = 0; i < sb.n_seqs; i++) p->h_len[(size_t)a->layer * prm.max_seqs + sb.seq[i]] += sb.rows[i];
+  return RELUX_OK;
+}
+
+// Converts q to the kernels' canonical device form and runs the attention, then delivers `out`.
+int32_t convert_layout(Device* dev, const void* src, void* dst, int n, int S, int H, int D, int src_dtype, int dst_dtype,
+                       int src_layout, int dst_layout);
+
+static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
+  if (!a) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
+  if (p->prm.kind != kind) { set_error("pool kind does not match this attention call"); return RELUX_ERR_INVALID_ARG; }
+  int32_t rc = check_layer(p, a->layer);
+  if (rc) return rc;
+  const relux_pool_params& prm = p->prm;
+  if (!a->q || !a->out || a->q_tokens <= 0 || a->num_heads <= 0 || a->head_dim <= 0 || a->extra_tokens < 0) {
+    set_error("bad attention arguments (nil q/out or non-positive sizes)");
+    return RELUX_ERR_INVALID_ARG;
+  }
+  if (kind == RELUX_POOL_MLA && (!a->q_rope || !a->w_uk || !a->w_uv)) {
+    set_error("MLA decode needs q_rope, w_uk and w_uv");
+    return RELUX_ERR_INVALID_ARG;
+  }
+  if (kind == RELUX_POOL_GQA && (a->head_dim != prm.gqa_head_dim || a->num_heads % prm.gqa_num_kv_heads != 0)) {
+    set_error("GQA decode: head_dim=%d (pool %d), num_heads=%d not a multiple of kv heads=%d", a->head_dim, prm.gqa_head_dim,
+              a->num_heads, prm.gqa_num_kv_heads);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  if (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE) { set_error("bad mode"); return RELUX_ERR_INVALID_ARG; }
+  SeqBatch sb;
+  rc = stage_batch(p, a->n_seqs, a->seq_ids, nullptr, a->q_tokens, &sb);
+  if (rc) return rc;
+  for (int i = 0; i < sb.n_seqs; i++) {
+    int s = sb.seq[i];
+    int T = p->h_len[(size_t)a->layer * prm.max_seqs + s] + a->extra_tokens;
+    if (T < a->q_tokens || T > p->seq_pages[s] * prm.page_tokens) {
+      set_error("sequence %d: %d cached rows (with extra_tokens) cannot serve %d query tokens within capacity %d", s, T,
+                a->q_tokens, p->seq_pages[s] * prm.page_tokens);
+      return RELUX_ERR_INVALID_ARG;
+    }
+  }
+  const int n = sb.n_seqs, S = a->q_tokens, H = a->num_heads, D = a->head_dim, R = prm.mla_dhr;
+  const size_t q_elems = (size_t)n * S * H * D, qr_elems = (size_t)n * S * H * R;
+  const void *dq = nullptr, *dqr = nullptr;
+  rc = stage_in(p, p->in_a, a->q, q_elems * dtype_size(a->q_dtype), a->q_mem, &dq);
+  if (rc) return rc;
+  if (kind == RELUX_POOL_MLA) {
+    rc = stage_in(p, p->in_b, a->q_rope, qr_elems * dtype_size(a->q_dtype), a->q_mem, &dqr);
+    if (rc) return rc;
+  }
+  // canonical kernel input: token-major; f32 for REFERENCE, caller's dtype for FAST
+  const int want_dtype = (a->mode == RELUX_ATTN_REFERENCE) ? RELUX_DTYPE_F32 : a->q_dtype;
+  const bool relayout_q = (a->q_layout == RELUX_LAYOUT_HEAD_MAJOR && S > 1) || want_dtype != a->q_dtype;
+  if (relayout_q) {
+    size_t need = (q_elems + qr_elems) * dtype_size(want_dtype);
+    rc = grow(p->dev, p->q_conv, need);
+    if (rc) return rc;
+    char* base = (char*)p->q_conv.p;
+    rc = convert_layout(p->dev, dq, base, n, S, H, D, a->q_dtype, want_dtype, a->q_layout, RELUX_LAYOUT_TOKEN_MAJOR);
+    if (rc) return rc;
+    dq = base;
+    if (kind == RELUX_POOL_MLA) {
+      char* b2 = base + q_elems * dtype_size(want_dtype);
+      rc = convert_layout(p->dev, dqr, b2, n, S, H, R, a->q_dtype, want_dtype, a->q_layout, RELUX_LAYOUT_TOKEN_MAJOR);
+      if (rc) return rc;
+      dqr = b2;
+    }
+  }
+  // kernels write f32 token-major into `kout`; deliver converts if the caller wants otherwise
+  const size_t out_elems = (size_t)n * S * H * D;
+  const bool direct = a->out_mem == RELUX_MEM_DEVICE && a->out_dtype == RELUX_DTYPE_F32 &&
+                      (a->out_layout == RELUX_LAYOUT_TOKEN_MAJOR || S == 1);
+  float* kout;
+  if (direct) kout = (float*)a->out;
+  else {
+    rc = grow(p->dev, p->out_buf, out_elems * 4 + out_elems * dtype_size(a->out_dtype));
+    if (rc) return rc;
+    kout = (float*)p->out_buf.p;
+  }
+  relux_attn_args aa = *a;
+  aa.q_dtype = want_dtype;
+  aa.q_layout = RELUX_LAYOUT_TOKEN_MAJOR;
+  if (a->mode == RELUX_ATTN_REFERENCE) {
+    rc = (kind == RELUX_POOL_MLA) ? launch_attn_reference_mla(p, sb, aa, (const float*)dq, (const float*)dqr, kout)
+                                  : launch_attn_reference_gqa(p, sb, aa, (const float*)dq, kout);
+  } else {
+    rc = (kind == RELUX_POOL_MLA) ? launch_mla_decode_fast(p, sb, aa, dq, dqr, kout) : launch_gqa_decode_fast(p, sb, aa, dq, kout);
+  }
+  if (rc) return rc;
+  if (!direct) {
+    void* conv = (char*)p->out_buf.p + out_elems * 4;
+    const bool need_conv = a->out_dtype != RELUX_DTYPE_F32 || (a->out_layout == RELUX_LAYOUT_HEAD_MAJOR && S > 1);
+    const void* src = kout;
+    if (need_conv) {
+      void* dst = (a->out_mem == RELUX_MEM_DEVICE) ? a->out : conv;
+      rc = convert_layout(p->dev, kout, dst, n, S, H, D, RELUX_DTYPE_F32, a->out_dtype, RELUX_LAYOUT_TOKEN_MAJOR, a->out_layout);
+      if (rc) return rc;
+      src = dst;
+    }
+    if (a->out_mem == RELUX_MEM_HOST) {
+      RELUX_CUDA_TRY(cudaMemcpyAsync(a->out, src, out_elems * dtype_size(a->out_dtype), cudaMemcpyDeviceToHost, p->dev->stream));
+      RELUX_CUDA_TRY(cudaStreamSynchronize(p->dev->stream));
+    }
+  }
+  return RELUX_OK;
+}
+
+}  // namespace relux
+
+using namespace relux;
+
+#define API extern "C" __attribute__((visibility("default")))
+#define GET_DEV(h)                                               \
+  Device* dev = as_device(h);                                    \
+  if (!dev) { set_error("bad device handle"); return RELUX_ERR_BAD_HANDLE; } \
+  DeviceGuard guard__(dev);                                      \
+  if (guard__.rc) return guard__.rc;
+#define GET_POOL(h)                                              \
+  Pool* p = as_pool(h);                                          \
+  if (!p) { set_error("bad pool handle"); return RELUX_ERR_BAD_HANDLE; } \
+  Device* dev = p->dev;                                          \
+  DeviceGuard guard__(dev);                                      \
+  if (guard__.rc) return guard__.rc;
+
+API int32_t relux_cuda_version(void) { return RELUX_CUDA_ABI_VERSION; }
+
+API int32_t relux_cuda_last_error(char* buf, int32_t buf_len) {
+  if (!buf || buf_len <= 0) return RELUX_ERR_INVALID_ARG;
+  snprintf(buf, (size_t)buf_len, "%s", g_err);
+  return RELUX_OK;
+}
+
+API int32_t relux_cuda_device_count(int32_t* count) {
+  if (!count) return RELUX_ERR_INVALID_ARG;
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) {
+    *count = 0;
+    return cuda_fail(e, "cudaGetDeviceCount");
+  }
+  *count = n;
+  return RELUX_OK;
+}
+
+API int32_t relux_cuda_device_open(int32_t device_index, relux_device_t* out) {
+  if (!out) return RELUX_ERR_INVALID_ARG;
+  *out = nullptr;
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGetDeviceCount");
+  if (n == 0) { set_error("no CUDA device"); return RELUX_ERR_NO_DEVICE; }
+  if (device_index < 0 || device_index >= n) { set_error("device index %d outside [0,%d)", device_index, n); return RELUX_ERR_INVALID_ARG; }
+  RELUX_CUDA_TRY(cudaSetDevice(device_index));
+  cudaDeviceProp prop;
+  RELUX_CUDA_TRY(cudaGetDeviceProperties(&prop, device_index));
+  if (prop.major != 10) {
+    set_error("device %d is sm_%d%d; this library holds sm_100a code only", device_index, prop.major, prop.minor);
+    return RELUX_ERR_UNSUPPORTED;
+  }
+  Device* d = new (std::nothrow) Device();
+  if (!d) return RELUX_ERR_OUT_OF_MEMORY;
+  d->index = device_index;
+  d->sm_count = prop.multiProcessorCount;
+  d->total_mem = prop.totalGlobalMem;
+  snprintf(d->name, sizeof(d->name), "%s", prop.name);
+  e = cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking);
+  if (e != cudaSuccess) { delete d; return cuda_fail(e, "cudaStreamCreate"); }
+  *out = d;
+  return RELUX_OK;
+}
+
+API int32_t relux_cuda_device_close(relux_device_t h) {
+  Device* dev = as_device(h);
+  if (!dev) { set_error("bad device handle"); return RELUX_ERR_BAD_HANDLE; }
+  {
+    DeviceGuard g(dev);
+    if (g.rc) return g.rc;
+    cudaStreamSynchronize(dev->stream);
+    if (dev->flush_buf) cudaFree(dev->flush_buf);
+    cudaStreamDestroy(dev->stream);
+    dev->magic = 0;
+  }
+  delete dev;
+  return RELUX_OK;
+}
+
+API int32_t relux_cuda_sync(relux_device_t h) {
+  GET_DEV(h);
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  return RELUX_OK;
+}
+
+API int32_t relux_cuda_device_info(relux_device_t h, char* name, int32_t name_len, int32_t* sm_count, int64_t* total_mem) {
+  GET_DEV(h);
+  if (name && name_len > 0) snprintf(name, (size_t)name_len, "%s", dev->name);
+  if (sm_count) *sm_count = dev->sm_count;
+  if (total_mem) *total_mem = (int64_t)dev->total_mem;
+  return RELUX_OK;
+}
+
+API int32_t relux_cuda_launch_count(relux_device_t h, int64_t* count) {
+  GET_DEV(h);
+  if (!count) return RELUX_ERR_INVALID_ARG;
+  *count = dev->launches;
+  return RELUX_OK;
+}
+
+API int32_t relux_cuda_stream(relux_device_t h, void** stream) {
+  GET_DEV(h);
+  if (!stream) return RELUX_ERR_INVALID_ARG;
+  *stream = (void*)dev->stream;
+  return RELUX_OK;
+}
+
+API int32_t relux_cuda_dev_alloc(relux_device_t h, size_t bytes, void** dptr) {
+  GET_DEV(h);
+  if (!dptr) return RELUX_ERR_INVALID_ARG;
+  *dptr = nullptr;
+  if (bytes == 0) return RELUX_OK;
+  RELUX_CUDA_TRY(cudaMalloc(dptr, bytes));
+  return RELUX_OK;
+}
+API int32_t relux_cuda_dev_free(relux_device_t h, void* dptr) {
+  GET_DEV(h);
+  if (!dptr) return RELUX_OK;
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  RELUX_CUDA_TRY(cudaFree(dptr));
+  return RELUX_OK;
+}
+API int32_t relux_cuda_host_alloc(relux_device_t h, size_t bytes, void** hptr) {
+  GET_DEV(h);
+  if (!hptr) return RELUX_ERR_INVALID_ARG;
+  *hptr = nullptr;
+  if (bytes == 0) return RELUX_OK;
+  RELUX_CUDA_TRY(cudaMallocHost(hptr, bytes));
+  return RELUX_OK;
+}
+API int32_t relux_cuda_host_free(relux_device_t h, void* hptr) {
+  GET_DEV(h);
+  if (!hptr) return RELUX_OK;
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  RELUX_CUDA_TRY(cudaFreeHost(hptr));
+  return RELUX_OK;
+}
+API int32_t relux_cuda_h2d(relux_device_t h, void* dst, const void* src, size_t bytes) {
+  GET_DEV(h);
+  if (bytes == 0) return RELUX_OK;
+  if (!dst || !src) return RELUX_ERR_INVALID_ARG;
+  RELUX_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, dev->stream));
+  return RELUX_OK;
+}
+API int32_t relux_cuda_d2h(relux_device_t h, void* dst, const void* src, size_t bytes) {
+  GET_DEV(h);
+  if (bytes == 0) return RELUX_OK;
+  if (!dst || !src) return RELUX_ERR_INVALID_ARG;
+  RELUX_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, dev->stream));
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  return RELUX_OK;
+}
+API int32_t relux_cuda_memset(relux_device_t h, void* dst, int32_t value, size_t bytes) {
+  GET_DEV(h);
+  if (bytes == 0) return RELUX_OK;
+  if (!dst) return RELUX_ERR_INVALID_ARG;
+  RELUX_CUDA_TRY(cudaMemsetAsync(dst, value, bytes, dev->stream));
+  return RELUX_OK;
+}
+
+API int32_t relux_cuda_event_create(relux_device_t h, relux_event_t* ev) {
+  GET_DEV(h);
+  if (!ev) return RELUX_ERR_INVALID_ARG;
+  cudaEvent_t e;
+  RELUX_CUDA_TRY(cudaEventCreate(&e));
+  *ev = (relux_event_t)e;
+  return RELUX_OK;
+}
+API int32_t relux_cuda_event_record(relux_device_t h, relux_event_t ev) {
+  GET_DEV(h);
+  if (!ev) return RELUX_ERR_INVALID_ARG;
+  RELUX_CUDA_TRY(cudaEventRecord((cudaEvent_t)ev, dev->stream));
+  return RELUX_OK;
+}
+API int32_t relux_cuda_event_elapsed_ms(relux_device_t h, relux_event_t a, relux_event_t b, float* ms) {
+  GET_DEV(h);
+  if (!a || !b || !ms) return RELUX_ERR_INVALID_ARG;
+  RELUX_CUDA_TRY(cudaEventSynchronize((cudaEvent_t)b));
+  RELUX_CUDA_TRY(cudaEventElapsedTime(ms, (cudaEvent_t)a, (cudaEvent_t)b));
+  return RELUX_OK;
+}
+API int32_t relux_cuda_event_destroy(relux_device_t h, relux_event_t ev) {
+  GET_DEV(h);
+  if (!ev) return RELUX_OK;
+  RELUX_CUDA_TRY(cudaEventDestroy((cudaEvent_t)ev));
+  return RELUX_OK;
+}
+API int32_t relux_cuda_flush_l2(relux_device_t h) {
+  GET_DEV(h);
+  const size_t bytes = (size_t)256 << 20;  // twice the 126 MB L2
+  if (!dev->flush_buf) {
+    RELUX_CUDA_TRY(cudaMalloc(&dev->flush_buf, bytes));
+    dev->flush_bytes = bytes;
+  }
+  RELUX_CUDA_TRY(cudaMemsetAsync(dev->flush_buf, 0, dev->flush_bytes, dev->stream));
+  return RELUX_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// pools
+// ---------------------------------------------------------------------------------------------
+API int32_t relux_pool_create(relux_device_t h, const relux_pool_params* prm, relux_pool_t* out) {
+  GET_DEV(h);
+  if (!prm || !out) { set_error("nil argument"); return RELUX_ERR_INVALID_ARG; }
+  *out = nullptr;
+  if (prm->num_layers <= 0) { set_error("NewCache: numLayers=%d, must be > 0", prm->num_layers); return RELUX_ERR_INVALID_ARG; }
+  if (prm->num_pages <= 0 || prm->page_tokens <= 0 || prm->max_seqs <= 0 || prm->max_pages_per_seq <= 0) {
+    set_error("NewCache: num_pages, page_tokens, max_seqs, max_pages_per_seq must all be > 0");
+    return RELUX_ERR_INVALID_ARG;
+  }
+  for (int i = 0; i < 6; i++)
+    if (prm->reserved[i]) { set_error("reserved fields must be zero"); return RELUX_ERR_INVALID_ARG; }
+  Pool* p = new (std::nothrow) Pool();
+  if (!p) return RELUX_ERR_OUT_OF_MEMORY;
+  p->dev = dev;
+  p->prm = *prm;
+  if (prm->kind == RELUX_POOL_MLA) {
+    if (prm->mla_dc <= 0 || prm->mla_dhr <= 0 || prm->mla_dhr % 2 || (prm->mla_dc % 8) || (prm->mla_dhr % 8)) {
+      set_error("MLA pool: dC=%d and dHR=%d must be positive multiples of 8 (16-byte rows)", prm->mla_dc, prm->mla_dhr);
+      delete p;
+      return RELUX_ERR_INVALID_ARG;
+    }
+    p->row_elems_a = prm->mla_dc + prm->mla_dhr;
+    p->page_elems = (size_t)prm->page_tokens * p->row_elems_a;
+    p->layer_elems = p->page_elems * prm->num_pages;
+  } else if (prm->kind == RELUX_POOL_GQA) {
+    if (prm->gqa_num_kv_heads <= 0 || prm->gqa_head_dim <= 0 || prm->gqa_head_dim % 8) {
+      set_error("GQA pool: num_kv_heads=%d, head_dim=%d (must be a positive multiple of 8)", prm->gqa_num_kv_heads, prm->gqa_head_dim);
+      delete p;
+      return RELUX_ERR_INVALID_ARG;
+    }
+    p->row_elems_a = prm->gqa_head_dim;
+    p->page_elems = (size_t)prm->gqa_num_kv_heads * prm->page_tokens * prm->gqa_head_dim;
+    p->layer_elems = 2 * p->page_elems * prm->num_pages;
+  } else {
+    set_error("unknown pool kind %d", prm->kind);
+    delete p;
+    return RELUX_ERR_INVALID_ARG;
+  }
+  const size_t storage_bytes = p->layer_elems * prm->num_layers * sizeof(uint16_t);
+  const size_t table_n = (size_t)prm->max_seqs * prm->max_pages_per_seq, len_n = (size_t)prm->num_layers * prm->max_seqs;
+  cudaError_t e = cudaSuccess;
+  auto A = [&](void** q, size_t bytes) { if (e == cudaSuccess) e = cudaMalloc(q, bytes); };
+  A((void**)&p->storage, storage_bytes);
+  A((void**)&p->d_table, table_n * 4);
+  A((void**)&p->d_len, len_n * 4);
+  A((void**)&p->d_status, 4);
+  A((void**)&p->d_seq_ids, (size_t)prm->max_seqs * 4);
+  A((void**)&p->d_row_off, ((size_t)prm->max_seqs + 1) * 4);
+  if (e == cudaSuccess) e = cudaMallocHost((void**)&p->h_stage, (2 * (size_t)prm->max_seqs + 1) * 4);
+  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->stage_ev, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaEventCreate(&p->ev0);
+  if (e == cudaSuccess) e = cudaEventCreate(&p->ev1);
+  if (e == cudaSuccess) e = cudaMemsetAsync(p->d_table, 0xFF, table_n * 4, dev->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(p->d_len, 0, len_n * 4, dev->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(p->d_status, 0, 4, dev->stream);
+  // The reference zero-fills new caches (kvcache.go:73-84, mla_cache.go:46-52).
+  if (e == cudaSuccess) e = cudaMemsetAsync(p->storage, 0, storage_bytes, dev->stream);
+  if (e != cudaSuccess) {
+    int32_t rc = cuda_fail(e, "pool allocation");
+    pool_free_all(p);
+    return rc;
+  }
+  p->h_table.assign(table_n, -1);
+  p->h_len.assign(len_n, 0);
+  p->seq_pages.assign(prm->max_seqs, 0);
+  p->seq_owned.assign(prm->max_seqs, 0);
+  p->free_pages.resize(prm->num_pages);
+  for (int i = 0; i < prm->num_pages; i++) p->free_pages[i] = prm->num_pages - 1 - i;
+  // TMA views of the storage: all layers form one 2-D array of 64-row page slabs
+  p->has_tmap = false;
+  if (prm->page_tokens == 64) {
+    if (prm->kind == RELUX_POOL_MLA && p->row_elems_a % 64 == 0) {
+      uint64_t rows = (uint64_t)prm->num_layers * prm->num_pages * prm->page_tokens;
+      p->has_tmap = make_tmap_2d(&p->tmap_mla, p->storage, rows, (uint64_t)p->row_elems_a, 64, 64);
+    } else if (prm->kind == RELUX_POOL_GQA && prm->gqa_head_dim % 64 == 0) {
+      uint64_t rows = (uint64_t)prm->num_layers * 2 * prm->num_pages * prm->gqa_num_kv_heads * prm->page_tokens;
+      p->has_tmap = make_tmap_2d(&p->tmap_gqa, p->storage, rows, (uint64_t)prm->gqa_head_dim, 64, 64);
+    }
+  }
+  *out = p;
+  return RELUX_OK;
+}
+
+API int32_t relux_pool_destroy(relux_pool_t h) {
+  GET_POOL(h);
+  cudaStreamSynchronize(dev->stream);
+  pool_free_all(p);
+  return RELUX_OK;
+}
+
+API int32_t relux_pool_reset(relux_pool_t h) {
+  GET_POOL(h);
+  const relux_pool_params& prm = p->prm;
+  std::fill(p->h_len.begin(), p->h_len.end(), 0);
+  for (int s = 0; s < prm.max_seqs; s++)
+    if (p->seq_owned[s]) {
+      for (int i = 0; i < p->seq_pages[s]; i++) p->free_pages.push_back(p->h_table[(size_t)s * prm.max_pages_per_seq + i]);
+      p->seq_pages[s] = 0;
+      p->seq_owned[s] = 0;
+    }
+  RELUX_CUDA_TRY(cudaMemsetAsync(p->d_len, 0, p->h_len.size() * 4, dev->stream));
+  RELUX_CUDA_TRY(cudaMemsetAsync(p->d_status, 0, 4, dev->stream));
+  return RELUX_OK;
+}
+
+API int32_t relux_pool_set_tables(relux_pool_t h, const int32_t* table, int32_t n_seqs, int32_t stride, const int32_t* ctx_len) {
+  GET_POOL(h);
+  const relux_pool_params& prm = p->prm;
+  if (!table || n_seqs <= 0 || n_seqs > prm.max_seqs || stride <= 0 || stride > prm.max_pages_per_seq) {
+    set_error("set_tables: n_seqs=%d (max %d), stride=%d (max %d)", n_seqs, prm.max_seqs, stride, prm.max_pages_per_seq);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  for (int s = 0; s < n_seqs; s++) {
+    if (p->seq_owned[s]) { set_error("sequence %d is owned by relux_seq_alloc", s); return RELUX_ERR_INVALID_ARG; }
+    for (int i = 0; i < stride; i++) {
+      int pg = table[(size_t)s * stride + i];
+      if (pg < 0 || pg >= prm.num_pages) {
+        set_error("page table entry [%d][%d]=%d outside [0,%d)", s, i, pg, prm.num_pages);
+        return RELUX_ERR_BAD_PAGE;
+      }
+    }
+    if (ctx_len && (ctx_len[s] < 0 || ctx_len[s] > stride * prm.page_tokens)) {
+      set_error("ctx_len[%d]=%d exceeds the %d tokens its pages hold", s, ctx_len[s], stride * prm.page_tokens);
+      return RELUX_ERR_OVERFLOW;
+    }
+  }
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  for (int s = 0; s < n_seqs; s++) {
+    for (int i = 0; i < stride; i++) p->h_table[(size_t)s * prm.max_pages_per_seq + i] = table[(size_t)s * stride + i];
+    p->seq_pages[s] = stride;
+    for (int l = 0; l < prm.num_layers; l++) p->h_len[(size_t)l * prm.max_seqs + s] = ctx_len ? ctx_len[s] : 0;
+  }
+  RELUX_CUDA_TRY(cudaMemcpy(p->d_table, p->h_table.data(), p->h_table.size() * 4, cudaMemcpyHostToDevice));
+  RELUX_CUDA_TRY(cudaMemcpy(p->d_len, p->h_len.data(), p->h_len.size() * 4, cudaMemcpyHostToDevice));
+  return RELUX_OK;
+}
+
+API int32_t relux_seq_alloc(relux_pool_t h, int32_t max_tokens, int32_t* seq_id) {
+  GET_POOL(h);
+  const relux_pool_params& prm = p->prm;
+  if (!seq_id || max_tokens <= 0) { set_error("seq_alloc: maxLen=%d, must be > 0", max_tokens); return RELUX_ERR_INVALID_ARG; }
+  int need = (max_tokens + prm.page_tokens - 1) / prm.page_tokens;
+  if (need > prm.max_pages_per_seq) { set_error("seq_alloc: %d tokens need %d pages, max_pages_per_seq=%d", max_tokens, need, prm.max_pages_per_seq); return RELUX_ERR_OVERFLOW; }
+  int s = -1;
+  for (int i = 0; i < prm.max_seqs; i++)
+    if (p->seq_pages[i] == 0) { s = i; break; }
+  if (s < 0 || (int)p->free_pages.size() < need) { set_error("pool exhausted: %d free pages, %d needed", (int)p->free_pages.size(), need); return RELUX_ERR_POOL_EXHAUSTED; }
+  for (int i = 0; i < need; i++) {
+    p->h_table[(size_t)s * prm.max_pages_per_seq + i] = p->free_pages.back();
+    p->free_pages.pop_back();
+  }
+  p->seq_pages[s] = need;
+  p->seq_owned[s] = 1;
+  for (int l = 0; l < prm.num_layers; l++) p->h_len[(size_t)l * prm.max_seqs + s] = 0;
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  RELUX_CUDA_TRY(cudaMemcpy(p->d_table + (size_t)s * prm.max_pages_per_seq, &p->h_table[(size_t)s * prm.max_pages_per_seq], (size_t)need * 4, cudaMemcpyHostToDevice));
+  for (int l = 0; l < prm.num_layers; l++) RELUX_CUDA_TRY(cudaMemset(p->d_len + (size_t)l * prm.max_seqs + s, 0, 4));
+  *seq_id = s;
+  return RELUX_OK;
+}
+
+API int32_t relux_seq_free(relux_pool_t h, int32_t s) {
+  GET_POOL(h);
+  const relux_pool_params& prm = p->prm;
+  if (s < 0 || s >= prm.max_seqs || p->seq_pages[s] == 0) { set_error("seq_free: sequence %d is not live", s); return RELUX_ERR_INVALID_ARG; }
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  if (p->seq_owned[s])
+    for (int i = 0; i < p->seq_pages[s]; i++) p->free_pages.push_back(p->h_table[(size_t)s * prm.max_pages_per_seq + i]);
+  p->seq_pages[s] = 0;
+  p->seq_owned[s] = 0;
+  for (int l = 0; l < prm.num_layers; l++) {
+    p->h_len[(size_t)l * prm.max_seqs + s] = 0;
+    RELUX_CUDA_TRY(cudaMemset(p->d_len + (size_t)l * prm.max_seqs + s, 0, 4));
+  }
+  return RELUX_OK;
+}
+
+API int32_t relux_seq_len(relux_pool_t h, int32_t layer, int32_t s, int32_t* len) {
+  GET_POOL(h);
+  if (!len) return RELUX_ERR_INVALID_ARG;
+  // TotalLen returns 0 for an out-of-range layer (kvcache.go:383-388)
+  if (layer < 0 || layer >= p->prm.num_layers || s < 0 || s >= p->prm.max_seqs) { *len = 0; return RELUX_OK; }
+  *len = p->h_len[(size_t)layer * p->prm.max_seqs + s];
+  return RELUX_OK;
+}
+
+API int32_t relux_seq_set_len(relux_pool_t h, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const int32_t* new_len) {
+  GET_POOL(h);
+  const relux_pool_params& prm = p->prm;
+  if (!new_len || layer >= prm.num_layers) { set_error("set_len: bad arguments"); return RELUX_ERR_INVALID_ARG; }
+  SeqBatch sb;
+  int32_t rc = stage_batch(p, n_seqs, seq_ids, nullptr, 1, &sb);
+  if (rc) return rc;
+  for (int i = 0; i < n_seqs; i++)
+    if (new_len[i] < 0 || new_len[i] > p->seq_pages[sb.seq[i]] * prm.page_tokens) {
+      set_error("set_len: length %d outside the capacity of sequence %d", new_len[i], sb.seq[i]);
+      return RELUX_ERR_OVERFLOW;
+    }
+  // lengths travel through the row-offset staging block
+  if (p->stage_busy) { RELUX_CUDA_TRY(cudaEventSynchronize(p->stage_ev)); p->stage_busy = false; }
+  int32_t* hs = p->h_stage + prm.max_seqs;
+  memcpy(hs, new_len, sizeof(int32_t) * n_seqs);
+  RELUX_CUDA_TRY(cudaMemcpyAsync(p->d_row_off, hs, sizeof(int32_t) * n_seqs, cudaMemcpyHostToDevice, dev->stream));
+  RELUX_CUDA_TRY(cudaEventRecord(p->stage_ev, dev->stream));
+  p->stage_busy = true;
+  int l0 = layer < 0 ? 0 : layer, l1 = layer < 0 ? prm.num_layers : layer + 1;
+  for (int l = l0; l < l1; l++) {
+    rc = launch_set_len(p, sb, l, p->d_row_off);
+    if (rc) return rc;
+    for (int i = 0; i < n_seqs; i++) p->h_len[(size_t)l * prm.max_seqs + sb.seq[i]] = new_len[i];
+  }
+  return RELUX_OK;
+}
+
+API int32_t relux_pool_status(relux_pool_t h, int32_t* status) {
+  GET_POOL(h);
+  if (!status) return RELUX_ERR_INVALID_ARG;
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  RELUX_CUDA_TRY(cudaMemcpy(status, p->d_status, 4, cudaMemcpyDeviceToHost));
+  if (*status) RELUX_CUDA_TRY(cudaMemset(p->d_status, 0, 4));
+  return RELUX_OK;
+}
+
+API int32_t relux_pool_read_rows(relux_pool_t h, int32_t layer, int32_t s, int32_t tok0, int32_t n, void* dst_a, void* dst_b) {
+  GET_POOL(h);
+  const relux_pool_params& prm = p->prm;
+  int32_t rc = check_layer(p, layer);
+  if (rc) return rc;
+  if (s < 0 || s >= prm.max_seqs || p->seq_pages[s] == 0 || tok0 < 0 || n < 0 || tok0 + n > p->seq_pages[s] * prm.page_tokens) {
+    set_error("read_rows: sequence %d rows [%d,%d) outside its capacity", s, tok0, tok0 + n);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  if (n == 0) return RELUX_OK;
+  size_t ea, eb;
+  if (prm.kind == RELUX_POOL_MLA) { ea = (size_t)n * prm.mla_dc; eb = (size_t)n * prm.mla_dhr; }
+  else { ea = eb = (size_t)n * prm.gqa_num_kv_heads * prm.gqa_head_dim; }
+  rc = grow(dev, p->out_buf, (ea + eb) * 2);
+  if (rc) return rc;
+  uint16_t* da = (uint16_t*)p->out_buf.p;
+  uint16_t* db = da + ea;
+  rc = launch_gather_rows(p, layer, s, tok0, n, da, db);
+  if (rc) return rc;
+  if (dst_a) RELUX_CUDA_TRY(cudaMemcpyAsync(dst_a, da, ea * 2, cudaMemcpyDeviceToHost, dev->stream));
+  if (dst_b) RELUX_CUDA_TRY(cudaMemcpyAsync(dst_b, db, eb * 2, cudaMemcpyDeviceToHost, dev->stream));
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  return RELUX_OK;
+}
+
+API int32_t relux_mla_append(relux_pool_t h, const relux_append_args* a) {
+  GET_POOL(h);
+  return do_append(p, a, RELUX_POOL_MLA);
+}
+API int32_t relux_gqa_append(relux_pool_t h, const relux_append_args* a) {
+  GET_POOL(h);
+  return do_append(p, a, RELUX_POOL_GQA);
+}
+API int32_t relux_mla_decode(relux_pool_t h, const relux_attn_args* a) {
+  GET_POOL(h);
+  return do_attention(p, a, RELUX_POOL_MLA);
+}
+API int32_t relux_gqa_decode(relux_pool_t h, const relux_attn_args* a) {
+  GET_POOL(h);
+  return do_attention(p, a, RELUX_POOL_GQA);
+}
+
+static int32_t do_verify(Pool* p, const relux_attn_args* attn, const relux_append_args* kv, int kind) {
+  if (!attn || !kv) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
+  if (kv->advance != 0) { set_error("verify: draft rows must be appended with advance=0"); return RELUX_ERR_INVALID_ARG; }
+  if (kv->layer != attn->layer || kv->n_seqs != attn->n_seqs) { set_error("verify: append and attention arguments disagree"); return RELUX_ERR_INVALID_ARG; }
+  if (attn->extra_tokens != attn->q_tokens) { set_error("verify: extra_tokens must equal q_tokens"); return RELUX_ERR_INVALID_ARG; }
+  int32_t rc = do_append(p, kv, kind);
+  if (rc) return rc;
+  return do_attention(p, attn, kind);
+}
+API int32_t relux_gqa_verify(relux_pool_t h, const relux_attn_args* attn, const relux_append_args* kv) {
+  GET_POOL(h);
+  return do_verify(p, attn, kv, RELUX_POOL_GQA);
+}
+API int32_t relux_mla_verify(relux_pool_t h, const relux_attn_args* attn, const relux_append_args* kv) {
+  GET_POOL(h);
+  return do_verify(p, attn, kv, RELUX_POOL_MLA);
+}
+
+API int32_t relux_pool_last_kernel_ms(relux_pool_t h, float* ms) {
+  GET_POOL(h);
+  if (!ms) return RELUX_ERR_INVALID_ARG;
+  if (!p->timed) { set_error("no attention kernel has been timed on this pool yet"); return RELUX_ERR_INVALID_ARG; }
+  RELUX_CUDA_TRY(cudaEventSynchronize(p->ev1));
+  RELUX_CUDA_TRY(cudaEventElapsedTime(ms, p->ev0, p->ev1));
+  return RELUX_OK;
+}

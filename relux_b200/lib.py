@@ -1,0 +1,131 @@
+"""ctypes binding of librelux_cuda.so (the C ABI declared in include/relux_cuda.h).
+
+This is the Python stand-in for the purego binding a Go caller would write: same entry points, same
+argument structs.  There is no fallback: if the shared library is missing or a call fails, an exception
+is raised.
+"""
+import ctypes as C
+import os
+import subprocess
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+SO_PATH = os.path.join(_HERE, "librelux_cuda.so")
+CSRC = os.path.join(_HERE, "csrc")
+
+OK = 0
+ERR_INVALID_ARG, ERR_CUDA, ERR_OUT_OF_MEMORY, ERR_POOL_EXHAUSTED, ERR_OVERFLOW = -1, -2, -3, -4, -5
+ERR_BAD_PAGE, ERR_TIMEOUT, ERR_BAD_HANDLE, ERR_UNSUPPORTED, ERR_NO_DEVICE = -6, -7, -8, -9, -10
+DTYPE_F32, DTYPE_BF16 = 0, 1
+MEM_HOST, MEM_DEVICE = 0, 1
+LAYOUT_TOKEN_MAJOR, LAYOUT_HEAD_MAJOR = 0, 1
+POOL_MLA, POOL_GQA = 0, 1
+ATTN_FAST, ATTN_REFERENCE = 0, 1
+
+# Every symbol include/relux_cuda.h declares; tests check that the library exports each one.
+EXPORTS = [
+    "relux_cuda_version", "relux_cuda_device_count", "relux_cuda_device_open", "relux_cuda_device_close", "relux_cuda_sync",
+    "relux_cuda_last_error", "relux_cuda_device_info", "relux_cuda_launch_count", "relux_cuda_stream", "relux_cuda_dev_alloc",
+    "relux_cuda_dev_free", "relux_cuda_host_alloc", "relux_cuda_host_free", "relux_cuda_h2d", "relux_cuda_d2h",
+    "relux_cuda_memset", "relux_cuda_event_create", "relux_cuda_event_record", "relux_cuda_event_elapsed_ms",
+    "relux_cuda_event_destroy", "relux_cuda_flush_l2", "relux_pool_create", "relux_pool_destroy", "relux_pool_reset",
+    "relux_pool_set_tables", "relux_seq_alloc", "relux_seq_free", "relux_seq_len", "relux_seq_set_len", "relux_pool_status",
+    "relux_pool_read_rows", "relux_mla_append", "relux_gqa_append", "relux_mla_decode", "relux_gqa_decode", "relux_gqa_verify",
+    "relux_mla_verify", "relux_pool_last_kernel_ms",
+]
+
+
+class PoolParams(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("num_layers", C.c_int32), ("num_pages", C.c_int32), ("page_tokens", C.c_int32),
+                ("max_seqs", C.c_int32), ("max_pages_per_seq", C.c_int32), ("mla_dc", C.c_int32), ("mla_dhr", C.c_int32),
+                ("gqa_num_kv_heads", C.c_int32), ("gqa_head_dim", C.c_int32), ("reserved", C.c_int32 * 6)]
+
+
+class AppendArgs(C.Structure):
+    _fields_ = [("layer", C.c_int32), ("n_seqs", C.c_int32), ("seq_ids", C.c_void_p), ("n_new", C.c_void_p),
+                ("a", C.c_void_p), ("b", C.c_void_p), ("dtype", C.c_int32), ("mem", C.c_int32), ("layout", C.c_int32),
+                ("advance", C.c_int32), ("reserved", C.c_int32 * 4)]
+
+
+class AttnArgs(C.Structure):
+    _fields_ = [("layer", C.c_int32), ("n_seqs", C.c_int32), ("seq_ids", C.c_void_p), ("q_tokens", C.c_int32),
+                ("extra_tokens", C.c_int32), ("causal", C.c_int32), ("num_heads", C.c_int32), ("head_dim", C.c_int32),
+                ("scale", C.c_float), ("q", C.c_void_p), ("q_rope", C.c_void_p), ("q_dtype", C.c_int32), ("q_mem", C.c_int32),
+                ("q_layout", C.c_int32), ("w_uk", C.c_void_p), ("w_uv", C.c_void_p), ("out", C.c_void_p),
+                ("out_dtype", C.c_int32), ("out_mem", C.c_int32), ("out_layout", C.c_int32), ("mode", C.c_int32),
+                ("reserved", C.c_int32 * 5)]
+
+
+class ReluxCudaError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__("librelux_cuda status %d: %s" % (code, msg))
+        self.code = code
+
+
+def build(force=False, verbose=False):
+    """Compiles librelux_cuda.so for sm_100a with nvcc (cross-compiles without a GPU)."""
+    args = ["make", "-C", CSRC, "-j8"] + ([] if verbose else ["-s"])
+    if force:
+        subprocess.check_call(["make", "-C", CSRC, "clean", "-s"])
+    subprocess.check_call(args)
+    return SO_PATH
+
+
+_lib = None
+
+
+def load():
+    """Loads the shared library (never builds, never falls back)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(SO_PATH):
+            raise FileNotFoundError("%s is missing: run `python -c 'import __graft_entry__ as g; g.build()'` or "
+                                    "`make -C relux_b200/csrc`; there is no CPU fallback" % SO_PATH)
+        L = C.CDLL(SO_PATH)
+        for name in EXPORTS:
+            getattr(L, name).restype = C.c_int32
+        L.relux_cuda_dev_alloc.argtypes = [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]
+        L.relux_cuda_host_alloc.argtypes = [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)]
+        L.relux_cuda_dev_free.argtypes = [C.c_void_p, C.c_void_p]
+        L.relux_cuda_host_free.argtypes = [C.c_void_p, C.c_void_p]
+        L.relux_cuda_h2d.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
+        L.relux_cuda_d2h.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t]
+        L.relux_cuda_memset.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_size_t]
+        L.relux_cuda_sync.argtypes = [C.c_void_p]
+        L.relux_cuda_device_close.argtypes = [C.c_void_p]
+        L.relux_cuda_flush_l2.argtypes = [C.c_void_p]
+        L.relux_cuda_event_create.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+        L.relux_cuda_event_record.argtypes = [C.c_void_p, C.c_void_p]
+        L.relux_cuda_event_elapsed_ms.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(C.c_float)]
+        L.relux_cuda_event_destroy.argtypes = [C.c_void_p, C.c_void_p]
+        L.relux_pool_create.argtypes = [C.c_void_p, C.POINTER(PoolParams), C.POINTER(C.c_void_p)]
+        for n in ("relux_pool_destroy", "relux_pool_reset"):
+            getattr(L, n).argtypes = [C.c_void_p]
+        L.relux_pool_set_tables.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
+        L.relux_seq_alloc.argtypes = [C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]
+        L.relux_seq_free.argtypes = [C.c_void_p, C.c_int32]
+        L.relux_seq_len.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int32)]
+        L.relux_seq_set_len.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+        L.relux_pool_status.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
+        L.relux_pool_read_rows.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+        for n in ("relux_mla_append", "relux_gqa_append"):
+            getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AppendArgs)]
+        for n in ("relux_mla_decode", "relux_gqa_decode"):
+            getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AttnArgs)]
+        for n in ("relux_gqa_verify", "relux_mla_verify"):
+            getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AttnArgs), C.POINTER(AppendArgs)]
+        L.relux_pool_last_kernel_ms.argtypes = [C.c_void_p, C.POINTER(C.c_float)]
+        L.relux_cuda_launch_count.argtypes = [C.c_void_p, C.POINTER(C.c_int64)]
+        L.relux_cuda_stream.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+        _lib = L
+    return _lib
+
+
+def last_error():
+    buf = C.create_string_buffer(512)
+    load().relux_cuda_last_error(buf, 512)
+    return buf.value.decode("utf-8", "replace")
+
+
+def check(rc):
+    if rc != OK:
+        raise ReluxCudaError(rc, last_error())

@@ -1,0 +1,76 @@
+"""CPU-side checks of the C-ABI boundary: the library loads, exports every symbol the header declares,
+and fails cleanly (status + message, no crash) when no GPU is present."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def so():
+    import __graft_entry__ as g
+    g.build()
+    from relux_b200 import lib as L
+    return L
+
+
+def header_functions():
+    src = open(os.path.join(ROOT, "include", "relux_cuda.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\bint32_t\s+(relux_\w+)\s*\(", src)))
+
+
+def test_header_and_binding_agree(so):
+    assert header_functions() == sorted(so.EXPORTS)
+
+
+def test_every_declared_symbol_is_exported(so):
+    lib = C.CDLL(so.SO_PATH)
+    for name in header_functions():
+        assert hasattr(lib, name), "librelux_cuda.so does not export %s" % name
+
+
+def test_version_and_error_text(so):
+    lib = so.load()
+    assert lib.relux_cuda_version() == 1
+    buf = C.create_string_buffer(64)
+    assert lib.relux_cuda_last_error(buf, 64) == 0
+
+
+def test_bad_handles_are_rejected(so):
+    lib = so.load()
+    assert lib.relux_cuda_sync(None) == so.ERR_BAD_HANDLE
+    assert lib.relux_pool_destroy(None) == so.ERR_BAD_HANDLE
+    args = so.AppendArgs()
+    assert lib.relux_mla_append(None, C.byref(args)) == so.ERR_BAD_HANDLE
+
+
+def test_struct_sizes_match_the_header(so):
+    # relux_pool_params: 16 int32; relux_append_args / relux_attn_args as laid out by a C compiler
+    assert C.sizeof(so.PoolParams) == 64
+    import subprocess, tempfile, textwrap
+    prog = textwrap.dedent("""
+        #include <stdio.h>
+        #include "relux_cuda.h"
+        int main(void){ printf("%zu %zu %zu\\n", sizeof(relux_pool_params), sizeof(relux_append_args), sizeof(relux_attn_args)); return 0; }
+    """)
+    with tempfile.TemporaryDirectory() as d:
+        c = os.path.join(d, "s.c")
+        open(c, "w").write(prog)
+        exe = os.path.join(d, "s")
+        subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
+        sizes = [int(x) for x in subprocess.check_output([exe]).split()]
+    assert sizes == [C.sizeof(so.PoolParams), C.sizeof(so.AppendArgs), C.sizeof(so.AttnArgs)]
+
+
+def test_no_gpu_means_a_clean_error(so):
+    from tests.helpers import have_gpu
+    if have_gpu():
+        pytest.skip("a GPU is present")
+    import relux_b200 as rb
+    with pytest.raises(so.ReluxCudaError) as e:
+        rb.Device(0)
+    assert e.value.code in (so.ERR_NO_DEVICE, so.ERR_CUDA)

@@ -1,0 +1,233 @@
+"""Cached-attention parity on the GPU against the CPU oracle (calls go through the C ABI).
+
+RELUX_ATTN_REFERENCE must match the oracle BIT FOR BIT (same float32 operation order, same fastexp32).
+RELUX_ATTN_FAST (bf16 tensor-core arithmetic, exact exp2 softmax) is checked two ways:
+  * against the oracle's reference arithmetic at context lengths of the benchmark configs' order, within the
+    stated tolerance max-abs 2e-2 / mean-abs 2e-3;
+  * against the oracle with libm exp (oracle.exact_exp) at short and page-boundary lengths, with a tighter
+    tolerance.  At a few dozen tokens the reference's fastexp32 (-3.3 % .. +2.7 % per weight) alone moves the
+    output by about 3e-3, which would mask indexing or masking mistakes; the exact-exp comparison cannot."""
+
+EDGE_MAX, EDGE_MEAN = 1e-2, 1e-3
+import numpy as np
+import pytest
+
+from tests.helpers import check_attention, permuted_tables, ragged_to_padded
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    import relux_b200 as rb
+    d = rb.Device(0)
+    yield d
+    d.close()
+
+
+def build_gqa(dev, oracle, rng, ctx, Hkv, D, P=64, extra_pages=1):
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    B = len(ctx)
+    pages_per = (int(max(ctx)) + P - 1) // P + extra_pages
+    pool = rb.Pool(dev, L.POOL_GQA, 1, B * pages_per, P, B, pages_per, num_kv_heads=Hkv, head_dim=D)
+    pool.set_tables(permuted_tables(rng, B, pages_per))
+    K = rng.standard_normal((int(np.sum(ctx)), Hkv, D)).astype(np.float32)
+    V = rng.standard_normal((int(np.sum(ctx)), Hkv, D)).astype(np.float32)
+    pool.append(0, K, V, B, n_new=np.asarray(ctx, np.int32))
+    Kl = ragged_to_padded(oracle.bf16_from_f32(K), ctx, (Hkv, D))
+    Vl = ragged_to_padded(oracle.bf16_from_f32(V), ctx, (Hkv, D))
+    return pool, Kl, Vl
+
+
+def build_mla(dev, oracle, rng, ctx, dC, dHR, P=64, extra_pages=1):
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    B = len(ctx)
+    pages_per = (int(max(ctx)) + P - 1) // P + extra_pages
+    pool = rb.Pool(dev, L.POOL_MLA, 1, B * pages_per, P, B, pages_per, dC=dC, dHR=dHR)
+    pool.set_tables(permuted_tables(rng, B, pages_per))
+    c = rng.standard_normal((int(np.sum(ctx)), dC)).astype(np.float32)
+    r = rng.standard_normal((int(np.sum(ctx)), dHR)).astype(np.float32)
+    pool.append(0, c, r, B, n_new=np.asarray(ctx, np.int32))
+    cl = ragged_to_padded(oracle.bf16_from_f32(c), ctx, (dC,))
+    rl = ragged_to_padded(oracle.bf16_from_f32(r), ctx, (dHR,))
+    return pool, cl, rl
+
+
+# ---------------------------------------------------------------- REFERENCE arithmetic: bit-exact
+@pytest.mark.parametrize("S,causal", [(1, True), (3, True), (3, False)])
+def test_gqa_reference_mode_is_bit_exact(dev, oracle, S, causal):
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(11)
+    ctx = [1 + S, 17, 63 + S, 64, 65, 200]
+    H, Hkv, D = 4, 2, 16
+    pool, Kl, Vl = build_gqa(dev, oracle, rng, ctx, Hkv, D, P=16)
+    q = rng.standard_normal((len(ctx), S, H, D)).astype(np.float32)
+    out = np.empty_like(q)
+    scale = np.float32(1.0 / np.sqrt(D))
+    pool.decode(0, len(ctx), q, out, H, D, float(scale), q_tokens=S, causal=causal, mode=L.ATTN_REFERENCE)
+    ref = oracle.gqa_attend(Kl, Vl, ctx, q, float(scale), causal=causal)
+    assert np.array_equal(out, ref), "max diff %g" % np.abs(out - ref).max()
+    pool.destroy()
+
+
+@pytest.mark.parametrize("S,causal", [(1, True), (2, True), (2, False)])
+def test_mla_reference_mode_is_bit_exact(dev, oracle, S, causal):
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(12)
+    ctx = [S, 33, 64, 65, 130]
+    H, Dh, dC, dHR = 8, 32, 64, 16
+    pool, cl, rl = build_mla(dev, oracle, rng, ctx, dC, dHR)
+    wuk = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.1)
+    wuv = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.1)
+    d_wuk, d_wuv = dev.upload(wuk), dev.upload(wuv)
+    qc = rng.standard_normal((len(ctx), S, H, Dh)).astype(np.float32)
+    qr = rng.standard_normal((len(ctx), S, H, dHR)).astype(np.float32)
+    out = np.empty_like(qc)
+    scale = np.float32(1.0 / np.sqrt(Dh + dHR))
+    pool.decode(0, len(ctx), qc, out, H, Dh, float(scale), q_rope=qr, w_uk=d_wuk, w_uv=d_wuv, q_tokens=S, causal=causal,
+                mode=L.ATTN_REFERENCE)
+    ref = oracle.mla_attend(cl, rl, ctx, qc, qr, wuk, wuv, float(scale), causal=causal)
+    assert np.array_equal(out, ref), "max diff %g" % np.abs(out - ref).max()
+    pool.destroy(); d_wuk.free(); d_wuv.free()
+
+
+# ---------------------------------------------------------------- FAST: tolerance
+@pytest.mark.parametrize("S", [1, 4])
+def test_gqa_fast_decode_and_verify(dev, oracle, S):
+    """config-5 shapes (32 heads, 8 kv heads, head dim 128, page 64) at lengths the oracle finishes in seconds;
+    includes lengths around page boundaries and a ragged batch."""
+    rng = np.random.default_rng(3)
+    H, Hkv, D = 32, 8, 128
+    scale = float(1.0 / np.sqrt(D))
+    # (a) edge lengths against the exact-exp oracle
+    ctx = [S, 63, 64, 65, 127 + S, 129, 700]
+    pool, Kl, Vl = build_gqa(dev, oracle, rng, ctx, Hkv, D)
+    B = len(ctx)
+    q = rng.standard_normal((B, S, H, D)).astype(np.float32)
+    out = np.empty_like(q)
+    pool.decode(0, B, q, out, H, D, scale, q_tokens=S, causal=True)
+    with oracle.exact_exp():
+        ref = oracle.gqa_attend(Kl, Vl, ctx, q, scale, causal=True)
+    check_attention(out, ref, "gqa fast edge S=%d" % S, max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+    # bf16 q from device memory, bf16 output
+    qb = oracle.bf16_from_f32(q)
+    d_q = dev.upload(qb)
+    d_out = dev.alloc(out.size * 2)
+    pool.decode(0, B, d_q, d_out, H, D, scale, q_tokens=S, causal=True)
+    out2 = oracle.f32_from_bf16(d_out.download(out.shape, np.uint16))
+    with oracle.exact_exp():
+        ref2 = oracle.gqa_attend(Kl, Vl, ctx, oracle.f32_from_bf16(qb), scale, causal=True)
+    check_attention(out2, ref2, "gqa fast bf16 io S=%d" % S, bf16_output=True, max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+    assert pool.status() == 0
+    pool.destroy(); d_q.free(); d_out.free()
+    # (b) config-5 context length (8192) against the reference arithmetic, stated tolerance
+    ctx = [8192, 8192 - 37, 4096 + S]
+    pool, Kl, Vl = build_gqa(dev, oracle, rng, ctx, Hkv, D)
+    B = len(ctx)
+    q = rng.standard_normal((B, S, H, D)).astype(np.float32)
+    out = np.empty_like(q)
+    pool.decode(0, B, q, out, H, D, scale, q_tokens=S, causal=True)
+    ref = oracle.gqa_attend(Kl, Vl, ctx, q, scale, causal=True)
+    check_attention(out, ref, "gqa fast ctx8192 S=%d" % S)
+    assert pool.status() == 0
+    pool.destroy()
+
+
+def test_gqa_verify_then_commit_accepted_prefix(dev, oracle):
+    """config 5's step: verify 4 draft tokens (causal inside the draft), keep an accepted prefix of 1..4, go on."""
+    rng = np.random.default_rng(5)
+    ctx = np.array([100, 64, 190], np.int32)
+    H, Hkv, D, S, B = 32, 8, 128, 4, 3
+    pool, Kl, Vl = build_gqa(dev, oracle, rng, ctx, Hkv, D, extra_pages=2)
+    scale = float(1.0 / np.sqrt(D))
+    Kc = [oracle.f32_from_bf16(Kl[b, :ctx[b]]) for b in range(B)]   # logical caches as f32 of the stored bf16
+    Vc = [oracle.f32_from_bf16(Vl[b, :ctx[b]]) for b in range(B)]
+    for step in range(3):
+        dK = rng.standard_normal((B * S, Hkv, D)).astype(np.float32)
+        dV = rng.standard_normal((B * S, Hkv, D)).astype(np.float32)
+        q = rng.standard_normal((B, S, H, D)).astype(np.float32)
+        out = np.empty_like(q)
+        pool.verify(0, B, q, out, dK, dV, H, D, scale, S)
+        lens = np.array([len(k) for k in Kc], np.int32)
+        Tm = int(lens.max()) + S
+        Kp = np.zeros((B, Tm, Hkv, D), np.uint16); Vp = np.zeros_like(Kp)
+        for b in range(B):
+            Kp[b, :lens[b] + S] = oracle.bf16_from_f32(np.concatenate([Kc[b], dK[b * S:(b + 1) * S]]))
+            Vp[b, :lens[b] + S] = oracle.bf16_from_f32(np.concatenate([Vc[b], dV[b * S:(b + 1) * S]]))
+        with oracle.exact_exp():
+            ref = oracle.gqa_attend(Kp, Vp, lens + S, q, scale, causal=True)
+        check_attention(out, ref, "verify step %d" % step, max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+        accepted = rng.integers(1, S + 1, B).astype(np.int32)
+        pool.set_len(0, lens + accepted)
+        for b in range(B):
+            Kc[b] = oracle.f32_from_bf16(oracle.bf16_from_f32(np.concatenate([Kc[b], dK[b * S:b * S + accepted[b]]])))
+            Vc[b] = oracle.f32_from_bf16(oracle.bf16_from_f32(np.concatenate([Vc[b], dV[b * S:b * S + accepted[b]]])))
+            assert pool.seq_len(0, b) == len(Kc[b])
+            gk, gv = pool.read_rows(0, b, 0, len(Kc[b]))
+            assert np.array_equal(gk, oracle.bf16_from_f32(Kc[b])) and np.array_equal(gv, oracle.bf16_from_f32(Vc[b]))
+    assert pool.status() == 0
+    pool.destroy()
+
+
+@pytest.mark.parametrize("shape", ["v2", "small"])
+@pytest.mark.parametrize("S", [1, 2])
+def test_mla_fast_decode(dev, oracle, shape, S):
+    """config-3 widths (128 heads, latent 512, rope 64, nope/v 128) and config-2 widths, ragged lengths."""
+    rng = np.random.default_rng(7)
+    if shape == "v2":
+        H, Dh, dC, dHR = 128, 128, 512, 64
+        ctx = [S, 64, 65, 200, 333]
+        wstd = 0.02
+    else:
+        H, Dh, dC, dHR = 8, 32, 64, 16
+        ctx = [S, 31, 64, 65, 512]
+        wstd = 0.1
+    B = len(ctx)
+    pool, cl, rl = build_mla(dev, oracle, rng, ctx, dC, dHR)
+    wuk = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * wstd)
+    wuv = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * wstd)
+    d_wuk, d_wuv = dev.upload(wuk), dev.upload(wuv)
+    qc = rng.standard_normal((B, S, H, Dh)).astype(np.float32)
+    qr = rng.standard_normal((B, S, H, dHR)).astype(np.float32)
+    out = np.empty_like(qc)
+    scale = float(1.0 / np.sqrt(Dh + dHR))
+    pool.decode(0, B, qc, out, H, Dh, scale, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv, q_tokens=S, causal=True)
+    with oracle.exact_exp():
+        ref = oracle.mla_attend(cl, rl, ctx, qc, qr, wuk, wuv, scale, causal=True, absorbed=(shape == "v2"))
+    check_attention(out, ref, "mla fast edge %s S=%d" % (shape, S), max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+    assert pool.status() == 0
+    pool.destroy()
+    # config-3 context length (4096 + new tokens) against the reference arithmetic, stated tolerance
+    ctx = [4096 + S, 4096 - 100] if shape == "v2" else [512, 480]
+    B = len(ctx)
+    pool, cl, rl = build_mla(dev, oracle, rng, ctx, dC, dHR)
+    qc = rng.standard_normal((B, S, H, Dh)).astype(np.float32)
+    qr = rng.standard_normal((B, S, H, dHR)).astype(np.float32)
+    out = np.empty_like(qc)
+    pool.decode(0, B, qc, out, H, Dh, scale, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv, q_tokens=S, causal=True)
+    ref = oracle.mla_attend(cl, rl, ctx, qc, qr, wuk, wuv, scale, causal=True, absorbed=(shape == "v2"))
+    check_attention(out, ref, "mla fast cfg-length %s S=%d" % (shape, S))
+    assert pool.status() == 0
+    pool.destroy(); d_wuk.free(); d_wuv.free()
+
+
+def test_head_major_layout_round_trip(dev, oracle):
+    """The reference hands q as [1,H,S,D] (after rearrangeBSNH); the cache objects accept that layout."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(9)
+    H, Hkv, D, S = 4, 2, 16, 3
+    c = rb.KVCache(dev, 1, 64, Hkv, D, page_tokens=16)
+    k = rng.standard_normal((1, Hkv, 20, D)).astype(np.float32)
+    v = rng.standard_normal((1, Hkv, 20, D)).astype(np.float32)
+    c.Append(0, k, v)
+    q = rng.standard_normal((1, H, S, D)).astype(np.float32)
+    scale = float(np.float32(1.0 / np.sqrt(D)))
+    out = c.attend(0, q, scale, causal=True, mode=L.ATTN_REFERENCE)
+    Kl = oracle.bf16_from_f32(k[0].transpose(1, 0, 2))[None]
+    Vl = oracle.bf16_from_f32(v[0].transpose(1, 0, 2))[None]
+    ref = oracle.gqa_attend(Kl, Vl, [20], q.transpose(0, 2, 1, 3), scale, causal=True)
+    assert np.array_equal(out, ref.transpose(0, 2, 1, 3))
+    c.close()
