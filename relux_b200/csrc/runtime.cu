@@ -1,6 +1,7 @@
 // Runtime half of librelux_cuda: handles, errors, memory, paged pools, page tables, and the
 // C-ABI entry points that validate arguments and dispatch to the kernels.
 #include <algorithm>
+#include <cstdlib>
 #include <new>
 
 #include "internal.h"

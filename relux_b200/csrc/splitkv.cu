@@ -4,6 +4,7 @@
 // is one work item handled by one CTA (or CTA pair), so a handful of long sequences still fills
 // all SMs.  The list is built on the device from the device-resident lengths; the host computes
 // only the item COUNT from its shadow lengths, so no host->device copy is needed per step.
+#include <cstdlib>
 #include "common.cuh"
 #include "internal.h"
 #include "splitkv.h"
@@ -40,7 +41,8 @@ __global__ void build_worklist_kernel(const int32_t* __restrict__ len, const int
   }
 }
 
-int32_t plan_splitkv(Pool* p, const SeqBatch& sb, int layer, int extra, int ctas_per_item, int min_chunk_pages, SplitPlan* plan) {
+int32_t plan_splitkv(Pool* p, const SeqBatch& sb, int layer, int extra, int ctas_per_item, int min_chunk_pages, int chunk_multiple,
+                     SplitPlan* plan) {
   const relux_pool_params& prm = p->prm;
   long total_pages = 0;
   int max_pages = 0;
@@ -54,6 +56,8 @@ int32_t plan_splitkv(Pool* p, const SeqBatch& sb, int layer, int extra, int ctas
   int chunk = (int)((total_pages + target_items - 1) / target_items);
   chunk = std::max(chunk, min_chunk_pages);
   chunk = std::max(1, std::min(chunk, std::max(1, max_pages)));
+  if (const char* ov = getenv("RELUX_CHUNK_PAGES")) chunk = std::max(1, atoi(ov));  // tuning aid
+  chunk = (chunk + chunk_multiple - 1) / chunk_multiple * chunk_multiple;
   int items = 0;
   for (int i = 0; i < sb.n_seqs; i++) {
     int T = p->h_len[(size_t)layer * prm.max_seqs + sb.seq[i]] + extra;
