@@ -300,7 +300,7 @@ int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
     return RELUX_ERR_UNSUPPORTED;
   }
   SplitPlan plan;
-  int32_t rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, prm.gqa_num_kv_heads, 2, 1, &plan);
+  int32_t rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, prm.gqa_num_kv_heads, 2, 1, 0, &plan);
   if (rc) return rc;
   const int rows_total = a.q_tokens * a.num_heads;
   rc = grow(p->dev, p->part_o, (size_t)plan.num_items * rows_total * kD * sizeof(float));

@@ -252,7 +252,7 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   }
   const bool sm100 = mla_sm100_eligible(p, a);
   SplitPlan plan;
-  rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, sm100 ? 2 * S : std::max(1, rows_total / 16), sm100 ? 2 : 1, sm100 ? 2 : 1, &plan);
+  rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, sm100 ? 2 * S : std::max(1, rows_total / 16), sm100 ? 2 : 1, sm100 ? 2 : 1, sm100 ? 320 : 0, &plan);
   if (rc) return rc;
   rc = grow(p->dev, p->part_o, (size_t)plan.num_items * rows_total * dC * sizeof(float));
   if (rc) return rc;

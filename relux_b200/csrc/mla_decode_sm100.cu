@@ -44,13 +44,15 @@ constexpr int kSmemK = kSmemQ + kNumKB * kBlk;        // 73728
 constexpr int kSmemV = kSmemK + kNumKB * kBlk;        // 147456
 constexpr int kSmemP = kSmemV + 4 * 2 * kBlk;         // 212992
 constexpr int kSmemBar = kSmemP + 2 * kBlk;           // 229376
-constexpr int kSmemTotal = kSmemBar + 2048;           // 231424
+constexpr int kSmemTotal = kSmemBar + 3072;           // 232448 = the 227 KB a CTA may use
+constexpr int kMaxChunkPages = 320;                   // page ids of a chunk are cached in shared memory
+constexpr int kKGroups = 3, kKPerGroup = kNumKB / kKGroups;  // K slots are armed / released in groups of 3 blocks
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemO = 0, kTmemS = 256;          // O: 2 x 128 columns; S: 2 buffers x 64 columns
 constexpr float kRescaleThreshold = 8.0f;             // log2 units: rescale O only when the max grew by > 2^8
 
 struct Bars {
-  uint64_t k_full[kNumKB], k_empty[kNumKB];
+  uint64_t k_full[kKGroups], k_empty[kKGroups];
   uint64_t v_full[4], v_empty[4];
   uint64_t s_full[2];
   uint64_t p_full, pv_done, q_full;
@@ -58,8 +60,12 @@ struct Bars {
   volatile int32_t abort_flag;
   float rowmax[2][2][64];   // [tile parity][token half][row]
   float lsum[64];
+  int32_t page_row[kMaxChunkPages];   // first pool row (TMA y coordinate) of every page of this chunk
+#ifdef RELUX_MLA_PROF
+  long long ts_k[kNumKB], ts_v[4], ts_pv;
+#endif
 };
-static_assert(sizeof(Bars) <= 2048, "barrier block too large");
+static_assert(sizeof(Bars) <= 3072, "barrier block too large");
 
 struct MlaSm100Params {
   const WorkItem* items;
@@ -73,26 +79,36 @@ struct MlaSm100Params {
   float* part_ml;
   int32_t rows_total;
   int32_t* status;
+  long long* prof;   // optional cycle counters of cluster 0 (RELUX_MLA_PROF builds only)
 };
 
-__device__ __forceinline__ bool wait_abortable(uint64_t* bar, uint32_t parity, Bars* b, int32_t* status, bool cluster_scope) {
-  if (b->abort_flag) return false;
+#ifdef RELUX_MLA_PROF
+#define PROF_T0() long long prof_t0__ = clock64()
+#define PROF_ADD(slot) do { if (prm.prof && blockIdx.x < 2 && blockIdx.y == 0) prof_acc[slot] += clock64() - prof_t0__; } while (0)
+#define PROF_DECL() long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_start = clock64()
+#define PROF_FLUSH(base) do { if (prm.prof && blockIdx.x < 2 && blockIdx.y == 0) { for (int q_ = 0; q_ < 7; q_++) prm.prof[(blockIdx.x * 4 + (base)) * 8 + q_] = prof_acc[q_]; prm.prof[(blockIdx.x * 4 + (base)) * 8 + 7] = clock64() - prof_start; } } while (0)
+#else
+#define PROF_T0()
+#define PROF_ADD(slot)
+#define PROF_DECL()
+#define PROF_FLUSH(base)
+#endif
+
+// Bounded wait.  The common case (phase already complete) is a single try_wait.  When the bound runs out the
+// waiter records RELUX_ERR_TIMEOUT, raises the CTA's abort flag and RETURNS: nobody leaves a loop early, every
+// later wait sees the flag on its first failed poll and returns at once, so all warps still reach the named
+// barriers and the final cluster barrier with garbage results and a non-zero status word.
+__device__ __noinline__ void wait_slow(uint64_t* bar, uint32_t parity, Bars* b, int32_t* status) {
   for (uint32_t i = 0; i < kSpinLimit; i++) {
-    uint32_t ok;
-    if (cluster_scope) {
-      asm volatile(
-          "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-          : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    } else {
-      ok = mbar_try_wait(bar, parity) ? 1u : 0u;
-    }
-    if (ok) return true;
-    if ((i & 1023) == 1023 && b->abort_flag) return false;
-    if (i > 256) __nanosleep(20);
+    if (mbar_try_wait(bar, parity)) return;
+    if ((i & 255) == 255 && b->abort_flag) return;
+    if (i > 512) __nanosleep(20);
   }
   b->abort_flag = 1;
   set_status(status, RELUX_ERR_TIMEOUT);
-  return false;
+}
+__device__ __forceinline__ void wait_bar(uint64_t* bar, uint32_t parity, Bars* b, int32_t* status) {
+  if (!mbar_try_wait(bar, parity)) wait_slow(bar, parity, b, status);
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
@@ -116,7 +132,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     return;
   }
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kNumKB; i++) { mbar_init(&bars->k_full[i], 1); mbar_init(&bars->k_empty[i], 1); }
+    for (int i = 0; i < kKGroups; i++) { mbar_init(&bars->k_full[i], 1); mbar_init(&bars->k_empty[i], 1); }
     for (int i = 0; i < 4; i++) { mbar_init(&bars->v_full[i], 1); mbar_init(&bars->v_empty[i], 1); }
     mbar_init(&bars->s_full[0], 1);
     mbar_init(&bars->s_full[1], 1);
@@ -130,6 +146,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     tmem_alloc<2>(&bars->tmem_base, kTmemCols);
     tmem_relinquish<2>();
   }
+  // page table slice of this chunk -> shared memory (validated once; a bad id is reported and replaced by page 0)
+  for (int i = threadIdx.x; i < npages && i < kMaxChunkPages; i += blockDim.x) {
+    int32_t pg = prm.table[(size_t)item.seq * prm.table_stride + item.page_begin + i];
+    if (pg < 0 || pg >= prm.num_pages) {
+      set_status(prm.status, RELUX_ERR_BAD_PAGE);
+      pg = 0;
+    }
+    bars->page_row[i] = prm.layer_row0 + pg * kPage;
+  }
   tc_fence_before();
   cluster_sync();
   tc_fence_after();
@@ -137,92 +162,116 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 
   if (warp == 4) {
     // =============================== producer: TMA loads into this CTA's slots ===============================
-    if (lane == 0) {
+    // The whole warp stays converged and one elected lane issues: operands that every lane computes identically
+    // live in uniform registers, which is what keeps the issue rate of TMA / tcgen05 instructions high.
+    const bool el = elect_one();
+    const uint32_t lead_q = mapa_u32(smem_u32(&bars->q_full), 0);
+    const int qrow = (item.seq_index * prm.S + sq) * kHeads + 64 * (int)rank;   // Q~ rows of this CTA's 64 heads
+    if (el) {
       tma_prefetch_desc(&tmap_kv);
       tma_prefetch_desc(&tmap_q);
-      const uint32_t lead_q = mapa_u32(smem_u32(&bars->q_full), 0);
-      // Q~ rows of this CTA's 64 heads: row = (seq_index * S + sq) * 128 + 64 * rank
-      const int qrow = (item.seq_index * prm.S + sq) * kHeads + 64 * (int)rank;
       if (rank == 0) mbar_expect_tx(&bars->q_full, 2 * kNumKB * kBlk);
+#pragma unroll
       for (int db = 0; db < kNumKB; db++) tma_load_2d_2sm(smem + kSmemQ + db * kBlk, &tmap_q, db * 64, qrow, lead_q);
-      bool ok = true;
-      // page of the tile held by CTA r (falls back to the chunk's first page when the tile has only one page)
-      auto page_row = [&](int tile, int r) -> int32_t {
-        int lp = item.page_begin + 2 * tile + r;
-        if (lp >= item.page_end) lp = item.page_begin;
-        int32_t pg = prm.table[(size_t)item.seq * prm.table_stride + lp];
-        if (pg < 0 || pg >= prm.num_pages) {
-          set_status(prm.status, RELUX_ERR_BAD_PAGE);
-          pg = 0;
+    }
+    __syncwarp();
+    // page of the tile held by CTA r (falls back to the chunk's first page when the tile has only one page)
+    auto page_row = [&](int tile, int r) -> int32_t {
+      int lp = 2 * tile + r;
+      if (lp >= npages) lp = 0;
+      return bars->page_row[lp];
+    };
+    auto load_k = [&](int tile) {
+      const int32_t y = page_row(tile, rank);
+#pragma unroll
+      for (int g = 0; g < kKGroups; g++) {
+        if (tile > 0) wait_bar(&bars->k_empty[g], (tile - 1) & 1, bars, prm.status);
+        const uint32_t lead = mapa_u32(smem_u32(&bars->k_full[g]), 0);
+        if (el) {
+          if (rank == 0) mbar_expect_tx(&bars->k_full[g], 2 * kKPerGroup * kBlk);
+#pragma unroll
+          for (int j = 0; j < kKPerGroup; j++) {
+            const int db = g * kKPerGroup + j;
+            tma_load_2d_2sm(smem + kSmemK + db * kBlk, &tmap_kv, db * 64, y, lead);
+          }
         }
-        return prm.layer_row0 + pg * kPage;
-      };
-      auto load_k = [&](int tile) {
-        const int32_t y = page_row(tile, rank);
-        for (int db = 0; db < kNumKB && ok; db++) {
-          if (tile > 0 && !wait_abortable(&bars->k_empty[db], (tile - 1) & 1, bars, prm.status, true)) { ok = false; break; }
-          if (rank == 0) mbar_expect_tx(&bars->k_full[db], 2 * kBlk);
-          tma_load_2d_2sm(smem + kSmemK + db * kBlk, &tmap_kv, db * 64, y, mapa_u32(smem_u32(&bars->k_full[db]), 0));
-        }
-      };
-      auto load_v = [&](int tile) {
-        for (int u = 0; u < 4 && ok; u++) {  // u = nb * 2 + kb
-          const int nb = u >> 1, kb = u & 1;
-          if (tile > 0 && !wait_abortable(&bars->v_empty[u], (tile - 1) & 1, bars, prm.status, true)) { ok = false; break; }
+        __syncwarp();
+      }
+    };
+    auto load_v = [&](int tile) {
+#pragma unroll
+      for (int u = 0; u < 4; u++) {  // u = nb * 2 + kb
+        const int nb = u >> 1, kb = u & 1;
+        if (tile > 0) wait_bar(&bars->v_empty[u], (tile - 1) & 1, bars, prm.status);
+        const int32_t y = page_row(tile, kb);
+        const uint32_t lead = mapa_u32(smem_u32(&bars->v_full[u]), 0);
+        const int x = 256 * nb + 128 * (int)rank;
+        if (el) {
           if (rank == 0) mbar_expect_tx(&bars->v_full[u], 4 * kBlk);
-          const int32_t y = page_row(tile, kb);
-          const uint32_t lead = mapa_u32(smem_u32(&bars->v_full[u]), 0);
-          const int x = 256 * nb + 128 * (int)rank;
           tma_load_2d_2sm(smem + kSmemV + u * 2 * kBlk, &tmap_kv, x, y, lead);
           tma_load_2d_2sm(smem + kSmemV + u * 2 * kBlk + kBlk, &tmap_kv, x + 64, y, lead);
         }
-      };
-      load_k(0);
-      for (int i = 0; i < ntiles && ok; i++) {
-        if (i + 1 < ntiles) load_k(i + 1);
-        load_v(i);
+        __syncwarp();
       }
+    };
+    load_k(0);
+    for (int i = 0; i < ntiles; i++) {
+      if (i + 1 < ntiles) load_k(i + 1);
+      load_v(i);
     }
   } else if (warp == 5) {
-    // =============================== MMA issuer (leader CTA only) ===============================
-    if (rank == 0 && lane == 0) {
+    // =============================== MMA issuer (leader CTA only, converged warp + elected lane) ===============================
+    if (rank == 0) {
+      const bool el = elect_one();
       const uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
       const uint32_t idesc_pv = make_idesc_bf16(128, 256, false, true);
-      const uint32_t sQ = smem_u32(smem + kSmemQ), sK = smem_u32(smem + kSmemK), sV = smem_u32(smem + kSmemV),
-                     sP = smem_u32(smem + kSmemP);
-      bool ok = wait_abortable(&bars->q_full, 0, bars, prm.status, true);
+      // descriptors of the region bases; an operand at +bytes is base + (bytes >> 4) in the low word
+      const uint64_t dQ = make_desc_kmajor_sw128(smem_u32(smem + kSmemQ));
+      const uint64_t dK = make_desc_kmajor_sw128(smem_u32(smem + kSmemK));
+      const uint64_t dP = make_desc_kmajor_sw128(smem_u32(smem + kSmemP));
+      const uint64_t dV = make_desc_mnmajor_sw128(smem_u32(smem + kSmemV), kBlk);
+      wait_bar(&bars->q_full, 0, bars, prm.status);
       auto issue_qk = [&](int tile) {
         const uint32_t d = tmem + kTmemS + (tile & 1) * 64;
-        for (int db = 0; db < kNumKB && ok; db++) {
-          if (!wait_abortable(&bars->k_full[db], tile & 1, bars, prm.status, true)) { ok = false; break; }
-          tc_fence_after();
 #pragma unroll
-          for (int kk = 0; kk < 4; kk++)
-            umma_ss<2>(d, make_desc_kmajor_sw128(sQ + db * kBlk + kk * 32), make_desc_kmajor_sw128(sK + db * kBlk + kk * 32), idesc_qk,
-                       (db | kk) != 0);
-          umma_commit_mc<2>(&bars->k_empty[db], 0x3);
+        for (int g = 0; g < kKGroups; g++) {
+          wait_bar(&bars->k_full[g], tile & 1, bars, prm.status);
+          if (el) {
+#pragma unroll
+            for (int j = 0; j < kKPerGroup * 4; j++) {
+              const uint32_t off = (uint32_t)((g * kKPerGroup + (j >> 2)) * kBlk + (j & 3) * 32) >> 4;
+              umma_ss<2>(d, dQ + off, dK + off, idesc_qk, (g | j) != 0);
+            }
+            umma_commit_mc<2>(&bars->k_empty[g], 0x3);
+          }
+          __syncwarp();
         }
-        if (ok) umma_commit_mc<2>(&bars->s_full[tile & 1], 0x3);
+        if (el) umma_commit_mc<2>(&bars->s_full[tile & 1], 0x3);
+        __syncwarp();
       };
       auto issue_pv = [&](int tile) {
-        if (!wait_abortable(&bars->p_full, tile & 1, bars, prm.status, true)) { ok = false; return; }
-        tc_fence_after();
-        for (int u = 0; u < 4 && ok; u++) {
-          const int nb = u >> 1, kb = u & 1;
-          if (!wait_abortable(&bars->v_full[u], tile & 1, bars, prm.status, true)) { ok = false; break; }
-          tc_fence_after();
+        wait_bar(&bars->p_full, tile & 1, bars, prm.status);
+        tc_fence_after();   // P rows and a possible O rescale were written by the softmax warps of both CTAs
 #pragma unroll
-          for (int kk = 0; kk < 4; kk++)
-            umma_ss<2>(tmem + kTmemO + nb * 128, make_desc_kmajor_sw128(sP + kb * kBlk + kk * 32),
-                       make_desc_mnmajor_sw128(sV + u * 2 * kBlk + kk * 2048, kBlk), idesc_pv, (tile | kb | kk) != 0);
-          umma_commit_mc<2>(&bars->v_empty[u], 0x3);
+        for (int u = 0; u < 4; u++) {
+          const int nb = u >> 1, kb = u & 1;
+          wait_bar(&bars->v_full[u], tile & 1, bars, prm.status);
+          if (el) {
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++)
+              umma_ss<2>(tmem + kTmemO + nb * 128, dP + ((uint32_t)(kb * kBlk + kk * 32) >> 4),
+                         dV + ((uint32_t)(u * 2 * kBlk + kk * 2048) >> 4), idesc_pv, (tile | kb | kk) != 0);
+            umma_commit_mc<2>(&bars->v_empty[u], 0x3);
+          }
+          __syncwarp();
         }
-        if (ok) umma_commit_mc<2>(&bars->pv_done, 0x3);
+        if (el) umma_commit_mc<2>(&bars->pv_done, 0x3);
+        __syncwarp();
       };
-      if (ok) issue_qk(0);
-      for (int i = 0; i < ntiles && ok; i++) {
+      issue_qk(0);
+      for (int i = 0; i < ntiles; i++) {
         if (i + 1 < ntiles) issue_qk(i + 1);
-        if (ok) issue_pv(i);
+        issue_pv(i);
       }
     }
   } else {
@@ -233,11 +282,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
+    PROF_DECL();
     const uint32_t p_full_lead = mapa_u32(smem_u32(&bars->p_full), 0);
     for (int i = 0; i < ntiles; i++) {
       // no thread leaves this loop early: every thread must reach the same named barriers
-      ok = wait_abortable(&bars->s_full[i & 1], (i >> 1) & 1, bars, prm.status, false) && ok;
+      { PROF_T0();
+      wait_bar(&bars->s_full[i & 1], (i >> 1) & 1, bars, prm.status);
+      PROF_ADD(0); }
       tc_fence_after();
+      PROF_T0();
       uint32_t sv[2][32];
       tmem_ld_32x32b_x32(tmem + lane_addr + kTmemS + (i & 1) * 64, sv[0]);
       tmem_ld_32x32b_x32(tmem + lane_addr + kTmemS + (i & 1) * 64 + 32, sv[1]);
@@ -256,7 +309,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
           mx = fmaxf(mx, v);
         }
       bars->rowmax[i & 1][hf][row] = mx;
+      PROF_ADD(1);
+      { PROF_T0();
       asm volatile("bar.sync 1, 128;" ::: "memory");
+      PROF_ADD(2); }
+      long long prof_t1__ = 0;
+#ifdef RELUX_MLA_PROF
+      prof_t1__ = clock64();
+#endif
       mx = fmaxf(mx, bars->rowmax[i & 1][hf ^ 1][row]);
       // lazily updated running max: both threads of a row take the same decision
       float alpha = 1.f;
@@ -281,8 +341,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         }
       l_run = l_run * alpha + psum;
       // P(i) may overwrite the buffer, and O may be rescaled, only after PV(i-1) has completed
-      if (i > 0) ok = wait_abortable(&bars->pv_done, (i - 1) & 1, bars, prm.status, false) && ok;
-      if (rescale && i > 0 && ok) {
+#ifdef RELUX_MLA_PROF
+      if (prm.prof && blockIdx.x < 2 && blockIdx.y == 0) prof_acc[3] += clock64() - prof_t1__;
+#endif
+      { PROF_T0();
+      if (i > 0) wait_bar(&bars->pv_done, (i - 1) & 1, bars, prm.status);
+      PROF_ADD(4); }
+      if (rescale && i > 0) {
+#ifdef RELUX_MLA_PROF
+        if (prm.prof && blockIdx.x < 2 && blockIdx.y == 0) prof_acc[6] += 1;
+#endif
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < 256; c += 32) {
@@ -302,11 +370,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       for (int c = 0; c < 8; c++)
         *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
       fence_proxy_async();
+      { PROF_T0();
       asm volatile("bar.sync 2, 128;" ::: "memory");
+      PROF_ADD(5); }
       if (threadIdx.x == 0) mbar_arrive_cluster(p_full_lead);
     }
+    if (threadIdx.x == 0) PROF_FLUSH(2);
     // ---- epilogue: O (unnormalised), running max and sum of this chunk -> split-KV partial ----
-    if (ok && ntiles > 0) ok = wait_abortable(&bars->pv_done, (ntiles - 1) & 1, bars, prm.status, false);
+    wait_bar(&bars->pv_done, (ntiles - 1) & 1, bars, prm.status);
+    ok = !bars->abort_flag;
     tc_fence_after();
     if (hf == 1) bars->lsum[row] = l_run;
     asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -392,10 +464,32 @@ int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_ar
   k.part_ml = (float*)p->part_ml.p;
   k.rows_total = a.q_tokens * kHeads;
   k.status = p->d_status;
+  k.prof = nullptr;
+#ifdef RELUX_MLA_PROF
+  static long long* d_prof = nullptr;
+  if (!d_prof) cudaMalloc(&d_prof, 64 * 8 * sizeof(long long));
+  cudaMemsetAsync(d_prof, 0, 64 * 8 * sizeof(long long), p->dev->stream);
+  k.prof = d_prof;
+#endif
   RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_decode_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
   dim3 grid(2 * plan.num_items, a.q_tokens);
   mla_decode_sm100_kernel<<<grid, 192, kSmemTotal, p->dev->stream>>>(p->tmap_mla, tq, k);
   RELUX_CUDA_TRY(cudaGetLastError());
+#ifdef RELUX_MLA_PROF
+  {
+    long long h[64 * 8];
+    cudaStreamSynchronize(p->dev->stream);
+    cudaMemcpy(h, d_prof, sizeof(h), cudaMemcpyDeviceToHost);
+    const char* names[3] = {"producer [k_empty v_empty]", "mma      [k_full p_full v_full k_age_sum k_stalls v_age_sum v_stalls]", "softmax  [s_full math1 barmax math2 pv_done barP nrescale]"};
+    for (int cta = 0; cta < 2; cta++)
+      for (int r = 0; r < 3; r++) {
+        fprintf(stderr, "prof cta%d %s:", cta, names[r]);
+        for (int q = 0; q < 8; q++) fprintf(stderr, " %lld", h[(cta * 4 + r) * 8 + q]);
+        fprintf(stderr, "  (last = total)\n");
+      }
+    fprintf(stderr, "prof items=%d chunk_pages=%d stalled_k_waits=%lld\n", plan.num_items, plan.chunk_pages, h[200]);
+  }
+#endif
   return RELUX_OK;
 }
 

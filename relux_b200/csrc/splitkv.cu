@@ -42,7 +42,7 @@ __global__ void build_worklist_kernel(const int32_t* __restrict__ len, const int
 }
 
 int32_t plan_splitkv(Pool* p, const SeqBatch& sb, int layer, int extra, int ctas_per_item, int min_chunk_pages, int chunk_multiple,
-                     SplitPlan* plan) {
+                     int max_chunk_pages, SplitPlan* plan) {
   const relux_pool_params& prm = p->prm;
   long total_pages = 0;
   int max_pages = 0;
@@ -58,6 +58,7 @@ int32_t plan_splitkv(Pool* p, const SeqBatch& sb, int layer, int extra, int ctas
   chunk = std::max(1, std::min(chunk, std::max(1, max_pages)));
   if (const char* ov = getenv("RELUX_CHUNK_PAGES")) chunk = std::max(1, atoi(ov));  // tuning aid
   chunk = (chunk + chunk_multiple - 1) / chunk_multiple * chunk_multiple;
+  if (max_chunk_pages > 0) chunk = std::min(chunk, max_chunk_pages / chunk_multiple * chunk_multiple);
   int items = 0;
   for (int i = 0; i < sb.n_seqs; i++) {
     int T = p->h_len[(size_t)layer * prm.max_seqs + sb.seq[i]] + extra;

@@ -21,7 +21,7 @@ struct SplitPlan {
 struct Pool;
 struct SeqBatch;
 int32_t plan_splitkv(Pool* p, const SeqBatch& sb, int layer, int extra, int ctas_per_item, int min_chunk_pages, int chunk_multiple,
-                     SplitPlan* plan);
+                     int max_chunk_pages, SplitPlan* plan);
 int32_t launch_merge(Pool* p, const SplitPlan& plan, int n_seqs, int rows, int width, float* out, uint16_t* out_bf16);
 
 }  // namespace relux

@@ -7,6 +7,15 @@
 
 namespace relux {
 
+// One lane of a fully converged warp.  Code that every lane executes identically up to this point keeps its
+// operands in uniform registers; tcgen05 / TMA instructions issued from a divergent single-thread branch
+// instead pay a register-to-uniform-register move per operand and issue several times slower.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- cluster helpers ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
