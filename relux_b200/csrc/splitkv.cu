@@ -5,6 +5,7 @@
 // all SMs.  The list is built on the device from the device-resident lengths; the host computes
 // only the item COUNT from its shadow lengths, so no host->device copy is needed per step.
 #include <cstdlib>
+#include <vector>
 #include "common.cuh"
 #include "internal.h"
 #include "splitkv.h"
@@ -41,30 +42,49 @@ __global__ void build_worklist_kernel(const int32_t* __restrict__ len, const int
   }
 }
 
+// Chooses the chunk length.  CTAs are scheduled in waves over the SMs, so the step time is about
+//   waves(chunk) * (chunk + overhead),  waves = ceil(items(chunk) * ctas_per_item / sm_count),
+// in units of "time to stream one page"; `overhead` stands for the prologue (query load, TMEM set-up) and
+// epilogue (partial write + its share of the merge) of one item.  All candidates are evaluated and the
+// cheapest wins, which avoids a nearly empty last wave (e.g. 4.3 waves costing 5).
 int32_t plan_splitkv(Pool* p, const SeqBatch& sb, int layer, int extra, int ctas_per_item, int min_chunk_pages, int chunk_multiple,
                      int max_chunk_pages, SplitPlan* plan) {
   const relux_pool_params& prm = p->prm;
-  long total_pages = 0;
-  int max_pages = 0;
+  std::vector<int> pages(sb.n_seqs);
+  int max_pages = 1;
   for (int i = 0; i < sb.n_seqs; i++) {
     int T = p->h_len[(size_t)layer * prm.max_seqs + sb.seq[i]] + extra;
-    int pages = (T + prm.page_tokens - 1) / prm.page_tokens;
-    total_pages += pages;
-    max_pages = std::max(max_pages, pages);
+    pages[i] = (T + prm.page_tokens - 1) / prm.page_tokens;
+    max_pages = std::max(max_pages, pages[i]);
   }
-  long target_items = std::max(1L, 4L * p->dev->sm_count / std::max(1, ctas_per_item));
-  int chunk = (int)((total_pages + target_items - 1) / target_items);
-  chunk = std::max(chunk, min_chunk_pages);
-  chunk = std::max(1, std::min(chunk, std::max(1, max_pages)));
-  if (const char* ov = getenv("RELUX_CHUNK_PAGES")) chunk = std::max(1, atoi(ov));  // tuning aid
-  chunk = (chunk + chunk_multiple - 1) / chunk_multiple * chunk_multiple;
-  if (max_chunk_pages > 0) chunk = std::min(chunk, max_chunk_pages / chunk_multiple * chunk_multiple);
+  const int mult = std::max(1, chunk_multiple);
+  int lo = std::max(std::max(1, min_chunk_pages), mult);
+  lo = (lo + mult - 1) / mult * mult;
+  int hi = (max_pages + mult - 1) / mult * mult;
+  if (max_chunk_pages > 0) hi = std::min(hi, max_chunk_pages / mult * mult);
+  hi = std::max(hi, lo);
+  const double overhead = 6.0;
+  const int sms = std::max(1, p->dev->sm_count);
+  int chunk = hi;
+  double best = 1e300;
+  const int step = std::max(mult, (hi - lo) / 512 / mult * mult);
+  for (int c = lo; c <= hi; c += step) {
+    long items_c = 0;
+    for (int i = 0; i < sb.n_seqs; i++) items_c += (pages[i] + c - 1) / c;
+    const long waves = (items_c * ctas_per_item + sms - 1) / sms;
+    const double cost = (double)waves * (c + overhead);
+    if (cost < best - 1e-9 || (cost < best + 1e-9 && c > chunk)) {
+      best = cost;
+      chunk = c;
+    }
+  }
+  if (const char* ov = getenv("RELUX_CHUNK_PAGES")) {  // tuning aid
+    chunk = std::max(1, atoi(ov));
+    chunk = (chunk + mult - 1) / mult * mult;
+    if (max_chunk_pages > 0) chunk = std::min(chunk, max_chunk_pages / mult * mult);
+  }
   int items = 0;
-  for (int i = 0; i < sb.n_seqs; i++) {
-    int T = p->h_len[(size_t)layer * prm.max_seqs + sb.seq[i]] + extra;
-    int pages = (T + prm.page_tokens - 1) / prm.page_tokens;
-    items += (pages + chunk - 1) / chunk;
-  }
+  for (int i = 0; i < sb.n_seqs; i++) items += (pages[i] + chunk - 1) / chunk;
   plan->chunk_pages = chunk;
   plan->num_items = items;
   size_t bytes = sizeof(WorkItem) * (size_t)items + sizeof(int32_t) * ((size_t)sb.n_seqs + 1) + 64;

@@ -45,3 +45,115 @@ def ragged_to_padded(rows, lens, width_shape):
         out[b, :n] = rows[o:o + n]
         o += n
     return out
+
+
+# ---- the two CPU-runnable model configurations ------------------------------------------------
+def model_config(name):
+    from oracle import binding as orc
+    if name == "config1":
+        return orc.ModelCfg(vocab=100, dModel=64, numHeads=4, numKVHeads=2, numLayers=2, dFF=128, maxSeqLen=64, ropeBase=10000.0,
+                            causal=1, swiglu=1, mla=0, dC=0, dHR=0)
+    if name == "config2":
+        # 8 heads x (content 32 + rope 16), value dim 32, latent 64; the benchmark names no FFN type: GELU, the reference default
+        return orc.ModelCfg(vocab=1024, dModel=256, numHeads=8, numKVHeads=8, numLayers=4, dFF=512, maxSeqLen=512, ropeBase=10000.0,
+                            causal=1, swiglu=0, mla=1, dC=64, dHR=16)
+    raise KeyError(name)
+
+
+def model_weights(cfg, seed=0, std=0.02):
+    from oracle import binding as orc
+    n = orc.Model.weight_count(cfg)
+    rng = np.random.default_rng(seed)
+    return orc.bf16_from_f32((rng.standard_normal(n, dtype=np.float32) * np.float32(std)))
+
+
+def prompts_for(name, seed=1):
+    rng = np.random.default_rng(seed)
+    if name == "config1":
+        return [rng.integers(0, 100, 8).astype(np.int32)]
+    if name == "config2":
+        return [rng.integers(0, 1024, 32).astype(np.int32) for _ in range(4)]
+    raise KeyError(name)
+
+
+def layer_weight_offsets(cfg):
+    """Element offsets of W_UK / W_UV of every layer inside the flat weight buffer (order documented in
+    oracle/relux_oracle.cpp): used to hand the MLA up-projections to the GPU."""
+    D, H, F, V = cfg.dModel, cfg.numHeads, cfg.dFF, cfg.vocab
+    hd = D // H
+    off = V * D
+    out = []
+    for _ in range(cfg.numLayers):
+        if cfg.mla:
+            o_wq = off
+            o_dkv = o_wq + D * H * hd
+            o_uk = o_dkv + D * cfg.dC
+            o_uv = o_uk + cfg.dC * H * hd
+            o_kr = o_uv + cfg.dC * H * hd
+            o_qr = o_kr + D * cfg.dHR
+            o_o = o_qr + D * H * cfg.dHR
+            off = o_o + H * hd * D
+            out.append((o_uk, o_uv))
+        else:
+            off += D * H * hd + 2 * D * cfg.numKVHeads * hd + H * hd * D
+            out.append(None)
+        off += D * F * (2 if cfg.swiglu else 1) + F * D
+    return out
+
+
+class GpuAttention:
+    """Plugs the CUDA library into the oracle's decoder forward at the reference's seam: the cache object
+    (Append / TotalLen) plus the attention loops of forwardCached.  Everything else of the forward
+    (projections, RoPE, norms, MLP, lm head, greedy pick) stays the CPU restatement."""
+
+    def __init__(self, dev, cfg, weights, mode):
+        import ctypes as C
+        import relux_b200 as rb
+        self.C, self.cfg, self.mode, self.dev = C, cfg, mode, dev
+        self.hd = cfg.dModel // cfg.numHeads
+        if cfg.mla:
+            self.cache = rb.MLACache(dev, cfg.numLayers, cfg.maxSeqLen, cfg.dC, cfg.dHR)
+            self.w = [(dev.upload(weights[a:a + cfg.dC * cfg.numHeads * self.hd]), dev.upload(weights[b:b + cfg.dC * cfg.numHeads * self.hd]))
+                      for a, b in layer_weight_offsets(cfg)]
+            self.scale = float(np.float32(1.0 / np.sqrt(np.float64(self.hd + cfg.dHR))))
+        else:
+            self.cache = rb.KVCache(dev, cfg.numLayers, cfg.maxSeqLen, cfg.numKVHeads, self.hd)
+            self.scale = float(np.float32(1.0 / np.sqrt(np.float64(self.hd))))
+
+    def reset(self):
+        self.cache.Reset()
+
+    def _arr(self, ptr, shape):
+        return np.ctypeslib.as_array(ptr, shape=shape)
+
+    def mha_hook(self, user, layer, S, start_pos, q, k, v, out):
+        cfg, hd = self.cfg, self.hd
+        try:
+            assert self.cache.TotalLen(layer) == start_pos
+            self.cache.Append(layer, self._arr(k, (1, cfg.numKVHeads, S, hd)), self._arr(v, (1, cfg.numKVHeads, S, hd)))
+            o = self.cache.attend(layer, self._arr(q, (1, cfg.numHeads, S, hd)), self.scale, causal=bool(cfg.causal), mode=self.mode)
+            self._arr(out, (1, cfg.numHeads, S, hd))[...] = o
+            return 0
+        except Exception as e:  # noqa: BLE001 - must not propagate through the C callback
+            self.error = e
+            return -100
+
+    def mla_hook(self, user, layer, S, start_pos, qc, qr, ckv, kr, out):
+        cfg, hd = self.cfg, self.hd
+        try:
+            assert self.cache.TotalLen(layer) == start_pos
+            self.cache.Append(layer, self._arr(ckv, (1, S, cfg.dC)), self._arr(kr, (1, S, cfg.dHR)))
+            wuk, wuv = self.w[layer]
+            o = self.cache.attend(layer, self._arr(qc, (1, cfg.numHeads, S, hd)), self._arr(qr, (1, cfg.numHeads, S, cfg.dHR)), wuk, wuv,
+                                  self.scale, causal=bool(cfg.causal), mode=self.mode)
+            self._arr(out, (1, cfg.numHeads, S, hd))[...] = o
+            return 0
+        except Exception as e:  # noqa: BLE001
+            self.error = e
+            return -100
+
+    def close(self):
+        self.cache.close()
+        if self.cfg.mla:
+            for a, b in self.w:
+                a.free(); b.free()
