@@ -86,7 +86,7 @@ struct MlaSm100Params {
 #define PROF_T0() long long prof_t0__ = clock64()
 #define PROF_ADD(slot) do { if (prm.prof && blockIdx.x < 2 && blockIdx.y == 0) prof_acc[slot] += clock64() - prof_t0__; } while (0)
 #define PROF_DECL() long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_start = clock64()
-#define PROF_FLUSH(base) do { if (prm.prof && blockIdx.x < 2 && blockIdx.y == 0) { for (int q_ = 0; q_ < 7; q_++) prm.prof[(blockIdx.x * 4 + (base)) * 8 + q_] = prof_acc[q_]; prm.prof[(blockIdx.x * 4 + (base)) * 8 + 7] = clock64() - prof_start; } } while (0)
+#define PROF_FLUSH(base) do { if (prm.prof && blockIdx.x < 2 && blockIdx.y == 0) { for (int q_ = 0; q_ < 8; q_++) prm.prof[(blockIdx.x * 4 + (base)) * 8 + q_] = prof_acc[q_]; prm.prof[100 + blockIdx.x * 4 + (base)] = clock64() - prof_start; } } while (0)
 #else
 #define PROF_T0()
 #define PROF_ADD(slot)
@@ -349,7 +349,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       PROF_ADD(4); }
       if (rescale && i > 0) {
 #ifdef RELUX_MLA_PROF
-        if (prm.prof && blockIdx.x < 2 && blockIdx.y == 0) prof_acc[6] += 1;
+        ;
 #endif
         tc_fence_after();
 #pragma unroll 1
@@ -365,11 +365,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         tc_fence_before();
       }
       // P row: 64 tokens = 128 bytes = one swizzled row of block hf
+      { PROF_T0();
       uint8_t* prow = smem + kSmemP + hf * kBlk + row * 128;
 #pragma unroll
       for (int c = 0; c < 8; c++)
         *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+      PROF_ADD(6); }
+      { PROF_T0();
       fence_proxy_async();
+      PROF_ADD(7); }
       { PROF_T0();
       asm volatile("bar.sync 2, 128;" ::: "memory");
       PROF_ADD(5); }
@@ -480,12 +484,12 @@ int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_ar
     long long h[64 * 8];
     cudaStreamSynchronize(p->dev->stream);
     cudaMemcpy(h, d_prof, sizeof(h), cudaMemcpyDeviceToHost);
-    const char* names[3] = {"producer [k_empty v_empty]", "mma      [k_full p_full v_full k_age_sum k_stalls v_age_sum v_stalls]", "softmax  [s_full math1 barmax math2 pv_done barP nrescale]"};
+    const char* names[3] = {"producer [k_empty v_empty]", "mma      [k_full p_full v_full k_age_sum k_stalls v_age_sum v_stalls]", "softmax  [s_full math1 barmax math2 pv_done barP Pwrite fence_proxy]"};
     for (int cta = 0; cta < 2; cta++)
       for (int r = 0; r < 3; r++) {
         fprintf(stderr, "prof cta%d %s:", cta, names[r]);
         for (int q = 0; q < 8; q++) fprintf(stderr, " %lld", h[(cta * 4 + r) * 8 + q]);
-        fprintf(stderr, "  (last = total)\n");
+        fprintf(stderr, "  total %lld\n", h[100 + cta * 4 + r]);
       }
     fprintf(stderr, "prof items=%d chunk_pages=%d stalled_k_waits=%lld\n", plan.num_items, plan.chunk_pages, h[200]);
   }

@@ -31,8 +31,11 @@ __device__ __forceinline__ uint32_t mapa_u32(uint32_t local_addr, uint32_t cta) 
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(cta));
   return r;
 }
+// Arrive on an mbarrier of another CTA of the cluster.  The default (CTA-scope release) form is used on purpose:
+// the cluster-scope release variant costs thousands of cycles per call, and the data handed over with these
+// arrivals is published separately (fence.proxy.async for shared-memory operands, tcgen05 fences for TMEM).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // Wait with cluster-scope acquire (the arrivals may come from the peer CTA).  Bounded like mbar_wait.
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
