@@ -219,6 +219,27 @@ int32_t relux_gqa_decode(relux_pool_t pool, const relux_attn_args* args);
 int32_t relux_gqa_verify(relux_pool_t pool, const relux_attn_args* attn, const relux_append_args* draft_kv);
 int32_t relux_mla_verify(relux_pool_t pool, const relux_attn_args* attn, const relux_append_args* draft_kv);
 
+/* GQA flash-decode / verify that allocates nothing.  It has no counterpart in the reference; it exists for callers
+ * that may not allocate device memory at the moment they decode: a serving loop whose memory budget has been handed
+ * out completely (so a late cudaMalloc can fail or stall the whole device while it synchronises), or code running
+ * under rules that forbid allocator calls after start-up.  relux_gqa_decode grows its split-KV scratch with
+ * cudaMalloc when a call needs more than any earlier one; this entry point never does.  Its work list and split-KV
+ * partials live in one fixed 16 MiB array in device memory that every GPU holds from the moment the library is
+ * loaded until the process exits.
+ *   - Same arguments and results as relux_gqa_decode, restricted to what needs no staging: RELUX_ATTN_FAST, q and
+ *     out in device memory, q token-major f32 or bf16, out token-major f32, page_tokens 64, head_dim 128,
+ *     (num_heads / num_kv_heads) * q_tokens <= 32.
+ *   - Limits of the fixed scratch: at most 4096 sequences per call, at most 4096 (sequence, chunk) work items, and
+ *     work_items * q_tokens * num_heads * 520 bytes of partials within 16 MiB minus a 96 KiB header.  Chunks are
+ *     lengthened to fit; a call that cannot fit even with one chunk per sequence returns RELUX_ERR_UNSUPPORTED and
+ *     its message names the limit.
+ *   - The first call on a device looks up the array's device address (one cudaGetSymbolAddress, checked); make that
+ *     first call before starting any stream capture.  No call uses cudaMalloc, cudaFree or another allocating routine.
+ *   - All calls share the array and it keeps whatever the last call left in it; nothing in it has to start at zero.
+ *     Two calls whose kernels overlap on the GPU (different pools on different streams, or different processes'
+ *     copies aside) would overwrite each other's partials: run calls of this entry point one after another. */
+int32_t relux_gqa_decode_noalloc(relux_pool_t pool, const relux_attn_args* args);
+
 /* Device-time of the dominant attention kernel of the most recent relux_*_decode / verify call on this
  * pool, measured with CUDA events around that one launch.  Synchronises the stream. */
 int32_t relux_pool_last_kernel_ms(relux_pool_t pool, float* ms);

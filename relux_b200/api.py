@@ -259,6 +259,14 @@ class Pool:
         fn = self.lib.relux_mla_decode if self.kind == L.POOL_MLA else self.lib.relux_gqa_decode
         L.check(fn(self.h, C.byref(args)))
 
+    def decode_noalloc(self, layer, n_seqs, q, out, num_heads, head_dim, scale, q_tokens=1, extra_tokens=0, causal=True,
+                       seq_ids=None):
+        """GQA decode through the entry point that allocates no device memory (fixed 16 MiB scratch, device-resident
+        q and f32 out only; see relux_gqa_decode_noalloc in include/relux_cuda.h)."""
+        args = self._attn_args(layer, n_seqs, q, None, out, num_heads, head_dim, scale, q_tokens, extra_tokens, causal, L.ATTN_FAST,
+                               None, None, seq_ids, L.LAYOUT_TOKEN_MAJOR, L.LAYOUT_TOKEN_MAJOR, None, None)
+        L.check(self.lib.relux_gqa_decode_noalloc(self.h, C.byref(args)))
+
     def verify(self, layer, n_seqs, q, out, draft_a, draft_b, num_heads, head_dim, scale, q_tokens, q_rope=None, w_uk=None,
                w_uv=None, mode=L.ATTN_FAST, seq_ids=None, kv_layout=L.LAYOUT_TOKEN_MAJOR, q_dtype=None, out_dtype=None,
                kv_dtype=None):

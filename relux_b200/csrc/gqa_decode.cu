@@ -11,6 +11,9 @@
 //   * at the end the four warps' (max, sum, O) are combined through shared memory and written as one
 //     split-KV partial; merge_splits_kernel combines the chunks of a sequence.
 // All mbarrier waits are bounded; a wait that runs out records RELUX_ERR_TIMEOUT and the CTA leaves.
+#include <algorithm>
+#include <mutex>
+#include <vector>
 #include "common.cuh"
 #include "internal.h"
 #include "splitkv.h"
@@ -349,4 +352,167 @@ int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   return launch_merge(p, plan, sb.n_seqs, rows_total, kD, (float*)d_out, nullptr);
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// relux_gqa_decode_noalloc: the same split-KV flash-decode for callers that must not allocate device memory
+// (see include/relux_cuda.h).  Its work list and split-KV partials live in one fixed array in device memory.
+// ---------------------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kNoAllocScratchBytes = (size_t)16 << 20;  // 16 MiB, held by every GPU that loads the library
+constexpr int kNoAllocMaxItems = 4096;
+constexpr int kNoAllocMaxSeqs = 4096;
+constexpr int kNoAllocMaxDevices = 64;
+
+// In host code this name is only a handle for cudaGetSymbolAddress; the kernels get the resolved device address.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+struct NoAllocSlot {
+  bool ready = false;
+  unsigned char* base = nullptr;
+};
+NoAllocSlot g_noalloc_slot[kNoAllocMaxDevices];
+std::mutex g_noalloc_mu;
+
+constexpr size_t kNaItemsOff = 0;
+constexpr size_t kNaChunkOff = kNaItemsOff + sizeof(WorkItem) * kNoAllocMaxItems;                         // 64 KiB
+constexpr size_t kNaPartOff = (kNaChunkOff + sizeof(int32_t) * (kNoAllocMaxSeqs + 1) + 255) & ~(size_t)255;
+constexpr size_t kNaPartBytes = kNoAllocScratchBytes - kNaPartOff;
+constexpr size_t kNaBytesPerRow = (size_t)(kD + 2) * sizeof(float);  // one partial row: D accumulators + (max, sum)
+
+}  // namespace
+
 }  // namespace relux
+
+extern "C" __attribute__((visibility("default"))) int32_t relux_gqa_decode_noalloc(relux_pool_t handle, const relux_attn_args* a) {
+  using namespace relux;
+  Pool* p = as_pool(handle);
+  if (!p) { set_error("bad pool handle"); return RELUX_ERR_BAD_HANDLE; }
+  Device* dev = p->dev;
+  std::unique_lock<std::mutex> lk(dev->mu);
+  RELUX_CUDA_TRY(cudaSetDevice(dev->index));
+  const relux_pool_params& prm = p->prm;
+  if (!a) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
+  if (prm.kind != RELUX_POOL_GQA) { set_error("relux_gqa_decode_noalloc needs a GQA pool"); return RELUX_ERR_INVALID_ARG; }
+  if (a->layer < 0 || a->layer >= prm.num_layers) { set_error("layerIdx=%d out of range [0, %d)", a->layer, prm.num_layers); return RELUX_ERR_INVALID_ARG; }
+  if (!a->q || !a->out || a->q_tokens <= 0 || a->extra_tokens < 0 || a->num_heads <= 0 || a->head_dim != prm.gqa_head_dim ||
+      a->num_heads % prm.gqa_num_kv_heads != 0) {
+    set_error("relux_gqa_decode_noalloc: bad attention arguments");
+    return RELUX_ERR_INVALID_ARG;
+  }
+  // Nothing may be staged or converted here, because staging buffers are grown with cudaMalloc.
+  if (a->mode != RELUX_ATTN_FAST || a->q_mem != RELUX_MEM_DEVICE || a->out_mem != RELUX_MEM_DEVICE || a->out_dtype != RELUX_DTYPE_F32 ||
+      (a->q_dtype != RELUX_DTYPE_F32 && a->q_dtype != RELUX_DTYPE_BF16) ||
+      (a->q_tokens > 1 && (a->q_layout != RELUX_LAYOUT_TOKEN_MAJOR || a->out_layout != RELUX_LAYOUT_TOKEN_MAJOR))) {
+    set_error("relux_gqa_decode_noalloc takes device-resident token-major q (f32 or bf16) and writes device-resident f32 output, FAST mode only");
+    return RELUX_ERR_UNSUPPORTED;
+  }
+  const int g = a->num_heads / prm.gqa_num_kv_heads, R = g * a->q_tokens;
+  if (!p->has_tmap || prm.page_tokens != kPageTok || prm.gqa_head_dim != kD || R > 32) {
+    set_error("relux_gqa_decode_noalloc needs page_tokens=64, head_dim=128 and (num_heads/num_kv_heads)*q_tokens <= 32");
+    return RELUX_ERR_UNSUPPORTED;
+  }
+  if (a->n_seqs > kNoAllocMaxSeqs) {
+    set_error("relux_gqa_decode_noalloc: n_seqs=%d exceeds the fixed scratch limit of %d sequences", a->n_seqs, kNoAllocMaxSeqs);
+    return RELUX_ERR_UNSUPPORTED;
+  }
+  SeqBatch sb;  // uses the pool's pre-allocated pinned staging only
+  int32_t rc = stage_batch(p, a->n_seqs, a->seq_ids, nullptr, a->q_tokens, &sb);
+  if (rc) return rc;
+  const int rows_total = a->q_tokens * a->num_heads;
+  long total_pages = 0;
+  int max_pages = 1;
+  std::vector<int> pages(sb.n_seqs);
+  for (int i = 0; i < sb.n_seqs; i++) {
+    const int s = sb.seq[i];
+    const int T = p->h_len[(size_t)a->layer * prm.max_seqs + s] + a->extra_tokens;
+    if (T < a->q_tokens || T > p->seq_pages[s] * prm.page_tokens) {
+      set_error("sequence %d: %d cached rows cannot serve %d query tokens within its capacity", s, T, a->q_tokens);
+      return RELUX_ERR_INVALID_ARG;
+    }
+    pages[i] = (T + kPageTok - 1) / kPageTok;
+    total_pages += pages[i];
+    max_pages = std::max(max_pages, pages[i]);
+  }
+  // Chunk length: about four waves of CTAs, then lengthened until the partials fit the fixed scratch.
+  const long max_items_by_bytes = (long)(kNaPartBytes / (kNaBytesPerRow * (size_t)rows_total));
+  const long item_cap = std::min<long>(kNoAllocMaxItems, max_items_by_bytes);
+  const long target = std::max(1L, 4L * dev->sm_count / prm.gqa_num_kv_heads);
+  int chunk = std::max(2, (int)((total_pages + target - 1) / target));
+  chunk = std::min(chunk, max_pages);
+  long items = 0;
+  for (;;) {
+    items = 0;
+    for (int i = 0; i < sb.n_seqs; i++) items += (pages[i] + chunk - 1) / chunk;
+    if (items <= item_cap || chunk >= max_pages) break;
+    chunk = std::min(max_pages, chunk + std::max(1, chunk / 8));
+  }
+  if (items > item_cap) {
+    set_error("relux_gqa_decode_noalloc: %ld work items x %d query rows need %zu bytes of partials; the fixed scratch holds %zu "
+              "(limits: %d items, %d sequences, 16 MiB in total)",
+              items, rows_total, (size_t)items * rows_total * kNaBytesPerRow, kNaPartBytes, kNoAllocMaxItems, kNoAllocMaxSeqs);
+    return RELUX_ERR_UNSUPPORTED;
+  }
+  // First call on this device: resolve the device address of the scratch array (the device is current here).
+  if (dev->index < 0 || dev->index >= kNoAllocMaxDevices) { set_error("device index %d beyond %d", dev->index, kNoAllocMaxDevices); return RELUX_ERR_UNSUPPORTED; }
+  unsigned char* base = nullptr;
+  {
+    std::lock_guard<std::mutex> g2(g_noalloc_mu);
+    NoAllocSlot& slot = g_noalloc_slot[dev->index];
+    if (!slot.ready) {
+      void* ptr = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+      if (e != cudaSuccess || !ptr) return cuda_fail(e != cudaSuccess ? e : cudaErrorInvalidSymbol, "cudaGetSymbolAddress(g_noalloc_scratch)");
+      slot.base = (unsigned char*)ptr;
+      slot.ready = true;
+    }
+    base = slot.base;
+  }
+  WorkItem* d_items = (WorkItem*)(base + kNaItemsOff);
+  int32_t* d_chunk_off = (int32_t*)(base + kNaChunkOff);
+  float* d_part_ml = (float*)(base + kNaPartOff);
+  float* d_part_o = d_part_ml + (size_t)items * rows_total * 2;
+  cudaStream_t st = dev->stream;
+  const int32_t* len = p->d_len + (size_t)a->layer * prm.max_seqs;
+  rc = launch_build_worklist_raw(st, len, sb.d_seq_ids, sb.n_seqs, a->extra_tokens, prm.page_tokens, chunk, d_items, d_chunk_off);
+  if (rc) return rc;
+  count_launch(dev);
+  GqaParams k;
+  k.items = d_items;
+  k.table = p->d_table;
+  k.table_stride = prm.max_pages_per_seq;
+  k.len = len;
+  k.num_pages = prm.num_pages;
+  k.Hkv = prm.gqa_num_kv_heads;
+  k.H = a->num_heads;
+  k.g = g;
+  k.S = a->q_tokens;
+  k.R = R;
+  k.extra = a->extra_tokens;
+  k.causal = a->causal;
+  const int64_t rows_per_block = (int64_t)prm.num_pages * prm.gqa_num_kv_heads * kPageTok;
+  k.krow0 = (int32_t)((int64_t)a->layer * 2 * rows_per_block);
+  k.vrow0 = (int32_t)((int64_t)a->layer * 2 * rows_per_block + rows_per_block);
+  k.scale_log2 = a->scale * 1.4426950408889634f;
+  k.q = a->q;
+  k.q_bf16 = a->q_dtype == RELUX_DTYPE_BF16;
+  k.part_o = d_part_o;
+  k.part_ml = d_part_ml;
+  k.rows_total = rows_total;
+  k.status = p->d_status;
+  dim3 grid((unsigned)items, prm.gqa_num_kv_heads);
+  if (R <= 16) {
+    constexpr size_t smem = gqa_smem_bytes<1>();
+    RELUX_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    gqa_decode_kernel<1><<<grid, 160, smem, st>>>(p->tmap_gqa, k);
+  } else {
+    constexpr size_t smem = gqa_smem_bytes<2>();
+    RELUX_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    gqa_decode_kernel<2><<<grid, 160, smem, st>>>(p->tmap_gqa, k);
+  }
+  RELUX_CUDA_TRY(cudaGetLastError());
+  count_launch(dev);
+  rc = launch_merge_raw(st, d_part_o, d_part_ml, d_chunk_off, sb.n_seqs, rows_total, kD, (float*)a->out);
+  if (rc) return rc;
+  count_launch(dev);
+  return RELUX_OK;
+}

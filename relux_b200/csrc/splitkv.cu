@@ -139,4 +139,19 @@ int32_t launch_merge(Pool* p, const SplitPlan& plan, int n_seqs, int rows, int w
   return RELUX_OK;
 }
 
+// Raw launchers on caller-provided buffers (no pool scratch involved).
+int32_t launch_build_worklist_raw(cudaStream_t st, const int32_t* len, const int32_t* seq_ids, int n_seqs, int extra, int page_tokens,
+                                  int chunk_pages, WorkItem* items, int32_t* chunk_off) {
+  build_worklist_kernel<<<1, 256, 0, st>>>(len, seq_ids, n_seqs, extra, page_tokens, chunk_pages, items, chunk_off);
+  RELUX_CUDA_TRY(cudaGetLastError());
+  return RELUX_OK;
+}
+int32_t launch_merge_raw(cudaStream_t st, const float* part_o, const float* part_ml, const int32_t* chunk_off, int n_seqs, int rows,
+                         int width, float* out) {
+  dim3 grid(rows, n_seqs);
+  merge_splits_kernel<<<grid, 128, 0, st>>>(part_o, part_ml, chunk_off, rows, width, out, nullptr);
+  RELUX_CUDA_TRY(cudaGetLastError());
+  return RELUX_OK;
+}
+
 }  // namespace relux

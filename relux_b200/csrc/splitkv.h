@@ -1,5 +1,6 @@
 // Split-KV work list shared by the FAST attention kernels.
 #pragma once
+#include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace relux {
@@ -22,6 +23,10 @@ struct Pool;
 struct SeqBatch;
 int32_t plan_splitkv(Pool* p, const SeqBatch& sb, int layer, int extra, int ctas_per_item, int min_chunk_pages, int chunk_multiple,
                      int max_chunk_pages, SplitPlan* plan);
+int32_t launch_build_worklist_raw(cudaStream_t st, const int32_t* len, const int32_t* seq_ids, int n_seqs, int extra, int page_tokens,
+                                  int chunk_pages, WorkItem* items, int32_t* chunk_off);
+int32_t launch_merge_raw(cudaStream_t st, const float* part_o, const float* part_ml, const int32_t* chunk_off, int n_seqs, int rows,
+                         int width, float* out);
 int32_t launch_merge(Pool* p, const SplitPlan& plan, int n_seqs, int rows, int width, float* out, uint16_t* out_bf16);
 
 }  // namespace relux
