@@ -18,6 +18,10 @@ namespace relux {
 
 int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const SplitPlan& plan, const uint16_t* q_abs);
 bool mla_sm100_eligible(const Pool* p, const relux_attn_args& a);
+bool mla_proj_mma_eligible(int Dh, int dC);
+int32_t launch_mla_absorb_mma(Device* dev, const void* q_nope, const void* q_rope, int q_bf16, const uint16_t* W_UK, uint16_t* q_abs,
+                              int rows, int H, int dC, int dHR);
+int32_t launch_mla_vup_mma(Device* dev, const uint16_t* o_lat, const uint16_t* W_UV, float* out, int rows, int H, int dC);
 
 namespace {
 
@@ -241,7 +245,12 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   cudaStream_t st = p->dev->stream;
   int32_t rc = grow(p->dev, p->q_abs, (size_t)rows * H * roww * 2);
   if (rc) return rc;
-  {
+  const bool proj_mma = mla_proj_mma_eligible(Dh, dC);
+  if (proj_mma) {
+    rc = launch_mla_absorb_mma(p->dev, d_q, d_qr, a.q_dtype == RELUX_DTYPE_BF16, (const uint16_t*)a.w_uk, (uint16_t*)p->q_abs.p, rows, H, dC,
+                               dHR);
+    if (rc) return rc;
+  } else {
     dim3 grid(H, (dC + 63) / 64, (rows + 15) / 16);
     size_t smem = ((size_t)64 * (Dh + 1) + (size_t)16 * Dh) * 4;
     if (smem > 48 * 1024) RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_absorb_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -295,9 +304,15 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   RELUX_CUDA_TRY(cudaEventRecord(p->ev1, st));
   p->timed = true;
   count_launch(p->dev);
-  rc = launch_merge(p, plan, sb.n_seqs, rows_total, dC, (float*)p->o_lat.p, nullptr);
-  if (rc) return rc;
-  {
+  if (proj_mma) {
+    // merged latent output goes to the up-projection as bf16 (tensor-core operand)
+    rc = launch_merge(p, plan, sb.n_seqs, rows_total, dC, nullptr, (uint16_t*)p->o_lat.p);
+    if (rc) return rc;
+    rc = launch_mla_vup_mma(p->dev, (const uint16_t*)p->o_lat.p, (const uint16_t*)a.w_uv, (float*)d_out, rows, H, dC);
+    if (rc) return rc;
+  } else {
+    rc = launch_merge(p, plan, sb.n_seqs, rows_total, dC, (float*)p->o_lat.p, nullptr);
+    if (rc) return rc;
     dim3 grid(H, (rows + 7) / 8);
     size_t smem = (size_t)8 * dC * 4;
     int threads = ((Dh + 31) / 32) * 32;

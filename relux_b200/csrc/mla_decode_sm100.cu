@@ -98,6 +98,12 @@ struct MlaSm100Params {
 // waiter records RELUX_ERR_TIMEOUT, raises the CTA's abort flag and RETURNS: nobody leaves a loop early, every
 // later wait sees the flag on its first failed poll and returns at once, so all warps still reach the named
 // barriers and the final cluster barrier with garbage results and a non-zero status word.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __noinline__ void wait_slow(uint64_t* bar, uint32_t parity, Bars* b, int32_t* status) {
   for (uint32_t i = 0; i < kSpinLimit; i++) {
     if (mbar_try_wait(bar, parity)) return;
@@ -136,7 +142,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     for (int i = 0; i < 4; i++) { mbar_init(&bars->v_full[i], 1); mbar_init(&bars->v_empty[i], 1); }
     mbar_init(&bars->s_full[0], 1);
     mbar_init(&bars->s_full[1], 1);
-    mbar_init(&bars->p_full, 2);    // one arrival per CTA of the pair
+    mbar_init(&bars->p_full, 8);    // one arrival per softmax warp of each CTA of the pair
     mbar_init(&bars->pv_done, 1);
     mbar_init(&bars->q_full, 1);
     bars->abort_flag = 0;
@@ -295,19 +301,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       tmem_ld_32x32b_x32(tmem + lane_addr + kTmemS + (i & 1) * 64, sv[0]);
       tmem_ld_32x32b_x32(tmem + lane_addr + kTmemS + (i & 1) * 64 + 32, sv[1]);
       tmem_ld_wait();
-      // valid tokens of this thread's 64: [0, nvalid)
+      // valid tokens of this thread's 64: [0, nvalid); only the last tile(s) of a chunk are partial
       const int tok0 = (item.page_begin + 2 * i + hf) * kPage;
       const int nvalid = (item.page_begin + 2 * i + hf < item.page_end) ? max(0, min(kPage, tok_end - tok0)) : 0;
+      if (nvalid < kPage) {
+#pragma unroll
+        for (int h2 = 0; h2 < 2; h2++)
+#pragma unroll
+          for (int j = 0; j < 32; j++)
+            if (h2 * 32 + j >= nvalid) sv[h2][j] = 0xFF800000u;  // -inf
+      }
+      // row max of the raw scores (the softmax scale is positive, so it commutes with max)
       float mx = -INFINITY;
 #pragma unroll
       for (int h2 = 0; h2 < 2; h2++)
 #pragma unroll
-        for (int j = 0; j < 32; j++) {
-          float v = __uint_as_float(sv[h2][j]) * prm.scale_log2;
-          if (h2 * 32 + j >= nvalid) v = -INFINITY;
-          sv[h2][j] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
+        for (int j = 0; j < 32; j++) mx = fmaxf(mx, __uint_as_float(sv[h2][j]));
+      mx *= prm.scale_log2;
       bars->rowmax[i & 1][hf][row] = mx;
       PROF_ADD(1);
       { PROF_T0();
@@ -326,15 +336,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         rescale = (m_used != -INFINITY);
         m_used = mx;
       }
-      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+      // p = 2^(s * scale_log2 - m): one FFMA and one MUFU.EX2 per score
+      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
       float psum = 0.f;
       uint32_t pk[32];
 #pragma unroll
       for (int h2 = 0; h2 < 2; h2++)
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          const float p0 = exp2f(__uint_as_float(sv[h2][j]) - m_sub);
-          const float p1 = exp2f(__uint_as_float(sv[h2][j + 1]) - m_sub);
+          const float p0 = ex2_approx(fmaf(__uint_as_float(sv[h2][j]), prm.scale_log2, neg_m));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(sv[h2][j + 1]), prm.scale_log2, neg_m));
           psum += p0 + p1;
           __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
           pk[h2 * 16 + j / 2] = *reinterpret_cast<uint32_t*>(&b2);
@@ -375,9 +386,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       fence_proxy_async();
       PROF_ADD(7); }
       { PROF_T0();
-      asm volatile("bar.sync 2, 128;" ::: "memory");
+      __syncwarp();
       PROF_ADD(5); }
-      if (threadIdx.x == 0) mbar_arrive_cluster(p_full_lead);
+      if (lane == 0) mbar_arrive_cluster(p_full_lead);
     }
     if (threadIdx.x == 0) PROF_FLUSH(2);
     // ---- epilogue: O (unnormalised), running max and sum of this chunk -> split-KV partial ----

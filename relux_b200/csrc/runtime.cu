@@ -253,6 +253,7 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
     return RELUX_ERR_INVALID_ARG;
   }
   if (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE) { set_error("bad mode"); return RELUX_ERR_INVALID_ARG; }
+  if (!(a->scale > 0.f)) { set_error("scale=%g, must be > 0", (double)a->scale); return RELUX_ERR_INVALID_ARG; }
   SeqBatch sb;
   rc = stage_batch(p, a->n_seqs, a->seq_ids, nullptr, a->q_tokens, &sb);
   if (rc) return rc;
