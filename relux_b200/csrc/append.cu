@@ -35,7 +35,7 @@ struct AppendGeom {
 // MLA row = [dC | dHR] fused, dC and dHR multiples of 8.
 template <bool kF32>
 __global__ void mla_append_kernel(AppendGeom g, uint16_t* __restrict__ layer_base, const void* __restrict__ ckv,
-                                  const void* __restrict__ kr, int dC, int dHR) {
+                                  const void* __restrict__ kr, int dC, int dHR, int blocked) {
   const int i = blockIdx.x;
   const int seq = g.seq_ids ? g.seq_ids[i] : i;
   const int r0 = g.row_off ? g.row_off[i] : i;
@@ -50,11 +50,11 @@ __global__ void mla_append_kernel(AppendGeom g, uint16_t* __restrict__ layer_bas
       if (slot >= g.max_pages_per_seq) set_status(g.status, RELUX_ERR_OVERFLOW);
       continue;
     }
-    uint16_t* dst = layer_base + ((size_t)pg * g.page_tokens + (pos % g.page_tokens)) * row_elems;
+    uint16_t* page = layer_base + (size_t)pg * g.page_tokens * row_elems;
     for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
       uint4 w = (v < vc) ? load8_as_bf16<kF32>(ckv, (size_t)(r0 + r) * dC + (size_t)v * 8)
                          : load8_as_bf16<kF32>(kr, (size_t)(r0 + r) * dHR + (size_t)(v - vc) * 8);
-      reinterpret_cast<uint4*>(dst)[v] = w;
+      *reinterpret_cast<uint4*>(page + mla_page_off(blocked != 0, g.page_tokens, row_elems, pos % g.page_tokens, v * 8)) = w;
     }
   }
 }
@@ -137,9 +137,9 @@ int32_t launch_mla_append(Pool* p, const SeqBatch& sb, int layer, const void* ck
   dim3 grid(sb.n_seqs, std::min(std::max(sb.max_rows, 1), 64));
   int threads = 96;  // 72 vectors per 576-element row
   if (dtype == RELUX_DTYPE_F32)
-    mla_append_kernel<true><<<grid, threads, 0, p->dev->stream>>>(g, base, ckv, kr, p->prm.mla_dc, p->prm.mla_dhr);
+    mla_append_kernel<true><<<grid, threads, 0, p->dev->stream>>>(g, base, ckv, kr, p->prm.mla_dc, p->prm.mla_dhr, p->mla_blocked);
   else
-    mla_append_kernel<false><<<grid, threads, 0, p->dev->stream>>>(g, base, ckv, kr, p->prm.mla_dc, p->prm.mla_dhr);
+    mla_append_kernel<false><<<grid, threads, 0, p->dev->stream>>>(g, base, ckv, kr, p->prm.mla_dc, p->prm.mla_dhr, p->mla_blocked);
   return finish_append(p, sb, layer, advance);
 }
 
@@ -169,7 +169,7 @@ int32_t launch_set_len(Pool* p, const SeqBatch& sb, int layer, const int32_t* d_
 // Logical rows [tok0, tok0+n) of one sequence -> dense buffers (the View of the reference caches).
 __global__ void gather_rows_kernel(const uint16_t* __restrict__ layer_base, const int32_t* __restrict__ table, int table_stride,
                                    int seq, int tok0, int n, int num_pages, int page_tokens, int kind, int dC, int dHR, int Hkv, int D,
-                                   size_t v_off, uint16_t* __restrict__ da, uint16_t* __restrict__ db, int32_t* status) {
+                                   size_t v_off, uint16_t* __restrict__ da, uint16_t* __restrict__ db, int32_t* status, int blocked) {
   const int r = blockIdx.x;
   if (r >= n) return;
   const int pos = tok0 + r;
@@ -177,10 +177,11 @@ __global__ void gather_rows_kernel(const uint16_t* __restrict__ layer_base, cons
   if (!page_of(table, table_stride, seq, pos / page_tokens, num_pages, status, &pg)) return;
   const int in_pg = pos % page_tokens;
   if (kind == RELUX_POOL_MLA) {
-    const uint16_t* src = layer_base + ((size_t)pg * page_tokens + in_pg) * (dC + dHR);
+    const uint16_t* page = layer_base + (size_t)pg * page_tokens * (dC + dHR);
     for (int e = threadIdx.x; e < dC + dHR; e += blockDim.x) {
-      if (e < dC) da[(size_t)r * dC + e] = src[e];
-      else db[(size_t)r * dHR + (e - dC)] = src[e];
+      const uint16_t x = page[mla_page_off(blocked != 0, page_tokens, dC + dHR, in_pg, e)];
+      if (e < dC) da[(size_t)r * dC + e] = x;
+      else db[(size_t)r * dHR + (e - dC)] = x;
     }
   } else {
     for (int e = threadIdx.x; e < Hkv * D; e += blockDim.x) {
@@ -197,7 +198,7 @@ int32_t launch_gather_rows(Pool* p, int layer, int seq, int tok0, int n, uint16_
   const uint16_t* base = p->storage + (size_t)layer * p->layer_elems;
   gather_rows_kernel<<<n, 128, 0, p->dev->stream>>>(base, p->d_table, prm.max_pages_per_seq, seq, tok0, n, prm.num_pages,
                                                     prm.page_tokens, prm.kind, prm.mla_dc, prm.mla_dhr, prm.gqa_num_kv_heads,
-                                                    prm.gqa_head_dim, p->page_elems * prm.num_pages, d_a, d_b, p->d_status);
+                                                    prm.gqa_head_dim, p->page_elems * prm.num_pages, d_a, d_b, p->d_status, p->mla_blocked);
   RELUX_CUDA_TRY(cudaGetLastError());
   count_launch(p->dev);
   return RELUX_OK;

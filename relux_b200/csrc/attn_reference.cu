@@ -22,6 +22,7 @@ struct RefGeom {
   int32_t* status;
   int32_t S, extra, causal, H;
   float scale;
+  int32_t blocked;   // MLA page layout (see mla_page_off)
 };
 
 // Shared tail: softmaxRows over w[S][T] and nothing else; all threads of the CTA call it.
@@ -114,7 +115,9 @@ __global__ void mla_reference_kernel(RefGeom g, const uint16_t* __restrict__ bas
   for (int j = tid; j < T; j += nt) {
     int32_t pg;
     bool ok = page_of(g.table, g.table_stride, seq, j / g.page_tokens, g.num_pages, g.status, &pg);
-    const uint16_t* cr = base + ((size_t)(ok ? pg : 0) * g.page_tokens + (j % g.page_tokens)) * row;
+    const uint16_t* page = base + (size_t)(ok ? pg : 0) * g.page_tokens * row;
+    const int tk = j % g.page_tokens;
+    const bool blk = g.blocked != 0;
     for (int s = 0; s < S; s++) {
       const float* qcv = qc + (((size_t)i * S + s) * H + h) * Dh;
       const float* qrv = qr + (((size_t)i * S + s) * H + h) * dHR;
@@ -123,11 +126,13 @@ __global__ void mla_reference_kernel(RefGeom g, const uint16_t* __restrict__ bas
       for (int d = 0; d < Dh; d++) {
         float kc = 0.0f;
         for (int c = 0; c < dC; c++)
-          kc = __fadd_rn(kc, __fmul_rn(f32_from_bf16_bits(cr[c]), f32_from_bf16_bits(W_UK[(size_t)c * wstride + (size_t)h * Dh + d])));
+          kc = __fadd_rn(kc, __fmul_rn(f32_from_bf16_bits(page[mla_page_off(blk, g.page_tokens, row, tk, c)]),
+                                       f32_from_bf16_bits(W_UK[(size_t)c * wstride + (size_t)h * Dh + d])));
         a = __fadd_rn(a, __fmul_rn(qcv[d], kc));
       }
       float r = 0.0f;
-      for (int d = 0; d < dHR; d++) r = __fadd_rn(r, __fmul_rn(qrv[d], f32_from_bf16_bits(cr[dC + d])));
+      for (int d = 0; d < dHR; d++)
+        r = __fadd_rn(r, __fmul_rn(qrv[d], f32_from_bf16_bits(page[mla_page_off(blk, g.page_tokens, row, tk, dC + d)])));
       float v = __fmul_rn(__fadd_rn(a, r), g.scale);
       if (g.causal && j > T - S + s) v = -INFINITY;
       w[(size_t)s * T + j] = ok ? v : -INFINITY;
@@ -141,10 +146,12 @@ __global__ void mla_reference_kernel(RefGeom g, const uint16_t* __restrict__ bas
     for (int j = 0; j < T; j++) {
       int32_t pg = g.table[(size_t)seq * g.table_stride + j / g.page_tokens];
       if (pg < 0 || pg >= g.num_pages) continue;
-      const uint16_t* cr = base + ((size_t)pg * g.page_tokens + (j % g.page_tokens)) * row;
+      const uint16_t* page = base + (size_t)pg * g.page_tokens * row;
+      const int tk = j % g.page_tokens;
       float vv = 0.0f;
       for (int c = 0; c < dC; c++)
-        vv = __fadd_rn(vv, __fmul_rn(f32_from_bf16_bits(cr[c]), f32_from_bf16_bits(W_UV[(size_t)c * wstride + (size_t)h * Dh + d])));
+        vv = __fadd_rn(vv, __fmul_rn(f32_from_bf16_bits(page[mla_page_off(g.blocked != 0, g.page_tokens, row, tk, c)]),
+                                     f32_from_bf16_bits(W_UV[(size_t)c * wstride + (size_t)h * Dh + d])));
       o = __fadd_rn(o, __fmul_rn(w[(size_t)s * T + j], vv));
     }
     out[(((size_t)i * S + s) * H + h) * Dh + d] = o;
@@ -173,6 +180,7 @@ static int32_t ref_geom(Pool* p, const SeqBatch& sb, const relux_attn_args& a, R
   g->causal = a.causal;
   g->H = a.num_heads;
   g->scale = a.scale;
+  g->blocked = p->mla_blocked ? 1 : 0;
   return RELUX_OK;
 }
 

@@ -60,6 +60,16 @@ __device__ __forceinline__ bool page_of(const int32_t* __restrict__ table, int32
   return true;
 }
 
+// Element offset of (token-in-page, column) inside one MLA page.
+//   blocked (page_tokens = 64 and row width a multiple of 64): the page is stored as
+//     [row_width / 64 column blocks][64 tokens][64 columns], so each 64 x 64 tile a TMA box fetches is one
+//     contiguous 8 KB run of HBM instead of 64 pieces of 128 bytes 1152 bytes apart;
+//   otherwise token-major [page_tokens][row_width].
+// A vector of 8 consecutive columns starting at a multiple of 8 never straddles a block.
+__device__ __forceinline__ size_t mla_page_off(bool blocked, int page_tokens, int row_width, int tok, int col) {
+  return blocked ? ((size_t)(col >> 6) * page_tokens + tok) * 64 + (col & 63) : (size_t)tok * row_width + col;
+}
+
 // ---------------------------------------------------------------------------------------------
 // PTX wrappers: shared-memory addresses, mbarrier with bounded waits, TMA, ldmatrix, mma.sync.
 // ---------------------------------------------------------------------------------------------

@@ -80,6 +80,7 @@ struct Pool {
   CUtensorMap tmap_mla{};   // 2-D [rows][dC+dHR], box 64 x 64, 128-byte swizzle
   CUtensorMap tmap_gqa{};   // 2-D [rows][D],      box 64 x 64, 128-byte swizzle
   bool has_tmap = false;
+  bool mla_blocked = false;   // MLA pages stored as 64-column blocks (see mla_page_off)
   // timing of the dominant kernel
   cudaEvent_t ev0 = nullptr, ev1 = nullptr;
   bool timed = false;

@@ -103,7 +103,7 @@ struct MlaGenParams {
   const int32_t* table;
   int32_t table_stride;
   const int32_t* len;
-  int32_t num_pages, page_tokens, H, S, extra, causal, dHR;
+  int32_t num_pages, page_tokens, H, S, extra, causal, dHR, blocked;
   const uint16_t* base;
   const uint16_t* q_abs;
   float scale_log2;
@@ -154,7 +154,8 @@ __global__ void __launch_bounds__(256) mla_decode_generic_kernel(const MlaGenPar
       if (tok < tok_end) {
         int32_t pg;
         if (page_of(prm.table, prm.table_stride, item.seq, tok / prm.page_tokens, prm.num_pages, prm.status, &pg))
-          x = reinterpret_cast<const uint4*>(prm.base + ((size_t)pg * prm.page_tokens + tok % prm.page_tokens) * roww)[v];
+          x = *reinterpret_cast<const uint4*>(prm.base + (size_t)pg * prm.page_tokens * roww +
+                                              mla_page_off(prm.blocked != 0, prm.page_tokens, roww, tok % prm.page_tokens, v * 8));
       }
       uint32_t* dst = tile + r * stride_w + v * 4;
       dst[0] = x.x; dst[1] = x.y; dst[2] = x.z; dst[3] = x.w;
@@ -286,6 +287,7 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
     k.extra = a.extra_tokens;
     k.causal = a.causal;
     k.dHR = dHR;
+    k.blocked = p->mla_blocked ? 1 : 0;
     k.base = p->storage + (size_t)a.layer * p->layer_elems;
     k.q_abs = (const uint16_t*)p->q_abs.p;
     k.scale_log2 = a.scale * 1.4426950408889634f;

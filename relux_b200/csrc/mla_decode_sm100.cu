@@ -159,7 +159,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       set_status(prm.status, RELUX_ERR_BAD_PAGE);
       pg = 0;
     }
-    bars->page_row[i] = prm.layer_row0 + pg * kPage;
+    bars->page_row[i] = prm.layer_row0 + pg * (kNumKB * kPage);   // first TMA row of the page's block 0
   }
   tc_fence_before();
   cluster_sync();
@@ -198,7 +198,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 #pragma unroll
           for (int j = 0; j < kKPerGroup; j++) {
             const int db = g * kKPerGroup + j;
-            tma_load_2d_2sm(smem + kSmemK + db * kBlk, &tmap_kv, db * 64, y, lead);
+            tma_load_2d_2sm(smem + kSmemK + db * kBlk, &tmap_kv, 0, y + db * kPage, lead);
           }
         }
         __syncwarp();
@@ -211,11 +211,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         if (tile > 0) wait_bar(&bars->v_empty[u], (tile - 1) & 1, bars, prm.status);
         const int32_t y = page_row(tile, kb);
         const uint32_t lead = mapa_u32(smem_u32(&bars->v_full[u]), 0);
-        const int x = 256 * nb + 128 * (int)rank;
+        const int blk0 = 4 * nb + 2 * (int)rank;   // this CTA's 128 output dims of block nb = column blocks blk0, blk0 + 1
         if (el) {
           if (rank == 0) mbar_expect_tx(&bars->v_full[u], 4 * kBlk);
-          tma_load_2d_2sm(smem + kSmemV + u * 2 * kBlk, &tmap_kv, x, y, lead);
-          tma_load_2d_2sm(smem + kSmemV + u * 2 * kBlk + kBlk, &tmap_kv, x + 64, y, lead);
+          tma_load_2d_2sm(smem + kSmemV + u * 2 * kBlk, &tmap_kv, 0, y + blk0 * kPage, lead);
+          tma_load_2d_2sm(smem + kSmemV + u * 2 * kBlk + kBlk, &tmap_kv, 0, y + (blk0 + 1) * kPage, lead);
         }
         __syncwarp();
       }
@@ -228,6 +228,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
   } else if (warp == 5) {
     // =============================== MMA issuer (leader CTA only, converged warp + elected lane) ===============================
     if (rank == 0) {
+      PROF_DECL();
       const bool el = elect_one();
       const uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
       const uint32_t idesc_pv = make_idesc_bf16(128, 256, false, true);
@@ -241,7 +242,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         const uint32_t d = tmem + kTmemS + (tile & 1) * 64;
 #pragma unroll
         for (int g = 0; g < kKGroups; g++) {
+          { PROF_T0();
           wait_bar(&bars->k_full[g], tile & 1, bars, prm.status);
+          PROF_ADD(0); }
           if (el) {
 #pragma unroll
             for (int j = 0; j < kKPerGroup * 4; j++) {
@@ -256,12 +259,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         __syncwarp();
       };
       auto issue_pv = [&](int tile) {
+        { PROF_T0();
         wait_bar(&bars->p_full, tile & 1, bars, prm.status);
+        PROF_ADD(1); }
         tc_fence_after();   // P rows and a possible O rescale were written by the softmax warps of both CTAs
 #pragma unroll
         for (int u = 0; u < 4; u++) {
           const int nb = u >> 1, kb = u & 1;
+          { PROF_T0();
           wait_bar(&bars->v_full[u], tile & 1, bars, prm.status);
+          PROF_ADD(2); }
           if (el) {
 #pragma unroll
             for (int kk = 0; kk < 4; kk++)
@@ -279,6 +286,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         if (i + 1 < ntiles) issue_qk(i + 1);
         issue_pv(i);
       }
+      if (lane == 0) PROF_FLUSH(1);
     }
   } else {
     // =============================== softmax / correction / epilogue (warps 0-3) ===============================
@@ -432,7 +440,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 bool mla_sm100_eligible(const Pool* p, const relux_attn_args& a) {
   const relux_pool_params& prm = p->prm;
   if (getenv("RELUX_MLA_GENERIC")) return false;
-  return p->has_tmap && prm.page_tokens == kPage && prm.mla_dc == kDC && prm.mla_dhr == kDR && a.num_heads == kHeads;
+  return p->has_tmap && p->mla_blocked && prm.page_tokens == kPage && prm.mla_dc == kDC && prm.mla_dhr == kDR && a.num_heads == kHeads;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -473,7 +481,7 @@ int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_ar
   k.S = a.q_tokens;
   k.extra = a.extra_tokens;
   k.causal = a.causal;
-  k.layer_row0 = (int32_t)((int64_t)a.layer * prm.num_pages * kPage);
+  k.layer_row0 = (int32_t)((int64_t)a.layer * prm.num_pages * kNumKB * kPage);
   k.scale_log2 = a.scale * 1.4426950408889634f;
   k.part_o = (float*)p->part_o.p;
   k.part_ml = (float*)p->part_ml.p;
@@ -495,7 +503,7 @@ int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_ar
     long long h[64 * 8];
     cudaStreamSynchronize(p->dev->stream);
     cudaMemcpy(h, d_prof, sizeof(h), cudaMemcpyDeviceToHost);
-    const char* names[3] = {"producer [k_empty v_empty]", "mma      [k_full p_full v_full k_age_sum k_stalls v_age_sum v_stalls]", "softmax  [s_full math1 barmax math2 pv_done barP Pwrite fence_proxy]"};
+    const char* names[3] = {"producer [k_empty v_empty]", "mma      [k_full p_full v_full]", "softmax  [s_full math1 barmax math2 pv_done barP Pwrite fence_proxy]"};
     for (int cta = 0; cta < 2; cta++)
       for (int r = 0; r < 3; r++) {
         fprintf(stderr, "prof cta%d %s:", cta, names[r]);

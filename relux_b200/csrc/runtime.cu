@@ -605,8 +605,10 @@ API int32_t relux_pool_create(relux_device_t h, const relux_pool_params* prm, re
   p->has_tmap = false;
   if (prm->page_tokens == 64) {
     if (prm->kind == RELUX_POOL_MLA && p->row_elems_a % 64 == 0) {
-      uint64_t rows = (uint64_t)prm->num_layers * prm->num_pages * prm->page_tokens;
-      p->has_tmap = make_tmap_2d(&p->tmap_mla, p->storage, rows, (uint64_t)p->row_elems_a, 64, 64);
+      // blocked page layout: the whole pool is one [blocks * 64][64] array, every TMA box is one contiguous 8 KB block
+      p->mla_blocked = true;
+      uint64_t rows = (uint64_t)prm->num_layers * prm->num_pages * (p->row_elems_a / 64) * prm->page_tokens;
+      p->has_tmap = make_tmap_2d(&p->tmap_mla, p->storage, rows, 64, 64, 64);
     } else if (prm->kind == RELUX_POOL_GQA && prm->gqa_head_dim % 64 == 0) {
       uint64_t rows = (uint64_t)prm->num_layers * 2 * prm->num_pages * prm->gqa_num_kv_heads * prm->page_tokens;
       p->has_tmap = make_tmap_2d(&p->tmap_gqa, p->storage, rows, (uint64_t)prm->gqa_head_dim, 64, 64);
