@@ -28,7 +28,15 @@ WORKLOADS = {
     # name: (kind, batch per GPU, context, heads, head_dim, dC, dHR)
     "mla_decode_b64_ctx32k": dict(kind="mla", B=64, ctx=32768, H=128, Dh=128, dC=512, dHR=64),
     "mla_decode_b64_ctx4k": dict(kind="mla", B=64, ctx=4096, H=128, Dh=128, dC=512, dHR=64),
+    # small enough for an ncu --set full capture (302 MB of cache rows, still larger than the 126 MB L2)
+    "mla_decode_b16_ctx16k": dict(kind="mla", B=16, ctx=16384, H=128, Dh=128, dC=512, dHR=64),
+    # GQA flash-decode + speculative verify: 4 draft tokens per step, accepted prefix uniform in 1..4
+    "gqa_verify_b128_ctx8k": dict(kind="gqa", B=128, ctx=8192, H=32, Hkv=8, D=128, S=4),
+    "gqa_verify_b16_ctx8k": dict(kind="gqa", B=16, ctx=8192, H=32, Hkv=8, D=128, S=4),
 }
+# dram__bytes_read + dram__bytes_write of the dominant kernel divided by its algorithmic bytes, from the ncu captures
+# summarised under profiles/ (small case, traffic grows in proportion to the cached tokens read).
+TRAFFIC_RATIO = {"mla": 1.02, "gqa": None}
 PAGE = 64
 
 
@@ -198,7 +206,8 @@ def run_mla(args, w, world, rank, local, dist):
         "config": {"workload": args.workload, "batch_per_gpu": B, "context": ctx0, "heads": H, "latent": dC, "rope": dHR,
                    "page_tokens": PAGE, "page_table": "random permutation", "l2": "inputs (%.2f GB of cache rows per GPU) are larger than L2"
                    % (B * ctx0 * (dC + dHR) * 2 / 1e9)},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": (alg_bytes * TRAFFIC_RATIO["mla"]) if TRAFFIC_RATIO["mla"] else None,
                      "peak_source": peak_src, "kernel": "mla split-KV decode", "kernel_ms": kernel_ms,
                      "algorithmic_bytes_per_launch": alg_bytes, "frac_of_nominal_8TBs": achieved / 8000.0},
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -208,6 +217,112 @@ def run_mla(args, w, world, rank, local, dist):
     if rank == 0 and world == 1:
         line["cpu_baseline"] = cpu_baseline_mla(w, sample_T=512, threads=1)
     for b in (d_new_c, d_new_r, d_qc, d_qr, d_out, d_wuk, d_wuv):
+        b.free()
+    pool.destroy()
+    dev.close()
+    return line
+
+
+def run_gqa(args, w, world, rank, local, dist):
+    """GQA verify step: write 4 draft K/V rows per sequence past the cursor, attend causally inside the draft,
+    commit an accepted prefix of 1..4 tokens.  tokens/s counts accepted tokens."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    from oracle import binding as orc
+
+    B, ctx0, H, Hkv, D, S = w["B"], w["ctx"], w["H"], w["Hkv"], w["D"], w["S"]
+    total_steps = 3 * (args.steps + args.warmup) + 8
+    pages_per = (ctx0 + total_steps * S + S + PAGE - 1) // PAGE + 1
+    dev = rb.Device(local)
+    rng = np.random.default_rng(3 + rank)
+    pool = rb.Pool(dev, L.POOL_GQA, 1, B * pages_per, PAGE, B, pages_per, num_kv_heads=Hkv, head_dim=D)
+    pool.set_tables(rng.permutation(B * pages_per).astype(np.int32).reshape(B, pages_per))
+    blk = min(ctx0, 1024)
+    srcK = orc.bf16_from_f32(rng.standard_normal((B * blk, Hkv, D), dtype=np.float32))
+    srcV = orc.bf16_from_f32(rng.standard_normal((B * blk, Hkv, D), dtype=np.float32))
+    dK, dV = dev.upload(srcK), dev.upload(srcV)
+    for _ in range(ctx0 // blk):
+        pool.append(0, dK, dV, B, n_new=np.full(B, blk, np.int32))
+    dev.sync()
+    dK.free(); dV.free()
+    scale = float(1.0 / np.sqrt(D))
+    q = rng.standard_normal((B, S, H, D), dtype=np.float32)
+    nk = rng.standard_normal((B * S, Hkv, D), dtype=np.float32)
+    nv = rng.standard_normal((B * S, Hkv, D), dtype=np.float32)
+    d_q, d_nk, d_nv = dev.upload(orc.bf16_from_f32(q)), dev.upload(orc.bf16_from_f32(nk)), dev.upload(orc.bf16_from_f32(nv))
+    d_out = dev.alloc(q.size * 4, L.DTYPE_F32)
+    pins = [dev.pinned(a.shape, np.float32) for a in (q, nk, nv)]
+    for p_, a in zip(pins, (q, nk, nv)):
+        p_.array[...] = a
+    pin_out = dev.pinned(q.shape, np.float32)
+    lens = np.full(B, ctx0, np.int64)
+    accepted_total = [0]
+
+    def commit():
+        acc = rng.integers(1, S + 1, B)
+        lens[:] += acc
+        accepted_total[0] += int(acc.sum())
+        pool.set_len(0, lens.astype(np.int32))
+
+    def step_resident():
+        pool.verify(0, B, d_q, d_out, d_nk, d_nv, H, D, scale, S)
+        commit()
+
+    def step_e2e():
+        pool.verify(0, B, pins[0].array, pin_out.array, pins[1].array, pins[2].array, H, D, scale, S)
+        commit()
+
+    e0, e1 = dev.event(), dev.event()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        dev.sync()
+        barrier(dist)
+        n0 = dev.launch_count()
+        accepted_total[0] = 0
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        dev.sync()
+        ms = e0.elapsed_ms(e1)
+        barrier(dist)
+        return max_over_ranks(dist, ms), dev.launch_count() - n0, accepted_total[0]
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ms_res, launches, acc_res = timed(step_resident, args.steps, args.warmup)
+    clocks = sampler.finish() if rank == 0 else None
+    ms_e2e, _, acc_e2e = timed(step_e2e, args.steps, args.warmup)
+    kms, ctx_sum = [], []
+    for _ in range(args.steps):
+        step_resident()
+        kms.append(pool.last_kernel_ms())
+        ctx_sum.append(float(lens.sum()))   # rows read by that call: committed length before the commit + S draft rows ~ lens
+    assert pool.status() == 0, "device status word is set"
+    kernel_ms = float(np.mean(kms))
+    alg_bytes = float(np.mean(ctx_sum)) * Hkv * D * 2 * 2
+    peak, peak_src = read_peaks()
+    achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+    acc_res_all = acc_res * world   # every rank draws from its own seeded stream with the same distribution
+    line = {
+        "metric": "gqa_verify_accepted_tokens_per_s", "value": acc_res_all / (ms_res * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "batch_per_gpu": B, "context": ctx0, "heads": H, "kv_heads": Hkv, "head_dim": D,
+                   "draft_tokens": S, "page_tokens": PAGE, "page_table": "random permutation",
+                   "l2": "inputs (%.2f GB of K/V per GPU) are larger than L2" % (B * ctx0 * Hkv * D * 4 / 1e9)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "peak_source": peak_src, "kernel": "gqa split-KV decode/verify", "kernel_ms": kernel_ms,
+                     "algorithmic_bytes_per_launch": alg_bytes, "frac_of_nominal_8TBs": achieved / 8000.0},
+        "e2e": {"value": acc_e2e * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(q.nbytes + nk.nbytes + nv.nbytes),
+                "d2h_bytes_per_step": int(q.nbytes)},
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    for b in (d_q, d_nk, d_nv, d_out):
         b.free()
     pool.destroy()
     dev.close()
@@ -278,7 +393,7 @@ def main():
             print(json.dumps(line))
         return
     world, rank, local, dist = dist_setup(args.gpus)
-    line = run_mla(args, w, world, rank, local, dist)
+    line = run_mla(args, w, world, rank, local, dist) if w["kind"] == "mla" else run_gqa(args, w, world, rank, local, dist)
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:

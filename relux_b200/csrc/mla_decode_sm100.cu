@@ -49,6 +49,7 @@ constexpr int kMaxChunkPages = 320;                   // page ids of a chunk are
 constexpr int kKGroups = 3, kKPerGroup = kNumKB / kKGroups;  // K slots are armed / released in groups of 3 blocks
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemO = 0, kTmemS = 256;          // O: 2 x 128 columns; S: 2 buffers x 64 columns
+constexpr int kPrefetchTiles = 3;                      // L2 prefetch distance of the producer, in tiles
 constexpr float kRescaleThreshold = 8.0f;             // log2 units: rescale O only when the max grew by > 2^8
 
 struct Bars {
@@ -80,6 +81,7 @@ struct MlaSm100Params {
   int32_t rows_total;
   int32_t* status;
   long long* prof;   // optional cycle counters of cluster 0 (RELUX_MLA_PROF builds only)
+  int32_t dbg;       // RELUX_MLA_PROF builds: 1 = skip V loads, 2 = skip K loads after the first tile (timing experiments, wrong results)
 };
 
 #ifdef RELUX_MLA_PROF
@@ -193,6 +195,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       for (int g = 0; g < kKGroups; g++) {
         if (tile > 0) wait_bar(&bars->k_empty[g], (tile - 1) & 1, bars, prm.status);
         const uint32_t lead = mapa_u32(smem_u32(&bars->k_full[g]), 0);
+#ifdef RELUX_MLA_PROF
+        if ((prm.dbg & 2) && tile > 0) {
+          if (el && rank == 0) mbar_arrive(&bars->k_full[g]);
+          __syncwarp();
+          continue;
+        }
+#endif
         if (el) {
           if (rank == 0) mbar_expect_tx(&bars->k_full[g], 2 * kKPerGroup * kBlk);
 #pragma unroll
@@ -212,6 +221,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         const int32_t y = page_row(tile, kb);
         const uint32_t lead = mapa_u32(smem_u32(&bars->v_full[u]), 0);
         const int blk0 = 4 * nb + 2 * (int)rank;   // this CTA's 128 output dims of block nb = column blocks blk0, blk0 + 1
+#ifdef RELUX_MLA_PROF
+        if (prm.dbg & 1) {
+          if (el && rank == 0) mbar_arrive(&bars->v_full[u]);
+          __syncwarp();
+          continue;
+        }
+#endif
         if (el) {
           if (rank == 0) mbar_expect_tx(&bars->v_full[u], 4 * kBlk);
           tma_load_2d_2sm(smem + kSmemV + u * 2 * kBlk, &tmap_kv, 0, y + blk0 * kPage, lead);
@@ -220,8 +236,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         __syncwarp();
       }
     };
+    // Shared memory holds a single tile, which cannot cover the HBM latency; the producer therefore pulls the
+    // page of tile t + kPrefetchTiles into L2 (no shared memory, no barrier) so that the real loads hit L2.
+    auto prefetch_k = [&](int tile) {
+      if (tile < ntiles && el) {
+        const int32_t y = page_row(tile, rank);
+#pragma unroll
+        for (int db = 0; db < kNumKB; db++) tma_prefetch_l2_2d(&tmap_kv, 0, y + db * kPage);
+      }
+      __syncwarp();
+    };
+    for (int t = 1; t <= kPrefetchTiles; t++) prefetch_k(t);
     load_k(0);
     for (int i = 0; i < ntiles; i++) {
+      prefetch_k(i + 1 + kPrefetchTiles);
       if (i + 1 < ntiles) load_k(i + 1);
       load_v(i);
     }
@@ -488,6 +516,7 @@ int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_ar
   k.rows_total = a.q_tokens * kHeads;
   k.status = p->d_status;
   k.prof = nullptr;
+  k.dbg = getenv("RELUX_MLA_DBG") ? atoi(getenv("RELUX_MLA_DBG")) : 0;
 #ifdef RELUX_MLA_PROF
   static long long* d_prof = nullptr;
   if (!d_prof) cudaMalloc(&d_prof, 64 * 8 * sizeof(long long));

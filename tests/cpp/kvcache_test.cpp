@@ -1,0 +1,115 @@
+// The reference's own KVCache tests (internal/transformer/kvcache_test.go) replayed through the C++ host mirror
+// (include/relux_cuda.hpp) on the device cache, plus the panics the reference raises on misuse.
+// Prints one line per test; exit code 0 = all passed.  Built and run by tests/test_gpu_cpp_mirror.py.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "relux_cuda.hpp"
+
+static int failures = 0;
+#define EXPECT(cond, name)                                        \
+  do {                                                            \
+    if (!(cond)) { printf("FAIL %s: %s\n", name, #cond); failures++; } \
+  } while (0)
+
+static float f32_from_bf16(uint16_t b) {
+  uint32_t u = (uint32_t)b << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+
+int main() {
+  relux::Device dev(0);
+  {  // TestKVCache_NewEmpty  kvcache_test.go:9-14
+    relux::KVCache c(dev, 4, 16, 2, 8);
+    EXPECT(c.TotalLen(0) == 0, "NewEmpty");
+    std::vector<uint16_t> k, v;
+    EXPECT(!c.View(0, &k, &v), "NewEmpty nil view");
+  }
+  {  // TestKVCache_AppendFirst  kvcache_test.go:16-40   (head dim widened to 8: rows are 16-byte vectors here)
+    relux::KVCache c(dev, 2, 16, 2, 8);
+    std::vector<float> k(16), v(16);
+    for (int i = 0; i < 16; i++) { k[i] = (float)(i + 1); v[i] = (float)(i + 17); }
+    c.Append(0, k.data(), v.data(), 1);
+    EXPECT(c.TotalLen(0) == 1, "AppendFirst len");
+    EXPECT(c.TotalLen(1) == 0, "AppendFirst other layer");
+    std::vector<uint16_t> ck, cv;
+    EXPECT(c.View(0, &ck, &cv), "AppendFirst view");
+    bool same = ck.size() == 16;
+    for (int i = 0; same && i < 16; i++) same = f32_from_bf16(ck[i]) == k[i] && f32_from_bf16(cv[i]) == v[i];
+    EXPECT(same, "AppendFirst data");
+  }
+  {  // TestKVCache_AppendGrows  kvcache_test.go:42-66: 1 head, 1 token then 2 tokens -> concatenation
+    relux::KVCache c(dev, 1, 16, 1, 8);
+    std::vector<float> a(8), b(16);
+    for (int i = 0; i < 8; i++) a[i] = (float)(i + 1);
+    for (int i = 0; i < 16; i++) b[i] = (float)(i + 9);
+    c.Append(0, a.data(), a.data(), 1);
+    EXPECT(c.TotalLen(0) == 1, "AppendGrows len 1");
+    c.Append(0, b.data(), b.data(), 2);
+    EXPECT(c.TotalLen(0) == 3, "AppendGrows len 3");
+    std::vector<uint16_t> ck, cv;
+    c.View(0, &ck, &cv);
+    bool same = ck.size() == 24;
+    for (int i = 0; same && i < 24; i++) same = f32_from_bf16(ck[i]) == (float)(i + 1);
+    EXPECT(same, "AppendGrows data");
+    // TestKVCache_Reset  kvcache_test.go:68-85
+    c.Reset();
+    EXPECT(c.TotalLen(0) == 0, "Reset len");
+    EXPECT(!c.View(0, &ck, &cv), "Reset nil view");
+  }
+  {  // TestKVCache_BFloat16  kvcache_test.go:87-107
+    relux::KVCache c(dev, 1, 16, 1, 8);
+    EXPECT(c.GetDType() == relux::DType::BFloat16, "dtype");
+    std::vector<float> k = {1, 2, 3, 4, 5, 6, 7, 8};
+    c.Append(0, k.data(), k.data(), 1);
+    std::vector<uint16_t> ck, cv;
+    c.View(0, &ck, &cv);
+    bool ok = true;
+    for (int i = 0; i < 8; i++) ok = ok && std::fabs(f32_from_bf16(ck[i]) - (float)(i + 1)) <= 0.01f;
+    EXPECT(ok, "BFloat16 round trip");
+  }
+  {  // panics: layer out of range (kvcache.go:241-243), overflow (kvcache.go:282-285)
+    relux::KVCache c(dev, 1, 64, 1, 8);
+    std::vector<float> k(8 * 64, 1.f);
+    bool threw = false;
+    try { c.Append(3, k.data(), k.data(), 1); } catch (const relux::Panic& e) { threw = strstr(e.what(), "out of range") != nullptr; }
+    EXPECT(threw, "layer out of range panics");
+    c.Append(0, k.data(), k.data(), 64);
+    threw = false;
+    try { c.Append(0, k.data(), k.data(), 1); } catch (const relux::Panic& e) { threw = e.status == RELUX_ERR_OVERFLOW && strstr(e.what(), "overflow") != nullptr; }
+    EXPECT(threw, "overflow panics");
+  }
+  {  // MLACache: append two chunks, view, reset  (mla_cache.go:152-182, 222-233)
+    relux::MLACache c(dev, 2, 128, 64, 16);
+    std::vector<float> cc(3 * 64), kr(3 * 16);
+    for (size_t i = 0; i < cc.size(); i++) cc[i] = (float)(i % 97) * 0.5f;
+    for (size_t i = 0; i < kr.size(); i++) kr[i] = (float)(i % 31) - 15.f;
+    c.Append(1, cc.data(), kr.data(), 2);
+    c.Append(1, cc.data() + 2 * 64, kr.data() + 2 * 16, 1);
+    EXPECT(c.TotalLen(1) == 3 && c.TotalLen(0) == 0, "MLACache len");
+    std::vector<uint16_t> vc, vk;
+    EXPECT(c.View(1, &vc, &vk), "MLACache view");
+    bool same = vc.size() == cc.size() && vk.size() == kr.size();
+    for (size_t i = 0; same && i < cc.size(); i++) same = f32_from_bf16(vc[i]) == cc[i];
+    for (size_t i = 0; same && i < kr.size(); i++) same = f32_from_bf16(vk[i]) == kr[i];
+    EXPECT(same, "MLACache data");
+    c.Reset();
+    EXPECT(c.TotalLen(1) == 0, "MLACache reset");
+  }
+  {  // attention through the mirror: one cached row -> the output is that V row (softmax of one score = 1)
+    relux::KVCache c(dev, 1, 64, 1, 128);
+    std::vector<float> k(128), v(128), q(128, 0.25f), out(128, -1.f);
+    for (int i = 0; i < 128; i++) { k[i] = 0.5f; v[i] = (float)(i % 8); }
+    c.Append(0, k.data(), v.data(), 1);
+    c.Attend(0, q.data(), out.data(), 1, 1, 0.0884f, true);
+    bool same = true;
+    for (int i = 0; i < 128; i++) same = same && std::fabs(out[i] - v[i]) < 1e-3f;
+    EXPECT(same, "Attend single row");
+  }
+  if (failures == 0) printf("ALL PASSED\n");
+  return failures ? 1 : 0;
+}
