@@ -214,7 +214,7 @@ def run_mla(args, w, world, rank, local, dist):
         "gpu_launches": launches, "clocks": clocks,
         "kv_read_gbs_whole_step": alg_bytes * world / (ms_res / args.steps * 1e-3) / 1e9,
     }
-    if rank == 0 and world == 1:
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_mla(w, sample_T=512, threads=1)
     for b in (d_new_c, d_new_r, d_qc, d_qr, d_out, d_wuk, d_wuv):
         b.free()
@@ -382,6 +382,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mla_decode_b64_ctx32k", choices=sorted(WORKLOADS))
+    ap.add_argument("--skip-cpu-baseline", action="store_true", help="profiling runs: leave out the 10-30 s CPU baseline leg")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]

@@ -12,34 +12,51 @@
 
 namespace relux {
 
+// One block of 256 threads: every thread counts the chunks of its sequences, a block-wide exclusive scan gives the
+// offsets, then every thread writes the items of its sequences.
 __global__ void build_worklist_kernel(const int32_t* __restrict__ len, const int32_t* __restrict__ seq_ids, int n_seqs, int extra,
                                       int page_tokens, int chunk_pages, WorkItem* __restrict__ items, int32_t* __restrict__ chunk_off) {
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    for (int i = 0; i < n_seqs; i++) {
-      chunk_off[i] = acc;
-      int seq = seq_ids ? seq_ids[i] : i;
-      int T = len[seq] + extra;
-      int pages = (T + page_tokens - 1) / page_tokens;
-      acc += (pages + chunk_pages - 1) / chunk_pages;
-    }
-    chunk_off[n_seqs] = acc;
-  }
+  __shared__ int32_t s_warp[8];
+  __shared__ int32_t s_base;
+  if (threadIdx.x == 0) s_base = 0;
   __syncthreads();
-  for (int i = threadIdx.x; i < n_seqs; i += blockDim.x) {
-    int seq = seq_ids ? seq_ids[i] : i;
-    int T = len[seq] + extra;
-    int pages = (T + page_tokens - 1) / page_tokens;
-    int c0 = chunk_off[i], nc = chunk_off[i + 1] - c0;
-    for (int c = 0; c < nc; c++) {
-      WorkItem w;
-      w.seq_index = i;
-      w.seq = seq;
-      w.page_begin = c * chunk_pages;
-      w.page_end = min(pages, (c + 1) * chunk_pages);
-      items[c0 + c] = w;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i0 = 0; i0 < n_seqs; i0 += blockDim.x) {
+    const int i = i0 + threadIdx.x;
+    int seq = 0, pages = 0, nc = 0;
+    if (i < n_seqs) {
+      seq = seq_ids ? seq_ids[i] : i;
+      const int T = len[seq] + extra;
+      pages = (T + page_tokens - 1) / page_tokens;
+      nc = (pages + chunk_pages - 1) / chunk_pages;
     }
+    int incl = nc;   // inclusive scan inside the warp
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    int wbase = 0;
+    for (int w = 0; w < warp; w++) wbase += s_warp[w];
+    const int c0 = s_base + wbase + incl - nc;
+    if (i < n_seqs) {
+      chunk_off[i] = c0;
+      for (int c = 0; c < nc; c++) {
+        WorkItem w;
+        w.seq_index = i;
+        w.seq = seq;
+        w.page_begin = c * chunk_pages;
+        w.page_end = min(pages, (c + 1) * chunk_pages);
+        items[c0 + c] = w;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) s_base = c0 + nc;   // running total after this batch of sequences
+    __syncthreads();
   }
+  if (threadIdx.x == 0) chunk_off[n_seqs] = s_base;
 }
 
 // Chooses the chunk length.  CTAs are scheduled in waves over the SMs, so the step time is about
