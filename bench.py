@@ -36,7 +36,7 @@ WORKLOADS = {
 }
 # dram__bytes_read + dram__bytes_write of the dominant kernel divided by its algorithmic bytes, from the ncu captures
 # summarised under profiles/ (small case, traffic grows in proportion to the cached tokens read).
-TRAFFIC_RATIO = {"mla": 1.02, "gqa": None}
+TRAFFIC_RATIO = {"mla": 1.03, "gqa": 1.015}
 PAGE = 64
 
 
@@ -315,7 +315,8 @@ def run_gqa(args, w, world, rank, local, dist):
         "config": {"workload": args.workload, "batch_per_gpu": B, "context": ctx0, "heads": H, "kv_heads": Hkv, "head_dim": D,
                    "draft_tokens": S, "page_tokens": PAGE, "page_table": "random permutation",
                    "l2": "inputs (%.2f GB of K/V per GPU) are larger than L2" % (B * ctx0 * Hkv * D * 4 / 1e9)},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": alg_bytes * TRAFFIC_RATIO["gqa"],
                      "peak_source": peak_src, "kernel": "gqa split-KV decode/verify", "kernel_ms": kernel_ms,
                      "algorithmic_bytes_per_launch": alg_bytes, "frac_of_nominal_8TBs": achieved / 8000.0},
         "e2e": {"value": acc_e2e * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(q.nbytes + nk.nbytes + nv.nbytes),
