@@ -10,6 +10,7 @@
 // This replaces the reference's "decompress every cached latent, then attend" (mla.go:323-377): the cache
 // row (dC + dHR values, shared by all heads) is read once per token instead of being expanded to
 // 2 * H * head_dim values.
+#include <cstdlib>
 #include "common.cuh"
 #include "internal.h"
 #include "splitkv.h"
@@ -18,6 +19,7 @@ namespace relux {
 
 int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const SplitPlan& plan, const uint16_t* q_abs);
 bool mla_sm100_eligible(const Pool* p, const relux_attn_args& a);
+int32_t launch_mla_decode_sm100_t256(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const SplitPlan& plan, const uint16_t* q_abs);
 bool mla_proj_mma_eligible(int Dh, int dC);
 int32_t launch_mla_absorb_mma(Device* dev, const void* q_nope, const void* q_rope, int q_bf16, const uint16_t* W_UK, uint16_t* q_abs,
                               int rows, int H, int dC, int dHR);
@@ -261,8 +263,12 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
     count_launch(p->dev);
   }
   const bool sm100 = mla_sm100_eligible(p, a);
+  // two tensor-core variants: 128-token tiles (default) and 256-token tiles (RELUX_MLA_TILE=256; fewer tensor
+  // cycles per token but too little shared memory left to cover the load latency, measured 12 % slower)
+  const char* tile_env = getenv("RELUX_MLA_TILE");
+  const bool t256 = sm100 && tile_env && atoi(tile_env) == 256;
   SplitPlan plan;
-  rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, sm100 ? 2 * S : std::max(1, rows_total / 16), sm100 ? 2 : 1, sm100 ? 2 : 1, sm100 ? 320 : 0, &plan);
+  rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, sm100 ? 2 * S : std::max(1, rows_total / 16), sm100 ? (t256 ? 4 : 2) : 1, sm100 ? (t256 ? 4 : 2) : 1, sm100 ? 320 : 0, &plan);
   if (rc) return rc;
   rc = grow(p->dev, p->part_o, (size_t)plan.num_items * rows_total * dC * sizeof(float));
   if (rc) return rc;
@@ -272,7 +278,8 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   if (rc) return rc;
   RELUX_CUDA_TRY(cudaEventRecord(p->ev0, st));
   if (sm100) {
-    rc = launch_mla_decode_sm100(p, sb, a, plan, (const uint16_t*)p->q_abs.p);
+    rc = t256 ? launch_mla_decode_sm100_t256(p, sb, a, plan, (const uint16_t*)p->q_abs.p)
+              : launch_mla_decode_sm100(p, sb, a, plan, (const uint16_t*)p->q_abs.p);
     if (rc) return rc;
   } else {
     MlaGenParams k;
