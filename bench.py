@@ -215,7 +215,7 @@ def run_mla(args, w, world, rank, local, dist):
         "kv_read_gbs_whole_step": alg_bytes * world / (ms_res / args.steps * 1e-3) / 1e9,
     }
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline_mla(w, sample_T=512, threads=1)
+        line["cpu_baseline"] = cpu_baseline(w, 1, bounded=True)
     for b in (d_new_c, d_new_r, d_qc, d_qr, d_out, d_wuk, d_wuv):
         b.free()
     pool.destroy()
@@ -323,6 +323,8 @@ def run_gqa(args, w, world, rank, local, dist):
                 "d2h_bytes_per_step": int(q.nbytes)},
         "gpu_launches": launches, "clocks": clocks,
     }
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(w, 1, bounded=True)
     for b in (d_q, d_nk, d_nv, d_out):
         b.free()
     pool.destroy()
@@ -353,6 +355,33 @@ def cpu_baseline_mla(w, sample_T, threads):
                       "decompress-then-attend in float32" % (nb, sample_T, dt, ctx // sample_T, ctx)}
 
 
+def cpu_baseline_gqa(w, sample_T, threads):
+    """Times the oracle's restatement of the reference's GQA verify step (widen the cached bf16 rows to float32,
+    expand the KV heads by copy, attend S draft rows causally; mha.go:292-348) on `threads` host threads, one
+    sequence per thread, at a reduced context, scaled linearly in context length.  tokens/s counts accepted tokens
+    with the bench's acceptance law (uniform on 1..S, mean (S + 1) / 2 per sequence and step)."""
+    from oracle import binding as orc
+    H, Hkv, D, S, ctx = w["H"], w["Hkv"], w["D"], w["S"], w["ctx"]
+    rng = np.random.default_rng(0)
+    nb = threads
+    K = orc.bf16_from_f32(rng.standard_normal((nb, sample_T + S, Hkv, D), dtype=np.float32))
+    V = orc.bf16_from_f32(rng.standard_normal((nb, sample_T + S, Hkv, D), dtype=np.float32))
+    q = rng.standard_normal((nb, S, H, D), dtype=np.float32)
+    t0 = time.time()
+    orc.gqa_attend(K, V, [sample_T + S] * nb, q, float(1.0 / np.sqrt(D)), causal=True, threads=threads, reference_cost=True)
+    dt = time.time() - t0
+    return {"value": nb * (S + 1) / 2.0 / (dt * (ctx / sample_T)), "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": "%d sequence(s) x 1 verify step of %d draft tokens at context %d (%.2f s), time scaled x%d to context %d; "
+                      "reference-style widen + head expansion + attend in float32" % (nb, S, sample_T, dt, ctx // sample_T, ctx)}
+
+
+def cpu_baseline(w, threads, bounded):
+    """The CPU leg of either workload kind; `bounded` picks the sample of the default run (about 10-30 s on one core)."""
+    if w["kind"] == "mla":
+        return cpu_baseline_mla(w, sample_T=512 if bounded else 128, threads=threads)
+    return cpu_baseline_gqa(w, sample_T=w["ctx"], threads=threads)
+
+
 def run_reference(args, w, world, rank):
     """--impl reference: the reference's own CPU algorithm (oracle restatement; the Go sources cannot be built
     here) on all host threads, on the same workload definition."""
@@ -362,14 +391,16 @@ def run_reference(args, w, world, rank):
     threads = orc.num_threads()
     vals = []
     for _ in range(args.warmup + args.steps):
-        vals.append(cpu_baseline_mla(w, sample_T=256, threads=threads))
+        vals.append(cpu_baseline(w, threads, bounded=False))
     vals = vals[args.warmup:]
     v = float(np.mean([x["value"] for x in vals]))
     cb = dict(vals[-1])
     cb["value"] = v
     B = w["B"]
-    return {"impl": "reference", "metric": "mla_decode_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": B * world / v * 1e3, "higher_is_better": True,
+    metric = "mla_decode_tokens_per_s" if w["kind"] == "mla" else "gqa_verify_accepted_tokens_per_s"
+    per_step = B * world if w["kind"] == "mla" else B * world * (w["S"] + 1) / 2.0
+    return {"impl": "reference", "metric": metric, "value": v, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step / v * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": args.workload, "batch_per_gpu": B, "context": w["ctx"]},
             "cpu_baseline": cb, "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
