@@ -49,40 +49,50 @@ def read_peaks():
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples the SM clock and the throttle reasons through NVML (the counters nvidia-smi prints) every few
+    milliseconds while the timed region runs; read-only."""
 
-    def __init__(self, index):
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
+
+    def __init__(self, index, period_s=0.003):
         super().__init__(daemon=True)
         self.index = index
-        self.samples = []
+        self.period_s = period_s
+        self.sm = []
+        self.mask = 0
+        self.max_mhz = None
         self.stop_flag = False
-        self.proc = None
+        self.error = None
 
     def run(self):
-        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            for line in self.proc.stdout:
-                if self.stop_flag:
-                    break
-                parts = [x.strip() for x in line.split(",")]
-                if len(parts) >= 6:
-                    self.samples.append(parts)
-        except Exception:
-            pass
+            import pynvml as nv
+            nv.nvmlInit()
+            # NVML numbers devices like nvidia-smi; honour CUDA_VISIBLE_DEVICES when it is a plain index list
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            ids = [int(x) for x in vis.split(",") if x.strip().isdigit()]
+            h = nv.nvmlDeviceGetHandleByIndex(ids[self.index] if self.index < len(ids) else self.index)
+            self.max_mhz = int(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            while not self.stop_flag:
+                self.sm.append(int(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                self.mask |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
+                time.sleep(self.period_s)
+        except Exception as e:  # no NVML: the line then carries no clock record
+            self.error = repr(e)
+
+    def begin(self):
+        """Drops what was sampled so far (warm-up); call right before the timed region."""
+        self.sm, self.mask = [], 0
 
     def finish(self):
         self.stop_flag = True
-        if self.proc:
-            self.proc.terminate()
-        sm = [int(s[0]) for s in self.samples if s[0].isdigit()]
-        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({names[i] for s in self.samples for i in range(4) if s[2 + i].lower().startswith("active")})
-        return {"sm_mhz": int(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
-                "samples": len(sm)}
+        self.join(timeout=2.0)
+        reasons = sorted(n for n, bit in self.REASONS if self.mask & bit)
+        out = {"sm_mhz": int(np.median(self.sm)) if self.sm else None, "sm_min_mhz": min(self.sm) if self.sm else None,
+               "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(self.sm), "source": "nvml"}
+        if self.error:
+            out["error"] = self.error
+        return out
 
 
 def dist_setup(n_gpus):
@@ -161,12 +171,14 @@ def run_mla(args, w, world, rank, local, dist):
 
     e0, e1 = dev.event(), dev.event()
 
-    def timed(fn, steps, warmup):
+    def timed(fn, steps, warmup, sampler=None):
         for _ in range(warmup):
             fn()
         dev.sync()
         barrier(dist)
         n0 = dev.launch_count()
+        if sampler is not None:
+            sampler.begin()
         e0.record()
         for _ in range(steps):
             fn()
@@ -179,8 +191,8 @@ def run_mla(args, w, world, rank, local, dist):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
-    ms_res, launches = timed(step_resident, args.steps, args.warmup)
+        time.sleep(0.05)
+    ms_res, launches = timed(step_resident, args.steps, args.warmup, sampler if rank == 0 else None)
     clocks = sampler.finish() if rank == 0 else None
     ms_e2e, _ = timed(step_e2e, args.steps, args.warmup)
     # dominant kernel: the split-KV decode kernel, timed alone with CUDA events around its launch
@@ -215,7 +227,7 @@ def run_mla(args, w, world, rank, local, dist):
         "kv_read_gbs_whole_step": alg_bytes * world / (ms_res / args.steps * 1e-3) / 1e9,
     }
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(w, 1, bounded=True)
+        line["cpu_baseline"] = cpu_baseline_bounded(w)
     for b in (d_new_c, d_new_r, d_qc, d_qr, d_out, d_wuk, d_wuv):
         b.free()
     pool.destroy()
@@ -274,13 +286,15 @@ def run_gqa(args, w, world, rank, local, dist):
 
     e0, e1 = dev.event(), dev.event()
 
-    def timed(fn, steps, warmup):
+    def timed(fn, steps, warmup, sampler=None):
         for _ in range(warmup):
             fn()
         dev.sync()
         barrier(dist)
         n0 = dev.launch_count()
         accepted_total[0] = 0
+        if sampler is not None:
+            sampler.begin()
         e0.record()
         for _ in range(steps):
             fn()
@@ -293,8 +307,8 @@ def run_gqa(args, w, world, rank, local, dist):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.3)
-    ms_res, launches, acc_res = timed(step_resident, args.steps, args.warmup)
+        time.sleep(0.05)
+    ms_res, launches, acc_res = timed(step_resident, args.steps, args.warmup, sampler if rank == 0 else None)
     clocks = sampler.finish() if rank == 0 else None
     ms_e2e, _, acc_e2e = timed(step_e2e, args.steps, args.warmup)
     kms, ctx_sum = [], []
@@ -324,7 +338,7 @@ def run_gqa(args, w, world, rank, local, dist):
         "gpu_launches": launches, "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline(w, 1, bounded=True)
+        line["cpu_baseline"] = cpu_baseline_bounded(w)
     for b in (d_q, d_nk, d_nv, d_out):
         b.free()
     pool.destroy()
@@ -332,14 +346,14 @@ def run_gqa(args, w, world, rank, local, dist):
     return line
 
 
-def cpu_baseline_mla(w, sample_T, threads):
+def cpu_baseline_mla(w, sample_T, threads, seqs=None):
     """Times the oracle's restatement of the reference's own path (decompress every latent, then attend;
     mla.go:323-377) on `threads` host threads, one sequence per thread, at a reduced context, and scales the time
     linearly in context length to the workload's (the work is linear in T)."""
     from oracle import binding as orc
     H, Dh, dC, dHR, ctx = w["H"], w["Dh"], w["dC"], w["dHR"], w["ctx"]
     rng = np.random.default_rng(0)
-    nb = threads
+    nb = seqs or threads
     ckv = orc.bf16_from_f32(rng.standard_normal((nb, sample_T, dC), dtype=np.float32))
     kr = orc.bf16_from_f32(rng.standard_normal((nb, sample_T, dHR), dtype=np.float32))
     qc = rng.standard_normal((nb, 1, H, Dh), dtype=np.float32)
@@ -355,7 +369,7 @@ def cpu_baseline_mla(w, sample_T, threads):
                       "decompress-then-attend in float32" % (nb, sample_T, dt, ctx // sample_T, ctx)}
 
 
-def cpu_baseline_gqa(w, sample_T, threads):
+def cpu_baseline_gqa(w, sample_T, threads, seqs=None):
     """Times the oracle's restatement of the reference's GQA verify step (widen the cached bf16 rows to float32,
     expand the KV heads by copy, attend S draft rows causally; mha.go:292-348) on `threads` host threads, one
     sequence per thread, at a reduced context, scaled linearly in context length.  tokens/s counts accepted tokens
@@ -363,7 +377,7 @@ def cpu_baseline_gqa(w, sample_T, threads):
     from oracle import binding as orc
     H, Hkv, D, S, ctx = w["H"], w["Hkv"], w["D"], w["S"], w["ctx"]
     rng = np.random.default_rng(0)
-    nb = threads
+    nb = seqs or threads
     K = orc.bf16_from_f32(rng.standard_normal((nb, sample_T + S, Hkv, D), dtype=np.float32))
     V = orc.bf16_from_f32(rng.standard_normal((nb, sample_T + S, Hkv, D), dtype=np.float32))
     q = rng.standard_normal((nb, S, H, D), dtype=np.float32)
@@ -375,23 +389,36 @@ def cpu_baseline_gqa(w, sample_T, threads):
                       "reference-style widen + head expansion + attend in float32" % (nb, S, sample_T, dt, ctx // sample_T, ctx)}
 
 
-def cpu_baseline(w, threads, bounded):
-    """The CPU leg of either workload kind; `bounded` picks the sample of the default run (about 10-30 s on one core)."""
+def cpu_baseline(w, threads, sample_T, seqs=None):
     if w["kind"] == "mla":
-        return cpu_baseline_mla(w, sample_T=512 if bounded else 128, threads=threads)
-    return cpu_baseline_gqa(w, sample_T=w["ctx"], threads=threads)
+        return cpu_baseline_mla(w, sample_T=sample_T, threads=threads, seqs=seqs)
+    return cpu_baseline_gqa(w, sample_T=sample_T, threads=threads, seqs=seqs)
+
+
+def cpu_baseline_bounded(w):
+    """The cpu_baseline leg of the default run: one host core, a sample of about 10 s."""
+    if w["kind"] == "mla":
+        return cpu_baseline(w, 1, sample_T=512)
+    return cpu_baseline(w, 1, sample_T=w["ctx"], seqs=32)
 
 
 def run_reference(args, w, world, rank):
     """--impl reference: the reference's own CPU algorithm (oracle restatement; the Go sources cannot be built
-    here) on all host threads, on the same workload definition."""
+    here) on all host threads, on the same workload definition.  One step = one sequence per thread at a sample
+    context chosen from a short calibration run so that warm-up + steps take about 100 s in total."""
     from oracle import binding as orc
     if rank != 0:
         return None
     threads = orc.num_threads()
+    t0 = time.time()
+    cpu_baseline(w, threads, sample_T=16)
+    per_token = max(1e-6, (time.time() - t0) / 16)
+    budget = 100.0 / max(1, args.warmup + args.steps)
+    cap = 512 if w["kind"] == "mla" else w["ctx"]
+    sample_T = int(min(w["ctx"], cap, max(16, budget / per_token)) // 8 * 8)
     vals = []
     for _ in range(args.warmup + args.steps):
-        vals.append(cpu_baseline(w, threads, bounded=False))
+        vals.append(cpu_baseline(w, threads, sample_T=sample_T))
     vals = vals[args.warmup:]
     v = float(np.mean([x["value"] for x in vals]))
     cb = dict(vals[-1])
@@ -410,8 +437,8 @@ def run_reference(args, w, world, rank):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="mla_decode_b64_ctx32k", choices=sorted(WORKLOADS))
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="profiling runs: leave out the 10-30 s CPU baseline leg")

@@ -19,6 +19,7 @@ namespace relux {
 
 int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const SplitPlan& plan, const uint16_t* q_abs);
 bool mla_sm100_eligible(const Pool* p, const relux_attn_args& a);
+int mla_sm100_workers(Pool* p, int q_tokens);
 int32_t launch_mla_decode_sm100_t256(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const SplitPlan& plan, const uint16_t* q_abs);
 bool mla_proj_mma_eligible(int Dh, int dC);
 int32_t launch_mla_absorb_mma(Device* dev, const void* q_nope, const void* q_rope, int q_bf16, const uint16_t* W_UK, uint16_t* q_abs,
@@ -268,7 +269,10 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   const char* tile_env = getenv("RELUX_MLA_TILE");
   const bool t256 = sm100 && tile_env && atoi(tile_env) == 256;
   SplitPlan plan;
-  rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, sm100 ? 2 * S : std::max(1, rows_total / 16), sm100 ? (t256 ? 4 : 2) : 1, sm100 ? (t256 ? 4 : 2) : 1, sm100 ? 320 : 0, &plan);
+  if (sm100 && !t256)   // persistent CTA pairs over a stream partition; ranges are whole 128-token tiles
+    rc = plan_stream(p, sb, a.layer, a.extra_tokens, mla_sm100_workers(p, S), 2, &plan);
+  else
+    rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, t256 ? 2 * S : std::max(1, rows_total / 16), t256 ? 4 : 1, t256 ? 4 : 1, t256 ? 320 : 0, &plan);
   if (rc) return rc;
   rc = grow(p->dev, p->part_o, (size_t)plan.num_items * rows_total * dC * sizeof(float));
   if (rc) return rc;

@@ -118,6 +118,111 @@ int32_t plan_splitkv(Pool* p, const SeqBatch& sb, int layer, int extra, int ctas
   return RELUX_OK;
 }
 
+// Exclusive prefix sum over the block (blockDim.x = 256); *total receives the block's sum.
+__device__ __forceinline__ int block_excl_scan(int v, int32_t* s_warp, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  __syncthreads();   // s_warp may still be read from the previous call
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  int base = 0, sum = 0;
+  for (int w = 0; w < 8; w++) {
+    if (w < warp) base += s_warp[w];
+    sum += s_warp[w];
+  }
+  *total = sum;
+  return base + incl - v;
+}
+
+// Stream partition (see plan_stream): sequence i occupies pages [start_i, start_i + pages_i) of the stream and
+// is cut at every multiple of G; items are numbered in stream order, so the items of a sequence and the items of
+// a worker are both contiguous.
+__global__ void build_stream_kernel(const int32_t* __restrict__ len, const int32_t* __restrict__ seq_ids, int n_seqs, int extra,
+                                    int page_tokens, int G, int workers, StreamItem* __restrict__ items, int32_t* __restrict__ chunk_off,
+                                    int32_t* __restrict__ worker_first) {
+  __shared__ int32_t s_warp[8];
+  int page_base = 0, item_base = 0;
+  for (int i0 = 0; i0 < n_seqs; i0 += blockDim.x) {
+    const int i = i0 + threadIdx.x;
+    int seq = 0, pages = 0, tokens = 0;
+    if (i < n_seqs) {
+      seq = seq_ids ? seq_ids[i] : i;
+      tokens = len[seq] + extra;
+      pages = (tokens + page_tokens - 1) / page_tokens;
+    }
+    int tot_pages, tot_items;
+    const int start = page_base + block_excl_scan(pages, s_warp, &tot_pages);
+    const int w0 = start / G;
+    const int nc = pages > 0 ? (start + pages - 1) / G - w0 + 1 : 0;
+    const int c0 = item_base + block_excl_scan(nc, s_warp, &tot_items);
+    if (i < n_seqs) {
+      chunk_off[i] = c0;
+      for (int c = 0; c < nc; c++) {
+        const int lo = max(start, (w0 + c) * G), hi = min(start + pages, (w0 + c + 1) * G);
+        StreamItem w;
+        w.seq_index = i;
+        w.seq = seq;
+        w.page_begin = lo - start;
+        w.page_end = hi - start;
+        w.tokens = tokens;
+        w.pad[0] = w.pad[1] = w.pad[2] = 0;
+        items[c0 + c] = w;
+        if (lo == (w0 + c) * G) worker_first[w0 + c] = c0 + c;   // the item that holds the first page of a range
+      }
+    }
+    page_base += tot_pages;
+    item_base += tot_items;
+  }
+  if (threadIdx.x == 0) chunk_off[n_seqs] = item_base;
+  // ranges past the end of the stream are empty
+  for (int w = (page_base + G - 1) / G + threadIdx.x; w <= workers; w += blockDim.x) worker_first[w] = item_base;
+}
+
+int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int workers, int page_multiple, SplitPlan* plan) {
+  const relux_pool_params& prm = p->prm;
+  long total = 0;
+  std::vector<int> pages(sb.n_seqs);
+  for (int i = 0; i < sb.n_seqs; i++) {
+    const int T = p->h_len[(size_t)layer * prm.max_seqs + sb.seq[i]] + extra;
+    pages[i] = (T + prm.page_tokens - 1) / prm.page_tokens;
+    total += pages[i];
+  }
+  workers = std::max(1, workers);
+  const int mult = std::max(1, page_multiple);
+  long G = (total + workers - 1) / workers;
+  G = std::max<long>((G + mult - 1) / mult * mult, 2L * mult);   // at least two tiles per range
+  if (const char* ov = getenv("RELUX_CHUNK_PAGES")) G = std::max<long>(mult, (atol(ov) + mult - 1) / mult * mult);   // tuning aid
+  workers = (int)std::max<long>(1, (total + G - 1) / G);
+  int items = 0;
+  long start = 0;
+  for (int i = 0; i < sb.n_seqs; i++) {
+    if (pages[i] > 0) items += (int)((start + pages[i] - 1) / G - start / G + 1);
+    start += pages[i];
+  }
+  plan->chunk_pages = (int)G;
+  plan->num_items = items;
+  plan->num_workers = workers;
+  const size_t off_chunk = sizeof(StreamItem) * (size_t)items;
+  const size_t off_worker = (off_chunk + sizeof(int32_t) * ((size_t)sb.n_seqs + 1) + 15) & ~(size_t)15;
+  int32_t rc = grow(p->dev, p->work, off_worker + sizeof(int32_t) * ((size_t)workers + 1) + 64);
+  if (rc) return rc;
+  plan->items = nullptr;
+  plan->stream_items = (StreamItem*)p->work.p;
+  plan->chunk_off = (int32_t*)((char*)p->work.p + off_chunk);
+  plan->worker_first = (int32_t*)((char*)p->work.p + off_worker);
+  const int32_t* len = p->d_len + (size_t)layer * prm.max_seqs;
+  build_stream_kernel<<<1, 256, 0, p->dev->stream>>>(len, sb.d_seq_ids, sb.n_seqs, extra, prm.page_tokens, (int)G, workers,
+                                                     plan->stream_items, plan->chunk_off, plan->worker_first);
+  RELUX_CUDA_TRY(cudaGetLastError());
+  count_launch(p->dev);
+  return RELUX_OK;
+}
+
 // Combines the partial results of every chunk of a sequence:
 //   M = max_c m_c,  L = sum_c l_c 2^(m_c - M),  O = sum_c O_c 2^(m_c - M) / L
 // part_o [item][rows][width] f32 holds UNNORMALISED accumulators, part_ml [item][rows][2] = (m, l) with m in

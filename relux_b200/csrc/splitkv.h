@@ -12,17 +12,36 @@ struct WorkItem {
   int32_t page_end;    // one past the last logical page
 };
 
+// Item of a stream plan (plan_stream): like WorkItem plus the sequence's token count, so that a persistent kernel
+// needs a single load per item.
+struct __align__(16) StreamItem {
+  int32_t seq_index;
+  int32_t seq;
+  int32_t page_begin;
+  int32_t page_end;
+  int32_t tokens;      // cached length of the sequence + the call's extra tokens
+  int32_t pad[3];
+};
+
 struct SplitPlan {
   int chunk_pages = 0;
   int num_items = 0;
   WorkItem* items = nullptr;    // device
   int32_t* chunk_off = nullptr; // device [n_seqs + 1]
+  // stream plans only (plan_stream): worker w owns items [worker_first[w], worker_first[w + 1])
+  int num_workers = 0;
+  StreamItem* stream_items = nullptr;  // device [num_items]
+  int32_t* worker_first = nullptr;     // device [num_workers + 1]
 };
 
 struct Pool;
 struct SeqBatch;
 int32_t plan_splitkv(Pool* p, const SeqBatch& sb, int layer, int extra, int ctas_per_item, int min_chunk_pages, int chunk_multiple,
                      int max_chunk_pages, SplitPlan* plan);
+// Stream partition for persistent kernels: the pages of all sequences of the call, laid end to end, are cut into
+// `workers` equal ranges of `chunk_pages` pages (a multiple of `page_multiple`); one item = the part of one sequence
+// inside one range, so a worker meets an item boundary only where a sequence ends inside its range.
+int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int workers, int page_multiple, SplitPlan* plan);
 int32_t launch_build_worklist_raw(cudaStream_t st, const int32_t* len, const int32_t* seq_ids, int n_seqs, int extra, int page_tokens,
                                   int chunk_pages, WorkItem* items, int32_t* chunk_off);
 int32_t launch_merge_raw(cudaStream_t st, const float* part_o, const float* part_ml, const int32_t* chunk_off, int n_seqs, int rows,
