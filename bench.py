@@ -49,12 +49,13 @@ def read_peaks():
 
 
 class ClockSampler(threading.Thread):
-    """Samples the SM clock and the throttle reasons through NVML (the counters nvidia-smi prints) every few
-    milliseconds while the timed region runs; read-only."""
+    """Samples the SM clock and the throttle reasons through NVML (the counters nvidia-smi prints) every 25 ms
+    while the timed region runs; read-only.  (Sampling every few milliseconds slowed the kernel launches of the
+    timed loop down: NVML queries and launches share driver locks.)"""
 
     REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
 
-    def __init__(self, index, period_s=0.003):
+    def __init__(self, index, period_s=0.025):
         super().__init__(daemon=True)
         self.index = index
         self.period_s = period_s
@@ -129,7 +130,7 @@ def run_mla(args, w, world, rank, local, dist):
     from oracle import binding as orc  # used only for the bf16 rounding helper of inputs and the CPU baseline leg
 
     B, ctx0, H, Dh, dC, dHR = w["B"], w["ctx"], w["H"], w["Dh"], w["dC"], w["dHR"]
-    total_steps = 2 * (args.steps + args.warmup) + args.steps + 8
+    total_steps = 2 * (args.steps + args.warmup) + 8
     pages_per = (ctx0 + total_steps + PAGE - 1) // PAGE + 1
     dev = rb.Device(local)
     rng = np.random.default_rng(7 + rank)
@@ -194,18 +195,19 @@ def run_mla(args, w, world, rank, local, dist):
         time.sleep(0.05)
     ms_res, launches = timed(step_resident, args.steps, args.warmup, sampler if rank == 0 else None)
     clocks = sampler.finish() if rank == 0 else None
+    # dominant kernel: the decode kernel; every call records a CUDA event pair around that launch on the launching
+    # stream, read here for the calls of the timed region (the library keeps the last 256)
+    kernel_ms, counted = pool.mean_kernel_ms(args.steps)
+    len_end = pool.seq_len(0, 0)                                  # every sequence has the same length
+    rows_mean = B * (len_end - (counted - 1) / 2.0)               # cached rows read per launch, mean over those calls
     ms_e2e, _ = timed(step_e2e, args.steps, args.warmup)
-    # dominant kernel: the split-KV decode kernel, timed alone with CUDA events around its launch
-    kms, ctx_sum = [], []
-    for _ in range(args.steps):
-        step_resident()
-        kms.append(pool.last_kernel_ms())
-        ctx_sum.append(sum(pool.seq_len(0, b) for b in range(B)))
     assert pool.status() == 0, "device status word is set"
-    kernel_ms = float(np.mean(kms))
-    alg_bytes = float(np.mean(ctx_sum)) * (dC + dHR) * 2
+    alg_bytes = rows_mean * (dC + dHR) * 2
+    alg_flops = 2.0 * H * rows_mean * ((dC + dHR) + dC)
     peak, peak_src = read_peaks()
+    pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if peak_src == "measured" else {}
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+    tflops = alg_flops / (kernel_ms * 1e-3) / 1e12
     tokens = B * world
     value = tokens * args.steps / (ms_res * 1e-3)
     e2e = tokens * args.steps / (ms_e2e * 1e-3)
@@ -220,8 +222,13 @@ def run_mla(args, w, world, rank, local, dist):
                    % (B * ctx0 * (dC + dHR) * 2 / 1e9)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": (alg_bytes * TRAFFIC_RATIO["mla"]) if TRAFFIC_RATIO["mla"] else None,
-                     "peak_source": peak_src, "kernel": "mla split-KV decode", "kernel_ms": kernel_ms,
-                     "algorithmic_bytes_per_launch": alg_bytes, "frac_of_nominal_8TBs": achieved / 8000.0},
+                     "peak_source": peak_src, "kernel": "mla_decode_sm100_kernel", "kernel_ms": kernel_ms, "launches_timed": counted,
+                     "algorithmic_bytes_per_launch": alg_bytes, "frac_of_nominal_8TBs": achieved / 8000.0,
+                     # the same kernel against the tensor roofline (128 heads put it at the ridge point)
+                     "tensor": {"achieved": tflops, "unit": "TFLOP/s", "algorithmic_flops_per_launch": alg_flops,
+                                "peak_burst": pk.get("bf16_tflops", 1590.0), "peak_sustained": pk.get("bf16_tflops_sustained", 1400.0),
+                                "frac_of_burst": tflops / pk.get("bf16_tflops", 1590.0),
+                                "frac_of_sustained": tflops / pk.get("bf16_tflops_sustained", 1400.0)}},
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches, "clocks": clocks,
         "kv_read_gbs_whole_step": alg_bytes * world / (ms_res / args.steps * 1e-3) / 1e9,
@@ -243,7 +250,7 @@ def run_gqa(args, w, world, rank, local, dist):
     from oracle import binding as orc
 
     B, ctx0, H, Hkv, D, S = w["B"], w["ctx"], w["H"], w["Hkv"], w["D"], w["S"]
-    total_steps = 3 * (args.steps + args.warmup) + 8
+    total_steps = 2 * (args.steps + args.warmup) + 8
     pages_per = (ctx0 + total_steps * S + S + PAGE - 1) // PAGE + 1
     dev = rb.Device(local)
     rng = np.random.default_rng(3 + rank)
@@ -276,7 +283,10 @@ def run_gqa(args, w, world, rank, local, dist):
         accepted_total[0] += int(acc.sum())
         pool.set_len(0, lens.astype(np.int32))
 
+    rows_read = []
+
     def step_resident():
+        rows_read.append(float(lens.sum()) + B * S)   # committed rows + the S draft rows of every sequence
         pool.verify(0, B, d_q, d_out, d_nk, d_nv, H, D, scale, S)
         commit()
 
@@ -310,15 +320,11 @@ def run_gqa(args, w, world, rank, local, dist):
         time.sleep(0.05)
     ms_res, launches, acc_res = timed(step_resident, args.steps, args.warmup, sampler if rank == 0 else None)
     clocks = sampler.finish() if rank == 0 else None
+    # dominant kernel: event pairs recorded by the calls of the timed region themselves (the library keeps the last 256)
+    kernel_ms, counted = pool.mean_kernel_ms(args.steps)
+    alg_bytes = float(np.mean(rows_read[-counted:])) * Hkv * D * 2 * 2
     ms_e2e, _, acc_e2e = timed(step_e2e, args.steps, args.warmup)
-    kms, ctx_sum = [], []
-    for _ in range(args.steps):
-        step_resident()
-        kms.append(pool.last_kernel_ms())
-        ctx_sum.append(float(lens.sum()))   # rows read by that call: committed length before the commit + S draft rows ~ lens
     assert pool.status() == 0, "device status word is set"
-    kernel_ms = float(np.mean(kms))
-    alg_bytes = float(np.mean(ctx_sum)) * Hkv * D * 2 * 2
     peak, peak_src = read_peaks()
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
     acc_res_all = acc_res * world   # every rank draws from its own seeded stream with the same distribution
@@ -331,7 +337,7 @@ def run_gqa(args, w, world, rank, local, dist):
                    "l2": "inputs (%.2f GB of K/V per GPU) are larger than L2" % (B * ctx0 * Hkv * D * 4 / 1e9)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": alg_bytes * TRAFFIC_RATIO["gqa"],
-                     "peak_source": peak_src, "kernel": "gqa split-KV decode/verify", "kernel_ms": kernel_ms,
+                     "peak_source": peak_src, "kernel": "gqa_decode_kernel", "kernel_ms": kernel_ms, "launches_timed": counted,
                      "algorithmic_bytes_per_launch": alg_bytes, "frac_of_nominal_8TBs": achieved / 8000.0},
         "e2e": {"value": acc_e2e * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(q.nbytes + nk.nbytes + nv.nbytes),
                 "d2h_bytes_per_step": int(q.nbytes)},

@@ -244,6 +244,12 @@ int32_t relux_gqa_decode_noalloc(relux_pool_t pool, const relux_attn_args* args)
  * pool, measured with CUDA events around that one launch.  Synchronises the stream. */
 int32_t relux_pool_last_kernel_ms(relux_pool_t pool, float* ms);
 
+/* Mean device time of that kernel over the most recent `last_n` decode / verify calls on this pool (at most
+ * 256 are kept); `counted` receives how many calls went into the mean.  The event pairs are recorded by the
+ * calls themselves, so reading them after a timed loop does not disturb the loop.  Synchronises the stream.
+ * Measurement aid: no counterpart in the reference. */
+int32_t relux_pool_kernel_ms_mean(relux_pool_t pool, int32_t last_n, float* mean_ms, int32_t* counted);
+
 #ifdef __cplusplus
 }
 #endif

@@ -193,11 +193,11 @@ int32_t launch_attn_reference_gqa(Pool* p, const SeqBatch& sb, const relux_attn_
   const uint16_t* vb = kb + p->page_elems * p->prm.num_pages;
   if (smem > 48 * 1024) RELUX_CUDA_TRY(cudaFuncSetAttribute(gqa_reference_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(a.num_heads, sb.n_seqs);
-  RELUX_CUDA_TRY(cudaEventRecord(p->ev0, p->dev->stream));
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), p->dev->stream));
   gqa_reference_kernel<<<grid, 128, smem, p->dev->stream>>>(g, kb, vb, d_q, d_out, p->prm.gqa_num_kv_heads, p->prm.gqa_head_dim);
   RELUX_CUDA_TRY(cudaGetLastError());
-  RELUX_CUDA_TRY(cudaEventRecord(p->ev1, p->dev->stream));
-  p->timed = true;
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), p->dev->stream));
+  p->timed_calls++;
   count_launch(p->dev);
   return RELUX_OK;
 }
@@ -211,12 +211,12 @@ int32_t launch_attn_reference_mla(Pool* p, const SeqBatch& sb, const relux_attn_
   const uint16_t* base = p->storage + (size_t)a.layer * p->layer_elems;
   if (smem > 48 * 1024) RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_reference_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(a.num_heads, sb.n_seqs);
-  RELUX_CUDA_TRY(cudaEventRecord(p->ev0, p->dev->stream));
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), p->dev->stream));
   mla_reference_kernel<<<grid, 128, smem, p->dev->stream>>>(g, base, d_q, d_qr, (const uint16_t*)a.w_uk, (const uint16_t*)a.w_uv, d_out,
                                                             a.head_dim, p->prm.mla_dc, p->prm.mla_dhr);
   RELUX_CUDA_TRY(cudaGetLastError());
-  RELUX_CUDA_TRY(cudaEventRecord(p->ev1, p->dev->stream));
-  p->timed = true;
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), p->dev->stream));
+  p->timed_calls++;
   count_launch(p->dev);
   return RELUX_OK;
 }

@@ -335,7 +335,7 @@ int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   k.status = p->d_status;
   dim3 grid(plan.num_items, prm.gqa_num_kv_heads);
   cudaStream_t st = p->dev->stream;
-  RELUX_CUDA_TRY(cudaEventRecord(p->ev0, st));
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), st));
   if (R <= 16) {
     constexpr size_t smem = gqa_smem_bytes<1>();
     RELUX_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -346,8 +346,8 @@ int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
     gqa_decode_kernel<2><<<grid, 160, smem, st>>>(p->tmap_gqa, k);
   }
   RELUX_CUDA_TRY(cudaGetLastError());
-  RELUX_CUDA_TRY(cudaEventRecord(p->ev1, st));
-  p->timed = true;
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), st));
+  p->timed_calls++;
   count_launch(p->dev);
   return launch_merge(p, plan, sb.n_seqs, rows_total, kD, (float*)d_out, nullptr);
 }

@@ -81,9 +81,13 @@ struct Pool {
   CUtensorMap tmap_gqa{};   // 2-D [rows][D],      box 64 x 64, 128-byte swizzle
   bool has_tmap = false;
   bool mla_blocked = false;   // MLA pages stored as 64-column blocks (see mla_page_off)
-  // timing of the dominant kernel
-  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-  bool timed = false;
+  // timing of the dominant kernel: a ring of event pairs, one pair per attention call, so that a caller can read
+  // the device times of its last kTimeRing calls after the fact without a synchronisation between them
+  static constexpr int kTimeRing = 256;
+  cudaEvent_t ev_ring[kTimeRing][2] = {};
+  uint64_t timed_calls = 0;
+  cudaEvent_t ev_begin() const { return ev_ring[timed_calls % kTimeRing][0]; }
+  cudaEvent_t ev_end() const { return ev_ring[timed_calls % kTimeRing][1]; }
 };
 
 inline Device* as_device(relux_device_t h) {

@@ -280,7 +280,7 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   if (rc) return rc;
   rc = grow(p->dev, p->o_lat, (size_t)rows * H * dC * sizeof(float));
   if (rc) return rc;
-  RELUX_CUDA_TRY(cudaEventRecord(p->ev0, st));
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), st));
   if (sm100) {
     rc = t256 ? launch_mla_decode_sm100_t256(p, sb, a, plan, (const uint16_t*)p->q_abs.p)
               : launch_mla_decode_sm100(p, sb, a, plan, (const uint16_t*)p->q_abs.p);
@@ -314,8 +314,8 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
     }
     if (rc) return rc;
   }
-  RELUX_CUDA_TRY(cudaEventRecord(p->ev1, st));
-  p->timed = true;
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), st));
+  p->timed_calls++;
   count_launch(p->dev);
   if (proj_mma) {
     // merged latent output goes to the up-projection as bf16 (tensor-core operand)

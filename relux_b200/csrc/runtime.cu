@@ -153,8 +153,9 @@ static void pool_free_all(Pool* p) {
   fr(p->o_lat.p); fr(p->q_conv.p);
   if (p->h_stage) cudaFreeHost(p->h_stage);
   if (p->stage_ev) cudaEventDestroy(p->stage_ev);
-  if (p->ev0) cudaEventDestroy(p->ev0);
-  if (p->ev1) cudaEventDestroy(p->ev1);
+  for (auto& pair : p->ev_ring)
+    for (cudaEvent_t ev : pair)
+      if (ev) cudaEventDestroy(ev);
   p->magic = 0;
   delete p;
 }
@@ -583,8 +584,9 @@ API int32_t relux_pool_create(relux_device_t h, const relux_pool_params* prm, re
   A((void**)&p->d_row_off, ((size_t)prm->max_seqs + 1) * 4);
   if (e == cudaSuccess) e = cudaMallocHost((void**)&p->h_stage, (2 * (size_t)prm->max_seqs + 1) * 4);
   if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->stage_ev, cudaEventDisableTiming);
-  if (e == cudaSuccess) e = cudaEventCreate(&p->ev0);
-  if (e == cudaSuccess) e = cudaEventCreate(&p->ev1);
+  for (auto& pair : p->ev_ring)
+    for (cudaEvent_t& ev : pair)
+      if (e == cudaSuccess) e = cudaEventCreate(&ev);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_table, 0xFF, table_n * 4, dev->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_len, 0, len_n * 4, dev->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_status, 0, 4, dev->stream);
@@ -821,8 +823,27 @@ API int32_t relux_mla_verify(relux_pool_t h, const relux_attn_args* attn, const 
 API int32_t relux_pool_last_kernel_ms(relux_pool_t h, float* ms) {
   GET_POOL(h);
   if (!ms) return RELUX_ERR_INVALID_ARG;
-  if (!p->timed) { set_error("no attention kernel has been timed on this pool yet"); return RELUX_ERR_INVALID_ARG; }
-  RELUX_CUDA_TRY(cudaEventSynchronize(p->ev1));
-  RELUX_CUDA_TRY(cudaEventElapsedTime(ms, p->ev0, p->ev1));
+  if (!p->timed_calls) { set_error("no attention kernel has been timed on this pool yet"); return RELUX_ERR_INVALID_ARG; }
+  const auto& pair = p->ev_ring[(p->timed_calls - 1) % Pool::kTimeRing];
+  RELUX_CUDA_TRY(cudaEventSynchronize(pair[1]));
+  RELUX_CUDA_TRY(cudaEventElapsedTime(ms, pair[0], pair[1]));
+  return RELUX_OK;
+}
+
+API int32_t relux_pool_kernel_ms_mean(relux_pool_t h, int32_t last_n, float* mean_ms, int32_t* counted) {
+  GET_POOL(h);
+  if (!mean_ms || last_n <= 0) return RELUX_ERR_INVALID_ARG;
+  if (!p->timed_calls) { set_error("no attention kernel has been timed on this pool yet"); return RELUX_ERR_INVALID_ARG; }
+  const uint64_t n = std::min<uint64_t>(std::min<uint64_t>((uint64_t)last_n, p->timed_calls), Pool::kTimeRing);
+  double sum = 0.0;
+  for (uint64_t i = 0; i < n; i++) {
+    const auto& pair = p->ev_ring[(p->timed_calls - 1 - i) % Pool::kTimeRing];
+    float ms = 0.f;
+    RELUX_CUDA_TRY(cudaEventSynchronize(pair[1]));
+    RELUX_CUDA_TRY(cudaEventElapsedTime(&ms, pair[0], pair[1]));
+    sum += ms;
+  }
+  *mean_ms = (float)(sum / (double)n);
+  if (counted) *counted = (int32_t)n;
   return RELUX_OK;
 }
