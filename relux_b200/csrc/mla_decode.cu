@@ -25,6 +25,8 @@ bool mla_proj_mma_eligible(int Dh, int dC);
 int32_t launch_mla_absorb_mma(Device* dev, const void* q_nope, const void* q_rope, int q_bf16, const uint16_t* W_UK, uint16_t* q_abs,
                               int rows, int H, int dC, int dHR);
 int32_t launch_mla_vup_mma(Device* dev, const uint16_t* o_lat, const uint16_t* W_UV, float* out, int rows, int H, int dC);
+int32_t launch_mla_merge_vup_mma(Device* dev, const float* part_o, const float* part_ml, const int32_t* chunk_off, const uint16_t* W_UV,
+                                 float* out, int rows, int S, int H, int dC);
 
 namespace {
 
@@ -317,7 +319,12 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), st));
   p->timed_calls++;
   count_launch(p->dev);
-  if (proj_mma) {
+  if (proj_mma && dC <= 512 && !getenv("RELUX_MLA_UNFUSED_MERGE")) {
+    // split-KV merge fused into the up-projection: the merged latent output never touches HBM
+    rc = launch_mla_merge_vup_mma(p->dev, (const float*)p->part_o.p, (const float*)p->part_ml.p, plan.chunk_off, (const uint16_t*)a.w_uv,
+                                  (float*)d_out, rows, S, H, dC);
+    if (rc) return rc;
+  } else if (proj_mma) {
     // merged latent output goes to the up-projection as bf16 (tensor-core operand)
     rc = launch_merge(p, plan, sb.n_seqs, rows_total, dC, nullptr, (uint16_t*)p->o_lat.p);
     if (rc) return rc;

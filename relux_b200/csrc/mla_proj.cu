@@ -5,7 +5,8 @@
 //   up-proj: out[row][h][:]    = O_lat[row][h][:] . W_UV[:, h*Dh:(h+1)*Dh]          M = rows, N = Dh,  K = dC
 // Both are about 1 GFLOP per step at batch 64 (1.5 % of the decode's work) and move ~30 MB; they are written to stay
 // out of the way of the decode kernel, not to chase the tensor peak: one CTA per (head, 128-wide slice, 64 rows),
-// operands staged in padded shared memory, fragments through ldmatrix.
+// operands staged in padded shared memory (cp.async, every load of a CTA in flight at once), fragments through
+// ldmatrix.  The up-projection also performs the split-KV merge while it builds its A operand.
 // Shapes: Dh = 128, dC a multiple of 128.  Other shapes use the scalar kernels in mla_decode.cu.
 #include "common.cuh"
 #include "internal.h"
@@ -49,7 +50,15 @@ __device__ __forceinline__ void tile_mma_64x128x128(const uint16_t* As, const ui
   }
 }
 
-// grid (H, dC/128, ceil(rows/64)), 128 threads.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// grid (H, dC/128, ceil(rows/64)), 128 threads.  Every load of the CTA is in flight at once (cp.async for bf16
+// sources), the result leaves through shared memory as 16-byte row-contiguous stores.
 __global__ void __launch_bounds__(128) mla_absorb_mma_kernel(const void* __restrict__ q_nope, const void* __restrict__ q_rope, int q_bf16,
                                                              const uint16_t* __restrict__ W_UK, uint16_t* __restrict__ q_abs, int rows,
                                                              int H, int dC, int dHR) {
@@ -58,26 +67,48 @@ __global__ void __launch_bounds__(128) mla_absorb_mma_kernel(const void* __restr
   uint16_t* Bs = sm + 64 * kStride;   // [128][kStride]   rows = latent index c, cols = d
   const int h = blockIdx.x, c0 = blockIdx.y * 128, r0 = blockIdx.z * 64;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll 4
+  for (int e = threadIdx.x; e < 128 * (kDh / 8); e += blockDim.x) {
+    const int c = e / (kDh / 8), v = e % (kDh / 8);
+    cp_async16(Bs + c * kStride + v * 8, W_UK + (size_t)(c0 + c) * H * kDh + (size_t)h * kDh + (size_t)v * 8);
+  }
   // A: 64 rows x 128 d, 8 elements per thread per step
+#pragma unroll 4
   for (int e = threadIdx.x; e < 64 * (kDh / 8); e += blockDim.x) {
     const int r = e / (kDh / 8), v = e % (kDh / 8);
-    uint4 w = make_uint4(0, 0, 0, 0);
-    if (r0 + r < rows) {
-      const size_t off = ((size_t)(r0 + r) * H + h) * kDh + (size_t)v * 8;
-      if (q_bf16) w = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(q_nope) + off);
+    uint16_t* dst = As + r * kStride + v * 8;
+    if (r0 + r >= rows) {
+      *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    const size_t off = ((size_t)(r0 + r) * H + h) * kDh + (size_t)v * 8;
+    if (q_bf16) {
+      cp_async16(dst, reinterpret_cast<const uint16_t*>(q_nope) + off);
+    } else {
+      const float4* s = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(q_nope) + off);
+      const float4 x = s[0], y = s[1];
+      *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16x2(x.x, x.y), pack_bf16x2(x.z, x.w), pack_bf16x2(y.x, y.y), pack_bf16x2(y.z, y.w));
+    }
+  }
+  cp_async_commit();
+  const int roww = dC + dHR;
+  if (blockIdx.y == 0) {   // the rope part of q~ is a copy (with the same rounding when the source is float32)
+    const int vecs = dHR / 8;
+    for (int e = threadIdx.x; e < 64 * vecs; e += blockDim.x) {
+      const int r = e / vecs, v = e % vecs;
+      if (r0 + r >= rows) continue;
+      const size_t off = ((size_t)(r0 + r) * H + h) * dHR + (size_t)v * 8;
+      uint4 w;
+      if (q_bf16) w = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(q_rope) + off);
       else {
-        const float4* s = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(q_nope) + off);
+        const float4* s = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(q_rope) + off);
         const float4 x = s[0], y = s[1];
         w = make_uint4(pack_bf16x2(x.x, x.y), pack_bf16x2(x.z, x.w), pack_bf16x2(y.x, y.y), pack_bf16x2(y.z, y.w));
       }
+      *reinterpret_cast<uint4*>(q_abs + ((size_t)(r0 + r) * H + h) * roww + dC + (size_t)v * 8) = w;
     }
-    *reinterpret_cast<uint4*>(As + r * kStride + v * 8) = w;
   }
-  for (int e = threadIdx.x; e < 128 * (kDh / 8); e += blockDim.x) {
-    const int c = e / (kDh / 8), v = e % (kDh / 8);
-    const uint4 w = *reinterpret_cast<const uint4*>(W_UK + (size_t)(c0 + c) * H * kDh + (size_t)h * kDh + (size_t)v * 8);
-    *reinterpret_cast<uint4*>(Bs + c * kStride + v * 8) = w;
-  }
+  cp_async_wait<0>();
   __syncthreads();
   float acc[16][4];
 #pragma unroll
@@ -85,24 +116,20 @@ __global__ void __launch_bounds__(128) mla_absorb_mma_kernel(const void* __restr
 #pragma unroll
     for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
   tile_mma_64x128x128<false>(As, Bs, acc, warp, lane);
-  const int roww = dC + dHR;
+  __syncthreads();   // every warp is done with As / Bs: Bs becomes the 64 x 128 output staging tile
+  uint16_t* Os = Bs;
 #pragma unroll
   for (int hf = 0; hf < 2; hf++) {
-    const int r = r0 + warp * 16 + hf * 8 + (lane >> 2);
-    if (r >= rows) continue;
-    uint16_t* dst = q_abs + ((size_t)r * H + h) * roww + c0;
+    const int r = warp * 16 + hf * 8 + (lane >> 2);
 #pragma unroll
     for (int nt = 0; nt < 16; nt++)
-      *reinterpret_cast<uint32_t*>(dst + nt * 8 + 2 * (lane & 3)) = pack_bf16x2(acc[nt][hf * 2], acc[nt][hf * 2 + 1]);
+      *reinterpret_cast<uint32_t*>(Os + r * kStride + nt * 8 + 2 * (lane & 3)) = pack_bf16x2(acc[nt][hf * 2], acc[nt][hf * 2 + 1]);
   }
-  if (blockIdx.y == 0) {
-    for (int e = threadIdx.x; e < 64 * dHR; e += blockDim.x) {
-      const int r = e / dHR, d = e % dHR;
-      if (r0 + r >= rows) continue;
-      const size_t off = ((size_t)(r0 + r) * H + h) * dHR + d;
-      const uint16_t b = q_bf16 ? reinterpret_cast<const uint16_t*>(q_rope)[off] : bf16_bits_from_f32(reinterpret_cast<const float*>(q_rope)[off]);
-      q_abs[((size_t)(r0 + r) * H + h) * roww + dC + d] = b;
-    }
+  __syncthreads();
+  for (int e = threadIdx.x; e < 64 * 16; e += blockDim.x) {
+    const int r = e / 16, v = e % 16;
+    if (r0 + r >= rows) continue;
+    *reinterpret_cast<uint4*>(q_abs + ((size_t)(r0 + r) * H + h) * roww + c0 + v * 8) = *reinterpret_cast<const uint4*>(Os + r * kStride + v * 8);
   }
 }
 
@@ -146,6 +173,113 @@ __global__ void __launch_bounds__(128) mla_vup_mma_kernel(const uint16_t* __rest
   }
 }
 
+// Split-KV merge fused into the value up-projection: the A operand (the merged, normalised latent output of
+// 64 rows of one head, as bf16) is built straight from the per-item partials
+//   part_o [item][S * H][dC] f32 (unnormalised), part_ml [item][S * H][2] = (max in the log2 domain, sum),
+// items of sequence i = [chunk_off[i], chunk_off[i + 1]).  All of W_UV's slice for this head (dC x 128 bf16) streams
+// into shared memory with cp.async while the partials are combined.
+// grid (H, ceil(rows/64)), 128 threads, row = seq_index * S + query token.  dC = 128 * kChunks, kChunks <= 4.
+constexpr int kMaxChunks = 4;
+__global__ void __launch_bounds__(128) mla_merge_vup_mma_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                                const int32_t* __restrict__ chunk_off, const uint16_t* __restrict__ W_UV,
+                                                                float* __restrict__ out, int rows, int S, int H, int dC) {
+  extern __shared__ __align__(16) uint16_t sm[];
+  const int nk = dC / 128;
+  uint16_t* As = sm;                             // [nk][64][kStride]
+  uint16_t* Bs = sm + (size_t)nk * 64 * kStride;  // [nk][128][kStride]
+  __shared__ float sM[64], sInv[64];
+  __shared__ int32_t sC0[64], sC1[64];
+  const int h = blockIdx.x, r0 = blockIdx.y * 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows_total = S * H;
+  for (int k = 0; k < nk; k++) {
+#pragma unroll 4
+    for (int e = threadIdx.x; e < 128 * 16; e += blockDim.x) {
+      const int c = e / 16, v = e % 16;
+      cp_async16(Bs + ((size_t)k * 128 + c) * kStride + v * 8, W_UV + (size_t)(k * 128 + c) * H * kDh + (size_t)h * kDh + (size_t)v * 8);
+    }
+    cp_async_commit();
+  }
+  if (threadIdx.x < 64) {
+    const int r = r0 + threadIdx.x;
+    int c0 = 0, c1 = 0;
+    float M = -INFINITY, L = 0.f;
+    if (r < rows) {
+      const int i = r / S, sq = r % S;
+      c0 = chunk_off[i];
+      c1 = chunk_off[i + 1];
+      const size_t prow = (size_t)sq * H + h;
+      for (int c = c0; c < c1; c++) M = fmaxf(M, part_ml[((size_t)c * rows_total + prow) * 2]);
+      for (int c = c0; c < c1; c++) {
+        const float* ml = part_ml + ((size_t)c * rows_total + prow) * 2;
+        if (ml[0] != -INFINITY) L += ml[1] * exp2f(ml[0] - M);
+      }
+    }
+    sM[threadIdx.x] = M;
+    sInv[threadIdx.x] = (L > 0.f) ? 1.0f / L : 0.f;
+    sC0[threadIdx.x] = c0;
+    sC1[threadIdx.x] = c1;
+  }
+  __syncthreads();
+  {
+    // two threads per row, 64 columns of every 128-column chunk each
+    const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
+    const int r = r0 + row;
+    const int c0 = sC0[row], c1 = sC1[row];
+    const float M = sM[row], inv = sInv[row];
+    const size_t prow = (r < rows) ? (size_t)(r % S) * H + h : 0;
+    for (int k = 0; k < nk; k++) {
+      float acc[64];
+#pragma unroll
+      for (int j = 0; j < 64; j++) acc[j] = 0.f;
+      for (int c = c0; c < c1; c++) {
+        const size_t pr = (size_t)c * rows_total + prow;
+        const float m = __ldg(part_ml + pr * 2);
+        const float w = (m == -INFINITY) ? 0.f : exp2f(m - M) * inv;
+        const float4* src = reinterpret_cast<const float4*>(part_o + pr * dC + k * 128 + half * 64);
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+          const float4 x = __ldg(src + j);
+          acc[4 * j] = fmaf(x.x, w, acc[4 * j]);
+          acc[4 * j + 1] = fmaf(x.y, w, acc[4 * j + 1]);
+          acc[4 * j + 2] = fmaf(x.z, w, acc[4 * j + 2]);
+          acc[4 * j + 3] = fmaf(x.w, w, acc[4 * j + 3]);
+        }
+      }
+      uint16_t* dst = As + ((size_t)k * 64 + row) * kStride + half * 64;
+#pragma unroll
+      for (int j = 0; j < 8; j++)
+        *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(pack_bf16x2(acc[8 * j], acc[8 * j + 1]), pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3]),
+                                                            pack_bf16x2(acc[8 * j + 4], acc[8 * j + 5]), pack_bf16x2(acc[8 * j + 6], acc[8 * j + 7]));
+    }
+  }
+  float acc[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; i++)
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+  for (int k = 0; k < nk; k++) {
+    // chunk k of W_UV has landed once at most nk - 1 - k younger groups are still in flight
+    switch (nk - 1 - k) {
+      case 3: cp_async_wait<3>(); break;
+      case 2: cp_async_wait<2>(); break;
+      case 1: cp_async_wait<1>(); break;
+      default: cp_async_wait<0>(); break;
+    }
+    __syncthreads();   // also publishes the merged A tiles (first iteration)
+    tile_mma_64x128x128<true>(As + (size_t)k * 64 * kStride, Bs + (size_t)k * 128 * kStride, acc, warp, lane);
+  }
+#pragma unroll
+  for (int hf = 0; hf < 2; hf++) {
+    const int r = r0 + warp * 16 + hf * 8 + (lane >> 2);
+    if (r >= rows) continue;
+    float* dst = out + ((size_t)r * H + h) * kDh;
+#pragma unroll
+    for (int nt = 0; nt < 16; nt++)
+      *reinterpret_cast<float2*>(dst + nt * 8 + 2 * (lane & 3)) = make_float2(acc[nt][hf * 2], acc[nt][hf * 2 + 1]);
+  }
+}
+
 }  // namespace
 
 bool mla_proj_mma_eligible(int Dh, int dC) { return Dh == kDh && dC % 128 == 0; }
@@ -166,6 +300,17 @@ int32_t launch_mla_vup_mma(Device* dev, const uint16_t* o_lat, const uint16_t* W
   const size_t smem = (size_t)(64 + 128) * kStride * 2;
   RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_vup_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   mla_vup_mma_kernel<<<grid, 128, smem, dev->stream>>>(o_lat, W_UV, out, rows, H, dC);
+  RELUX_CUDA_TRY(cudaGetLastError());
+  count_launch(dev);
+  return RELUX_OK;
+}
+
+int32_t launch_mla_merge_vup_mma(Device* dev, const float* part_o, const float* part_ml, const int32_t* chunk_off, const uint16_t* W_UV,
+                                 float* out, int rows, int S, int H, int dC) {
+  dim3 grid(H, (rows + 63) / 64);
+  const size_t smem = (size_t)(dC / 128) * (64 + 128) * kStride * 2;
+  RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_merge_vup_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  mla_merge_vup_mma_kernel<<<grid, 128, smem, dev->stream>>>(part_o, part_ml, chunk_off, W_UV, out, rows, S, H, dC);
   RELUX_CUDA_TRY(cudaGetLastError());
   count_launch(dev);
   return RELUX_OK;
