@@ -29,7 +29,27 @@ struct AppendGeom {
   int32_t num_pages, page_tokens, max_pages_per_seq;
   int32_t* status;
   int32_t advance;
+  uint32_t* done;      // zero between launches; counts finished blocks of the running append
 };
+
+// Length bookkeeping fused into the append: every block reads its sequence's length before it arrives here, so the
+// last block to arrive may advance all lengths (and re-arm the counter for the next launch).  grid.x = n_seqs.
+__device__ __forceinline__ void advance_lengths_by_last_block(const AppendGeom& g) {
+  if (!g.advance) return;
+  __shared__ bool s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = atomicAdd(g.done, 1u) == gridDim.x * gridDim.y - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  for (int i = threadIdx.x; i < (int)gridDim.x; i += blockDim.x) {
+    const int seq = g.seq_ids ? g.seq_ids[i] : i;
+    g.len[seq] += g.row_off ? g.row_off[i + 1] - g.row_off[i] : 1;
+  }
+  if (threadIdx.x == 0) *g.done = 0u;
+}
 
 // grid (n_seqs, row_slices).  One sequence's new rows are spread over blockIdx.y.
 // MLA row = [dC | dHR] fused, dC and dHR multiples of 8.
@@ -57,6 +77,7 @@ __global__ void mla_append_kernel(AppendGeom g, uint16_t* __restrict__ layer_bas
       *reinterpret_cast<uint4*>(page + mla_page_off(blocked != 0, g.page_tokens, row_elems, pos % g.page_tokens, v * 8)) = w;
     }
   }
+  advance_lengths_by_last_block(g);
 }
 
 // GQA: source rows K,V [tok][Hkv][D] (token-major) or [Hkv][n_new][D] per sequence (head-major);
@@ -89,15 +110,9 @@ __global__ void gqa_append_kernel(AppendGeom g, uint16_t* __restrict__ k_base, u
       *reinterpret_cast<uint4*>(dst) = w;
     }
   }
+  advance_lengths_by_last_block(g);
 }
 
-__global__ void advance_len_kernel(int32_t* len, const int32_t* seq_ids, const int32_t* row_off, int n_seqs) {
-  int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n_seqs) return;
-  int seq = seq_ids ? seq_ids[i] : i;
-  int n = row_off ? row_off[i + 1] - row_off[i] : 1;
-  len[seq] += n;
-}
 __global__ void set_len_kernel(int32_t* len, const int32_t* seq_ids, const int32_t* new_len, int n_seqs) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_seqs) return;
@@ -116,18 +131,13 @@ static AppendGeom make_geom(Pool* p, const SeqBatch& sb, int layer, int advance)
   g.max_pages_per_seq = p->prm.max_pages_per_seq;
   g.status = p->d_status;
   g.advance = advance;
+  g.done = reinterpret_cast<uint32_t*>(p->d_status + 1);
   return g;
 }
 
-static int32_t finish_append(Pool* p, const SeqBatch& sb, int layer, int advance) {
+static int32_t finish_append(Pool* p) {
   RELUX_CUDA_TRY(cudaGetLastError());
   count_launch(p->dev);
-  if (advance) {
-    int32_t* len = p->d_len + (size_t)layer * p->prm.max_seqs;
-    advance_len_kernel<<<(sb.n_seqs + 127) / 128, 128, 0, p->dev->stream>>>(len, sb.d_seq_ids, sb.d_row_off, sb.n_seqs);
-    RELUX_CUDA_TRY(cudaGetLastError());
-    count_launch(p->dev);
-  }
   return RELUX_OK;
 }
 
@@ -140,7 +150,7 @@ int32_t launch_mla_append(Pool* p, const SeqBatch& sb, int layer, const void* ck
     mla_append_kernel<true><<<grid, threads, 0, p->dev->stream>>>(g, base, ckv, kr, p->prm.mla_dc, p->prm.mla_dhr, p->mla_blocked);
   else
     mla_append_kernel<false><<<grid, threads, 0, p->dev->stream>>>(g, base, ckv, kr, p->prm.mla_dc, p->prm.mla_dhr, p->mla_blocked);
-  return finish_append(p, sb, layer, advance);
+  return finish_append(p);
 }
 
 int32_t launch_gqa_append(Pool* p, const SeqBatch& sb, int layer, const void* k, const void* v, int dtype, int layout,
@@ -155,7 +165,7 @@ int32_t launch_gqa_append(Pool* p, const SeqBatch& sb, int layer, const void* k,
     gqa_append_kernel<true><<<grid, threads, 0, p->dev->stream>>>(g, kb, vb, k, v, p->prm.gqa_num_kv_heads, p->prm.gqa_head_dim, hm);
   else
     gqa_append_kernel<false><<<grid, threads, 0, p->dev->stream>>>(g, kb, vb, k, v, p->prm.gqa_num_kv_heads, p->prm.gqa_head_dim, hm);
-  return finish_append(p, sb, layer, advance);
+  return finish_append(p);
 }
 
 int32_t launch_set_len(Pool* p, const SeqBatch& sb, int layer, const int32_t* d_new_len) {

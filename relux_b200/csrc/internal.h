@@ -57,7 +57,7 @@ struct Pool {
   uint16_t* storage = nullptr;  // bf16 bits
   int32_t* d_table = nullptr;   // [max_seqs][max_pages_per_seq]
   int32_t* d_len = nullptr;     // [num_layers][max_seqs]
-  int32_t* d_status = nullptr;
+  int32_t* d_status = nullptr;   // [0] status word, [1] block counter of the append kernels
   std::vector<int32_t> h_table, h_len;
   std::vector<int32_t> seq_pages;  // pages reserved per sequence (capacity), 0 = slot not live
   std::vector<uint8_t> seq_owned;  // 1 = table rows were filled by relux_seq_alloc

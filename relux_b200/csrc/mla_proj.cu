@@ -17,6 +17,7 @@ namespace {
 
 constexpr int kDh = 128;
 constexpr int kStride = kDh + 8;  // bf16 elements per shared-memory row (272 B: conflict-free ldmatrix)
+constexpr int kMaxChunks = 4;     // the fused merge + up-projection keeps at most 4 x 128 latent columns in shared memory
 
 // 64 x 128 A tile (rows x k) and 128 x 128 B tile; warp w owns rows 16w..16w+15 and all 128 columns.
 // kBTrans = false: Bs is [n][k] (k contiguous)  -> ldmatrix;  true: Bs is [k][n] (n contiguous) -> ldmatrix.trans
@@ -173,14 +174,39 @@ __global__ void __launch_bounds__(128) mla_vup_mma_kernel(const uint16_t* __rest
   }
 }
 
+// 64 x 128 x 128 tile for eight warps: warp w owns rows 16 (w & 3) .. +15 and the 64 columns of half (w >> 2).
+// Bs is [k][n] (n contiguous) -> ldmatrix.trans.
+__device__ __forceinline__ void tile_mma_64x64x128_bt(const uint16_t* As, const uint16_t* Bs, float (&acc)[8][4], int warp, int lane) {
+  const int wr = warp & 3, wn = warp >> 2;
+#pragma unroll
+  for (int ks = 0; ks < 8; ks++) {
+    uint32_t a[4];
+    const int m = lane >> 3;
+    {
+      const int row = wr * 16 + (m & 1) * 8 + (lane & 7);
+      const int col = ks * 16 + (m >> 1) * 8;
+      ldmatrix_x4(a[0], a[1], a[2], a[3], smem_u32(As + row * kStride + col));
+    }
+#pragma unroll
+    for (int n2 = 0; n2 < 4; n2++) {
+      uint32_t b0, b1, b2, b3;
+      const int krow = ks * 16 + (m & 1) * 8 + (lane & 7);
+      const int ncol = wn * 64 + n2 * 16 + (m >> 1) * 8;
+      ldmatrix_x4_trans(b0, b1, b2, b3, smem_u32(Bs + krow * kStride + ncol));
+      mma_bf16_16816(acc[2 * n2], a, b0, b1);
+      mma_bf16_16816(acc[2 * n2 + 1], a, b2, b3);
+    }
+  }
+}
+
 // Split-KV merge fused into the value up-projection: the A operand (the merged, normalised latent output of
 // 64 rows of one head, as bf16) is built straight from the per-item partials
 //   part_o [item][S * H][dC] f32 (unnormalised), part_ml [item][S * H][2] = (max in the log2 domain, sum),
 // items of sequence i = [chunk_off[i], chunk_off[i + 1]).  All of W_UV's slice for this head (dC x 128 bf16) streams
-// into shared memory with cp.async while the partials are combined.
-// grid (H, ceil(rows/64)), 128 threads, row = seq_index * S + query token.  dC = 128 * kChunks, kChunks <= 4.
-constexpr int kMaxChunks = 4;
-__global__ void __launch_bounds__(128) mla_merge_vup_mma_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+// into shared memory with cp.async while the partials are combined; four threads per row keep 32 independent
+// 16-byte loads in flight per item, so the merge costs about one memory round trip per item of a sequence.
+// grid (H, ceil(rows/64)), 256 threads, row = seq_index * S + query token.  dC = 128 * nk, nk <= 4.
+__global__ void __launch_bounds__(256) mla_merge_vup_mma_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                                 const int32_t* __restrict__ chunk_off, const uint16_t* __restrict__ W_UV,
                                                                 float* __restrict__ out, int rows, int S, int H, int dC) {
   extern __shared__ __align__(16) uint16_t sm[];
@@ -222,40 +248,51 @@ __global__ void __launch_bounds__(128) mla_merge_vup_mma_kernel(const float* __r
   }
   __syncthreads();
   {
-    // two threads per row, 64 columns of every 128-column chunk each
-    const int row = threadIdx.x >> 1, half = threadIdx.x & 1;
+    // four threads per row; thread `qt` of a row owns columns [32 qt, 32 qt + 32) of every 128-column chunk
+    const int row = threadIdx.x >> 2, qt = threadIdx.x & 3;
     const int r = r0 + row;
     const int c0 = sC0[row], c1 = sC1[row];
     const float M = sM[row], inv = sInv[row];
     const size_t prow = (r < rows) ? (size_t)(r % S) * H + h : 0;
-    for (int k = 0; k < nk; k++) {
-      float acc[64];
+    float acc[kMaxChunks][32];
 #pragma unroll
-      for (int j = 0; j < 64; j++) acc[j] = 0.f;
-      for (int c = c0; c < c1; c++) {
-        const size_t pr = (size_t)c * rows_total + prow;
-        const float m = __ldg(part_ml + pr * 2);
-        const float w = (m == -INFINITY) ? 0.f : exp2f(m - M) * inv;
-        const float4* src = reinterpret_cast<const float4*>(part_o + pr * dC + k * 128 + half * 64);
+    for (int k = 0; k < kMaxChunks; k++)
 #pragma unroll
-        for (int j = 0; j < 16; j++) {
-          const float4 x = __ldg(src + j);
-          acc[4 * j] = fmaf(x.x, w, acc[4 * j]);
-          acc[4 * j + 1] = fmaf(x.y, w, acc[4 * j + 1]);
-          acc[4 * j + 2] = fmaf(x.z, w, acc[4 * j + 2]);
-          acc[4 * j + 3] = fmaf(x.w, w, acc[4 * j + 3]);
+      for (int j = 0; j < 32; j++) acc[k][j] = 0.f;
+    for (int c = c0; c < c1; c++) {
+      const size_t pr = (size_t)c * rows_total + prow;
+      const float m = __ldg(part_ml + pr * 2);
+      const float w = (m == -INFINITY) ? 0.f : exp2f(m - M) * inv;
+      const float4* src = reinterpret_cast<const float4*>(part_o + pr * dC + qt * 32);
+#pragma unroll
+      for (int k = 0; k < kMaxChunks; k++) {
+        if (k < nk) {
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const float4 x = __ldg(src + k * 32 + j);
+            acc[k][4 * j] = fmaf(x.x, w, acc[k][4 * j]);
+            acc[k][4 * j + 1] = fmaf(x.y, w, acc[k][4 * j + 1]);
+            acc[k][4 * j + 2] = fmaf(x.z, w, acc[k][4 * j + 2]);
+            acc[k][4 * j + 3] = fmaf(x.w, w, acc[k][4 * j + 3]);
+          }
         }
       }
-      uint16_t* dst = As + ((size_t)k * 64 + row) * kStride + half * 64;
+    }
 #pragma unroll
-      for (int j = 0; j < 8; j++)
-        *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(pack_bf16x2(acc[8 * j], acc[8 * j + 1]), pack_bf16x2(acc[8 * j + 2], acc[8 * j + 3]),
-                                                            pack_bf16x2(acc[8 * j + 4], acc[8 * j + 5]), pack_bf16x2(acc[8 * j + 6], acc[8 * j + 7]));
+    for (int k = 0; k < kMaxChunks; k++) {
+      if (k < nk) {
+        uint16_t* dst = As + ((size_t)k * 64 + row) * kStride + qt * 32;
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+          *reinterpret_cast<uint4*>(dst + j * 8) =
+              make_uint4(pack_bf16x2(acc[k][8 * j], acc[k][8 * j + 1]), pack_bf16x2(acc[k][8 * j + 2], acc[k][8 * j + 3]),
+                         pack_bf16x2(acc[k][8 * j + 4], acc[k][8 * j + 5]), pack_bf16x2(acc[k][8 * j + 6], acc[k][8 * j + 7]));
+      }
     }
   }
-  float acc[16][4];
+  float acc[8][4];
 #pragma unroll
-  for (int i = 0; i < 16; i++)
+  for (int i = 0; i < 8; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
   for (int k = 0; k < nk; k++) {
@@ -267,15 +304,15 @@ __global__ void __launch_bounds__(128) mla_merge_vup_mma_kernel(const float* __r
       default: cp_async_wait<0>(); break;
     }
     __syncthreads();   // also publishes the merged A tiles (first iteration)
-    tile_mma_64x128x128<true>(As + (size_t)k * 64 * kStride, Bs + (size_t)k * 128 * kStride, acc, warp, lane);
+    tile_mma_64x64x128_bt(As + (size_t)k * 64 * kStride, Bs + (size_t)k * 128 * kStride, acc, warp, lane);
   }
 #pragma unroll
   for (int hf = 0; hf < 2; hf++) {
-    const int r = r0 + warp * 16 + hf * 8 + (lane >> 2);
+    const int r = r0 + (warp & 3) * 16 + hf * 8 + (lane >> 2);
     if (r >= rows) continue;
-    float* dst = out + ((size_t)r * H + h) * kDh;
+    float* dst = out + ((size_t)r * H + h) * kDh + (warp >> 2) * 64;
 #pragma unroll
-    for (int nt = 0; nt < 16; nt++)
+    for (int nt = 0; nt < 8; nt++)
       *reinterpret_cast<float2*>(dst + nt * 8 + 2 * (lane & 3)) = make_float2(acc[nt][hf * 2], acc[nt][hf * 2 + 1]);
   }
 }
@@ -310,7 +347,7 @@ int32_t launch_mla_merge_vup_mma(Device* dev, const float* part_o, const float* 
   dim3 grid(H, (rows + 63) / 64);
   const size_t smem = (size_t)(dC / 128) * (64 + 128) * kStride * 2;
   RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_merge_vup_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  mla_merge_vup_mma_kernel<<<grid, 128, smem, dev->stream>>>(part_o, part_ml, chunk_off, W_UV, out, rows, S, H, dC);
+  mla_merge_vup_mma_kernel<<<grid, 256, smem, dev->stream>>>(part_o, part_ml, chunk_off, W_UV, out, rows, S, H, dC);
   RELUX_CUDA_TRY(cudaGetLastError());
   count_launch(dev);
   return RELUX_OK;

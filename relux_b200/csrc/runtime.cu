@@ -579,7 +579,7 @@ API int32_t relux_pool_create(relux_device_t h, const relux_pool_params* prm, re
   A((void**)&p->storage, storage_bytes);
   A((void**)&p->d_table, table_n * 4);
   A((void**)&p->d_len, len_n * 4);
-  A((void**)&p->d_status, 4);
+  A((void**)&p->d_status, 8);   // [0] status word, [1] block counter of the append kernels
   A((void**)&p->d_seq_ids, (size_t)prm->max_seqs * 4);
   A((void**)&p->d_row_off, ((size_t)prm->max_seqs + 1) * 4);
   if (e == cudaSuccess) e = cudaMallocHost((void**)&p->h_stage, (2 * (size_t)prm->max_seqs + 1) * 4);
@@ -589,7 +589,7 @@ API int32_t relux_pool_create(relux_device_t h, const relux_pool_params* prm, re
       if (e == cudaSuccess) e = cudaEventCreate(&ev);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_table, 0xFF, table_n * 4, dev->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_len, 0, len_n * 4, dev->stream);
-  if (e == cudaSuccess) e = cudaMemsetAsync(p->d_status, 0, 4, dev->stream);
+  if (e == cudaSuccess) e = cudaMemsetAsync(p->d_status, 0, 8, dev->stream);
   // The reference zero-fills new caches (kvcache.go:73-84, mla_cache.go:46-52).
   if (e == cudaSuccess) e = cudaMemsetAsync(p->storage, 0, storage_bytes, dev->stream);
   if (e != cudaSuccess) {
