@@ -415,7 +415,8 @@ def run_reference(args, w, world, rank):
     from oracle import binding as orc
     if rank != 0:
         return None
-    threads = orc.num_threads()
+    # every host core this process may run on (a launcher's OMP_NUM_THREADS=1 default is not a property of the box)
+    threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or orc.num_threads())
     t0 = time.time()
     cpu_baseline(w, threads, sample_T=16)
     per_token = max(1e-6, (time.time() - t0) / 16)
