@@ -49,51 +49,55 @@ def read_peaks():
 
 
 class ClockSampler(threading.Thread):
-    """Samples the SM clock and the throttle reasons through NVML (the counters nvidia-smi prints) every 25 ms
-    while the timed region runs; read-only.  (Sampling every few milliseconds slowed the kernel launches of the
-    timed loop down: NVML queries and launches share driver locks.)"""
+    """Samples SM clock and throttle reasons with a separate `nvidia-smi -lms 50` process while the timed region runs
+    (read-only).  In-process NVML polling was tried and dropped: its queries share driver locks with kernel launches
+    and slowed the timed loop by up to 2x."""
 
-    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
-    def __init__(self, index, period_s=0.025):
+    def __init__(self, index):
         super().__init__(daemon=True)
         self.index = index
-        self.period_s = period_s
-        self.sm = []
-        self.mask = 0
-        self.max_mhz = None
+        self.samples = []   # (arrival time, fields)
+        self.t_begin = None
         self.stop_flag = False
-        self.error = None
+        self.proc = None
 
     def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        vis = [x for x in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if x.strip()]
+        dev_id = vis[self.index] if self.index < len(vis) else str(self.index)
         try:
-            import pynvml as nv
-            nv.nvmlInit()
-            # NVML numbers devices like nvidia-smi; honour CUDA_VISIBLE_DEVICES when it is a plain index list
-            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
-            ids = [int(x) for x in vis.split(",") if x.strip().isdigit()]
-            h = nv.nvmlDeviceGetHandleByIndex(ids[self.index] if self.index < len(ids) else self.index)
-            self.max_mhz = int(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
-            while not self.stop_flag:
-                self.sm.append(int(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
-                self.mask |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(h))
-                time.sleep(self.period_s)
-        except Exception as e:  # no NVML: the line then carries no clock record
-            self.error = repr(e)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", dev_id, "--query-gpu=" + q, "--format=csv,noheader,nounits",
+                                          "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            for line in self.proc.stdout:
+                if self.stop_flag:
+                    break
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) >= 6:
+                    self.samples.append((time.time(), parts))
+        except Exception:
+            pass
 
     def begin(self):
-        """Drops what was sampled so far (warm-up); call right before the timed region."""
-        self.sm, self.mask = [], 0
+        """Marks the start of the timed region; earlier samples (warm-up) are used only if the region saw none."""
+        self.t_begin = time.time()
 
     def finish(self):
+        t_end = time.time()
+        time.sleep(0.06)   # let the sample that covers the end of the region arrive
         self.stop_flag = True
-        self.join(timeout=2.0)
-        reasons = sorted(n for n, bit in self.REASONS if self.mask & bit)
-        out = {"sm_mhz": int(np.median(self.sm)) if self.sm else None, "sm_min_mhz": min(self.sm) if self.sm else None,
-               "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(self.sm), "source": "nvml"}
-        if self.error:
-            out["error"] = self.error
-        return out
+        if self.proc:
+            self.proc.terminate()
+        inside = [s for t, s in self.samples if self.t_begin is not None and self.t_begin <= t <= t_end + 0.06]
+        used = inside if inside else [s for _, s in self.samples]
+        sm = [int(s[0]) for s in used if s[0].isdigit()]
+        mx = [int(s[1]) for s in used if s[1].isdigit()]
+        reasons = sorted({self.NAMES[i] for s in used for i in range(4) if s[2 + i].lower().startswith("active")})
+        return {"sm_mhz": int(np.median(sm)) if sm else None, "sm_min_mhz": min(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": reasons, "samples": len(sm),
+                "samples_inside_timed_region": len(inside), "source": "nvidia-smi -lms 50"}
 
 
 def dist_setup(n_gpus):
@@ -192,7 +196,7 @@ def run_mla(args, w, world, rank, local, dist):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.05)
+        time.sleep(0.3)
     ms_res, launches = timed(step_resident, args.steps, args.warmup, sampler if rank == 0 else None)
     clocks = sampler.finish() if rank == 0 else None
     # dominant kernel: the decode kernel; every call records a CUDA event pair around that launch on the launching
@@ -317,7 +321,7 @@ def run_gqa(args, w, world, rank, local, dist):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.05)
+        time.sleep(0.3)
     ms_res, launches, acc_res = timed(step_resident, args.steps, args.warmup, sampler if rank == 0 else None)
     clocks = sampler.finish() if rank == 0 else None
     # dominant kernel: event pairs recorded by the calls of the timed region themselves (the library keeps the last 256)
