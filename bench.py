@@ -36,7 +36,7 @@ WORKLOADS = {
 }
 # dram__bytes_read + dram__bytes_write of the dominant kernel divided by its algorithmic bytes, from the ncu captures
 # summarised under profiles/ (small case, traffic grows in proportion to the cached tokens read).
-TRAFFIC_RATIO = {"mla": 1.03, "gqa": 1.015}
+TRAFFIC_RATIO = {"mla": 1.04, "gqa": 1.015}
 PAGE = 64
 
 
