@@ -219,6 +219,46 @@ int32_t relux_gqa_decode(relux_pool_t pool, const relux_attn_args* args);
 int32_t relux_gqa_verify(relux_pool_t pool, const relux_attn_args* attn, const relux_append_args* draft_kv);
 int32_t relux_mla_verify(relux_pool_t pool, const relux_attn_args* attn, const relux_append_args* draft_kv);
 
+/* One MLA attention layer step, device-resident end to end: MLA.forwardCached (mla.go:272-397) for a batch of
+ * independent sequences.  x [n_seqs][q_tokens][d_model] float32 (host or device) is projected with the reference's
+ * bf16 weight matrices (row-major [in][out] exactly as optim.Param.Data holds them, mla.go:41-47, on the device):
+ *   q^C = x W_Q, q^R = x W_QR, c^KV = x W_DKV, k^R = x W_KR                      (mla.go:285-288)
+ * q^R and k^R are rotated with the decoupled RoPE of NewMLA (mla.go:83, tables built as rope.go:59-68) at position
+ * cached_len + s for the s-th new token of a sequence, (c^KV, k^R) are appended to this pool's layer `layer`
+ * (cursors advance by q_tokens), the absorbed attention runs over the cache with scale 1/sqrt(head_dim + dHR)
+ * (mla.go:344-345; causal != 0 masks inside the q_tokens new rows), and out = o W_O [n_seqs][q_tokens][d_model]
+ * float32 (host or device).  head_dim = d_model / num_heads like NewMLA; dC and dHR are the pool's.
+ * RELUX_ATTN_FAST runs the projections on the tensor cores with x rounded to bf16; RELUX_ATTN_REFERENCE runs every
+ * step in the reference's float32 operation order.  Errors: RELUX_ERR_OVERFLOW when a sequence would pass its
+ * capacity (the reference panics, mla_cache.go:160-164) or a position passes the RoPE table (rope.go:160-162). */
+typedef struct relux_mla_layer_weights {
+  const void* w_q;    /* device bf16 [d_model][num_heads*head_dim] */
+  const void* w_qr;   /* device bf16 [d_model][num_heads*dHR] */
+  const void* w_dkv;  /* device bf16 [d_model][dC] */
+  const void* w_kr;   /* device bf16 [d_model][dHR] */
+  const void* w_uk;   /* device bf16 [dC][num_heads*head_dim] */
+  const void* w_uv;   /* device bf16 [dC][num_heads*head_dim] */
+  const void* w_o;    /* device bf16 [num_heads*head_dim][d_model] */
+} relux_mla_layer_weights;
+typedef struct relux_mla_layer_args {
+  int32_t layer;
+  int32_t n_seqs;
+  const int32_t* seq_ids;   /* host [n_seqs]; NULL = 0..n_seqs-1 */
+  int32_t q_tokens;         /* new tokens per sequence (1 for decode) */
+  int32_t causal;
+  int32_t d_model;
+  int32_t num_heads;
+  float rope_base;          /* 0 = 10000 like NewMLA (mla.go:78-80) */
+  int32_t mode;             /* RELUX_ATTN_FAST | RELUX_ATTN_REFERENCE */
+  const void* x;
+  int32_t x_dtype, x_mem;   /* RELUX_DTYPE_F32; RELUX_MEM_HOST | RELUX_MEM_DEVICE */
+  void* out;
+  int32_t out_mem;
+  int32_t reserved[3];
+  const relux_mla_layer_weights* w;
+} relux_mla_layer_args;
+int32_t relux_mla_forward_cached(relux_pool_t pool, const relux_mla_layer_args* args);
+
 /* GQA flash-decode / verify that allocates nothing.  It has no counterpart in the reference; it exists for callers
  * that may not allocate device memory at the moment they decode: a serving loop whose memory budget has been handed
  * out completely (so a late cudaMalloc can fail or stall the whole device while it synchronises), or code running

@@ -278,6 +278,18 @@ class Pool:
         fn = self.lib.relux_mla_verify if self.kind == L.POOL_MLA else self.lib.relux_gqa_verify
         L.check(fn(self.h, C.byref(at), C.byref(ap)))
 
+    def forward_cached(self, layer, n_seqs, x, out, weights, d_model, num_heads, q_tokens=1, causal=True, rope_base=0.0,
+                       mode=L.ATTN_FAST, seq_ids=None):
+        """One MLA layer step (MLA.forwardCached, mla.go:272-397): x [n_seqs, q_tokens, d_model] float32 ->
+        out [n_seqs, q_tokens, d_model] float32; `weights` maps w_q, w_qr, w_dkv, w_kr, w_uk, w_uv, w_o to device
+        buffers of bf16 bits in the reference's [in, out] layout.  Appends q_tokens rows per sequence."""
+        ids = None if seq_ids is None else np.ascontiguousarray(seq_ids, dtype=np.int32)
+        w = L.MlaLayerWeights(**{k: _ptr(weights[k]) for k in ("w_q", "w_qr", "w_dkv", "w_kr", "w_uk", "w_uv", "w_o")})
+        args = L.MlaLayerArgs(layer=layer, n_seqs=n_seqs, seq_ids=_ptr(ids), q_tokens=q_tokens, causal=int(causal), d_model=d_model,
+                              num_heads=num_heads, rope_base=float(rope_base), mode=mode, x=_ptr(x), x_dtype=_dtype_flag(x),
+                              x_mem=_mem(x), out=_ptr(out), out_mem=_mem(out), w=C.pointer(w))
+        L.check(self.lib.relux_mla_forward_cached(self.h, C.byref(args)))
+
     def last_kernel_ms(self):
         ms = C.c_float()
         L.check(self.lib.relux_pool_last_kernel_ms(self.h, C.byref(ms)))

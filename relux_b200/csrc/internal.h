@@ -81,6 +81,10 @@ struct Pool {
   CUtensorMap tmap_gqa{};   // 2-D [rows][D],      box 64 x 64, 128-byte swizzle
   bool has_tmap = false;
   bool mla_blocked = false;   // MLA pages stored as 64-column blocks (see mla_page_off)
+  // layer-level step (mla_layer.cu): RoPE tables [cos | sin][positions][dHR / 2] and the step's scratch block
+  GrowBuf rope_tab, layer_buf;
+  int rope_dim = 0, rope_positions = 0;
+  float rope_base = 0.f;
   // timing of the dominant kernel: a ring of event pairs, one pair per attention call, so that a caller can read
   // the device times of its last kTimeRing calls after the fact without a synchronisation between them
   static constexpr int kTimeRing = 256;
@@ -126,6 +130,8 @@ int32_t launch_attn_reference_mla(Pool* p, const SeqBatch& sb, const relux_attn_
 int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, void* d_out);
 int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, const void* d_qr,
                                void* d_out);
+
+int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a);
 
 inline void count_launch(Device* d, int n = 1) { d->launches += n; }
 

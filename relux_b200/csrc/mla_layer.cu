@@ -1,0 +1,552 @@
+// One MLA attention layer step on the device: the work of MLA.forwardCached (internal/transformer/mla.go:272-397)
+// either side of the cached attention, so that a caller hands over the layer input x and gets the layer output back.
+//   1. projections  q^C = x W_Q, q^R = x W_QR, c^KV = x W_DKV, k^R = x W_KR          mla.go:285-288
+//   2. decoupled RoPE on q^R and k^R at position cacheLen + s                          mla.go:297-307, rope.go:130-180
+//   3. append (c^KV, k^R) to the paged latent cache                                    mla.go:309-314
+//   4. absorbed attention over the cache (the kernels of mla_decode.cu)                mla.go:317-377
+//   5. output projection  out = o W_O                                                  mla.go:380-389
+// The projections are skinny GEMMs (M = sequences x new tokens, at most a few hundred rows) against bf16 weight
+// matrices of up to 16384 x 16384: they are bound by streaming the weights from HBM once.  FAST mode runs them on
+// tcgen05 (activations rounded to bf16, f32 accumulation in tensor memory, split along K so that every SM streams an
+// equal share of the weights); REFERENCE mode runs them in the reference's own float32 operation order
+// (matmulBatched3D, matmul.go: k ascending, multiply then add, never fused), bit for bit.
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include "common.cuh"
+#include "internal.h"
+#include "umma.cuh"
+
+namespace relux {
+
+bool make_tmap_2d(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows);
+int32_t stage_in(Pool* p, GrowBuf& buf, const void* src, size_t bytes, int mem, const void** dptr);
+
+namespace {
+
+constexpr int kMaxWeights = 4;   // weight matrices that share one activation matrix in a launch
+constexpr int kTileN = 128, kTileM = 128, kTileK = 64;
+constexpr int kStages = 6;
+constexpr int kStageA = kTileM * kTileK * 2;   // 16 KB: [128 rows][64 k] bf16, 128-byte swizzle, K-major
+constexpr int kStageB = kTileK * kTileN * 2;   // 16 KB: two [64 k][64 n] blocks, 128-byte swizzle, MN-major
+constexpr int kGemmSmem = kStages * (kStageA + kStageB) + 1024;
+
+struct GemmMaps {
+  CUtensorMap a;                 // activations [M][K] bf16
+  CUtensorMap w[kMaxWeights];    // weights [K][N_j] bf16
+};
+struct GemmParams {
+  int32_t n_weights;
+  int32_t tile_first[kMaxWeights + 1];   // first 128-column tile of every weight
+  int32_t n_cols[kMaxWeights];           // N_j
+  int32_t col_first[kMaxWeights];        // first output column of weight j in the concatenated result
+  int32_t M, K, n_total, split_k;
+  float* part;                           // [split_k][M][n_total] f32
+  int32_t* status;
+};
+
+struct GemmBars {
+  uint64_t full[kStages], empty[kStages], done;
+  uint32_t tmem_base;
+  volatile int32_t abort_flag;
+};
+
+__device__ __noinline__ void gemm_wait_slow(uint64_t* bar, uint32_t parity, GemmBars* b, int32_t* status) {
+  for (uint32_t i = 0; i < kSpinLimit; i++) {
+    if (mbar_try_wait(bar, parity)) return;
+    if ((i & 255) == 255 && b->abort_flag) return;
+    if (i > 512) __nanosleep(20);
+  }
+  b->abort_flag = 1;
+  set_status(status, RELUX_ERR_TIMEOUT);
+}
+// Bounded wait: a wait that runs out records RELUX_ERR_TIMEOUT and raises the CTA's abort flag; nobody leaves a loop early.
+__device__ __forceinline__ void gemm_wait(uint64_t* bar, uint32_t parity, GemmBars* b, int32_t* status) {
+  if (!mbar_try_wait(bar, parity)) gemm_wait_slow(bar, parity, b, status);
+}
+
+// grid (tiles * split_k, ceil(M / 128)), 192 threads: warps 0-3 epilogue, warp 4 TMA producer, warp 5 MMA issuer.
+// Unit = (128-column tile of one weight, K split): D[128 x 128] f32 in tensor memory accumulates
+// A[128 x 64] (K-major) x W[64 x 128] (MN-major: the row-major weight rows as they lie in HBM) per pipeline stage.
+__global__ void __launch_bounds__(192, 1) skinny_gemm_sm100_kernel(const __grid_constant__ GemmMaps maps, const GemmParams prm) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  GemmBars* bars = reinterpret_cast<GemmBars*>(smem + kStages * (kStageA + kStageB));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x / prm.split_k, split = blockIdx.x % prm.split_k;
+  const int m0 = blockIdx.y * kTileM;
+  int j = 0;
+  while (j + 1 < prm.n_weights && tile >= prm.tile_first[j + 1]) j++;
+  const int n0 = (tile - prm.tile_first[j]) * kTileN;
+  const int steps_total = (prm.K + kTileK - 1) / kTileK;
+  const int step0 = (int)((long long)steps_total * split / prm.split_k);
+  const int step1 = (int)((long long)steps_total * (split + 1) / prm.split_k);
+  const int nsteps = step1 - step0;
+
+  if ((smem_u32(smem) & 1023u) != 0) {
+    if (threadIdx.x == 0) set_status(prm.status, RELUX_ERR_UNSUPPORTED);
+    return;
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; s++) { mbar_init(&bars->full[s], 1); mbar_init(&bars->empty[s], 1); }
+    mbar_init(&bars->done, 1);
+    bars->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0) {
+    tmem_alloc<1>(&bars->tmem_base, 128);
+    tmem_relinquish<1>();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+
+  if (warp == 4) {
+    const bool el = elect_one();
+    const CUtensorMap* wmap = &maps.w[j];
+    if (el) {
+      tma_prefetch_desc(&maps.a);
+      tma_prefetch_desc(wmap);
+    }
+    for (int i = 0; i < nsteps; i++) {
+      const int s = i % kStages, use = i / kStages;
+      if (use > 0) gemm_wait(&bars->empty[s], (use - 1) & 1, bars, prm.status);
+      if (el) {
+        uint8_t* sa = smem + s * (kStageA + kStageB);
+        uint8_t* sb = sa + kStageA;
+        const int k0 = (step0 + i) * kTileK;
+        mbar_expect_tx(&bars->full[s], kStageA + kStageB);   // out-of-range parts of a box are zero-filled and still counted
+        tma_load_2d(sa, &maps.a, k0, m0, &bars->full[s]);
+        tma_load_2d(sb, wmap, n0, k0, &bars->full[s]);
+        tma_load_2d(sb + kStageB / 2, wmap, n0 + 64, k0, &bars->full[s]);
+      }
+      __syncwarp();
+    }
+  } else if (warp == 5) {
+    const bool el = elect_one();
+    const uint32_t idesc = make_idesc_bf16(kTileM, kTileN, false, true);
+    for (int i = 0; i < nsteps; i++) {
+      const int s = i % kStages, use = i / kStages;
+      gemm_wait(&bars->full[s], use & 1, bars, prm.status);
+      tc_fence_after();
+      if (el) {
+        const uint32_t sa = smem_u32(smem + s * (kStageA + kStageB));
+        const uint64_t dA = make_desc_kmajor_sw128(sa);
+        const uint64_t dB = make_desc_mnmajor_sw128(sa + kStageA, kStageB / 2);
+#pragma unroll
+        for (int kk = 0; kk < kTileK / 16; kk++)
+          umma_ss<1>(tmem, dA + ((uint32_t)(kk * 32) >> 4), dB + ((uint32_t)(kk * 2048) >> 4), idesc, (i | kk) != 0);
+        umma_commit<1>(&bars->empty[s]);
+      }
+      __syncwarp();
+    }
+    if (el) umma_commit<1>(&bars->done);
+    __syncwarp();
+  } else {
+    // epilogue: thread = accumulator row
+    gemm_wait(&bars->done, 0, bars, prm.status);
+    tc_fence_after();
+    const int row = m0 + warp * 32 + lane;
+    const int ncols = min(kTileN, prm.n_cols[j] - n0);   // a multiple of 8
+    const bool ok = !bars->abort_flag && nsteps > 0;
+    float* dst = prm.part + ((size_t)split * prm.M + row) * prm.n_total + prm.col_first[j] + n0;
+#pragma unroll 1
+    for (int c = 0; c < kTileN; c += 32) {
+      uint32_t v[32];
+      if (ok) {
+        tmem_ld_32x32b_x32(tmem + ((uint32_t)(warp * 32) << 16) + c, v);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int q = 0; q < 32; q++) v[q] = 0u;
+      }
+      if (row < prm.M) {
+#pragma unroll
+        for (int q = 0; q < 32; q += 4)
+          if (c + q < ncols)
+            *reinterpret_cast<float4*>(dst + c + q) = make_float4(__uint_as_float(v[q]), __uint_as_float(v[q + 1]),
+                                                                  __uint_as_float(v[q + 2]), __uint_as_float(v[q + 3]));
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc<1>(tmem, 128);
+}
+
+// The reference's matmulBatched3D in its own operation order: out[m][n] = sum over k ascending of x[m][k] * w[k][n],
+// float32, multiply then add, never fused.  One thread per output element; threads of a warp read consecutive n.
+__global__ void gemm_reference_kernel(const float* __restrict__ x, const uint16_t* __restrict__ w, float* __restrict__ out, int M, int K,
+                                      int N, int out_stride, int col_first) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x, m = blockIdx.y;
+  if (n >= N || m >= M) return;
+  const float* xr = x + (size_t)m * K;
+  float acc = 0.f;
+  for (int k = 0; k < K; k++) acc = __fadd_rn(acc, __fmul_rn(xr[k], f32_from_bf16_bits(w[(size_t)k * N + n])));
+  out[(size_t)m * out_stride + col_first + n] = acc;
+}
+
+__global__ void cast_bf16_kernel(const float* __restrict__ src, uint16_t* __restrict__ dst, size_t n8) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const float4 a = reinterpret_cast<const float4*>(src)[2 * i], b = reinterpret_cast<const float4*>(src)[2 * i + 1];
+  reinterpret_cast<uint4*>(dst)[i] = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w));
+}
+
+// Sums the K splits of the projection result (fixed order, so the result does not depend on scheduling), applies the
+// decoupled RoPE (rope.go:168-176: pairs (2i, 2i+1), out0 = x0 c - x1 s, out1 = x1 c + x0 s, unfused) to q^R and k^R
+// at position len[seq] + s, and scatters the four results.  One thread per pair of adjacent columns.
+struct FinishParams {
+  const float* part;
+  int32_t split_k, M, n_total, S;
+  int32_t n_qc, n_qr, n_c, n_kr;   // H*Dh, H*dHR, dC, dHR
+  int32_t dHR;
+  const int32_t* len;              // this layer's lengths BEFORE the append
+  const int32_t* seq_ids;
+  const float* rope_cos;           // [positions][dHR/2]
+  const float* rope_sin;
+  int32_t rope_positions;
+  void* qc;                        // [M][H*Dh]  f32 or bf16
+  void* qr;                        // [M][H*dHR] f32 or bf16
+  float* c;                        // [M][dC]
+  float* kr;                       // [M][dHR]
+  int32_t q_bf16;
+  int32_t* status;
+};
+__global__ void proj_finish_kernel(const FinishParams p) {
+  const int pair = blockIdx.x * blockDim.x + threadIdx.x, m = blockIdx.y;
+  const int col = 2 * pair;
+  if (col >= p.n_total || m >= p.M) return;
+  float v0 = 0.f, v1 = 0.f;
+  for (int s = 0; s < p.split_k; s++) {
+    const float2 t = *reinterpret_cast<const float2*>(p.part + ((size_t)s * p.M + m) * p.n_total + col);
+    v0 += t.x;
+    v1 += t.y;
+  }
+  int c = col;
+  if (c < p.n_qc) {
+    if (p.q_bf16) reinterpret_cast<uint32_t*>(p.qc)[((size_t)m * p.n_qc + c) >> 1] = pack_bf16x2(v0, v1);
+    else *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.qc) + (size_t)m * p.n_qc + c) = make_float2(v0, v1);
+    return;
+  }
+  c -= p.n_qc;
+  const bool is_qr = c < p.n_qr;
+  if (!is_qr) {
+    c -= p.n_qr;
+    if (c < p.n_c) {
+      *reinterpret_cast<float2*>(p.c + (size_t)m * p.n_c + c) = make_float2(v0, v1);
+      return;
+    }
+    c -= p.n_c;
+  }
+  // rotate
+  const int i = m / p.S, s = m % p.S;
+  const int seq = p.seq_ids ? p.seq_ids[i] : i;
+  const int pos = p.len[seq] + s;
+  float r0 = v0, r1 = v1;
+  if (pos >= p.rope_positions) {
+    set_status(p.status, RELUX_ERR_OVERFLOW);   // the reference panics: position >= maxSeqLen (rope.go:160-162)
+  } else {
+    const int half = p.dHR / 2, idx = (c % p.dHR) >> 1;
+    const float cs = p.rope_cos[(size_t)pos * half + idx], sn = p.rope_sin[(size_t)pos * half + idx];
+    r0 = __fsub_rn(__fmul_rn(v0, cs), __fmul_rn(v1, sn));
+    r1 = __fadd_rn(__fmul_rn(v1, cs), __fmul_rn(v0, sn));
+  }
+  if (is_qr) {
+    if (p.q_bf16) reinterpret_cast<uint32_t*>(p.qr)[((size_t)m * p.n_qr + c) >> 1] = pack_bf16x2(r0, r1);
+    else *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.qr) + (size_t)m * p.n_qr + c) = make_float2(r0, r1);
+  } else {
+    *reinterpret_cast<float2*>(p.kr + (size_t)m * p.n_kr + c) = make_float2(r0, r1);
+  }
+}
+
+__global__ void sum_splits_kernel(const float* __restrict__ part, int split_k, size_t n4, float* __restrict__ out) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n4) return;
+  float4 acc = reinterpret_cast<const float4*>(part)[i];
+  for (int s = 1; s < split_k; s++) {
+    const float4 t = reinterpret_cast<const float4*>(part)[(size_t)s * n4 + i];
+    acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+  }
+  reinterpret_cast<float4*>(out)[i] = acc;
+}
+
+struct WeightRef {
+  const void* w;
+  int n;
+};
+
+// part[split][M][n_total] = A[M][K] x [W_0 | W_1 | ...]; returns the number of splits used.
+int32_t launch_skinny_gemm(Pool* p, const uint16_t* a_bf16, int M, int K, const WeightRef* ws, int nw, float* part, size_t part_cap_bytes,
+                           int* split_out) {
+  GemmMaps maps;
+  GemmParams g;
+  memset(&g, 0, sizeof(g));
+  if (!make_tmap_2d(&maps.a, (void*)a_bf16, (uint64_t)M, (uint64_t)K, kTileK, kTileM)) {
+    set_error("tensor map for the activations could not be encoded");
+    return RELUX_ERR_CUDA;
+  }
+  int tiles = 0, cols = 0;
+  for (int j = 0; j < nw; j++) {
+    if (!make_tmap_2d(&maps.w[j], (void*)ws[j].w, (uint64_t)K, (uint64_t)ws[j].n, 64, kTileK)) {
+      set_error("tensor map for a weight matrix could not be encoded");
+      return RELUX_ERR_CUDA;
+    }
+    g.tile_first[j] = tiles;
+    g.n_cols[j] = ws[j].n;
+    g.col_first[j] = cols;
+    tiles += (ws[j].n + kTileN - 1) / kTileN;
+    cols += ws[j].n;
+  }
+  for (int j = nw; j < kMaxWeights; j++) maps.w[j] = maps.w[0];
+  g.tile_first[nw] = tiles;
+  g.n_weights = nw;
+  g.M = M;
+  g.K = K;
+  g.n_total = cols;
+  const int mblocks = (M + kTileM - 1) / kTileM;
+  const int steps = (K + kTileK - 1) / kTileK;
+  const int sms = std::max(1, p->dev->sm_count);
+  // split K so that the units fill whole waves of SMs: cost = waves x (steps per unit + fixed cost per unit)
+  int best = 1;
+  double best_cost = 1e300;
+  const int max_split = std::min(std::min(steps, 32), (int)std::max<size_t>(1, part_cap_bytes / ((size_t)M * cols * 4)));
+  for (int s = 1; s <= max_split; s++) {
+    const long units = (long)tiles * mblocks * s;
+    const long waves = (units + sms - 1) / sms;
+    const double cost = (double)waves * ((double)(steps + s - 1) / s + 6.0);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  if (const char* ov = getenv("RELUX_GEMM_SPLIT")) best = std::max(1, std::min(max_split, atoi(ov)));   // tuning aid
+  g.split_k = best;
+  g.part = part;
+  g.status = p->d_status;
+  RELUX_CUDA_TRY(cudaFuncSetAttribute(skinny_gemm_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
+  dim3 grid(tiles * best, mblocks);
+  skinny_gemm_sm100_kernel<<<grid, 192, kGemmSmem, p->dev->stream>>>(maps, g);
+  RELUX_CUDA_TRY(cudaGetLastError());
+  count_launch(p->dev);
+  *split_out = best;
+  return RELUX_OK;
+}
+
+bool gemm_sm100_eligible(int K, const WeightRef* ws, int nw) {
+  if (getenv("RELUX_GEMM_GENERIC")) return false;
+  if (K % 8 != 0 || nw > kMaxWeights) return false;
+  for (int j = 0; j < nw; j++)
+    if (ws[j].n % 8 != 0 || ((uintptr_t)ws[j].w & 15) != 0) return false;
+  return true;
+}
+
+int32_t launch_gemm_reference(Pool* p, const float* x, int M, int K, const WeightRef* ws, int nw, float* out, int out_stride) {
+  int col = 0;
+  for (int j = 0; j < nw; j++) {
+    dim3 grid((ws[j].n + 127) / 128, M);
+    gemm_reference_kernel<<<grid, 128, 0, p->dev->stream>>>(x, (const uint16_t*)ws[j].w, out, M, K, ws[j].n, out_stride, col);
+    RELUX_CUDA_TRY(cudaGetLastError());
+    count_launch(p->dev);
+    col += ws[j].n;
+  }
+  return RELUX_OK;
+}
+
+// cos / sin tables of the decoupled RoPE exactly as NewRotaryEmbedding builds them (rope.go:59-68):
+// theta = float32(1) / float32(pow(base, 2i / headDim)), angle = float32(pos * theta), cos / sin in float64, rounded.
+int32_t ensure_rope_table(Pool* p, int dHR, float base, int positions) {
+  if (p->rope_dim == dHR && p->rope_base == base && p->rope_positions >= positions) return RELUX_OK;
+  const int half = dHR / 2;
+  std::vector<float> tab((size_t)2 * positions * half);
+  for (int pos = 0; pos < positions; pos++)
+    for (int i = 0; i < half; i++) {
+      const float theta = 1.0f / (float)std::pow((double)base, (double)(2 * i) / (double)dHR);
+      const float angle = (float)((double)pos * (double)theta);
+      tab[(size_t)pos * half + i] = (float)std::cos((double)angle);
+      tab[(size_t)positions * half + (size_t)pos * half + i] = (float)std::sin((double)angle);
+    }
+  int32_t rc = grow(p->dev, p->rope_tab, tab.size() * 4);
+  if (rc) return rc;
+  RELUX_CUDA_TRY(cudaMemcpyAsync(p->rope_tab.p, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, p->dev->stream));
+  RELUX_CUDA_TRY(cudaStreamSynchronize(p->dev->stream));   // `tab` goes out of scope
+  p->rope_dim = dHR;
+  p->rope_base = base;
+  p->rope_positions = positions;
+  return RELUX_OK;
+}
+
+}  // namespace
+
+int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a) {
+  if (!a || !a->w) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
+  const relux_pool_params& prm = p->prm;
+  if (prm.kind != RELUX_POOL_MLA) { set_error("pool kind does not match this call (MLA pool needed)"); return RELUX_ERR_INVALID_ARG; }
+  if (a->layer < 0 || a->layer >= prm.num_layers) {
+    set_error("layerIdx=%d out of range [0, %d)", a->layer, prm.num_layers);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  const relux_mla_layer_weights& w = *a->w;
+  if (!a->x || !a->out || !w.w_q || !w.w_qr || !w.w_dkv || !w.w_kr || !w.w_uk || !w.w_uv || !w.w_o) {
+    set_error("nil input, output or weight pointer");
+    return RELUX_ERR_INVALID_ARG;
+  }
+  const int H = a->num_heads, D = a->d_model, S = a->q_tokens, dC = prm.mla_dc, dHR = prm.mla_dhr;
+  if (H <= 0 || D <= 0 || S <= 0 || D % H != 0) {   // NewMLA, mla.go:69-74
+    set_error("NewMLA: dModel=%d not divisible by numHeads=%d (or non-positive sizes)", D, H);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  if (dHR % 2 != 0) { set_error("NewMLA: dHR=%d must be even for paired RoPE rotation", dHR); return RELUX_ERR_INVALID_ARG; }
+  if (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE) { set_error("bad mode"); return RELUX_ERR_INVALID_ARG; }
+  if (a->x_dtype != RELUX_DTYPE_F32) { set_error("x must be float32"); return RELUX_ERR_UNSUPPORTED; }
+  const int Dh = D / H;
+  const float rope_base = a->rope_base == 0.f ? 10000.f : a->rope_base;   // NewMLA, mla.go:78-80
+  // rows per sequence are passed explicitly: the append kernels read "no row offsets" as one row per sequence
+  SeqBatch sb;
+  if (a->n_seqs <= 0 || a->n_seqs > prm.max_seqs) {
+    set_error("n_seqs=%d outside [1, max_seqs=%d]", a->n_seqs, prm.max_seqs);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  const std::vector<int32_t> rows_per_seq((size_t)a->n_seqs, S);
+  int32_t rc = stage_batch(p, a->n_seqs, a->seq_ids, rows_per_seq.data(), 1, &sb);
+  if (rc) return rc;
+  const int M = sb.n_seqs * S;
+  if (M == 0) return RELUX_OK;
+  for (int i = 0; i < sb.n_seqs; i++) {   // the reference panics on overflow (mla_cache.go:160-164)
+    const int s = sb.seq[i];
+    const int len = p->h_len[(size_t)a->layer * prm.max_seqs + s], cap = p->seq_pages[s] * prm.page_tokens;
+    if (len + S > cap) {
+      set_error("MLACache.Append: layer %d overflow: total=%d + newLen=%d > capacity=%d (sequence %d)", a->layer, len, S, cap, s);
+      return RELUX_ERR_OVERFLOW;
+    }
+  }
+  rc = ensure_rope_table(p, dHR, rope_base, prm.max_pages_per_seq * prm.page_tokens);
+  if (rc) return rc;
+  cudaStream_t st = p->dev->stream;
+  const void* dx = nullptr;
+  rc = stage_in(p, p->in_a, a->x, (size_t)M * D * 4, a->x_mem, &dx);
+  if (rc) return rc;
+
+  const WeightRef proj[4] = {{w.w_q, H * Dh}, {w.w_qr, H * dHR}, {w.w_dkv, dC}, {w.w_kr, dHR}};
+  const int n_total = H * Dh + H * dHR + dC + dHR;
+  const WeightRef outp[1] = {{w.w_o, D}};
+  const bool fast = a->mode == RELUX_ATTN_FAST;
+  const bool mma = fast && gemm_sm100_eligible(D, proj, 4) && gemm_sm100_eligible(H * Dh, outp, 1) && n_total % 2 == 0;
+  // scratch: [activations as bf16 | split partials | q^C | q^R | c | k^R | attention output]
+  const size_t part_cap = std::max<size_t>((size_t)64 << 20, (size_t)M * std::max(n_total, D) * 4 * 4);
+  const size_t q_es = fast ? 2 : 4;
+  const size_t off_abf = 0;
+  const size_t off_part = off_abf + (((size_t)M * std::max(D, H * Dh) * 2 + 255) & ~(size_t)255);
+  const size_t off_qc = off_part + part_cap;
+  const size_t off_qr = off_qc + (((size_t)M * H * Dh * q_es + 255) & ~(size_t)255);
+  const size_t off_c = off_qr + (((size_t)M * H * dHR * q_es + 255) & ~(size_t)255);
+  const size_t off_kr = off_c + (((size_t)M * dC * 4 + 255) & ~(size_t)255);
+  const size_t off_attn = off_kr + (((size_t)M * dHR * 4 + 255) & ~(size_t)255);
+  const size_t total = off_attn + (size_t)M * H * Dh * 4;
+  rc = grow(p->dev, p->layer_buf, total);
+  if (rc) return rc;
+  char* base = (char*)p->layer_buf.p;
+  uint16_t* a_bf16 = (uint16_t*)(base + off_abf);
+  float* part = (float*)(base + off_part);
+  void* d_qc = base + off_qc;
+  void* d_qr = base + off_qr;
+  float* d_c = (float*)(base + off_c);
+  float* d_kr = (float*)(base + off_kr);
+  float* d_attn = (float*)(base + off_attn);
+
+  // 1. projections
+  int split = 1;
+  if (mma) {
+    const size_t n8 = (size_t)M * D / 8;
+    cast_bf16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>((const float*)dx, a_bf16, n8);
+    RELUX_CUDA_TRY(cudaGetLastError());
+    count_launch(p->dev);
+    rc = launch_skinny_gemm(p, a_bf16, M, D, proj, 4, part, part_cap, &split);
+  } else {
+    rc = launch_gemm_reference(p, (const float*)dx, M, D, proj, 4, part, n_total);
+  }
+  if (rc) return rc;
+  // 2. split sum + RoPE + scatter
+  FinishParams f;
+  f.part = part;
+  f.split_k = split;
+  f.M = M;
+  f.n_total = n_total;
+  f.S = S;
+  f.n_qc = H * Dh;
+  f.n_qr = H * dHR;
+  f.n_c = dC;
+  f.n_kr = dHR;
+  f.dHR = dHR;
+  f.len = p->d_len + (size_t)a->layer * prm.max_seqs;
+  f.seq_ids = sb.d_seq_ids;
+  f.rope_cos = (const float*)p->rope_tab.p;
+  f.rope_sin = f.rope_cos + (size_t)p->rope_positions * (dHR / 2);
+  f.rope_positions = p->rope_positions;
+  f.qc = d_qc;
+  f.qr = d_qr;
+  f.c = d_c;
+  f.kr = d_kr;
+  f.q_bf16 = fast ? 1 : 0;
+  f.status = p->d_status;
+  {
+    dim3 grid((n_total / 2 + 255) / 256, M);
+    proj_finish_kernel<<<grid, 256, 0, st>>>(f);
+    RELUX_CUDA_TRY(cudaGetLastError());
+    count_launch(p->dev);
+  }
+  // 3. append (advances the cursors)
+  rc = launch_mla_append(p, sb, a->layer, d_c, d_kr, RELUX_DTYPE_F32, 1);
+  if (rc) return rc;
+  for (int i = 0; i < sb.n_seqs; i++) p->h_len[(size_t)a->layer * prm.max_seqs + sb.seq[i]] += S;
+  // 4. attention over the cache, the S new rows included
+  relux_attn_args aa;
+  memset(&aa, 0, sizeof(aa));
+  aa.layer = a->layer;
+  aa.n_seqs = sb.n_seqs;
+  aa.seq_ids = a->seq_ids;
+  aa.q_tokens = S;
+  aa.extra_tokens = 0;
+  aa.causal = a->causal;
+  aa.num_heads = H;
+  aa.head_dim = Dh;
+  aa.scale = (float)(1.0 / std::sqrt((double)(Dh + dHR)));   // mla.go:344-345
+  aa.q_dtype = fast ? RELUX_DTYPE_BF16 : RELUX_DTYPE_F32;
+  aa.q_layout = RELUX_LAYOUT_TOKEN_MAJOR;
+  aa.w_uk = w.w_uk;
+  aa.w_uv = w.w_uv;
+  aa.mode = a->mode;
+  rc = fast ? launch_mla_decode_fast(p, sb, aa, d_qc, d_qr, d_attn)
+            : launch_attn_reference_mla(p, sb, aa, (const float*)d_qc, (const float*)d_qr, d_attn);
+  if (rc) return rc;
+  // 5. output projection
+  const bool direct = a->out_mem == RELUX_MEM_DEVICE;
+  float* d_out = direct ? (float*)a->out : nullptr;
+  if (!direct) {
+    rc = grow(p->dev, p->out_buf, (size_t)M * D * 4);
+    if (rc) return rc;
+    d_out = (float*)p->out_buf.p;
+  }
+  if (mma) {
+    const size_t n8 = (size_t)M * H * Dh / 8;
+    cast_bf16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(d_attn, a_bf16, n8);
+    RELUX_CUDA_TRY(cudaGetLastError());
+    count_launch(p->dev);
+    rc = launch_skinny_gemm(p, a_bf16, M, H * Dh, outp, 1, part, part_cap, &split);
+    if (rc) return rc;
+    const size_t n4 = (size_t)M * D / 4;
+    sum_splits_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(part, split, n4, d_out);
+    RELUX_CUDA_TRY(cudaGetLastError());
+    count_launch(p->dev);
+  } else {
+    rc = launch_gemm_reference(p, d_attn, M, H * Dh, outp, 1, d_out, D);
+    if (rc) return rc;
+  }
+  if (!direct) {
+    RELUX_CUDA_TRY(cudaMemcpyAsync(a->out, d_out, (size_t)M * D * 4, cudaMemcpyDeviceToHost, st));
+    RELUX_CUDA_TRY(cudaStreamSynchronize(st));
+  }
+  return RELUX_OK;
+}
+
+}  // namespace relux

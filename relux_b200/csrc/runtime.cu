@@ -134,7 +134,7 @@ static EncodeTiledFn get_encode() {
   return fn;
 }
 // 2-D bf16 tensor [rows][cols] (cols contiguous), box = box_cols x box_rows, 128-byte swizzle.
-static bool make_tmap_2d(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
+bool make_tmap_2d(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return false;
   cuuint64_t dims[2] = {cols, rows};
@@ -150,7 +150,7 @@ static void pool_free_all(Pool* p) {
   auto fr = [](void* q) { if (q) cudaFree(q); };
   fr(p->storage); fr(p->d_table); fr(p->d_len); fr(p->d_status); fr(p->d_seq_ids); fr(p->d_row_off);
   fr(p->in_a.p); fr(p->in_b.p); fr(p->out_buf.p); fr(p->q_abs.p); fr(p->part_o.p); fr(p->part_ml.p); fr(p->work.p);
-  fr(p->o_lat.p); fr(p->q_conv.p);
+  fr(p->o_lat.p); fr(p->q_conv.p); fr(p->rope_tab.p); fr(p->layer_buf.p);
   if (p->h_stage) cudaFreeHost(p->h_stage);
   if (p->stage_ev) cudaEventDestroy(p->stage_ev);
   for (auto& pair : p->ev_ring)
@@ -169,7 +169,7 @@ static int32_t check_layer(Pool* p, int layer) {
 }
 
 // Moves an activation that arrives in host memory to the device staging block.
-static int32_t stage_in(Pool* p, GrowBuf& buf, const void* src, size_t bytes, int mem, const void** dptr) {
+int32_t stage_in(Pool* p, GrowBuf& buf, const void* src, size_t bytes, int mem, const void** dptr) {
   if (mem == RELUX_MEM_DEVICE) {
     *dptr = src;
     return RELUX_OK;
@@ -818,6 +818,11 @@ API int32_t relux_gqa_verify(relux_pool_t h, const relux_attn_args* attn, const 
 API int32_t relux_mla_verify(relux_pool_t h, const relux_attn_args* attn, const relux_append_args* kv) {
   GET_POOL(h);
   return do_verify(p, attn, kv, RELUX_POOL_MLA);
+}
+
+API int32_t relux_mla_forward_cached(relux_pool_t h, const relux_mla_layer_args* a) {
+  GET_POOL(h);
+  return do_mla_layer(p, a);
 }
 
 API int32_t relux_pool_last_kernel_ms(relux_pool_t h, float* ms) {

@@ -30,7 +30,7 @@ EXPORTS = [
     "relux_cuda_event_destroy", "relux_cuda_flush_l2", "relux_pool_create", "relux_pool_destroy", "relux_pool_reset",
     "relux_pool_set_tables", "relux_seq_alloc", "relux_seq_free", "relux_seq_len", "relux_seq_set_len", "relux_pool_status",
     "relux_pool_read_rows", "relux_mla_append", "relux_gqa_append", "relux_mla_decode", "relux_gqa_decode", "relux_gqa_verify",
-    "relux_mla_verify", "relux_pool_last_kernel_ms", "relux_pool_kernel_ms_mean", "relux_gqa_decode_noalloc",
+    "relux_mla_verify", "relux_pool_last_kernel_ms", "relux_pool_kernel_ms_mean", "relux_mla_forward_cached", "relux_gqa_decode_noalloc",
 ]
 
 
@@ -53,6 +53,18 @@ class AttnArgs(C.Structure):
                 ("q_layout", C.c_int32), ("w_uk", C.c_void_p), ("w_uv", C.c_void_p), ("out", C.c_void_p),
                 ("out_dtype", C.c_int32), ("out_mem", C.c_int32), ("out_layout", C.c_int32), ("mode", C.c_int32),
                 ("reserved", C.c_int32 * 5)]
+
+
+class MlaLayerWeights(C.Structure):
+    _fields_ = [("w_q", C.c_void_p), ("w_qr", C.c_void_p), ("w_dkv", C.c_void_p), ("w_kr", C.c_void_p), ("w_uk", C.c_void_p),
+                ("w_uv", C.c_void_p), ("w_o", C.c_void_p)]
+
+
+class MlaLayerArgs(C.Structure):
+    _fields_ = [("layer", C.c_int32), ("n_seqs", C.c_int32), ("seq_ids", C.c_void_p), ("q_tokens", C.c_int32),
+                ("causal", C.c_int32), ("d_model", C.c_int32), ("num_heads", C.c_int32), ("rope_base", C.c_float),
+                ("mode", C.c_int32), ("x", C.c_void_p), ("x_dtype", C.c_int32), ("x_mem", C.c_int32), ("out", C.c_void_p),
+                ("out_mem", C.c_int32), ("reserved", C.c_int32 * 3), ("w", C.POINTER(MlaLayerWeights))]
 
 
 class ReluxCudaError(RuntimeError):
@@ -113,6 +125,7 @@ def load():
             getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AttnArgs)]
         for n in ("relux_gqa_verify", "relux_mla_verify"):
             getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AttnArgs), C.POINTER(AppendArgs)]
+        L.relux_mla_forward_cached.argtypes = [C.c_void_p, C.POINTER(MlaLayerArgs)]
         L.relux_pool_last_kernel_ms.argtypes = [C.c_void_p, C.POINTER(C.c_float)]
         L.relux_pool_kernel_ms_mean.argtypes = [C.c_void_p, C.c_int32, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
         L.relux_cuda_launch_count.argtypes = [C.c_void_p, C.POINTER(C.c_int64)]

@@ -1,0 +1,206 @@
+"""MLA layer step on the GPU (relux_mla_forward_cached) against the oracle's restatement of MLA.forwardCached
+(mla.go:272-397) composed from its pinned pieces: matmul, RoPE tables and rotation, bf16 cache rows, attention.
+
+RELUX_ATTN_REFERENCE must match BIT FOR BIT (outputs and the rows that land in the cache); RELUX_ATTN_FAST
+(activations rounded to bf16 for the tensor cores, exact exp2 softmax) within tolerance."""
+import numpy as np
+import pytest
+
+from tests.helpers import permuted_tables
+
+pytestmark = pytest.mark.gpu
+
+WEIGHTS = ("w_q", "w_qr", "w_dkv", "w_kr", "w_uk", "w_uv", "w_o")
+
+
+@pytest.fixture(scope="module")
+def dev():
+    import relux_b200 as rb
+    d = rb.Device(0)
+    yield d
+    d.close()
+
+
+def make_weights(oracle, rng, D, H, dC, dHR):
+    Dh = D // H
+    shapes = {"w_q": (D, H * Dh), "w_qr": (D, H * dHR), "w_dkv": (D, dC), "w_kr": (D, dHR), "w_uk": (dC, H * Dh),
+              "w_uv": (dC, H * Dh), "w_o": (H * Dh, D)}
+    out = {}
+    for k in WEIGHTS:
+        r, c = shapes[k]
+        w = rng.standard_normal((r, c), dtype=np.float32)
+        w *= np.float32(1.0 / np.sqrt(r))      # the spread of NewMLA's initialiser (mla.go:86-95)
+        out[k] = oracle.bf16_from_f32(w)
+    return out
+
+
+class OracleLayer:
+    """Batch of independent sequences, one MLA layer, INTENDED semantics, bf16 cache rows."""
+
+    def __init__(self, oracle, W, D, H, dC, dHR, rope_base, max_pos, causal):
+        self.o, self.W, self.D, self.H, self.dC, self.dHR, self.causal = oracle, W, D, H, dC, dHR, causal
+        self.Wf = {k: oracle.f32_from_bf16(v) for k, v in W.items() if k not in ("w_uk", "w_uv")}
+        self.rope = oracle.Rope(dHR, rope_base, max_pos)
+        self.c, self.kr = [], []   # per sequence: bf16 bits [T, dC], [T, dHR]
+
+    def add_sequences(self, n):
+        for _ in range(n):
+            self.c.append(np.zeros((0, self.dC), np.uint16))
+            self.kr.append(np.zeros((0, self.dHR), np.uint16))
+
+    def step(self, x):
+        o, H, dC, dHR = self.o, self.H, self.dC, self.dHR
+        B, S, D = x.shape
+        Dh = D // H
+        x2 = np.ascontiguousarray(x.reshape(B * S, D))
+        qc = o.matmul(x2, self.Wf["w_q"]).reshape(B, S, H, Dh)
+        qr = o.matmul(x2, self.Wf["w_qr"]).reshape(B, S, H, dHR)
+        c = o.matmul(x2, self.Wf["w_dkv"]).reshape(B, S, dC)
+        kr = o.matmul(x2, self.Wf["w_kr"]).reshape(B, S, dHR)
+        qr_rot = np.empty_like(qr)
+        for b in range(B):
+            start = self.c[b].shape[0]
+            qh = np.ascontiguousarray(qr[b].transpose(1, 0, 2))            # [H, S, dHR] like rearrangeBSNH
+            qr_rot[b] = self.rope.apply(qh, start, intended_positions=True).transpose(1, 0, 2)
+            kb = self.rope.apply(np.ascontiguousarray(kr[b]), start, intended_positions=True)
+            self.c[b] = np.concatenate([self.c[b], o.bf16_from_f32(c[b])])
+            self.kr[b] = np.concatenate([self.kr[b], o.bf16_from_f32(kb)])
+        lens = [a.shape[0] for a in self.c]
+        Tm = max(lens)
+        ck = np.zeros((B, Tm, dC), np.uint16)
+        kk = np.zeros((B, Tm, dHR), np.uint16)
+        for b in range(B):
+            ck[b, :lens[b]] = self.c[b]
+            kk[b, :lens[b]] = self.kr[b]
+        scale = float(np.float32(1.0 / np.sqrt(float(Dh + dHR))))
+        attn = o.mla_attend(ck, kk, lens, qc, qr_rot, self.W["w_uk"], self.W["w_uv"], scale, causal=self.causal)
+        return o.matmul(np.ascontiguousarray(attn.reshape(B * S, H * Dh)), self.Wf["w_o"]).reshape(B, S, D)
+
+
+def build_pool(dev, rng, B, capacity, dC, dHR, P=64):
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    pages_per = (capacity + P - 1) // P
+    pool = rb.Pool(dev, L.POOL_MLA, 1, B * pages_per, P, B, pages_per, dC=dC, dHR=dHR)
+    pool.set_tables(permuted_tables(rng, B, pages_per))
+    return pool
+
+
+def prefill(rng, oracle, pool, ol, lens, dC, dHR):
+    """Seeds caches of different lengths with random rows (the same bf16 rows on both sides)."""
+    B = len(lens)
+    c = oracle.bf16_from_f32(rng.standard_normal((int(np.sum(lens)), dC), dtype=np.float32))
+    r = oracle.bf16_from_f32(rng.standard_normal((int(np.sum(lens)), dHR), dtype=np.float32))
+    if int(np.sum(lens)) > 0:
+        pool.append(0, c, r, B, n_new=np.asarray(lens, np.int32))
+    o = 0
+    for b, n in enumerate(lens):
+        ol.c[b] = c[o:o + n].copy()
+        ol.kr[b] = r[o:o + n].copy()
+        o += n
+
+
+def run_steps(dev, oracle, seed, D, H, dC, dHR, lens, steps, mode, causal=True, rope_base=10000.0, capacity=256):
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(seed)
+    B = len(lens)
+    W = make_weights(oracle, rng, D, H, dC, dHR)
+    dW = {k: dev.upload(v) for k, v in W.items()}
+    pool = build_pool(dev, rng, B, capacity, dC, dHR)
+    ol = OracleLayer(oracle, W, D, H, dC, dHR, rope_base, capacity, causal)
+    ol.add_sequences(B)
+    prefill(rng, oracle, pool, ol, lens, dC, dHR)
+    results = []
+    for S in steps:
+        x = rng.standard_normal((B, S, D), dtype=np.float32)
+        got = np.empty((B, S, D), np.float32)
+        pool.forward_cached(0, B, x, got, dW, D, H, q_tokens=S, causal=causal, rope_base=rope_base, mode=mode)
+        ref = ol.step(x)
+        results.append((got, ref))
+    assert pool.status() == 0
+    caches = []
+    for b in range(B):
+        n = ol.c[b].shape[0]
+        assert pool.seq_len(0, b) == n
+        gc, gr = pool.read_rows(0, b, 0, n)
+        caches.append((gc, gr, ol.c[b], ol.kr[b]))
+    pool.destroy()
+    for v in dW.values():
+        v.free()
+    return results, caches
+
+
+def test_layer_reference_mode_is_bit_exact_small(dev, oracle):
+    """config-2 layer shapes (dModel 256, 8 heads, latent 64, rope 16); ragged caches, decode and multi-token steps."""
+    from relux_b200 import lib as L
+    results, caches = run_steps(dev, oracle, 11, 256, 8, 64, 16, [0, 5, 70], [1, 3, 1], L.ATTN_REFERENCE)
+    for got, ref in results:
+        assert np.array_equal(got, ref)
+    for gc, gr, rc, rr in caches:
+        assert np.array_equal(gc, rc) and np.array_equal(gr, rr)
+
+
+def _close(oracle, got, ref, what):
+    rel = np.linalg.norm(got.astype(np.float64) - ref) / np.linalg.norm(ref)
+    err = np.abs(got - ref)
+    assert np.isfinite(got).all()
+    assert rel <= 2e-2, "%s: relative error %g" % (what, rel)
+    assert err.max() <= 2e-2 * max(1.0, float(np.abs(ref).max())), "%s: max-abs %g" % (what, err.max())
+    return rel
+
+
+def test_layer_fast_mode_small(dev, oracle):
+    """Same shapes through the tensor-core projections (K = 256: four pipeline steps, column tiles narrower than a box)."""
+    from relux_b200 import lib as L
+    with oracle.exact_exp():
+        results, caches = run_steps(dev, oracle, 12, 256, 8, 64, 16, [1, 64, 129], [1, 2, 1], L.ATTN_FAST)
+    for i, (got, ref) in enumerate(results):
+        _close(oracle, got, ref, "step %d" % i)
+    for gc, gr, rc, rr in caches:   # rows computed from bf16-rounded activations: close, not identical
+        d = np.abs(oracle.f32_from_bf16(gc) - oracle.f32_from_bf16(rc))
+        assert d.max() <= 0.05 and d.mean() <= 5e-3
+        d = np.abs(oracle.f32_from_bf16(gr) - oracle.f32_from_bf16(rr))
+        assert d.max() <= 0.05 and d.mean() <= 5e-3
+
+
+def test_layer_fast_mode_matches_reference_mode_on_device(dev, oracle):
+    """FAST and REFERENCE on the same inputs agree within the bf16 tolerance (no oracle involved: the two device paths)."""
+    from relux_b200 import lib as L
+    a, _ = run_steps(dev, oracle, 13, 256, 8, 64, 16, [17, 40], [1, 1], L.ATTN_FAST)
+    b, _ = run_steps(dev, oracle, 13, 256, 8, 64, 16, [17, 40], [1, 1], L.ATTN_REFERENCE)
+    for (ga, _), (gb, _) in zip(a, b):
+        assert np.linalg.norm(ga - gb) / np.linalg.norm(gb) <= 3e-2
+
+
+def test_layer_fast_mode_tcgen05_shapes(dev, oracle):
+    """128 heads x 128, latent 512, rope 64 (dModel 16384): split-K tensor-core projections feeding the tcgen05 decode."""
+    from relux_b200 import lib as L
+    with oracle.exact_exp():
+        results, _ = run_steps(dev, oracle, 14, 16384, 128, 512, 64, [130, 300], [1], L.ATTN_FAST, capacity=512)
+    for i, (got, ref) in enumerate(results):
+        _close(oracle, got, ref, "step %d" % i)
+
+
+def test_layer_errors(dev, oracle):
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(1)
+    W = make_weights(oracle, rng, 256, 8, 64, 16)
+    dW = {k: dev.upload(v) for k, v in W.items()}
+    pool = build_pool(dev, rng, 2, 64, 64, 16)
+    x = rng.standard_normal((2, 1, 256), dtype=np.float32)
+    out = np.empty_like(x)
+    with pytest.raises(L.ReluxCudaError) as e:      # dModel not divisible by numHeads (NewMLA panics, mla.go:72-74)
+        pool.forward_cached(0, 2, x, out, dW, 256, 7)
+    assert e.value.code == L.ERR_INVALID_ARG
+    with pytest.raises(L.ReluxCudaError) as e:      # layer out of range
+        pool.forward_cached(3, 2, x, out, dW, 256, 8)
+    assert e.value.code == L.ERR_INVALID_ARG
+    pool.append(0, oracle.bf16_from_f32(rng.standard_normal((128, 64), dtype=np.float32)),
+                oracle.bf16_from_f32(rng.standard_normal((128, 16), dtype=np.float32)), 2, n_new=np.asarray([64, 64], np.int32))
+    with pytest.raises(L.ReluxCudaError) as e:      # capacity 64 is full (MLACache.Append panics, mla_cache.go:160-164)
+        pool.forward_cached(0, 2, x, out, dW, 256, 8)
+    assert e.value.code == L.ERR_OVERFLOW
+    pool.destroy()
+    for v in dW.values():
+        v.free()
