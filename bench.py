@@ -28,6 +28,9 @@ WORKLOADS = {
     # name: (kind, batch per GPU, context, heads, head_dim, dC, dHR)
     "mla_decode_b64_ctx32k": dict(kind="mla", B=64, ctx=32768, H=128, Dh=128, dC=512, dHR=64),
     "mla_decode_b64_ctx4k": dict(kind="mla", B=64, ctx=4096, H=128, Dh=128, dC=512, dHR=64),
+    # the whole attention layer step on the device (projections + RoPE + append + decode + output projection)
+    "mla_layer_b64_ctx32k": dict(kind="mla", B=64, ctx=32768, H=128, Dh=128, dC=512, dHR=64, layer=True),
+    "mla_layer_b16_ctx4k": dict(kind="mla", B=16, ctx=4096, H=128, Dh=128, dC=512, dHR=64, layer=True),
     # small enough for an ncu --set full capture (302 MB of cache rows, still larger than the 126 MB L2)
     "mla_decode_b16_ctx16k": dict(kind="mla", B=16, ctx=16384, H=128, Dh=128, dC=512, dHR=64),
     # GQA flash-decode + speculative verify: 4 draft tokens per step, accepted prefix uniform in 1..4
@@ -174,6 +177,33 @@ def run_mla(args, w, world, rank, local, dist):
         pool.append(0, pins[0].array, pins[1].array, B)
         pool.decode(0, B, pins[2].array, pin_out.array, H, Dh, scale, q_rope=pins[3].array, w_uk=d_wuk, w_uv=d_wuv)
 
+    layer = bool(w.get("layer"))
+    if layer:
+        # layer step: x [B, 1, dModel] in, [B, 1, dModel] out; dModel = H * Dh like NewMLA.  Weights N(0, 1/in) -> bf16,
+        # generated as one 1024-column block repeated along the output dimension (the values do not matter to the timing)
+        D = H * Dh
+
+        def weight(rows, cols):
+            blk_cols = min(cols, 1024)
+            blk_w = orc.bf16_from_f32(rng.standard_normal((rows, blk_cols), dtype=np.float32) * np.float32(1.0 / np.sqrt(rows)))
+            return dev.upload(np.ascontiguousarray(np.tile(blk_w, (1, cols // blk_cols))))
+
+        dW = {"w_q": weight(D, H * Dh), "w_qr": weight(D, H * dHR), "w_dkv": weight(D, dC), "w_kr": weight(D, dHR),
+              "w_uk": d_wuk, "w_uv": d_wuv, "w_o": weight(H * Dh, D)}
+        weight_bytes = 2 * (D * (H * Dh + H * dHR + dC + dHR) + H * Dh * D)
+        x_host = rng.standard_normal((B, 1, D), dtype=np.float32)
+        d_x = dev.upload(x_host)
+        d_y = dev.alloc(B * D * 4, L.DTYPE_F32)
+        pin_x = dev.pinned(x_host.shape, np.float32)
+        pin_x.array[...] = x_host
+        pin_y = dev.pinned(x_host.shape, np.float32)
+
+        def step_resident():
+            pool.forward_cached(0, B, d_x, d_y, dW, D, H)
+
+        def step_e2e():
+            pool.forward_cached(0, B, pin_x.array, pin_y.array, dW, D, H)
+
     e0, e1 = dev.event(), dev.event()
 
     def timed(fn, steps, warmup, sampler=None):
@@ -217,8 +247,10 @@ def run_mla(args, w, world, rank, local, dist):
     e2e = tokens * args.steps / (ms_e2e * 1e-3)
     h2d = sum(a.nbytes for a in (new_c, new_r, qc, qr))
     d2h = pin_out.array.nbytes
+    if layer:
+        h2d, d2h = x_host.nbytes, x_host.nbytes
     line = {
-        "metric": "mla_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "metric": "mla_layer_decode_tokens_per_s" if layer else "mla_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": args.workload, "batch_per_gpu": B, "context": ctx0, "heads": H, "latent": dC, "rope": dHR,
@@ -237,8 +269,17 @@ def run_mla(args, w, world, rank, local, dist):
         "gpu_launches": launches, "clocks": clocks,
         "kv_read_gbs_whole_step": alg_bytes * world / (ms_res / args.steps * 1e-3) / 1e9,
     }
+    if layer:
+        proj_ms, proj_n = pool.mean_projection_ms(args.steps)
+        in_bytes = 2 * H * Dh * (H * Dh + H * dHR + dC + dHR)
+        line["projections"] = {"kernel": "skinny_gemm_sm100_kernel (x . [W_Q | W_QR | W_DKV | W_KR])", "kernel_ms": proj_ms,
+                               "launches_timed": proj_n, "weight_bytes_per_launch": in_bytes,
+                               "achieved_gbs": in_bytes / (proj_ms * 1e-3) / 1e9, "frac_of_measured_hbm": in_bytes / (proj_ms * 1e-3) / 1e9 / peak,
+                               "weight_bytes_per_step_all_projections": weight_bytes}
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_bounded(w)
+        if layer:
+            line["cpu_baseline"]["sample"] += "; attention part of the layer only (the projections are not included)"
     for b in (d_new_c, d_new_r, d_qc, d_qr, d_out, d_wuk, d_wuv):
         b.free()
     pool.destroy()

@@ -290,6 +290,10 @@ int32_t relux_pool_last_kernel_ms(relux_pool_t pool, float* ms);
  * Measurement aid: no counterpart in the reference. */
 int32_t relux_pool_kernel_ms_mean(relux_pool_t pool, int32_t last_n, float* mean_ms, int32_t* counted);
 
+/* Same for the input-projection launch (x . [W_Q | W_QR | W_DKV | W_KR]) of the most recent
+ * relux_mla_forward_cached calls on this pool.  Measurement aid: no counterpart in the reference. */
+int32_t relux_pool_projection_ms_mean(relux_pool_t pool, int32_t last_n, float* mean_ms, int32_t* counted);
+
 #ifdef __cplusplus
 }
 #endif

@@ -295,6 +295,12 @@ class Pool:
         L.check(self.lib.relux_pool_last_kernel_ms(self.h, C.byref(ms)))
         return ms.value
 
+    def mean_projection_ms(self, last_n):
+        """(mean device time of the input-projection GEMM over the last `last_n` forward_cached calls, calls counted)."""
+        ms, n = C.c_float(), C.c_int32()
+        L.check(self.lib.relux_pool_projection_ms_mean(self.h, int(last_n), C.byref(ms), C.byref(n)))
+        return ms.value, n.value
+
     def mean_kernel_ms(self, last_n):
         """(mean device time of the attention kernel over the last `last_n` decode / verify calls, calls counted)."""
         ms, n = C.c_float(), C.c_int32()

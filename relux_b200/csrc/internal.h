@@ -90,6 +90,8 @@ struct Pool {
   static constexpr int kTimeRing = 256;
   cudaEvent_t ev_ring[kTimeRing][2] = {};
   uint64_t timed_calls = 0;
+  cudaEvent_t proj_ring[kTimeRing][2] = {};   // same, around the input-projection GEMM of the layer step
+  uint64_t proj_calls = 0;
   cudaEvent_t ev_begin() const { return ev_ring[timed_calls % kTimeRing][0]; }
   cudaEvent_t ev_end() const { return ev_ring[timed_calls % kTimeRing][1]; }
 };

@@ -461,11 +461,17 @@ int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a) {
     cast_bf16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>((const float*)dx, a_bf16, n8);
     RELUX_CUDA_TRY(cudaGetLastError());
     count_launch(p->dev);
+    RELUX_CUDA_TRY(cudaEventRecord(p->proj_ring[p->proj_calls % Pool::kTimeRing][0], st));
     rc = launch_skinny_gemm(p, a_bf16, M, D, proj, 4, part, part_cap, &split);
+    if (rc) return rc;
+    RELUX_CUDA_TRY(cudaEventRecord(p->proj_ring[p->proj_calls % Pool::kTimeRing][1], st));
   } else {
+    RELUX_CUDA_TRY(cudaEventRecord(p->proj_ring[p->proj_calls % Pool::kTimeRing][0], st));
     rc = launch_gemm_reference(p, (const float*)dx, M, D, proj, 4, part, n_total);
+    if (rc) return rc;
+    RELUX_CUDA_TRY(cudaEventRecord(p->proj_ring[p->proj_calls % Pool::kTimeRing][1], st));
   }
-  if (rc) return rc;
+  p->proj_calls++;
   // 2. split sum + RoPE + scatter
   FinishParams f;
   f.part = part;

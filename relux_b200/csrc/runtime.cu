@@ -156,6 +156,9 @@ static void pool_free_all(Pool* p) {
   for (auto& pair : p->ev_ring)
     for (cudaEvent_t ev : pair)
       if (ev) cudaEventDestroy(ev);
+  for (auto& pair : p->proj_ring)
+    for (cudaEvent_t ev : pair)
+      if (ev) cudaEventDestroy(ev);
   p->magic = 0;
   delete p;
 }
@@ -587,6 +590,10 @@ API int32_t relux_pool_create(relux_device_t h, const relux_pool_params* prm, re
   for (auto& pair : p->ev_ring)
     for (cudaEvent_t& ev : pair)
       if (e == cudaSuccess) e = cudaEventCreate(&ev);
+  if (prm->kind == RELUX_POOL_MLA)
+    for (auto& pair : p->proj_ring)
+      for (cudaEvent_t& ev : pair)
+        if (e == cudaSuccess) e = cudaEventCreate(&ev);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_table, 0xFF, table_n * 4, dev->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_len, 0, len_n * 4, dev->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_status, 0, 8, dev->stream);
@@ -835,14 +842,11 @@ API int32_t relux_pool_last_kernel_ms(relux_pool_t h, float* ms) {
   return RELUX_OK;
 }
 
-API int32_t relux_pool_kernel_ms_mean(relux_pool_t h, int32_t last_n, float* mean_ms, int32_t* counted) {
-  GET_POOL(h);
-  if (!mean_ms || last_n <= 0) return RELUX_ERR_INVALID_ARG;
-  if (!p->timed_calls) { set_error("no attention kernel has been timed on this pool yet"); return RELUX_ERR_INVALID_ARG; }
-  const uint64_t n = std::min<uint64_t>(std::min<uint64_t>((uint64_t)last_n, p->timed_calls), Pool::kTimeRing);
+static int32_t ring_mean(cudaEvent_t (*ring)[2], uint64_t calls, int32_t last_n, float* mean_ms, int32_t* counted) {
+  const uint64_t n = std::min<uint64_t>(std::min<uint64_t>((uint64_t)last_n, calls), Pool::kTimeRing);
   double sum = 0.0;
   for (uint64_t i = 0; i < n; i++) {
-    const auto& pair = p->ev_ring[(p->timed_calls - 1 - i) % Pool::kTimeRing];
+    cudaEvent_t* pair = ring[(calls - 1 - i) % Pool::kTimeRing];
     float ms = 0.f;
     RELUX_CUDA_TRY(cudaEventSynchronize(pair[1]));
     RELUX_CUDA_TRY(cudaEventElapsedTime(&ms, pair[0], pair[1]));
@@ -851,4 +855,18 @@ API int32_t relux_pool_kernel_ms_mean(relux_pool_t h, int32_t last_n, float* mea
   *mean_ms = (float)(sum / (double)n);
   if (counted) *counted = (int32_t)n;
   return RELUX_OK;
+}
+
+API int32_t relux_pool_kernel_ms_mean(relux_pool_t h, int32_t last_n, float* mean_ms, int32_t* counted) {
+  GET_POOL(h);
+  if (!mean_ms || last_n <= 0) return RELUX_ERR_INVALID_ARG;
+  if (!p->timed_calls) { set_error("no attention kernel has been timed on this pool yet"); return RELUX_ERR_INVALID_ARG; }
+  return ring_mean(p->ev_ring, p->timed_calls, last_n, mean_ms, counted);
+}
+
+API int32_t relux_pool_projection_ms_mean(relux_pool_t h, int32_t last_n, float* mean_ms, int32_t* counted) {
+  GET_POOL(h);
+  if (!mean_ms || last_n <= 0) return RELUX_ERR_INVALID_ARG;
+  if (!p->proj_calls) { set_error("no layer step has run on this pool yet"); return RELUX_ERR_INVALID_ARG; }
+  return ring_mean(p->proj_ring, p->proj_calls, last_n, mean_ms, counted);
 }
