@@ -231,3 +231,45 @@ def test_head_major_layout_round_trip(dev, oracle):
     ref = oracle.gqa_attend(Kl, Vl, [20], q.transpose(0, 2, 1, 3), scale, causal=True)
     assert np.array_equal(out, ref.transpose(0, 2, 1, 3))
     c.close()
+
+
+def _mla_v2_case(dev, oracle, seed, ctx, S, causal=True):
+    rng = np.random.default_rng(seed)
+    H, Dh, dC, dHR = 128, 128, 512, 64
+    B = len(ctx)
+    pool, cl, rl = build_mla(dev, oracle, rng, ctx, dC, dHR)
+    wuk = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02)
+    wuv = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02)
+    d_wuk, d_wuv = dev.upload(wuk), dev.upload(wuv)
+    qc = rng.standard_normal((B, S, H, Dh)).astype(np.float32)
+    qr = rng.standard_normal((B, S, H, dHR)).astype(np.float32)
+    out = np.empty_like(qc)
+    scale = float(1.0 / np.sqrt(Dh + dHR))
+    pool.decode(0, B, qc, out, H, Dh, scale, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv, q_tokens=S, causal=causal)
+    with oracle.exact_exp():
+        ref = oracle.mla_attend(cl, rl, ctx, qc, qr, wuk, wuv, scale, causal=causal, absorbed=True)
+    assert pool.status() == 0
+    pool.destroy(); d_wuk.free(); d_wuv.free()
+    return out, ref
+
+
+def test_mla_stream_partition_many_sequences(dev, oracle):
+    """300 short sequences (more than one 256-thread pass of the partition builder, several sequences per worker
+    range, odd page counts) on the tcgen05 path."""
+    rng = np.random.default_rng(21)
+    ctx = [int(x) for x in rng.integers(1, 200, 300)]
+    out, ref = _mla_v2_case(dev, oracle, 22, ctx, 1)
+    check_attention(out, ref, "mla stream 300 seqs", max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+
+
+def test_mla_stream_partition_one_long_sequence(dev, oracle):
+    """One sequence cut over all workers: as many split-KV partials as CTA pairs."""
+    out, ref = _mla_v2_case(dev, oracle, 23, [9000], 1)
+    check_attention(out, ref, "mla stream one long sequence", max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+
+
+@pytest.mark.parametrize("S", [3, 8, 9])
+def test_mla_query_token_counts(dev, oracle, S):
+    """S <= 8 query tokens run as S workers side by side on a range; more than 8 fall back to one grid row per token."""
+    out, ref = _mla_v2_case(dev, oracle, 24 + S, [S, 70, 130 + S, 777], S)
+    check_attention(out, ref, "mla S=%d" % S, max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
