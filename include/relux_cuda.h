@@ -259,6 +259,41 @@ typedef struct relux_mla_layer_args {
 } relux_mla_layer_args;
 int32_t relux_mla_forward_cached(relux_pool_t pool, const relux_mla_layer_args* args);
 
+/* One GQA attention layer step, device-resident end to end: MHA.forwardCached (mha.go:245-369) for a batch of
+ * independent sequences.  x [n_seqs][q_tokens][d_model] float32 is projected with Wq [d_model][num_heads*head_dim],
+ * Wk and Wv [d_model][num_kv_heads*head_dim] (mha.go:251-258; bf16, row-major [in][out], on the device); with
+ * rope != 0 q and k are rotated at position cached_len + s (mha.go:272-282, tables as rope.go:59-68); k / v are
+ * written to this pool's layer (advance != 0: cursors move by q_tokens, decode / prefill; advance = 0: the rows stay
+ * past the cursor, the speculative verify step, commit the accepted prefix with relux_seq_set_len); attention with
+ * scale 1/sqrt(head_dim) (mha.go:319), causal inside the q_tokens new rows; out = o Wo [n_seqs][q_tokens][d_model]
+ * float32.  head_dim = d_model / num_heads must equal the pool's, num_kv_heads is the pool's. */
+typedef struct relux_gqa_layer_weights {
+  const void* w_q;   /* device bf16 [d_model][num_heads*head_dim] */
+  const void* w_k;   /* device bf16 [d_model][num_kv_heads*head_dim] */
+  const void* w_v;   /* device bf16 [d_model][num_kv_heads*head_dim] */
+  const void* w_o;   /* device bf16 [num_heads*head_dim][d_model] */
+} relux_gqa_layer_weights;
+typedef struct relux_gqa_layer_args {
+  int32_t layer;
+  int32_t n_seqs;
+  const int32_t* seq_ids;   /* host [n_seqs]; NULL = 0..n_seqs-1 */
+  int32_t q_tokens;
+  int32_t causal;
+  int32_t d_model;
+  int32_t num_heads;
+  int32_t rope;             /* 0: the layer has no rotary embedding (m.rope == nil) */
+  float rope_base;          /* 0 = 10000 */
+  int32_t advance;
+  int32_t mode;             /* RELUX_ATTN_FAST | RELUX_ATTN_REFERENCE */
+  const void* x;
+  int32_t x_dtype, x_mem;
+  void* out;
+  int32_t out_mem;
+  int32_t reserved[3];
+  const relux_gqa_layer_weights* w;
+} relux_gqa_layer_args;
+int32_t relux_gqa_forward_cached(relux_pool_t pool, const relux_gqa_layer_args* args);
+
 /* GQA flash-decode / verify that allocates nothing.  It has no counterpart in the reference; it exists for callers
  * that may not allocate device memory at the moment they decode: a serving loop whose memory budget has been handed
  * out completely (so a late cudaMalloc can fail or stall the whole device while it synchronises), or code running

@@ -279,7 +279,26 @@ class Pool:
         L.check(fn(self.h, C.byref(at), C.byref(ap)))
 
     def forward_cached(self, layer, n_seqs, x, out, weights, d_model, num_heads, q_tokens=1, causal=True, rope_base=0.0,
-                       mode=L.ATTN_FAST, seq_ids=None):
+                       mode=L.ATTN_FAST, seq_ids=None, rope=True, advance=True):
+        if self.kind == L.POOL_GQA:
+            return self._gqa_forward_cached(layer, n_seqs, x, out, weights, d_model, num_heads, q_tokens, causal, rope_base, mode,
+                                            seq_ids, rope, advance)
+        return self._mla_forward_cached(layer, n_seqs, x, out, weights, d_model, num_heads, q_tokens, causal, rope_base, mode, seq_ids)
+
+    def _gqa_forward_cached(self, layer, n_seqs, x, out, weights, d_model, num_heads, q_tokens, causal, rope_base, mode, seq_ids,
+                            rope, advance):
+        """One GQA layer step (MHA.forwardCached, mha.go:245-369): x [n_seqs, q_tokens, d_model] float32 -> out of the
+        same shape; `weights` maps w_q, w_k, w_v, w_o to device buffers of bf16 bits in the reference's [in, out] layout.
+        advance=False leaves the q_tokens new rows past the cursor (speculative verify)."""
+        ids = None if seq_ids is None else np.ascontiguousarray(seq_ids, dtype=np.int32)
+        w = L.GqaLayerWeights(**{k: _ptr(weights[k]) for k in ("w_q", "w_k", "w_v", "w_o")})
+        args = L.GqaLayerArgs(layer=layer, n_seqs=n_seqs, seq_ids=_ptr(ids), q_tokens=q_tokens, causal=int(causal), d_model=d_model,
+                              num_heads=num_heads, rope=int(rope), rope_base=float(rope_base), advance=int(advance), mode=mode,
+                              x=_ptr(x), x_dtype=_dtype_flag(x), x_mem=_mem(x), out=_ptr(out), out_mem=_mem(out), w=C.pointer(w))
+        L.check(self.lib.relux_gqa_forward_cached(self.h, C.byref(args)))
+
+    def _mla_forward_cached(self, layer, n_seqs, x, out, weights, d_model, num_heads, q_tokens=1, causal=True, rope_base=0.0,
+                            mode=L.ATTN_FAST, seq_ids=None):
         """One MLA layer step (MLA.forwardCached, mla.go:272-397): x [n_seqs, q_tokens, d_model] float32 ->
         out [n_seqs, q_tokens, d_model] float32; `weights` maps w_q, w_qr, w_dkv, w_kr, w_uk, w_uv, w_o to device
         buffers of bf16 bits in the reference's [in, out] layout.  Appends q_tokens rows per sequence."""

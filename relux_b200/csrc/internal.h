@@ -81,7 +81,7 @@ struct Pool {
   CUtensorMap tmap_gqa{};   // 2-D [rows][D],      box 64 x 64, 128-byte swizzle
   bool has_tmap = false;
   bool mla_blocked = false;   // MLA pages stored as 64-column blocks (see mla_page_off)
-  // layer-level step (mla_layer.cu): RoPE tables [cos | sin][positions][dHR / 2] and the step's scratch block
+  // layer-level step (layer_step.cu): RoPE tables [cos | sin][positions][dHR / 2] and the step's scratch block
   GrowBuf rope_tab, layer_buf;
   int rope_dim = 0, rope_positions = 0;
   float rope_base = 0.f;
@@ -134,6 +134,7 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
                                void* d_out);
 
 int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a);
+int32_t do_gqa_layer(Pool* p, const relux_gqa_layer_args* a);
 
 inline void count_launch(Device* d, int n = 1) { d->launches += n; }
 

@@ -1,10 +1,13 @@
-// One MLA attention layer step on the device: the work of MLA.forwardCached (internal/transformer/mla.go:272-397)
-// either side of the cached attention, so that a caller hands over the layer input x and gets the layer output back.
+// Whole attention layer steps on the device: the work of MLA.forwardCached (internal/transformer/mla.go:272-397) and
+// MHA.forwardCached (mha.go:245-369) either side of the cached attention, so that a caller hands over the layer
+// input x and gets the layer output back.  For MLA:
 //   1. projections  q^C = x W_Q, q^R = x W_QR, c^KV = x W_DKV, k^R = x W_KR          mla.go:285-288
 //   2. decoupled RoPE on q^R and k^R at position cacheLen + s                          mla.go:297-307, rope.go:130-180
 //   3. append (c^KV, k^R) to the paged latent cache                                    mla.go:309-314
 //   4. absorbed attention over the cache (the kernels of mla_decode.cu)                mla.go:317-377
 //   5. output projection  out = o W_O                                                  mla.go:380-389
+// and for GQA: q, k, v = x Wq, x Wk, x Wv (mha.go:251-258), RoPE on q and k (mha.go:272-282), append k / v
+// (mha.go:284-289), attention (mha.go:292-348), Wo (mha.go:351-355).
 // The projections are skinny GEMMs (M = sequences x new tokens, at most a few hundred rows) against bf16 weight
 // matrices of up to 16384 x 16384: they are bound by streaming the weights from HBM once.  FAST mode runs them on
 // tcgen05 (activations rounded to bf16, f32 accumulation in tensor memory, split along K so that every SM streams an
@@ -193,24 +196,25 @@ __global__ void cast_bf16_kernel(const float* __restrict__ src, uint16_t* __rest
   reinterpret_cast<uint4*>(dst)[i] = make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w));
 }
 
-// Sums the K splits of the projection result (fixed order, so the result does not depend on scheduling), applies the
-// decoupled RoPE (rope.go:168-176: pairs (2i, 2i+1), out0 = x0 c - x1 s, out1 = x1 c + x0 s, unfused) to q^R and k^R
-// at position len[seq] + s, and scatters the four results.  One thread per pair of adjacent columns.
+// Sums the K splits of the projection result (fixed order, so the result does not depend on scheduling), applies
+// RoPE (rope.go:168-176: pairs (2i, 2i+1) of a head, out0 = x0 c - x1 s, out1 = x1 c + x0 s, unfused) at position
+// len[seq] + s to the segments that ask for it, and scatters every segment to its own buffer.
+// One thread per pair of adjacent columns of the concatenated result.
+struct ProjSeg {
+  int32_t n;          // columns of this segment (= of its weight matrix)
+  int32_t rope_dim;   // 0: no rotation; else the per-head width the rotation works on
+  void* dst;          // [M][n], f32 or bf16
+  int32_t bf16;
+};
 struct FinishParams {
   const float* part;
-  int32_t split_k, M, n_total, S;
-  int32_t n_qc, n_qr, n_c, n_kr;   // H*Dh, H*dHR, dC, dHR
-  int32_t dHR;
+  int32_t split_k, M, n_total, S, n_segs;
+  ProjSeg seg[kMaxWeights];
   const int32_t* len;              // this layer's lengths BEFORE the append
   const int32_t* seq_ids;
-  const float* rope_cos;           // [positions][dHR/2]
+  const float* rope_cos;           // [positions][rope_dim / 2]
   const float* rope_sin;
   int32_t rope_positions;
-  void* qc;                        // [M][H*Dh]  f32 or bf16
-  void* qr;                        // [M][H*dHR] f32 or bf16
-  float* c;                        // [M][dC]
-  float* kr;                       // [M][dHR]
-  int32_t q_bf16;
   int32_t* status;
 };
 __global__ void proj_finish_kernel(const FinishParams p) {
@@ -223,41 +227,29 @@ __global__ void proj_finish_kernel(const FinishParams p) {
     v0 += t.x;
     v1 += t.y;
   }
-  int c = col;
-  if (c < p.n_qc) {
-    if (p.q_bf16) reinterpret_cast<uint32_t*>(p.qc)[((size_t)m * p.n_qc + c) >> 1] = pack_bf16x2(v0, v1);
-    else *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.qc) + (size_t)m * p.n_qc + c) = make_float2(v0, v1);
-    return;
+  int c = col, j = 0;
+  while (j + 1 < p.n_segs && c >= p.seg[j].n) {
+    c -= p.seg[j].n;
+    j++;
   }
-  c -= p.n_qc;
-  const bool is_qr = c < p.n_qr;
-  if (!is_qr) {
-    c -= p.n_qr;
-    if (c < p.n_c) {
-      *reinterpret_cast<float2*>(p.c + (size_t)m * p.n_c + c) = make_float2(v0, v1);
-      return;
+  const ProjSeg sg = p.seg[j];
+  if (sg.rope_dim > 0) {
+    const int i = m / p.S, s = m % p.S;
+    const int seq = p.seq_ids ? p.seq_ids[i] : i;
+    const int pos = p.len[seq] + s;
+    if (pos >= p.rope_positions) {
+      set_status(p.status, RELUX_ERR_OVERFLOW);   // the reference panics: position >= maxSeqLen (rope.go:160-162)
+    } else {
+      const int half = sg.rope_dim / 2, idx = (c % sg.rope_dim) >> 1;
+      const float cs = p.rope_cos[(size_t)pos * half + idx], sn = p.rope_sin[(size_t)pos * half + idx];
+      const float r0 = __fsub_rn(__fmul_rn(v0, cs), __fmul_rn(v1, sn));
+      const float r1 = __fadd_rn(__fmul_rn(v1, cs), __fmul_rn(v0, sn));
+      v0 = r0;
+      v1 = r1;
     }
-    c -= p.n_c;
   }
-  // rotate
-  const int i = m / p.S, s = m % p.S;
-  const int seq = p.seq_ids ? p.seq_ids[i] : i;
-  const int pos = p.len[seq] + s;
-  float r0 = v0, r1 = v1;
-  if (pos >= p.rope_positions) {
-    set_status(p.status, RELUX_ERR_OVERFLOW);   // the reference panics: position >= maxSeqLen (rope.go:160-162)
-  } else {
-    const int half = p.dHR / 2, idx = (c % p.dHR) >> 1;
-    const float cs = p.rope_cos[(size_t)pos * half + idx], sn = p.rope_sin[(size_t)pos * half + idx];
-    r0 = __fsub_rn(__fmul_rn(v0, cs), __fmul_rn(v1, sn));
-    r1 = __fadd_rn(__fmul_rn(v1, cs), __fmul_rn(v0, sn));
-  }
-  if (is_qr) {
-    if (p.q_bf16) reinterpret_cast<uint32_t*>(p.qr)[((size_t)m * p.n_qr + c) >> 1] = pack_bf16x2(r0, r1);
-    else *reinterpret_cast<float2*>(reinterpret_cast<float*>(p.qr) + (size_t)m * p.n_qr + c) = make_float2(r0, r1);
-  } else {
-    *reinterpret_cast<float2*>(p.kr + (size_t)m * p.n_kr + c) = make_float2(r0, r1);
-  }
+  if (sg.bf16) reinterpret_cast<uint32_t*>(sg.dst)[((size_t)m * sg.n + c) >> 1] = pack_bf16x2(v0, v1);
+  else *reinterpret_cast<float2*>(reinterpret_cast<float*>(sg.dst) + (size_t)m * sg.n + c) = make_float2(v0, v1);
 }
 
 __global__ void sum_splits_kernel(const float* __restrict__ part, int split_k, size_t n4, float* __restrict__ out) {
@@ -376,16 +368,147 @@ int32_t ensure_rope_table(Pool* p, int dHR, float base, int positions) {
   return RELUX_OK;
 }
 
+// x [M][K] f32 -> every segment's buffer: cast + split-K tensor-core GEMM (or the reference-order GEMM), then the
+// finish kernel.  `proj_timing` records the event pair of the GEMM launch in the pool's projection ring.
+int32_t project_and_finish(Pool* p, const SeqBatch& sb, int layer, const float* dx, int M, int K, int S, const WeightRef* ws,
+                           const ProjSeg* segs, int nw, bool mma, uint16_t* a_bf16, float* part, size_t part_cap) {
+  cudaStream_t st = p->dev->stream;
+  int n_total = 0;
+  for (int j = 0; j < nw; j++) n_total += ws[j].n;
+  int split = 1;
+  cudaEvent_t* evs = p->proj_ring[p->proj_calls % Pool::kTimeRing];
+  if (mma) {
+    const size_t n8 = (size_t)M * K / 8;
+    cast_bf16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(dx, a_bf16, n8);
+    RELUX_CUDA_TRY(cudaGetLastError());
+    count_launch(p->dev);
+    if (evs[0]) RELUX_CUDA_TRY(cudaEventRecord(evs[0], st));
+    int32_t rc = launch_skinny_gemm(p, a_bf16, M, K, ws, nw, part, part_cap, &split);
+    if (rc) return rc;
+  } else {
+    if (evs[0]) RELUX_CUDA_TRY(cudaEventRecord(evs[0], st));
+    int32_t rc = launch_gemm_reference(p, dx, M, K, ws, nw, part, n_total);
+    if (rc) return rc;
+  }
+  if (evs[0]) {
+    RELUX_CUDA_TRY(cudaEventRecord(evs[1], st));
+    p->proj_calls++;
+  }
+  FinishParams f;
+  memset(&f, 0, sizeof(f));
+  f.part = part;
+  f.split_k = split;
+  f.M = M;
+  f.n_total = n_total;
+  f.S = S;
+  f.n_segs = nw;
+  int rope_dim = 0;
+  for (int j = 0; j < nw; j++) {
+    f.seg[j] = segs[j];
+    if (segs[j].rope_dim) rope_dim = segs[j].rope_dim;
+  }
+  f.len = p->d_len + (size_t)layer * p->prm.max_seqs;
+  f.seq_ids = sb.d_seq_ids;
+  f.rope_cos = (const float*)p->rope_tab.p;
+  f.rope_sin = f.rope_cos ? f.rope_cos + (size_t)p->rope_positions * (rope_dim / 2) : nullptr;
+  f.rope_positions = p->rope_positions;
+  f.status = p->d_status;
+  dim3 grid((n_total / 2 + 255) / 256, M);
+  proj_finish_kernel<<<grid, 256, 0, st>>>(f);
+  RELUX_CUDA_TRY(cudaGetLastError());
+  count_launch(p->dev);
+  return RELUX_OK;
+}
+
+// out [M][N] f32 = attn [M][K] f32 x W_O [K][N]; `out` is the caller's buffer (host or device).
+int32_t output_projection(Pool* p, const float* d_attn, int M, int K, const void* w_o, int N, bool mma, uint16_t* a_bf16, float* part,
+                          size_t part_cap, void* out, int out_mem) {
+  cudaStream_t st = p->dev->stream;
+  const bool direct = out_mem == RELUX_MEM_DEVICE;
+  float* d_out = direct ? (float*)out : nullptr;
+  if (!direct) {
+    int32_t rc = grow(p->dev, p->out_buf, (size_t)M * N * 4);
+    if (rc) return rc;
+    d_out = (float*)p->out_buf.p;
+  }
+  const WeightRef outp[1] = {{w_o, N}};
+  if (mma) {
+    const size_t n8 = (size_t)M * K / 8;
+    cast_bf16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(d_attn, a_bf16, n8);
+    RELUX_CUDA_TRY(cudaGetLastError());
+    count_launch(p->dev);
+    int split = 1;
+    int32_t rc = launch_skinny_gemm(p, a_bf16, M, K, outp, 1, part, part_cap, &split);
+    if (rc) return rc;
+    const size_t n4 = (size_t)M * N / 4;
+    sum_splits_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(part, split, n4, d_out);
+    RELUX_CUDA_TRY(cudaGetLastError());
+    count_launch(p->dev);
+  } else {
+    int32_t rc = launch_gemm_reference(p, d_attn, M, K, outp, 1, d_out, N);
+    if (rc) return rc;
+  }
+  if (!direct) {
+    RELUX_CUDA_TRY(cudaMemcpyAsync(out, d_out, (size_t)M * N * 4, cudaMemcpyDeviceToHost, st));
+    RELUX_CUDA_TRY(cudaStreamSynchronize(st));
+  }
+  return RELUX_OK;
+}
+
+// Validation shared by the two layer entry points; fills the batch with explicit rows per sequence (the append
+// kernels read "no row offsets" as one row per sequence).
+int32_t layer_batch(Pool* p, int layer, int n_seqs, const int32_t* seq_ids, int S, const char* what, SeqBatch* sb) {
+  const relux_pool_params& prm = p->prm;
+  if (layer < 0 || layer >= prm.num_layers) {
+    set_error("layerIdx=%d out of range [0, %d)", layer, prm.num_layers);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  if (n_seqs <= 0 || n_seqs > prm.max_seqs) {
+    set_error("n_seqs=%d outside [1, max_seqs=%d]", n_seqs, prm.max_seqs);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  const std::vector<int32_t> rows_per_seq((size_t)n_seqs, S);
+  int32_t rc = stage_batch(p, n_seqs, seq_ids, rows_per_seq.data(), 1, sb);
+  if (rc) return rc;
+  for (int i = 0; i < sb->n_seqs; i++) {   // the reference panics on overflow (kvcache.go:282-285, mla_cache.go:160-164)
+    const int s = sb->seq[i];
+    const int len = p->h_len[(size_t)layer * prm.max_seqs + s], cap = p->seq_pages[s] * prm.page_tokens;
+    if (len + S > cap) {
+      set_error("%s: layer %d overflow: total=%d + newLen=%d > capacity=%d (sequence %d)", what, layer, len, S, cap, s);
+      return RELUX_ERR_OVERFLOW;
+    }
+  }
+  return RELUX_OK;
+}
+
+struct LayerScratch {
+  uint16_t* a_bf16;
+  float* part;
+  size_t part_cap;
+  char* rest;
+};
+// [activations as bf16 (M x max_k) | split partials | caller's buffers (rest_bytes)]
+int32_t layer_scratch(Pool* p, int M, int max_k, int max_n, size_t rest_bytes, LayerScratch* out) {
+  const size_t part_cap = std::max<size_t>((size_t)64 << 20, (size_t)M * max_n * 4 * 4);
+  const size_t off_part = ((size_t)M * max_k * 2 + 255) & ~(size_t)255;
+  const size_t off_rest = off_part + part_cap;
+  int32_t rc = grow(p->dev, p->layer_buf, off_rest + rest_bytes);
+  if (rc) return rc;
+  char* base = (char*)p->layer_buf.p;
+  out->a_bf16 = (uint16_t*)base;
+  out->part = (float*)(base + off_part);
+  out->part_cap = part_cap;
+  out->rest = base + off_rest;
+  return RELUX_OK;
+}
+inline size_t pad256(size_t b) { return (b + 255) & ~(size_t)255; }
+
 }  // namespace
 
 int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a) {
   if (!a || !a->w) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
   const relux_pool_params& prm = p->prm;
   if (prm.kind != RELUX_POOL_MLA) { set_error("pool kind does not match this call (MLA pool needed)"); return RELUX_ERR_INVALID_ARG; }
-  if (a->layer < 0 || a->layer >= prm.num_layers) {
-    set_error("layerIdx=%d out of range [0, %d)", a->layer, prm.num_layers);
-    return RELUX_ERR_INVALID_ARG;
-  }
   const relux_mla_layer_weights& w = *a->w;
   if (!a->x || !a->out || !w.w_q || !w.w_qr || !w.w_dkv || !w.w_kr || !w.w_uk || !w.w_uv || !w.w_o) {
     set_error("nil input, output or weight pointer");
@@ -401,106 +524,36 @@ int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a) {
   if (a->x_dtype != RELUX_DTYPE_F32) { set_error("x must be float32"); return RELUX_ERR_UNSUPPORTED; }
   const int Dh = D / H;
   const float rope_base = a->rope_base == 0.f ? 10000.f : a->rope_base;   // NewMLA, mla.go:78-80
-  // rows per sequence are passed explicitly: the append kernels read "no row offsets" as one row per sequence
   SeqBatch sb;
-  if (a->n_seqs <= 0 || a->n_seqs > prm.max_seqs) {
-    set_error("n_seqs=%d outside [1, max_seqs=%d]", a->n_seqs, prm.max_seqs);
-    return RELUX_ERR_INVALID_ARG;
-  }
-  const std::vector<int32_t> rows_per_seq((size_t)a->n_seqs, S);
-  int32_t rc = stage_batch(p, a->n_seqs, a->seq_ids, rows_per_seq.data(), 1, &sb);
+  int32_t rc = layer_batch(p, a->layer, a->n_seqs, a->seq_ids, S, "MLACache.Append", &sb);
   if (rc) return rc;
   const int M = sb.n_seqs * S;
-  if (M == 0) return RELUX_OK;
-  for (int i = 0; i < sb.n_seqs; i++) {   // the reference panics on overflow (mla_cache.go:160-164)
-    const int s = sb.seq[i];
-    const int len = p->h_len[(size_t)a->layer * prm.max_seqs + s], cap = p->seq_pages[s] * prm.page_tokens;
-    if (len + S > cap) {
-      set_error("MLACache.Append: layer %d overflow: total=%d + newLen=%d > capacity=%d (sequence %d)", a->layer, len, S, cap, s);
-      return RELUX_ERR_OVERFLOW;
-    }
-  }
   rc = ensure_rope_table(p, dHR, rope_base, prm.max_pages_per_seq * prm.page_tokens);
   if (rc) return rc;
-  cudaStream_t st = p->dev->stream;
   const void* dx = nullptr;
   rc = stage_in(p, p->in_a, a->x, (size_t)M * D * 4, a->x_mem, &dx);
   if (rc) return rc;
 
   const WeightRef proj[4] = {{w.w_q, H * Dh}, {w.w_qr, H * dHR}, {w.w_dkv, dC}, {w.w_kr, dHR}};
-  const int n_total = H * Dh + H * dHR + dC + dHR;
   const WeightRef outp[1] = {{w.w_o, D}};
+  const int n_total = H * Dh + H * dHR + dC + dHR;
   const bool fast = a->mode == RELUX_ATTN_FAST;
-  const bool mma = fast && gemm_sm100_eligible(D, proj, 4) && gemm_sm100_eligible(H * Dh, outp, 1) && n_total % 2 == 0;
-  // scratch: [activations as bf16 | split partials | q^C | q^R | c | k^R | attention output]
-  const size_t part_cap = std::max<size_t>((size_t)64 << 20, (size_t)M * std::max(n_total, D) * 4 * 4);
+  const bool mma = fast && gemm_sm100_eligible(D, proj, 4) && gemm_sm100_eligible(H * Dh, outp, 1);
   const size_t q_es = fast ? 2 : 4;
-  const size_t off_abf = 0;
-  const size_t off_part = off_abf + (((size_t)M * std::max(D, H * Dh) * 2 + 255) & ~(size_t)255);
-  const size_t off_qc = off_part + part_cap;
-  const size_t off_qr = off_qc + (((size_t)M * H * Dh * q_es + 255) & ~(size_t)255);
-  const size_t off_c = off_qr + (((size_t)M * H * dHR * q_es + 255) & ~(size_t)255);
-  const size_t off_kr = off_c + (((size_t)M * dC * 4 + 255) & ~(size_t)255);
-  const size_t off_attn = off_kr + (((size_t)M * dHR * 4 + 255) & ~(size_t)255);
-  const size_t total = off_attn + (size_t)M * H * Dh * 4;
-  rc = grow(p->dev, p->layer_buf, total);
+  const size_t b_qc = pad256((size_t)M * H * Dh * q_es), b_qr = pad256((size_t)M * H * dHR * q_es), b_c = pad256((size_t)M * dC * 4),
+               b_kr = pad256((size_t)M * dHR * 4);
+  LayerScratch sc;
+  rc = layer_scratch(p, M, std::max(D, H * Dh), std::max(n_total, D), b_qc + b_qr + b_c + b_kr + (size_t)M * H * Dh * 4, &sc);
   if (rc) return rc;
-  char* base = (char*)p->layer_buf.p;
-  uint16_t* a_bf16 = (uint16_t*)(base + off_abf);
-  float* part = (float*)(base + off_part);
-  void* d_qc = base + off_qc;
-  void* d_qr = base + off_qr;
-  float* d_c = (float*)(base + off_c);
-  float* d_kr = (float*)(base + off_kr);
-  float* d_attn = (float*)(base + off_attn);
-
-  // 1. projections
-  int split = 1;
-  if (mma) {
-    const size_t n8 = (size_t)M * D / 8;
-    cast_bf16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>((const float*)dx, a_bf16, n8);
-    RELUX_CUDA_TRY(cudaGetLastError());
-    count_launch(p->dev);
-    RELUX_CUDA_TRY(cudaEventRecord(p->proj_ring[p->proj_calls % Pool::kTimeRing][0], st));
-    rc = launch_skinny_gemm(p, a_bf16, M, D, proj, 4, part, part_cap, &split);
-    if (rc) return rc;
-    RELUX_CUDA_TRY(cudaEventRecord(p->proj_ring[p->proj_calls % Pool::kTimeRing][1], st));
-  } else {
-    RELUX_CUDA_TRY(cudaEventRecord(p->proj_ring[p->proj_calls % Pool::kTimeRing][0], st));
-    rc = launch_gemm_reference(p, (const float*)dx, M, D, proj, 4, part, n_total);
-    if (rc) return rc;
-    RELUX_CUDA_TRY(cudaEventRecord(p->proj_ring[p->proj_calls % Pool::kTimeRing][1], st));
-  }
-  p->proj_calls++;
-  // 2. split sum + RoPE + scatter
-  FinishParams f;
-  f.part = part;
-  f.split_k = split;
-  f.M = M;
-  f.n_total = n_total;
-  f.S = S;
-  f.n_qc = H * Dh;
-  f.n_qr = H * dHR;
-  f.n_c = dC;
-  f.n_kr = dHR;
-  f.dHR = dHR;
-  f.len = p->d_len + (size_t)a->layer * prm.max_seqs;
-  f.seq_ids = sb.d_seq_ids;
-  f.rope_cos = (const float*)p->rope_tab.p;
-  f.rope_sin = f.rope_cos + (size_t)p->rope_positions * (dHR / 2);
-  f.rope_positions = p->rope_positions;
-  f.qc = d_qc;
-  f.qr = d_qr;
-  f.c = d_c;
-  f.kr = d_kr;
-  f.q_bf16 = fast ? 1 : 0;
-  f.status = p->d_status;
-  {
-    dim3 grid((n_total / 2 + 255) / 256, M);
-    proj_finish_kernel<<<grid, 256, 0, st>>>(f);
-    RELUX_CUDA_TRY(cudaGetLastError());
-    count_launch(p->dev);
-  }
+  void* d_qc = sc.rest;
+  void* d_qr = sc.rest + b_qc;
+  float* d_c = (float*)(sc.rest + b_qc + b_qr);
+  float* d_kr = (float*)(sc.rest + b_qc + b_qr + b_c);
+  float* d_attn = (float*)(sc.rest + b_qc + b_qr + b_c + b_kr);
+  // 1 + 2. projections, RoPE on q^R and k^R
+  const ProjSeg segs[4] = {{H * Dh, 0, d_qc, fast ? 1 : 0}, {H * dHR, dHR, d_qr, fast ? 1 : 0}, {dC, 0, d_c, 0}, {dHR, dHR, d_kr, 0}};
+  rc = project_and_finish(p, sb, a->layer, (const float*)dx, M, D, S, proj, segs, 4, mma, sc.a_bf16, sc.part, sc.part_cap);
+  if (rc) return rc;
   // 3. append (advances the cursors)
   rc = launch_mla_append(p, sb, a->layer, d_c, d_kr, RELUX_DTYPE_F32, 1);
   if (rc) return rc;
@@ -526,33 +579,86 @@ int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a) {
             : launch_attn_reference_mla(p, sb, aa, (const float*)d_qc, (const float*)d_qr, d_attn);
   if (rc) return rc;
   // 5. output projection
-  const bool direct = a->out_mem == RELUX_MEM_DEVICE;
-  float* d_out = direct ? (float*)a->out : nullptr;
-  if (!direct) {
-    rc = grow(p->dev, p->out_buf, (size_t)M * D * 4);
-    if (rc) return rc;
-    d_out = (float*)p->out_buf.p;
+  return output_projection(p, d_attn, M, H * Dh, w.w_o, D, mma, sc.a_bf16, sc.part, sc.part_cap, a->out, a->out_mem);
+}
+
+// MHA.forwardCached (mha.go:245-369) for a batch of independent sequences: projections with Wq / Wk / Wv, RoPE on q
+// and k at position cacheLen + s (when the layer has a rotary embedding), append of k / v, GQA attention, Wo.
+int32_t do_gqa_layer(Pool* p, const relux_gqa_layer_args* a) {
+  if (!a || !a->w) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
+  const relux_pool_params& prm = p->prm;
+  if (prm.kind != RELUX_POOL_GQA) { set_error("pool kind does not match this call (GQA pool needed)"); return RELUX_ERR_INVALID_ARG; }
+  const relux_gqa_layer_weights& w = *a->w;
+  if (!a->x || !a->out || !w.w_q || !w.w_k || !w.w_v || !w.w_o) {
+    set_error("nil input, output or weight pointer");
+    return RELUX_ERR_INVALID_ARG;
   }
-  if (mma) {
-    const size_t n8 = (size_t)M * H * Dh / 8;
-    cast_bf16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(d_attn, a_bf16, n8);
-    RELUX_CUDA_TRY(cudaGetLastError());
-    count_launch(p->dev);
-    rc = launch_skinny_gemm(p, a_bf16, M, H * Dh, outp, 1, part, part_cap, &split);
-    if (rc) return rc;
-    const size_t n4 = (size_t)M * D / 4;
-    sum_splits_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(part, split, n4, d_out);
-    RELUX_CUDA_TRY(cudaGetLastError());
-    count_launch(p->dev);
-  } else {
-    rc = launch_gemm_reference(p, d_attn, M, H * Dh, outp, 1, d_out, D);
+  const int H = a->num_heads, D = a->d_model, S = a->q_tokens, Hkv = prm.gqa_num_kv_heads, hd = prm.gqa_head_dim;
+  if (H <= 0 || D <= 0 || S <= 0 || D % H != 0 || D / H != hd || H % Hkv != 0) {   // NewMHAGQA, mha.go
+    set_error("dModel=%d / numHeads=%d must equal the pool's head_dim=%d, numHeads a multiple of numKVHeads=%d", D, H, hd, Hkv);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  if (a->rope && hd % 2 != 0) { set_error("NewRotaryEmbedding: headDim=%d, must be even and > 0", hd); return RELUX_ERR_INVALID_ARG; }
+  if (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE) { set_error("bad mode"); return RELUX_ERR_INVALID_ARG; }
+  if (a->x_dtype != RELUX_DTYPE_F32) { set_error("x must be float32"); return RELUX_ERR_UNSUPPORTED; }
+  if (a->mode == RELUX_ATTN_FAST && (!p->has_tmap || prm.page_tokens != 64 || hd != 128 || (H / Hkv) * S > 32)) {
+    // checked before anything is written to the cache
+    set_error("GQA FAST kernels need page_tokens=64, head_dim=128 and (num_heads/num_kv_heads)*q_tokens <= 32 "
+              "(got page_tokens=%d head_dim=%d rows=%d); use RELUX_ATTN_REFERENCE for other shapes", prm.page_tokens, hd, (H / Hkv) * S);
+    return RELUX_ERR_UNSUPPORTED;
+  }
+  const float rope_base = a->rope_base == 0.f ? 10000.f : a->rope_base;
+  SeqBatch sb;
+  int32_t rc = layer_batch(p, a->layer, a->n_seqs, a->seq_ids, S, "Append", &sb);
+  if (rc) return rc;
+  const int M = sb.n_seqs * S;
+  if (a->rope) {
+    rc = ensure_rope_table(p, hd, rope_base, prm.max_pages_per_seq * prm.page_tokens);
     if (rc) return rc;
   }
-  if (!direct) {
-    RELUX_CUDA_TRY(cudaMemcpyAsync(a->out, d_out, (size_t)M * D * 4, cudaMemcpyDeviceToHost, st));
-    RELUX_CUDA_TRY(cudaStreamSynchronize(st));
-  }
-  return RELUX_OK;
+  const void* dx = nullptr;
+  rc = stage_in(p, p->in_a, a->x, (size_t)M * D * 4, a->x_mem, &dx);
+  if (rc) return rc;
+  const WeightRef proj[3] = {{w.w_q, H * hd}, {w.w_k, Hkv * hd}, {w.w_v, Hkv * hd}};
+  const WeightRef outp[1] = {{w.w_o, D}};
+  const int n_total = (H + 2 * Hkv) * hd;
+  const bool fast = a->mode == RELUX_ATTN_FAST;
+  const bool mma = fast && gemm_sm100_eligible(D, proj, 3) && gemm_sm100_eligible(H * hd, outp, 1);
+  const size_t q_es = fast ? 2 : 4;
+  const size_t b_q = pad256((size_t)M * H * hd * q_es), b_kv = pad256((size_t)M * Hkv * hd * 4);
+  LayerScratch sc;
+  rc = layer_scratch(p, M, std::max(D, H * hd), std::max(n_total, D), b_q + 2 * b_kv + (size_t)M * H * hd * 4, &sc);
+  if (rc) return rc;
+  void* d_q = sc.rest;
+  float* d_k = (float*)(sc.rest + b_q);
+  float* d_v = (float*)(sc.rest + b_q + b_kv);
+  float* d_attn = (float*)(sc.rest + b_q + 2 * b_kv);
+  const int rd = a->rope ? hd : 0;
+  const ProjSeg segs[3] = {{H * hd, rd, d_q, fast ? 1 : 0}, {Hkv * hd, rd, d_k, 0}, {Hkv * hd, 0, d_v, 0}};
+  rc = project_and_finish(p, sb, a->layer, (const float*)dx, M, D, S, proj, segs, 3, mma, sc.a_bf16, sc.part, sc.part_cap);
+  if (rc) return rc;
+  // append: the GEMM rows are token-major [row][Hkv][hd]; advance = 0 leaves the rows past the cursor (verify)
+  rc = launch_gqa_append(p, sb, a->layer, d_k, d_v, RELUX_DTYPE_F32, RELUX_LAYOUT_TOKEN_MAJOR, a->advance);
+  if (rc) return rc;
+  if (a->advance)
+    for (int i = 0; i < sb.n_seqs; i++) p->h_len[(size_t)a->layer * prm.max_seqs + sb.seq[i]] += S;
+  relux_attn_args aa;
+  memset(&aa, 0, sizeof(aa));
+  aa.layer = a->layer;
+  aa.n_seqs = sb.n_seqs;
+  aa.seq_ids = a->seq_ids;
+  aa.q_tokens = S;
+  aa.extra_tokens = a->advance ? 0 : S;
+  aa.causal = a->causal;
+  aa.num_heads = H;
+  aa.head_dim = hd;
+  aa.scale = (float)(1.0 / std::sqrt((double)hd));   // mha.go:319
+  aa.q_dtype = fast ? RELUX_DTYPE_BF16 : RELUX_DTYPE_F32;
+  aa.q_layout = RELUX_LAYOUT_TOKEN_MAJOR;
+  aa.mode = a->mode;
+  rc = fast ? launch_gqa_decode_fast(p, sb, aa, d_q, d_attn) : launch_attn_reference_gqa(p, sb, aa, (const float*)d_q, d_attn);
+  if (rc) return rc;
+  return output_projection(p, d_attn, M, H * hd, w.w_o, D, mma, sc.a_bf16, sc.part, sc.part_cap, a->out, a->out_mem);
 }
 
 }  // namespace relux

@@ -590,10 +590,9 @@ API int32_t relux_pool_create(relux_device_t h, const relux_pool_params* prm, re
   for (auto& pair : p->ev_ring)
     for (cudaEvent_t& ev : pair)
       if (e == cudaSuccess) e = cudaEventCreate(&ev);
-  if (prm->kind == RELUX_POOL_MLA)
-    for (auto& pair : p->proj_ring)
-      for (cudaEvent_t& ev : pair)
-        if (e == cudaSuccess) e = cudaEventCreate(&ev);
+  for (auto& pair : p->proj_ring)
+    for (cudaEvent_t& ev : pair)
+      if (e == cudaSuccess) e = cudaEventCreate(&ev);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_table, 0xFF, table_n * 4, dev->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_len, 0, len_n * 4, dev->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_status, 0, 8, dev->stream);
@@ -830,6 +829,11 @@ API int32_t relux_mla_verify(relux_pool_t h, const relux_attn_args* attn, const 
 API int32_t relux_mla_forward_cached(relux_pool_t h, const relux_mla_layer_args* a) {
   GET_POOL(h);
   return do_mla_layer(p, a);
+}
+
+API int32_t relux_gqa_forward_cached(relux_pool_t h, const relux_gqa_layer_args* a) {
+  GET_POOL(h);
+  return do_gqa_layer(p, a);
 }
 
 API int32_t relux_pool_last_kernel_ms(relux_pool_t h, float* ms) {

@@ -30,7 +30,7 @@ EXPORTS = [
     "relux_cuda_event_destroy", "relux_cuda_flush_l2", "relux_pool_create", "relux_pool_destroy", "relux_pool_reset",
     "relux_pool_set_tables", "relux_seq_alloc", "relux_seq_free", "relux_seq_len", "relux_seq_set_len", "relux_pool_status",
     "relux_pool_read_rows", "relux_mla_append", "relux_gqa_append", "relux_mla_decode", "relux_gqa_decode", "relux_gqa_verify",
-    "relux_mla_verify", "relux_pool_last_kernel_ms", "relux_pool_kernel_ms_mean", "relux_mla_forward_cached", "relux_pool_projection_ms_mean", "relux_gqa_decode_noalloc",
+    "relux_mla_verify", "relux_pool_last_kernel_ms", "relux_pool_kernel_ms_mean", "relux_mla_forward_cached", "relux_gqa_forward_cached", "relux_pool_projection_ms_mean", "relux_gqa_decode_noalloc",
 ]
 
 
@@ -65,6 +65,18 @@ class MlaLayerArgs(C.Structure):
                 ("causal", C.c_int32), ("d_model", C.c_int32), ("num_heads", C.c_int32), ("rope_base", C.c_float),
                 ("mode", C.c_int32), ("x", C.c_void_p), ("x_dtype", C.c_int32), ("x_mem", C.c_int32), ("out", C.c_void_p),
                 ("out_mem", C.c_int32), ("reserved", C.c_int32 * 3), ("w", C.POINTER(MlaLayerWeights))]
+
+
+class GqaLayerWeights(C.Structure):
+    _fields_ = [("w_q", C.c_void_p), ("w_k", C.c_void_p), ("w_v", C.c_void_p), ("w_o", C.c_void_p)]
+
+
+class GqaLayerArgs(C.Structure):
+    _fields_ = [("layer", C.c_int32), ("n_seqs", C.c_int32), ("seq_ids", C.c_void_p), ("q_tokens", C.c_int32),
+                ("causal", C.c_int32), ("d_model", C.c_int32), ("num_heads", C.c_int32), ("rope", C.c_int32),
+                ("rope_base", C.c_float), ("advance", C.c_int32), ("mode", C.c_int32), ("x", C.c_void_p), ("x_dtype", C.c_int32),
+                ("x_mem", C.c_int32), ("out", C.c_void_p), ("out_mem", C.c_int32), ("reserved", C.c_int32 * 3),
+                ("w", C.POINTER(GqaLayerWeights))]
 
 
 class ReluxCudaError(RuntimeError):
@@ -126,6 +138,7 @@ def load():
         for n in ("relux_gqa_verify", "relux_mla_verify"):
             getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AttnArgs), C.POINTER(AppendArgs)]
         L.relux_pool_projection_ms_mean.argtypes = [C.c_void_p, C.c_int32, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
+        L.relux_gqa_forward_cached.argtypes = [C.c_void_p, C.POINTER(GqaLayerArgs)]
         L.relux_mla_forward_cached.argtypes = [C.c_void_p, C.POINTER(MlaLayerArgs)]
         L.relux_pool_last_kernel_ms.argtypes = [C.c_void_p, C.POINTER(C.c_float)]
         L.relux_pool_kernel_ms_mean.argtypes = [C.c_void_p, C.c_int32, C.POINTER(C.c_float), C.POINTER(C.c_int32)]

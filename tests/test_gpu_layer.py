@@ -204,3 +204,145 @@ def test_layer_errors(dev, oracle):
     pool.destroy()
     for v in dW.values():
         v.free()
+
+
+# ------------------------------------------------------------------------------------------------ GQA layer step
+class OracleGqaLayer:
+    """MHA.forwardCached (mha.go:245-369) for a batch of independent sequences, INTENDED semantics, bf16 cache rows."""
+
+    def __init__(self, oracle, W, D, H, Hkv, rope_base, max_pos, causal, rope=True):
+        self.o, self.W, self.D, self.H, self.Hkv, self.causal = oracle, W, D, H, Hkv, causal
+        self.hd = D // H
+        self.Wf = {k: oracle.f32_from_bf16(v) for k, v in W.items()}
+        self.rope = oracle.Rope(self.hd, rope_base, max_pos) if rope else None
+        self.k, self.v = [], []
+
+    def add_sequences(self, n):
+        for _ in range(n):
+            self.k.append(np.zeros((0, self.Hkv, self.hd), np.uint16))
+            self.v.append(np.zeros((0, self.Hkv, self.hd), np.uint16))
+
+    def step(self, x, keep=None):
+        """keep[b] = rows of this step that stay in the cache (None: all; speculative verify commits a prefix)."""
+        o, H, Hkv, hd = self.o, self.H, self.Hkv, self.hd
+        B, S, D = x.shape
+        x2 = np.ascontiguousarray(x.reshape(B * S, D))
+        q = o.matmul(x2, self.Wf["w_q"]).reshape(B, S, H, hd)
+        k = o.matmul(x2, self.Wf["w_k"]).reshape(B, S, Hkv, hd)
+        v = o.matmul(x2, self.Wf["w_v"]).reshape(B, S, Hkv, hd)
+        if self.rope is not None:
+            for b in range(B):
+                start = self.k[b].shape[0]
+                q[b] = self.rope.apply(np.ascontiguousarray(q[b].transpose(1, 0, 2)), start, intended_positions=True).transpose(1, 0, 2)
+                k[b] = self.rope.apply(np.ascontiguousarray(k[b].transpose(1, 0, 2)), start, intended_positions=True).transpose(1, 0, 2)
+        full_k = [np.concatenate([self.k[b], o.bf16_from_f32(k[b])]) for b in range(B)]
+        full_v = [np.concatenate([self.v[b], o.bf16_from_f32(v[b])]) for b in range(B)]
+        lens = [a.shape[0] for a in full_k]
+        Tm = max(lens)
+        Kp = np.zeros((B, Tm, Hkv, hd), np.uint16)
+        Vp = np.zeros_like(Kp)
+        for b in range(B):
+            Kp[b, :lens[b]] = full_k[b]
+            Vp[b, :lens[b]] = full_v[b]
+        scale = float(np.float32(1.0 / np.sqrt(float(hd))))
+        attn = o.gqa_attend(Kp, Vp, lens, q, scale, causal=self.causal)
+        for b in range(B):
+            n = S if keep is None else int(keep[b])
+            self.k[b] = full_k[b][:lens[b] - S + n]
+            self.v[b] = full_v[b][:lens[b] - S + n]
+        return o.matmul(np.ascontiguousarray(attn.reshape(B * S, H * hd)), self.Wf["w_o"]).reshape(B, S, D)
+
+
+def make_gqa_weights(oracle, rng, D, H, Hkv):
+    hd = D // H
+    shapes = {"w_q": (D, H * hd), "w_k": (D, Hkv * hd), "w_v": (D, Hkv * hd), "w_o": (H * hd, D)}
+    return {k: oracle.bf16_from_f32(rng.standard_normal(sh, dtype=np.float32) * np.float32(1.0 / np.sqrt(sh[0]))) for k, sh in shapes.items()}
+
+
+def build_gqa_pool(dev, rng, B, capacity, Hkv, hd, P=64):
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    pages_per = (capacity + P - 1) // P
+    pool = rb.Pool(dev, L.POOL_GQA, 1, B * pages_per, P, B, pages_per, num_kv_heads=Hkv, head_dim=hd)
+    pool.set_tables(permuted_tables(rng, B, pages_per))
+    return pool
+
+
+def gqa_prefill(rng, oracle, pool, ol, lens):
+    B = len(lens)
+    K = oracle.bf16_from_f32(rng.standard_normal((int(np.sum(lens)), ol.Hkv, ol.hd), dtype=np.float32))
+    V = oracle.bf16_from_f32(rng.standard_normal((int(np.sum(lens)), ol.Hkv, ol.hd), dtype=np.float32))
+    if int(np.sum(lens)) > 0:
+        pool.append(0, K, V, B, n_new=np.asarray(lens, np.int32))
+    o = 0
+    for b, n in enumerate(lens):
+        ol.k[b], ol.v[b] = K[o:o + n].copy(), V[o:o + n].copy()
+        o += n
+
+
+@pytest.mark.parametrize("rope", [True, False])
+def test_gqa_layer_reference_mode_is_bit_exact_small(dev, oracle, rope):
+    """config-1 layer shapes (dModel 64, 4 heads, 2 kv heads, head_dim 16): outputs and cache rows, bit for bit."""
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(31)
+    D, H, Hkv, B = 64, 4, 2, 3
+    W = make_gqa_weights(oracle, rng, D, H, Hkv)
+    dW = {k: dev.upload(v) for k, v in W.items()}
+    pool = build_gqa_pool(dev, rng, B, 128, Hkv, D // H)
+    ol = OracleGqaLayer(oracle, W, D, H, Hkv, 10000.0, 128, True, rope=rope)
+    ol.add_sequences(B)
+    gqa_prefill(rng, oracle, pool, ol, [0, 7, 66])
+    for S in (1, 3, 1):
+        x = rng.standard_normal((B, S, D), dtype=np.float32)
+        got = np.empty_like(x)
+        pool.forward_cached(0, B, x, got, dW, D, H, q_tokens=S, mode=L.ATTN_REFERENCE, rope=rope)
+        assert np.array_equal(got, ol.step(x))
+    for b in range(B):
+        n = ol.k[b].shape[0]
+        assert pool.seq_len(0, b) == n
+        gk, gv = pool.read_rows(0, b, 0, n)
+        assert np.array_equal(gk, ol.k[b]) and np.array_equal(gv, ol.v[b])
+    assert pool.status() == 0
+    with pytest.raises(L.ReluxCudaError) as e:     # the tensor-core kernels do not cover head_dim 16: refused before any write
+        pool.forward_cached(0, B, x, got, dW, D, H, q_tokens=1, mode=L.ATTN_FAST, rope=rope)
+    assert e.value.code == L.ERR_UNSUPPORTED and pool.seq_len(0, 0) == ol.k[0].shape[0]
+    pool.destroy()
+    for v in dW.values():
+        v.free()
+
+
+def test_gqa_layer_fast_decode_and_verify(dev, oracle):
+    """config-5 layer shapes (dModel 4096, 32 heads, 8 kv heads, head_dim 128): a decode step, then speculative verify
+    steps of 4 draft tokens (rows left past the cursor) with an accepted prefix committed afterwards."""
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(32)
+    D, H, Hkv, B, S = 4096, 32, 8, 3, 4
+    W = make_gqa_weights(oracle, rng, D, H, Hkv)
+    dW = {k: dev.upload(v) for k, v in W.items()}
+    pool = build_gqa_pool(dev, rng, B, 320, Hkv, D // H)
+    ol = OracleGqaLayer(oracle, W, D, H, Hkv, 10000.0, 320, True)
+    ol.add_sequences(B)
+    gqa_prefill(rng, oracle, pool, ol, [100, 64, 190])
+    x = rng.standard_normal((B, 1, D), dtype=np.float32)
+    got = np.empty_like(x)
+    pool.forward_cached(0, B, x, got, dW, D, H, q_tokens=1)
+    with oracle.exact_exp():
+        ref = ol.step(x)
+    _close(oracle, got, ref, "gqa layer decode")
+    for step in range(2):
+        x = rng.standard_normal((B, S, D), dtype=np.float32)
+        got = np.empty_like(x)
+        lens = np.array([pool.seq_len(0, b) for b in range(B)], np.int32)
+        pool.forward_cached(0, B, x, got, dW, D, H, q_tokens=S, advance=False)
+        accepted = rng.integers(1, S + 1, B).astype(np.int32)
+        with oracle.exact_exp():
+            ref = ol.step(x, keep=accepted)
+        _close(oracle, got, ref, "gqa layer verify %d" % step)
+        assert all(pool.seq_len(0, b) == lens[b] for b in range(B))     # verify leaves the cursors alone
+        pool.set_len(0, lens + accepted)
+        for b in range(B):
+            assert pool.seq_len(0, b) == ol.k[b].shape[0]
+    assert pool.status() == 0
+    pool.destroy()
+    for v in dW.values():
+        v.free()
