@@ -36,6 +36,8 @@ WORKLOADS = {
     # GQA flash-decode + speculative verify: 4 draft tokens per step, accepted prefix uniform in 1..4
     "gqa_verify_b128_ctx8k": dict(kind="gqa", B=128, ctx=8192, H=32, Hkv=8, D=128, S=4),
     "gqa_verify_b16_ctx8k": dict(kind="gqa", B=16, ctx=8192, H=32, Hkv=8, D=128, S=4),
+    # the whole GQA layer step of a verify: x [B, 4, 4096] -> projections + RoPE + draft rows + attention + Wo
+    "gqa_layer_verify_b128_ctx8k": dict(kind="gqa", B=128, ctx=8192, H=32, Hkv=8, D=128, S=4, layer=True),
 }
 # dram__bytes_read + dram__bytes_write of the dominant kernel divided by its algorithmic bytes, from the ncu captures
 # summarised under profiles/ (small case, traffic grows in proportion to the cached tokens read).
@@ -339,6 +341,30 @@ def run_gqa(args, w, world, rank, local, dist):
         pool.verify(0, B, pins[0].array, pin_out.array, pins[1].array, pins[2].array, H, D, scale, S)
         commit()
 
+    layer = bool(w.get("layer"))
+    if layer:
+        dm = H * D   # dModel = numHeads * headDim like NewMHA
+
+        def weight(rows, cols):
+            return dev.upload(orc.bf16_from_f32(rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(1.0 / np.sqrt(rows))))
+
+        dW = {"w_q": weight(dm, H * D), "w_k": weight(dm, Hkv * D), "w_v": weight(dm, Hkv * D), "w_o": weight(H * D, dm)}
+        x_host = rng.standard_normal((B, S, dm), dtype=np.float32)
+        d_x = dev.upload(x_host)
+        d_y = dev.alloc(x_host.size * 4, L.DTYPE_F32)
+        pin_x = dev.pinned(x_host.shape, np.float32)
+        pin_x.array[...] = x_host
+        pin_y = dev.pinned(x_host.shape, np.float32)
+
+        def step_resident():
+            rows_read.append(float(lens.sum()) + B * S)
+            pool.forward_cached(0, B, d_x, d_y, dW, dm, H, q_tokens=S, advance=False)
+            commit()
+
+        def step_e2e():
+            pool.forward_cached(0, B, pin_x.array, pin_y.array, dW, dm, H, q_tokens=S, advance=False)
+            commit()
+
     e0, e1 = dev.event(), dev.event()
 
     def timed(fn, steps, warmup, sampler=None):
@@ -374,7 +400,8 @@ def run_gqa(args, w, world, rank, local, dist):
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
     acc_res_all = acc_res * world   # every rank draws from its own seeded stream with the same distribution
     line = {
-        "metric": "gqa_verify_accepted_tokens_per_s", "value": acc_res_all / (ms_res * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "metric": "gqa_layer_verify_accepted_tokens_per_s" if layer else "gqa_verify_accepted_tokens_per_s",
+        "value": acc_res_all / (ms_res * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": args.workload, "batch_per_gpu": B, "context": ctx0, "heads": H, "kv_heads": Hkv, "head_dim": D,
@@ -384,8 +411,9 @@ def run_gqa(args, w, world, rank, local, dist):
                      "traffic": alg_bytes * TRAFFIC_RATIO["gqa"],
                      "peak_source": peak_src, "kernel": "gqa_decode_kernel", "kernel_ms": kernel_ms, "launches_timed": counted,
                      "algorithmic_bytes_per_launch": alg_bytes, "frac_of_nominal_8TBs": achieved / 8000.0},
-        "e2e": {"value": acc_e2e * world / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": int(q.nbytes + nk.nbytes + nv.nbytes),
-                "d2h_bytes_per_step": int(q.nbytes)},
+        "e2e": {"value": acc_e2e * world / (ms_e2e * 1e-3), "unit": "tokens/s",
+                "h2d_bytes_per_step": int(x_host.nbytes) if layer else int(q.nbytes + nk.nbytes + nv.nbytes),
+                "d2h_bytes_per_step": int(x_host.nbytes) if layer else int(q.nbytes)},
         "gpu_launches": launches, "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
