@@ -65,9 +65,14 @@ struct Pool {
   // per-call staging of small host arrays (seq ids, row offsets)
   int32_t* d_seq_ids = nullptr;  // [max_seqs]
   int32_t* d_row_off = nullptr;  // [max_seqs + 1]
-  int32_t* h_stage = nullptr;    // pinned [2 * (max_seqs + 1)]
-  cudaEvent_t stage_ev = nullptr;
-  bool stage_busy = false;
+  // Pinned staging for per-call id / row-offset / length arrays: a ring of slots, each guarded by its own event, so
+  // that a call waits for a copy issued kStageSlots calls ago (long finished) instead of for the previous step's kernels.
+  static constexpr int kStageSlots = 8;
+  int32_t* h_stage = nullptr;    // pinned [kStageSlots][2 * max_seqs + 1]
+  cudaEvent_t stage_ev[kStageSlots] = {};
+  bool stage_busy[kStageSlots] = {};
+  uint32_t stage_next = 0;
+  size_t stage_slot_ints() const { return 2 * (size_t)prm.max_seqs + 1; }
   // staging of activations that arrive in host memory, and outputs that leave to it
   GrowBuf in_a, in_b, out_buf, q_conv;
   // attention scratch
@@ -106,6 +111,9 @@ inline Pool* as_pool(relux_pool_t h) {
 }
 
 int32_t grow(Device* dev, GrowBuf& b, size_t bytes);
+// Next staging slot (waits for the copy that last used it); call stage_release after the copies are enqueued.
+int32_t stage_acquire(Pool* p, int32_t** slot, int* slot_index);
+int32_t stage_release(Pool* p, int slot_index);
 
 // Resolved view of one call's sequences on the device.
 struct SeqBatch {

@@ -38,6 +38,22 @@ int32_t grow(Device* dev, GrowBuf& b, size_t bytes) {
   return RELUX_OK;
 }
 
+int32_t stage_acquire(Pool* p, int32_t** slot, int* slot_index) {
+  const int i = (int)(p->stage_next++ % Pool::kStageSlots);
+  if (p->stage_busy[i]) {
+    RELUX_CUDA_TRY(cudaEventSynchronize(p->stage_ev[i]));
+    p->stage_busy[i] = false;
+  }
+  *slot = p->h_stage + (size_t)i * p->stage_slot_ints();
+  *slot_index = i;
+  return RELUX_OK;
+}
+int32_t stage_release(Pool* p, int slot_index) {
+  RELUX_CUDA_TRY(cudaEventRecord(p->stage_ev[slot_index], p->dev->stream));
+  p->stage_busy[slot_index] = true;
+  return RELUX_OK;
+}
+
 // Copies the call's sequence ids / rows-per-sequence to the device when they are not the
 // trivial (identity, uniform) case, through one pinned staging block guarded by an event.
 int32_t stage_batch(Pool* p, int32_t n_seqs, const int32_t* seq_ids, const int32_t* n_rows, int32_t uniform_rows,
@@ -82,12 +98,12 @@ int32_t stage_batch(Pool* p, int32_t n_seqs, const int32_t* seq_ids, const int32
   out->d_row_off = nullptr;
   if (!seq_ids && uniform) return RELUX_OK;
   Device* dev = p->dev;
-  if (p->stage_busy) {
-    RELUX_CUDA_TRY(cudaEventSynchronize(p->stage_ev));
-    p->stage_busy = false;
-  }
-  int32_t* h_ids = p->h_stage;
-  int32_t* h_off = p->h_stage + prm.max_seqs;
+  int32_t* slot = nullptr;
+  int slot_index = 0;
+  int32_t rc_stage = stage_acquire(p, &slot, &slot_index);
+  if (rc_stage) return rc_stage;
+  int32_t* h_ids = slot;
+  int32_t* h_off = slot + prm.max_seqs;
   if (seq_ids) {
     memcpy(h_ids, out->seq.data(), sizeof(int32_t) * n_seqs);
     RELUX_CUDA_TRY(cudaMemcpyAsync(p->d_seq_ids, h_ids, sizeof(int32_t) * n_seqs, cudaMemcpyHostToDevice, dev->stream));
@@ -103,9 +119,7 @@ int32_t stage_batch(Pool* p, int32_t n_seqs, const int32_t* seq_ids, const int32
     RELUX_CUDA_TRY(cudaMemcpyAsync(p->d_row_off, h_off, sizeof(int32_t) * (n_seqs + 1), cudaMemcpyHostToDevice, dev->stream));
     out->d_row_off = p->d_row_off;
   }
-  RELUX_CUDA_TRY(cudaEventRecord(p->stage_ev, dev->stream));
-  p->stage_busy = true;
-  return RELUX_OK;
+  return stage_release(p, slot_index);
 }
 
 struct DeviceGuard {
@@ -152,7 +166,8 @@ static void pool_free_all(Pool* p) {
   fr(p->in_a.p); fr(p->in_b.p); fr(p->out_buf.p); fr(p->q_abs.p); fr(p->part_o.p); fr(p->part_ml.p); fr(p->work.p);
   fr(p->o_lat.p); fr(p->q_conv.p); fr(p->rope_tab.p); fr(p->layer_buf.p);
   if (p->h_stage) cudaFreeHost(p->h_stage);
-  if (p->stage_ev) cudaEventDestroy(p->stage_ev);
+  for (cudaEvent_t ev : p->stage_ev)
+    if (ev) cudaEventDestroy(ev);
   for (auto& pair : p->ev_ring)
     for (cudaEvent_t ev : pair)
       if (ev) cudaEventDestroy(ev);
@@ -585,8 +600,9 @@ API int32_t relux_pool_create(relux_device_t h, const relux_pool_params* prm, re
   A((void**)&p->d_status, 8);   // [0] status word, [1] block counter of the append kernels
   A((void**)&p->d_seq_ids, (size_t)prm->max_seqs * 4);
   A((void**)&p->d_row_off, ((size_t)prm->max_seqs + 1) * 4);
-  if (e == cudaSuccess) e = cudaMallocHost((void**)&p->h_stage, (2 * (size_t)prm->max_seqs + 1) * 4);
-  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&p->stage_ev, cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaMallocHost((void**)&p->h_stage, Pool::kStageSlots * (2 * (size_t)prm->max_seqs + 1) * 4);
+  for (cudaEvent_t& ev : p->stage_ev)
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
   for (auto& pair : p->ev_ring)
     for (cudaEvent_t& ev : pair)
       if (e == cudaSuccess) e = cudaEventCreate(&ev);
@@ -742,12 +758,14 @@ API int32_t relux_seq_set_len(relux_pool_t h, int32_t layer, int32_t n_seqs, con
       return RELUX_ERR_OVERFLOW;
     }
   // lengths travel through the row-offset staging block
-  if (p->stage_busy) { RELUX_CUDA_TRY(cudaEventSynchronize(p->stage_ev)); p->stage_busy = false; }
-  int32_t* hs = p->h_stage + prm.max_seqs;
+  int32_t* hs = nullptr;
+  int slot_index = 0;
+  rc = stage_acquire(p, &hs, &slot_index);
+  if (rc) return rc;
   memcpy(hs, new_len, sizeof(int32_t) * n_seqs);
   RELUX_CUDA_TRY(cudaMemcpyAsync(p->d_row_off, hs, sizeof(int32_t) * n_seqs, cudaMemcpyHostToDevice, dev->stream));
-  RELUX_CUDA_TRY(cudaEventRecord(p->stage_ev, dev->stream));
-  p->stage_busy = true;
+  rc = stage_release(p, slot_index);
+  if (rc) return rc;
   int l0 = layer < 0 ? 0 : layer, l1 = layer < 0 ? prm.num_layers : layer + 1;
   for (int l = l0; l < l1; l++) {
     rc = launch_set_len(p, sb, l, p->d_row_off);
