@@ -28,6 +28,9 @@ WORKLOADS = {
     # name: (kind, batch per GPU, context, heads, head_dim, dC, dHR)
     "mla_decode_b64_ctx32k": dict(kind="mla", B=64, ctx=32768, H=128, Dh=128, dC=512, dHR=64),
     "mla_decode_b64_ctx4k": dict(kind="mla", B=64, ctx=4096, H=128, Dh=128, dC=512, dHR=64),
+    # config 4 per GPU: 16 sequences with context lengths uniform in [1024, 32768] (one global seeded draw of 16 x world
+    # lengths, dealt to the ranks longest-first so that every GPU holds about the same number of cached tokens)
+    "mla_decode_ragged_b16": dict(kind="mla", B=16, ctx=32768, H=128, Dh=128, dC=512, dHR=64, ragged=True),
     # the whole attention layer step on the device (projections + RoPE + append + decode + output projection)
     "mla_layer_b64_ctx32k": dict(kind="mla", B=64, ctx=32768, H=128, Dh=128, dC=512, dHR=64, layer=True),
     "mla_layer_b16_ctx4k": dict(kind="mla", B=16, ctx=4096, H=128, Dh=128, dC=512, dHR=64, layer=True),
@@ -145,13 +148,20 @@ def run_mla(args, w, world, rank, local, dist):
     rng = np.random.default_rng(7 + rank)
     pool = rb.Pool(dev, L.POOL_MLA, 1, B * pages_per, PAGE, B, pages_per, dC=dC, dHR=dHR)
     pool.set_tables(rng.permutation(B * pages_per).astype(np.int32).reshape(B, pages_per))
-    # fill the cache: one seeded N(0,1) block of `blk` tokens per sequence, appended ctx0/blk times from device memory
+    # fill the cache: one seeded N(0,1) block of `blk` tokens per sequence, appended from device memory until every
+    # sequence has its context length
+    if w.get("ragged"):
+        from relux_b200.sharding import balanced_assignment
+        all_lens = np.random.default_rng(11).integers(1024, ctx0 + 1, B * world)
+        lens0 = all_lens[balanced_assignment(all_lens, world)[rank]].astype(np.int64)
+    else:
+        lens0 = np.full(B, ctx0, np.int64)
     blk = min(ctx0, 2048)
     src_c = orc.bf16_from_f32(rng.standard_normal((B * blk, dC), dtype=np.float32))
     src_r = orc.bf16_from_f32(rng.standard_normal((B * blk, dHR), dtype=np.float32))
     d_c, d_r = dev.upload(src_c), dev.upload(src_r)
-    for _ in range(ctx0 // blk):
-        pool.append(0, d_c, d_r, B, n_new=np.full(B, blk, np.int32))
+    for off in range(0, int(lens0.max()), blk):
+        pool.append(0, d_c, d_r, B, n_new=np.clip(lens0 - off, 0, blk).astype(np.int32))
     dev.sync()
     d_c.free(); d_r.free()
     wuk = orc.bf16_from_f32((rng.standard_normal((dC, H * Dh), dtype=np.float32) * 0.02))
@@ -234,8 +244,8 @@ def run_mla(args, w, world, rank, local, dist):
     # dominant kernel: the decode kernel; every call records a CUDA event pair around that launch on the launching
     # stream, read here for the calls of the timed region (the library keeps the last 256)
     kernel_ms, counted = pool.mean_kernel_ms(args.steps)
-    len_end = pool.seq_len(0, 0)                                  # every sequence has the same length
-    rows_mean = B * (len_end - (counted - 1) / 2.0)               # cached rows read per launch, mean over those calls
+    len_end = sum(pool.seq_len(0, b) for b in range(B))          # every sequence grew by one row per call
+    rows_mean = len_end - B * (counted - 1) / 2.0                 # cached rows read per launch, mean over those calls
     ms_e2e, _ = timed(step_e2e, args.steps, args.warmup)
     assert pool.status() == 0, "device status word is set"
     alg_bytes = rows_mean * (dC + dHR) * 2
@@ -255,9 +265,11 @@ def run_mla(args, w, world, rank, local, dist):
         "metric": "mla_layer_decode_tokens_per_s" if layer else "mla_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "batch_per_gpu": B, "context": ctx0, "heads": H, "latent": dC, "rope": dHR,
+        "config": {"workload": args.workload, "batch_per_gpu": B,
+                   "context": ("uniform[1024,%d], %d tokens on rank 0" % (ctx0, int(lens0.sum()))) if w.get("ragged") else ctx0,
+                   "heads": H, "latent": dC, "rope": dHR,
                    "page_tokens": PAGE, "page_table": "random permutation", "l2": "inputs (%.2f GB of cache rows per GPU) are larger than L2"
-                   % (B * ctx0 * (dC + dHR) * 2 / 1e9)},
+                   % (float(lens0.sum()) * (dC + dHR) * 2 / 1e9)},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": (alg_bytes * TRAFFIC_RATIO["mla"]) if TRAFFIC_RATIO["mla"] else None,
                      "peak_source": peak_src, "kernel": "mla_decode_sm100_kernel", "kernel_ms": kernel_ms, "launches_timed": counted,
