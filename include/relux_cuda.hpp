@@ -7,7 +7,8 @@
 //   relux::MLACache  <- transformer.MLACache  (internal/transformer/mla_cache.go:21-59, Append :152-182,
 //                       View :222-233, TotalLen :236-241, Reset :118-133)
 // plus Attend(), the replacement of the attention loops of MHA.forwardCached (mha.go:292-348) and
-// MLA.forwardCached (mla.go:317-377).  Where the reference panics, these throw relux::Panic with the same wording.
+// MLA.forwardCached (mla.go:317-377), and ForwardCached(), the whole of those two functions (layer input in,
+// layer output out) with the weight matrices resident on the device.  Where the reference panics, these throw relux::Panic with the same wording.
 // One object = one sequence, every layer, exactly like the reference's caches; batched serving uses the pool-level
 // C functions directly.
 #ifndef RELUX_CUDA_HPP_
@@ -149,6 +150,29 @@ class KVCache {
     a.mode = mode;
     check(relux_gqa_decode(pool_, &a));
   }
+  // MHA.forwardCached (mha.go:245-369): x, out [1, seqQ, dModel] float32; w = device copies of Wq, Wk, Wv, Wo.
+  void ForwardCached(int layerIdx, const float* x, float* out, const relux_gqa_layer_weights& w, int dModel, int numHeads, int seqQ,
+                     bool causal, bool rope, float ropeBase = 10000.f, int mode = RELUX_ATTN_FAST) {
+    relux_gqa_layer_args a{};
+    a.layer = layerIdx;
+    a.n_seqs = 1;
+    a.seq_ids = &seq_;
+    a.q_tokens = seqQ;
+    a.causal = causal ? 1 : 0;
+    a.d_model = dModel;
+    a.num_heads = numHeads;
+    a.rope = rope ? 1 : 0;
+    a.rope_base = ropeBase;
+    a.advance = 1;
+    a.mode = mode;
+    a.x = x;
+    a.x_dtype = RELUX_DTYPE_F32;
+    a.x_mem = RELUX_MEM_HOST;
+    a.out = out;
+    a.out_mem = RELUX_MEM_HOST;
+    a.w = &w;
+    check(relux_gqa_forward_cached(pool_, &a));
+  }
 
  private:
   relux_pool_t pool_ = nullptr;
@@ -236,6 +260,27 @@ class MLACache {
     a.out_layout = RELUX_LAYOUT_HEAD_MAJOR;
     a.mode = mode;
     check(relux_mla_decode(pool_, &a));
+  }
+  // MLA.forwardCached (mla.go:272-397): x, out [1, seqQ, dModel] float32; w = device copies of the seven matrices.
+  void ForwardCached(int layerIdx, const float* x, float* out, const relux_mla_layer_weights& w, int dModel, int numHeads, int seqQ,
+                     bool causal, float ropeBase = 10000.f, int mode = RELUX_ATTN_FAST) {
+    relux_mla_layer_args a{};
+    a.layer = layerIdx;
+    a.n_seqs = 1;
+    a.seq_ids = &seq_;
+    a.q_tokens = seqQ;
+    a.causal = causal ? 1 : 0;
+    a.d_model = dModel;
+    a.num_heads = numHeads;
+    a.rope_base = ropeBase;
+    a.mode = mode;
+    a.x = x;
+    a.x_dtype = RELUX_DTYPE_F32;
+    a.x_mem = RELUX_MEM_HOST;
+    a.out = out;
+    a.out_mem = RELUX_MEM_HOST;
+    a.w = &w;
+    check(relux_mla_forward_cached(pool_, &a));
   }
 
  private:

@@ -110,6 +110,25 @@ int main() {
     for (int i = 0; i < 128; i++) same = same && std::fabs(out[i] - v[i]) < 1e-3f;
     EXPECT(same, "Attend single row");
   }
+  {  // the whole layer through the mirror: with Wv = Wo = identity blocks and one cached row the output is x itself
+    // (softmax of a single score is 1, so o = v = x Wv = x, out = o Wo = x); dModel 128, one head, no RoPE.
+    const int D = 128;
+    relux::KVCache c(dev, 1, 64, 1, D);
+    std::vector<uint16_t> ident((size_t)D * D, 0), zero((size_t)D * D, 0);
+    for (int i = 0; i < D; i++) ident[(size_t)i * D + i] = 0x3F80;   // bf16 1.0
+    relux_gqa_layer_weights w;
+    w.w_q = dev.Upload(zero.data(), zero.size() * 2);
+    w.w_k = dev.Upload(zero.data(), zero.size() * 2);
+    w.w_v = dev.Upload(ident.data(), ident.size() * 2);
+    w.w_o = dev.Upload(ident.data(), ident.size() * 2);
+    std::vector<float> x(D), out(D, -1.f);
+    for (int i = 0; i < D; i++) x[i] = (float)(i % 16) * 0.25f;     // exactly representable in bf16
+    c.ForwardCached(0, x.data(), out.data(), w, D, 1, 1, true, false, 10000.f, RELUX_ATTN_REFERENCE);
+    bool same = c.TotalLen(0) == 1;
+    for (int i = 0; i < D; i++) same = same && out[i] == x[i];
+    EXPECT(same, "ForwardCached identity layer");
+    dev.Free((void*)w.w_q); dev.Free((void*)w.w_k); dev.Free((void*)w.w_v); dev.Free((void*)w.w_o);
+  }
   if (failures == 0) printf("ALL PASSED\n");
   return failures ? 1 : 0;
 }

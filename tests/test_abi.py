@@ -55,7 +55,11 @@ def test_struct_sizes_match_the_header(so):
     prog = textwrap.dedent("""
         #include <stdio.h>
         #include "relux_cuda.h"
-        int main(void){ printf("%zu %zu %zu\\n", sizeof(relux_pool_params), sizeof(relux_append_args), sizeof(relux_attn_args)); return 0; }
+        #include <stddef.h>
+        int main(void){ printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(relux_pool_params), sizeof(relux_append_args),
+                               sizeof(relux_attn_args), sizeof(relux_mla_layer_weights), sizeof(relux_mla_layer_args),
+                               sizeof(relux_gqa_layer_weights), sizeof(relux_gqa_layer_args),
+                               offsetof(relux_mla_layer_args, w), offsetof(relux_gqa_layer_args, w)); return 0; }
     """)
     with tempfile.TemporaryDirectory() as d:
         c = os.path.join(d, "s.c")
@@ -63,7 +67,9 @@ def test_struct_sizes_match_the_header(so):
         exe = os.path.join(d, "s")
         subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
         sizes = [int(x) for x in subprocess.check_output([exe]).split()]
-    assert sizes == [C.sizeof(so.PoolParams), C.sizeof(so.AppendArgs), C.sizeof(so.AttnArgs)]
+    assert sizes == [C.sizeof(so.PoolParams), C.sizeof(so.AppendArgs), C.sizeof(so.AttnArgs), C.sizeof(so.MlaLayerWeights),
+                     C.sizeof(so.MlaLayerArgs), C.sizeof(so.GqaLayerWeights), C.sizeof(so.GqaLayerArgs), so.MlaLayerArgs.w.offset,
+                     so.GqaLayerArgs.w.offset]
 
 
 def test_no_gpu_means_a_clean_error(so):

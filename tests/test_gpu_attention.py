@@ -273,3 +273,45 @@ def test_mla_query_token_counts(dev, oracle, S):
     """S <= 8 query tokens run as S workers side by side on a range; more than 8 fall back to one grid row per token."""
     out, ref = _mla_v2_case(dev, oracle, 24 + S, [S, 70, 130 + S, 777], S)
     check_attention(out, ref, "mla S=%d" % S, max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+
+
+def test_mla_verify_then_commit_accepted_prefix(dev, oracle):
+    """relux_mla_verify on the tcgen05 path: 4 draft rows written past the cursor, causal inside the draft, an accepted
+    prefix committed with set_len; cache rows stay bit-exact through the steps."""
+    rng = np.random.default_rng(41)
+    H, Dh, dC, dHR, S = 128, 128, 512, 64, 4
+    ctx = np.array([100, 64, 190], np.int32)
+    B = len(ctx)
+    pool, cl, rl = build_mla(dev, oracle, rng, ctx, dC, dHR, extra_pages=2)
+    wuk = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02)
+    wuv = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02)
+    d_wuk, d_wuv = dev.upload(wuk), dev.upload(wuv)
+    scale = float(1.0 / np.sqrt(Dh + dHR))
+    C_ = [cl[b, :ctx[b]].copy() for b in range(B)]
+    R_ = [rl[b, :ctx[b]].copy() for b in range(B)]
+    for step in range(3):
+        dc = rng.standard_normal((B * S, dC)).astype(np.float32)
+        dr = rng.standard_normal((B * S, dHR)).astype(np.float32)
+        qc = rng.standard_normal((B, S, H, Dh)).astype(np.float32)
+        qr = rng.standard_normal((B, S, H, dHR)).astype(np.float32)
+        out = np.empty_like(qc)
+        pool.verify(0, B, qc, out, dc, dr, H, Dh, scale, S, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv)
+        lens = np.array([len(c) for c in C_], np.int32)
+        Tm = int(lens.max()) + S
+        cp = np.zeros((B, Tm, dC), np.uint16); rp = np.zeros((B, Tm, dHR), np.uint16)
+        for b in range(B):
+            cp[b, :lens[b] + S] = np.concatenate([C_[b], oracle.bf16_from_f32(dc[b * S:(b + 1) * S])])
+            rp[b, :lens[b] + S] = np.concatenate([R_[b], oracle.bf16_from_f32(dr[b * S:(b + 1) * S])])
+        with oracle.exact_exp():
+            ref = oracle.mla_attend(cp, rp, lens + S, qc, qr, wuk, wuv, scale, causal=True, absorbed=True)
+        check_attention(out, ref, "mla verify step %d" % step, max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+        accepted = rng.integers(1, S + 1, B).astype(np.int32)
+        pool.set_len(0, lens + accepted)
+        for b in range(B):
+            C_[b] = cp[b, :lens[b] + accepted[b]].copy()
+            R_[b] = rp[b, :lens[b] + accepted[b]].copy()
+            assert pool.seq_len(0, b) == len(C_[b])
+            gc, gr = pool.read_rows(0, b, 0, len(C_[b]))
+            assert np.array_equal(gc, C_[b]) and np.array_equal(gr, R_[b])
+    assert pool.status() == 0
+    pool.destroy(); d_wuk.free(); d_wuv.free()
