@@ -42,6 +42,7 @@ struct GqaParams {
   float* part_o;
   float* part_ml;
   int32_t rows_total;  // S * H
+  int32_t q_tokens_total, q_token0;   // the S query tokens of this launch are tokens [q_token0, q_token0 + S) of a call with q_tokens_total
   int32_t* status;
 };
 
@@ -74,7 +75,7 @@ __global__ void __launch_bounds__(160, 1) gqa_decode_kernel(const __grid_constan
     uint32_t w = 0;
     if (r < prm.R) {
       const int s = r / prm.g, hq = r % prm.g;
-      const size_t off = (((size_t)item.seq_index * prm.S + s) * prm.H + (size_t)kvh * prm.g + hq) * kD + c;
+      const size_t off = (((size_t)item.seq_index * prm.q_tokens_total + prm.q_token0 + s) * prm.H + (size_t)kvh * prm.g + hq) * kD + c;
       if (prm.q_bf16) w = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(prm.q) + off);
       else {
         float2 f = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(prm.q) + off);
@@ -293,19 +294,17 @@ constexpr size_t gqa_smem_bytes() {
 
 }  // namespace
 
-int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, void* d_out) {
+// One launch of the decode kernel + merge for query tokens [s0, s0 + Sg) of a call with a.q_tokens tokens.
+// With the causal mask a group of tokens sees the cache as if it ended with its own last token, so the group is
+// exactly a call with q_tokens = Sg on a cache shortened by the tokens that follow it (extra_g <= a.extra_tokens).
+static int32_t launch_gqa_group(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, void* d_out, int s0, int Sg) {
   const relux_pool_params& prm = p->prm;
-  const int g = a.num_heads / prm.gqa_num_kv_heads, R = g * a.q_tokens;
-  if (!p->has_tmap || prm.page_tokens != kPageTok || prm.gqa_head_dim != kD || R > 32) {
-    set_error("GQA FAST kernel needs page_tokens=64, head_dim=128 and (num_heads/num_kv_heads)*q_tokens <= 32 "
-              "(got page_tokens=%d head_dim=%d rows=%d); use RELUX_ATTN_REFERENCE for other shapes",
-              prm.page_tokens, prm.gqa_head_dim, R);
-    return RELUX_ERR_UNSUPPORTED;
-  }
+  const int g = a.num_heads / prm.gqa_num_kv_heads, R = g * Sg;
+  const int extra_g = a.causal ? a.extra_tokens - (a.q_tokens - s0 - Sg) : a.extra_tokens;
   SplitPlan plan;
-  int32_t rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, prm.gqa_num_kv_heads, 2, 1, 0, &plan);
+  int32_t rc = plan_splitkv(p, sb, a.layer, extra_g, prm.gqa_num_kv_heads, 2, 1, 0, &plan);
   if (rc) return rc;
-  const int rows_total = a.q_tokens * a.num_heads;
+  const int rows_total = Sg * a.num_heads;
   rc = grow(p->dev, p->part_o, (size_t)plan.num_items * rows_total * kD * sizeof(float));
   if (rc) return rc;
   rc = grow(p->dev, p->part_ml, (size_t)plan.num_items * rows_total * 2 * sizeof(float));
@@ -319,10 +318,12 @@ int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   k.Hkv = prm.gqa_num_kv_heads;
   k.H = a.num_heads;
   k.g = g;
-  k.S = a.q_tokens;
+  k.S = Sg;
   k.R = R;
-  k.extra = a.extra_tokens;
+  k.extra = extra_g;
   k.causal = a.causal;
+  k.q_tokens_total = a.q_tokens;
+  k.q_token0 = s0;
   const int64_t rows_per_block = (int64_t)prm.num_pages * prm.gqa_num_kv_heads * kPageTok;
   k.krow0 = (int32_t)((int64_t)a.layer * 2 * rows_per_block);
   k.vrow0 = (int32_t)((int64_t)a.layer * 2 * rows_per_block + rows_per_block);
@@ -349,7 +350,26 @@ int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), st));
   p->timed_calls++;
   count_launch(p->dev);
-  return launch_merge(p, plan, sb.n_seqs, rows_total, kD, (float*)d_out, nullptr);
+  return launch_merge_rows(p, plan, sb.n_seqs, rows_total, kD, (float*)d_out, a.q_tokens * a.num_heads, s0 * a.num_heads);
+}
+
+int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, void* d_out) {
+  const relux_pool_params& prm = p->prm;
+  const int g = a.num_heads / prm.gqa_num_kv_heads;
+  if (!p->has_tmap || prm.page_tokens != kPageTok || prm.gqa_head_dim != kD || g > 32) {
+    set_error("GQA FAST kernel needs page_tokens=64, head_dim=128 and num_heads/num_kv_heads <= 32 "
+              "(got page_tokens=%d head_dim=%d group=%d); use RELUX_ATTN_REFERENCE for other shapes",
+              prm.page_tokens, prm.gqa_head_dim, g);
+    return RELUX_ERR_UNSUPPORTED;
+  }
+  // the kernel holds (num_heads / num_kv_heads) * q_tokens <= 32 query rows per kv head; longer multi-token calls
+  // (a prompt) run as consecutive groups of tokens
+  const int per_group = std::max(1, 32 / g);
+  for (int s0 = 0; s0 < a.q_tokens; s0 += per_group) {
+    int32_t rc = launch_gqa_group(p, sb, a, d_q, d_out, s0, std::min(per_group, a.q_tokens - s0));
+    if (rc) return rc;
+  }
+  return RELUX_OK;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -489,6 +509,8 @@ extern "C" __attribute__((visibility("default"))) int32_t relux_gqa_decode_noall
   k.R = R;
   k.extra = a->extra_tokens;
   k.causal = a->causal;
+  k.q_tokens_total = a->q_tokens;
+  k.q_token0 = 0;
   const int64_t rows_per_block = (int64_t)prm.num_pages * prm.gqa_num_kv_heads * kPageTok;
   k.krow0 = (int32_t)((int64_t)a->layer * 2 * rows_per_block);
   k.vrow0 = (int32_t)((int64_t)a->layer * 2 * rows_per_block + rows_per_block);

@@ -601,10 +601,10 @@ int32_t do_gqa_layer(Pool* p, const relux_gqa_layer_args* a) {
   if (a->rope && hd % 2 != 0) { set_error("NewRotaryEmbedding: headDim=%d, must be even and > 0", hd); return RELUX_ERR_INVALID_ARG; }
   if (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE) { set_error("bad mode"); return RELUX_ERR_INVALID_ARG; }
   if (a->x_dtype != RELUX_DTYPE_F32) { set_error("x must be float32"); return RELUX_ERR_UNSUPPORTED; }
-  if (a->mode == RELUX_ATTN_FAST && (!p->has_tmap || prm.page_tokens != 64 || hd != 128 || (H / Hkv) * S > 32)) {
+  if (a->mode == RELUX_ATTN_FAST && (!p->has_tmap || prm.page_tokens != 64 || hd != 128 || H / Hkv > 32)) {
     // checked before anything is written to the cache
-    set_error("GQA FAST kernels need page_tokens=64, head_dim=128 and (num_heads/num_kv_heads)*q_tokens <= 32 "
-              "(got page_tokens=%d head_dim=%d rows=%d); use RELUX_ATTN_REFERENCE for other shapes", prm.page_tokens, hd, (H / Hkv) * S);
+    set_error("GQA FAST kernels need page_tokens=64, head_dim=128 and num_heads/num_kv_heads <= 32 "
+              "(got page_tokens=%d head_dim=%d group=%d); use RELUX_ATTN_REFERENCE for other shapes", prm.page_tokens, hd, H / Hkv);
     return RELUX_ERR_UNSUPPORTED;
   }
   const float rope_base = a->rope_base == 0.f ? 10000.f : a->rope_base;

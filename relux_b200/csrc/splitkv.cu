@@ -227,9 +227,11 @@ int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int worke
 //   M = max_c m_c,  L = sum_c l_c 2^(m_c - M),  O = sum_c O_c 2^(m_c - M) / L
 // part_o [item][rows][width] f32 holds UNNORMALISED accumulators, part_ml [item][rows][2] = (m, l) with m in
 // the log2 domain.  grid (rows, n_seqs); out row stride and placement given by the caller.
+// The rows of sequence i land at out row i * out_rows + out_row0 + r (out_rows = rows, out_row0 = 0 unless the launch
+// covers only some of a call's query tokens).
 __global__ void merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const int32_t* __restrict__ chunk_off, int rows, int width, float* __restrict__ out,
-                                    uint16_t* __restrict__ out_bf16) {
+                                    uint16_t* __restrict__ out_bf16, int out_rows, int out_row0) {
   const int r = blockIdx.x, i = blockIdx.y;
   const int c0 = chunk_off[i], c1 = chunk_off[i + 1];
   float M = -INFINITY;
@@ -246,7 +248,7 @@ __global__ void merge_splits_kernel(const float* __restrict__ part_o, const floa
       const float m = part_ml[((size_t)c * rows + r) * 2];
       acc += part_o[((size_t)c * rows + r) * width + d] * exp2f(m - M);
     }
-    const size_t o = ((size_t)i * rows + r) * width + d;
+    const size_t o = ((size_t)i * out_rows + out_row0 + r) * width + d;
     if (out) out[o] = acc * inv;
     if (out_bf16) out_bf16[o] = bf16_bits_from_f32(acc * inv);
   }
@@ -255,7 +257,16 @@ __global__ void merge_splits_kernel(const float* __restrict__ part_o, const floa
 int32_t launch_merge(Pool* p, const SplitPlan& plan, int n_seqs, int rows, int width, float* out, uint16_t* out_bf16) {
   dim3 grid(rows, n_seqs);
   merge_splits_kernel<<<grid, 128, 0, p->dev->stream>>>((const float*)p->part_o.p, (const float*)p->part_ml.p, plan.chunk_off, rows,
-                                                        width, out, out_bf16);
+                                                        width, out, out_bf16, rows, 0);
+  RELUX_CUDA_TRY(cudaGetLastError());
+  count_launch(p->dev);
+  return RELUX_OK;
+}
+
+int32_t launch_merge_rows(Pool* p, const SplitPlan& plan, int n_seqs, int rows, int width, float* out, int out_rows, int out_row0) {
+  dim3 grid(rows, n_seqs);
+  merge_splits_kernel<<<grid, 128, 0, p->dev->stream>>>((const float*)p->part_o.p, (const float*)p->part_ml.p, plan.chunk_off, rows,
+                                                        width, out, nullptr, out_rows, out_row0);
   RELUX_CUDA_TRY(cudaGetLastError());
   count_launch(p->dev);
   return RELUX_OK;
@@ -271,7 +282,7 @@ int32_t launch_build_worklist_raw(cudaStream_t st, const int32_t* len, const int
 int32_t launch_merge_raw(cudaStream_t st, const float* part_o, const float* part_ml, const int32_t* chunk_off, int n_seqs, int rows,
                          int width, float* out) {
   dim3 grid(rows, n_seqs);
-  merge_splits_kernel<<<grid, 128, 0, st>>>(part_o, part_ml, chunk_off, rows, width, out, nullptr);
+  merge_splits_kernel<<<grid, 128, 0, st>>>(part_o, part_ml, chunk_off, rows, width, out, nullptr, rows, 0);
   RELUX_CUDA_TRY(cudaGetLastError());
   return RELUX_OK;
 }

@@ -47,5 +47,7 @@ int32_t launch_build_worklist_raw(cudaStream_t st, const int32_t* len, const int
 int32_t launch_merge_raw(cudaStream_t st, const float* part_o, const float* part_ml, const int32_t* chunk_off, int n_seqs, int rows,
                          int width, float* out);
 int32_t launch_merge(Pool* p, const SplitPlan& plan, int n_seqs, int rows, int width, float* out, uint16_t* out_bf16);
+// Same, for a launch that covers `rows` of the `out_rows` output rows of every sequence, starting at row out_row0.
+int32_t launch_merge_rows(Pool* p, const SplitPlan& plan, int n_seqs, int rows, int width, float* out, int out_rows, int out_row0);
 
 }  // namespace relux

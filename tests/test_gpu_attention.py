@@ -315,3 +315,23 @@ def test_mla_verify_then_commit_accepted_prefix(dev, oracle):
             assert np.array_equal(gc, C_[b]) and np.array_equal(gr, R_[b])
     assert pool.status() == 0
     pool.destroy(); d_wuk.free(); d_wuv.free()
+
+
+@pytest.mark.parametrize("causal", [True, False])
+def test_gqa_fast_prompt_longer_than_one_group(dev, oracle, causal):
+    """A multi-token cached call with more query rows than one kernel launch holds (a prompt: 40 tokens x 4 heads per
+    kv head): the FAST path runs it as consecutive groups of 8 tokens."""
+    rng = np.random.default_rng(51)
+    H, Hkv, D, S = 32, 8, 128, 40
+    ctx = [S, 70 + S, 200]
+    pool, Kl, Vl = build_gqa(dev, oracle, rng, ctx, Hkv, D)
+    B = len(ctx)
+    q = rng.standard_normal((B, S, H, D)).astype(np.float32)
+    out = np.empty_like(q)
+    scale = float(1.0 / np.sqrt(D))
+    pool.decode(0, B, q, out, H, D, scale, q_tokens=S, causal=causal)
+    with oracle.exact_exp():
+        ref = oracle.gqa_attend(Kl, Vl, ctx, q, scale, causal=causal)
+    check_attention(out, ref, "gqa prompt causal=%s" % causal, max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+    assert pool.status() == 0
+    pool.destroy()
