@@ -18,6 +18,7 @@ FLAG_MLA_BF16_CACHE = 1
 
 MHA_HOOK = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float),
                        C.POINTER(C.c_float), C.POINTER(C.c_float))
+LAYER_HOOK = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float))
 MLA_HOOK = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float),
                        C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float))
 
@@ -280,6 +281,12 @@ class Model:
         b = MLA_HOOK(mla) if mla else C.cast(None, MLA_HOOK)
         self._hooks = (a, b)  # keep alive
         lib().ro_model_set_hooks(C.c_void_p(self.h), a, b, None)
+
+    def set_layer_hook(self, fn):
+        """fn(user, layer, S, x_ptr, out_ptr) -> int replaces the whole cached attention layer forward."""
+        h = LAYER_HOOK(fn) if fn else C.cast(None, LAYER_HOOK)
+        self._layer_hook = h  # keep alive
+        lib().ro_model_set_layer_hook(C.c_void_p(self.h), h)
 
     def begin(self):
         lib().ro_model_begin(C.c_void_p(self.h))

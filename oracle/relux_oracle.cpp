@@ -519,6 +519,8 @@ typedef int (*ro_mha_hook)(void* user, int layer, int S, int startPos, const flo
 // MLA: qc [H,S,Dh], qr [H,S,dHR] (post-RoPE), ckv [S,dC], kr [S,dHR] (post-RoPE) -> out [H,S,Dh]
 typedef int (*ro_mla_hook)(void* user, int layer, int S, int startPos, const float* qc, const float* qr,
                            const float* ckv, const float* kr, float* out);
+// Whole attention layer (MHA.forwardCached / MLA.forwardCached): x [S, dModel] -> out [S, dModel].
+typedef int (*ro_layer_hook)(void* user, int layer, int S, const float* x, float* out);
 
 // ----------------------------------------------------------------------------
 // Attention core shared by the cached paths: per head, S = QK^T * scale (+mask),
@@ -585,6 +587,7 @@ struct Model {
   // intended-mode caches: per layer [Hkv][maxLen][D] bf16 for K and V
   std::vector<std::vector<uint16_t>> ik, iv; std::vector<int> ilen;
   ro_mha_hook mhaHook = nullptr; ro_mla_hook mlaHook = nullptr; void* hookUser = nullptr;
+  ro_layer_hook layerHook = nullptr;
   int status = 0;
 };
 RO_API int64_t ro_model_weight_count(const ModelCfg* c) {
@@ -651,6 +654,7 @@ RO_API void ro_model_set_mode(void* p, int mode, int flags) { Model* m = (Model*
 RO_API void ro_model_set_hooks(void* p, ro_mha_hook a, ro_mla_hook b, void* user) {
   Model* m = (Model*)p; m->mhaHook = a; m->mlaHook = b; m->hookUser = user;
 }
+RO_API void ro_model_set_layer_hook(void* p, ro_layer_hook h) { ((Model*)p)->layerHook = h; }
 RO_API int ro_model_status(void* p) { return ((Model*)p)->status; }
 
 // rmsnorm.go:69-97 with gamma = 1 (stored bf16 1.0), eps = 1e-5 fixed in blocks
@@ -830,8 +834,9 @@ static int model_forward(Model* m, const int* tokens, int seq, float* logits) {
   }
   for (int l = 0; l < m->cfg.numLayers; l++) {
     rmsnorm(normed.data(), h.data(), seq, D, 1e-5f);
-    int rc = m->cfg.mla ? mla_forward_cached(m, l, attn.data(), normed.data(), seq)
-                        : mha_forward_cached(m, l, attn.data(), normed.data(), seq);
+    int rc = m->layerHook ? m->layerHook(m->hookUser, l, seq, normed.data(), attn.data())
+             : m->cfg.mla ? mla_forward_cached(m, l, attn.data(), normed.data(), seq)
+                          : mha_forward_cached(m, l, attn.data(), normed.data(), seq);
     if (rc) return rc;
     for (size_t i = 0; i < (size_t)seq * D; i++) post[i] = h[i] + attn[i];
     rmsnorm(normed.data(), post.data(), seq, D, 1e-5f);

@@ -157,3 +157,69 @@ class GpuAttention:
         if self.cfg.mla:
             for a, b in self.w:
                 a.free(); b.free()
+
+
+def layer_weight_arrays(cfg, weights):
+    """Per layer, the attention weight matrices as slices of the flat buffer (order documented in
+    oracle/relux_oracle.cpp, ro_model_new), keyed like the arguments of Pool.forward_cached."""
+    D, H, F, V = cfg.dModel, cfg.numHeads, cfg.dFF, cfg.vocab
+    hd = D // H
+    off = V * D
+    out = []
+
+    def take(n):
+        nonlocal off
+        a = weights[off:off + n]
+        off += n
+        return a
+
+    for _ in range(cfg.numLayers):
+        if cfg.mla:
+            d = {"w_q": take(D * H * hd), "w_dkv": take(D * cfg.dC), "w_uk": take(cfg.dC * H * hd), "w_uv": take(cfg.dC * H * hd),
+                 "w_kr": take(D * cfg.dHR), "w_qr": take(D * H * cfg.dHR), "w_o": take(H * hd * D)}
+        else:
+            d = {"w_q": take(D * H * hd), "w_k": take(D * cfg.numKVHeads * hd), "w_v": take(D * cfg.numKVHeads * hd), "w_o": take(H * hd * D)}
+        out.append(d)
+        off += D * F * (2 if cfg.swiglu else 1) + F * D
+    return out
+
+
+class GpuLayer:
+    """Plugs the CUDA library into the oracle's decoder forward one level higher than GpuAttention: the whole
+    MHA.forwardCached / MLA.forwardCached (projections, RoPE, cache append, attention, output projection) is one
+    relux_*_forward_cached call; norms, MLP, lm head and the greedy pick stay the CPU restatement."""
+
+    def __init__(self, dev, cfg, weights, mode, page_tokens=64):
+        import relux_b200 as rb
+        from relux_b200 import lib as L
+        self.cfg, self.mode, self.dev, self.error = cfg, mode, dev, None
+        pages = (cfg.maxSeqLen + page_tokens - 1) // page_tokens
+        hd = cfg.dModel // cfg.numHeads
+        if cfg.mla:
+            self.pool = rb.Pool(dev, L.POOL_MLA, cfg.numLayers, pages, page_tokens, 1, pages, dC=cfg.dC, dHR=cfg.dHR)
+        else:
+            self.pool = rb.Pool(dev, L.POOL_GQA, cfg.numLayers, pages, page_tokens, 1, pages, num_kv_heads=cfg.numKVHeads, head_dim=hd)
+        self.pool.set_tables(np.arange(pages, dtype=np.int32)[::-1].copy().reshape(1, pages))
+        self.w = [{k: dev.upload(np.ascontiguousarray(v)) for k, v in d.items()} for d in layer_weight_arrays(cfg, weights)]
+
+    def hook(self, user, layer, S, x, out):
+        cfg = self.cfg
+        try:
+            xa = np.ctypeslib.as_array(x, shape=(1, S, cfg.dModel))
+            oa = np.ctypeslib.as_array(out, shape=(1, S, cfg.dModel))
+            res = np.empty((1, S, cfg.dModel), np.float32)
+            # the model's MLA rotary embedding has base 10000 (transformer_block.go:70-75); MHA uses the configured base
+            base = 10000.0 if cfg.mla else float(cfg.ropeBase)
+            self.pool.forward_cached(layer, 1, np.ascontiguousarray(xa), res, self.w[layer], cfg.dModel, cfg.numHeads, q_tokens=S,
+                                     causal=bool(cfg.causal), rope_base=base, mode=self.mode)
+            oa[...] = res
+            return 0
+        except Exception as e:  # noqa: BLE001 - must not propagate through the C callback
+            self.error = e
+            return -100
+
+    def close(self):
+        self.pool.destroy()
+        for d in self.w:
+            for b in d.values():
+                b.free()

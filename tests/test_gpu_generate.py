@@ -6,7 +6,7 @@ import os
 import numpy as np
 import pytest
 
-from tests.helpers import GpuAttention, model_config, model_weights, prompts_for
+from tests.helpers import GpuAttention, GpuLayer, model_config, model_weights, prompts_for
 
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
@@ -71,3 +71,38 @@ def test_config2_fast_mode_first_tokens(oracle, dev):
     agree = next((i for i in range(96) if ids[i] != gold[i]), 96)
     print("FAST mode agrees with the oracle for %d of 64 generated tokens" % (agree - 32))
     assert agree >= 32 + 1
+
+
+def _generate_layer_level(oracle, dev, name, prompt, n_new, mode):
+    cfg = model_config(name)
+    w = model_weights(cfg)
+    lay = GpuLayer(dev, cfg, w, mode)
+    m = oracle.Model(cfg, w)
+    m.set_mode(oracle.INTENDED)
+    m.set_layer_hook(lay.hook)
+    try:
+        ids, margins, ties = m.generate(prompt, n_new)
+    except RuntimeError:
+        raise lay.error or RuntimeError("hooked forward failed")
+    finally:
+        lay.close()
+    return ids
+
+
+def test_config1_greedy_ids_identical_with_the_whole_layer_on_the_gpu(oracle, dev):
+    """Generate with relux_gqa_forward_cached in place of MHA.forwardCached (projections, RoPE, append, attention, Wo on the
+    device, reference-order arithmetic): the 56 greedy ids equal the oracle's."""
+    from relux_b200 import lib as L
+    g = json.load(open(os.path.join(GOLD, "config1_generate.json")))
+    ids = _generate_layer_level(oracle, dev, "config1", prompts_for("config1")[0], 56, L.ATTN_REFERENCE)
+    assert ids.tolist() == g["runs"]["intended"]["ids"][0]
+
+
+def test_config2_greedy_ids_identical_with_the_whole_layer_on_the_gpu(oracle, dev):
+    """Same for the MLA decoder (relux_mla_forward_cached in place of MLA.forwardCached), first prompt, 480 new tokens."""
+    from relux_b200 import lib as L
+    g = json.load(open(os.path.join(GOLD, "config2_generate.json")))
+    ids = _generate_layer_level(oracle, dev, "config2", prompts_for("config2")[0], 480, L.ATTN_REFERENCE)
+    gold = g["runs"]["intended_bf16_cache"]["ids"][0]
+    first = next((i for i in range(len(gold)) if ids[i] != gold[i]), None)
+    assert first is None, "diverges at position %d" % first
