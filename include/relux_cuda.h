@@ -315,6 +315,15 @@ int32_t relux_gqa_forward_cached(relux_pool_t pool, const relux_gqa_layer_args* 
  *     copies aside) would overwrite each other's partials: run calls of this entry point one after another. */
 int32_t relux_gqa_decode_noalloc(relux_pool_t pool, const relux_attn_args* args);
 
+/* One sequence's cache as a file in the layout of the reference's file-backed caches: NewKVCacheFile
+ * (kvcache.go:104-166: per layer K [1, numKVHeads, maxLen, headDim] then V, bf16) or NewMLACacheFile
+ * (mla_cache.go:63-113: per layer C_KV [1, maxLen, dC] then K_R [1, maxLen, dHR], float32).  Rows past a layer's
+ * length are zeros.  Like the reference's files these hold no lengths: relux_seq_load_file takes the per-layer lengths
+ * (host [num_layers]) from the caller, resets the sequence and appends the rows (MLA rows are rounded to bf16 with the
+ * reference's rule).  max_len is the maxLen the file was / is to be made with (>= every layer's length). */
+int32_t relux_seq_save_file(relux_pool_t pool, int32_t seq_id, const char* path, int32_t max_len);
+int32_t relux_seq_load_file(relux_pool_t pool, int32_t seq_id, const char* path, int32_t max_len, const int32_t* layer_len);
+
 /* Device-time of the dominant attention kernel of the most recent relux_*_decode / verify call on this
  * pool, measured with CUDA events around that one launch.  Synchronises the stream. */
 int32_t relux_pool_last_kernel_ms(relux_pool_t pool, float* ms);

@@ -15,6 +15,8 @@ operation is a call into the shared library.
 """
 import ctypes as C
 
+import os
+
 import numpy as np
 
 from . import lib as L
@@ -313,6 +315,15 @@ class Pool:
         ms = C.c_float()
         L.check(self.lib.relux_pool_last_kernel_ms(self.h, C.byref(ms)))
         return ms.value
+
+    def save_file(self, seq, path, max_len):
+        """Writes sequence `seq` in the layout of the reference's NewKVCacheFile / NewMLACacheFile."""
+        L.check(self.lib.relux_seq_save_file(self.h, int(seq), os.fsencode(path), int(max_len)))
+
+    def load_file(self, seq, path, max_len, layer_len):
+        """Resets sequence `seq` and fills it from such a file; layer_len[l] rows are taken for layer l."""
+        ll = np.ascontiguousarray(layer_len, dtype=np.int32)
+        L.check(self.lib.relux_seq_load_file(self.h, int(seq), os.fsencode(path), int(max_len), ll.ctypes.data))
 
     def mean_projection_ms(self, last_n):
         """(mean device time of the input-projection GEMM over the last `last_n` forward_cached calls, calls counted)."""
