@@ -280,8 +280,11 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   if (rc) return rc;
   rc = grow(p->dev, p->part_ml, (size_t)plan.num_items * rows_total * 2 * sizeof(float));
   if (rc) return rc;
-  rc = grow(p->dev, p->o_lat, (size_t)rows * H * dC * sizeof(float));
-  if (rc) return rc;
+  const bool fused_merge = proj_mma && dC <= 512 && !getenv("RELUX_MLA_UNFUSED_MERGE");
+  if (!fused_merge) {   // the unfused paths hand the merged latent output to the up-projection through this buffer
+    rc = grow(p->dev, p->o_lat, (size_t)rows * H * dC * sizeof(float));
+    if (rc) return rc;
+  }
   RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), st));
   if (sm100) {
     rc = t256 ? launch_mla_decode_sm100_t256(p, sb, a, plan, (const uint16_t*)p->q_abs.p)
@@ -319,7 +322,7 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), st));
   p->timed_calls++;
   count_launch(p->dev);
-  if (proj_mma && dC <= 512 && !getenv("RELUX_MLA_UNFUSED_MERGE")) {
+  if (fused_merge) {
     // split-KV merge fused into the up-projection: the merged latent output never touches HBM
     rc = launch_mla_merge_vup_mma(p->dev, (const float*)p->part_o.p, (const float*)p->part_ml.p, plan.chunk_off, (const uint16_t*)a.w_uv,
                                   (float*)d_out, rows, S, H, dC);
