@@ -28,6 +28,8 @@ WORKLOADS = {
     # name: (kind, batch per GPU, context, heads, head_dim, dC, dHR)
     "mla_decode_b64_ctx32k": dict(kind="mla", B=64, ctx=32768, H=128, Dh=128, dC=512, dHR=64),
     "mla_decode_b64_ctx4k": dict(kind="mla", B=64, ctx=4096, H=128, Dh=128, dC=512, dHR=64),
+    # the reference's own MLA example shape (mla_test.go:96-101: d_model 4096, 32 heads of 128, latent 512, rope 64)
+    "mla_decode_h32_b64_ctx32k": dict(kind="mla", B=64, ctx=32768, H=32, Dh=128, dC=512, dHR=64),
     # config 4 per GPU: 16 sequences with context lengths uniform in [1024, 32768] (one global seeded draw of 16 x world
     # lengths, dealt to the ranks longest-first so that every GPU holds about the same number of cached tokens)
     "mla_decode_ragged_b16": dict(kind="mla", B=16, ctx=32768, H=128, Dh=128, dC=512, dHR=64, ragged=True),

@@ -44,7 +44,7 @@ namespace relux {
 
 namespace {
 
-constexpr int kHeads = 128, kDC = 512, kDR = 64, kRow = kDC + kDR;  // 576
+constexpr int kMaxHeads = 128, kDC = 512, kDR = 64, kRow = kDC + kDR;  // 576
 constexpr int kPage = 64;
 constexpr int kBlk = 8192;                  // one [64 rows x 64 cols] bf16 block, 128-byte swizzled
 constexpr int kNumKB = kRow / 64;           // 9 column blocks per row
@@ -78,6 +78,8 @@ struct MlaSm100Params {
   const int32_t* table;
   int32_t table_stride;
   int32_t num_pages, S, sx, causal;   // sx: query tokens interleaved along grid x (their workers share the range through L2)
+  int32_t H;                          // query heads, <= 128: the M = 128 tile is padded with whatever rows follow in q~
+                                      // (finite values, computed and thrown away; rows past the end of q~ are zero-filled by TMA)
   int32_t layer_row0;
   float scale_log2;
   float* part_o;
@@ -186,7 +188,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
     };
     // g = worker-wide index of the tile being loaded
     auto load_q = [&](const StreamItem& it) {
-      const int qrow = (it.seq_index * prm.S + sq) * kHeads + 64 * (int)rank;   // Q~ rows of this CTA's 64 heads
+      const int qrow = (it.seq_index * prm.S + sq) * prm.H + 64 * (int)rank;   // Q~ rows of this CTA's 64 heads
       if (el) {
         if (rank == 0) mbar_expect_tx(&bars->q_full, 2 * kNumKB * kBlk);
 #pragma unroll
@@ -436,8 +438,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
       tc_fence_after();
       if (hf == 1) bars->lsum[row] = l_run;
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      const size_t prow = (size_t)it * prm.rows_total + (size_t)sq * kHeads + 64 * rank + row;
-      if (hf == 0) {
+      const bool real_head = 64 * (int)rank + row < prm.H;   // padding rows of the tile are not written
+      const size_t prow = (size_t)it * prm.rows_total + (size_t)sq * prm.H + 64 * rank + row;
+      if (hf == 0 && real_head) {
         prm.part_ml[prow * 2] = ok ? m_used : -INFINITY;
         prm.part_ml[prow * 2 + 1] = ok ? (l_run + bars->lsum[row]) : 0.f;
       }
@@ -455,10 +458,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
             for (int j = 0; j < 32; j++) ov[j] = 0u;
           }
           float4* dst = reinterpret_cast<float4*>(orow + 256 * nb + 128 * hf + c);
+          if (real_head) {
 #pragma unroll
-          for (int j = 0; j < 8; j++)
-            dst[j] = make_float4(__uint_as_float(ov[4 * j]), __uint_as_float(ov[4 * j + 1]), __uint_as_float(ov[4 * j + 2]),
-                                 __uint_as_float(ov[4 * j + 3]));
+            for (int j = 0; j < 8; j++)
+              dst[j] = make_float4(__uint_as_float(ov[4 * j]), __uint_as_float(ov[4 * j + 1]), __uint_as_float(ov[4 * j + 2]),
+                                   __uint_as_float(ov[4 * j + 3]));
+          }
         }
       tc_fence_before();   // the O read-out is ordered before this thread's next p_full arrival, which releases the first PV of the next item
       cur = nxt;
@@ -474,7 +479,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 bool mla_sm100_eligible(const Pool* p, const relux_attn_args& a) {
   const relux_pool_params& prm = p->prm;
   if (getenv("RELUX_MLA_GENERIC")) return false;
-  return p->has_tmap && p->mla_blocked && prm.page_tokens == kPage && prm.mla_dc == kDC && prm.mla_dhr == kDR && a.num_heads == kHeads;
+  // fewer than 128 heads run on the same M = 128 tile (padded); below 16 heads the CUDA-core kernel is the better fit
+  return p->has_tmap && p->mla_blocked && prm.page_tokens == kPage && prm.mla_dc == kDC && prm.mla_dhr == kDR && a.num_heads <= kMaxHeads &&
+         a.num_heads >= 16;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -525,7 +532,7 @@ int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_ar
   }
   CUtensorMap tq;
   {
-    const uint64_t rows = (uint64_t)sb.n_seqs * a.q_tokens * kHeads;
+    const uint64_t rows = (uint64_t)sb.n_seqs * a.q_tokens * a.num_heads;
     cuuint64_t dims[2] = {kRow, rows};
     cuuint64_t strides[1] = {kRow * 2};
     cuuint32_t box[2] = {64, 64};
@@ -550,7 +557,8 @@ int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_ar
   k.scale_log2 = a.scale * 1.4426950408889634f;
   k.part_o = (float*)p->part_o.p;
   k.part_ml = (float*)p->part_ml.p;
-  k.rows_total = a.q_tokens * kHeads;
+  k.rows_total = a.q_tokens * a.num_heads;
+  k.H = a.num_heads;
   k.status = p->d_status;
   RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_decode_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
   dim3 grid(2 * plan.num_workers * sx, a.q_tokens / sx);

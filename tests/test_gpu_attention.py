@@ -233,9 +233,9 @@ def test_head_major_layout_round_trip(dev, oracle):
     c.close()
 
 
-def _mla_v2_case(dev, oracle, seed, ctx, S, causal=True):
+def _mla_v2_case(dev, oracle, seed, ctx, S, causal=True, H=128):
     rng = np.random.default_rng(seed)
-    H, Dh, dC, dHR = 128, 128, 512, 64
+    Dh, dC, dHR = 128, 512, 64
     B = len(ctx)
     pool, cl, rl = build_mla(dev, oracle, rng, ctx, dC, dHR)
     wuk = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02)
@@ -335,3 +335,13 @@ def test_gqa_fast_prompt_longer_than_one_group(dev, oracle, causal):
     check_attention(out, ref, "gqa prompt causal=%s" % causal, max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
     assert pool.status() == 0
     pool.destroy()
+
+
+@pytest.mark.parametrize("H", [16, 32, 64, 96])
+def test_mla_fewer_than_128_heads_on_the_tensor_path(dev, oracle, H):
+    """Head counts below 128 (the reference's own MLA example has 32: mla_test.go:96-101) run on the same M = 128
+    tcgen05 tile, padded; the padding rows must not leak into any output."""
+    out, ref = _mla_v2_case(dev, oracle, 60 + H, [1, 64, 130, 515], 1, H=H)
+    check_attention(out, ref, "mla H=%d" % H, max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+    out, ref = _mla_v2_case(dev, oracle, 61 + H, [2, 200], 2, H=H)
+    check_attention(out, ref, "mla H=%d S=2" % H, max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
