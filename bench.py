@@ -155,7 +155,7 @@ def run_mla(args, w, world, rank, local, dist):
     if w.get("ragged"):
         from relux_b200.sharding import balanced_assignment
         all_lens = np.random.default_rng(11).integers(1024, ctx0 + 1, B * world)
-        lens0 = all_lens[balanced_assignment(all_lens, world)[rank]].astype(np.int64)
+        lens0 = all_lens[balanced_assignment(all_lens, world, per_rank=B)[rank]].astype(np.int64)
     else:
         lens0 = np.full(B, ctx0, np.int64)
     blk = min(ctx0, 2048)

@@ -11,14 +11,18 @@ def shard_range(n_items, world, rank):
     return begin, begin + base + (1 if rank < rem else 0)
 
 
-def balanced_assignment(lengths, world):
+def balanced_assignment(lengths, world, per_rank=None):
     """Greedy longest-first assignment of sequences to ranks by context length (for ragged batches):
-    returns a list of index lists, one per rank."""
+    returns a list of index lists, one per rank.  With `per_rank` every rank receives at most that many
+    sequences (a rank whose pool has a fixed number of sequence slots)."""
+    if per_rank is not None and per_rank * world < len(lengths):
+        raise ValueError("%d sequences do not fit %d ranks of %d slots" % (len(lengths), world, per_rank))
     order = sorted(range(len(lengths)), key=lambda i: -int(lengths[i]))
     loads = [0] * world
     out = [[] for _ in range(world)]
     for i in order:
-        r = loads.index(min(loads))
+        open_ranks = [r for r in range(world) if per_rank is None or len(out[r]) < per_rank]
+        r = min(open_ranks, key=lambda k: loads[k])
         out[r].append(i)
         loads[r] += int(lengths[i])
     return out

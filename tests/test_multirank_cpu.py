@@ -7,6 +7,7 @@ import sys
 import textwrap
 
 import numpy as np
+import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -32,6 +33,13 @@ def test_balanced_assignment_of_ragged_lengths():
     assert sorted(i for p in parts for i in p) == list(range(128))
     loads = [int(lens[p].sum()) for p in parts]
     assert (max(loads) - min(loads)) / max(loads) < 0.02
+    # with a fixed number of sequence slots per rank (the benchmark's pools hold 16 sequences each)
+    parts = balanced_assignment(lens, 8, per_rank=16)
+    assert sorted(i for p in parts for i in p) == list(range(128)) and all(len(p) == 16 for p in parts)
+    loads = [int(lens[p].sum()) for p in parts]
+    assert (max(loads) - min(loads)) / max(loads) < 0.05
+    with pytest.raises(ValueError):
+        balanced_assignment(lens, 4, per_rank=16)
 
 
 def test_two_gloo_ranks_shard_and_reduce_timings():
