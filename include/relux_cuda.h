@@ -324,6 +324,15 @@ int32_t relux_gqa_decode_noalloc(relux_pool_t pool, const relux_attn_args* args)
 int32_t relux_seq_save_file(relux_pool_t pool, int32_t seq_id, const char* path, int32_t max_len);
 int32_t relux_seq_load_file(relux_pool_t pool, int32_t seq_id, const char* path, int32_t max_len, const int32_t* layer_len);
 
+/* The stream partition the persistent MLA decode kernel works on, computed on the host from page counts (no device
+ * needed): the pages of all sequences, laid end to end, are cut into ranges of range_pages_out pages (a multiple of
+ * page_multiple), one range per worker; an item is the part of one sequence inside one range.
+ * items_out: n x {seq_index, page_begin, page_end, worker} (cap items of room), worker_first [*workers_out + 1],
+ * chunk_off [n_seqs + 1]; any of the three may be NULL.  Returns the number of items, -1 on bad arguments or when cap
+ * is too small.  Scheduling aid: no counterpart in the reference. */
+int32_t relux_stream_partition(const int32_t* pages, int32_t n_seqs, int32_t workers, int32_t page_multiple, int32_t* range_pages_out,
+                               int32_t* workers_out, int32_t* items_out, int32_t cap, int32_t* worker_first, int32_t* chunk_off);
+
 /* Device-time of the dominant attention kernel of the most recent relux_*_decode / verify call on this
  * pool, measured with CUDA events around that one launch.  Synchronises the stream. */
 int32_t relux_pool_last_kernel_ms(relux_pool_t pool, float* ms);

@@ -183,27 +183,39 @@ __global__ void build_stream_kernel(const int32_t* __restrict__ len, const int32
   for (int w = (page_base + G - 1) / G + threadIdx.x; w <= workers; w += blockDim.x) worker_first[w] = item_base;
 }
 
-int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int workers, int page_multiple, SplitPlan* plan) {
-  const relux_pool_params& prm = p->prm;
+// Host statement of the stream partition: range length G and the counts that follow from it.  The device builder
+// (build_stream_kernel) applies the same arithmetic to the device-resident lengths.
+void stream_partition_shape(const int* pages, int n_seqs, int workers, int page_multiple, long chunk_override, long* G_out,
+                            int* workers_out, int* items_out) {
   long total = 0;
-  std::vector<int> pages(sb.n_seqs);
-  for (int i = 0; i < sb.n_seqs; i++) {
-    const int T = p->h_len[(size_t)layer * prm.max_seqs + sb.seq[i]] + extra;
-    pages[i] = (T + prm.page_tokens - 1) / prm.page_tokens;
-    total += pages[i];
-  }
+  for (int i = 0; i < n_seqs; i++) total += pages[i];
   workers = std::max(1, workers);
   const int mult = std::max(1, page_multiple);
   long G = (total + workers - 1) / workers;
   G = std::max<long>((G + mult - 1) / mult * mult, 2L * mult);   // at least two tiles per range
-  if (const char* ov = getenv("RELUX_CHUNK_PAGES")) G = std::max<long>(mult, (atol(ov) + mult - 1) / mult * mult);   // tuning aid
-  workers = (int)std::max<long>(1, (total + G - 1) / G);
+  if (chunk_override > 0) G = std::max<long>(mult, (chunk_override + mult - 1) / mult * mult);
   int items = 0;
   long start = 0;
-  for (int i = 0; i < sb.n_seqs; i++) {
+  for (int i = 0; i < n_seqs; i++) {
     if (pages[i] > 0) items += (int)((start + pages[i] - 1) / G - start / G + 1);
     start += pages[i];
   }
+  *G_out = G;
+  *workers_out = (int)std::max<long>(1, (total + G - 1) / G);
+  *items_out = items;
+}
+
+int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int workers, int page_multiple, SplitPlan* plan) {
+  const relux_pool_params& prm = p->prm;
+  std::vector<int> pages(sb.n_seqs);
+  for (int i = 0; i < sb.n_seqs; i++) {
+    const int T = p->h_len[(size_t)layer * prm.max_seqs + sb.seq[i]] + extra;
+    pages[i] = (T + prm.page_tokens - 1) / prm.page_tokens;
+  }
+  long G = 0;
+  int items = 0;
+  const char* ov = getenv("RELUX_CHUNK_PAGES");   // tuning aid
+  stream_partition_shape(pages.data(), sb.n_seqs, workers, page_multiple, ov ? atol(ov) : 0, &G, &workers, &items);
   plan->chunk_pages = (int)G;
   plan->num_items = items;
   plan->num_workers = workers;
@@ -222,6 +234,52 @@ int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int worke
   count_launch(p->dev);
   return RELUX_OK;
 }
+
+}  // namespace relux
+
+// The stream partition computed on the host from page counts (no device involved): what the persistent MLA decode
+// kernel's planner produces for sequences of pages[i] pages.  items_out receives n_items x {seq_index, page_begin,
+// page_end, worker}; worker_first [workers_out + 1]; chunk_off [n_seqs + 1].  Returns the number of items, or -1 when
+// `cap` items are not enough.  Scheduling aid for callers and tests; no counterpart in the reference.
+extern "C" __attribute__((visibility("default"))) int32_t relux_stream_partition(const int32_t* pages, int32_t n_seqs, int32_t workers,
+                                                                               int32_t page_multiple, int32_t* range_pages_out,
+                                                                               int32_t* workers_out, int32_t* items_out, int32_t cap,
+                                                                               int32_t* worker_first, int32_t* chunk_off) {
+  if (!pages || n_seqs <= 0 || !range_pages_out || !workers_out) return -1;
+  long G = 0;
+  int W = 0, items = 0;
+  std::vector<int> pg(pages, pages + n_seqs);
+  relux::stream_partition_shape(pg.data(), n_seqs, workers, page_multiple, 0, &G, &W, &items);
+  *range_pages_out = (int32_t)G;
+  *workers_out = W;
+  if (items > cap) return -1;
+  long start = 0;
+  int n = 0;
+  if (worker_first)
+    for (int w = 0; w <= W; w++) worker_first[w] = items;
+  for (int i = 0; i < n_seqs; i++) {
+    if (chunk_off) chunk_off[i] = n;
+    if (pages[i] > 0) {
+      const long w0 = start / G, w1 = (start + pages[i] - 1) / G;
+      for (long w = w0; w <= w1; w++) {
+        const long lo = std::max(start, w * G), hi = std::min(start + pages[i], (w + 1) * G);
+        if (items_out) {
+          items_out[4 * n] = i;
+          items_out[4 * n + 1] = (int32_t)(lo - start);
+          items_out[4 * n + 2] = (int32_t)(hi - start);
+          items_out[4 * n + 3] = (int32_t)w;
+        }
+        if (worker_first && lo == w * G) worker_first[w] = n;
+        n++;
+      }
+    }
+    start += pages[i];
+  }
+  if (chunk_off) chunk_off[n_seqs] = n;
+  return n;
+}
+
+namespace relux {
 
 // Combines the partial results of every chunk of a sequence:
 //   M = max_c m_c,  L = sum_c l_c 2^(m_c - M),  O = sum_c O_c 2^(m_c - M) / L

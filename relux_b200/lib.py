@@ -30,7 +30,7 @@ EXPORTS = [
     "relux_cuda_event_destroy", "relux_cuda_flush_l2", "relux_pool_create", "relux_pool_destroy", "relux_pool_reset",
     "relux_pool_set_tables", "relux_seq_alloc", "relux_seq_free", "relux_seq_len", "relux_seq_set_len", "relux_pool_status",
     "relux_pool_read_rows", "relux_mla_append", "relux_gqa_append", "relux_mla_decode", "relux_gqa_decode", "relux_gqa_verify",
-    "relux_mla_verify", "relux_pool_last_kernel_ms", "relux_pool_kernel_ms_mean", "relux_mla_forward_cached", "relux_gqa_forward_cached", "relux_seq_save_file", "relux_seq_load_file", "relux_pool_projection_ms_mean", "relux_gqa_decode_noalloc",
+    "relux_mla_verify", "relux_pool_last_kernel_ms", "relux_pool_kernel_ms_mean", "relux_mla_forward_cached", "relux_gqa_forward_cached", "relux_stream_partition", "relux_seq_save_file", "relux_seq_load_file", "relux_pool_projection_ms_mean", "relux_gqa_decode_noalloc",
 ]
 
 
@@ -138,6 +138,8 @@ def load():
         for n in ("relux_gqa_verify", "relux_mla_verify"):
             getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AttnArgs), C.POINTER(AppendArgs)]
         L.relux_pool_projection_ms_mean.argtypes = [C.c_void_p, C.c_int32, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
+        L.relux_stream_partition.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32),
+                                             C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
         L.relux_seq_save_file.argtypes = [C.c_void_p, C.c_int32, C.c_char_p, C.c_int32]
         L.relux_seq_load_file.argtypes = [C.c_void_p, C.c_int32, C.c_char_p, C.c_int32, C.c_void_p]
         L.relux_gqa_forward_cached.argtypes = [C.c_void_p, C.POINTER(GqaLayerArgs)]

@@ -31,3 +31,26 @@ def balanced_assignment(lengths, world, per_rank=None):
 def aggregate_throughput(units_per_rank, ms_per_rank):
     """Whole-job throughput: all units of all ranks over the slowest rank's device time."""
     return float(sum(units_per_rank)) / (max(ms_per_rank) * 1e-3)
+
+
+def stream_partition(pages, workers, page_multiple=2):
+    """The stream partition of the persistent MLA decode kernel for sequences of pages[i] pages (computed by the
+    library on the host; no GPU needed).  Returns (range_pages, n_workers, items, worker_first, chunk_off) with items an
+    int32 array [n, 4] of {seq_index, page_begin, page_end, worker}."""
+    import ctypes as C
+
+    import numpy as np
+
+    from . import lib as L
+    lib = L.load()
+    pg = np.ascontiguousarray(pages, dtype=np.int32)
+    cap = int(len(pg) + max(1, workers) + int(pg.sum()) // 2 + 8)
+    items = np.empty((cap, 4), np.int32)
+    wf = np.empty(cap + 2, np.int32)
+    co = np.empty(len(pg) + 1, np.int32)
+    G, W = C.c_int32(), C.c_int32()
+    n = lib.relux_stream_partition(pg.ctypes.data, len(pg), int(workers), int(page_multiple), C.byref(G), C.byref(W), items.ctypes.data,
+                                   cap, wf.ctypes.data, co.ctypes.data)
+    if n < 0:
+        raise ValueError("stream_partition: bad arguments")
+    return G.value, W.value, items[:n].copy(), wf[:W.value + 1].copy(), co

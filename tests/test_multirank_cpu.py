@@ -75,3 +75,36 @@ def test_two_gloo_ranks_shard_and_reduce_timings():
     line = [l for l in out.stdout.splitlines() if l.startswith("{")][-1]
     d = json.loads(line)
     assert d["max_ms"] == 15.0 and d["units"] == 129 and abs(d["tps"] - 129 / 0.015) < 1e-6
+
+
+def test_stream_partition_properties():
+    """The partition the persistent MLA decode kernel walks (host statement of the same arithmetic): every page of every
+    sequence is in exactly one item, items of a sequence and of a worker are contiguous, no worker holds more than one
+    range, ranges are whole tiles."""
+    from relux_b200.sharding import stream_partition
+    rng = np.random.default_rng(4)
+    cases = [[512] * 64, [1], [0, 3, 0, 9], list(rng.integers(1, 200, 300)), [9000], list(rng.integers(16, 513, 16))]
+    for pages in cases:
+        for workers in (1, 7, 74):
+            G, W, items, wf, co = stream_partition(pages, workers, 2)
+            total = int(np.sum(pages))
+            assert G % 2 == 0 and G >= 4
+            assert W == max(1, -(-total // G)) and W <= max(workers, 1)
+            covered = {}
+            start = np.concatenate([[0], np.cumsum(pages)])
+            for k, (i, b, e, w) in enumerate(items):
+                assert 0 <= b < e <= pages[i]
+                lo, hi = start[i] + b, start[i] + e
+                assert lo // G == w == (hi - 1) // G                      # an item lies inside its worker's range
+                for pg in range(b, e):
+                    assert (i, pg) not in covered
+                    covered[(i, pg)] = k
+            assert len(covered) == total
+            assert list(items[:, 0]) == sorted(items[:, 0]) and list(items[:, 3]) == sorted(items[:, 3])
+            for i in range(len(pages)):
+                assert list(items[co[i]:co[i + 1], 0]) == [i] * (co[i + 1] - co[i])
+            for w in range(W):
+                assert all(items[k, 3] == w for k in range(wf[w], wf[w + 1]))
+            assert wf[W] == len(items)
+            loads = np.bincount(items[:, 3], weights=items[:, 2] - items[:, 1], minlength=W)
+            assert loads.max() <= G
