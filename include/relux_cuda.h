@@ -137,6 +137,10 @@ int32_t relux_pool_set_tables(relux_pool_t pool, const int32_t* table, int32_t n
 /* Library-owned page tables: reserves pages for max_tokens tokens and returns a sequence id. */
 int32_t relux_seq_alloc(relux_pool_t pool, int32_t max_tokens, int32_t* seq_id);
 int32_t relux_seq_free(relux_pool_t pool, int32_t seq_id);
+/* Grows a sequence created by relux_seq_alloc to hold max_tokens rows, taking the missing pages from the pool's free
+ * list (never shrinks; cached rows stay where they are).  The reference's caches are sized once at construction
+ * (NewKVCacheSized, kvcache.go:66-93); this is the paged pool's way to start small and grow. */
+int32_t relux_seq_extend(relux_pool_t pool, int32_t seq_id, int32_t max_tokens);
 /* KVCache.TotalLen / MLACache.TotalLen (kvcache.go:383-388, mla_cache.go:236-241). */
 int32_t relux_seq_len(relux_pool_t pool, int32_t layer, int32_t seq_id, int32_t* len);
 /* Sets the length of n_seqs sequences on one layer (layer < 0: on every layer).  Used to commit the accepted

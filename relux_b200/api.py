@@ -206,6 +206,10 @@ class Pool:
     def seq_free(self, seq):
         L.check(self.lib.relux_seq_free(self.h, seq))
 
+    def seq_extend(self, seq, max_tokens):
+        """Grows a sequence made by seq_alloc to hold max_tokens rows (pages come from the pool's free list)."""
+        L.check(self.lib.relux_seq_extend(self.h, seq, max_tokens))
+
     def seq_len(self, layer, seq):
         n = C.c_int32()
         L.check(self.lib.relux_seq_len(self.h, layer, seq, C.byref(n)))

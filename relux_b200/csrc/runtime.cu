@@ -720,6 +720,27 @@ API int32_t relux_seq_alloc(relux_pool_t h, int32_t max_tokens, int32_t* seq_id)
   return RELUX_OK;
 }
 
+API int32_t relux_seq_extend(relux_pool_t h, int32_t s, int32_t max_tokens) {
+  GET_POOL(h);
+  const relux_pool_params& prm = p->prm;
+  if (s < 0 || s >= prm.max_seqs || p->seq_pages[s] == 0) { set_error("seq_extend: sequence %d is not live", s); return RELUX_ERR_INVALID_ARG; }
+  if (!p->seq_owned[s]) { set_error("seq_extend: sequence %d uses a caller-supplied page table", s); return RELUX_ERR_INVALID_ARG; }
+  const int need = (max_tokens + prm.page_tokens - 1) / prm.page_tokens, have = p->seq_pages[s];
+  if (need <= have) return RELUX_OK;   // never shrinks: cached rows keep their pages
+  if (need > prm.max_pages_per_seq) { set_error("seq_extend: %d tokens need %d pages, max_pages_per_seq=%d", max_tokens, need, prm.max_pages_per_seq); return RELUX_ERR_OVERFLOW; }
+  if ((int)p->free_pages.size() < need - have) { set_error("pool exhausted: %d free pages, %d needed", (int)p->free_pages.size(), need - have); return RELUX_ERR_POOL_EXHAUSTED; }
+  for (int i = have; i < need; i++) {
+    p->h_table[(size_t)s * prm.max_pages_per_seq + i] = p->free_pages.back();
+    p->free_pages.pop_back();
+  }
+  p->seq_pages[s] = need;
+  // the new table entries lie past every page a queued kernel of this sequence can touch; the copy is ordered on the stream
+  RELUX_CUDA_TRY(cudaMemcpyAsync(p->d_table + (size_t)s * prm.max_pages_per_seq + have, &p->h_table[(size_t)s * prm.max_pages_per_seq + have],
+                                 (size_t)(need - have) * 4, cudaMemcpyHostToDevice, dev->stream));
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));   // h_table is pageable host memory
+  return RELUX_OK;
+}
+
 API int32_t relux_seq_free(relux_pool_t h, int32_t s) {
   GET_POOL(h);
   const relux_pool_params& prm = p->prm;

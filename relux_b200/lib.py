@@ -28,7 +28,7 @@ EXPORTS = [
     "relux_cuda_dev_free", "relux_cuda_host_alloc", "relux_cuda_host_free", "relux_cuda_h2d", "relux_cuda_d2h",
     "relux_cuda_memset", "relux_cuda_event_create", "relux_cuda_event_record", "relux_cuda_event_elapsed_ms",
     "relux_cuda_event_destroy", "relux_cuda_flush_l2", "relux_pool_create", "relux_pool_destroy", "relux_pool_reset",
-    "relux_pool_set_tables", "relux_seq_alloc", "relux_seq_free", "relux_seq_len", "relux_seq_set_len", "relux_pool_status",
+    "relux_pool_set_tables", "relux_seq_alloc", "relux_seq_free", "relux_seq_extend", "relux_seq_len", "relux_seq_set_len", "relux_pool_status",
     "relux_pool_read_rows", "relux_mla_append", "relux_gqa_append", "relux_mla_decode", "relux_gqa_decode", "relux_gqa_verify",
     "relux_mla_verify", "relux_pool_last_kernel_ms", "relux_pool_kernel_ms_mean", "relux_mla_forward_cached", "relux_gqa_forward_cached", "relux_stream_partition", "relux_seq_save_file", "relux_seq_load_file", "relux_pool_projection_ms_mean", "relux_gqa_decode_noalloc",
 ]
@@ -127,6 +127,7 @@ def load():
         L.relux_pool_set_tables.argtypes = [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p]
         L.relux_seq_alloc.argtypes = [C.c_void_p, C.c_int32, C.POINTER(C.c_int32)]
         L.relux_seq_free.argtypes = [C.c_void_p, C.c_int32]
+        L.relux_seq_extend.argtypes = [C.c_void_p, C.c_int32, C.c_int32]
         L.relux_seq_len.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int32)]
         L.relux_seq_set_len.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
         L.relux_pool_status.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]

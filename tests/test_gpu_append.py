@@ -190,3 +190,34 @@ def test_library_owned_sequences_and_exhaustion(dev):
     pool.reset()
     assert pool.seq_len(0, b) == 0
     pool.destroy()
+
+
+def test_sequence_grows_page_by_page(dev, oracle):
+    """relux_seq_extend: a sequence starts with one page and takes more from the free list as it fills; rows already
+    cached stay bit-exact, and the free list is honoured."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(71)
+    pool = rb.Pool(dev, L.POOL_MLA, 1, 5, 64, 2, 4, dC=64, dHR=16)
+    s = pool.seq_alloc(64)
+    other = pool.seq_alloc(64)
+    c = rng.standard_normal((200, 64), dtype=np.float32)
+    r = rng.standard_normal((200, 16), dtype=np.float32)
+    pool.append(0, c[:64], r[:64], 1, seq_ids=[s])
+    with pytest.raises(L.ReluxCudaError) as e:       # the page is full
+        pool.append(0, c[64:65], r[64:65], 1, seq_ids=[s])
+    assert e.value.code == L.ERR_OVERFLOW
+    pool.seq_extend(s, 200)                           # 4 pages = 3 more of the 3 free ones
+    pool.append(0, c[64:200], r[64:200], 1, seq_ids=[s], n_new=[136])
+    gc, gr = pool.read_rows(0, s, 0, 200)
+    assert np.array_equal(gc, oracle.bf16_from_f32(c)) and np.array_equal(gr, oracle.bf16_from_f32(r))
+    pool.seq_extend(s, 100)                           # never shrinks
+    assert pool.seq_len(0, s) == 200
+    with pytest.raises(L.ReluxCudaError) as e:
+        pool.seq_extend(other, 128)                   # no free page left
+    assert e.value.code == L.ERR_POOL_EXHAUSTED
+    with pytest.raises(L.ReluxCudaError) as e:
+        pool.seq_extend(s, 64 * 5)                    # beyond max_pages_per_seq
+    assert e.value.code == L.ERR_OVERFLOW
+    assert pool.status() == 0
+    pool.destroy()
