@@ -291,6 +291,15 @@ class Model:
     def begin(self):
         lib().ro_model_begin(C.c_void_p(self.h))
 
+    def attention_forward(self, layer, x):
+        """The attention module of `layer` alone (forwardCached on the session's caches): x [seq, dModel] -> [seq, dModel]."""
+        x = f32(x)
+        out = np.empty_like(x)
+        rc = lib().ro_model_attention_forward(C.c_void_p(self.h), int(layer), _p(x), C.c_int(x.shape[0]), _p(out))
+        if rc:
+            raise RuntimeError("forwardCached failed with code %d" % rc)
+        return out
+
     def forward(self, tokens):
         t = np.ascontiguousarray(tokens, dtype=np.int32)
         out = np.empty((t.size, self.cfg.vocab), np.float32)

@@ -872,6 +872,13 @@ static void model_begin(Model* m) {
 }
 // Starts a cached session (what Generate does at transformer.go:907-947).
 RO_API void ro_model_begin(void* p) { model_begin((Model*)p); }
+// The attention module of one layer alone on the session's caches: MHA.Forward / MLA.Forward in Inference mode with a
+// cache attached (mha.go:126-128, mla.go:130-132 -> forwardCached).  x [seq, dModel] -> out [seq, dModel].
+RO_API int ro_model_attention_forward(void* p, int layer, const float* x, int seq, float* out) {
+  Model* m = (Model*)p;
+  if (layer < 0 || layer >= m->cfg.numLayers || (m->cfg.mla ? m->mc == nullptr : (m->mode == RO_FAITHFUL && m->kv == nullptr))) return -7;
+  return m->cfg.mla ? mla_forward_cached(m, layer, out, x, seq) : mha_forward_cached(m, layer, out, x, seq);
+}
 // One cached Forward over `seq` tokens; logits [seq, vocab].
 RO_API int ro_model_forward(void* p, const int* tokens, int seq, float* logits) {
   Model* m = (Model*)p;
