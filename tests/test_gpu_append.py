@@ -203,7 +203,7 @@ def test_sequence_grows_page_by_page(dev, oracle):
     other = pool.seq_alloc(64)
     c = rng.standard_normal((200, 64), dtype=np.float32)
     r = rng.standard_normal((200, 16), dtype=np.float32)
-    pool.append(0, c[:64], r[:64], 1, seq_ids=[s])
+    pool.append(0, c[:64], r[:64], 1, seq_ids=[s], n_new=[64])
     with pytest.raises(L.ReluxCudaError) as e:       # the page is full
         pool.append(0, c[64:65], r[64:65], 1, seq_ids=[s])
     assert e.value.code == L.ERR_OVERFLOW
