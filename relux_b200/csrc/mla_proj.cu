@@ -199,6 +199,72 @@ __device__ __forceinline__ void tile_mma_64x64x128_bt(const uint16_t* As, const 
   }
 }
 
+// Merges the split-KV partials of the tile's rows into the bf16 A operand.  COLS = columns of every 128-column chunk
+// one thread owns; 128 / COLS threads share a row, 256 * COLS / 128 rows are covered (the rest of the 64-row tile is
+// zeroed).  Two items are in flight per thread at a time: their loads do not depend on each other.
+template <int COLS>
+__device__ __forceinline__ void merge_rows(uint16_t* As, const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                           const int32_t* sC0, const int32_t* sC1, const float* sM, const float* sInv, int r0, int rows,
+                                           int S, int H, int h, int dC, int nk, int rows_total) {
+  constexpr int TPR = 128 / COLS, ROWS = 256 / TPR;
+  const int row = threadIdx.x / TPR, qt = threadIdx.x % TPR;
+  for (int e = threadIdx.x; e < (64 - ROWS) * 16 * nk; e += 256) {   // rows of the MMA tile nobody merges into
+    const int k = e / ((64 - ROWS) * 16), rem = e % ((64 - ROWS) * 16);
+    *reinterpret_cast<uint4*>(As + ((size_t)k * 64 + ROWS + rem / 16) * kStride + (rem % 16) * 8) = make_uint4(0, 0, 0, 0);
+  }
+  const int r = r0 + row;
+  const int c0 = sC0[row], c1 = sC1[row];
+  const float M = sM[row], inv = sInv[row];
+  const size_t prow = (r < rows) ? (size_t)(r % S) * H + h : 0;
+  float acc[kMaxChunks][COLS];
+#pragma unroll
+  for (int k = 0; k < kMaxChunks; k++)
+#pragma unroll
+    for (int j = 0; j < COLS; j++) acc[k][j] = 0.f;
+  for (int c = c0; c < c1; c += 2) {
+    const bool two = c + 1 < c1;
+    const size_t pr0 = (size_t)c * rows_total + prow, pr1 = (size_t)(two ? c + 1 : c) * rows_total + prow;
+    const float m0 = __ldg(part_ml + pr0 * 2), m1 = __ldg(part_ml + pr1 * 2);
+    const float w0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - M) * inv;
+    const float w1 = (!two || m1 == -INFINITY) ? 0.f : exp2f(m1 - M) * inv;
+    const float4* s0 = reinterpret_cast<const float4*>(part_o + pr0 * dC + qt * COLS);
+    const float4* s1 = reinterpret_cast<const float4*>(part_o + pr1 * dC + qt * COLS);
+#pragma unroll
+    for (int k = 0; k < kMaxChunks; k++) {
+      if (k < nk) {
+        float4 x0[COLS / 4], x1[COLS / 4];
+#pragma unroll
+        for (int j = 0; j < COLS / 4; j++) {
+          x0[j] = __ldg(s0 + k * 32 + j);
+          x1[j] = __ldg(s1 + k * 32 + j);
+        }
+#pragma unroll
+        for (int j = 0; j < COLS / 4; j++) {
+          acc[k][4 * j] = fmaf(x1[j].x, w1, fmaf(x0[j].x, w0, acc[k][4 * j]));
+          acc[k][4 * j + 1] = fmaf(x1[j].y, w1, fmaf(x0[j].y, w0, acc[k][4 * j + 1]));
+          acc[k][4 * j + 2] = fmaf(x1[j].z, w1, fmaf(x0[j].z, w0, acc[k][4 * j + 2]));
+          acc[k][4 * j + 3] = fmaf(x1[j].w, w1, fmaf(x0[j].w, w0, acc[k][4 * j + 3]));
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < kMaxChunks; k++) {
+    if (k < nk) {
+      uint16_t* dst = As + ((size_t)k * 64 + row) * kStride + qt * COLS;
+      if constexpr (COLS >= 8) {
+#pragma unroll
+        for (int j = 0; j < COLS / 8; j++)
+          *reinterpret_cast<uint4*>(dst + j * 8) =
+              make_uint4(pack_bf16x2(acc[k][8 * j], acc[k][8 * j + 1]), pack_bf16x2(acc[k][8 * j + 2], acc[k][8 * j + 3]),
+                         pack_bf16x2(acc[k][8 * j + 4], acc[k][8 * j + 5]), pack_bf16x2(acc[k][8 * j + 6], acc[k][8 * j + 7]));
+      } else {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(acc[k][0], acc[k][1]), pack_bf16x2(acc[k][2], acc[k][3]));
+      }
+    }
+  }
+}
+
 // Split-KV merge fused into the value up-projection: the A operand (the merged, normalised latent output of
 // 64 rows of one head, as bf16) is built straight from the per-item partials
 //   part_o [item][S * H][dC] f32 (unnormalised), part_ml [item][S * H][2] = (max in the log2 domain, sum),
@@ -247,49 +313,12 @@ __global__ void __launch_bounds__(256) mla_merge_vup_mma_kernel(const float* __r
     sC1[threadIdx.x] = c1;
   }
   __syncthreads();
-  {
-    // four threads per row; thread `qt` of a row owns columns [32 qt, 32 qt + 32) of every 128-column chunk
-    const int row = threadIdx.x >> 2, qt = threadIdx.x & 3;
-    const int r = r0 + row;
-    const int c0 = sC0[row], c1 = sC1[row];
-    const float M = sM[row], inv = sInv[row];
-    const size_t prow = (r < rows) ? (size_t)(r % S) * H + h : 0;
-    float acc[kMaxChunks][32];
-#pragma unroll
-    for (int k = 0; k < kMaxChunks; k++)
-#pragma unroll
-      for (int j = 0; j < 32; j++) acc[k][j] = 0.f;
-    for (int c = c0; c < c1; c++) {
-      const size_t pr = (size_t)c * rows_total + prow;
-      const float m = __ldg(part_ml + pr * 2);
-      const float w = (m == -INFINITY) ? 0.f : exp2f(m - M) * inv;
-      const float4* src = reinterpret_cast<const float4*>(part_o + pr * dC + qt * 32);
-#pragma unroll
-      for (int k = 0; k < kMaxChunks; k++) {
-        if (k < nk) {
-#pragma unroll
-          for (int j = 0; j < 8; j++) {
-            const float4 x = __ldg(src + k * 32 + j);
-            acc[k][4 * j] = fmaf(x.x, w, acc[k][4 * j]);
-            acc[k][4 * j + 1] = fmaf(x.y, w, acc[k][4 * j + 1]);
-            acc[k][4 * j + 2] = fmaf(x.z, w, acc[k][4 * j + 2]);
-            acc[k][4 * j + 3] = fmaf(x.w, w, acc[k][4 * j + 3]);
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < kMaxChunks; k++) {
-      if (k < nk) {
-        uint16_t* dst = As + ((size_t)k * 64 + row) * kStride + qt * 32;
-#pragma unroll
-        for (int j = 0; j < 4; j++)
-          *reinterpret_cast<uint4*>(dst + j * 8) =
-              make_uint4(pack_bf16x2(acc[k][8 * j], acc[k][8 * j + 1]), pack_bf16x2(acc[k][8 * j + 2], acc[k][8 * j + 3]),
-                         pack_bf16x2(acc[k][8 * j + 4], acc[k][8 * j + 5]), pack_bf16x2(acc[k][8 * j + 6], acc[k][8 * j + 7]));
-      }
-    }
-  }
+  // fewer real rows in the tile -> more threads per row, so that a short batch still keeps every thread loading
+  const int rows_here = min(64, rows - r0);
+  if (rows_here > 32) merge_rows<32>(As, part_o, part_ml, sC0, sC1, sM, sInv, r0, rows, S, H, h, dC, nk, rows_total);
+  else if (rows_here > 16) merge_rows<16>(As, part_o, part_ml, sC0, sC1, sM, sInv, r0, rows, S, H, h, dC, nk, rows_total);
+  else if (rows_here > 8) merge_rows<8>(As, part_o, part_ml, sC0, sC1, sM, sInv, r0, rows, S, H, h, dC, nk, rows_total);
+  else merge_rows<4>(As, part_o, part_ml, sC0, sC1, sM, sInv, r0, rows, S, H, h, dC, nk, rows_total);
   float acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; i++)
