@@ -70,34 +70,42 @@ int32_t relux_cuda_device_count(int32_t* count);
 int32_t relux_cuda_device_open(int32_t device_index, relux_device_t* out);
 int32_t relux_cuda_device_close(relux_device_t dev);
 int32_t relux_cuda_sync(relux_device_t dev);
-/* Copies the calling thread's last error message (NUL terminated) into buf. */
+/* Copies the calling thread's last error message (NUL terminated) into buf.  The reference reports misuse by
+ * panic(fmt.Sprintf(...)) (kvcache.go:241-249, 282-285; mla_cache.go:153-167); a C ABI cannot unwind through the
+ * caller, so the same wording is fetched here after a non-zero status. */
 int32_t relux_cuda_last_error(char* buf, int32_t buf_len);
 /* Name, SM count, memory of the device (DeviceInfo() equivalent, interface.go:37-40). */
 int32_t relux_cuda_device_info(relux_device_t dev, char* name, int32_t name_len, int32_t* sm_count,
                                int64_t* total_mem_bytes);
-/* Number of kernels this library has launched on the handle since it was opened. */
+/* Number of kernels this library has launched on the handle since it was opened.  Measurement aid: no counterpart
+ * in the reference. */
 int32_t relux_cuda_launch_count(relux_device_t dev, int64_t* count);
-/* The CUDA stream (cudaStream_t) all work of this handle is issued on. */
+/* The CUDA stream (cudaStream_t) all work of this handle is issued on, for callers that order their own device work
+ * with it.  No counterpart in the reference. */
 int32_t relux_cuda_stream(relux_device_t dev, void** stream);
 
 /* ---- device memory ------------------------------------------------------------------------
  * Replaces internal/alloc/alloc.go:95-117,168-188,375-390 (alloc.Float32 / alloc.Uint16 / alloc.Free)
- * for buffers that must live on the GPU (weights, activations handed over as device pointers). */
+ * for buffers that must live on the GPU (weights, activations handed over as device pointers); host_alloc gives
+ * page-locked host memory, like the reference's off-heap buffers "with stable addresses" (alloc.go:15-18). */
 int32_t relux_cuda_dev_alloc(relux_device_t dev, size_t bytes, void** dptr);
 int32_t relux_cuda_dev_free(relux_device_t dev, void* dptr);
-int32_t relux_cuda_host_alloc(relux_device_t dev, size_t bytes, void** hptr); /* pinned */
+int32_t relux_cuda_host_alloc(relux_device_t dev, size_t bytes, void** hptr);
 int32_t relux_cuda_host_free(relux_device_t dev, void* hptr);
-/* Asynchronous on the handle's stream when the host side is pinned; ordered with kernel calls. */
+/* Host <-> device copies and fill; asynchronous on the handle's stream when the host side is pinned, ordered with
+ * kernel calls.  No counterpart in the reference, whose buffers all live in host memory (alloc.go:15-18). */
 int32_t relux_cuda_h2d(relux_device_t dev, void* dst_dev, const void* src_host, size_t bytes);
 int32_t relux_cuda_d2h(relux_device_t dev, void* dst_host, const void* src_dev, size_t bytes);
 int32_t relux_cuda_memset(relux_device_t dev, void* dst_dev, int32_t value, size_t bytes);
 
-/* ---- timing helpers (CUDA events on the handle's stream) -------------------------------- */
+/* ---- timing helpers (CUDA events on the handle's stream) --------------------------------
+ * Measurement aids: no counterpart in the reference. */
 int32_t relux_cuda_event_create(relux_device_t dev, relux_event_t* ev);
 int32_t relux_cuda_event_record(relux_device_t dev, relux_event_t ev);
 int32_t relux_cuda_event_elapsed_ms(relux_device_t dev, relux_event_t start, relux_event_t stop, float* ms);
 int32_t relux_cuda_event_destroy(relux_device_t dev, relux_event_t ev);
-/* Overwrites a scratch buffer larger than L2 so the next kernel starts cold. */
+/* Overwrites a scratch buffer larger than L2 so the next kernel starts cold.  Measurement aid: no counterpart in
+ * the reference. */
 int32_t relux_cuda_flush_l2(relux_device_t dev);
 
 /* ---- paged KV pools -----------------------------------------------------------------------
@@ -124,6 +132,8 @@ typedef struct relux_pool_params {
   int32_t reserved[6];       /* must be zero */
 } relux_pool_params;
 
+/* NewKVCacheSized (kvcache.go:66-93) / NewMLACache (mla_cache.go:38-59) for a whole batch of sequences; destroy
+ * frees what the reference leaves to the garbage collector and alloc.Free. */
 int32_t relux_pool_create(relux_device_t dev, const relux_pool_params* params, relux_pool_t* out);
 int32_t relux_pool_destroy(relux_pool_t pool);
 /* KVCache.Reset / MLACache.Reset (kvcache.go:174-202, mla_cache.go:118-133): every sequence length
@@ -131,10 +141,13 @@ int32_t relux_pool_destroy(relux_pool_t pool);
 int32_t relux_pool_reset(relux_pool_t pool);
 /* Caller-owned page tables: table is a host array [n_seqs][stride] of physical page ids, ctx_len a host
  * array [n_seqs] applied to every layer (NULL = 0).  Sequences 0..n_seqs-1 become live.  Ids are
- * validated on the host; a bad id is RELUX_ERR_BAD_PAGE. */
+ * validated on the host; a bad id is RELUX_ERR_BAD_PAGE.  No counterpart in the reference, whose caches are one
+ * contiguous buffer per layer (kvcache.go:66-93): page tables are what the paged pool adds. */
 int32_t relux_pool_set_tables(relux_pool_t pool, const int32_t* table, int32_t n_seqs, int32_t stride,
                               const int32_t* ctx_len);
-/* Library-owned page tables: reserves pages for max_tokens tokens and returns a sequence id. */
+/* Library-owned page tables: reserves pages for max_tokens tokens and returns a sequence id; per sequence what
+ * NewKVCacheSized(numLayers, maxLen, ...) (kvcache.go:66-93) does for the reference's single sequence.  relux_seq_free
+ * returns the pages (the reference: Reset + garbage collection, kvcache.go:174-202). */
 int32_t relux_seq_alloc(relux_pool_t pool, int32_t max_tokens, int32_t* seq_id);
 int32_t relux_seq_free(relux_pool_t pool, int32_t seq_id);
 /* Grows a sequence created by relux_seq_alloc to hold max_tokens rows, taking the missing pages from the pool's free
@@ -144,11 +157,12 @@ int32_t relux_seq_extend(relux_pool_t pool, int32_t seq_id, int32_t max_tokens);
 /* KVCache.TotalLen / MLACache.TotalLen (kvcache.go:383-388, mla_cache.go:236-241). */
 int32_t relux_seq_len(relux_pool_t pool, int32_t layer, int32_t seq_id, int32_t* len);
 /* Sets the length of n_seqs sequences on one layer (layer < 0: on every layer).  Used to commit the accepted
- * prefix after a speculative verify, or to roll a sequence back.  seq_ids NULL = 0..n_seqs-1. */
+ * prefix after a speculative verify, or to roll a sequence back.  seq_ids NULL = 0..n_seqs-1.  The reference has no
+ * such call: its speculative decoder never removes rejected draft rows from the cache (speculative.go:136-156). */
 int32_t relux_seq_set_len(relux_pool_t pool, int32_t layer, int32_t n_seqs, const int32_t* seq_ids,
                           const int32_t* new_len);
 /* Reads the device status word (0, or the first RELUX_ERR_BAD_PAGE / RELUX_ERR_TIMEOUT a kernel recorded)
- * and clears it.  Synchronises the stream. */
+ * and clears it.  Synchronises the stream.  No counterpart in the reference (its checks panic on the host). */
 int32_t relux_pool_status(relux_pool_t pool, int32_t* status);
 /* KVCache.View / MLACache.View equivalent used by the bit-exactness tests (kvcache.go:363-380,
  * mla_cache.go:222-233): copies n_tokens logical rows starting at token tok0 of one sequence to host memory
@@ -338,7 +352,8 @@ int32_t relux_stream_partition(const int32_t* pages, int32_t n_seqs, int32_t wor
                                int32_t* workers_out, int32_t* items_out, int32_t cap, int32_t* worker_first, int32_t* chunk_off);
 
 /* Device-time of the dominant attention kernel of the most recent relux_*_decode / verify call on this
- * pool, measured with CUDA events around that one launch.  Synchronises the stream. */
+ * pool, measured with CUDA events around that one launch.  Synchronises the stream.  Measurement aid: no counterpart
+ * in the reference. */
 int32_t relux_pool_last_kernel_ms(relux_pool_t pool, float* ms);
 
 /* Mean device time of that kernel over the most recent `last_n` decode / verify calls on this pool (at most

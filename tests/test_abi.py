@@ -80,3 +80,22 @@ def test_no_gpu_means_a_clean_error(so):
     with pytest.raises(so.ReluxCudaError) as e:
         rb.Device(0)
     assert e.value.code in (so.ERR_NO_DEVICE, so.ERR_CUDA)
+
+
+def test_every_entry_point_says_what_it_replaces():
+    """Each declaration in the header stands under a comment that cites the reference (file.go:line) or says that the
+    reference has no counterpart; a comment may head a group of consecutive declarations."""
+    import re
+    text = open(os.path.join(ROOT, "include", "relux_cuda.h")).read()
+    text = re.sub(r"typedef struct \w+ \{.*?\} \w+;", "", text, flags=re.S)      # field comments are not entry-point comments
+    missing = []
+    for m in re.finditer(r"^int32_t (relux_\w+)\(", text, re.M):
+        pre = text[:m.start()]
+        end = pre.rfind("*/")
+        begin = pre.rfind("/*", 0, end)
+        block = pre[begin:end + 2] if end >= 0 else ""
+        between = pre[end + 2:] if end >= 0 else pre
+        only_decls = re.sub(r"int32_t relux_\w+\([^;]*\);", "", between).strip() == ""
+        if not only_decls or not (re.search(r"\.go:\d", block) or "no counterpart" in block.lower()):
+            missing.append(m.group(1))
+    assert not missing, "entry points without a reference citation: %s" % missing
