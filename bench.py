@@ -50,6 +50,13 @@ TRAFFIC_RATIO = {"mla": 1.04, "gqa": 1.015}
 PAGE = 64
 
 
+def bf16_bits(x):
+    """float32 array -> bf16 bit patterns, round to nearest even with the reference's rule (dtype_convert.go:15-24).
+    Input preparation of the GPU arm; the oracle is not involved."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32)
+    return ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+
+
 def read_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -151,7 +158,6 @@ def max_over_ranks(dist, x):
 def run_mla(args, w, world, rank, local, dist):
     import relux_b200 as rb
     from relux_b200 import lib as L
-    from oracle import binding as orc  # used only for the bf16 rounding helper of inputs and the CPU baseline leg
 
     B, ctx0, H, Dh, dC, dHR = w["B"], w["ctx"], w["H"], w["Dh"], w["dC"], w["dHR"]
     total_steps = 2 * (args.steps + args.warmup) + 8
@@ -169,15 +175,15 @@ def run_mla(args, w, world, rank, local, dist):
     else:
         lens0 = np.full(B, ctx0, np.int64)
     blk = min(ctx0, 2048)
-    src_c = orc.bf16_from_f32(rng.standard_normal((B * blk, dC), dtype=np.float32))
-    src_r = orc.bf16_from_f32(rng.standard_normal((B * blk, dHR), dtype=np.float32))
+    src_c = bf16_bits(rng.standard_normal((B * blk, dC), dtype=np.float32))
+    src_r = bf16_bits(rng.standard_normal((B * blk, dHR), dtype=np.float32))
     d_c, d_r = dev.upload(src_c), dev.upload(src_r)
     for off in range(0, int(lens0.max()), blk):
         pool.append(0, d_c, d_r, B, n_new=np.clip(lens0 - off, 0, blk).astype(np.int32))
     dev.sync()
     d_c.free(); d_r.free()
-    wuk = orc.bf16_from_f32((rng.standard_normal((dC, H * Dh), dtype=np.float32) * 0.02))
-    wuv = orc.bf16_from_f32((rng.standard_normal((dC, H * Dh), dtype=np.float32) * 0.02))
+    wuk = bf16_bits((rng.standard_normal((dC, H * Dh), dtype=np.float32) * 0.02))
+    wuv = bf16_bits((rng.standard_normal((dC, H * Dh), dtype=np.float32) * 0.02))
     d_wuk, d_wuv = dev.upload(wuk), dev.upload(wuv)
     scale = float(1.0 / np.sqrt(Dh + dHR))
     # per-step inputs: new latent row + rope key per sequence, queries; resident copies and pinned host copies
@@ -185,8 +191,8 @@ def run_mla(args, w, world, rank, local, dist):
     new_r = rng.standard_normal((B, dHR), dtype=np.float32)
     qc = rng.standard_normal((B, 1, H, Dh), dtype=np.float32)
     qr = rng.standard_normal((B, 1, H, dHR), dtype=np.float32)
-    d_new_c, d_new_r = dev.upload(orc.bf16_from_f32(new_c)), dev.upload(orc.bf16_from_f32(new_r))
-    d_qc, d_qr = dev.upload(orc.bf16_from_f32(qc)), dev.upload(orc.bf16_from_f32(qr))
+    d_new_c, d_new_r = dev.upload(bf16_bits(new_c)), dev.upload(bf16_bits(new_r))
+    d_qc, d_qr = dev.upload(bf16_bits(qc)), dev.upload(bf16_bits(qr))
     d_out = dev.alloc(B * H * Dh * 4, L.DTYPE_F32)
     pins = [dev.pinned(a.shape, np.float32) for a in (new_c, new_r, qc, qr)]
     for p_, a in zip(pins, (new_c, new_r, qc, qr)):
@@ -209,7 +215,7 @@ def run_mla(args, w, world, rank, local, dist):
 
         def weight(rows, cols):
             blk_cols = min(cols, 1024)
-            blk_w = orc.bf16_from_f32(rng.standard_normal((rows, blk_cols), dtype=np.float32) * np.float32(1.0 / np.sqrt(rows)))
+            blk_w = bf16_bits(rng.standard_normal((rows, blk_cols), dtype=np.float32) * np.float32(1.0 / np.sqrt(rows)))
             return dev.upload(np.ascontiguousarray(np.tile(blk_w, (1, cols // blk_cols))))
 
         dW = {"w_q": weight(D, H * Dh), "w_qr": weight(D, H * dHR), "w_dkv": weight(D, dC), "w_kr": weight(D, dHR),
@@ -318,7 +324,6 @@ def run_gqa(args, w, world, rank, local, dist):
     commit an accepted prefix of 1..4 tokens.  tokens/s counts accepted tokens."""
     import relux_b200 as rb
     from relux_b200 import lib as L
-    from oracle import binding as orc
 
     B, ctx0, H, Hkv, D, S = w["B"], w["ctx"], w["H"], w["Hkv"], w["D"], w["S"]
     total_steps = 2 * (args.steps + args.warmup) + 8
@@ -328,8 +333,8 @@ def run_gqa(args, w, world, rank, local, dist):
     pool = rb.Pool(dev, L.POOL_GQA, 1, B * pages_per, PAGE, B, pages_per, num_kv_heads=Hkv, head_dim=D)
     pool.set_tables(rng.permutation(B * pages_per).astype(np.int32).reshape(B, pages_per))
     blk = min(ctx0, 1024)
-    srcK = orc.bf16_from_f32(rng.standard_normal((B * blk, Hkv, D), dtype=np.float32))
-    srcV = orc.bf16_from_f32(rng.standard_normal((B * blk, Hkv, D), dtype=np.float32))
+    srcK = bf16_bits(rng.standard_normal((B * blk, Hkv, D), dtype=np.float32))
+    srcV = bf16_bits(rng.standard_normal((B * blk, Hkv, D), dtype=np.float32))
     dK, dV = dev.upload(srcK), dev.upload(srcV)
     for _ in range(ctx0 // blk):
         pool.append(0, dK, dV, B, n_new=np.full(B, blk, np.int32))
@@ -339,7 +344,7 @@ def run_gqa(args, w, world, rank, local, dist):
     q = rng.standard_normal((B, S, H, D), dtype=np.float32)
     nk = rng.standard_normal((B * S, Hkv, D), dtype=np.float32)
     nv = rng.standard_normal((B * S, Hkv, D), dtype=np.float32)
-    d_q, d_nk, d_nv = dev.upload(orc.bf16_from_f32(q)), dev.upload(orc.bf16_from_f32(nk)), dev.upload(orc.bf16_from_f32(nv))
+    d_q, d_nk, d_nv = dev.upload(bf16_bits(q)), dev.upload(bf16_bits(nk)), dev.upload(bf16_bits(nv))
     d_out = dev.alloc(q.size * 4, L.DTYPE_F32)
     pins = [dev.pinned(a.shape, np.float32) for a in (q, nk, nv)]
     for p_, a in zip(pins, (q, nk, nv)):
@@ -370,7 +375,7 @@ def run_gqa(args, w, world, rank, local, dist):
         dm = H * D   # dModel = numHeads * headDim like NewMHA
 
         def weight(rows, cols):
-            return dev.upload(orc.bf16_from_f32(rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(1.0 / np.sqrt(rows))))
+            return dev.upload(bf16_bits(rng.standard_normal((rows, cols), dtype=np.float32) * np.float32(1.0 / np.sqrt(rows))))
 
         dW = {"w_q": weight(dm, H * D), "w_k": weight(dm, Hkv * D), "w_v": weight(dm, Hkv * D), "w_o": weight(H * D, dm)}
         x_host = rng.standard_normal((B, S, dm), dtype=np.float32)
