@@ -346,3 +346,27 @@ def test_gqa_layer_fast_decode_and_verify(dev, oracle):
     pool.destroy()
     for v in dW.values():
         v.free()
+
+
+def test_gqa_layer_fast_more_rows_than_one_mma_tile(dev, oracle):
+    """40 sequences x 4 new tokens = 160 activation rows: the projection GEMM runs two 128-row blocks (the second one
+    partly out of range), with two heads of 128 on one kv head."""
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(33)
+    D, H, Hkv, B, S = 256, 2, 1, 40, 4
+    W = make_gqa_weights(oracle, rng, D, H, Hkv)
+    dW = {k: dev.upload(v) for k, v in W.items()}
+    pool = build_gqa_pool(dev, rng, B, 192, Hkv, D // H)
+    ol = OracleGqaLayer(oracle, W, D, H, Hkv, 10000.0, 192, True)
+    ol.add_sequences(B)
+    gqa_prefill(rng, oracle, pool, ol, [int(x) for x in rng.integers(0, 150, B)])
+    x = rng.standard_normal((B, S, D), dtype=np.float32)
+    got = np.empty_like(x)
+    pool.forward_cached(0, B, x, got, dW, D, H, q_tokens=S)
+    with oracle.exact_exp():
+        ref = ol.step(x)
+    _close(oracle, got, ref, "gqa layer 160 rows")
+    assert pool.status() == 0
+    pool.destroy()
+    for v in dW.values():
+        v.free()
