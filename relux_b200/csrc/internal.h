@@ -34,6 +34,9 @@ struct Device {
   size_t total_mem = 0;
   char name[256] = {0};
   cudaStream_t stream = nullptr;
+  // side stream for small kernels that do not depend on their predecessor (forked from / joined to `stream` by events)
+  cudaStream_t side_stream = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
   std::mutex mu;
   int64_t launches = 0;
   void* flush_buf = nullptr;

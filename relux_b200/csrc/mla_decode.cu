@@ -251,6 +251,23 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   cudaStream_t st = p->dev->stream;
   int32_t rc = grow(p->dev, p->q_abs, (size_t)rows * H * roww * 2);
   if (rc) return rc;
+  const bool sm100 = mla_sm100_eligible(p, a);
+  // two tensor-core variants: 128-token tiles (default) and 256-token tiles (RELUX_MLA_TILE=256; fewer tensor
+  // cycles per token but too little shared memory left to cover the load latency, measured 12 % slower)
+  const char* tile_env = getenv("RELUX_MLA_TILE");
+  const bool t256 = sm100 && tile_env && atoi(tile_env) == 256;
+  SplitPlan plan;
+  // The stream partition depends on the cached lengths only, the absorb on the queries only: the one-block builder
+  // runs on the side stream next to the absorb kernel and is joined before the decode kernel.
+  cudaStream_t side = p->dev->side_stream;
+  const bool fork = sm100 && !t256 && side != nullptr && !getenv("RELUX_NO_SIDE_STREAM");
+  if (fork) {
+    RELUX_CUDA_TRY(cudaEventRecord(p->dev->ev_fork, st));
+    RELUX_CUDA_TRY(cudaStreamWaitEvent(side, p->dev->ev_fork, 0));
+    rc = plan_stream(p, sb, a.layer, a.extra_tokens, mla_sm100_workers(p, S), 2, &plan, side);
+    if (rc) return rc;
+    RELUX_CUDA_TRY(cudaEventRecord(p->dev->ev_join, side));
+  }
   const bool proj_mma = mla_proj_mma_eligible(Dh, dC);
   if (proj_mma) {
     rc = launch_mla_absorb_mma(p->dev, d_q, d_qr, a.q_dtype == RELUX_DTYPE_BF16, (const uint16_t*)a.w_uk, (uint16_t*)p->q_abs.p, rows, H, dC,
@@ -265,14 +282,10 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
     RELUX_CUDA_TRY(cudaGetLastError());
     count_launch(p->dev);
   }
-  const bool sm100 = mla_sm100_eligible(p, a);
-  // two tensor-core variants: 128-token tiles (default) and 256-token tiles (RELUX_MLA_TILE=256; fewer tensor
-  // cycles per token but too little shared memory left to cover the load latency, measured 12 % slower)
-  const char* tile_env = getenv("RELUX_MLA_TILE");
-  const bool t256 = sm100 && tile_env && atoi(tile_env) == 256;
-  SplitPlan plan;
-  if (sm100 && !t256)   // persistent CTA pairs over a stream partition; ranges are whole 128-token tiles
-    rc = plan_stream(p, sb, a.layer, a.extra_tokens, mla_sm100_workers(p, S), 2, &plan);
+  if (fork)
+    RELUX_CUDA_TRY(cudaStreamWaitEvent(st, p->dev->ev_join, 0));
+  else if (sm100 && !t256)   // persistent CTA pairs over a stream partition; ranges are whole 128-token tiles
+    rc = plan_stream(p, sb, a.layer, a.extra_tokens, mla_sm100_workers(p, S), 2, &plan, st);
   else
     rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, t256 ? 2 * S : std::max(1, rows_total / 16), t256 ? 4 : 1, t256 ? 4 : 1, t256 ? 320 : 0, &plan);
   if (rc) return rc;

@@ -411,6 +411,12 @@ API int32_t relux_cuda_device_open(int32_t device_index, relux_device_t* out) {
   snprintf(d->name, sizeof(d->name), "%s", prop.name);
   e = cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking);
   if (e != cudaSuccess) { delete d; return cuda_fail(e, "cudaStreamCreate"); }
+  if (cudaStreamCreateWithFlags(&d->side_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&d->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&d->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+    (void)cudaGetLastError();   // the side stream is an optimisation: without it the kernels stay on the main stream
+    d->side_stream = nullptr;
+  }
   *out = d;
   return RELUX_OK;
 }
@@ -423,6 +429,9 @@ API int32_t relux_cuda_device_close(relux_device_t h) {
     if (g.rc) return g.rc;
     cudaStreamSynchronize(dev->stream);
     if (dev->flush_buf) cudaFree(dev->flush_buf);
+    if (dev->side_stream) { cudaStreamSynchronize(dev->side_stream); cudaStreamDestroy(dev->side_stream); }
+    if (dev->ev_fork) cudaEventDestroy(dev->ev_fork);
+    if (dev->ev_join) cudaEventDestroy(dev->ev_join);
     cudaStreamDestroy(dev->stream);
     dev->magic = 0;
   }

@@ -41,7 +41,8 @@ int32_t plan_splitkv(Pool* p, const SeqBatch& sb, int layer, int extra, int ctas
 // Stream partition for persistent kernels: the pages of all sequences of the call, laid end to end, are cut into
 // `workers` equal ranges of `chunk_pages` pages (a multiple of `page_multiple`); one item = the part of one sequence
 // inside one range, so a worker meets an item boundary only where a sequence ends inside its range.
-int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int workers, int page_multiple, SplitPlan* plan);
+// `st`: the stream the builder kernel is launched on (the pool's main stream, or the device's side stream).
+int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int workers, int page_multiple, SplitPlan* plan, cudaStream_t st);
 int32_t launch_build_worklist_raw(cudaStream_t st, const int32_t* len, const int32_t* seq_ids, int n_seqs, int extra, int page_tokens,
                                   int chunk_pages, WorkItem* items, int32_t* chunk_off);
 int32_t launch_merge_raw(cudaStream_t st, const float* part_o, const float* part_ml, const int32_t* chunk_off, int n_seqs, int rows,
