@@ -100,3 +100,50 @@ def test_gqa_fast_against_reference_kernels(dev, oracle, trial):
     assert pool.status() == 0
     _check(fast, ref, "trial %d: B=%d S=%d H=%d Hkv=%d causal=%s lens=%s" % (trial, B, S, H, Hkv, causal, lens.tolist()[:8]))
     pool.destroy()
+
+
+@pytest.mark.parametrize("trial", range(8))
+def test_mla_layer_fast_against_reference_mode(dev, oracle, trial):
+    """Whole-layer step: tensor-core projections (odd K / N sizes: partial pipeline steps, column tiles narrower than a
+    TMA box, several row blocks) + RoPE + append + decode against the reference-order kernels on the same inputs."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(3000 + trial)
+    H = int(rng.choice([2, 4, 8]))
+    Dh = int(rng.choice([16, 24, 32, 40]))
+    D, dC, dHR, P = H * Dh, int(rng.choice([64, 128])), int(rng.choice([8, 16])), 64
+    B = int(rng.integers(1, 48))
+    S = int(rng.choice([1, 1, 2, 5]))
+    lens = rng.integers(0, 200, B).astype(np.int32)
+    shapes = {"w_q": (D, H * Dh), "w_qr": (D, H * dHR), "w_dkv": (D, dC), "w_kr": (D, dHR), "w_uk": (dC, H * Dh),
+              "w_uv": (dC, H * Dh), "w_o": (H * Dh, D)}
+    W = {k: oracle.bf16_from_f32(rng.standard_normal(sh, dtype=np.float32) * np.float32(1.0 / np.sqrt(sh[0]))) for k, sh in shapes.items()}
+    dW = {k: dev.upload(v) for k, v in W.items()}
+    pages_per = (int(lens.max()) + 2 * S + P - 1) // P + 1
+    outs = []
+    x1 = rng.standard_normal((B, S, D), dtype=np.float32)
+    x2 = rng.standard_normal((B, S, D), dtype=np.float32)
+    n = int(lens.sum())
+    c0 = oracle.bf16_from_f32(rng.standard_normal((n, dC), dtype=np.float32))
+    r0 = oracle.bf16_from_f32(rng.standard_normal((n, dHR), dtype=np.float32))
+    tables = permuted_tables(rng, B, pages_per)
+    for mode in (L.ATTN_FAST, L.ATTN_REFERENCE):
+        pool = rb.Pool(dev, L.POOL_MLA, 1, B * pages_per, P, B, pages_per, dC=dC, dHR=dHR)
+        pool.set_tables(tables)
+        if n:
+            pool.append(0, c0, r0, B, n_new=lens)
+        res = []
+        for x in (x1, x2):      # the second step attends over rows the first one wrote
+            y = np.empty_like(x)
+            pool.forward_cached(0, B, x, y, dW, D, H, q_tokens=S, mode=mode)
+            res.append(y)
+        assert pool.status() == 0
+        outs.append(res)
+        pool.destroy()
+    for v in dW.values():
+        v.free()
+    for step in range(2):
+        fast, ref = outs[0][step], outs[1][step]
+        rel = np.linalg.norm(fast.astype(np.float64) - ref) / max(np.linalg.norm(ref), 1e-30)
+        assert np.isfinite(fast).all() and rel <= 5e-2, "trial %d step %d: D=%d H=%d dC=%d dHR=%d B=%d S=%d rel %g" % (
+            trial, step, D, H, dC, dHR, B, S, rel)
