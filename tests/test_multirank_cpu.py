@@ -81,6 +81,8 @@ def test_stream_partition_properties():
     """The partition the persistent MLA decode kernel walks (host statement of the same arithmetic): every page of every
     sequence is in exactly one item, items of a sequence and of a worker are contiguous, no worker holds more than one
     range, ranges are whole tiles."""
+    import __graft_entry__ as g
+    g.build()     # the partition arithmetic is the library's own host code (no GPU needed to call it)
     from relux_b200.sharding import stream_partition
     rng = np.random.default_rng(4)
     cases = [[512] * 64, [1], [0, 3, 0, 9], list(rng.integers(1, 200, 300)), [9000], list(rng.integers(16, 513, 16))]
