@@ -30,6 +30,8 @@ WORKLOADS = {
     "mla_decode_b64_ctx4k": dict(kind="mla", B=64, ctx=4096, H=128, Dh=128, dC=512, dHR=64),
     # the reference's own MLA example shape (mla_test.go:96-101: d_model 4096, 32 heads of 128, latent 512, rope 64)
     "mla_decode_h32_b64_ctx32k": dict(kind="mla", B=64, ctx=32768, H=32, Dh=128, dC=512, dHR=64),
+    # MLA speculative verify: 4 draft tokens per step (the tensor work is 4x a decode step, the cache is read from HBM once)
+    "mla_verify_b64_ctx32k": dict(kind="mla", B=64, ctx=32768, H=128, Dh=128, dC=512, dHR=64, S=4),
     # config 4 per GPU: 16 sequences with context lengths uniform in [1024, 32768] (one global seeded draw of 16 x world
     # lengths, dealt to the ranks longest-first so that every GPU holds about the same number of cached tokens)
     "mla_decode_ragged_b16": dict(kind="mla", B=16, ctx=32768, H=128, Dh=128, dC=512, dHR=64, ragged=True),
@@ -160,8 +162,9 @@ def run_mla(args, w, world, rank, local, dist):
     from relux_b200 import lib as L
 
     B, ctx0, H, Dh, dC, dHR = w["B"], w["ctx"], w["H"], w["Dh"], w["dC"], w["dHR"]
+    S = int(w.get("S", 1))
     total_steps = 2 * (args.steps + args.warmup) + 8
-    pages_per = (ctx0 + total_steps + PAGE - 1) // PAGE + 1
+    pages_per = (ctx0 + total_steps * S + S + PAGE - 1) // PAGE + 1
     dev = rb.Device(local)
     rng = np.random.default_rng(7 + rank)
     pool = rb.Pool(dev, L.POOL_MLA, 1, B * pages_per, PAGE, B, pages_per, dC=dC, dHR=dHR)
@@ -207,6 +210,38 @@ def run_mla(args, w, world, rank, local, dist):
         pool.append(0, pins[0].array, pins[1].array, B)
         pool.decode(0, B, pins[2].array, pin_out.array, H, Dh, scale, q_rope=pins[3].array, w_uk=d_wuk, w_uv=d_wuv)
 
+    accepted = [0]
+    if S > 1:
+        # verify step: S draft rows per sequence written past the cursor, S query tokens (causal inside the draft), then
+        # an accepted prefix of 1..S tokens is committed; tokens/s counts accepted tokens
+        dr_c = rng.standard_normal((B * S, dC), dtype=np.float32)
+        dr_r = rng.standard_normal((B * S, dHR), dtype=np.float32)
+        vq = rng.standard_normal((B, S, H, Dh), dtype=np.float32)
+        vqr = rng.standard_normal((B, S, H, dHR), dtype=np.float32)
+        d_dr_c, d_dr_r = dev.upload(bf16_bits(dr_c)), dev.upload(bf16_bits(dr_r))
+        d_vq, d_vqr = dev.upload(bf16_bits(vq)), dev.upload(bf16_bits(vqr))
+        d_vout = dev.alloc(B * S * H * Dh * 4, L.DTYPE_F32)
+        vpins = [dev.pinned(a_.shape, np.float32) for a_ in (dr_c, dr_r, vq, vqr)]
+        for p_, a_ in zip(vpins, (dr_c, dr_r, vq, vqr)):
+            p_.array[...] = a_
+        vpin_out = dev.pinned((B, S, H, Dh), np.float32)
+        vlens = lens0.copy()
+
+        def commit():
+            acc = rng.integers(1, S + 1, B)
+            vlens[:] += acc
+            accepted[0] += int(acc.sum())
+            pool.set_len(0, vlens.astype(np.int32))
+
+        def step_resident():
+            pool.verify(0, B, d_vq, d_vout, d_dr_c, d_dr_r, H, Dh, scale, S, q_rope=d_vqr, w_uk=d_wuk, w_uv=d_wuv)
+            commit()
+
+        def step_e2e():
+            pool.verify(0, B, vpins[2].array, vpin_out.array, vpins[0].array, vpins[1].array, H, Dh, scale, S, q_rope=vpins[3].array,
+                        w_uk=d_wuk, w_uv=d_wuv)
+            commit()
+
     layer = bool(w.get("layer"))
     if layer:
         # layer step: x [B, 1, dModel] in, [B, 1, dModel] out; dModel = H * Dh like NewMLA.  Weights N(0, 1/in) -> bf16,
@@ -242,6 +277,7 @@ def run_mla(args, w, world, rank, local, dist):
         dev.sync()
         barrier(dist)
         n0 = dev.launch_count()
+        accepted[0] = 0
         if sampler is not None:
             sampler.begin()
         e0.record()
@@ -258,16 +294,21 @@ def run_mla(args, w, world, rank, local, dist):
         sampler.start()
         time.sleep(0.3)
     ms_res, launches = timed(step_resident, args.steps, args.warmup, sampler if rank == 0 else None)
+    acc_res = accepted[0]
     clocks = sampler.finish() if rank == 0 else None
     # dominant kernel: the decode kernel; every call records a CUDA event pair around that launch on the launching
     # stream, read here for the calls of the timed region (the library keeps the last 256)
     kernel_ms, counted = pool.mean_kernel_ms(args.steps)
-    len_end = sum(pool.seq_len(0, b) for b in range(B))          # every sequence grew by one row per call
-    rows_mean = len_end - B * (counted - 1) / 2.0                 # cached rows read per launch, mean over those calls
+    len_end = sum(pool.seq_len(0, b) for b in range(B))
+    if S > 1:   # verify: every call read the committed rows plus S draft rows; lengths grew by (S + 1) / 2 per call on average
+        rows_mean = len_end + B * S - B * (S + 1) / 2.0 * (counted + 1) / 2.0
+    else:       # every sequence grew by one row per call
+        rows_mean = len_end - B * (counted - 1) / 2.0              # cached rows read per launch, mean over those calls
     ms_e2e, _ = timed(step_e2e, args.steps, args.warmup)
+    acc_e2e = accepted[0]
     assert pool.status() == 0, "device status word is set"
     alg_bytes = rows_mean * (dC + dHR) * 2
-    alg_flops = 2.0 * H * rows_mean * ((dC + dHR) + dC)
+    alg_flops = 2.0 * H * S * rows_mean * ((dC + dHR) + dC)
     peak, peak_src = read_peaks()
     pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if peak_src == "measured" else {}
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
@@ -279,8 +320,12 @@ def run_mla(args, w, world, rank, local, dist):
     d2h = pin_out.array.nbytes
     if layer:
         h2d, d2h = x_host.nbytes, x_host.nbytes
+    if S > 1:   # accepted tokens; every rank draws from its own seeded stream with the same law
+        value = acc_res * world / (ms_res * 1e-3)
+        e2e = acc_e2e * world / (ms_e2e * 1e-3)
+        h2d, d2h = sum(a_.nbytes for a_ in (dr_c, dr_r, vq, vqr)), vpin_out.array.nbytes
     line = {
-        "metric": "mla_layer_decode_tokens_per_s" if layer else "mla_decode_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "metric": "mla_layer_decode_tokens_per_s" if layer else ("mla_verify_accepted_tokens_per_s" if S > 1 else "mla_decode_tokens_per_s"), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": args.workload, "batch_per_gpu": B,
