@@ -312,6 +312,49 @@ typedef struct relux_gqa_layer_args {
 } relux_gqa_layer_args;
 int32_t relux_gqa_forward_cached(relux_pool_t pool, const relux_gqa_layer_args* args);
 
+/* ---- token selection after a verify pass -----------------------------------------------------
+ * relux_spec_accept replaces SpeculativeDecoder.acceptPhase with resampleRejected (speculative.go:211-295; softmaxAlloc
+ * :346-368) for a batch of independent sequences, and the Sampler.Sample call it ends with when every draft token was
+ * accepted (internal/transformer/sampler.go:73-218: temperature, top-k, nucleus, min-p, categorical draw; the
+ * repetition penalties, which acceptPhase never uses, are left out).  The reference takes its uniform numbers from a
+ * math/rand stream; here the caller supplies them: draws [n_seqs][k + 1], consumed per sequence in the reference's
+ * order (one per examined draft token, then one for the resample or for the final sample).
+ *   draft_tokens [n_seqs][k], draft_logits [n_seqs][k][vocab], target_logits [n_seqs][k + 1][vocab] (row i judges
+ *   draft token i, row k gives the bonus token), all float32 / int32, in host or device memory (mem).
+ *   n_accepted [n_seqs] and next_token [n_seqs] are written to HOST memory; the call synchronises the stream.
+ * k = 0 is plain Sampler.Sample on target_logits [n_seqs][vocab] with draws [n_seqs] (n_accepted may be NULL).
+ * commit != 0: afterwards every layer's length of sequence seq_ids[i] grows by n_accepted[i] + 1 -- the rows of the
+ * token fed first and of the accepted draft tokens that a relux_*_verify call wrote past the cursor become part of
+ * the sequence (the reference's startPos += nAccepted + 1, speculative.go:155).
+ * RELUX_ATTN_FAST: one thread-block cluster per sequence, parallel float32 sums -- a decision can differ from the
+ * reference's only when a draw lies within rounding distance of a boundary.  RELUX_ATTN_REFERENCE: the reference's
+ * sequential float32 order, bit-exact, one thread per sequence.
+ * Errors: RELUX_ERR_INVALID_ARG for a draft token outside [0, vocab) (the reference would panic on the index). */
+typedef struct relux_sampler_params {
+  float temperature;        /* <= 0 is replaced by 1e-5 (sampler.go:90-93) */
+  int32_t top_k;            /* <= 0 or >= vocab: off */
+  float top_p;              /* <= 0 or >= 1: off */
+  float min_p;              /* <= 0: off */
+} relux_sampler_params;
+typedef struct relux_spec_accept_args {
+  int32_t n_seqs;
+  int32_t k;
+  int32_t vocab;
+  int32_t mem;              /* RELUX_MEM_* of draft_tokens, draft_logits, target_logits and draws */
+  const int32_t* draft_tokens;
+  const float* draft_logits;
+  const float* target_logits;
+  const float* draws;
+  relux_sampler_params sampler;
+  int32_t mode;             /* RELUX_ATTN_FAST | RELUX_ATTN_REFERENCE */
+  int32_t commit;
+  const int32_t* seq_ids;   /* host [n_seqs]; NULL = 0..n_seqs-1; only read when commit != 0 */
+  int32_t* n_accepted;      /* host [n_seqs], out */
+  int32_t* next_token;      /* host [n_seqs], out */
+  int32_t reserved[4];
+} relux_spec_accept_args;
+int32_t relux_spec_accept(relux_pool_t pool, const relux_spec_accept_args* args);
+
 /* GQA flash-decode / verify that allocates nothing.  It has no counterpart in the reference; it exists for callers
  * that may not allocate device memory at the moment they decode: a serving loop whose memory budget has been handed
  * out completely (so a late cudaMalloc can fail or stall the whole device while it synchronises), or code running

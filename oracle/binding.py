@@ -30,8 +30,8 @@ class ModelCfg(C.Structure):
 
 
 def build(force=False):
-    src = os.path.join(_HERE, "relux_oracle.cpp")
-    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+    srcs = [os.path.join(_HERE, n) for n in ("relux_oracle.cpp", "relux_oracle_sampling.inc")]
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < max(os.path.getmtime(s) for s in srcs):
         subprocess.check_call(["make", "-C", _HERE, "-s"])
     return _SO
 
@@ -373,3 +373,50 @@ class exact_exp:
 
 def num_threads():
     return int(lib().ro_num_threads())
+
+
+# ---- sampler and speculative accept step ------------------------------------
+class SamplerCfg(C.Structure):
+    """Sampler's fields (sampler.go:34-44) without the generator: draws are passed to each call."""
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("min_p", C.c_float),
+                ("repeat_penalty", C.c_float), ("frequency_penalty", C.c_float), ("presence_penalty", C.c_float),
+                ("repeat_window", C.c_int32)]
+
+
+def sampler_cfg(temperature=1.0, top_k=0, top_p=1.0, min_p=0.0, repeat_penalty=1.0, frequency_penalty=0.0,
+                presence_penalty=0.0, repeat_window=0):
+    return SamplerCfg(temperature, top_k, top_p, min_p, repeat_penalty, frequency_penalty, presence_penalty, repeat_window)
+
+
+def sampler_sample(cfg, logits, r, prev=None, return_probs=False):
+    """Sampler.Sample (sampler.go:73-218) with the categorical draw r supplied."""
+    l = f32(logits)
+    pv = _i32(prev) if prev is not None and len(prev) else None
+    probs = np.empty(l.size, np.float32)
+    lib().ro_sampler_sample.restype = C.c_int
+    tok = lib().ro_sampler_sample(C.byref(cfg), _p(l), C.c_int(l.size), _p(pv) if pv is not None else None,
+                                  C.c_int(0 if pv is None else pv.size), C.c_float(r), _p(probs))
+    return (int(tok), probs) if return_probs else int(tok)
+
+
+def softmax_alloc(logits):
+    """softmaxAlloc (speculative.go:346-368)."""
+    l = f32(logits)
+    out = np.empty_like(l)
+    lib().ro_softmax_alloc(_p(l), C.c_int(l.size), _p(out))
+    return out
+
+
+def spec_accept(cfg, draft_tokens, draft_logits, target_logits, draws):
+    """acceptPhase (speculative.go:211-253) for one sequence: draft_logits [k][V], target_logits [k+1][V],
+    draws [k+1] consumed in the reference's order.  Returns (n_accepted, next_token, draws_used, accept_probs[k])."""
+    dt = _i32(draft_tokens)
+    dl, tl, u = f32(draft_logits), f32(target_logits), f32(draws)
+    k, V = dl.shape
+    assert tl.shape == (k + 1, V) and u.size >= k + 1
+    nxt, used = C.c_int32(-1), C.c_int32(0)
+    ap = np.full(k, np.nan, np.float32)
+    lib().ro_spec_accept.restype = C.c_int
+    n = lib().ro_spec_accept(C.byref(cfg), _p(dt), _p(dl), _p(tl), C.c_int(k), C.c_int(V), _p(u), C.byref(nxt),
+                             C.byref(used), _p(ap))
+    return int(n), int(nxt.value), int(used.value), ap

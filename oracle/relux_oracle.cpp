@@ -1086,3 +1086,8 @@ RO_API int ro_num_threads(void) {
   return 1;
 #endif
 }
+
+// ----------------------------------------------------------------------------
+// Sampler.Sample and the speculative accept step   sampler.go:73-300, speculative.go:211-295, 346-368
+// ----------------------------------------------------------------------------
+#include "relux_oracle_sampling.inc"

@@ -284,6 +284,44 @@ class Pool:
         fn = self.lib.relux_mla_verify if self.kind == L.POOL_MLA else self.lib.relux_gqa_verify
         L.check(fn(self.h, C.byref(at), C.byref(ap)))
 
+    def spec_accept(self, n_seqs, k, vocab, draft_tokens, draft_logits, target_logits, draws, temperature=1.0, top_k=0,
+                    top_p=1.0, min_p=0.0, mode=L.ATTN_FAST, commit=False, seq_ids=None):
+        """acceptPhase + resampleRejected (speculative.go:211-295) for n_seqs sequences, ending in Sampler.Sample
+        (sampler.go:73-218) when all k draft tokens pass.  The four inputs are all numpy arrays or all device buffers;
+        draws [n_seqs, k + 1] are the uniform numbers the reference would take from its generator.  k = 0 samples one
+        token per row of target_logits [n_seqs, vocab].  Returns (n_accepted, next_token) as int32 arrays.
+        commit=True grows every layer of each sequence by n_accepted + 1 rows (the rows a verify call left past the cursor)."""
+        mems = {_mem(a) for a in (draft_tokens, draft_logits, target_logits, draws) if a is not None}
+        if len(mems) != 1:
+            raise TypeError("spec_accept: inputs must be all host arrays or all device buffers")
+        keep = []
+
+        def host(a, dt):
+            if a is None or _mem(a) == L.MEM_DEVICE:
+                return a
+            a = np.ascontiguousarray(a, dtype=dt)
+            keep.append(a)
+            return a
+
+        draft_tokens, draft_logits = host(draft_tokens, np.int32), host(draft_logits, np.float32)
+        target_logits, draws = host(target_logits, np.float32), host(draws, np.float32)
+        ids = None if seq_ids is None else np.ascontiguousarray(seq_ids, dtype=np.int32)
+        n_acc = np.full(n_seqs, -1, np.int32)
+        nxt = np.full(n_seqs, -1, np.int32)
+        args = L.SpecAcceptArgs(n_seqs=n_seqs, k=k, vocab=vocab, mem=mems.pop(), draft_tokens=_ptr(draft_tokens),
+                                draft_logits=_ptr(draft_logits), target_logits=_ptr(target_logits), draws=_ptr(draws),
+                                sampler=L.SamplerParams(float(temperature), int(top_k), float(top_p), float(min_p)), mode=mode,
+                                commit=int(commit), seq_ids=_ptr(ids), n_accepted=n_acc.ctypes.data, next_token=nxt.ctypes.data)
+        L.check(self.lib.relux_spec_accept(self.h, C.byref(args)))
+        return n_acc, nxt
+
+    def sample(self, logits, draws, vocab=None, n_rows=None, **kw):
+        """Sampler.Sample (sampler.go:73-218, without repetition penalties) for a batch of rows: logits [n, vocab],
+        draws [n]."""
+        if n_rows is None:
+            n_rows, vocab = logits.shape
+        return self.spec_accept(n_rows, 0, vocab, None, None, logits, draws, **kw)[1]
+
     def forward_cached(self, layer, n_seqs, x, out, weights, d_model, num_heads, q_tokens=1, causal=True, rope_base=0.0,
                        mode=L.ATTN_FAST, seq_ids=None, rope=True, advance=True):
         if self.kind == L.POOL_GQA:

@@ -777,6 +777,12 @@ API int32_t relux_seq_len(relux_pool_t h, int32_t layer, int32_t s, int32_t* len
 
 API int32_t relux_seq_set_len(relux_pool_t h, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const int32_t* new_len) {
   GET_POOL(h);
+  return seq_set_len(p, layer, n_seqs, seq_ids, new_len);
+}
+
+// The caller holds the device guard.
+int32_t relux::seq_set_len(Pool* p, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const int32_t* new_len) {
+  Device* dev = p->dev;
   const relux_pool_params& prm = p->prm;
   if (!new_len || layer >= prm.num_layers) { set_error("set_len: bad arguments"); return RELUX_ERR_INVALID_ARG; }
   SeqBatch sb;
@@ -882,6 +888,11 @@ API int32_t relux_mla_forward_cached(relux_pool_t h, const relux_mla_layer_args*
 API int32_t relux_gqa_forward_cached(relux_pool_t h, const relux_gqa_layer_args* a) {
   GET_POOL(h);
   return do_gqa_layer(p, a);
+}
+
+API int32_t relux_spec_accept(relux_pool_t h, const relux_spec_accept_args* a) {
+  GET_POOL(h);
+  return do_spec_accept(p, a);
 }
 
 API int32_t relux_pool_last_kernel_ms(relux_pool_t h, float* ms) {

@@ -1,0 +1,657 @@
+// Token selection after a speculative verify pass, on the device: SpeculativeDecoder.acceptPhase and
+// resampleRejected (speculative.go:211-295, softmaxAlloc :346-368) and Sampler.Sample without the repetition
+// penalties (internal/transformer/sampler.go:73-218).  The uniform draws the reference takes from math/rand are
+// arguments, consumed in the reference's order.
+//
+// FAST: one thread-block cluster per sequence.  The CTAs of a cluster split the vocabulary into contiguous slices;
+// every step of the reference's chain (row maximum, sum of exponentials, the top-k threshold, the nucleus cut, the
+// inverse-CDF search) is one pass over the row out of L2 with a reduction across the cluster through distributed shared
+// memory, so a row is read from HBM once however many passes follow.  Exponentials use the reference's fastexp32 bit
+// trick, which makes the distribution the reference's own; what differs is the order of the float32 sums (parallel
+// instead of sequential), so a decision can only differ when a draw falls within rounding distance of a boundary.
+// REFERENCE: one thread per sequence walks the reference's loops in the reference's order (bit-exact, slow).
+#include <cuda_runtime.h>
+#include <cooperative_groups.h>
+#include <cstdint>
+#include <vector>
+
+#include "common.cuh"
+#include "internal.h"
+
+namespace cg = cooperative_groups;
+
+namespace relux {
+
+int32_t stage_in(Pool* p, GrowBuf& buf, const void* src, size_t bytes, int mem, const void** dptr);   // runtime.cu
+
+namespace {
+
+constexpr int kSelThreads = 512;
+constexpr int kSelWarps = kSelThreads / 32;
+constexpr int kMaxCluster = 8;
+
+struct SelParams {
+  const int32_t* draft_tokens;   // [n][k] or nullptr (plain sampling)
+  const float* draft_logits;     // [n][k][V]
+  const float* target_logits;    // [n][k+1][V]; plain sampling: [n][V] with k = 0
+  const float* draws;            // [n][k+1]
+  int32_t* n_accepted;           // [n]
+  int32_t* next_token;           // [n]
+  int32_t* status;
+  int32_t k, vocab;
+  float temperature;
+  int32_t top_k;
+  float top_p, min_p;
+};
+
+// Shared memory of one CTA: exchange slots read by the other CTAs of the cluster.
+struct SelShared {
+  float red[2][4];            // double-buffered per-CTA partials of a cluster reduction (up to 4 values)
+  float warp_part[kSelWarps][4];
+  float hist_sum[256];
+  uint32_t hist_cnt[256];
+  float warp_seg[kSelWarps];  // per-warp segment sums of the search pass
+  int32_t found;
+};
+
+__device__ __forceinline__ uint32_t order_key(float x) {
+  uint32_t u = __float_as_uint(x);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// Everything the passes need to evaluate the reference's probability of one logit on the fly.
+struct Dist {
+  float temp;        // 1 = untouched
+  uint32_t topk_key; // elements whose key is below are masked (0 = nothing masked)
+  float m, inv1;     // maximum and 1 / sum of exponentials
+  float tau, inv2;   // nucleus: probabilities below tau are dropped, the rest scaled by inv2
+  float minp_thr, inv3;
+  __device__ __forceinline__ float scaled(float v) const { return temp == 1.0f ? v : __fdiv_rn(v, temp); }
+  __device__ __forceinline__ float p1(float v) const {
+    float x = scaled(v);
+    if (order_key(x) < topk_key) return 0.0f;
+    return __fmul_rn(fastexp32_ref(__fsub_rn(x, m)), inv1);
+  }
+};
+
+struct Ctx {
+  SelShared* sh;
+  int rank, csize;     // CTA rank in the cluster, cluster size
+  int lo, hi;          // this CTA's slice of the vocabulary
+  int wlo, whi;        // this warp's contiguous segment of the slice
+  int warp, lane;
+  uint32_t round;      // reduction counter (selects the exchange buffer)
+};
+
+// Sum (or maximum) of up to four per-thread values over the whole cluster; every thread of every CTA gets the same
+// result, added in CTA order.  One cluster barrier per call: the two exchange buffers alternate.
+template <bool kMax>
+__device__ void cluster_reduce4(Ctx& c, float (&v)[4]) {
+  cg::cluster_group cl = cg::this_cluster();
+#pragma unroll
+  for (int j = 0; j < 4; j++) v[j] = kMax ? warp_max(v[j]) : warp_sum(v[j]);
+  if (c.lane == 0) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) c.sh->warp_part[c.warp][j] = v[j];
+  }
+  __syncthreads();
+  const int buf = c.round & 1;
+  if (threadIdx.x < 4) {
+    float a = c.sh->warp_part[0][threadIdx.x];
+    for (int w = 1; w < kSelWarps; w++) a = kMax ? fmaxf(a, c.sh->warp_part[w][threadIdx.x]) : a + c.sh->warp_part[w][threadIdx.x];
+    c.sh->red[buf][threadIdx.x] = a;
+  }
+  cl.sync();
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    float a = kMax ? -INFINITY : 0.0f;
+    for (int r = 0; r < c.csize; r++) {
+      const float* remote = cl.map_shared_rank(&c.sh->red[buf][j], r);
+      a = kMax ? fmaxf(a, *remote) : a + *remote;
+    }
+    v[j] = a;
+  }
+  c.round++;
+}
+
+// Every CTA learns every CTA's value (in rank order), through the same exchange buffers as cluster_reduce4.
+__device__ void cluster_gather1(Ctx& c, float mine, float (&all)[kMaxCluster]) {
+  cg::cluster_group cl = cg::this_cluster();
+  const int buf = c.round & 1;
+  if (threadIdx.x == 0) c.sh->red[buf][0] = mine;
+  cl.sync();
+#pragma unroll
+  for (int r = 0; r < kMaxCluster; r++) all[r] = r < c.csize ? *cl.map_shared_rank(&c.sh->red[buf][0], r) : 0.0f;
+  c.round++;
+}
+
+// Calls f(index, value) for every element of this warp's segment of `row`, lanes interleaved (coalesced), four loads
+// in flight per lane.
+template <class F>
+__device__ __forceinline__ void for_segment(const Ctx& c, const float* __restrict__ row, F f) {
+  int i = c.wlo + c.lane;
+  for (; i + 96 < c.whi; i += 128) {
+    float a = __ldg(row + i), b = __ldg(row + i + 32), d = __ldg(row + i + 64), e = __ldg(row + i + 96);
+    f(i, a); f(i + 32, b); f(i + 64, d); f(i + 96, e);
+  }
+  for (; i < c.whi; i += 32) f(i, __ldg(row + i));
+}
+
+// Radix selection, eight bits a round, over keys that order like the values.  kWeighted = false: the key of the
+// `want`-th largest element (Sampler's kthLargest, sampler.go:283-300).  kWeighted = true: keys are probabilities and
+// the walk stops at the largest probability tau for which the sum of all probabilities >= tau reaches `want_sum` (the
+// nucleus cut of sampler.go:148-160; elements tied with tau are all kept).  Returns false when the total never
+// reaches want_sum.
+template <bool kWeighted, class KeyF>
+__device__ bool radix_select(Ctx& c, const float* __restrict__ row, KeyF key_weight, uint32_t want, float want_sum, uint32_t* key_out) {
+  cg::cluster_group cl = cg::this_cluster();
+  uint32_t prefix = 0, mask = 0;
+  float above = 0.0f;
+  __shared__ uint32_t comb_cnt[256];
+  __shared__ float comb_sum[256];
+  __shared__ uint32_t pick[2];
+  __shared__ float pick_above;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    if (threadIdx.x < 256) { c.sh->hist_cnt[threadIdx.x] = 0; c.sh->hist_sum[threadIdx.x] = 0.0f; }
+    __syncthreads();
+    for_segment(c, row, [&](int, float v) {
+      uint32_t key; float w;
+      key_weight(v, key, w);
+      if ((key & mask) == prefix) {
+        uint32_t d = (key >> shift) & 255u;
+        if (kWeighted) atomicAdd(&c.sh->hist_sum[d], w);
+        else atomicAdd(&c.sh->hist_cnt[d], 1u);
+      }
+    });
+    __syncthreads();
+    cl.sync();
+    if (threadIdx.x < 256) {
+      uint32_t n = 0; float s = 0.0f;
+      for (int r = 0; r < c.csize; r++) {
+        if (kWeighted) s += *cl.map_shared_rank(&c.sh->hist_sum[threadIdx.x], r);
+        else n += *cl.map_shared_rank(&c.sh->hist_cnt[threadIdx.x], r);
+      }
+      comb_cnt[threadIdx.x] = n; comb_sum[threadIdx.x] = s;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      pick[0] = 256;
+      if (kWeighted) {
+        float acc = above;
+        for (int b = 255; b >= 0; b--) {
+          float nxt = acc + comb_sum[b];
+          if (nxt >= want_sum) { pick[0] = b; break; }
+          acc = nxt;
+        }
+        pick_above = acc;
+      } else {
+        uint32_t acc = 0;
+        for (int b = 255; b >= 0; b--) {
+          if (acc + comb_cnt[b] >= want) { pick[0] = b; pick[1] = want - acc; break; }
+          acc += comb_cnt[b];
+        }
+      }
+    }
+    __syncthreads();
+    const uint32_t digit = pick[0];
+    if (kWeighted) above = pick_above; else want = pick[1];
+    cl.sync();   // remote readers are done with this round's histograms
+    if (digit == 256) return false;
+    prefix |= digit << shift;
+    mask |= 255u << shift;
+  }
+  *key_out = prefix;
+  return true;
+}
+
+// Inverse-CDF search: the first index whose running sum of prob(index, value) exceeds r (Sampler.Sample step 8,
+// sampler.go:200-209; resampleRejected, speculative.go:271-291), or `dflt` when the sum never does.  Sums run per
+// warp segment, then in segment order; the segment that crosses is walked again in index order.
+template <class ProbF>
+__device__ void cdf_find(Ctx& c, const float* __restrict__ row, ProbF prob, float r, int dflt, int32_t* out) {
+  float part = 0.0f;
+  for_segment(c, row, [&](int i, float v) { part += prob(i, v); });
+  part = warp_sum(part);
+  if (c.lane == 0) c.sh->warp_seg[c.warp] = part;
+  __syncthreads();
+  float tot = 0.0f;
+  for (int w = 0; w < kSelWarps; w++) tot += c.sh->warp_seg[w];
+  float all[kMaxCluster];
+  cluster_gather1(c, tot, all);
+  float base = 0.0f;
+  int cross = -1;
+  float run = 0.0f;
+  for (int q = 0; q < c.csize; q++) {
+    if (q == c.rank) base = run;
+    run += all[q];
+    if (cross < 0 && run > r) cross = q;
+  }
+  // No path below leaves early with the cluster's exchange still in use: the caller ends with a cluster barrier.
+  if (cross < 0) {
+    if (c.rank == 0 && threadIdx.x == 0) *out = dflt;
+  } else if (cross == c.rank) {
+    // this CTA holds the crossing: pick the warp, then walk its segment in order
+    int wsel = kSelWarps - 1;
+    float wbase = base;
+    float acc = base;
+    for (int w = 0; w < kSelWarps; w++) {
+      float nxt = acc + c.sh->warp_seg[w];
+      wbase = acc;
+      if (nxt > r) { wsel = w; break; }
+      acc = nxt;
+    }
+    if (c.warp == wsel) {
+      int last_pos = -1, hit_idx = -1;
+      acc = wbase;
+      for (int j = c.wlo; j < c.whi && hit_idx < 0; j += 32) {
+        const int i = j + c.lane;
+        float p = i < c.whi ? prob(i, __ldg(row + i)) : 0.0f;
+        float x = p;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          float y = __shfl_up_sync(0xffffffffu, x, o);
+          if (c.lane >= o) x += y;
+        }
+        const uint32_t hit = __ballot_sync(0xffffffffu, i < c.whi && acc + x > r);
+        if (hit) hit_idx = j + __ffs(hit) - 1;
+        const uint32_t pos = __ballot_sync(0xffffffffu, p > 0.0f);
+        if (pos) last_pos = j + 31 - __clz(pos);
+        acc += __shfl_sync(0xffffffffu, x, 31);
+      }
+      // when rounding put the crossing past the end of the segment: the last element that carries probability
+      if (hit_idx < 0) hit_idx = last_pos >= 0 ? last_pos : (c.whi > c.wlo ? c.whi - 1 : dflt);
+      if (c.lane == 0) *out = hit_idx;
+    }
+  }
+}
+
+// Sampler.Sample on one row (sampler.go:73-218, steps 3-8; no repetition penalties), one cluster per row.
+__device__ void sample_row(Ctx& c, const SelParams& prm, const float* __restrict__ row, float r, int32_t* out) {
+  const int V = prm.vocab;
+  Dist d;
+  d.temp = prm.temperature <= 0.0f ? 1e-5f : prm.temperature;
+  d.topk_key = 0; d.tau = 0.0f; d.inv2 = 1.0f; d.minp_thr = 0.0f; d.inv3 = 1.0f;
+  bool nucleus = false, minp = false;
+  int topk = prm.top_k;
+  if (topk < 0 || topk >= V) topk = 0;
+  if (topk > 0) {
+    uint32_t key = 0;
+    radix_select<false>(c, row, [&](float v, uint32_t& k, float& w) { k = order_key(d.scaled(v)); w = 0.0f; }, (uint32_t)topk, 0.0f, &key);
+    d.topk_key = key;
+  }
+  float v4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  for_segment(c, row, [&](int, float v) { v4[0] = fmaxf(v4[0], d.scaled(v)); });
+  cluster_reduce4<true>(c, v4);
+  d.m = v4[0];
+  d.inv1 = 1.0f;
+  v4[0] = v4[1] = v4[2] = v4[3] = 0.0f;
+  for_segment(c, row, [&](int, float v) { v4[0] += d.p1(v); });
+  cluster_reduce4<false>(c, v4);
+  if (v4[0] > 0.0f) d.inv1 = __fdiv_rn(1.0f, v4[0]);
+  float topP = prm.top_p;
+  if (topP <= 0.0f || topP > 1.0f) topP = 1.0f;
+  if (topP < 1.0f) {
+    nucleus = true;
+    uint32_t key = 0;
+    bool cut = radix_select<true>(c, row, [&](float v, uint32_t& k, float& w) { w = d.p1(v); k = __float_as_uint(w); }, 0u, topP, &key);
+    const float tau = cut ? __uint_as_float(key) : 0.0f;
+    v4[0] = v4[1] = v4[2] = v4[3] = 0.0f;
+    for_segment(c, row, [&](int, float v) { float p = d.p1(v); if (p >= tau) v4[0] += p; });
+    cluster_reduce4<false>(c, v4);
+    d.tau = tau;
+    d.inv2 = v4[0] > 0.0f ? __fdiv_rn(1.0f, v4[0]) : 1.0f;
+  }
+  // Dist::p2 drops below tau only when tau > 0; the renormalisation applies whenever the nucleus step ran
+  auto p2 = [&](float v) { float p = d.p1(v); if (nucleus) p = p < d.tau ? 0.0f : __fmul_rn(p, d.inv2); return p; };
+  if (prm.min_p > 0.0f) {
+    minp = true;
+    // the largest probability belongs to the row maximum, which no filter removes
+    v4[0] = v4[1] = v4[2] = v4[3] = 0.0f;
+    for_segment(c, row, [&](int, float v) { v4[0] = fmaxf(v4[0], p2(v)); });
+    cluster_reduce4<true>(c, v4);
+    const float thr = __fmul_rn(v4[0], prm.min_p);
+    v4[0] = v4[1] = v4[2] = v4[3] = 0.0f;
+    for_segment(c, row, [&](int, float v) { float p = p2(v); if (!(p < thr)) v4[0] += p; });
+    cluster_reduce4<false>(c, v4);
+    d.minp_thr = thr;
+    d.inv3 = v4[0] > 0.0f ? __fdiv_rn(1.0f, v4[0]) : 1.0f;
+  }
+  auto p3 = [&](int, float v) { float p = p2(v); if (minp) p = p < d.minp_thr ? 0.0f : __fmul_rn(p, d.inv3); return p; };
+  cdf_find(c, row, p3, r, V - 1, out);
+}
+
+__global__ void __launch_bounds__(kSelThreads) spec_accept_kernel(SelParams prm) {
+  cg::cluster_group cl = cg::this_cluster();
+  __shared__ SelShared sh;
+  Ctx c;
+  c.sh = &sh;
+  c.csize = (int)cl.num_blocks();
+  c.rank = (int)cl.block_rank();
+  c.warp = threadIdx.x >> 5;
+  c.lane = threadIdx.x & 31;
+  c.round = 0;
+  const int V = prm.vocab, k = prm.k;
+  const int per = (V + c.csize - 1) / c.csize;
+  c.lo = min(V, c.rank * per);
+  c.hi = min(V, c.lo + per);
+  const int wper = (c.hi - c.lo + kSelWarps - 1) / kSelWarps;
+  c.wlo = min(c.hi, c.lo + c.warp * wper);
+  c.whi = min(c.hi, c.wlo + wper);
+  const int b = blockIdx.x / c.csize;
+  const float* draws = prm.draws + (size_t)b * (k + 1);
+  int32_t* out_tok = prm.next_token + b;
+  const bool writer = c.rank == 0 && threadIdx.x == 0;
+  int used = 0;
+  int n_acc = k;
+  bool done = false;
+  for (int i = 0; i < k && !done; i++) {
+    const float* drow = prm.draft_logits + ((size_t)b * k + i) * V;
+    const float* trow = prm.target_logits + ((size_t)b * (k + 1) + i) * V;
+    const int tok = prm.draft_tokens[(size_t)b * k + i];
+    if (tok < 0 || tok >= V) {   // uniform over the cluster: every thread reads the same token
+      if (writer) { set_status(prm.status, RELUX_ERR_INVALID_ARG); *out_tok = -1; }
+      n_acc = -1;
+      done = true;
+      break;
+    }
+    float v4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    {
+      int j = c.wlo + c.lane;
+      for (; j < c.whi; j += 32) { v4[0] = fmaxf(v4[0], __ldg(drow + j)); v4[1] = fmaxf(v4[1], __ldg(trow + j)); }
+    }
+    cluster_reduce4<true>(c, v4);
+    const float md = v4[0], mt = v4[1];
+    v4[0] = v4[1] = v4[2] = v4[3] = 0.0f;
+    for (int j = c.wlo + c.lane; j < c.whi; j += 32) {
+      v4[0] += fastexp32_ref(__fsub_rn(__ldg(drow + j), md));
+      v4[1] += fastexp32_ref(__fsub_rn(__ldg(trow + j), mt));
+    }
+    cluster_reduce4<false>(c, v4);
+    const float invd = v4[0] > 0.0f ? __fdiv_rn(1.0f, v4[0]) : 1.0f;
+    const float invt = v4[1] > 0.0f ? __fdiv_rn(1.0f, v4[1]) : 1.0f;
+    const float dP = __fmul_rn(fastexp32_ref(__fsub_rn(__ldg(drow + tok), md)), invd);
+    const float tP = __fmul_rn(fastexp32_ref(__fsub_rn(__ldg(trow + tok), mt)), invt);
+    float ap = __fdiv_rn(tP, dP > 1e-10f ? dP : 1e-10f);
+    if (ap > 1.0f) ap = 1.0f;
+    const float u = draws[used++];
+    if (u < ap) continue;
+    // rejected at i: resample from norm(max(0, p_target - p_draft))   speculative.go:256-295
+    auto adj = [&](int j, float tv) {
+      float tp = __fmul_rn(fastexp32_ref(__fsub_rn(tv, mt)), invt);
+      float dp = __fmul_rn(fastexp32_ref(__fsub_rn(__ldg(drow + j), md)), invd);
+      float diff = __fsub_rn(tp, dp);
+      return diff < 0.0f ? 0.0f : diff;
+    };
+    v4[0] = v4[1] = v4[2] = v4[3] = 0.0f;
+    for_segment(c, trow, [&](int j, float tv) { v4[0] += adj(j, tv); });
+    cluster_reduce4<false>(c, v4);
+    const float r = draws[used++];
+    if (v4[0] > 0.0f) {
+      const float inv = __fdiv_rn(1.0f, v4[0]);
+      cdf_find(c, trow, [&](int j, float tv) { return __fmul_rn(adj(j, tv), inv); }, r, 0, out_tok);
+    } else {
+      cdf_find(c, trow, [&](int, float tv) { return __fmul_rn(fastexp32_ref(__fsub_rn(tv, mt)), invt); }, r, 0, out_tok);
+    }
+    n_acc = i;
+    done = true;
+  }
+  if (!done) sample_row(c, prm, prm.target_logits + ((size_t)b * (k + 1) + k) * V, draws[used++], out_tok);
+  if (writer && prm.n_accepted) prm.n_accepted[b] = n_acc;
+  cl.sync();   // no CTA leaves while another may still read its exchange buffers
+}
+
+// ---- REFERENCE: one thread per sequence, the reference's loops in the reference's order ------------------------
+__device__ void ref_softmax_alloc(const float* logits, int n, float* probs) {   // speculative.go:346-368
+  float maxV = logits[0];
+  for (int i = 1; i < n; i++)
+    if (logits[i] > maxV) maxV = logits[i];
+  float sum = 0.0f;
+  for (int i = 0; i < n; i++) {
+    probs[i] = fastexp32_ref(__fsub_rn(logits[i], maxV));
+    sum = __fadd_rn(sum, probs[i]);
+  }
+  if (sum > 0.0f) {
+    const float inv = __fdiv_rn(1.0f, sum);
+    for (int i = 0; i < n; i++) probs[i] = __fmul_rn(probs[i], inv);
+  }
+}
+
+__device__ void ref_renormalise(float* probs, int n) {
+  float s = 0.0f;
+  for (int i = 0; i < n; i++) s = __fadd_rn(s, probs[i]);
+  if (s > 0.0f) {
+    const float inv = __fdiv_rn(1.0f, s);
+    for (int i = 0; i < n; i++) probs[i] = __fmul_rn(probs[i], inv);
+  }
+}
+
+// Sampler.Sample steps 3-8 (sampler.go:89-209).  scratch, probs: [n] floats; idx: [n] ints.
+__device__ int ref_sample(const SelParams& prm, const float* logits, int n, float r, float* scratch, float* probs, int32_t* idx) {
+  float temp = prm.temperature <= 0.0f ? 1e-5f : prm.temperature;
+  for (int i = 0; i < n; i++) scratch[i] = temp != 1.0f ? __fdiv_rn(logits[i], temp) : logits[i];
+  int topK = prm.top_k;
+  if (topK < 0 || topK >= n) topK = 0;
+  if (topK > 0) {
+    // value of the topK-th largest element, duplicates counted (kthLargest, sampler.go:283-300)
+    float bound = INFINITY;
+    int seen = 0;
+    float threshold = scratch[0];
+    while (true) {
+      float best = -INFINITY;
+      int cnt = 0;
+      for (int i = 0; i < n; i++) {
+        const float v = scratch[i];
+        if (v < bound) {
+          if (v > best) { best = v; cnt = 1; }
+          else if (v == best) cnt++;
+        }
+      }
+      if (cnt == 0) break;
+      seen += cnt;
+      threshold = best;
+      if (seen >= topK) break;
+      bound = best;
+    }
+    for (int i = 0; i < n; i++)
+      if (scratch[i] < threshold) scratch[i] = -INFINITY;
+  }
+  float maxV = scratch[0];
+  for (int i = 1; i < n; i++)
+    if (scratch[i] > maxV) maxV = scratch[i];
+  float sum = 0.0f;
+  for (int i = 0; i < n; i++) {
+    if (scratch[i] == -INFINITY) probs[i] = 0.0f;
+    else { probs[i] = fastexp32_ref(__fsub_rn(scratch[i], maxV)); sum = __fadd_rn(sum, probs[i]); }
+  }
+  if (sum > 0.0f) {
+    const float inv = __fdiv_rn(1.0f, sum);
+    for (int i = 0; i < n; i++) probs[i] = __fmul_rn(probs[i], inv);
+  }
+  float topP = prm.top_p;
+  if (topP <= 0.0f || topP > 1.0f) topP = 1.0f;
+  if (topP < 1.0f) {
+    // argsortDescF32's selection sort (sampler.go:268-281), stopped at the cut-off: later positions are all zeroed
+    for (int i = 0; i < n; i++) idx[i] = i;
+    float cum = 0.0f;
+    int cutoff = n;
+    for (int i = 0; i < n; i++) {
+      int maxJ = i;
+      for (int j = i + 1; j < n; j++)
+        if (probs[idx[j]] > probs[idx[maxJ]]) maxJ = j;
+      const int t = idx[i]; idx[i] = idx[maxJ]; idx[maxJ] = t;
+      cum = __fadd_rn(cum, probs[idx[i]]);
+      if (cum >= topP) { cutoff = i + 1; break; }
+    }
+    for (int j = cutoff; j < n; j++) probs[idx[j]] = 0.0f;
+    ref_renormalise(probs, n);
+  }
+  if (prm.min_p > 0.0f) {
+    float maxProb = 0.0f;
+    for (int i = 0; i < n; i++)
+      if (probs[i] > maxProb) maxProb = probs[i];
+    const float threshold = __fmul_rn(maxProb, prm.min_p);
+    for (int i = 0; i < n; i++)
+      if (probs[i] < threshold) probs[i] = 0.0f;
+    ref_renormalise(probs, n);
+  }
+  float cum = 0.0f;
+  for (int i = 0; i < n; i++) {
+    cum = __fadd_rn(cum, probs[i]);
+    if (r < cum) return i;
+  }
+  return n - 1;
+}
+
+__global__ void spec_accept_reference_kernel(SelParams prm, int n_seqs, float* fscratch, int32_t* iscratch) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= n_seqs) return;
+  const int V = prm.vocab, k = prm.k;
+  float* dp = fscratch + (size_t)b * 2 * V;
+  float* tp = dp + V;
+  int32_t* idx = iscratch + (size_t)b * V;
+  const float* draws = prm.draws + (size_t)b * (k + 1);
+  int used = 0;
+  for (int i = 0; i < k; i++) {
+    const int tok = prm.draft_tokens[(size_t)b * k + i];
+    if (tok < 0 || tok >= V) {
+      set_status(prm.status, RELUX_ERR_INVALID_ARG);
+      prm.next_token[b] = -1;
+      if (prm.n_accepted) prm.n_accepted[b] = -1;
+      return;
+    }
+    ref_softmax_alloc(prm.draft_logits + ((size_t)b * k + i) * V, V, dp);
+    ref_softmax_alloc(prm.target_logits + ((size_t)b * (k + 1) + i) * V, V, tp);
+    const float dP = dp[tok], tP = tp[tok];
+    float ap = __fdiv_rn(tP, dP > 1e-10f ? dP : 1e-10f);
+    if (ap > 1.0f) ap = 1.0f;
+    if (draws[used++] < ap) continue;
+    // resampleRejected (speculative.go:256-295); the adjusted row overwrites dp
+    float sum = 0.0f;
+    for (int j = 0; j < V; j++) {
+      float diff = __fsub_rn(tp[j], dp[j]);
+      if (diff < 0.0f) diff = 0.0f;
+      dp[j] = diff;
+      sum = __fadd_rn(sum, diff);
+    }
+    const float r = draws[used++];
+    int result = 0;
+    float cum = 0.0f;
+    if (sum > 0.0f) {
+      const float inv = __fdiv_rn(1.0f, sum);
+      for (int j = 0; j < V; j++) {
+        cum = __fadd_rn(cum, __fmul_rn(dp[j], inv));
+        if (r < cum) { result = j; break; }
+      }
+    } else {
+      for (int j = 0; j < V; j++) {
+        cum = __fadd_rn(cum, tp[j]);
+        if (r < cum) { result = j; break; }
+      }
+    }
+    prm.next_token[b] = result;
+    if (prm.n_accepted) prm.n_accepted[b] = i;
+    return;
+  }
+  prm.next_token[b] = ref_sample(prm, prm.target_logits + ((size_t)b * (k + 1) + k) * V, V, draws[used++], dp, tp, idx);
+  if (prm.n_accepted) prm.n_accepted[b] = k;
+}
+
+}  // namespace
+
+int32_t do_spec_accept(Pool* p, const relux_spec_accept_args* a) {
+  if (!a) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
+  const int n = a->n_seqs, k = a->k, V = a->vocab;
+  if (n <= 0 || k < 0 || V <= 0 || !a->target_logits || !a->draws || !a->next_token ||
+      (k > 0 && (!a->draft_tokens || !a->draft_logits || !a->n_accepted)) ||
+      (a->mem != RELUX_MEM_HOST && a->mem != RELUX_MEM_DEVICE) ||
+      (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE)) {
+    set_error("spec_accept: bad arguments");
+    return RELUX_ERR_INVALID_ARG;
+  }
+  if (a->commit && n > p->prm.max_seqs) { set_error("spec_accept: more sequences than the pool holds"); return RELUX_ERR_INVALID_ARG; }
+  if (a->mem == RELUX_MEM_HOST)
+    for (size_t i = 0; i < (size_t)n * k; i++)
+      if (a->draft_tokens[i] < 0 || a->draft_tokens[i] >= V) {
+        set_error("spec_accept: draft token %d outside the vocabulary of %d", a->draft_tokens[i], V);
+        return RELUX_ERR_INVALID_ARG;
+      }
+  Device* dev = p->dev;
+  SelParams prm{};
+  const void* d = nullptr;
+  int32_t rc;
+  if (k > 0) {
+    rc = stage_in(p, p->in_a, a->draft_logits, sizeof(float) * (size_t)n * k * V, a->mem, &d);
+    if (rc) return rc;
+    prm.draft_logits = (const float*)d;
+    rc = stage_in(p, p->q_conv, a->draft_tokens, sizeof(int32_t) * (size_t)n * k, a->mem, &d);
+    if (rc) return rc;
+    prm.draft_tokens = (const int32_t*)d;
+  }
+  rc = stage_in(p, p->in_b, a->target_logits, sizeof(float) * (size_t)n * (k + 1) * V, a->mem, &d);
+  if (rc) return rc;
+  prm.target_logits = (const float*)d;
+  rc = stage_in(p, p->o_lat, a->draws, sizeof(float) * (size_t)n * (k + 1), a->mem, &d);
+  if (rc) return rc;
+  prm.draws = (const float*)d;
+  rc = grow(dev, p->out_buf, sizeof(int32_t) * 2 * (size_t)n);
+  if (rc) return rc;
+  prm.n_accepted = (int32_t*)p->out_buf.p;
+  prm.next_token = prm.n_accepted + n;
+  prm.status = p->d_status;
+  prm.k = k;
+  prm.vocab = V;
+  prm.temperature = a->sampler.temperature;
+  prm.top_k = a->sampler.top_k;
+  prm.top_p = a->sampler.top_p;
+  prm.min_p = a->sampler.min_p;
+  if (a->mode == RELUX_ATTN_REFERENCE) {
+    rc = grow(dev, p->part_o, sizeof(float) * 2 * (size_t)n * V);
+    if (rc) return rc;
+    rc = grow(dev, p->part_ml, sizeof(int32_t) * (size_t)n * V);
+    if (rc) return rc;
+    spec_accept_reference_kernel<<<(n + 31) / 32, 32, 0, dev->stream>>>(prm, n, (float*)p->part_o.p, (int32_t*)p->part_ml.p);
+  } else {
+    // the slices of a cluster's CTAs should stay long enough to keep 512 threads busy
+    int csize = V >= 32768 ? 8 : V >= 8192 ? 4 : V >= 2048 ? 2 : 1;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)(n * csize));
+    cfg.blockDim = dim3(kSelThreads);
+    cfg.stream = dev->stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = (unsigned)csize;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    RELUX_CUDA_TRY(cudaLaunchKernelEx(&cfg, spec_accept_kernel, prm));
+  }
+  RELUX_CUDA_TRY(cudaGetLastError());
+  count_launch(dev);
+  std::vector<int32_t> host((size_t)2 * n);
+  RELUX_CUDA_TRY(cudaMemcpyAsync(host.data(), p->out_buf.p, sizeof(int32_t) * 2 * (size_t)n, cudaMemcpyDeviceToHost, dev->stream));
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  for (int i = 0; i < n; i++) {
+    if (a->n_accepted) a->n_accepted[i] = host[i];
+    a->next_token[i] = host[(size_t)n + i];
+    if (host[(size_t)n + i] < 0 || (k > 0 && host[i] < 0)) {
+      set_error("spec_accept: a draft token of sequence %d lies outside the vocabulary of %d", i, V);
+      return RELUX_ERR_INVALID_ARG;
+    }
+  }
+  if (a->commit) {
+    std::vector<int32_t> new_len((size_t)n);
+    for (int l = 0; l < p->prm.num_layers; l++) {
+      for (int i = 0; i < n; i++) {
+        const int s = a->seq_ids ? a->seq_ids[i] : i;
+        if (s < 0 || s >= p->prm.max_seqs) { set_error("spec_accept: bad sequence id %d", s); return RELUX_ERR_INVALID_ARG; }
+        new_len[i] = p->h_len[(size_t)l * p->prm.max_seqs + s] + (k > 0 ? host[i] : 0) + 1;
+      }
+      rc = seq_set_len(p, l, n, a->seq_ids, new_len.data());
+      if (rc) return rc;
+    }
+  }
+  return RELUX_OK;
+}
+
+}  // namespace relux

@@ -204,3 +204,58 @@ def test_softmax_rows_sums_to_one_and_cuts_off(oracle):
     assert abs(p.sum() - 1.0) < 1e-6
     assert p[0, 2] == 0.0
     assert p[0, 0] > p[0, 1] > p[0, 3] > 0
+
+
+# ---- Sampler.Sample (sampler.go:73-218): the two property tests of sampler_test.go, over many draws ----
+def test_sampler_temperature_zero_is_argmax(oracle):  # sampler_test.go:28-40
+    cfg = oracle.sampler_cfg(temperature=1e-10)
+    for r in np.linspace(0.0, 0.9999, 100):
+        assert oracle.sampler_sample(cfg, [1, 5, 3], float(r)) == 1
+
+
+def test_sampler_top_k_two(oracle):  # sampler_test.go:42-56
+    cfg = oracle.sampler_cfg(top_k=2)
+    got = {oracle.sampler_sample(cfg, [1, 5, 3, 2, 4], float(r)) for r in np.linspace(0.0, 0.9999, 100)}
+    assert got == {1, 4}
+
+
+def test_sampler_filters_compose(oracle):
+    """penalties -> temperature -> top-k -> softmax -> top-p -> min-p -> draw (sampler.go:31-33): each filter only ever
+    removes tokens, the result sums to one, and the repetition penalty lowers a seen token's probability."""
+    rng = np.random.default_rng(4)
+    logits = (rng.standard_normal(500) * 2).astype(np.float32)
+    _, base = oracle.sampler_sample(oracle.sampler_cfg(), logits, 0.5, return_probs=True)
+    for kw in (dict(top_k=20), dict(top_p=0.8), dict(min_p=0.1), dict(top_k=50, top_p=0.9, min_p=0.05, temperature=0.7)):
+        _, p = oracle.sampler_sample(oracle.sampler_cfg(**kw), logits, 0.5, return_probs=True)
+        assert abs(float(p.sum()) - 1.0) < 1e-4
+        assert np.all((p > 0) <= (base > 0)) and (p > 0).sum() < (base > 0).sum()
+    _, p20 = oracle.sampler_sample(oracle.sampler_cfg(top_k=20), logits, 0.5, return_probs=True)
+    assert (p20 > 0).sum() == 20 and set(np.argsort(-logits)[:20]) == set(np.nonzero(p20)[0])
+    tok = int(np.argmax(logits))
+    _, pen = oracle.sampler_sample(oracle.sampler_cfg(repeat_penalty=1.5, presence_penalty=0.5), logits, 0.5, prev=[tok, tok],
+                                   return_probs=True)
+    assert pen[tok] < base[tok]
+
+
+# ---- acceptPhase / resampleRejected (speculative.go:211-295): no reference test; properties of the algorithm ----
+def test_spec_accept_properties(oracle):
+    rng = np.random.default_rng(8)
+    k, V = 4, 300
+    dl = (rng.standard_normal((k, V)) * 2).astype(np.float32)
+    last = (rng.standard_normal((1, V)) * 2).astype(np.float32)
+    toks = rng.integers(0, V, k)
+    cfg = oracle.sampler_cfg(temperature=1e-10)
+    # a draft equal to the target is accepted whole (acceptProb = 1 > every draw) and uses k + 1 draws
+    n, nxt, used, ap = oracle.spec_accept(cfg, toks, dl, np.vstack([dl, last]), rng.random(k + 1))
+    assert (n, used) == (k, k + 1) and nxt == int(np.argmax(last)) and np.all(ap == 1.0)
+    # a target without mass on the second draft token rejects there; the resampled token never is that token
+    tl = np.vstack([dl, last])
+    tl[1, toks[1]] = -90.0
+    n, nxt, used, ap = oracle.spec_accept(cfg, toks, dl, tl, np.asarray([0.0, 0.5, 0.5, 0.5, 0.5], np.float32))
+    assert (n, used) == (1, 3) and ap[1] == 0.0 and nxt != toks[1]
+    # acceptProb is min(1, p_target / p_draft) of the drafted token
+    tl = np.vstack([dl + (rng.standard_normal((k, V)) * 0.5).astype(np.float32), last])
+    _, _, _, ap = oracle.spec_accept(cfg, toks, dl, tl, np.zeros(k + 1, np.float32))
+    for i in range(k):
+        want = min(1.0, float(oracle.softmax_alloc(tl[i])[toks[i]]) / float(oracle.softmax_alloc(dl[i])[toks[i]]))
+        assert abs(float(ap[i]) - want) < 1e-6
