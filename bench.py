@@ -44,6 +44,9 @@ WORKLOADS = {
     "gqa_verify_b128_ctx8k": dict(kind="gqa", B=128, ctx=8192, H=32, Hkv=8, D=128, S=4),
     "gqa_verify_b16_ctx8k": dict(kind="gqa", B=16, ctx=8192, H=32, Hkv=8, D=128, S=4),
     # the whole GQA layer step of a verify: x [B, 4, 4096] -> projections + RoPE + draft rows + attention + Wo
+    # token selection after a verify pass (acceptPhase + resampleRejected + Sampler.Sample) for 64 sequences, four draft
+    # tokens, a vocabulary of 131072: 302 MB of float32 logits per step
+    "spec_accept_b64_k4_v128k": dict(kind="accept", B=64, k=4, V=131072),
     "gqa_layer_verify_b128_ctx8k": dict(kind="gqa", B=128, ctx=8192, H=32, Hkv=8, D=128, S=4, layer=True),
 }
 # dram__bytes_read + dram__bytes_write of the dominant kernel divided by its algorithmic bytes, from the ncu captures
@@ -502,6 +505,131 @@ def run_gqa(args, w, world, rank, local, dist):
 _CPU_INPUTS = {}   # inputs of the CPU legs, kept between steps of the reference arm
 
 
+def accept_inputs(w, seed):
+    """Seeded logits with the shape of a verify pass: draft rows N(0, 2.5), target rows = draft + N(0, 0.6) noise, the
+    drafted token is the draft row's argmax."""
+    B, k, V = w["B"], w["k"], w["V"]
+    rng = np.random.default_rng(seed)
+    dl = rng.standard_normal((B, k, V), dtype=np.float32) * np.float32(2.5)
+    tl = np.empty((B, k + 1, V), np.float32)
+    tl[:, :k] = dl + rng.standard_normal((B, k, V), dtype=np.float32) * np.float32(0.6)
+    tl[:, k] = rng.standard_normal((B, V), dtype=np.float32) * np.float32(2.5)
+    toks = dl.argmax(axis=2).astype(np.int32)
+    return toks, dl, tl, rng
+
+
+def run_accept(args, w, world, rank, local, dist):
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+
+    B, k, V = w["B"], w["k"], w["V"]
+    dev = rb.Device(local)
+    pool = rb.Pool(dev, L.POOL_MLA, 1, 2, PAGE, 1, 2, dC=64, dHR=16)   # the call needs a pool for its stream and scratch
+    toks, dl, tl, rng = accept_inputs(w, 7 + rank)
+    n_draws = 32
+    draws = [rng.random((B, k + 1), dtype=np.float32) for _ in range(n_draws)]
+    d_toks, d_dl, d_tl = dev.upload(toks), dev.upload(dl), dev.upload(tl)
+    d_draws = [dev.upload(d) for d in draws]
+    pins = [dev.pinned(a.shape, a.dtype) for a in (toks, dl, tl)]
+    for pin, a in zip(pins, (toks, dl, tl)):
+        pin.array[...] = a
+    sampler_kw = dict(temperature=0.8, top_k=50, top_p=0.95)
+    step_no = [0]
+    accepted_total = [0]
+    rows_needed = []
+
+    def account(n_acc):
+        accepted_total[0] += int(n_acc.sum()) + B          # accepted draft tokens plus the resampled / bonus token
+        rows_needed.append(float(np.where(n_acc < k, 2 * (n_acc + 1), 2 * k + 1).sum()))
+
+    def step_resident():
+        i = step_no[0] % n_draws
+        step_no[0] += 1
+        n_acc, _ = pool.spec_accept(B, k, V, d_toks, d_dl, d_tl, d_draws[i], **sampler_kw)
+        account(n_acc)
+
+    def step_e2e():
+        i = step_no[0] % n_draws
+        step_no[0] += 1
+        n_acc, _ = pool.spec_accept(B, k, V, pins[0].array, pins[1].array, pins[2].array, draws[i], **sampler_kw)
+        account(n_acc)
+
+    e0, e1 = dev.event(), dev.event()
+
+    def timed(fn, steps, warmup, sampler=None):
+        for _ in range(warmup):
+            fn()
+        dev.sync()
+        barrier(dist)
+        n0 = dev.launch_count()
+        accepted_total[0] = 0
+        del rows_needed[:]
+        if sampler is not None:
+            sampler.begin()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        dev.sync()
+        ms = e0.elapsed_ms(e1)
+        barrier(dist)
+        return max_over_ranks(dist, ms), dev.launch_count() - n0, accepted_total[0]
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    ms_res, launches, acc_res = timed(step_resident, args.steps, args.warmup, sampler if rank == 0 else None)
+    clocks = sampler.finish() if rank == 0 else None
+    kernel_ms, counted = pool.mean_kernel_ms(args.steps)
+    # algorithmic bytes: the logit rows the reference's loop touches (two per examined draft token, the last row when all
+    # pass), each read once, float32
+    alg_bytes = float(np.mean(rows_needed[-counted:])) * V * 4
+    e2e_steps = max(3, min(args.steps, 50))
+    ms_e2e, _, acc_e2e = timed(step_e2e, e2e_steps, 3)
+    assert pool.status() == 0, "device status word is set"
+    peak, peak_src = read_peaks()
+    achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+    line = {
+        "metric": "spec_accept_tokens_per_s", "value": acc_res * world / (ms_res * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, "batch_per_gpu": B, "draft_tokens": k, "vocab": V, "sampler": sampler_kw,
+                   "l2": "inputs (%.2f GB of logits per GPU) are larger than L2" % ((dl.nbytes + tl.nbytes) / 1e9)},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "peak_source": peak_src, "kernel": "spec_accept_kernel", "kernel_ms": kernel_ms, "launches_timed": counted,
+                     "algorithmic_bytes_per_launch": alg_bytes},
+        "e2e": {"value": acc_e2e * world / (ms_e2e * 1e-3), "unit": "tokens/s", "steps": e2e_steps,
+                "h2d_bytes_per_step": int(toks.nbytes + dl.nbytes + tl.nbytes + draws[0].nbytes), "d2h_bytes_per_step": 8 * B},
+        "gpu_launches": launches, "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_accept(w)
+    pool.destroy()
+    dev.close()
+    return line
+
+
+def cpu_baseline_accept(w, seqs=16, seconds=10.0):
+    """The CPU restatement on `seqs` sequences of the same workload, one core, repeated with fresh draws for `seconds`."""
+    from oracle import binding as ob
+    key = ("accept", seqs)
+    if key not in _CPU_INPUTS:
+        _CPU_INPUTS[key] = accept_inputs(dict(w, B=seqs), 7)
+    toks, dl, tl, rng = _CPU_INPUTS[key]
+    cfg = ob.sampler_cfg(temperature=0.8, top_k=50, top_p=0.95)
+    t0 = time.perf_counter()
+    tokens = passes = 0
+    while passes == 0 or time.perf_counter() - t0 < seconds:
+        draws = rng.random((seqs, w["k"] + 1), dtype=np.float32)
+        for b in range(seqs):
+            tokens += ob.spec_accept(cfg, toks[b], dl[b], tl[b], draws[b])[0] + 1
+        passes += 1
+    dt = time.perf_counter() - t0
+    return {"value": tokens / dt, "unit": "tokens/s", "cores": 1, "kind": "port",
+            "sample": "%d of the %d sequences, %d passes with fresh draws, %.1f s" % (seqs, w["B"], passes, dt)}
+
+
 def cpu_baseline_mla(w, sample_T, threads, seqs=None):
     """Times the oracle's restatement of the reference's own path (decompress every latent, then attend;
     mla.go:323-377) on `threads` host threads, one sequence per thread, at a reduced context, and scales the time
@@ -572,6 +700,17 @@ def run_reference(args, w, world, rank):
     from oracle import binding as orc
     if rank != 0:
         return None
+    if w["kind"] == "accept":
+        # the reference's accept loop is scalar Go: one core, sixteen sequences of the workload per pass
+        vals = [cpu_baseline_accept(w, seconds=min(2.0, 100.0 / max(1, args.warmup + args.steps))) for _ in range(args.warmup + args.steps)][args.warmup:]
+        v = float(np.mean([x["value"] for x in vals]))
+        cb = dict(vals[-1], value=v)
+        return {"impl": "reference", "metric": "spec_accept_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": w["B"] * world * (w["k"] + 2) / 2.0 / v * 1e3,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": args.workload, "batch_per_gpu": w["B"], "draft_tokens": w["k"], "vocab": w["V"]},
+                "cpu_baseline": cb, "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
     # every host core this process may run on (a launcher's OMP_NUM_THREADS=1 default is not a property of the box)
     threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or orc.num_threads())
     cpu_baseline(w, threads, sample_T=16)            # builds the inputs, warms the threads
@@ -620,7 +759,8 @@ def main():
             print(json.dumps(line))
         return
     world, rank, local, dist = dist_setup(args.gpus)
-    line = run_mla(args, w, world, rank, local, dist) if w["kind"] == "mla" else run_gqa(args, w, world, rank, local, dist)
+    runner = {"mla": run_mla, "gqa": run_gqa, "accept": run_accept}[w["kind"]]
+    line = runner(args, w, world, rank, local, dist)
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:

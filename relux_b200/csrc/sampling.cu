@@ -13,6 +13,7 @@
 #include <cuda_runtime.h>
 #include <cooperative_groups.h>
 #include <cstdint>
+#include <cstdlib>
 #include <vector>
 
 #include "common.cuh"
@@ -51,7 +52,7 @@ struct SelShared {
   float hist_sum[256];
   uint32_t hist_cnt[256];
   float warp_seg[kSelWarps];  // per-warp segment sums of the search pass
-  int32_t found;
+  uint32_t warp_hist[kSelWarps][256];   // radix selection: one histogram per warp (counts, or float sums)
 };
 
 __device__ __forceinline__ uint32_t order_key(float x) {
@@ -80,6 +81,7 @@ struct Ctx {
   int lo, hi;          // this CTA's slice of the vocabulary
   int wlo, whi;        // this warp's contiguous segment of the slice
   int warp, lane;
+  bool vec;            // rows can be read as aligned float4s
   uint32_t round;      // reduction counter (selects the exchange buffer)
 };
 
@@ -125,16 +127,74 @@ __device__ void cluster_gather1(Ctx& c, float mine, float (&all)[kMaxCluster]) {
   c.round++;
 }
 
-// Calls f(index, value) for every element of this warp's segment of `row`, lanes interleaved (coalesced), four loads
-// in flight per lane.
+// Calls f(index, value) for every element of this warp's segment of `row`.  Segments start on multiples of 128
+// elements, so when the vocabulary is a multiple of four and the rows are 16-byte aligned (c.vec) every lane reads
+// float4s, four in flight; otherwise lanes interleave single floats.
 template <class F>
 __device__ __forceinline__ void for_segment(const Ctx& c, const float* __restrict__ row, F f) {
+  if (c.vec) {
+    int i = c.wlo + c.lane * 4;
+    for (; i + 896 < c.whi; i += 1024) {   // eight float4 loads in flight per lane
+      float4 t[8];
+#pragma unroll
+      for (int q = 0; q < 8; q++) t[q] = __ldg(reinterpret_cast<const float4*>(row + i + 128 * q));
+#pragma unroll
+      for (int q = 0; q < 8; q++) { f(i + 128 * q, t[q].x); f(i + 128 * q + 1, t[q].y); f(i + 128 * q + 2, t[q].z); f(i + 128 * q + 3, t[q].w); }
+    }
+    for (; i + 384 < c.whi; i += 512) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(row + i));
+      const float4 b = __ldg(reinterpret_cast<const float4*>(row + i + 128));
+      const float4 d = __ldg(reinterpret_cast<const float4*>(row + i + 256));
+      const float4 e = __ldg(reinterpret_cast<const float4*>(row + i + 384));
+      f(i, a.x); f(i + 1, a.y); f(i + 2, a.z); f(i + 3, a.w);
+      f(i + 128, b.x); f(i + 129, b.y); f(i + 130, b.z); f(i + 131, b.w);
+      f(i + 256, d.x); f(i + 257, d.y); f(i + 258, d.z); f(i + 259, d.w);
+      f(i + 384, e.x); f(i + 385, e.y); f(i + 386, e.z); f(i + 387, e.w);
+    }
+    for (; i < c.whi; i += 128) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(row + i));
+      f(i, a.x); f(i + 1, a.y); f(i + 2, a.z); f(i + 3, a.w);
+    }
+    return;
+  }
   int i = c.wlo + c.lane;
   for (; i + 96 < c.whi; i += 128) {
     float a = __ldg(row + i), b = __ldg(row + i + 32), d = __ldg(row + i + 64), e = __ldg(row + i + 96);
     f(i, a); f(i + 32, b); f(i + 64, d); f(i + 96, e);
   }
   for (; i < c.whi; i += 32) f(i, __ldg(row + i));
+}
+
+// The same over two rows at once: f(index, value_a, value_b).
+template <class F>
+__device__ __forceinline__ void for_segment2(const Ctx& c, const float* __restrict__ ra, const float* __restrict__ rb, F f) {
+  if (c.vec) {
+    int i = c.wlo + c.lane * 4;
+    for (; i + 384 < c.whi; i += 512) {   // four float4 loads per row in flight per lane
+      float4 ta[4], tb[4];
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        ta[q] = __ldg(reinterpret_cast<const float4*>(ra + i + 128 * q));
+        tb[q] = __ldg(reinterpret_cast<const float4*>(rb + i + 128 * q));
+      }
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        f(i + 128 * q, ta[q].x, tb[q].x); f(i + 128 * q + 1, ta[q].y, tb[q].y);
+        f(i + 128 * q + 2, ta[q].z, tb[q].z); f(i + 128 * q + 3, ta[q].w, tb[q].w);
+      }
+    }
+    for (; i < c.whi; i += 128) {
+      const float4 a0 = __ldg(reinterpret_cast<const float4*>(ra + i)), b0 = __ldg(reinterpret_cast<const float4*>(rb + i));
+      f(i, a0.x, b0.x); f(i + 1, a0.y, b0.y); f(i + 2, a0.z, b0.z); f(i + 3, a0.w, b0.w);
+    }
+    return;
+  }
+  int i = c.wlo + c.lane;
+  for (; i + 32 < c.whi; i += 64) {
+    float a0 = __ldg(ra + i), b0 = __ldg(rb + i), a1 = __ldg(ra + i + 32), b1 = __ldg(rb + i + 32);
+    f(i, a0, b0); f(i + 32, a1, b1);
+  }
+  for (; i < c.whi; i += 32) f(i, __ldg(ra + i), __ldg(rb + i));
 }
 
 // Radix selection, eight bits a round, over keys that order like the values.  kWeighted = false: the key of the
@@ -152,18 +212,46 @@ __device__ bool radix_select(Ctx& c, const float* __restrict__ row, KeyF key_wei
   __shared__ uint32_t pick[2];
   __shared__ float pick_above;
   for (int shift = 24; shift >= 0; shift -= 8) {
-    if (threadIdx.x < 256) { c.sh->hist_cnt[threadIdx.x] = 0; c.sh->hist_sum[threadIdx.x] = 0.0f; }
+    // every warp fills a histogram of its own (no contention between warps); they are added up afterwards
+    for (int t = threadIdx.x; t < kSelWarps * 256; t += kSelThreads) (&c.sh->warp_hist[0][0])[t] = 0u;
     __syncthreads();
-    for_segment(c, row, [&](int, float v) {
-      uint32_t key; float w;
-      key_weight(v, key, w);
-      if ((key & mask) == prefix) {
-        uint32_t d = (key >> shift) & 255u;
-        if (kWeighted) atomicAdd(&c.sh->hist_sum[d], w);
-        else atomicAdd(&c.sh->hist_cnt[d], 1u);
+    uint32_t* my_cnt = c.sh->warp_hist[c.warp];
+    float* my_sum = reinterpret_cast<float*>(c.sh->warp_hist[c.warp]);
+    // Most keys share their leading bits (the exponent of neighbouring logits or probabilities), so plain atomics
+    // would pile onto two or three bins.  Every lane therefore keeps the bin it hit last in a register and only
+    // touches shared memory when the bin changes.
+    {
+      uint32_t cur = 0xffffffffu, cur_n = 0;
+      float cur_w = 0.0f;
+      for_segment(c, row, [&](int, float v) {
+        uint32_t key; float w;
+        key_weight(v, key, w);
+        if ((key & mask) != prefix) return;
+        const uint32_t d = (key >> shift) & 255u;
+        if (d != cur) {
+          if (cur != 0xffffffffu) {
+            if (kWeighted) atomicAdd(&my_sum[cur], cur_w);
+            else atomicAdd(&my_cnt[cur], cur_n);
+          }
+          cur = d; cur_n = 0; cur_w = 0.0f;
+        }
+        cur_n++;
+        cur_w += w;
+      });
+      if (cur != 0xffffffffu) {
+        if (kWeighted) atomicAdd(&my_sum[cur], cur_w);
+        else atomicAdd(&my_cnt[cur], cur_n);
       }
-    });
+    }
     __syncthreads();
+    if (threadIdx.x < 256) {
+      uint32_t n = 0; float sacc = 0.0f;
+      for (int wq = 0; wq < kSelWarps; wq++) {
+        if (kWeighted) sacc += reinterpret_cast<const float*>(c.sh->warp_hist[wq])[threadIdx.x];
+        else n += c.sh->warp_hist[wq][threadIdx.x];
+      }
+      c.sh->hist_cnt[threadIdx.x] = n; c.sh->hist_sum[threadIdx.x] = sacc;
+    }
     cl.sync();
     if (threadIdx.x < 256) {
       uint32_t n = 0; float s = 0.0f;
@@ -174,22 +262,50 @@ __device__ bool radix_select(Ctx& c, const float* __restrict__ row, KeyF key_wei
       comb_cnt[threadIdx.x] = n; comb_sum[threadIdx.x] = s;
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      pick[0] = 256;
+    // Walk the bins from the top until the running count (or sum) reaches the target: warp 0, eight bins a lane.
+    if (threadIdx.x == 0) { pick[0] = 256; pick_above = above; }
+    __syncthreads();
+    if (c.warp == 0) {
+      const int b_hi = 8 * c.lane + 7;
       if (kWeighted) {
-        float acc = above;
-        for (int b = 255; b >= 0; b--) {
-          float nxt = acc + comb_sum[b];
-          if (nxt >= want_sum) { pick[0] = b; break; }
+        float mine = 0.0f;
+        for (int q = 0; q < 8; q++) mine += comb_sum[b_hi - q];
+        float upper = mine;      // inclusive sum over this lane and the lanes above it
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          float y = __shfl_down_sync(0xffffffffu, upper, o);
+          if (c.lane + o < 32) upper += y;
+        }
+        const float higher = __shfl_down_sync(0xffffffffu, upper, 1);   // sum over the lanes above this one
+        float acc = above + (c.lane < 31 ? higher : 0.0f);
+        int hit = -1;
+        float acc_hit = acc;
+        for (int q = 0; q < 8 && hit < 0; q++) {
+          float nxt = acc + comb_sum[b_hi - q];
+          if (nxt >= want_sum) { hit = b_hi - q; acc_hit = acc; }
           acc = nxt;
         }
-        pick_above = acc;
+        const uint32_t any = __ballot_sync(0xffffffffu, hit >= 0);
+        if (any && c.lane == 31 - __clz(any)) { pick[0] = (uint32_t)hit; pick_above = acc_hit; }
+        if (!any && c.lane == 0) pick_above = acc;   // the whole row stays below the target
       } else {
-        uint32_t acc = 0;
-        for (int b = 255; b >= 0; b--) {
-          if (acc + comb_cnt[b] >= want) { pick[0] = b; pick[1] = want - acc; break; }
-          acc += comb_cnt[b];
+        uint32_t mine = 0;
+        for (int q = 0; q < 8; q++) mine += comb_cnt[b_hi - q];
+        uint32_t upper = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          uint32_t y = __shfl_down_sync(0xffffffffu, upper, o);
+          if (c.lane + o < 32) upper += y;
         }
+        uint32_t acc = upper - mine;
+        int hit = -1;
+        uint32_t acc_hit = 0;
+        for (int q = 0; q < 8 && hit < 0; q++) {
+          if (acc + comb_cnt[b_hi - q] >= want) { hit = b_hi - q; acc_hit = acc; }
+          acc += comb_cnt[b_hi - q];
+        }
+        const uint32_t any = __ballot_sync(0xffffffffu, hit >= 0);
+        if (any && c.lane == 31 - __clz(any)) { pick[0] = (uint32_t)hit; pick[1] = want - acc_hit; }
       }
     }
     __syncthreads();
@@ -241,25 +357,49 @@ __device__ void cdf_find(Ctx& c, const float* __restrict__ row, ProbF prob, floa
       acc = nxt;
     }
     if (c.warp == wsel) {
-      int last_pos = -1, hit_idx = -1;
-      acc = wbase;
-      for (int j = c.wlo; j < c.whi && hit_idx < 0; j += 32) {
-        const int i = j + c.lane;
-        float p = i < c.whi ? prob(i, __ldg(row + i)) : 0.0f;
-        float x = p;
+      // Two levels, so that the walk costs two memory latencies instead of one per 32 elements: every lane sums a
+      // contiguous chunk of the segment, a scan over the lanes finds the chunk that crosses, and that chunk alone is
+      // walked in index order.
+      const int seglen = c.whi - c.wlo;
+      const int chunk = (((seglen + 31) >> 5) + 3) & ~3;
+      const int l0 = min(c.whi, c.wlo + c.lane * chunk), l1 = min(c.whi, l0 + chunk);
+      float mine = 0.0f;
+#pragma unroll 4
+      for (int i = l0; i < l1; i++) mine += prob(i, __ldg(row + i));
+      float x = mine;
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-          float y = __shfl_up_sync(0xffffffffu, x, o);
-          if (c.lane >= o) x += y;
-        }
-        const uint32_t hit = __ballot_sync(0xffffffffu, i < c.whi && acc + x > r);
-        if (hit) hit_idx = j + __ffs(hit) - 1;
-        const uint32_t pos = __ballot_sync(0xffffffffu, p > 0.0f);
-        if (pos) last_pos = j + 31 - __clz(pos);
-        acc += __shfl_sync(0xffffffffu, x, 31);
+      for (int o = 1; o < 32; o <<= 1) {
+        float y = __shfl_up_sync(0xffffffffu, x, o);
+        if (c.lane >= o) x += y;
       }
-      // when rounding put the crossing past the end of the segment: the last element that carries probability
-      if (hit_idx < 0) hit_idx = last_pos >= 0 ? last_pos : (c.whi > c.wlo ? c.whi - 1 : dflt);
+      const uint32_t over = __ballot_sync(0xffffffffu, wbase + x > r);
+      const uint32_t carry = __ballot_sync(0xffffffffu, mine > 0.0f);
+      int hit_idx = -1;
+      if (over || carry) {
+        const int lsel = over ? __ffs(over) - 1 : 31 - __clz(carry);
+        const float before = __shfl_up_sync(0xffffffffu, x, 1);
+        float acc2 = wbase + __shfl_sync(0xffffffffu, c.lane > 0 ? before : 0.0f, lsel);
+        const int c0 = __shfl_sync(0xffffffffu, l0, lsel), c1 = __shfl_sync(0xffffffffu, l1, lsel);
+        int last_pos = -1;
+        for (int j = c0; j < c1 && hit_idx < 0; j += 32) {
+          const int i = j + c.lane;
+          const float pv = i < c1 ? prob(i, __ldg(row + i)) : 0.0f;
+          float z = pv;
+#pragma unroll
+          for (int o = 1; o < 32; o <<= 1) {
+            float y = __shfl_up_sync(0xffffffffu, z, o);
+            if (c.lane >= o) z += y;
+          }
+          const uint32_t hit = __ballot_sync(0xffffffffu, i < c1 && acc2 + z > r);
+          if (hit) hit_idx = j + __ffs(hit) - 1;
+          const uint32_t pos = __ballot_sync(0xffffffffu, pv > 0.0f);
+          if (pos) last_pos = j + 31 - __clz(pos);
+          acc2 += __shfl_sync(0xffffffffu, z, 31);
+        }
+        // when rounding put the crossing past the end of the chunk: its last element that carries probability
+        if (hit_idx < 0) hit_idx = last_pos;
+      }
+      if (hit_idx < 0) hit_idx = c.whi > c.wlo ? c.whi - 1 : dflt;
       if (c.lane == 0) *out = hit_idx;
     }
   }
@@ -320,7 +460,7 @@ __device__ void sample_row(Ctx& c, const SelParams& prm, const float* __restrict
   cdf_find(c, row, p3, r, V - 1, out);
 }
 
-__global__ void __launch_bounds__(kSelThreads) spec_accept_kernel(SelParams prm) {
+__global__ void __launch_bounds__(kSelThreads, 2) spec_accept_kernel(SelParams prm) {
   cg::cluster_group cl = cg::this_cluster();
   __shared__ SelShared sh;
   Ctx c;
@@ -331,10 +471,11 @@ __global__ void __launch_bounds__(kSelThreads) spec_accept_kernel(SelParams prm)
   c.lane = threadIdx.x & 31;
   c.round = 0;
   const int V = prm.vocab, k = prm.k;
-  const int per = (V + c.csize - 1) / c.csize;
+  const int per = ((V + c.csize - 1) / c.csize + 127) & ~127;
   c.lo = min(V, c.rank * per);
   c.hi = min(V, c.lo + per);
-  const int wper = (c.hi - c.lo + kSelWarps - 1) / kSelWarps;
+  const int wper = ((c.hi - c.lo + kSelWarps - 1) / kSelWarps + 127) & ~127;
+  c.vec = (V & 3) == 0 && (((uintptr_t)prm.target_logits | (uintptr_t)prm.draft_logits) & 15) == 0;
   c.wlo = min(c.hi, c.lo + c.warp * wper);
   c.whi = min(c.hi, c.wlo + wper);
   const int b = blockIdx.x / c.csize;
@@ -355,17 +496,14 @@ __global__ void __launch_bounds__(kSelThreads) spec_accept_kernel(SelParams prm)
       break;
     }
     float v4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-    {
-      int j = c.wlo + c.lane;
-      for (; j < c.whi; j += 32) { v4[0] = fmaxf(v4[0], __ldg(drow + j)); v4[1] = fmaxf(v4[1], __ldg(trow + j)); }
-    }
+    for_segment2(c, drow, trow, [&](int, float dv, float tv) { v4[0] = fmaxf(v4[0], dv); v4[1] = fmaxf(v4[1], tv); });
     cluster_reduce4<true>(c, v4);
     const float md = v4[0], mt = v4[1];
     v4[0] = v4[1] = v4[2] = v4[3] = 0.0f;
-    for (int j = c.wlo + c.lane; j < c.whi; j += 32) {
-      v4[0] += fastexp32_ref(__fsub_rn(__ldg(drow + j), md));
-      v4[1] += fastexp32_ref(__fsub_rn(__ldg(trow + j), mt));
-    }
+    for_segment2(c, drow, trow, [&](int, float dv, float tv) {
+      v4[0] += fastexp32_ref(__fsub_rn(dv, md));
+      v4[1] += fastexp32_ref(__fsub_rn(tv, mt));
+    });
     cluster_reduce4<false>(c, v4);
     const float invd = v4[0] > 0.0f ? __fdiv_rn(1.0f, v4[0]) : 1.0f;
     const float invt = v4[1] > 0.0f ? __fdiv_rn(1.0f, v4[1]) : 1.0f;
@@ -383,7 +521,10 @@ __global__ void __launch_bounds__(kSelThreads) spec_accept_kernel(SelParams prm)
       return diff < 0.0f ? 0.0f : diff;
     };
     v4[0] = v4[1] = v4[2] = v4[3] = 0.0f;
-    for_segment(c, trow, [&](int j, float tv) { v4[0] += adj(j, tv); });
+    for_segment2(c, drow, trow, [&](int, float dv, float tv) {
+      float diff = __fsub_rn(__fmul_rn(fastexp32_ref(__fsub_rn(tv, mt)), invt), __fmul_rn(fastexp32_ref(__fsub_rn(dv, md)), invd));
+      v4[0] += diff < 0.0f ? 0.0f : diff;
+    });
     cluster_reduce4<false>(c, v4);
     const float r = draws[used++];
     if (v4[0] > 0.0f) {
@@ -609,10 +750,43 @@ int32_t do_spec_accept(Pool* p, const relux_spec_accept_args* a) {
     if (rc) return rc;
     rc = grow(dev, p->part_ml, sizeof(int32_t) * (size_t)n * V);
     if (rc) return rc;
+  }
+  // device time of the selection kernel, readable through relux_pool_kernel_ms_mean like the attention kernels'
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), dev->stream));
+  if (a->mode == RELUX_ATTN_REFERENCE) {
     spec_accept_reference_kernel<<<(n + 31) / 32, 32, 0, dev->stream>>>(prm, n, (float*)p->part_o.p, (int32_t*)p->part_ml.p);
   } else {
-    // the slices of a cluster's CTAs should stay long enough to keep 512 threads busy
-    int csize = V >= 32768 ? 8 : V >= 8192 ? 4 : V >= 2048 ? 2 : 1;
+    // Cluster size: slices should stay long enough to keep 512 threads busy, and all sequences should be resident at
+    // once -- a second wave of clusters doubles the latency of the whole chain, which costs more than longer slices.
+    const int by_vocab = V >= 32768 ? 8 : V >= 8192 ? 4 : V >= 2048 ? 2 : 1;
+    static int resident[64][4] = {};   // [device][log2 cluster size]: clusters the device holds at once, 0 = not asked yet
+    int csize = 1;
+    double best = 1e30;
+    for (int lg = 3; lg >= 0; lg--) {
+      const int cs = 1 << lg;
+      if (cs > by_vocab) continue;
+      int& have = resident[dev->index & 63][lg];
+      if (have == 0) {
+        cudaLaunchConfig_t q{};
+        q.gridDim = dim3((unsigned)(cs * 64));
+        q.blockDim = dim3(kSelThreads);
+        cudaLaunchAttribute qa{};
+        qa.id = cudaLaunchAttributeClusterDimension;
+        qa.val.clusterDim.x = (unsigned)cs;
+        qa.val.clusterDim.y = qa.val.clusterDim.z = 1;
+        q.attrs = &qa;
+        q.numAttrs = 1;
+        int nc = 0;
+        if (cudaOccupancyMaxActiveClusters(&nc, spec_accept_kernel, &q) != cudaSuccess || nc <= 0) { cudaGetLastError(); nc = 1; }
+        have = nc;
+      }
+      const double cost = (double)((n + have - 1) / have) / cs;   // waves x slice length
+      if (cost <= best) { best = cost; csize = cs; }   // on a tie the smaller cluster: fewer waves, fewer remote reads
+    }
+    if (const char* e = getenv("RELUX_SEL_CLUSTER")) {   // tuning override: 1, 2, 4 or 8
+      const int v = atoi(e);
+      if (v == 1 || v == 2 || v == 4 || v == 8) csize = v;
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3((unsigned)(n * csize));
     cfg.blockDim = dim3(kSelThreads);
@@ -627,6 +801,8 @@ int32_t do_spec_accept(Pool* p, const relux_spec_accept_args* a) {
     RELUX_CUDA_TRY(cudaLaunchKernelEx(&cfg, spec_accept_kernel, prm));
   }
   RELUX_CUDA_TRY(cudaGetLastError());
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), dev->stream));
+  p->timed_calls++;
   count_launch(dev);
   std::vector<int32_t> host((size_t)2 * n);
   RELUX_CUDA_TRY(cudaMemcpyAsync(host.data(), p->out_buf.p, sizeof(int32_t) * 2 * (size_t)n, cudaMemcpyDeviceToHost, dev->stream));
