@@ -47,11 +47,13 @@ WORKLOADS = {
     # token selection after a verify pass (acceptPhase + resampleRejected + Sampler.Sample) for 64 sequences, four draft
     # tokens, a vocabulary of 131072: 302 MB of float32 logits per step
     "spec_accept_b64_k4_v128k": dict(kind="accept", B=64, k=4, V=131072),
+    # smaller case for profiler captures (151 MB of logits, still larger than L2)
+    "spec_accept_b32_k4_v128k": dict(kind="accept", B=32, k=4, V=131072),
     "gqa_layer_verify_b128_ctx8k": dict(kind="gqa", B=128, ctx=8192, H=32, Hkv=8, D=128, S=4, layer=True),
 }
 # dram__bytes_read + dram__bytes_write of the dominant kernel divided by its algorithmic bytes, from the ncu captures
 # summarised under profiles/ (small case, traffic grows in proportion to the cached tokens read).
-TRAFFIC_RATIO = {"mla": 1.04, "gqa": 1.015}
+TRAFFIC_RATIO = {"mla": 1.04, "gqa": 1.015, "accept": 1.08}
 PAGE = 64
 
 
@@ -596,7 +598,8 @@ def run_accept(args, w, world, rank, local, dist):
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "batch_per_gpu": B, "draft_tokens": k, "vocab": V, "sampler": sampler_kw,
                    "l2": "inputs (%.2f GB of logits per GPU) are larger than L2" % ((dl.nbytes + tl.nbytes) / 1e9)},
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": alg_bytes * TRAFFIC_RATIO["accept"],
                      "peak_source": peak_src, "kernel": "spec_accept_kernel", "kernel_ms": kernel_ms, "launches_timed": counted,
                      "algorithmic_bytes_per_launch": alg_bytes},
         "e2e": {"value": acc_e2e * world / (ms_e2e * 1e-3), "unit": "tokens/s", "steps": e2e_steps,
