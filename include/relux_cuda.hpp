@@ -173,6 +173,33 @@ class KVCache {
     a.w = &w;
     check(relux_gqa_forward_cached(pool_, &a));
   }
+  // SpeculativeDecoder.acceptPhase (speculative.go:211-253) for this cache's sequence: draftLogits [k][vocab],
+  // targetLogits [k + 1][vocab], draws [k + 1] = the uniform numbers the reference would take from its generator, in
+  // order.  Returns the number of accepted draft tokens, *resampled receives the resampled / bonus token.  commit:
+  // the rows a verify call left past the cursor become part of the sequence (nAccepted + 1 of them).
+  int AcceptPhase(const int32_t* draftTokens, const float* draftLogits, const float* targetLogits, int k, int vocab,
+                  const float* draws, const relux_sampler_params& sampling, int* resampled, bool commit = true,
+                  int mode = RELUX_ATTN_FAST) {
+    relux_spec_accept_args a{};
+    int32_t nAcc = 0, next = 0;
+    a.n_seqs = 1;
+    a.k = k;
+    a.vocab = vocab;
+    a.mem = RELUX_MEM_HOST;
+    a.draft_tokens = draftTokens;
+    a.draft_logits = draftLogits;
+    a.target_logits = targetLogits;
+    a.draws = draws;
+    a.sampler = sampling;
+    a.mode = mode;
+    a.commit = commit ? 1 : 0;
+    a.seq_ids = &seq_;
+    a.n_accepted = &nAcc;
+    a.next_token = &next;
+    check(relux_spec_accept(pool_, &a));
+    *resampled = next;
+    return nAcc;
+  }
 
  private:
   relux_pool_t pool_ = nullptr;

@@ -53,6 +53,7 @@ struct SelShared {
   uint32_t hist_cnt[256];
   float warp_seg[kSelWarps];  // per-warp segment sums of the search pass
   uint32_t warp_hist[kSelWarps][256];   // radix selection: one histogram per warp (counts, or float sums)
+  uint32_t list_count;        // candidate list of the small-top-k path (the list itself reuses warp_hist)
 };
 
 __device__ __forceinline__ uint32_t order_key(float x) {
@@ -202,14 +203,19 @@ __device__ __forceinline__ void for_segment2(const Ctx& c, const float* __restri
 // the walk stops at the largest probability tau for which the sum of all probabilities >= tau reaches `want_sum` (the
 // nucleus cut of sampler.go:148-160; elements tied with tau are all kept).  Returns false when the total never
 // reaches want_sum.
+// stop_at (counting walk only): as soon as no more than stop_at elements have a key >= the lower bound of the chosen
+// bin, the walk ends early; *key_out is then that lower bound and *n_ge_out the number of elements at or above it (a
+// superset of the `want` largest that is small enough to finish on a list).
 template <bool kWeighted, class KeyF>
-__device__ bool radix_select(Ctx& c, const float* __restrict__ row, KeyF key_weight, uint32_t want, float want_sum, uint32_t* key_out) {
+__device__ bool radix_select(Ctx& c, const float* __restrict__ row, KeyF key_weight, uint32_t want, float want_sum, uint32_t* key_out,
+                             uint32_t stop_at = 0, uint32_t* n_ge_out = nullptr) {
+  const uint32_t want0 = want;
   cg::cluster_group cl = cg::this_cluster();
   uint32_t prefix = 0, mask = 0;
   float above = 0.0f;
   __shared__ uint32_t comb_cnt[256];
   __shared__ float comb_sum[256];
-  __shared__ uint32_t pick[2];
+  __shared__ uint32_t pick[3];
   __shared__ float pick_above;
   for (int shift = 24; shift >= 0; shift -= 8) {
     // every warp fills a histogram of its own (no contention between warps); they are added up afterwards
@@ -305,16 +311,19 @@ __device__ bool radix_select(Ctx& c, const float* __restrict__ row, KeyF key_wei
           acc += comb_cnt[b_hi - q];
         }
         const uint32_t any = __ballot_sync(0xffffffffu, hit >= 0);
-        if (any && c.lane == 31 - __clz(any)) { pick[0] = (uint32_t)hit; pick[1] = want - acc_hit; }
+        if (any && c.lane == 31 - __clz(any)) { pick[0] = (uint32_t)hit; pick[1] = want - acc_hit; pick[2] = comb_cnt[hit]; }
       }
     }
     __syncthreads();
     const uint32_t digit = pick[0];
     if (kWeighted) above = pick_above; else want = pick[1];
+    const uint32_t n_ge = kWeighted ? 0u : (want0 - want) + pick[2];   // elements above the bin plus the bin itself
     cl.sync();   // remote readers are done with this round's histograms
     if (digit == 256) return false;
     prefix |= digit << shift;
     mask |= 255u << shift;
+    if (n_ge_out) *n_ge_out = n_ge;
+    if (!kWeighted && stop_at && n_ge <= stop_at) break;
   }
   *key_out = prefix;
   return true;
@@ -405,6 +414,174 @@ __device__ void cdf_find(Ctx& c, const float* __restrict__ row, ProbF prob, floa
   }
 }
 
+// Sampler.Sample with a small top-k, finished on a list: after top-k only the k largest logits (and their ties) carry
+// probability, so once the radix walk has narrowed the row down to at most kCandCap elements the CTAs collect them,
+// CTA 0 sorts them by index and walks the rest of the reference's chain (softmax, nucleus, min-p, draw) over the list.
+// Every float32 sum runs in index order over the kept elements -- the elements the reference adds zeros for are
+// skipped -- so this path gives the reference's token bit for bit.  Returns false (nothing written) when the list
+// would not fit; the caller then takes the pass-per-step path.
+constexpr int kCandTopK = 128;   // largest top-k that takes this path
+constexpr int kCandCap = 512;    // list capacity
+
+__device__ bool sample_row_candidates(Ctx& c, const SelParams& prm, const float* __restrict__ row, const Dist& d, int topk, float r,
+                                      int32_t* out) {
+  cg::cluster_group cl = cg::this_cluster();
+  const int V = prm.vocab;
+  uint32_t key_lo = 0, n_ge = 0;
+  radix_select<false>(c, row, [&](float v, uint32_t& k, float& w) { k = order_key(d.scaled(v)); w = 0.0f; }, (uint32_t)topk, 0.0f, &key_lo,
+                      (uint32_t)kCandCap, &n_ge);
+  if (n_ge > (uint32_t)kCandCap) return false;     // more ties at the threshold than the list holds (uniform over the cluster)
+  // the list lives in the histogram block: words [0,512) values, [512,1024) indices
+  float* l_val = reinterpret_cast<float*>(&c.sh->warp_hist[0][0]);
+  int32_t* l_idx = reinterpret_cast<int32_t*>(&c.sh->warp_hist[0][0]) + kCandCap;
+  uint32_t* l_cnt = &c.sh->list_count;
+  if (threadIdx.x == 0) *l_cnt = 0;
+  __syncthreads();
+  for_segment(c, row, [&](int i, float v) {
+    const float x = d.scaled(v);
+    if (order_key(x) >= key_lo) {
+      const uint32_t pos = atomicAdd(l_cnt, 1u);
+      if (pos < (uint32_t)kCandCap) { l_val[pos] = x; l_idx[pos] = i; }
+    }
+  });
+  __syncthreads();
+  cl.sync();
+  if (c.rank == 0) {
+    float* a_val = l_val + 2 * kCandCap;            // all candidates, then (sorted by index) the kept ones and their probabilities
+    int32_t* a_idx = l_idx + 2 * kCandCap;
+    float* k_val = l_val + 4 * kCandCap;
+    int32_t* k_idx = l_idx + 4 * kCandCap;
+    float* k_p = l_val + 6 * kCandCap;
+    int32_t* k_ord = l_idx + 6 * kCandCap;
+    __shared__ int s_n, s_cut, s_tok;
+    __shared__ float s_thr, s_scale;
+    // gather the lists of all CTAs (rank order)
+    int n_c = 0;
+    for (int q = 0; q < c.csize; q++) {
+      const uint32_t cnt = min(*cl.map_shared_rank(l_cnt, q), (uint32_t)kCandCap);
+      const float* rv = cl.map_shared_rank(l_val, q);
+      const int32_t* ri = cl.map_shared_rank(l_idx, q);
+      for (int t = threadIdx.x; t < (int)cnt; t += kSelThreads)
+        if (n_c + t < kCandCap) { a_val[n_c + t] = rv[t]; a_idx[n_c + t] = ri[t]; }
+      n_c += (int)cnt;
+    }
+    n_c = min(n_c, kCandCap);
+    __syncthreads();
+    // kthLargest (sampler.go:283-300): the value with fewer than topk elements above it and at least topk at or above
+    if (threadIdx.x < n_c) {
+      const float v = a_val[threadIdx.x];
+      int gt = 0, ge = 0;
+      for (int j = 0; j < n_c; j++) { gt += a_val[j] > v; ge += a_val[j] >= v; }
+      if (gt < topk && topk <= ge) s_thr = v;
+    }
+    if (threadIdx.x == 0) s_n = 0;
+    __syncthreads();
+    const float thr = s_thr;
+    // keep what the mask leaves (not below the threshold), in index order
+    if (threadIdx.x < n_c && !(a_val[threadIdx.x] < thr)) {
+      int pos = 0;
+      for (int j = 0; j < n_c; j++) pos += (!(a_val[j] < thr)) && a_idx[j] < a_idx[threadIdx.x];
+      k_val[pos] = a_val[threadIdx.x];
+      k_idx[pos] = a_idx[threadIdx.x];
+      atomicAdd(&s_n, 1);
+    }
+    __syncthreads();
+    const int n_k = s_n;
+    // softmax over the kept logits (sampler.go:118-137)
+    if (threadIdx.x == 0) {
+      float maxV = k_val[0];
+      for (int j = 1; j < n_k; j++) if (k_val[j] > maxV) maxV = k_val[j];
+      float sum = 0.0f;
+      for (int j = 0; j < n_k; j++) { k_p[j] = fastexp32_ref(__fsub_rn(k_val[j], maxV)); sum = __fadd_rn(sum, k_p[j]); }
+      s_scale = sum > 0.0f ? __fdiv_rn(1.0f, sum) : 1.0f;
+    }
+    __syncthreads();
+    if (threadIdx.x < n_k) k_p[threadIdx.x] = __fmul_rn(k_p[threadIdx.x], s_scale);
+    __syncthreads();
+    float topP = prm.top_p;
+    if (topP <= 0.0f || topP > 1.0f) topP = 1.0f;
+    if (topP < 1.0f) {
+      // argsortDescF32 (sampler.go:268-281) followed only as far as the cut: a selection sort over all indices whose
+      // step i swaps the first largest remaining entry with whatever sits at position i.  Entries without probability
+      // are interchangeable, so only the positions of the kept elements are tracked (k_ord: position in the reference's
+      // index array, -1 once selected, -2 selected and kept); which of two equal probabilities comes first follows
+      // from the swaps, exactly as in the reference.
+      if (threadIdx.x < n_k) k_ord[threadIdx.x] = k_idx[threadIdx.x];
+      __syncthreads();
+      if (c.warp == 0) {   // one warp: the search of every step is spread over its lanes, the running sum stays sequential
+        float cum = 0.0f;
+        bool cut = false;
+        for (int step = 0; step < n_k && !cut; step++) {
+          float bp = -1.0f;
+          int bpos = 0x7fffffff, bj = -1, at_i = -1;
+          for (int j = c.lane; j < n_k; j += 32) {
+            const int pj = k_ord[j];
+            if (pj < 0) continue;
+            if (pj == step) at_i = j;
+            const float pv = k_p[j];
+            if (pv > bp || (pv == bp && pj < bpos)) { bp = pv; bpos = pj; bj = j; }
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            const float op = __shfl_xor_sync(0xffffffffu, bp, o);
+            const int opos = __shfl_xor_sync(0xffffffffu, bpos, o), oj = __shfl_xor_sync(0xffffffffu, bj, o);
+            at_i = max(at_i, __shfl_xor_sync(0xffffffffu, at_i, o));
+            if (op > bp || (op == bp && opos < bpos)) { bp = op; bpos = opos; bj = oj; }
+          }
+          if (bj < 0 || !(bp > 0.0f)) break;      // only zeros are left: the running sum stays below top-p
+          if (c.lane == 0) {
+            if (at_i >= 0 && at_i != bj) k_ord[at_i] = bpos;   // what sat at position `step` moves to the winner's place
+            k_ord[bj] = -2;
+          }
+          __syncwarp();
+          cum = __fadd_rn(cum, bp);
+          if (cum >= topP) cut = true;
+        }
+        if (c.lane == 0) s_cut = cut ? 1 : 0;
+      }
+      __syncthreads();
+      if (s_cut && threadIdx.x < n_k && k_ord[threadIdx.x] != -2) k_p[threadIdx.x] = 0.0f;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float s2 = 0.0f;
+        for (int j = 0; j < n_k; j++) s2 = __fadd_rn(s2, k_p[j]);
+        s_scale = s2 > 0.0f ? __fdiv_rn(1.0f, s2) : 1.0f;
+      }
+      __syncthreads();
+      if (threadIdx.x < n_k) k_p[threadIdx.x] = __fmul_rn(k_p[threadIdx.x], s_scale);
+      __syncthreads();
+    }
+    if (prm.min_p > 0.0f) {
+      if (threadIdx.x == 0) {
+        float maxProb = 0.0f;
+        for (int j = 0; j < n_k; j++) if (k_p[j] > maxProb) maxProb = k_p[j];
+        s_thr = __fmul_rn(maxProb, prm.min_p);
+      }
+      __syncthreads();
+      if (threadIdx.x < n_k && k_p[threadIdx.x] < s_thr) k_p[threadIdx.x] = 0.0f;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float s3 = 0.0f;
+        for (int j = 0; j < n_k; j++) s3 = __fadd_rn(s3, k_p[j]);
+        s_scale = s3 > 0.0f ? __fdiv_rn(1.0f, s3) : 1.0f;
+      }
+      __syncthreads();
+      if (threadIdx.x < n_k) k_p[threadIdx.x] = __fmul_rn(k_p[threadIdx.x], s_scale);
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+      float cum = 0.0f;
+      int tok = V - 1;
+      for (int j = 0; j < n_k; j++) {
+        cum = __fadd_rn(cum, k_p[j]);
+        if (r < cum) { tok = k_idx[j]; break; }
+      }
+      *out = tok;
+    }
+  }
+  return true;
+}
+
 // Sampler.Sample on one row (sampler.go:73-218, steps 3-8; no repetition penalties), one cluster per row.
 __device__ void sample_row(Ctx& c, const SelParams& prm, const float* __restrict__ row, float r, int32_t* out) {
   const int V = prm.vocab;
@@ -414,6 +591,8 @@ __device__ void sample_row(Ctx& c, const SelParams& prm, const float* __restrict
   bool nucleus = false, minp = false;
   int topk = prm.top_k;
   if (topk < 0 || topk >= V) topk = 0;
+  d.m = 0.0f; d.inv1 = 1.0f;
+  if (topk > 0 && topk <= kCandTopK && sample_row_candidates(c, prm, row, d, topk, r, out)) return;
   if (topk > 0) {
     uint32_t key = 0;
     radix_select<false>(c, row, [&](float v, uint32_t& k, float& w) { k = order_key(d.scaled(v)); w = 0.0f; }, (uint32_t)topk, 0.0f, &key);

@@ -129,6 +129,28 @@ int main() {
     EXPECT(same, "ForwardCached identity layer");
     dev.Free((void*)w.w_q); dev.Free((void*)w.w_k); dev.Free((void*)w.w_v); dev.Free((void*)w.w_o);
   }
+  {  // acceptPhase through the mirror: a draft equal to the target is accepted whole, a near-zero temperature makes
+    // the bonus token the argmax of the last row, and the commit advances the cache by k + 1 rows; a target without
+    // mass on the first draft token rejects it and resamples another token (speculative.go:211-253).
+    const int k = 3, V = 512, D = 16;
+    relux::KVCache c(dev, 1, 64, 1, D);
+    std::vector<float> dl((size_t)k * V), tl((size_t)(k + 1) * V);
+    uint32_t state = 12345u;
+    auto next = [&]() { state = state * 1664525u + 1013904223u; return (float)(state >> 8) / 16777216.0f; };
+    for (auto& v : dl) v = next() * 8.f - 4.f;
+    for (int i = 0; i < k * V; i++) tl[i] = dl[i];
+    int best = 0;
+    for (int j = 0; j < V; j++) { tl[(size_t)k * V + j] = next() * 8.f - 4.f; if (tl[(size_t)k * V + j] > tl[(size_t)k * V + best]) best = j; }
+    int32_t toks[k] = {7, 400, 33};
+    float draws[k + 1] = {0.3f, 0.9f, 0.5f, 0.7f};
+    relux_sampler_params sp{1e-10f, 0, 1.0f, 0.0f};
+    int tok = -1;
+    int n = c.AcceptPhase(toks, dl.data(), tl.data(), k, V, draws, sp, &tok);
+    EXPECT(n == k && tok == best && c.TotalLen(0) == k + 1, "AcceptPhase accepts an identical draft and commits k + 1 rows");
+    tl[toks[0]] = -90.f;
+    n = c.AcceptPhase(toks, dl.data(), tl.data(), k, V, draws, sp, &tok, false);
+    EXPECT(n == 0 && tok != toks[0] && tok >= 0 && tok < V && c.TotalLen(0) == k + 1, "AcceptPhase rejects a token the target excludes");
+  }
   if (failures == 0) printf("ALL PASSED\n");
   return failures ? 1 : 0;
 }

@@ -145,6 +145,24 @@ def test_plain_sampling_rows(pool, oracle):
                 assert (cum[g - 1] if g else 0.0) - SUM_TOL <= draws[i] < cum[g] + SUM_TOL
 
 
+@pytest.mark.parametrize("V", [1000, 32000, 131072])
+def test_small_top_k_is_bit_exact_in_fast_mode(pool, oracle, V):
+    """With top-k <= 128 the fast path finishes the sampler on the list of kept logits in the reference's own order
+    of float32 operations: tokens equal the reference's exactly, whatever the other filters."""
+    rng = np.random.default_rng(V)
+    n = 24
+    logits = (rng.standard_normal((n, V)) * 3).astype(np.float32)
+    logits[3, :200] = logits[3, 0]          # a plateau of ties around the threshold
+    logits[4] = np.round(logits[4])          # many exact ties everywhere
+    draws = rng.random(n).astype(np.float32)
+    for sampler in (dict(top_k=1), dict(top_k=50), dict(top_k=128, temperature=0.6), dict(top_k=40, top_p=0.9),
+                    dict(top_k=64, top_p=0.5, min_p=0.1, temperature=1.4)):
+        cfg = oracle.sampler_cfg(**sampler)
+        want = [oracle.sampler_sample(cfg, logits[i], float(draws[i])) for i in range(n)]
+        got = pool.sample(logits, draws, **sampler)
+        assert got.tolist() == want, sampler
+
+
 def test_reference_sampler_properties(pool):
     """The two properties sampler_test.go checks: temperature -> 0 always yields the argmax, top-k 2 only the two
     largest logits."""
