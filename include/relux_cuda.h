@@ -355,6 +355,36 @@ typedef struct relux_spec_accept_args {
 } relux_spec_accept_args;
 int32_t relux_spec_accept(relux_pool_t pool, const relux_spec_accept_args* args);
 
+/* Sampler.Sample (internal/transformer/sampler.go:73-218) for a batch of rows, repetition control included: the
+ * logits of the tokens in a row's window of previous tokens are rewritten first (applyRepetitionPenalties,
+ * sampler.go:221-266: repeat penalty -- divide a positive logit, multiply a negative one --, frequency penalty times
+ * the count in the window, presence penalty; each once per distinct token; tokens outside [0, vocab) are ignored),
+ * then temperature, top-k, softmax, nucleus, min-p and the categorical draw run as in relux_spec_accept with k = 0.
+ * This is the call Transformer.Generate makes per step (transformer.go:955-962) and draftPhase per draft token
+ * (speculative.go:178).  logits [n_rows][vocab] float32 and draws [n_rows] (the reference's rng.Float32() per call) in
+ * host or device memory; prev_tokens host int32 [n_rows][prev_stride] with prev_len [n_rows] valid entries per row
+ * (NULL: previousTokens == nil); repeat_window 0 = all previous tokens.  tokens [n_rows] is written to HOST memory;
+ * the call synchronises the stream.  The input logits are never modified (the reference works on a copy too). */
+typedef struct relux_sample_args {
+  int32_t n_rows;
+  int32_t vocab;
+  int32_t mem;               /* RELUX_MEM_* of logits and draws */
+  int32_t mode;              /* RELUX_ATTN_FAST | RELUX_ATTN_REFERENCE */
+  const float* logits;
+  const float* draws;
+  relux_sampler_params sampler;
+  float repeat_penalty;      /* 0 or 1: off (sampler.go:246) */
+  float frequency_penalty;
+  float presence_penalty;
+  int32_t repeat_window;
+  const int32_t* prev_tokens;
+  const int32_t* prev_len;
+  int32_t prev_stride;
+  int32_t reserved[3];
+  int32_t* tokens;           /* host [n_rows], out */
+} relux_sample_args;
+int32_t relux_sampler_sample(relux_pool_t pool, const relux_sample_args* args);
+
 /* GQA flash-decode / verify that allocates nothing.  It has no counterpart in the reference; it exists for callers
  * that may not allocate device memory at the moment they decode: a serving loop whose memory budget has been handed
  * out completely (so a late cudaMalloc can fail or stall the whole device while it synchronises), or code running

@@ -315,12 +315,34 @@ class Pool:
         L.check(self.lib.relux_spec_accept(self.h, C.byref(args)))
         return n_acc, nxt
 
-    def sample(self, logits, draws, vocab=None, n_rows=None, **kw):
-        """Sampler.Sample (sampler.go:73-218, without repetition penalties) for a batch of rows: logits [n, vocab],
-        draws [n]."""
+    def sample(self, logits, draws, vocab=None, n_rows=None, temperature=1.0, top_k=0, top_p=1.0, min_p=0.0, mode=L.ATTN_FAST,
+               prev_tokens=None, repeat_penalty=1.0, frequency_penalty=0.0, presence_penalty=0.0, repeat_window=0):
+        """Sampler.Sample (sampler.go:73-218) for a batch of rows: logits [n, vocab] and draws [n] as numpy arrays or
+        device buffers (then pass n_rows and vocab); prev_tokens: one sequence of earlier token ids per row for the
+        repetition penalties (sampler.go:221-266), or None.  Returns the token ids (int32 array)."""
         if n_rows is None:
             n_rows, vocab = logits.shape
-        return self.spec_accept(n_rows, 0, vocab, None, None, logits, draws, **kw)[1]
+        if _mem(logits) != _mem(draws):
+            raise TypeError("sample: logits and draws must both be host arrays or both device buffers")
+        if _mem(logits) == L.MEM_HOST:
+            logits = np.ascontiguousarray(logits, dtype=np.float32)
+            draws = np.ascontiguousarray(draws, dtype=np.float32)
+        prev = plen = None
+        stride = 0
+        if prev_tokens is not None:
+            plen = np.asarray([len(t) for t in prev_tokens], np.int32)
+            stride = int(max(1, plen.max() if plen.size else 1))
+            prev = np.zeros((n_rows, stride), np.int32)
+            for i, t in enumerate(prev_tokens):
+                prev[i, :len(t)] = np.asarray(t, np.int32)
+        toks = np.full(n_rows, -1, np.int32)
+        args = L.SampleArgs(n_rows=n_rows, vocab=vocab, mem=_mem(logits), mode=mode, logits=_ptr(logits), draws=_ptr(draws),
+                            sampler=L.SamplerParams(float(temperature), int(top_k), float(top_p), float(min_p)),
+                            repeat_penalty=float(repeat_penalty), frequency_penalty=float(frequency_penalty),
+                            presence_penalty=float(presence_penalty), repeat_window=int(repeat_window), prev_tokens=_ptr(prev),
+                            prev_len=_ptr(plen), prev_stride=stride, tokens=toks.ctypes.data)
+        L.check(self.lib.relux_sampler_sample(self.h, C.byref(args)))
+        return toks
 
     def forward_cached(self, layer, n_seqs, x, out, weights, d_model, num_heads, q_tokens=1, causal=True, rope_base=0.0,
                        mode=L.ATTN_FAST, seq_ids=None, rope=True, advance=True):

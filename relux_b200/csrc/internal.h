@@ -147,6 +147,7 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
 int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a);
 int32_t do_gqa_layer(Pool* p, const relux_gqa_layer_args* a);
 int32_t do_spec_accept(Pool* p, const relux_spec_accept_args* a);
+int32_t do_sample(Pool* p, const relux_sample_args* a);
 int32_t seq_set_len(Pool* p, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const int32_t* new_len);
 
 inline void count_launch(Device* d, int n = 1) { d->launches += n; }

@@ -895,6 +895,11 @@ API int32_t relux_spec_accept(relux_pool_t h, const relux_spec_accept_args* a) {
   return do_spec_accept(p, a);
 }
 
+API int32_t relux_sampler_sample(relux_pool_t h, const relux_sample_args* a) {
+  GET_POOL(h);
+  return do_sample(p, a);
+}
+
 API int32_t relux_pool_last_kernel_ms(relux_pool_t h, float* ms) {
   GET_POOL(h);
   if (!ms) return RELUX_ERR_INVALID_ARG;

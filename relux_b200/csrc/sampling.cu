@@ -86,13 +86,16 @@ struct Ctx {
   uint32_t round;      // reduction counter (selects the exchange buffer)
 };
 
-// Sum (or maximum) of up to four per-thread values over the whole cluster; every thread of every CTA gets the same
-// result, added in CTA order.  One cluster barrier per call: the two exchange buffers alternate.
-template <bool kMax>
+// Sum or maximum of up to four per-thread values over the whole cluster; every thread of every CTA gets the same result,
+// combined in CTA order.  kMode 0: four sums; 1: four maxima; 2: values 0-1 summed, values 2-3 maximised (one barrier
+// for the sums of one row pair and the maxima of the next).  One cluster barrier per call: the two exchange buffers
+// alternate.
+template <int kMode>
 __device__ void cluster_reduce4(Ctx& c, float (&v)[4]) {
   cg::cluster_group cl = cg::this_cluster();
+  auto is_max = [](int j) { return kMode == 1 || (kMode == 2 && j >= 2); };
 #pragma unroll
-  for (int j = 0; j < 4; j++) v[j] = kMax ? warp_max(v[j]) : warp_sum(v[j]);
+  for (int j = 0; j < 4; j++) v[j] = is_max(j) ? warp_max(v[j]) : warp_sum(v[j]);
   if (c.lane == 0) {
 #pragma unroll
     for (int j = 0; j < 4; j++) c.sh->warp_part[c.warp][j] = v[j];
@@ -100,17 +103,18 @@ __device__ void cluster_reduce4(Ctx& c, float (&v)[4]) {
   __syncthreads();
   const int buf = c.round & 1;
   if (threadIdx.x < 4) {
+    const bool mx = is_max((int)threadIdx.x);
     float a = c.sh->warp_part[0][threadIdx.x];
-    for (int w = 1; w < kSelWarps; w++) a = kMax ? fmaxf(a, c.sh->warp_part[w][threadIdx.x]) : a + c.sh->warp_part[w][threadIdx.x];
+    for (int w = 1; w < kSelWarps; w++) a = mx ? fmaxf(a, c.sh->warp_part[w][threadIdx.x]) : a + c.sh->warp_part[w][threadIdx.x];
     c.sh->red[buf][threadIdx.x] = a;
   }
   cl.sync();
 #pragma unroll
   for (int j = 0; j < 4; j++) {
-    float a = kMax ? -INFINITY : 0.0f;
+    float a = is_max(j) ? -INFINITY : 0.0f;
     for (int r = 0; r < c.csize; r++) {
       const float* remote = cl.map_shared_rank(&c.sh->red[buf][j], r);
-      a = kMax ? fmaxf(a, *remote) : a + *remote;
+      a = is_max(j) ? fmaxf(a, *remote) : a + *remote;
     }
     v[j] = a;
   }
@@ -600,12 +604,12 @@ __device__ void sample_row(Ctx& c, const SelParams& prm, const float* __restrict
   }
   float v4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
   for_segment(c, row, [&](int, float v) { v4[0] = fmaxf(v4[0], d.scaled(v)); });
-  cluster_reduce4<true>(c, v4);
+  cluster_reduce4<1>(c, v4);
   d.m = v4[0];
   d.inv1 = 1.0f;
   v4[0] = v4[1] = v4[2] = v4[3] = 0.0f;
   for_segment(c, row, [&](int, float v) { v4[0] += d.p1(v); });
-  cluster_reduce4<false>(c, v4);
+  cluster_reduce4<0>(c, v4);
   if (v4[0] > 0.0f) d.inv1 = __fdiv_rn(1.0f, v4[0]);
   float topP = prm.top_p;
   if (topP <= 0.0f || topP > 1.0f) topP = 1.0f;
@@ -616,7 +620,7 @@ __device__ void sample_row(Ctx& c, const SelParams& prm, const float* __restrict
     const float tau = cut ? __uint_as_float(key) : 0.0f;
     v4[0] = v4[1] = v4[2] = v4[3] = 0.0f;
     for_segment(c, row, [&](int, float v) { float p = d.p1(v); if (p >= tau) v4[0] += p; });
-    cluster_reduce4<false>(c, v4);
+    cluster_reduce4<0>(c, v4);
     d.tau = tau;
     d.inv2 = v4[0] > 0.0f ? __fdiv_rn(1.0f, v4[0]) : 1.0f;
   }
@@ -627,11 +631,11 @@ __device__ void sample_row(Ctx& c, const SelParams& prm, const float* __restrict
     // the largest probability belongs to the row maximum, which no filter removes
     v4[0] = v4[1] = v4[2] = v4[3] = 0.0f;
     for_segment(c, row, [&](int, float v) { v4[0] = fmaxf(v4[0], p2(v)); });
-    cluster_reduce4<true>(c, v4);
+    cluster_reduce4<1>(c, v4);
     const float thr = __fmul_rn(v4[0], prm.min_p);
     v4[0] = v4[1] = v4[2] = v4[3] = 0.0f;
     for_segment(c, row, [&](int, float v) { float p = p2(v); if (!(p < thr)) v4[0] += p; });
-    cluster_reduce4<false>(c, v4);
+    cluster_reduce4<0>(c, v4);
     d.minp_thr = thr;
     d.inv3 = v4[0] > 0.0f ? __fdiv_rn(1.0f, v4[0]) : 1.0f;
   }
@@ -664,6 +668,15 @@ __global__ void __launch_bounds__(kSelThreads, 2) spec_accept_kernel(SelParams p
   int used = 0;
   int n_acc = k;
   bool done = false;
+  float next_md = 0.0f, next_mt = 0.0f;
+  if (k > 0) {
+    float v4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    for_segment2(c, prm.draft_logits + (size_t)b * k * V, prm.target_logits + (size_t)b * (k + 1) * V,
+                 [&](int, float dv, float tv) { v4[0] = fmaxf(v4[0], dv); v4[1] = fmaxf(v4[1], tv); });
+    cluster_reduce4<1>(c, v4);
+    next_md = v4[0];
+    next_mt = v4[1];
+  }
   for (int i = 0; i < k && !done; i++) {
     const float* drow = prm.draft_logits + ((size_t)b * k + i) * V;
     const float* trow = prm.target_logits + ((size_t)b * (k + 1) + i) * V;
@@ -674,16 +687,20 @@ __global__ void __launch_bounds__(kSelThreads, 2) spec_accept_kernel(SelParams p
       done = true;
       break;
     }
-    float v4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-    for_segment2(c, drow, trow, [&](int, float dv, float tv) { v4[0] = fmaxf(v4[0], dv); v4[1] = fmaxf(v4[1], tv); });
-    cluster_reduce4<true>(c, v4);
-    const float md = v4[0], mt = v4[1];
-    v4[0] = v4[1] = v4[2] = v4[3] = 0.0f;
+    // The maxima of this position's rows came with the previous position's sums (or from the pass before the loop);
+    // this pass adds up the exponentials and already takes the maxima of the next position's rows, so every draft
+    // position costs one barrier.  When this position rejects, the look-ahead was two rows read in vain.
+    const float md = next_md, mt = next_mt;
+    float v4[4] = {0.0f, 0.0f, -INFINITY, -INFINITY};
     for_segment2(c, drow, trow, [&](int, float dv, float tv) {
       v4[0] += fastexp32_ref(__fsub_rn(dv, md));
       v4[1] += fastexp32_ref(__fsub_rn(tv, mt));
     });
-    cluster_reduce4<false>(c, v4);
+    if (i + 1 < k)
+      for_segment2(c, drow + V, trow + V, [&](int, float dv, float tv) { v4[2] = fmaxf(v4[2], dv); v4[3] = fmaxf(v4[3], tv); });
+    cluster_reduce4<2>(c, v4);
+    next_md = v4[2];
+    next_mt = v4[3];
     const float invd = v4[0] > 0.0f ? __fdiv_rn(1.0f, v4[0]) : 1.0f;
     const float invt = v4[1] > 0.0f ? __fdiv_rn(1.0f, v4[1]) : 1.0f;
     const float dP = __fmul_rn(fastexp32_ref(__fsub_rn(__ldg(drow + tok), md)), invd);
@@ -704,7 +721,7 @@ __global__ void __launch_bounds__(kSelThreads, 2) spec_accept_kernel(SelParams p
       float diff = __fsub_rn(__fmul_rn(fastexp32_ref(__fsub_rn(tv, mt)), invt), __fmul_rn(fastexp32_ref(__fsub_rn(dv, md)), invd));
       v4[0] += diff < 0.0f ? 0.0f : diff;
     });
-    cluster_reduce4<false>(c, v4);
+    cluster_reduce4<0>(c, v4);
     const float r = draws[used++];
     if (v4[0] > 0.0f) {
       const float inv = __fdiv_rn(1.0f, v4[0]);
@@ -876,55 +893,58 @@ __global__ void spec_accept_reference_kernel(SelParams prm, int n_seqs, float* f
   if (prm.n_accepted) prm.n_accepted[b] = k;
 }
 
-}  // namespace
 
-int32_t do_spec_accept(Pool* p, const relux_spec_accept_args* a) {
-  if (!a) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
-  const int n = a->n_seqs, k = a->k, V = a->vocab;
-  if (n <= 0 || k < 0 || V <= 0 || !a->target_logits || !a->draws || !a->next_token ||
-      (k > 0 && (!a->draft_tokens || !a->draft_logits || !a->n_accepted)) ||
-      (a->mem != RELUX_MEM_HOST && a->mem != RELUX_MEM_DEVICE) ||
-      (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE)) {
-    set_error("spec_accept: bad arguments");
-    return RELUX_ERR_INVALID_ARG;
+// Sampler.applyRepetitionPenalties (sampler.go:221-266): copies every row to `dst` and rewrites the logits of the tokens
+// in the row's window of previous tokens -- repeat penalty (divide a positive logit, multiply a negative one), then
+// frequency penalty times the token's count in the window, then presence penalty, each applied once per distinct
+// token, in float32 like the reference.  One block per row; win_off [n + 1] delimits the rows' windows in win_tok.
+__global__ void repetition_penalty_kernel(const float* __restrict__ src, float* __restrict__ dst, int vocab,
+                                          const int32_t* __restrict__ win_tok, const int32_t* __restrict__ win_off,
+                                          float rp, float fp, float pp) {
+  const int b = blockIdx.x;
+  const float* s = src + (size_t)b * vocab;
+  float* d = dst + (size_t)b * vocab;
+  if ((vocab & 3) == 0 && ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0) {
+    for (int i = threadIdx.x * 4; i < vocab; i += blockDim.x * 4)
+      *reinterpret_cast<float4*>(d + i) = __ldg(reinterpret_cast<const float4*>(s + i));
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) d[i] = s[i];
   }
-  if (a->commit && n > p->prm.max_seqs) { set_error("spec_accept: more sequences than the pool holds"); return RELUX_ERR_INVALID_ARG; }
-  if (a->mem == RELUX_MEM_HOST)
-    for (size_t i = 0; i < (size_t)n * k; i++)
-      if (a->draft_tokens[i] < 0 || a->draft_tokens[i] >= V) {
-        set_error("spec_accept: draft token %d outside the vocabulary of %d", a->draft_tokens[i], V);
-        return RELUX_ERR_INVALID_ARG;
-      }
+  __syncthreads();
+  const int w0 = win_off[b], w1 = win_off[b + 1];
+  for (int j = w0 + threadIdx.x; j < w1; j += blockDim.x) {
+    const int tok = win_tok[j];
+    if (tok < 0 || tok >= vocab) continue;
+    bool first = true;
+    int freq = 0;
+    for (int q = w0; q < w1; q++) {
+      if (win_tok[q] == tok) { freq++; if (q < j) first = false; }
+    }
+    if (!first) continue;     // one thread per distinct token: the first occurrence owns the update
+    float x = d[tok];
+    if (rp != 1.0f && rp != 0.0f) x = x > 0.0f ? __fdiv_rn(x, rp) : __fmul_rn(x, rp);
+    if (fp != 0.0f) x = __fsub_rn(x, __fmul_rn(fp, (float)freq));
+    if (pp != 0.0f) x = __fsub_rn(x, pp);
+    d[tok] = x;
+  }
+}
+
+// Launches the selection kernel on device-resident inputs (prm holds the input pointers, k and vocab) and brings the
+// 2 n result words (accepted counts, then tokens) to the host; synchronises the stream.
+static int32_t launch_selection(Pool* p, SelParams& prm, int n, const relux_sampler_params& sp, int mode, std::vector<int32_t>& host) {
   Device* dev = p->dev;
-  SelParams prm{};
-  const void* d = nullptr;
+  const int V = prm.vocab;
   int32_t rc;
-  if (k > 0) {
-    rc = stage_in(p, p->in_a, a->draft_logits, sizeof(float) * (size_t)n * k * V, a->mem, &d);
-    if (rc) return rc;
-    prm.draft_logits = (const float*)d;
-    rc = stage_in(p, p->q_conv, a->draft_tokens, sizeof(int32_t) * (size_t)n * k, a->mem, &d);
-    if (rc) return rc;
-    prm.draft_tokens = (const int32_t*)d;
-  }
-  rc = stage_in(p, p->in_b, a->target_logits, sizeof(float) * (size_t)n * (k + 1) * V, a->mem, &d);
-  if (rc) return rc;
-  prm.target_logits = (const float*)d;
-  rc = stage_in(p, p->o_lat, a->draws, sizeof(float) * (size_t)n * (k + 1), a->mem, &d);
-  if (rc) return rc;
-  prm.draws = (const float*)d;
   rc = grow(dev, p->out_buf, sizeof(int32_t) * 2 * (size_t)n);
   if (rc) return rc;
   prm.n_accepted = (int32_t*)p->out_buf.p;
   prm.next_token = prm.n_accepted + n;
   prm.status = p->d_status;
-  prm.k = k;
-  prm.vocab = V;
-  prm.temperature = a->sampler.temperature;
-  prm.top_k = a->sampler.top_k;
-  prm.top_p = a->sampler.top_p;
-  prm.min_p = a->sampler.min_p;
-  if (a->mode == RELUX_ATTN_REFERENCE) {
+  prm.temperature = sp.temperature;
+  prm.top_k = sp.top_k;
+  prm.top_p = sp.top_p;
+  prm.min_p = sp.min_p;
+  if (mode == RELUX_ATTN_REFERENCE) {
     rc = grow(dev, p->part_o, sizeof(float) * 2 * (size_t)n * V);
     if (rc) return rc;
     rc = grow(dev, p->part_ml, sizeof(int32_t) * (size_t)n * V);
@@ -932,7 +952,7 @@ int32_t do_spec_accept(Pool* p, const relux_spec_accept_args* a) {
   }
   // device time of the selection kernel, readable through relux_pool_kernel_ms_mean like the attention kernels'
   RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), dev->stream));
-  if (a->mode == RELUX_ATTN_REFERENCE) {
+  if (mode == RELUX_ATTN_REFERENCE) {
     spec_accept_reference_kernel<<<(n + 31) / 32, 32, 0, dev->stream>>>(prm, n, (float*)p->part_o.p, (int32_t*)p->part_ml.p);
   } else {
     // Cluster size: slices should stay long enough to keep 512 threads busy, and all sequences should be resident at
@@ -983,9 +1003,54 @@ int32_t do_spec_accept(Pool* p, const relux_spec_accept_args* a) {
   RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), dev->stream));
   p->timed_calls++;
   count_launch(dev);
-  std::vector<int32_t> host((size_t)2 * n);
+  host.resize((size_t)2 * n);
   RELUX_CUDA_TRY(cudaMemcpyAsync(host.data(), p->out_buf.p, sizeof(int32_t) * 2 * (size_t)n, cudaMemcpyDeviceToHost, dev->stream));
   RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  return RELUX_OK;
+}
+
+}  // namespace
+
+int32_t do_spec_accept(Pool* p, const relux_spec_accept_args* a) {
+  if (!a) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
+  const int n = a->n_seqs, k = a->k, V = a->vocab;
+  if (n <= 0 || k < 0 || V <= 0 || !a->target_logits || !a->draws || !a->next_token ||
+      (k > 0 && (!a->draft_tokens || !a->draft_logits || !a->n_accepted)) ||
+      (a->mem != RELUX_MEM_HOST && a->mem != RELUX_MEM_DEVICE) ||
+      (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE)) {
+    set_error("spec_accept: bad arguments");
+    return RELUX_ERR_INVALID_ARG;
+  }
+  if (a->commit && n > p->prm.max_seqs) { set_error("spec_accept: more sequences than the pool holds"); return RELUX_ERR_INVALID_ARG; }
+  if (a->mem == RELUX_MEM_HOST)
+    for (size_t i = 0; i < (size_t)n * k; i++)
+      if (a->draft_tokens[i] < 0 || a->draft_tokens[i] >= V) {
+        set_error("spec_accept: draft token %d outside the vocabulary of %d", a->draft_tokens[i], V);
+        return RELUX_ERR_INVALID_ARG;
+      }
+  Device* dev = p->dev;
+  SelParams prm{};
+  const void* d = nullptr;
+  int32_t rc;
+  if (k > 0) {
+    rc = stage_in(p, p->in_a, a->draft_logits, sizeof(float) * (size_t)n * k * V, a->mem, &d);
+    if (rc) return rc;
+    prm.draft_logits = (const float*)d;
+    rc = stage_in(p, p->q_conv, a->draft_tokens, sizeof(int32_t) * (size_t)n * k, a->mem, &d);
+    if (rc) return rc;
+    prm.draft_tokens = (const int32_t*)d;
+  }
+  rc = stage_in(p, p->in_b, a->target_logits, sizeof(float) * (size_t)n * (k + 1) * V, a->mem, &d);
+  if (rc) return rc;
+  prm.target_logits = (const float*)d;
+  rc = stage_in(p, p->o_lat, a->draws, sizeof(float) * (size_t)n * (k + 1), a->mem, &d);
+  if (rc) return rc;
+  prm.draws = (const float*)d;
+  prm.k = k;
+  prm.vocab = V;
+  std::vector<int32_t> host;
+  rc = launch_selection(p, prm, n, a->sampler, a->mode, host);
+  if (rc) return rc;
   for (int i = 0; i < n; i++) {
     if (a->n_accepted) a->n_accepted[i] = host[i];
     a->next_token[i] = host[(size_t)n + i];
@@ -1006,6 +1071,60 @@ int32_t do_spec_accept(Pool* p, const relux_spec_accept_args* a) {
       if (rc) return rc;
     }
   }
+  return RELUX_OK;
+}
+
+int32_t do_sample(Pool* p, const relux_sample_args* a) {
+  if (!a) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
+  const int n = a->n_rows, V = a->vocab;
+  if (n <= 0 || V <= 0 || !a->logits || !a->draws || !a->tokens || (a->mem != RELUX_MEM_HOST && a->mem != RELUX_MEM_DEVICE) ||
+      (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE) || (a->prev_tokens && (!a->prev_len || a->prev_stride < 0))) {
+    set_error("sampler_sample: bad arguments");
+    return RELUX_ERR_INVALID_ARG;
+  }
+  Device* dev = p->dev;
+  SelParams prm{};
+  const void* d = nullptr;
+  int32_t rc = stage_in(p, p->in_b, a->logits, sizeof(float) * (size_t)n * V, a->mem, &d);
+  if (rc) return rc;
+  prm.target_logits = (const float*)d;
+  rc = stage_in(p, p->o_lat, a->draws, sizeof(float) * (size_t)n, a->mem, &d);
+  if (rc) return rc;
+  prm.draws = (const float*)d;
+  const bool penalties = a->prev_tokens && ((a->repeat_penalty != 1.0f && a->repeat_penalty != 0.0f) || a->frequency_penalty != 0.0f ||
+                                            a->presence_penalty != 0.0f);
+  if (penalties) {
+    // the window of every row (sampler.go:225-228), flattened: offsets [n + 1] then tokens
+    std::vector<int32_t> flat((size_t)n + 1, 0);
+    for (int i = 0; i < n; i++) {
+      int len = a->prev_len[i];
+      if (len < 0 || len > a->prev_stride) { set_error("sampler_sample: prev_len[%d] = %d outside [0, %d]", i, len, a->prev_stride); return RELUX_ERR_INVALID_ARG; }
+      int w0 = (a->repeat_window > 0 && len > a->repeat_window) ? len - a->repeat_window : 0;
+      const int32_t* row = a->prev_tokens + (size_t)i * a->prev_stride;
+      flat.insert(flat.end(), row + w0, row + len);
+      flat[i + 1] = (int32_t)(flat.size() - (size_t)n - 1);
+    }
+    if (flat.size() > (size_t)n + 1) {
+      rc = grow(dev, p->q_conv, sizeof(int32_t) * flat.size());
+      if (rc) return rc;
+      rc = grow(dev, p->layer_buf, sizeof(float) * (size_t)n * V);
+      if (rc) return rc;
+      // pageable source: the copy has left the vector when the call returns
+      RELUX_CUDA_TRY(cudaMemcpyAsync(p->q_conv.p, flat.data(), sizeof(int32_t) * flat.size(), cudaMemcpyHostToDevice, dev->stream));
+      const int32_t* d_off = (const int32_t*)p->q_conv.p;
+      repetition_penalty_kernel<<<n, 256, 0, dev->stream>>>(prm.target_logits, (float*)p->layer_buf.p, V, d_off + n + 1, d_off,
+                                                            a->repeat_penalty, a->frequency_penalty, a->presence_penalty);
+      RELUX_CUDA_TRY(cudaGetLastError());
+      count_launch(dev);
+      prm.target_logits = (const float*)p->layer_buf.p;
+    }
+  }
+  prm.k = 0;
+  prm.vocab = V;
+  std::vector<int32_t> host;
+  rc = launch_selection(p, prm, n, a->sampler, a->mode, host);
+  if (rc) return rc;
+  for (int i = 0; i < n; i++) a->tokens[i] = host[(size_t)n + i];
   return RELUX_OK;
 }
 

@@ -31,7 +31,7 @@ EXPORTS = [
     "relux_pool_set_tables", "relux_seq_alloc", "relux_seq_free", "relux_seq_extend", "relux_seq_len", "relux_seq_set_len", "relux_pool_status",
     "relux_pool_read_rows", "relux_mla_append", "relux_gqa_append", "relux_mla_decode", "relux_gqa_decode", "relux_gqa_verify",
     "relux_mla_verify", "relux_pool_last_kernel_ms", "relux_pool_kernel_ms_mean", "relux_mla_forward_cached", "relux_gqa_forward_cached", "relux_stream_partition", "relux_seq_save_file", "relux_seq_load_file", "relux_pool_projection_ms_mean", "relux_gqa_decode_noalloc",
-    "relux_spec_accept",
+    "relux_spec_accept", "relux_sampler_sample",
 ]
 
 
@@ -89,6 +89,13 @@ class SpecAcceptArgs(C.Structure):
                 ("draft_tokens", C.c_void_p), ("draft_logits", C.c_void_p), ("target_logits", C.c_void_p),
                 ("draws", C.c_void_p), ("sampler", SamplerParams), ("mode", C.c_int32), ("commit", C.c_int32),
                 ("seq_ids", C.c_void_p), ("n_accepted", C.c_void_p), ("next_token", C.c_void_p), ("reserved", C.c_int32 * 4)]
+
+
+class SampleArgs(C.Structure):
+    _fields_ = [("n_rows", C.c_int32), ("vocab", C.c_int32), ("mem", C.c_int32), ("mode", C.c_int32), ("logits", C.c_void_p),
+                ("draws", C.c_void_p), ("sampler", SamplerParams), ("repeat_penalty", C.c_float), ("frequency_penalty", C.c_float),
+                ("presence_penalty", C.c_float), ("repeat_window", C.c_int32), ("prev_tokens", C.c_void_p), ("prev_len", C.c_void_p),
+                ("prev_stride", C.c_int32), ("reserved", C.c_int32 * 3), ("tokens", C.c_void_p)]
 
 
 class ReluxCudaError(RuntimeError):
@@ -158,6 +165,7 @@ def load():
         L.relux_gqa_forward_cached.argtypes = [C.c_void_p, C.POINTER(GqaLayerArgs)]
         L.relux_mla_forward_cached.argtypes = [C.c_void_p, C.POINTER(MlaLayerArgs)]
         L.relux_spec_accept.argtypes = [C.c_void_p, C.POINTER(SpecAcceptArgs)]
+        L.relux_sampler_sample.argtypes = [C.c_void_p, C.POINTER(SampleArgs)]
         L.relux_pool_last_kernel_ms.argtypes = [C.c_void_p, C.POINTER(C.c_float)]
         L.relux_pool_kernel_ms_mean.argtypes = [C.c_void_p, C.c_int32, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
         L.relux_cuda_launch_count.argtypes = [C.c_void_p, C.POINTER(C.c_int64)]

@@ -56,12 +56,13 @@ def test_struct_sizes_match_the_header(so):
         #include <stdio.h>
         #include "relux_cuda.h"
         #include <stddef.h>
-        int main(void){ printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(relux_pool_params), sizeof(relux_append_args),
+        int main(void){ printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(relux_pool_params), sizeof(relux_append_args),
                                sizeof(relux_attn_args), sizeof(relux_mla_layer_weights), sizeof(relux_mla_layer_args),
                                sizeof(relux_gqa_layer_weights), sizeof(relux_gqa_layer_args),
                                offsetof(relux_mla_layer_args, w), offsetof(relux_gqa_layer_args, w),
                                sizeof(relux_sampler_params), sizeof(relux_spec_accept_args), offsetof(relux_spec_accept_args, sampler),
-                               offsetof(relux_spec_accept_args, next_token)); return 0; }
+                               offsetof(relux_spec_accept_args, next_token), sizeof(relux_sample_args),
+                               offsetof(relux_sample_args, prev_tokens), offsetof(relux_sample_args, tokens)); return 0; }
     """)
     with tempfile.TemporaryDirectory() as d:
         c = os.path.join(d, "s.c")
@@ -72,7 +73,8 @@ def test_struct_sizes_match_the_header(so):
     assert sizes == [C.sizeof(so.PoolParams), C.sizeof(so.AppendArgs), C.sizeof(so.AttnArgs), C.sizeof(so.MlaLayerWeights),
                      C.sizeof(so.MlaLayerArgs), C.sizeof(so.GqaLayerWeights), C.sizeof(so.GqaLayerArgs), so.MlaLayerArgs.w.offset,
                      so.GqaLayerArgs.w.offset, C.sizeof(so.SamplerParams), C.sizeof(so.SpecAcceptArgs),
-                     so.SpecAcceptArgs.sampler.offset, so.SpecAcceptArgs.next_token.offset]
+                     so.SpecAcceptArgs.sampler.offset, so.SpecAcceptArgs.next_token.offset, C.sizeof(so.SampleArgs),
+                     so.SampleArgs.prev_tokens.offset, so.SampleArgs.tokens.offset]
 
 
 def test_no_gpu_means_a_clean_error(so):

@@ -163,6 +163,44 @@ def test_small_top_k_is_bit_exact_in_fast_mode(pool, oracle, V):
         assert got.tolist() == want, sampler
 
 
+def test_repetition_penalties_match_the_reference(pool, oracle):
+    """applyRepetitionPenalties (sampler.go:221-266) before the sampler: REFERENCE mode and the small-top-k fast path give
+    the reference's token exactly; the input logits stay untouched."""
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(77)
+    n, V = 12, 4000
+    logits = (rng.standard_normal((n, V)) * 3).astype(np.float32)
+    keep = logits.copy()
+    draws = rng.random(n).astype(np.float32)
+    prev = []
+    for i in range(n):
+        top = np.argsort(-logits[i])[:20]                      # likely tokens, so the penalties change the outcome
+        hist = rng.choice(top, size=rng.integers(0, 90)).tolist()
+        if i == 5:
+            hist += [-3, V + 7]                                  # out-of-range ids are ignored like in the reference
+        prev.append(hist)
+    for pen in (dict(repeat_penalty=1.3), dict(frequency_penalty=0.4, presence_penalty=0.7),
+                dict(repeat_penalty=1.2, frequency_penalty=0.2, presence_penalty=0.3, repeat_window=16)):
+        for sampler in (dict(), dict(top_k=40, top_p=0.9), dict(temperature=0.7, min_p=0.03)):
+            cfg = oracle.sampler_cfg(**sampler, **pen)
+            want = [oracle.sampler_sample(cfg, logits[i], float(draws[i]), prev=prev[i]) for i in range(n)]
+            plain = [oracle.sampler_sample(oracle.sampler_cfg(**sampler), logits[i], float(draws[i])) for i in range(n)]
+            got = pool.sample(logits, draws, mode=L.ATTN_REFERENCE, prev_tokens=prev, **sampler, **pen)
+            assert got.tolist() == want, (pen, sampler)
+            fast = pool.sample(logits, draws, prev_tokens=prev, **sampler, **pen)
+            if sampler.get("top_k"):
+                assert fast.tolist() == want, (pen, sampler)
+            else:
+                for i in range(n):
+                    if fast[i] != want[i]:
+                        _, probs = oracle.sampler_sample(cfg, logits[i], float(draws[i]), prev=prev[i], return_probs=True)
+                        cum = np.cumsum(probs.astype(np.float64))
+                        g = int(fast[i])
+                        assert (cum[g - 1] if g else 0.0) - SUM_TOL <= draws[i] < cum[g] + SUM_TOL
+            assert want != plain                                 # the penalties did change some tokens
+    assert np.array_equal(logits, keep)
+
+
 def test_reference_sampler_properties(pool):
     """The two properties sampler_test.go checks: temperature -> 0 always yields the argmax, top-k 2 only the two
     largest logits."""
