@@ -43,6 +43,7 @@ struct SelParams {
   float temperature;
   int32_t top_k;
   float top_p, min_p;
+  int32_t lookahead;             // accept loop: take the next position's maxima in the pass that sums this one's
 };
 
 // Shared memory of one CTA: exchange slots read by the other CTAs of the cluster.
@@ -669,7 +670,7 @@ __global__ void __launch_bounds__(kSelThreads, 2) spec_accept_kernel(SelParams p
   int n_acc = k;
   bool done = false;
   float next_md = 0.0f, next_mt = 0.0f;
-  if (k > 0) {
+  if (k > 0 && prm.lookahead) {
     float v4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
     for_segment2(c, prm.draft_logits + (size_t)b * k * V, prm.target_logits + (size_t)b * (k + 1) * V,
                  [&](int, float dv, float tv) { v4[0] = fmaxf(v4[0], dv); v4[1] = fmaxf(v4[1], tv); });
@@ -687,16 +688,27 @@ __global__ void __launch_bounds__(kSelThreads, 2) spec_accept_kernel(SelParams p
       done = true;
       break;
     }
-    // The maxima of this position's rows came with the previous position's sums (or from the pass before the loop);
-    // this pass adds up the exponentials and already takes the maxima of the next position's rows, so every draft
-    // position costs one barrier.  When this position rejects, the look-ahead was two rows read in vain.
+    // With look-ahead the maxima of this position's rows came with the previous position's sums (or from the pass
+    // before the loop): the pass below adds up the exponentials and already takes the maxima of the next position's
+    // rows, one barrier per draft position, at the price of two rows read in vain when this position rejects.  That
+    // pays while the chain is bound by latency (few sequences); with many sequences the passes are bound by bytes and
+    // the maxima get a pass of their own.
+    float v4[4];
+    if (!prm.lookahead) {
+      v4[0] = v4[1] = v4[2] = v4[3] = -INFINITY;
+      for_segment2(c, drow, trow, [&](int, float dv, float tv) { v4[0] = fmaxf(v4[0], dv); v4[1] = fmaxf(v4[1], tv); });
+      cluster_reduce4<1>(c, v4);
+      next_md = v4[0];
+      next_mt = v4[1];
+    }
     const float md = next_md, mt = next_mt;
-    float v4[4] = {0.0f, 0.0f, -INFINITY, -INFINITY};
+    v4[0] = v4[1] = 0.0f;
+    v4[2] = v4[3] = -INFINITY;
     for_segment2(c, drow, trow, [&](int, float dv, float tv) {
       v4[0] += fastexp32_ref(__fsub_rn(dv, md));
       v4[1] += fastexp32_ref(__fsub_rn(tv, mt));
     });
-    if (i + 1 < k)
+    if (prm.lookahead && i + 1 < k)
       for_segment2(c, drow + V, trow + V, [&](int, float dv, float tv) { v4[2] = fmaxf(v4[2], dv); v4[3] = fmaxf(v4[3], tv); });
     cluster_reduce4<2>(c, v4);
     next_md = v4[2];
@@ -944,6 +956,8 @@ static int32_t launch_selection(Pool* p, SelParams& prm, int n, const relux_samp
   prm.top_k = sp.top_k;
   prm.top_p = sp.top_p;
   prm.min_p = sp.min_p;
+  prm.lookahead = n <= 32 ? 1 : 0;   // measured: 6 % faster at 4-16 sequences, even at 32, 1 % slower at 64
+  if (const char* e = getenv("RELUX_SEL_LOOKAHEAD")) prm.lookahead = atoi(e) ? 1 : 0;   // tuning override
   if (mode == RELUX_ATTN_REFERENCE) {
     rc = grow(dev, p->part_o, sizeof(float) * 2 * (size_t)n * V);
     if (rc) return rc;
