@@ -7,7 +7,8 @@
 //
 // tests/test_reference_golden_optional.py then compares the CPU oracle (FAITHFUL mode: the reference's behaviour with
 // its cache-layout and position rules as they are) with these outputs bit for bit, which pins the oracle's
-// restatement of MHA.forwardCached and MLA.forwardCached against a real relux run.
+// restatement of MHA.forwardCached and MLA.forwardCached against a real relux run; the "sampler" section does the same
+// for Sampler.Sample (tokens for recorded draws).
 //
 // Everything is generated from one 64-bit LCG so that the Python side can rebuild weights and inputs exactly:
 //
@@ -21,6 +22,7 @@ package transformer
 import (
 	"encoding/json"
 	"math"
+	"math/rand"
 	"os"
 	"testing"
 )
@@ -100,6 +102,40 @@ func TestDumpReluxGolden(t *testing.T) {
 			outs = append(outs, goldenBits(m.Forward(g.tensor(1, 64))))
 		}
 		result["mla"] = map[string]interface{}{"d_model": 64, "heads": 4, "dC": 32, "dHR": 8, "seed": 54321, "outputs_f32_bits": outs}
+	}
+
+	// ---- Sampler.Sample: 6 settings x 8 rows of 500 logits (LCG values * 6), seed 777.  Two generators with the same
+	// seed: one is consumed by Sample, the other records the draw Sample took, so the Python side needs no math/rand. ----
+	{
+		var g goldenLCG = 777
+		settings := []Sampler{
+			{Temperature: 1, TopP: 1},
+			{Temperature: 0.7, TopP: 1},
+			{Temperature: 1, TopK: 40, TopP: 1},
+			{Temperature: 1, TopP: 0.9},
+			{Temperature: 1, TopP: 1, MinP: 0.05},
+			{Temperature: 1.3, TopK: 100, TopP: 0.85, MinP: 0.02, RepeatPenalty: 1.2, FrequencyPenalty: 0.2, PresencePenalty: 0.3, RepeatWindow: 16},
+		}
+		var cases []map[string]interface{}
+		for si := range settings {
+			s := settings[si]
+			s.Rand = rand.New(rand.NewSource(int64(1000 + si)))
+			shadow := rand.New(rand.NewSource(int64(1000 + si)))
+			for row := 0; row < 8; row++ {
+				logits := make([]float32, 500)
+				for i := range logits {
+					logits[i] = g.next() * 6
+				}
+				prev := make([]int, 24)
+				for i := range prev {
+					prev[i] = int((g.next() + 1) * 250)
+				}
+				draw := shadow.Float32()
+				tok := s.Sample(logits, prev)
+				cases = append(cases, map[string]interface{}{"setting": si, "draw_bits": math.Float32bits(draw), "token": tok})
+			}
+		}
+		result["sampler"] = map[string]interface{}{"seed": 777, "vocab": 500, "rows_per_setting": 8, "prev_len": 24, "cases": cases}
 	}
 
 	b, err := json.Marshal(result)

@@ -75,3 +75,41 @@ def test_oracle_matches_a_real_relux_run(oracle, mla):
     for step, (o, gbits) in enumerate(zip(outs, gold)):
         want = np.asarray(gbits, np.uint32).view(np.float32).reshape(o.shape)
         assert np.array_equal(o.view(np.uint32), want.view(np.uint32)), "step %d differs from the relux run" % step
+
+
+SAMPLER_SETTINGS = [
+    dict(), dict(temperature=0.7), dict(top_k=40), dict(top_p=0.9), dict(min_p=0.05),
+    dict(temperature=1.3, top_k=100, top_p=0.85, min_p=0.02, repeat_penalty=1.2, frequency_penalty=0.2, presence_penalty=0.3,
+         repeat_window=16),
+]
+
+
+def _sampler_inputs():
+    """Logits and token histories of the dumper's sampler section, in its order of draws."""
+    g = LCG(777)
+    rows = []
+    for si in range(len(SAMPLER_SETTINGS)):
+        for _ in range(8):
+            logits = g.take(500) * np.float32(6)
+            prev = ((g.take(24) + np.float32(1)) * np.float32(250)).astype(np.int64)
+            rows.append((si, logits, prev))
+    return rows
+
+
+def test_sampler_harness_runs(oracle):
+    rows = _sampler_inputs()
+    assert len(rows) == 48
+    for si, logits, prev in rows[::7]:
+        tok = oracle.sampler_sample(oracle.sampler_cfg(**SAMPLER_SETTINGS[si]), logits, 0.5, prev=prev)
+        assert 0 <= tok < 500 and prev.min() >= 0 and prev.max() < 500
+
+
+def test_oracle_sampler_matches_a_real_relux_run(oracle):
+    if not os.path.exists(GOLD) or "sampler" not in json.load(open(GOLD)):
+        pytest.skip("no sampler section in tests/golden/relux_go_golden.json (produced by relux_golden_dump_test.go with Go)")
+    cases = json.load(open(GOLD))["sampler"]["cases"]
+    for (si, logits, prev), case in zip(_sampler_inputs(), cases):
+        assert case["setting"] == si
+        draw = float(np.asarray([case["draw_bits"]], np.uint32).view(np.float32)[0])
+        tok = oracle.sampler_sample(oracle.sampler_cfg(**SAMPLER_SETTINGS[si]), logits, draw, prev=prev)
+        assert tok == case["token"], "setting %d: oracle %d, relux %d" % (si, tok, case["token"])
