@@ -93,6 +93,7 @@ SAMPLERS = [
     dict(top_p=0.9),
     dict(min_p=0.05),
     dict(temperature=1.3, top_k=100, top_p=0.85, min_p=0.02),
+    dict(top_k=300, top_p=0.9),                 # above the list path's limit: top-k by the full radix walk
 ]
 
 
@@ -199,6 +200,54 @@ def test_repetition_penalties_match_the_reference(pool, oracle):
                         assert (cum[g - 1] if g else 0.0) - SUM_TOL <= draws[i] < cum[g] + SUM_TOL
             assert want != plain                                 # the penalties did change some tokens
     assert np.array_equal(logits, keep)
+
+
+def _within_cdf(oracle, cfg, logits_row, draw, got, prev=None):
+    _, probs = oracle.sampler_sample(cfg, logits_row, float(draw), prev=prev, return_probs=True)
+    cum = np.cumsum(probs.astype(np.float64))
+    g = int(got)
+    return (cum[g - 1] if g else 0.0) - SUM_TOL <= draw < cum[g] + SUM_TOL
+
+
+def test_more_ties_than_the_list_holds(pool, oracle):
+    """A plateau of 1500 equal logits at the top with top-k 50: the reference keeps every tie (it masks only what is
+    strictly below the k-th largest), the list path cannot hold them and hands over to the pass-per-step path."""
+    rng = np.random.default_rng(21)
+    n, V = 8, 20000
+    logits = (rng.standard_normal((n, V)) * 2).astype(np.float32)
+    for i in range(n):
+        logits[i, rng.choice(V, 1500, replace=False)] = 9.5
+    draws = rng.random(n).astype(np.float32)
+    cfg = oracle.sampler_cfg(top_k=50)
+    got = pool.sample(logits, draws, top_k=50)
+    for i in range(n):
+        assert logits[i, got[i]] == np.float32(9.5)
+        assert _within_cdf(oracle, cfg, logits[i], draws[i], got[i])
+
+
+def test_randomised_shapes_and_settings(pool, oracle):
+    """Seeded random vocabularies (aligned and not), batch sizes, draft lengths and sampler settings against the
+    restatement, with the summation-order criterion of this file."""
+    rng = np.random.default_rng(2024)
+    exact = []
+    for trial in range(10):
+        V = int(rng.choice([257, 1000, 3001, 8192, 20011, 65536]))
+        n = int(rng.integers(1, 40))
+        k = int(rng.integers(1, 7))
+        sampler = {}
+        if rng.random() < 0.5:
+            sampler["temperature"] = float(rng.choice([0.5, 0.9, 1.5]))
+        if rng.random() < 0.6:
+            sampler["top_k"] = int(rng.choice([1, 8, 64, 128, 129, 500]))
+        if rng.random() < 0.5:
+            sampler["top_p"] = float(rng.choice([0.3, 0.8, 0.97]))
+        if rng.random() < 0.3:
+            sampler["min_p"] = float(rng.choice([0.01, 0.2]))
+        toks, dl, tl, draws = make_case(rng, n, k, V, noise=float(rng.choice([0.0, 0.3, 1.0])))
+        cfg = oracle.sampler_cfg(**sampler)
+        n_acc, nxt = pool.spec_accept(n, k, V, toks, dl, tl, draws, **sampler)
+        exact.append(check_fast(oracle, cfg, toks, dl, tl, draws, n_acc, nxt))
+    assert np.mean(exact) > 0.9
 
 
 def test_reference_sampler_properties(pool):
