@@ -328,7 +328,8 @@ int32_t relux_gqa_forward_cached(relux_pool_t pool, const relux_gqa_layer_args* 
  * the sequence (the reference's startPos += nAccepted + 1, speculative.go:155).
  * RELUX_ATTN_FAST: one thread-block cluster per sequence, parallel float32 sums -- a decision can differ from the
  * reference's only when a draw lies within rounding distance of a boundary.  RELUX_ATTN_REFERENCE: the reference's
- * sequential float32 order, bit-exact, one thread per sequence.
+ * sequential float32 order, bit-exact, one thread per sequence (meant for parity checks: with the nucleus filter on it
+ * is quadratic in the vocabulary like the reference's selection sort, and returns RELUX_ERR_UNSUPPORTED above 32768).
  * Errors: RELUX_ERR_INVALID_ARG for a draft token outside [0, vocab) (the reference would panic on the index). */
 typedef struct relux_sampler_params {
   float temperature;        /* <= 0 is replaced by 1e-5 (sampler.go:90-93) */

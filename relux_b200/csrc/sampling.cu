@@ -959,6 +959,15 @@ static int32_t launch_selection(Pool* p, SelParams& prm, int n, const relux_samp
   prm.lookahead = n <= 32 ? 1 : 0;   // measured: 6 % faster at 4-16 sequences, even at 32, 1 % slower at 64
   if (const char* e = getenv("RELUX_SEL_LOOKAHEAD")) prm.lookahead = atoi(e) ? 1 : 0;   // tuning override
   if (mode == RELUX_ATTN_REFERENCE) {
+    // One thread per sequence repeats the reference's selection sorts: quadratic in the vocabulary for the nucleus cut,
+    // top_k x vocabulary for kthLargest.  Refuse sizes that would keep the device busy for many seconds.
+    const bool nucleus = sp.top_p > 0.0f && sp.top_p < 1.0f;
+    const bool topk = sp.top_k > 0 && sp.top_k < V;
+    if ((nucleus && V > 32768) || (topk && (double)sp.top_k * V > 1e9)) {
+      set_error("RELUX_ATTN_REFERENCE repeats the reference's O(vocab^2) sorts on one thread per sequence: vocab %d with these "
+                "filters is outside what it is meant for (parity checks); use RELUX_ATTN_FAST", V);
+      return RELUX_ERR_UNSUPPORTED;
+    }
     rc = grow(dev, p->part_o, sizeof(float) * 2 * (size_t)n * V);
     if (rc) return rc;
     rc = grow(dev, p->part_ml, sizeof(int32_t) * (size_t)n * V);

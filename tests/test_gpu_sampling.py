@@ -311,6 +311,18 @@ def test_draft_token_outside_vocabulary_is_an_error(dev, pool):
             b.free()
 
 
+def test_reference_mode_refuses_sizes_it_is_not_meant_for(pool, oracle):
+    from relux_b200 import lib as L
+    logits = np.zeros((1, 40000), np.float32)
+    draws = np.asarray([0.5], np.float32)
+    with pytest.raises(L.ReluxCudaError) as e:
+        pool.sample(logits, draws, top_p=0.9, mode=L.ATTN_REFERENCE)
+    assert e.value.code == L.ERR_UNSUPPORTED
+    # without the quadratic filters the same vocabulary is fine
+    want = oracle.sampler_sample(oracle.sampler_cfg(), logits[0], 0.5)
+    assert pool.sample(logits, draws, mode=L.ATTN_REFERENCE).tolist() == [want]
+
+
 def test_full_size_properties(dev, pool):
     """Vocabulary of 131072 (a cluster of eight CTAs per sequence), 64 sequences, four draft tokens: a draft equal to the
     target is accepted whole, and a near-zero temperature turns the bonus token into the argmax of the last row."""
