@@ -12,6 +12,7 @@
 //     split-KV partial; merge_splits_kernel combines the chunks of a sequence.
 // All mbarrier waits are bounded; a wait that runs out records RELUX_ERR_TIMEOUT and the CTA leaves.
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 #include <vector>
 #include "common.cuh"
@@ -43,6 +44,10 @@ struct GqaParams {
   float* part_ml;
   int32_t rows_total;  // S * H
   int32_t q_tokens_total, q_token0;   // the S query tokens of this launch are tokens [q_token0, q_token0 + S) of a call with q_tokens_total
+  // Grouped launch (a prompt): grid.z slices the call's query tokens into groups of group_tokens; slice z handles tokens
+  // [(group0 + z) * group_tokens, ...) and S, R, extra above describe the whole call.  0 = one group, described by S / R / extra.
+  int32_t group_tokens, group0;
+  int64_t part_group_rows;            // partial rows (work items x rows_total) between two slices
   int32_t* status;
 };
 
@@ -59,8 +64,19 @@ __global__ void __launch_bounds__(160, 1) gqa_decode_kernel(const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const WorkItem item = prm.items[blockIdx.x];
   const int kvh = blockIdx.y;
-  const int T = prm.len[item.seq] + prm.extra;
-  const int npages = item.page_end - item.page_begin;
+  int S = prm.S, R = prm.R, extra = prm.extra, q_token0 = prm.q_token0;
+  size_t part_row0 = 0;
+  if (prm.group_tokens) {
+    // With the causal mask a group of tokens sees the cache as if it ended with its own last token.
+    q_token0 = (prm.group0 + (int)blockIdx.z) * prm.group_tokens;
+    S = min(prm.group_tokens, prm.q_tokens_total - q_token0);
+    R = S * prm.g;
+    if (prm.causal) extra = prm.extra - (prm.q_tokens_total - q_token0 - S);
+    part_row0 = (size_t)blockIdx.z * (size_t)prm.part_group_rows;
+  }
+  const int T = prm.len[item.seq] + extra;
+  // pages of this chunk that hold tokens below T (a later group's chunk can lie wholly past an earlier group's end)
+  const int npages = max(0, min(item.page_end - item.page_begin, (T - item.page_begin * kPageTok + kPageTok - 1) / kPageTok));
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; s++) {
@@ -73,9 +89,9 @@ __global__ void __launch_bounds__(160, 1) gqa_decode_kernel(const __grid_constan
   for (int e = threadIdx.x; e < 16 * MT * (kD / 2); e += blockDim.x) {
     const int r = e / (kD / 2), c = (e % (kD / 2)) * 2;
     uint32_t w = 0;
-    if (r < prm.R) {
+    if (r < R) {
       const int s = r / prm.g, hq = r % prm.g;
-      const size_t off = (((size_t)item.seq_index * prm.q_tokens_total + prm.q_token0 + s) * prm.H + (size_t)kvh * prm.g + hq) * kD + c;
+      const size_t off = (((size_t)item.seq_index * prm.q_tokens_total + q_token0 + s) * prm.H + (size_t)kvh * prm.g + hq) * kD + c;
       if (prm.q_bf16) w = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(prm.q) + off);
       else {
         float2 f = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(prm.q) + off);
@@ -173,14 +189,14 @@ __global__ void __launch_bounds__(160, 1) gqa_decode_kernel(const __grid_constan
     }
     // scale to the log2 domain, mask the tail of the sequence and the causal part of the draft
     const int tok0 = (item.page_begin + it) * kPageTok + tb;
-    const bool need_mask = (tok0 + 16 > T - (prm.causal ? prm.S : 0));
+    const bool need_mask = (tok0 + 16 > T - (prm.causal ? S : 0));
     uint32_t pa[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) {
 #pragma unroll
       for (int hf = 0; hf < 2; hf++) {
         const int row = mt * 16 + hf * 8 + (lane >> 2);
-        const int limit = prm.causal ? (T - prm.S + row / prm.g) : (T - 1);  // last visible token
+        const int limit = prm.causal ? (T - S + row / prm.g) : (T - 1);  // last visible token
         float mx = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < 2; nt++)
@@ -265,7 +281,7 @@ __global__ void __launch_bounds__(160, 1) gqa_decode_kernel(const __grid_constan
     }
   asm volatile("bar.sync 1, 128;" ::: "memory");
   const int d = threadIdx.x;  // 128 consumer threads, one output dim each
-  for (int r = 0; r < prm.R; r++) {
+  for (int r = 0; r < R; r++) {
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kConsumerWarps; w++) M = fmaxf(M, mb[((size_t)w * 16 * MT + r) * kMStride + kD]);
@@ -278,7 +294,7 @@ __global__ void __launch_bounds__(160, 1) gqa_decode_kernel(const __grid_constan
       O += src[d] * f;
     }
     const int s = r / prm.g, hq = r % prm.g;
-    const size_t grow = (size_t)blockIdx.x * prm.rows_total + (size_t)s * prm.H + (size_t)kvh * prm.g + hq;
+    const size_t grow = part_row0 + (size_t)blockIdx.x * prm.rows_total + (size_t)s * prm.H + (size_t)kvh * prm.g + hq;
     prm.part_o[grow * kD + d] = O;
     if (d == 0) {
       prm.part_ml[grow * 2] = M;
@@ -309,7 +325,7 @@ static int32_t launch_gqa_group(Pool* p, const SeqBatch& sb, const relux_attn_ar
   if (rc) return rc;
   rc = grow(p->dev, p->part_ml, (size_t)plan.num_items * rows_total * 2 * sizeof(float));
   if (rc) return rc;
-  GqaParams k;
+  GqaParams k{};
   k.items = plan.items;
   k.table = p->d_table;
   k.table_stride = prm.max_pages_per_seq;
@@ -353,6 +369,82 @@ static int32_t launch_gqa_group(Pool* p, const SeqBatch& sb, const relux_attn_ar
   return launch_merge_rows(p, plan, sb.n_seqs, rows_total, kD, (float*)d_out, a.q_tokens * a.num_heads, s0 * a.num_heads);
 }
 
+// A multi-token call longer than one group (a prompt): one work list for the whole call, the groups of `per_group`
+// query tokens as z slices of the decode grid and of the merge grid.  Slice z sees the cache as if it ended with its own
+// last token (causal), so its chunks past that point load nothing and leave neutral partials.  The partials of all
+// slices of a launch are alive at once; launches are cut so that they stay within 256 MiB.
+static int32_t launch_gqa_prompt(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, void* d_out, int per_group) {
+  const relux_pool_params& prm = p->prm;
+  const int g = a.num_heads / prm.gqa_num_kv_heads;
+  const int groups = (a.q_tokens + per_group - 1) / per_group;
+  // every work item becomes groups x kv heads CTAs, so the planner may keep the chunks long: a prompt fills the SMs
+  // through its slices, and a CTA that streams many pages amortises its prologue
+  SplitPlan plan;
+  int32_t rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, prm.gqa_num_kv_heads * groups, 2, 1, 0, &plan);
+  if (rc) return rc;
+  const int rows_total = per_group * a.num_heads;
+  const size_t group_rows = (size_t)plan.num_items * rows_total;
+  const size_t group_bytes = group_rows * kD * sizeof(float);
+  size_t budget = (size_t)256 << 20;
+  if (const char* e = getenv("RELUX_GQA_PROMPT_PARTIAL_MB")) budget = (size_t)std::max(1, atoi(e)) << 20;   // tuning / test aid
+  const int zmax = (int)std::max<size_t>(1, std::min<size_t>({(size_t)groups, (size_t)65535, budget / std::max<size_t>(1, group_bytes)}));
+  rc = grow(p->dev, p->part_o, (size_t)zmax * group_bytes);
+  if (rc) return rc;
+  rc = grow(p->dev, p->part_ml, (size_t)zmax * group_rows * 2 * sizeof(float));
+  if (rc) return rc;
+  GqaParams k{};
+  k.items = plan.items;
+  k.table = p->d_table;
+  k.table_stride = prm.max_pages_per_seq;
+  k.len = p->d_len + (size_t)a.layer * prm.max_seqs;
+  k.num_pages = prm.num_pages;
+  k.Hkv = prm.gqa_num_kv_heads;
+  k.H = a.num_heads;
+  k.g = g;
+  k.S = a.q_tokens;                 // the whole call; every slice derives its own S, R and extra
+  k.R = per_group * g;
+  k.extra = a.extra_tokens;
+  k.causal = a.causal;
+  k.q_tokens_total = a.q_tokens;
+  k.q_token0 = 0;
+  k.group_tokens = per_group;
+  k.part_group_rows = (int64_t)group_rows;
+  const int64_t rows_per_block = (int64_t)prm.num_pages * prm.gqa_num_kv_heads * kPageTok;
+  k.krow0 = (int32_t)((int64_t)a.layer * 2 * rows_per_block);
+  k.vrow0 = (int32_t)((int64_t)a.layer * 2 * rows_per_block + rows_per_block);
+  k.scale_log2 = a.scale * 1.4426950408889634f;
+  k.q = d_q;
+  k.q_bf16 = a.q_dtype == RELUX_DTYPE_BF16;
+  k.part_o = (float*)p->part_o.p;
+  k.part_ml = (float*)p->part_ml.p;
+  k.rows_total = rows_total;
+  k.status = p->d_status;
+  cudaStream_t st = p->dev->stream;
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), st));
+  for (int z0 = 0; z0 < groups; z0 += zmax) {
+    const int nz = std::min(zmax, groups - z0);
+    k.group0 = z0;
+    dim3 grid(plan.num_items, prm.gqa_num_kv_heads, nz);
+    if (per_group * g <= 16) {
+      constexpr size_t smem = gqa_smem_bytes<1>();
+      RELUX_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      gqa_decode_kernel<1><<<grid, 160, smem, st>>>(p->tmap_gqa, k);
+    } else {
+      constexpr size_t smem = gqa_smem_bytes<2>();
+      RELUX_CUDA_TRY(cudaFuncSetAttribute(gqa_decode_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      gqa_decode_kernel<2><<<grid, 160, smem, st>>>(p->tmap_gqa, k);
+    }
+    RELUX_CUDA_TRY(cudaGetLastError());
+    count_launch(p->dev);
+    rc = launch_merge_rows(p, plan, sb.n_seqs, rows_total, kD, (float*)d_out, a.q_tokens * a.num_heads, z0 * rows_total, nz,
+                           (long long)group_rows);
+    if (rc) return rc;
+  }
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), st));
+  p->timed_calls++;
+  return RELUX_OK;
+}
+
 int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, void* d_out) {
   const relux_pool_params& prm = p->prm;
   const int g = a.num_heads / prm.gqa_num_kv_heads;
@@ -363,13 +455,17 @@ int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
     return RELUX_ERR_UNSUPPORTED;
   }
   // the kernel holds (num_heads / num_kv_heads) * q_tokens <= 32 query rows per kv head; longer multi-token calls
-  // (a prompt) run as consecutive groups of tokens
+  // (a prompt) are cut into groups of tokens that run as the z slices of one grid
   const int per_group = std::max(1, 32 / g);
-  for (int s0 = 0; s0 < a.q_tokens; s0 += per_group) {
-    int32_t rc = launch_gqa_group(p, sb, a, d_q, d_out, s0, std::min(per_group, a.q_tokens - s0));
-    if (rc) return rc;
+  if (a.q_tokens <= per_group) return launch_gqa_group(p, sb, a, d_q, d_out, 0, a.q_tokens);
+  if (getenv("RELUX_GQA_PROMPT_SERIAL")) {   // measurement aid: one launch per group, as before the grouped launch existed
+    for (int s0 = 0; s0 < a.q_tokens; s0 += per_group) {
+      int32_t rc = launch_gqa_group(p, sb, a, d_q, d_out, s0, std::min(per_group, a.q_tokens - s0));
+      if (rc) return rc;
+    }
+    return RELUX_OK;
   }
-  return RELUX_OK;
+  return launch_gqa_prompt(p, sb, a, d_q, d_out, per_group);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -496,7 +592,7 @@ extern "C" __attribute__((visibility("default"))) int32_t relux_gqa_decode_noall
   rc = launch_build_worklist_raw(st, len, sb.d_seq_ids, sb.n_seqs, a->extra_tokens, prm.page_tokens, chunk, d_items, d_chunk_off);
   if (rc) return rc;
   count_launch(dev);
-  GqaParams k;
+  GqaParams k{};
   k.items = d_items;
   k.table = p->d_table;
   k.table_stride = prm.max_pages_per_seq;

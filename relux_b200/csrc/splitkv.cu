@@ -289,22 +289,26 @@ namespace relux {
 // covers only some of a call's query tokens).
 __global__ void merge_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const int32_t* __restrict__ chunk_off, int rows, int width, float* __restrict__ out,
-                                    uint16_t* __restrict__ out_bf16, int out_rows, int out_row0) {
+                                    uint16_t* __restrict__ out_bf16, int out_rows, int out_row0, long long part_group_rows) {
+  // grid.z > 1: slices of a grouped launch, `rows` output rows and part_group_rows partial rows apart
   const int r = blockIdx.x, i = blockIdx.y;
+  out_row0 += (int)blockIdx.z * rows;
+  if (out_row0 + r >= out_rows) return;      // the last group of a prompt may be short
+  const size_t z0 = (size_t)blockIdx.z * (size_t)part_group_rows;
   const int c0 = chunk_off[i], c1 = chunk_off[i + 1];
   float M = -INFINITY;
-  for (int c = c0; c < c1; c++) M = fmaxf(M, part_ml[((size_t)c * rows + r) * 2]);
+  for (int c = c0; c < c1; c++) M = fmaxf(M, part_ml[(z0 + (size_t)c * rows + r) * 2]);
   float L = 0.f;
   for (int c = c0; c < c1; c++) {
-    const float* ml = part_ml + ((size_t)c * rows + r) * 2;
+    const float* ml = part_ml + (z0 + (size_t)c * rows + r) * 2;
     L += ml[1] * exp2f(ml[0] - M);
   }
   const float inv = (L > 0.f) ? 1.0f / L : 0.f;
   for (int d = threadIdx.x; d < width; d += blockDim.x) {
     float acc = 0.f;
     for (int c = c0; c < c1; c++) {
-      const float m = part_ml[((size_t)c * rows + r) * 2];
-      acc += part_o[((size_t)c * rows + r) * width + d] * exp2f(m - M);
+      const float m = part_ml[(z0 + (size_t)c * rows + r) * 2];
+      acc += part_o[(z0 + (size_t)c * rows + r) * width + d] * exp2f(m - M);
     }
     const size_t o = ((size_t)i * out_rows + out_row0 + r) * width + d;
     if (out) out[o] = acc * inv;
@@ -315,16 +319,17 @@ __global__ void merge_splits_kernel(const float* __restrict__ part_o, const floa
 int32_t launch_merge(Pool* p, const SplitPlan& plan, int n_seqs, int rows, int width, float* out, uint16_t* out_bf16) {
   dim3 grid(rows, n_seqs);
   merge_splits_kernel<<<grid, 128, 0, p->dev->stream>>>((const float*)p->part_o.p, (const float*)p->part_ml.p, plan.chunk_off, rows,
-                                                        width, out, out_bf16, rows, 0);
+                                                        width, out, out_bf16, rows, 0, 0);
   RELUX_CUDA_TRY(cudaGetLastError());
   count_launch(p->dev);
   return RELUX_OK;
 }
 
-int32_t launch_merge_rows(Pool* p, const SplitPlan& plan, int n_seqs, int rows, int width, float* out, int out_rows, int out_row0) {
-  dim3 grid(rows, n_seqs);
+int32_t launch_merge_rows(Pool* p, const SplitPlan& plan, int n_seqs, int rows, int width, float* out, int out_rows, int out_row0,
+                          int slices, long long part_group_rows) {
+  dim3 grid(rows, n_seqs, slices);
   merge_splits_kernel<<<grid, 128, 0, p->dev->stream>>>((const float*)p->part_o.p, (const float*)p->part_ml.p, plan.chunk_off, rows,
-                                                        width, out, nullptr, out_rows, out_row0);
+                                                        width, out, nullptr, out_rows, out_row0, part_group_rows);
   RELUX_CUDA_TRY(cudaGetLastError());
   count_launch(p->dev);
   return RELUX_OK;
@@ -340,7 +345,7 @@ int32_t launch_build_worklist_raw(cudaStream_t st, const int32_t* len, const int
 int32_t launch_merge_raw(cudaStream_t st, const float* part_o, const float* part_ml, const int32_t* chunk_off, int n_seqs, int rows,
                          int width, float* out) {
   dim3 grid(rows, n_seqs);
-  merge_splits_kernel<<<grid, 128, 0, st>>>(part_o, part_ml, chunk_off, rows, width, out, nullptr, rows, 0);
+  merge_splits_kernel<<<grid, 128, 0, st>>>(part_o, part_ml, chunk_off, rows, width, out, nullptr, rows, 0, 0);
   RELUX_CUDA_TRY(cudaGetLastError());
   return RELUX_OK;
 }

@@ -49,6 +49,7 @@ int32_t launch_merge_raw(cudaStream_t st, const float* part_o, const float* part
                          int width, float* out);
 int32_t launch_merge(Pool* p, const SplitPlan& plan, int n_seqs, int rows, int width, float* out, uint16_t* out_bf16);
 // Same, for a launch that covers `rows` of the `out_rows` output rows of every sequence, starting at row out_row0.
-int32_t launch_merge_rows(Pool* p, const SplitPlan& plan, int n_seqs, int rows, int width, float* out, int out_rows, int out_row0);
+int32_t launch_merge_rows(Pool* p, const SplitPlan& plan, int n_seqs, int rows, int width, float* out, int out_rows, int out_row0,
+                          int slices = 1, long long part_group_rows = 0);
 
 }  // namespace relux
