@@ -173,6 +173,32 @@ class KVCache {
     a.w = &w;
     check(relux_gqa_forward_cached(pool_, &a));
   }
+  // Sampler.Sample (internal/transformer/sampler.go:73-218) on one row of logits: `draw` is the uniform number the
+  // reference would take from its generator; previousTokens / nPrevious as in the reference (nullptr: no repetition
+  // control).  Uses this cache's pool for the device work; the cache itself is not touched.
+  int Sample(const float* logits, int vocab, float draw, const relux_sampler_params& sampling, const int32_t* previousTokens = nullptr,
+             int nPrevious = 0, float repeatPenalty = 0.f, float frequencyPenalty = 0.f, float presencePenalty = 0.f, int repeatWindow = 0,
+             int mode = RELUX_ATTN_FAST) {
+    relux_sample_args a{};
+    int32_t tok = -1, len = nPrevious;
+    a.n_rows = 1;
+    a.vocab = vocab;
+    a.mem = RELUX_MEM_HOST;
+    a.mode = mode;
+    a.logits = logits;
+    a.draws = &draw;
+    a.sampler = sampling;
+    a.repeat_penalty = repeatPenalty;
+    a.frequency_penalty = frequencyPenalty;
+    a.presence_penalty = presencePenalty;
+    a.repeat_window = repeatWindow;
+    a.prev_tokens = previousTokens;
+    a.prev_len = previousTokens ? &len : nullptr;
+    a.prev_stride = nPrevious;
+    a.tokens = &tok;
+    check(relux_sampler_sample(pool_, &a));
+    return tok;
+  }
   // SpeculativeDecoder.acceptPhase (speculative.go:211-253) for this cache's sequence: draftLogits [k][vocab],
   // targetLogits [k + 1][vocab], draws [k + 1] = the uniform numbers the reference would take from its generator, in
   // order.  Returns the number of accepted draft tokens, *resampled receives the resampled / bonus token.  commit:

@@ -147,6 +147,14 @@ int main() {
     int tok = -1;
     int n = c.AcceptPhase(toks, dl.data(), tl.data(), k, V, draws, sp, &tok);
     EXPECT(n == k && tok == best && c.TotalLen(0) == k + 1, "AcceptPhase accepts an identical draft and commits k + 1 rows");
+    // Sampler.Sample through the mirror: near-zero temperature is the argmax; a presence penalty on the argmax moves it
+    int32_t prevTok[2] = {best, best};
+    relux_sampler_params greedy{1e-10f, 0, 1.0f, 0.0f};
+    const float* last = tl.data() + (size_t)k * V;
+    int second = best == 0 ? 1 : 0;
+    for (int j = 0; j < V; j++) if (j != best && last[j] > last[second]) second = j;
+    EXPECT(c.Sample(last, V, 0.4f, greedy) == best, "Sample at temperature -> 0 is the argmax");
+    EXPECT(c.Sample(last, V, 0.4f, greedy, prevTok, 2, 0.f, 0.f, 100.f) == second, "a presence penalty removes the seen argmax");
     tl[toks[0]] = -90.f;
     n = c.AcceptPhase(toks, dl.data(), tl.data(), k, V, draws, sp, &tok, false);
     EXPECT(n == 0 && tok != toks[0] && tok >= 0 && tok < V && c.TotalLen(0) == k + 1, "AcceptPhase rejects a token the target excludes");
