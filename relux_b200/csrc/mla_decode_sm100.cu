@@ -513,8 +513,13 @@ int mla_sm100_workers(Pool* p, int q_tokens) {
     if (const char* ov = getenv("RELUX_MLA_WORKERS")) n = std::max(1, atoi(ov));   // tuning aid
     max_clusters = n;
   }
-  const int sx = q_tokens <= kMaxInterleavedQ ? q_tokens : 1;
-  return std::max(1, max_clusters / sx);
+  if (q_tokens > kMaxInterleavedQ) {
+    // A long multi-token call (a prompt) has one row of workers per query token: the rows already fill the device, so a
+    // row needs only enough workers for about two waves in total, and each worker walks a long piece of the stream
+    // (2048 tokens, one sequence: 3.2 ms with a full row of workers per token, 0.94 ms with one).
+    return std::min(max_clusters, std::max(1, (2 * max_clusters + q_tokens - 1) / q_tokens));
+  }
+  return std::max(1, max_clusters / q_tokens);
 }
 
 int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const SplitPlan& plan, const uint16_t* q_abs) {
