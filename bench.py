@@ -49,6 +49,9 @@ WORKLOADS = {
     "spec_accept_b64_k4_v128k": dict(kind="accept", B=64, k=4, V=131072),
     # smaller case for profiler captures (151 MB of logits, still larger than L2)
     "spec_accept_b32_k4_v128k": dict(kind="accept", B=32, k=4, V=131072),
+    # prompt processing through the decode kernels (a multi-token cached call on an empty cache): 8 sequences x 2048 tokens
+    "gqa_prompt_b8_2k": dict(kind="prompt", pool="gqa", B=8, S=2048, H=32, Hkv=8, D=128),
+    "mla_prompt_b4_1k": dict(kind="prompt", pool="mla", B=4, S=1024, H=128, Dh=128, dC=512, dHR=64),
     "gqa_layer_verify_b128_ctx8k": dict(kind="gqa", B=128, ctx=8192, H=32, Hkv=8, D=128, S=4, layer=True),
 }
 # dram__bytes_read + dram__bytes_write of the dominant kernel divided by its algorithmic bytes, from the ncu captures
@@ -507,6 +510,127 @@ def run_gqa(args, w, world, rank, local, dist):
 _CPU_INPUTS = {}   # inputs of the CPU legs, kept between steps of the reference arm
 
 
+def run_prompt(args, w, world, rank, local, dist):
+    """Prompt processing: every step empties the sequences, appends the S prompt rows and runs one causal multi-token
+    attention call over them (device-resident inputs).  There is no dedicated prefill kernel: the decode kernels take
+    the prompt in groups of query tokens, so the bound reported is the tensor pipe (2 * 2 * S^2 / 2 * H * D flop per
+    sequence for GQA, 2 * S^2 / 2 * H * (2 dC + dHR) for absorbed MLA), not HBM."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+
+    B, S, H = w["B"], w["S"], w["H"]
+    mla = w["pool"] == "mla"
+    dev = rb.Device(local)
+    rng = np.random.default_rng(7 + rank)
+    pages = (S + PAGE - 1) // PAGE + 1
+    if mla:
+        dC, dHR, Dh = w["dC"], w["dHR"], w["Dh"]
+        pool = rb.Pool(dev, L.POOL_MLA, 1, B * pages, PAGE, B, pages, dC=dC, dHR=dHR)
+        rows_a = dev.upload(bf16_bits(rng.standard_normal((B * S, dC), dtype=np.float32)))
+        rows_b = dev.upload(bf16_bits(rng.standard_normal((B * S, dHR), dtype=np.float32)))
+        q = dev.upload(bf16_bits(rng.standard_normal((B, S, H, Dh), dtype=np.float32)))
+        qr = dev.upload(bf16_bits(rng.standard_normal((B, S, H, dHR), dtype=np.float32)))
+        wuk = dev.upload(bf16_bits(rng.standard_normal((dC, H * Dh), dtype=np.float32) * np.float32(0.02)))
+        wuv = dev.upload(bf16_bits(rng.standard_normal((dC, H * Dh), dtype=np.float32) * np.float32(0.02)))
+        out = dev.alloc(B * S * H * Dh * 4, L.DTYPE_F32)
+        scale = float(1.0 / np.sqrt(Dh + dHR))
+        flops = B * (S * (S + 1) / 2) * H * 2 * (2 * dC + dHR)
+        kw = dict(q_rope=qr, w_uk=wuk, w_uv=wuv)
+        head_dim = Dh
+    else:
+        Hkv, D = w["Hkv"], w["D"]
+        pool = rb.Pool(dev, L.POOL_GQA, 1, B * pages, PAGE, B, pages, num_kv_heads=Hkv, head_dim=D)
+        rows_a = dev.upload(bf16_bits(rng.standard_normal((B * S, Hkv, D), dtype=np.float32)))
+        rows_b = dev.upload(bf16_bits(rng.standard_normal((B * S, Hkv, D), dtype=np.float32)))
+        q = dev.upload(bf16_bits(rng.standard_normal((B, S, H, D), dtype=np.float32)))
+        out = dev.alloc(B * S * H * D * 4, L.DTYPE_F32)
+        scale = float(1.0 / np.sqrt(D))
+        flops = B * (S * (S + 1) / 2) * H * 2 * 2 * D
+        kw = {}
+        head_dim = D
+    pool.set_tables(rng.permutation(B * pages).astype(np.int32).reshape(B, pages))
+    zeros, n_new = np.zeros(B, np.int32), np.full(B, S, np.int32)
+
+    def step():
+        pool.set_len(-1, zeros)
+        pool.append(0, rows_a, rows_b, B, n_new=n_new)
+        pool.decode(0, B, q, out, H, head_dim, scale, q_tokens=S, causal=True, **kw)
+
+    steps, warmup = min(args.steps, 200), args.warmup
+    for _ in range(warmup):
+        step()
+    dev.sync()
+    barrier(dist)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+        sampler.begin()
+    n0 = dev.launch_count()
+    e0, e1 = dev.event(), dev.event()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    dev.sync()
+    ms = max_over_ranks(dist, e0.elapsed_ms(e1))
+    launches = dev.launch_count() - n0
+    clocks = sampler.finish() if rank == 0 else None
+    kernel_ms, counted = pool.mean_kernel_ms(steps)
+    assert pool.status() == 0, "device status word is set"
+    pk = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks = json.load(open(pk)) if os.path.exists(pk) else {}
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    achieved = flops / (kernel_ms * 1e-3) / 1e12
+    line = {
+        "metric": "prompt_tokens_per_s", "value": B * S * world * steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "batch_per_gpu": B, "prompt_tokens": S, "heads": H,
+                   "l2": "every step rewrites and re-reads %.1f MB of cache rows; the flush between steps is the append itself"
+                         % ((B * S * ((w["dC"] + w["dHR"]) if mla else 2 * w["Hkv"] * w["D"]) * 2) / 1e6)},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                     "peak_source": "measured" if peaks else "fallback", "kernel": "mla_decode_sm100_kernel" if mla else "gqa_decode_kernel",
+                     "kernel_ms": kernel_ms, "launches_timed": counted, "algorithmic_flops_per_launch": flops},
+        "e2e": None, "gpu_launches": launches, "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.skip_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline_prompt(w)
+    pool.destroy()
+    dev.close()
+    return line
+
+
+def cpu_baseline_prompt(w, threads=1, sample_S=None):
+    """The CPU restatement on ONE sequence with a prompt of sample_S tokens (the cost grows with the square of the
+    prompt length, so the figure belongs to that length)."""
+    from oracle import binding as ob
+    rng = np.random.default_rng(7)
+    H = w["H"]
+    if sample_S is None:
+        sample_S = 96 if w["pool"] == "mla" else 512     # a few seconds each
+    if w["pool"] == "mla":
+        dC, dHR, Dh = w["dC"], w["dHR"], w["Dh"]
+        c = bf16_bits(rng.standard_normal((1, sample_S, dC), dtype=np.float32))
+        r = bf16_bits(rng.standard_normal((1, sample_S, dHR), dtype=np.float32))
+        qc = rng.standard_normal((1, sample_S, H, Dh), dtype=np.float32)
+        qr = rng.standard_normal((1, sample_S, H, dHR), dtype=np.float32)
+        wuk = bf16_bits(rng.standard_normal((dC, H * Dh), dtype=np.float32) * np.float32(0.02))
+        wuv = bf16_bits(rng.standard_normal((dC, H * Dh), dtype=np.float32) * np.float32(0.02))
+        t0 = time.perf_counter()
+        ob.mla_attend(c, r, np.asarray([sample_S], np.int32), qc, qr, wuk, wuv, float(1.0 / np.sqrt(Dh + dHR)), causal=True, threads=threads)
+    else:
+        Hkv, D = w["Hkv"], w["D"]
+        K = bf16_bits(rng.standard_normal((1, sample_S, Hkv, D), dtype=np.float32))
+        V = bf16_bits(rng.standard_normal((1, sample_S, Hkv, D), dtype=np.float32))
+        q = rng.standard_normal((1, sample_S, H, D), dtype=np.float32)
+        t0 = time.perf_counter()
+        ob.gqa_attend(K, V, np.asarray([sample_S], np.int32), q, float(1.0 / np.sqrt(D)), causal=True, threads=threads)
+    dt = time.perf_counter() - t0
+    return {"value": sample_S / dt, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": "one sequence, prompt of %d tokens instead of %d (%.1f s); cost grows with the square of the length" % (sample_S, w["S"], dt)}
+
+
 def accept_inputs(w, seed):
     """Seeded logits with the shape of a verify pass: draft rows N(0, 2.5), target rows = draft + N(0, 0.6) noise, the
     drafted token is the draft row's argmax."""
@@ -703,6 +827,16 @@ def run_reference(args, w, world, rank):
     from oracle import binding as orc
     if rank != 0:
         return None
+    if w["kind"] == "prompt":
+        vals = [cpu_baseline_prompt(w) for _ in range(args.warmup + args.steps)][args.warmup:]
+        v = float(np.mean([x["value"] for x in vals]))
+        cb = dict(vals[-1], value=v)
+        return {"impl": "reference", "metric": "prompt_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": w["B"] * w["S"] * world / v * 1e3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": args.workload, "batch_per_gpu": w["B"], "prompt_tokens": w["S"]},
+                "cpu_baseline": cb, "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "gpu_launches": 0}
     if w["kind"] == "accept":
         # the reference's accept loop is scalar Go: one core, sixteen sequences of the workload per pass
         vals = [cpu_baseline_accept(w, seconds=min(2.0, 100.0 / max(1, args.warmup + args.steps))) for _ in range(args.warmup + args.steps)][args.warmup:]
@@ -762,7 +896,7 @@ def main():
             print(json.dumps(line))
         return
     world, rank, local, dist = dist_setup(args.gpus)
-    runner = {"mla": run_mla, "gqa": run_gqa, "accept": run_accept}[w["kind"]]
+    runner = {"mla": run_mla, "gqa": run_gqa, "accept": run_accept, "prompt": run_prompt}[w["kind"]]
     line = runner(args, w, world, rank, local, dist)
     if rank == 0:
         print(json.dumps(line))
