@@ -34,14 +34,14 @@ def dev():
 def _lengths(rng, B, S, hi):
     kind = rng.integers(0, 4)
     if kind == 0:
-        lens = rng.integers(S, hi, B)
+        lens = rng.integers(S, max(S + 1, hi), B)
     elif kind == 1:                                   # around page and tile boundaries
         lens = rng.choice([63, 64, 65, 127, 128, 129, 191, 192, 193, 256, 257], B) + rng.integers(0, 2, B) * 128
     elif kind == 2:                                   # one long sequence among short ones
-        lens = rng.integers(S, 80, B)
+        lens = rng.integers(S, max(S + 1, 80), B)
         lens[rng.integers(0, B)] = hi
     else:
-        lens = np.full(B, rng.integers(S, hi))
+        lens = np.full(B, rng.integers(S, max(S + 1, hi)))
     return np.maximum(lens, S).astype(np.int32)
 
 
@@ -100,6 +100,66 @@ def test_gqa_fast_against_reference_kernels(dev, oracle, trial):
     assert pool.status() == 0
     _check(fast, ref, "trial %d: B=%d S=%d H=%d Hkv=%d causal=%s lens=%s" % (trial, B, S, H, Hkv, causal, lens.tolist()[:8]))
     pool.destroy()
+
+
+@pytest.mark.parametrize("trial", range(5))
+def test_gqa_prompt_fast_against_reference_kernels(dev, oracle, trial):
+    """Multi-token calls longer than one group of query tokens (prompts): the groups run as slices of one grid over
+    chunks of random cached lengths; causal and not."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(2500 + trial)
+    Hkv, D, P = int(rng.choice([1, 2, 8])), 128, 64
+    H = Hkv * int(rng.choice([1, 4, 8]))
+    B = int(rng.integers(1, 7))
+    S = int(rng.choice([17, 40, 97, 130]))
+    lens = _lengths(rng, B, S, int(rng.choice([300, 700])))
+    pages_per = (int(lens.max()) + P - 1) // P + 1
+    pool = rb.Pool(dev, L.POOL_GQA, 1, B * pages_per, P, B, pages_per, num_kv_heads=Hkv, head_dim=D)
+    pool.set_tables(permuted_tables(rng, B, pages_per))
+    n = int(lens.sum())
+    pool.append(0, oracle.bf16_from_f32(rng.standard_normal((n, Hkv, D), dtype=np.float32)),
+                oracle.bf16_from_f32(rng.standard_normal((n, Hkv, D), dtype=np.float32)), B, n_new=lens)
+    q = rng.standard_normal((B, S, H, D), dtype=np.float32)
+    scale = float(1.0 / np.sqrt(D))
+    causal = bool(rng.integers(0, 4))
+    fast, ref = np.empty_like(q), np.empty_like(q)
+    pool.decode(0, B, q, fast, H, D, scale, q_tokens=S, causal=causal)
+    pool.decode(0, B, q, ref, H, D, scale, q_tokens=S, causal=causal, mode=L.ATTN_REFERENCE)
+    assert pool.status() == 0
+    _check(fast, ref, "prompt trial %d: B=%d S=%d H=%d Hkv=%d causal=%s lens=%s" % (trial, B, S, H, Hkv, causal, lens.tolist()[:8]))
+    pool.destroy()
+
+
+@pytest.mark.parametrize("trial", range(4))
+def test_mla_prompt_fast_against_reference_kernels(dev, oracle, trial):
+    """The same for MLA: more than eight query tokens run as rows of workers, few workers per row."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(1500 + trial)
+    H = int(rng.choice([16, 128]))
+    Dh, dC, dHR, P = 128, 512, 64, 64
+    B = int(rng.integers(1, 5))
+    S = int(rng.choice([12, 33, 70]))
+    lens = _lengths(rng, B, S, int(rng.choice([200, 600])))
+    pages_per = (int(lens.max()) + P - 1) // P + 1
+    pool = rb.Pool(dev, L.POOL_MLA, 1, B * pages_per, P, B, pages_per, dC=dC, dHR=dHR)
+    pool.set_tables(permuted_tables(rng, B, pages_per))
+    n = int(lens.sum())
+    pool.append(0, oracle.bf16_from_f32(rng.standard_normal((n, dC), dtype=np.float32)),
+                oracle.bf16_from_f32(rng.standard_normal((n, dHR), dtype=np.float32)), B, n_new=lens)
+    wuk = dev.upload(oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh), dtype=np.float32) * 0.02))
+    wuv = dev.upload(oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh), dtype=np.float32) * 0.02))
+    qc = rng.standard_normal((B, S, H, Dh), dtype=np.float32)
+    qr = rng.standard_normal((B, S, H, dHR), dtype=np.float32)
+    scale = float(1.0 / np.sqrt(Dh + dHR))
+    causal = bool(rng.integers(0, 4))
+    fast, ref = np.empty_like(qc), np.empty_like(qc)
+    pool.decode(0, B, qc, fast, H, Dh, scale, q_rope=qr, w_uk=wuk, w_uv=wuv, q_tokens=S, causal=causal)
+    pool.decode(0, B, qc, ref, H, Dh, scale, q_rope=qr, w_uk=wuk, w_uv=wuv, q_tokens=S, causal=causal, mode=L.ATTN_REFERENCE)
+    assert pool.status() == 0
+    _check(fast, ref, "prompt trial %d: B=%d S=%d H=%d causal=%s lens=%s" % (trial, B, S, H, causal, lens.tolist()[:8]))
+    pool.destroy(); wuk.free(); wuv.free()
 
 
 @pytest.mark.parametrize("trial", range(8))
