@@ -54,6 +54,9 @@ WORKLOADS = {
     "mla_prompt_b4_1k": dict(kind="prompt", pool="mla", B=4, S=1024, H=128, Dh=128, dC=512, dHR=64),
     "gqa_layer_verify_b128_ctx8k": dict(kind="gqa", B=128, ctx=8192, H=32, Hkv=8, D=128, S=4, layer=True),
 }
+DEFAULT_WORKLOAD = "mla_decode_b64_ctx32k"
+# config 3, config 4 (one GPU's share) and config 5 of the benchmark definition: run after the headline workload
+ALSO_WORKLOADS = ("mla_decode_b64_ctx4k", "mla_decode_ragged_b16", "gqa_verify_b128_ctx8k")
 # dram__bytes_read + dram__bytes_write of the dominant kernel divided by its algorithmic bytes, from the ncu captures
 # summarised under profiles/ (small case, traffic grows in proportion to the cached tokens read).
 TRAFFIC_RATIO = {"mla": 1.04, "gqa": 1.015, "accept": 1.08}
@@ -73,6 +76,31 @@ def read_peaks():
         d = json.load(open(p))
         return float(d["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def workload_config(name, w, lens0=None):
+    """The `config` object of a workload: the same keys in the GPU arm and in the reference arm."""
+    kind = w["kind"]
+    if kind == "mla":
+        ctx0 = w["ctx"]
+        rows = float(np.sum(lens0)) if lens0 is not None else float(w["B"]) * ctx0 * (0.515 if w.get("ragged") else 1.0)
+        return {"workload": name, "batch_per_gpu": w["B"],
+                "context": ("uniform[1024,%d] (seed 11), dealt to the ranks longest-first" % ctx0) if w.get("ragged") else ctx0,
+                "heads": w["H"], "latent": w["dC"], "rope": w["dHR"], "query_tokens": int(w.get("S", 1)), "page_tokens": PAGE,
+                "page_table": "random permutation",
+                "l2": "inputs (about %.1f GB of cache rows per GPU) are larger than L2" % (rows * (w["dC"] + w["dHR"]) * 2 / 1e9)}
+    if kind == "gqa":
+        return {"workload": name, "batch_per_gpu": w["B"], "context": w["ctx"], "heads": w["H"], "kv_heads": w["Hkv"], "head_dim": w["D"],
+                "draft_tokens": w["S"], "page_tokens": PAGE, "page_table": "random permutation",
+                "l2": "inputs (%.2f GB of K/V per GPU) are larger than L2" % (w["B"] * w["ctx"] * w["Hkv"] * w["D"] * 4 / 1e9)}
+    if kind == "accept":
+        return {"workload": name, "batch_per_gpu": w["B"], "draft_tokens": w["k"], "vocab": w["V"],
+                "sampler": dict(temperature=0.8, top_k=50, top_p=0.95),
+                "l2": "inputs (%.2f GB of logits per GPU) are larger than L2" % (w["B"] * (2 * w["k"] + 1) * w["V"] * 4 / 1e9)}
+    mla = w["pool"] == "mla"
+    return {"workload": name, "batch_per_gpu": w["B"], "prompt_tokens": w["S"], "heads": w["H"],
+            "l2": "every step rewrites and re-reads %.1f MB of cache rows; the flush between steps is the append itself"
+                  % ((w["B"] * w["S"] * ((w["dC"] + w["dHR"]) if mla else 2 * w["Hkv"] * w["D"]) * 2) / 1e6)}
 
 
 class ClockSampler(threading.Thread):
@@ -164,6 +192,65 @@ def max_over_ranks(dist, x):
     return float(t.item())
 
 
+
+MIN_SECONDS = 3.0      # the timed region of --steps steps is repeated back to back until this much device time has passed
+SETTLE_SECONDS = 1.0   # repeats that end within the first second (boost clocks, power-cap transient) do not enter the headline
+
+
+def timed_repeats(dev, dist, step, steps, warmup, reset=None, min_seconds=MIN_SECONDS, sampler=None):
+    """W warm-up steps, then the K-step region again and again, back to back with no host synchronisation in between,
+    until `min_seconds` have passed; every repeat is bracketed by its own CUDA events on the launching stream.  `reset`
+    runs between two repeats, outside their event pairs (it puts the sequence lengths back, so that every repeat is the
+    same workload).  Returns the per-repeat device times (ms, max over ranks at the same repeat index is taken by the
+    caller through `summarise`), the launches counted, and the host time of the loop."""
+    for _ in range(warmup):
+        step()
+    if reset is not None:
+        reset()
+    dev.sync()
+    barrier(dist)
+    n0 = dev.launch_count()
+    if sampler is not None:
+        sampler.begin()
+    events = []
+    t0 = time.perf_counter()
+    while True:
+        a, b = dev.event(), dev.event()
+        a.record()
+        for _ in range(steps):
+            step()
+        b.record()
+        events.append((a, b))
+        if reset is not None:
+            reset()
+        if time.perf_counter() - t0 >= min_seconds or len(events) >= 4000:
+            break
+    dev.sync()
+    host_s = time.perf_counter() - t0
+    launches = dev.launch_count() - n0
+    ms = [a.elapsed_ms(b) for a, b in events]
+    for a, b in events:
+        a.close(); b.close()
+    barrier(dist)
+    return ms, launches, host_s
+
+
+def summarise(dist, ms, settle_seconds=SETTLE_SECONDS):
+    """(headline ms of one K-step region, burst ms = the first repeat, repeats used, index of the first repeat used).
+    Headline = median of the repeats that START after the first `settle_seconds` of device time (all repeats when the
+    run is shorter than that); with several ranks, the maximum over ranks of each rank's median."""
+    t, first = 0.0, len(ms)
+    for i, x in enumerate(ms):
+        if t >= settle_seconds * 1e3:
+            first = i
+            break
+        t += x
+    used = ms[first:] if first < len(ms) else ms
+    if first >= len(ms):
+        first = 0
+    med = float(np.median(used))
+    return max_over_ranks(dist, med), max_over_ranks(dist, float(ms[0])), len(used), first
+
 # --------------------------------------------------------------------------------------------------
 def run_mla(args, w, world, rank, local, dist):
     import relux_b200 as rb
@@ -171,8 +258,8 @@ def run_mla(args, w, world, rank, local, dist):
 
     B, ctx0, H, Dh, dC, dHR = w["B"], w["ctx"], w["H"], w["Dh"], w["dC"], w["dHR"]
     S = int(w.get("S", 1))
-    total_steps = 2 * (args.steps + args.warmup) + 8
-    pages_per = (ctx0 + total_steps * S + S + PAGE - 1) // PAGE + 1
+    # the lengths are put back between repeats of the timed region, so a sequence grows by one region (+ warm-up) at most
+    pages_per = (ctx0 + (args.steps + args.warmup + 2) * S + S + PAGE - 1) // PAGE + 1
     dev = rb.Device(local)
     rng = np.random.default_rng(7 + rank)
     pool = rb.Pool(dev, L.POOL_MLA, 1, B * pages_per, PAGE, B, pages_per, dC=dC, dHR=dHR)
@@ -210,15 +297,25 @@ def run_mla(args, w, world, rank, local, dist):
         p_.array[...] = a
     pin_out = dev.pinned((B, 1, H, Dh), np.float32)
 
+    lens0_i32 = lens0.astype(np.int32)
+    rows_now = [float(lens0.sum())]   # cached rows of all sequences, as the host tracks them
+    rows_log = []                     # rows read by every attention call of the resident arm
+    accepted = [0]
+
+    def reset():
+        pool.set_len(0, lens0_i32)
+        rows_now[0] = float(lens0.sum())
+
     def step_resident():
         pool.append(0, d_new_c, d_new_r, B)
+        rows_now[0] += B
+        rows_log.append(rows_now[0])
         pool.decode(0, B, d_qc, d_out, H, Dh, scale, q_rope=d_qr, w_uk=d_wuk, w_uv=d_wuv)
 
     def step_e2e():
         pool.append(0, pins[0].array, pins[1].array, B)
         pool.decode(0, B, pins[2].array, pin_out.array, H, Dh, scale, q_rope=pins[3].array, w_uk=d_wuk, w_uv=d_wuv)
 
-    accepted = [0]
     if S > 1:
         # verify step: S draft rows per sequence written past the cursor, S query tokens (causal inside the draft), then
         # an accepted prefix of 1..S tokens is committed; tokens/s counts accepted tokens
@@ -235,6 +332,10 @@ def run_mla(args, w, world, rank, local, dist):
         vpin_out = dev.pinned((B, S, H, Dh), np.float32)
         vlens = lens0.copy()
 
+        def reset():
+            vlens[:] = lens0
+            pool.set_len(0, lens0_i32)
+
         def commit():
             acc = rng.integers(1, S + 1, B)
             vlens[:] += acc
@@ -242,6 +343,7 @@ def run_mla(args, w, world, rank, local, dist):
             pool.set_len(0, vlens.astype(np.int32))
 
         def step_resident():
+            rows_log.append(float(vlens.sum()) + B * S)   # committed rows + the S draft rows of every sequence
             pool.verify(0, B, d_vq, d_vout, d_dr_c, d_dr_r, H, Dh, scale, S, q_rope=d_vqr, w_uk=d_wuk, w_uv=d_wuv)
             commit()
 
@@ -272,48 +374,33 @@ def run_mla(args, w, world, rank, local, dist):
         pin_y = dev.pinned(x_host.shape, np.float32)
 
         def step_resident():
+            rows_now[0] += B
+            rows_log.append(rows_now[0])
             pool.forward_cached(0, B, d_x, d_y, dW, D, H)
 
         def step_e2e():
             pool.forward_cached(0, B, pin_x.array, pin_y.array, dW, D, H)
 
-    e0, e1 = dev.event(), dev.event()
-
-    def timed(fn, steps, warmup, sampler=None):
-        for _ in range(warmup):
-            fn()
-        dev.sync()
-        barrier(dist)
-        n0 = dev.launch_count()
-        accepted[0] = 0
-        if sampler is not None:
-            sampler.begin()
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        dev.sync()
-        ms = e0.elapsed_ms(e1)
-        barrier(dist)
-        return max_over_ranks(dist, ms), dev.launch_count() - n0
-
+    K = args.steps
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    ms_res, launches = timed(step_resident, args.steps, args.warmup, sampler if rank == 0 else None)
-    acc_res = accepted[0]
+    ms_list, launches, host_s = timed_repeats(dev, dist, step_resident, K, args.warmup, reset, args.min_seconds, sampler if rank == 0 else None)
     clocks = sampler.finish() if rank == 0 else None
+    ms_res, ms_burst, used, first_used = summarise(dist, ms_list)
+    acc_per_step = accepted[0] / float(len(ms_list) * K + args.warmup) if S > 1 else 0.0
     # dominant kernel: the decode kernel; every call records a CUDA event pair around that launch on the launching
-    # stream, read here for the calls of the timed region (the library keeps the last 256)
-    kernel_ms, counted = pool.mean_kernel_ms(args.steps)
-    len_end = sum(pool.seq_len(0, b) for b in range(B))
-    if S > 1:   # verify: every call read the committed rows plus S draft rows; lengths grew by (S + 1) / 2 per call on average
-        rows_mean = len_end + B * S - B * (S + 1) / 2.0 * (counted + 1) / 2.0
-    else:       # every sequence grew by one row per call
-        rows_mean = len_end - B * (counted - 1) / 2.0              # cached rows read per launch, mean over those calls
-    ms_e2e, _ = timed(step_e2e, args.steps, args.warmup)
-    acc_e2e = accepted[0]
+    # stream; read here for the calls of the repeats that make the headline (the library keeps the last 8192)
+    kms = pool.kernel_ms_list(min(used * K, 8192))
+    counted = len(kms)
+    kernel_ms = float(np.mean(kms))
+    rows_mean = float(np.mean(rows_log[-counted:]))            # cached rows read per launch, mean over those calls
+    kernel_ms_burst = float(np.mean(pool.kernel_ms_list(len(ms_list) * K)[:K])) if len(ms_list) * K <= 8192 else None
+    accepted[0] = 0
+    ms_e2e_list, _, _ = timed_repeats(dev, dist, step_e2e, K, args.warmup, reset, args.min_seconds)
+    ms_e2e, ms_e2e_burst, _, _ = summarise(dist, ms_e2e_list)
+    acc_per_step_e2e = accepted[0] / float(len(ms_e2e_list) * K + args.warmup) if S > 1 else 0.0
     assert pool.status() == 0, "device status word is set"
     alg_bytes = rows_mean * (dC + dHR) * 2
     alg_flops = 2.0 * H * S * rows_mean * ((dC + dHR) + dC)
@@ -322,37 +409,46 @@ def run_mla(args, w, world, rank, local, dist):
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
     tflops = alg_flops / (kernel_ms * 1e-3) / 1e12
     tokens = B * world
-    value = tokens * args.steps / (ms_res * 1e-3)
-    e2e = tokens * args.steps / (ms_e2e * 1e-3)
+    value = tokens * K / (ms_res * 1e-3)
+    e2e = tokens * K / (ms_e2e * 1e-3)
+    value_burst = tokens * K / (ms_burst * 1e-3)
     h2d = sum(a.nbytes for a in (new_c, new_r, qc, qr))
     d2h = pin_out.array.nbytes
     if layer:
         h2d, d2h = x_host.nbytes, x_host.nbytes
     if S > 1:   # accepted tokens; every rank draws from its own seeded stream with the same law
-        value = acc_res * world / (ms_res * 1e-3)
-        e2e = acc_e2e * world / (ms_e2e * 1e-3)
+        value = acc_per_step * K * world / (ms_res * 1e-3)
+        e2e = acc_per_step_e2e * K * world / (ms_e2e * 1e-3)
+        value_burst = acc_per_step * K * world / (ms_burst * 1e-3)
         h2d, d2h = sum(a_.nbytes for a_ in (dr_c, dr_r, vq, vqr)), vpin_out.array.nbytes
+    sm_mhz = (clocks or {}).get("sm_mhz")
     line = {
-        "metric": "mla_layer_decode_tokens_per_s" if layer else ("mla_verify_accepted_tokens_per_s" if S > 1 else "mla_decode_tokens_per_s"), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": "weak",
+        "metric": "mla_layer_decode_tokens_per_s" if layer else ("mla_verify_accepted_tokens_per_s" if S > 1 else "mla_decode_tokens_per_s"), "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K,
+        "warmup": args.warmup, "ms_per_step": ms_res / K, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "batch_per_gpu": B,
-                   "context": ("uniform[1024,%d], %d tokens on rank 0" % (ctx0, int(lens0.sum()))) if w.get("ragged") else ctx0,
-                   "heads": H, "latent": dC, "rope": dHR,
-                   "page_tokens": PAGE, "page_table": "random permutation", "l2": "inputs (%.2f GB of cache rows per GPU) are larger than L2"
-                   % (float(lens0.sum()) * (dC + dHR) * 2 / 1e9)},
+        "config": workload_config(args.workload, w), "cached_tokens_rank0": int(lens0.sum()),
+        "timing": {"repeats": len(ms_list), "repeats_in_headline": used, "first_repeat_in_headline": first_used,
+                   "rule": "the %d-step region is repeated back to back for >= %.1f s; value = median of the repeats that start after the "
+                           "first %.1f s of device time; lengths are put back between repeats" % (K, args.min_seconds, SETTLE_SECONDS),
+                   "device_seconds": sum(ms_list) / 1e3, "host_seconds": host_s},
+        "burst": {"value": value_burst, "ms_per_step": ms_burst / K, "kernel_ms": kernel_ms_burst,
+                  "roofline_frac": (alg_bytes / (kernel_ms_burst * 1e-3) / 1e9 / peak) if kernel_ms_burst else None,
+                  "what": "the first repeat of the timed region (boost clocks, before the power cap settles)"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": (alg_bytes * TRAFFIC_RATIO["mla"]) if TRAFFIC_RATIO["mla"] else None,
                      "peak_source": peak_src, "kernel": "mla_decode_sm100_kernel", "kernel_ms": kernel_ms, "launches_timed": counted,
                      "algorithmic_bytes_per_launch": alg_bytes, "frac_of_nominal_8TBs": achieved / 8000.0,
+                     "kernel_ms_x_sm_mhz": (kernel_ms * sm_mhz) if sm_mhz else None,
                      # the same kernel against the tensor roofline (128 heads put it at the ridge point)
                      "tensor": {"achieved": tflops, "unit": "TFLOP/s", "algorithmic_flops_per_launch": alg_flops,
                                 "peak_burst": pk.get("bf16_tflops", 1590.0), "peak_sustained": pk.get("bf16_tflops_sustained", 1400.0),
                                 "frac_of_burst": tflops / pk.get("bf16_tflops", 1590.0),
                                 "frac_of_sustained": tflops / pk.get("bf16_tflops_sustained", 1400.0)}},
-        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": launches, "clocks": clocks,
-        "kv_read_gbs_whole_step": alg_bytes * world / (ms_res / args.steps * 1e-3) / 1e9,
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": ms_e2e / K, "burst_value": (e2e * ms_e2e / ms_e2e_burst),
+                "h2d_d2h_gbs_per_rank": (h2d + d2h) / (ms_e2e / K * 1e-3) / 1e9},
+        "gpu_launches": int(round(launches / float(len(ms_list)))), "clocks": clocks,
+        "kv_read_gbs_whole_step": alg_bytes * world / (ms_res / K * 1e-3) / 1e9,
     }
     if layer:
         proj_ms, proj_n = pool.mean_projection_ms(args.steps)
@@ -379,8 +475,8 @@ def run_gqa(args, w, world, rank, local, dist):
     from relux_b200 import lib as L
 
     B, ctx0, H, Hkv, D, S = w["B"], w["ctx"], w["H"], w["Hkv"], w["D"], w["S"]
-    total_steps = 2 * (args.steps + args.warmup) + 8
-    pages_per = (ctx0 + total_steps * S + S + PAGE - 1) // PAGE + 1
+    # the lengths are put back between repeats of the timed region, so a sequence grows by one region (+ warm-up) at most
+    pages_per = (ctx0 + (args.steps + args.warmup + 2) * S + S + PAGE - 1) // PAGE + 1
     dev = rb.Device(local)
     rng = np.random.default_rng(3 + rank)
     pool = rb.Pool(dev, L.POOL_GQA, 1, B * pages_per, PAGE, B, pages_per, num_kv_heads=Hkv, head_dim=D)
@@ -404,7 +500,12 @@ def run_gqa(args, w, world, rank, local, dist):
         p_.array[...] = a
     pin_out = dev.pinned(q.shape, np.float32)
     lens = np.full(B, ctx0, np.int64)
+    lens0_i32 = np.full(B, ctx0, np.int32)
     accepted_total = [0]
+
+    def reset():
+        lens[:] = ctx0
+        pool.set_len(0, lens0_i32)
 
     def commit():
         acc = rng.integers(1, S + 1, B)
@@ -447,56 +548,48 @@ def run_gqa(args, w, world, rank, local, dist):
             pool.forward_cached(0, B, pin_x.array, pin_y.array, dW, dm, H, q_tokens=S, advance=False)
             commit()
 
-    e0, e1 = dev.event(), dev.event()
-
-    def timed(fn, steps, warmup, sampler=None):
-        for _ in range(warmup):
-            fn()
-        dev.sync()
-        barrier(dist)
-        n0 = dev.launch_count()
-        accepted_total[0] = 0
-        if sampler is not None:
-            sampler.begin()
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        dev.sync()
-        ms = e0.elapsed_ms(e1)
-        barrier(dist)
-        return max_over_ranks(dist, ms), dev.launch_count() - n0, accepted_total[0]
-
+    K = args.steps
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    ms_res, launches, acc_res = timed(step_resident, args.steps, args.warmup, sampler if rank == 0 else None)
+    ms_list, launches, host_s = timed_repeats(dev, dist, step_resident, K, args.warmup, reset, args.min_seconds, sampler if rank == 0 else None)
     clocks = sampler.finish() if rank == 0 else None
-    # dominant kernel: event pairs recorded by the calls of the timed region themselves (the library keeps the last 256)
-    kernel_ms, counted = pool.mean_kernel_ms(args.steps)
+    ms_res, ms_burst, used, first_used = summarise(dist, ms_list)
+    # accepted tokens per step: the acceptance law is uniform on 1..S, every rank draws from its own seeded stream
+    acc_per_step = accepted_total[0] / float((len(ms_list) * K + args.warmup))
+    # dominant kernel: event pairs recorded by the calls of the repeats that make the headline (the library keeps the last 8192)
+    kms = pool.kernel_ms_list(min(used * K, 8192))
+    counted = len(kms)
+    kernel_ms = float(np.mean(kms))
     alg_bytes = float(np.mean(rows_read[-counted:])) * Hkv * D * 2 * 2
-    ms_e2e, _, acc_e2e = timed(step_e2e, args.steps, args.warmup)
+    ms_e2e_list, _, _ = timed_repeats(dev, dist, step_e2e, K, args.warmup, reset, args.min_seconds)
+    ms_e2e, ms_e2e_burst, _, _ = summarise(dist, ms_e2e_list)
     assert pool.status() == 0, "device status word is set"
     peak, peak_src = read_peaks()
     achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
-    acc_res_all = acc_res * world   # every rank draws from its own seeded stream with the same distribution
+    sm_mhz = (clocks or {}).get("sm_mhz")
     line = {
         "metric": "gqa_layer_verify_accepted_tokens_per_s" if layer else "gqa_verify_accepted_tokens_per_s",
-        "value": acc_res_all / (ms_res * 1e-3), "unit": "tokens/s", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": "weak",
+        "value": acc_per_step * K * world / (ms_res * 1e-3), "unit": "tokens/s", "n_gpus": world,
+        "steps": K, "warmup": args.warmup, "ms_per_step": ms_res / K, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "batch_per_gpu": B, "context": ctx0, "heads": H, "kv_heads": Hkv, "head_dim": D,
-                   "draft_tokens": S, "page_tokens": PAGE, "page_table": "random permutation",
-                   "l2": "inputs (%.2f GB of K/V per GPU) are larger than L2" % (B * ctx0 * Hkv * D * 4 / 1e9)},
+        "config": workload_config(args.workload, w),
+        "timing": {"repeats": len(ms_list), "repeats_in_headline": used, "first_repeat_in_headline": first_used,
+                   "rule": "the %d-step region is repeated back to back for >= %.1f s; value = median of the repeats that start after the "
+                           "first %.1f s of device time; lengths are put back between repeats" % (K, args.min_seconds, SETTLE_SECONDS),
+                   "device_seconds": sum(ms_list) / 1e3, "host_seconds": host_s, "accepted_per_step": acc_per_step},
+        "burst": {"value": acc_per_step * K * world / (ms_burst * 1e-3), "ms_per_step": ms_burst / K,
+                  "what": "the first repeat of the timed region (boost clocks, before the power cap settles)"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": alg_bytes * TRAFFIC_RATIO["gqa"],
                      "peak_source": peak_src, "kernel": "gqa_decode_kernel", "kernel_ms": kernel_ms, "launches_timed": counted,
-                     "algorithmic_bytes_per_launch": alg_bytes, "frac_of_nominal_8TBs": achieved / 8000.0},
-        "e2e": {"value": acc_e2e * world / (ms_e2e * 1e-3), "unit": "tokens/s",
+                     "algorithmic_bytes_per_launch": alg_bytes, "frac_of_nominal_8TBs": achieved / 8000.0,
+                     "kernel_ms_x_sm_mhz": (kernel_ms * sm_mhz) if sm_mhz else None},
+        "e2e": {"value": acc_per_step * K * world / (ms_e2e * 1e-3), "unit": "tokens/s",
                 "h2d_bytes_per_step": int(x_host.nbytes) if layer else int(q.nbytes + nk.nbytes + nv.nbytes),
-                "d2h_bytes_per_step": int(x_host.nbytes) if layer else int(q.nbytes)},
-        "gpu_launches": launches, "clocks": clocks,
+                "d2h_bytes_per_step": int(x_host.nbytes) if layer else int(q.nbytes), "ms_per_step": ms_e2e / K},
+        "gpu_launches": int(round(launches / float(len(ms_list)))), "clocks": clocks,
     }
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_bounded(w)
@@ -586,9 +679,7 @@ def run_prompt(args, w, world, rank, local, dist):
         "metric": "prompt_tokens_per_s", "value": B * S * world * steps / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic",
-        "config": {"workload": args.workload, "batch_per_gpu": B, "prompt_tokens": S, "heads": H,
-                   "l2": "every step rewrites and re-reads %.1f MB of cache rows; the flush between steps is the append itself"
-                         % ((B * S * ((w["dC"] + w["dHR"]) if mla else 2 * w["Hkv"] * w["D"]) * 2) / 1e6)},
+        "config": workload_config(args.workload, w),
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
                      "peak_source": "measured" if peaks else "fallback", "kernel": "mla_decode_sm100_kernel" if mla else "gqa_decode_kernel",
                      "kernel_ms": kernel_ms, "launches_timed": counted, "algorithmic_flops_per_launch": flops},
@@ -720,8 +811,7 @@ def run_accept(args, w, world, rank, local, dist):
         "metric": "spec_accept_tokens_per_s", "value": acc_res * world / (ms_res * 1e-3), "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_res / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "batch_per_gpu": B, "draft_tokens": k, "vocab": V, "sampler": sampler_kw,
-                   "l2": "inputs (%.2f GB of logits per GPU) are larger than L2" % ((dl.nbytes + tl.nbytes) / 1e9)},
+        "config": workload_config(args.workload, w),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": alg_bytes * TRAFFIC_RATIO["accept"],
                      "peak_source": peak_src, "kernel": "spec_accept_kernel", "kernel_ms": kernel_ms, "launches_timed": counted,
@@ -834,7 +924,7 @@ def run_reference(args, w, world, rank):
         return {"impl": "reference", "metric": "prompt_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": w["B"] * w["S"] * world / v * 1e3, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": args.workload, "batch_per_gpu": w["B"], "prompt_tokens": w["S"]},
+                "config": workload_config(args.workload, w),
                 "cpu_baseline": cb, "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
     if w["kind"] == "accept":
@@ -845,7 +935,7 @@ def run_reference(args, w, world, rank):
         return {"impl": "reference", "metric": "spec_accept_tokens_per_s", "value": v, "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": w["B"] * world * (w["k"] + 2) / 2.0 / v * 1e3,
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": args.workload, "batch_per_gpu": w["B"], "draft_tokens": w["k"], "vocab": w["V"]},
+                "config": workload_config(args.workload, w),
                 "cpu_baseline": cb, "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "gpu_launches": 0}
     # every host core this process may run on (a launcher's OMP_NUM_THREADS=1 default is not a property of the box)
@@ -872,7 +962,7 @@ def run_reference(args, w, world, rank):
     return {"impl": "reference", "metric": metric, "value": v, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step / v * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "batch_per_gpu": B, "context": w["ctx"]},
+            "config": workload_config(args.workload, w),
             "cpu_baseline": cb, "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
 
@@ -883,8 +973,12 @@ def main():
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="mla_decode_b64_ctx32k", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="profiling runs: leave out the 10-30 s CPU baseline leg")
+    ap.add_argument("--min-seconds", type=float, default=MIN_SECONDS,
+                    help="the timed region of --steps steps is repeated back to back until this much time has passed (0: run it once)")
+    ap.add_argument("--only", action="store_true", help="run the named workload alone (the default run appends short passes of the other "
+                                                        "benchmark configurations under `also`)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     w = WORKLOADS[args.workload]
@@ -896,8 +990,17 @@ def main():
             print(json.dumps(line))
         return
     world, rank, local, dist = dist_setup(args.gpus)
-    runner = {"mla": run_mla, "gqa": run_gqa, "accept": run_accept, "prompt": run_prompt}[w["kind"]]
-    line = runner(args, w, world, rank, local, dist)
+    runners = {"mla": run_mla, "gqa": run_gqa, "accept": run_accept, "prompt": run_prompt}
+    line = runners[w["kind"]](args, w, world, rank, local, dist)
+    if args.workload == DEFAULT_WORKLOAD and not args.only:
+        # the other benchmark configurations, as shorter passes of the same measurement (every rank runs them, in this order)
+        also = []
+        for name in ALSO_WORKLOADS:
+            sub = argparse.Namespace(**vars(args))
+            sub.workload, sub.skip_cpu_baseline, sub.min_seconds = name, True, min(args.min_seconds, 2.0)
+            wl = WORKLOADS[name]
+            also.append(runners[wl["kind"]](sub, wl, world, rank, local, dist))
+        line["also"] = also
     if rank == 0:
         print(json.dumps(line))
     if dist is not None:

@@ -8,7 +8,10 @@
  *   - no callbacks, no struct by value, no C++ exceptions cross the boundary;
  *   - every call selects the handle's CUDA device itself (goroutines migrate between OS threads);
  *   - calls on one device handle are serialised internally; distinct handles are independent;
- *   - there is no CPU fallback: when a GPU cannot do the work the call fails with a status.
+ *   - there is no CPU fallback: when a GPU cannot do the work the call fails with a status;
+ *   - every pointer flagged RELUX_MEM_DEVICE (and every weight pointer) must be 16-byte aligned and every row of the
+ *     array it names a multiple of 16 bytes long: the kernels read them with 16-byte vector loads.  A misaligned device
+ *     pointer is refused with RELUX_ERR_INVALID_ARG before anything is launched.  Host pointers have no such rule.
  *
  * "Reference" below is the relux source tree; paths are relative to its root.
  */
@@ -57,6 +60,21 @@ extern "C" {
  *   meant for small models where token-id identity with the reference matters. */
 #define RELUX_ATTN_FAST 0
 #define RELUX_ATTN_REFERENCE 1
+/* REFERENCE_FAITHFUL: the REFERENCE arithmetic with the reference's own indexing, for the small models on which greedy
+ * token ids are compared with what relux itself emits.  Needs a pool created with RELUX_POOL_FLAG_REFERENCE_COMPAT.
+ *   GQA: the cache is written chunk by chunk (one chunk per Append call, head-major inside the chunk:
+ *        internal/transformer/kvcache.go:407-438) but read as one head-major [numKVHeads, T, headDim] array
+ *        (mha.go:299-312): logical (kv head h, position j) reads stream row h*T + j.
+ *   MLA: the decompressed keys / values are token-major [T, H, headDim] but indexed as head-major
+ *        (mla.go:323-326 vs :348, 351): logical (head h, position j) reads token (h*T + j) / H, head (h*T + j) % H; the
+ *        latent rows are read as float32, the reference's cache dtype (mla_cache.go:46-52).
+ *   A causal mask is applied only when the call's q_tokens equal the cached length (mha.go:340, mla.go:368), and the
+ *   layer-level calls give every row of a multi-token call on a non-empty cache the same RoPE position
+ *   (rope.go:151-158).  extra_tokens must be 0. */
+#define RELUX_ATTN_REFERENCE_FAITHFUL 2
+/* relux_pool_params.flags */
+#define RELUX_POOL_FLAG_REFERENCE_COMPAT 1   /* keep what RELUX_ATTN_REFERENCE_FAITHFUL needs: the chunk boundaries of every
+                                                Append (GQA), a float32 copy of every appended row (MLA) */
 
 typedef void* relux_device_t;
 typedef void* relux_pool_t;
@@ -129,7 +147,8 @@ typedef struct relux_pool_params {
   int32_t mla_dhr;           /* MLA decoupled RoPE key width */
   int32_t gqa_num_kv_heads;
   int32_t gqa_head_dim;
-  int32_t reserved[6];       /* must be zero */
+  int32_t flags;             /* RELUX_POOL_FLAG_* */
+  int32_t reserved[5];       /* must be zero */
 } relux_pool_params;
 
 /* NewKVCacheSized (kvcache.go:66-93) / NewMLACache (mla_cache.go:38-59) for a whole batch of sequences; destroy
@@ -169,8 +188,32 @@ int32_t relux_pool_status(relux_pool_t pool, int32_t* status);
  * as bf16 bit patterns.  MLA: dst_a = latent rows [n][dC], dst_b = rope-key rows [n][dHR].
  * GQA: dst_a = K rows [n][Hkv][D], dst_b = V rows.  Either destination may be NULL.  Rows past the
  * sequence length are returned as stored (unspecified content). */
-int32_t relux_pool_read_rows(relux_pool_t pool, int32_t layer, int32_t seq_id, int32_t tok0, int32_t n_tokens,
-                             void* dst_a, void* dst_b);
+typedef struct relux_read_rows_args {
+  int32_t layer;
+  int32_t seq_id;
+  int32_t tok0;
+  int32_t n_tokens;
+  void* dst_a;               /* host */
+  void* dst_b;               /* host */
+  int32_t reserved[4];
+} relux_read_rows_args;
+int32_t relux_pool_read_rows(relux_pool_t pool, const relux_read_rows_args* args);
+
+/* Tuning knobs of relux_pool_tune. */
+#define RELUX_TUNE_MLA_GENERIC 0        /* RELUX_MLA_GENERIC: 1 = MLA decode on the CUDA-core kernels                      */
+#define RELUX_TUNE_MLA_WORKERS 1        /* RELUX_MLA_WORKERS: ranges the stream of pages is cut into (0 = resident pairs)   */
+#define RELUX_TUNE_CHUNK_PAGES 2        /* RELUX_CHUNK_PAGES: chunk length of the split-KV planner (0 = chosen per call)    */
+#define RELUX_TUNE_GEMM_GENERIC 3       /* RELUX_GEMM_GENERIC: 1 = projections on the plain kernel                          */
+#define RELUX_TUNE_GEMM_SPLIT 4         /* RELUX_GEMM_SPLIT: split-K factor of the tcgen05 GEMM (0 = chosen per call)       */
+#define RELUX_TUNE_GQA_PROMPT_PARTIAL_MB 5 /* RELUX_GQA_PROMPT_PARTIAL_MB: partial-buffer budget of a GQA prompt (256)      */
+#define RELUX_TUNE_SEL_CLUSTER 6        /* RELUX_SEL_CLUSTER: cluster size of the selection kernel, 1/2/4/8 (0 = per call) */
+#define RELUX_TUNE_SEL_LOOKAHEAD 7      /* RELUX_SEL_LOOKAHEAD: 0/1 (-1 = per call)                                         */
+#define RELUX_TUNE_SEL_BATCHED 8        /* RELUX_SEL_BATCHED: 0/1 (-1 = per call)                                           */
+#define RELUX_TUNE_COUNT 9
+/* Changes one tuning knob of a pool (see RELUX_TUNE_*).  A pool takes its defaults once, when it is created, from the
+ * environment variables named beside the knobs; no call reads the environment afterwards.  value < 0 restores the
+ * built-in default.  Tuning aid: no counterpart in the reference. */
+int32_t relux_pool_tune(relux_pool_t pool, int32_t knob, int32_t value);
 
 /* ---- append -------------------------------------------------------------------------------
  * MLACache.Append (mla_cache.go:152-182) fed by MLA.forwardCached step 4 (mla.go:309-312):
@@ -417,13 +460,24 @@ int32_t relux_seq_save_file(relux_pool_t pool, int32_t seq_id, const char* path,
 int32_t relux_seq_load_file(relux_pool_t pool, int32_t seq_id, const char* path, int32_t max_len, const int32_t* layer_len);
 
 /* The stream partition the persistent MLA decode kernel works on, computed on the host from page counts (no device
- * needed): the pages of all sequences, laid end to end, are cut into ranges of range_pages_out pages (a multiple of
+ * needed): the pages of all sequences, laid end to end, are cut into ranges of *range_pages_out pages (a multiple of
  * page_multiple), one range per worker; an item is the part of one sequence inside one range.
  * items_out: n x {seq_index, page_begin, page_end, worker} (cap items of room), worker_first [*workers_out + 1],
  * chunk_off [n_seqs + 1]; any of the three may be NULL.  Returns the number of items, -1 on bad arguments or when cap
  * is too small.  Scheduling aid: no counterpart in the reference. */
-int32_t relux_stream_partition(const int32_t* pages, int32_t n_seqs, int32_t workers, int32_t page_multiple, int32_t* range_pages_out,
-                               int32_t* workers_out, int32_t* items_out, int32_t cap, int32_t* worker_first, int32_t* chunk_off);
+typedef struct relux_stream_partition_args {
+  const int32_t* pages;      /* [n_seqs] pages per sequence */
+  int32_t n_seqs;
+  int32_t workers;
+  int32_t page_multiple;
+  int32_t cap;               /* room in items_out, in items */
+  int32_t* range_pages_out;
+  int32_t* workers_out;
+  int32_t* items_out;
+  int32_t* worker_first;
+  int32_t* chunk_off;
+} relux_stream_partition_args;
+int32_t relux_stream_partition(const relux_stream_partition_args* args);
 
 /* Device-time of the dominant attention kernel of the most recent relux_*_decode / verify call on this
  * pool, measured with CUDA events around that one launch.  Synchronises the stream.  Measurement aid: no counterpart
@@ -431,14 +485,79 @@ int32_t relux_stream_partition(const int32_t* pages, int32_t n_seqs, int32_t wor
 int32_t relux_pool_last_kernel_ms(relux_pool_t pool, float* ms);
 
 /* Mean device time of that kernel over the most recent `last_n` decode / verify calls on this pool (at most
- * 256 are kept); `counted` receives how many calls went into the mean.  The event pairs are recorded by the
+ * 8192 are kept); `counted` receives how many calls went into the mean.  The event pairs are recorded by the
  * calls themselves, so reading them after a timed loop does not disturb the loop.  Synchronises the stream.
  * Measurement aid: no counterpart in the reference. */
 int32_t relux_pool_kernel_ms_mean(relux_pool_t pool, int32_t last_n, float* mean_ms, int32_t* counted);
+/* The same times one by one: ms_out [last_n] receives the device time of each of the most recent calls, oldest first;
+ * `counted` how many were written.  Measurement aid: no counterpart in the reference. */
+int32_t relux_pool_kernel_ms_list(relux_pool_t pool, int32_t last_n, float* ms_out, int32_t* counted);
 
 /* Same for the input-projection launch (x . [W_Q | W_QR | W_DKV | W_KR]) of the most recent
  * relux_mla_forward_cached calls on this pool.  Measurement aid: no counterpart in the reference. */
 int32_t relux_pool_projection_ms_mean(relux_pool_t pool, int32_t last_n, float* mean_ms, int32_t* counted);
+
+/* ---- the matmul of the compute backend ---------------------------------------------------------
+ * ComputeBackend.MatMulFloat32 (internal/compute/interface.go:25-29) as matmulBatched3D calls it for every projection
+ * (internal/transformer/mha.go:759-785 -> nativeBackend.MatMulFloat32, internal/compute/native.go:175-187):
+ *   C [M][N] float32 = A [M][K] float32 x B [K][N] bf16 (row-major, the layout of optim.Param.Data).
+ * A and C in host or device memory, B on the device (weights are uploaded once).
+ * RELUX_ATTN_FAST: A rounded to bf16, tcgen05 tensor-core GEMM with split-K (needs K and N multiples of 8);
+ * RELUX_ATTN_REFERENCE: one k-ascending chain of unfused float32 multiply-then-add per output, the order of
+ * internal/transformer/matmul.go:15-27 -- bit-identical to the reference.
+ * An error is an error: the reference's caller falls back to Go when the backend fails (mha.go:768-772); this library has
+ * no fallback, the binding must surface the status. */
+typedef struct relux_matmul_args {
+  int32_t m, k, n;
+  int32_t mode;              /* RELUX_ATTN_FAST | RELUX_ATTN_REFERENCE */
+  const float* a;
+  int32_t a_mem;
+  int32_t c_mem;
+  const void* b;             /* device bf16 [k][n] */
+  float* c;
+  int32_t reserved[4];
+} relux_matmul_args;
+int32_t relux_matmul_f32_bf16(relux_pool_t pool, const relux_matmul_args* args);
+
+/* ---- weight import -------------------------------------------------------------------------------
+ * Brings the attention weights of one MLA layer from checkpoint layout into the device layout the layer calls take.
+ * The reference's DeepSeek mapper names the checkpoint tensors (internal/loader/mapper.go:139-180): q_proj -> mla.W_Q,
+ * kv_a_proj_with_mqa -> mla.W_DKV, kv_b_proj -> the fused "mla.W_UK_W_UV", o_proj -> mla.W_O, every one with
+ * Transpose: true (checkpoints store [out][in], relux holds [in][out]); its loader converts each tensor to bf16 with
+ * BF16FromF32 (loader.go:239-281, 394-404) and has a slot for the separate matrices only (loader.go:322-338): the fused
+ * kind is named but never split.  This call does the split and the transposes on the device:
+ *   kv_b_proj [H * (nope + v)][dC], per head nope rows then v rows (the shape rule of mapper.go:146-152)
+ *                                                      -> w_uk [dC][H * nope], w_uv [dC][H * v]
+ *   o_proj [d_model][H * v]                            -> w_o [H * v][d_model]
+ *   fused_rope == 0, the tensors the reference's mapper names (mapper.go:139-180):
+ *     q_proj [H * nope][d_model] -> w_q;  q_pe_proj [H * rope][d_model] -> w_qr;
+ *     kv_a_proj_with_mqa [dC][d_model] -> w_dkv;  k_pe_proj [rope][d_model] -> w_kr
+ *   fused_rope != 0, the layout of published DeepSeek-V2 checkpoints (the rope rows ride inside the two tensors):
+ *     q_proj [H * (nope + rope)][d_model], per head nope rows then rope rows -> w_q, w_qr
+ *     kv_a_proj_with_mqa [dC + rope][d_model], latent rows then the shared rope-key rows -> w_dkv, w_kr
+ * Sources are float32 or bf16 in host or device memory (src_dtype, src_mem); destinations are device bf16 buffers of the
+ * caller, the seven pointers of relux_mla_layer_weights.  A NULL source skips its destinations.  float32 values are
+ * rounded with the reference's rule (dtype_convert.go:15-24); bf16 values are moved bit for bit. */
+typedef struct relux_mla_import_args {
+  int32_t d_model, num_heads, nope_dim, rope_dim, v_dim, dc;
+  int32_t src_dtype, src_mem;
+  int32_t fused_rope;
+  int32_t reserved[3];
+  const void* q_proj;
+  const void* kv_a_proj_with_mqa;
+  const void* kv_b_proj;
+  const void* o_proj;
+  const void* q_pe_proj;                /* fused_rope == 0 only */
+  const void* k_pe_proj;                /* fused_rope == 0 only */
+  const relux_mla_layer_weights* dst;   /* device buffers */
+} relux_mla_import_args;
+int32_t relux_mla_import_weights(relux_pool_t pool, const relux_mla_import_args* args);
+
+/* Test aid for the bounded waits of the kernels: launches one warp that waits, through the same bounded mbarrier wait
+ * the attention kernels use, on a barrier nobody arrives at, with a poll limit of `polls`.  The wait gives up, the kernel
+ * records RELUX_ERR_TIMEOUT in the pool's status word and returns; relux_pool_status then reports it.  Nothing hangs and
+ * nothing faults.  No counterpart in the reference. */
+int32_t relux_pool_selftest_wait(relux_pool_t pool, int32_t polls);
 
 #ifdef __cplusplus
 }

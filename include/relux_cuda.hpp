@@ -112,7 +112,9 @@ class KVCache {
     const int t = TotalLen(layerIdx);
     if (t == 0) return false;
     std::vector<uint16_t> kt((size_t)t * hkv_ * d_), vt(kt.size());
-    check(relux_pool_read_rows(pool_, layerIdx, seq_, 0, t, kt.data(), vt.data()));
+    relux_read_rows_args rr{};
+    rr.layer = layerIdx; rr.seq_id = seq_; rr.tok0 = 0; rr.n_tokens = t; rr.dst_a = kt.data(); rr.dst_b = vt.data();
+    check(relux_pool_read_rows(pool_, &rr));
     k->resize(kt.size());
     v->resize(vt.size());
     for (int tok = 0; tok < t; tok++)
@@ -281,7 +283,9 @@ class MLACache {
     if (t == 0) return false;
     c->resize((size_t)t * dc_);
     kr->resize((size_t)t * dhr_);
-    check(relux_pool_read_rows(pool_, layerIdx, seq_, 0, t, c->data(), kr->data()));
+    relux_read_rows_args rr{};
+    rr.layer = layerIdx; rr.seq_id = seq_; rr.tok0 = 0; rr.n_tokens = t; rr.dst_a = c->data(); rr.dst_b = kr->data();
+    check(relux_pool_read_rows(pool_, &rr));
     return true;
   }
   void Reset() {

@@ -420,3 +420,53 @@ def spec_accept(cfg, draft_tokens, draft_logits, target_logits, draws):
     n = lib().ro_spec_accept(C.byref(cfg), _p(dt), _p(dl), _p(tl), C.c_int(k), C.c_int(V), _p(u), C.byref(nxt),
                              C.byref(used), _p(ap))
     return int(n), int(nxt.value), int(used.value), ap
+
+
+# ---- matmulBatched3D and the checkpoint -> relux weight layout ---------------------------------
+def matmul_batched3d(a, w_bf16):
+    """matmulBatched3D (internal/transformer/mha.go:759-785 -> nativeBackend.MatMulFloat32, internal/compute/native.go:175-187):
+    a [M, K] float32 x w [K, N] bf16 bits -> [M, N] float32, one k-ascending unfused multiply-add chain per output."""
+    a = f32(a)
+    w = np.ascontiguousarray(w_bf16, dtype=np.uint16)
+    out = np.empty((a.shape[0], w.shape[1]), np.float32)
+    fn = lib().ro_matmul_batched3d
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]
+    fn.restype = None
+    fn(_p(out), _p(a), _p(w), 1, a.shape[0], a.shape[1], w.shape[1])
+    return out
+
+
+def import_mla_weights(d_model, num_heads, nope_dim, rope_dim, v_dim, dc, q_proj=None, kv_a_proj_with_mqa=None, kv_b_proj=None,
+                       o_proj=None, q_pe_proj=None, k_pe_proj=None, fused_rope=False):
+    """Restatement (numpy) of what the reference's loader is specified to do with a DeepSeek MLA layer: every tensor is
+    stored [out, in] and marked Transpose: true (internal/loader/mapper.go:43-49, 139-180), converted to bf16 with
+    BF16FromF32 (loader.go:239-281, 394-404); kv_b_proj holds, per head, the nope rows of W_UK followed by the v rows of W_UV
+    (mapper.go:146-152).  Sources: float32 arrays or uint16 bf16 bits.  Returns a dict of uint16 arrays in relux's [in, out]
+    layout, keyed like relux_mla_layer_weights."""
+    def bits(x):
+        x = np.ascontiguousarray(x)
+        return x if x.dtype == np.uint16 else bf16_from_f32(x)
+
+    H, out = num_heads, {}
+    if q_proj is not None:
+        per = nope_dim + (rope_dim if fused_rope else 0)
+        q = bits(q_proj).reshape(H, per, d_model)
+        out["w_q"] = np.ascontiguousarray(q[:, :nope_dim].reshape(H * nope_dim, d_model).T)
+        if fused_rope:
+            out["w_qr"] = np.ascontiguousarray(q[:, nope_dim:].reshape(H * rope_dim, d_model).T)
+    if kv_a_proj_with_mqa is not None:
+        a = bits(kv_a_proj_with_mqa)
+        out["w_dkv"] = np.ascontiguousarray(a[:dc].T)
+        if fused_rope:
+            out["w_kr"] = np.ascontiguousarray(a[dc:dc + rope_dim].T)
+    if q_pe_proj is not None:
+        out["w_qr"] = np.ascontiguousarray(bits(q_pe_proj).T)
+    if k_pe_proj is not None:
+        out["w_kr"] = np.ascontiguousarray(bits(k_pe_proj).T)
+    if kv_b_proj is not None:
+        b = bits(kv_b_proj).reshape(H, nope_dim + v_dim, dc)
+        out["w_uk"] = np.ascontiguousarray(b[:, :nope_dim].reshape(H * nope_dim, dc).T)
+        out["w_uv"] = np.ascontiguousarray(b[:, nope_dim:].reshape(H * v_dim, dc).T)
+    if o_proj is not None:
+        out["w_o"] = np.ascontiguousarray(bits(o_proj).T)
+    return out

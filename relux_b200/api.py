@@ -170,14 +170,14 @@ class Pool:
     """Paged bf16 KV pool on one device (see relux_pool_create in include/relux_cuda.h)."""
 
     def __init__(self, dev, kind, num_layers, num_pages, page_tokens=64, max_seqs=1, max_pages_per_seq=None, dC=0, dHR=0,
-                 num_kv_heads=0, head_dim=0):
+                 num_kv_heads=0, head_dim=0, reference_compat=False):
         self.dev = dev
         self.lib = dev.lib
         if max_pages_per_seq is None:
             max_pages_per_seq = num_pages
         prm = L.PoolParams(kind=kind, num_layers=num_layers, num_pages=num_pages, page_tokens=page_tokens, max_seqs=max_seqs,
                            max_pages_per_seq=max_pages_per_seq, mla_dc=dC, mla_dhr=dHR, gqa_num_kv_heads=num_kv_heads,
-                           gqa_head_dim=head_dim)
+                           gqa_head_dim=head_dim, flags=L.POOL_FLAG_REFERENCE_COMPAT if reference_compat else 0)
         self.prm = prm
         self.kind = kind
         h = C.c_void_p()
@@ -232,8 +232,61 @@ class Pool:
         else:
             a = np.empty((n, p.gqa_num_kv_heads, p.gqa_head_dim), np.uint16)
             b = np.empty_like(a)
-        L.check(self.lib.relux_pool_read_rows(self.h, layer, seq, tok0, n, a.ctypes.data, b.ctypes.data))
+        args = L.ReadRowsArgs(layer=layer, seq_id=seq, tok0=tok0, n_tokens=n, dst_a=a.ctypes.data, dst_b=b.ctypes.data)
+        L.check(self.lib.relux_pool_read_rows(self.h, C.byref(args)))
         return a, b
+
+    def tune(self, knob, value):
+        """Sets one tuning knob (L.TUNE_*); a negative value restores the built-in default."""
+        L.check(self.lib.relux_pool_tune(self.h, int(knob), int(value)))
+
+    def matmul(self, a, w, n, out=None, mode=L.ATTN_FAST):
+        """C [M, N] float32 = a [M, K] float32 x w [K, N] bf16 on the device (ComputeBackend.MatMulFloat32 as
+        matmulBatched3D calls it: mha.go:759-785).  a / out: numpy arrays or device buffers; w: device buffer."""
+        if isinstance(a, DeviceBuffer):
+            raise TypeError("matmul: pass a as a numpy array, or call the C entry point with explicit sizes")
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        m, k = a.shape
+        res = np.empty((m, n), np.float32) if out is None else out
+        args = L.MatmulArgs(m=m, k=k, n=n, mode=mode, a=_ptr(a), a_mem=_mem(a), c_mem=_mem(res), b=_ptr(w), c=_ptr(res))
+        L.check(self.lib.relux_matmul_f32_bf16(self.h, C.byref(args)))
+        return res
+
+    def import_mla_weights(self, d_model, num_heads, nope_dim, rope_dim, v_dim, dc, dst, q_proj=None, kv_a_proj_with_mqa=None,
+                           kv_b_proj=None, o_proj=None, q_pe_proj=None, k_pe_proj=None, fused_rope=False):
+        """Splits and transposes one layer's DeepSeek-style checkpoint tensors (numpy float32 or uint16 bf16 bits, all of
+        one dtype) into the device buffers `dst` (dict w_q, w_qr, w_dkv, w_kr, w_uk, w_uv, w_o); see relux_mla_import_weights."""
+        srcs = [x for x in (q_proj, kv_a_proj_with_mqa, kv_b_proj, o_proj, q_pe_proj, k_pe_proj) if x is not None]
+        srcs = [np.ascontiguousarray(x) for x in srcs]
+        dt = {_dtype_flag(x) for x in srcs}
+        if len(dt) != 1:
+            raise TypeError("import_mla_weights: sources must share one dtype")
+        hold = {}
+
+        def src(x):
+            if x is None:
+                return None
+            x = np.ascontiguousarray(x)
+            hold[id(x)] = x
+            return x.ctypes.data
+
+        w = L.MlaLayerWeights(**{k: _ptr(dst.get(k)) for k in ("w_q", "w_qr", "w_dkv", "w_kr", "w_uk", "w_uv", "w_o")})
+        args = L.MlaImportArgs(d_model=d_model, num_heads=num_heads, nope_dim=nope_dim, rope_dim=rope_dim, v_dim=v_dim, dc=dc,
+                               src_dtype=dt.pop(), src_mem=L.MEM_HOST, fused_rope=int(fused_rope), q_proj=src(q_proj),
+                               kv_a_proj_with_mqa=src(kv_a_proj_with_mqa), kv_b_proj=src(kv_b_proj), o_proj=src(o_proj),
+                               q_pe_proj=src(q_pe_proj), k_pe_proj=src(k_pe_proj), dst=C.pointer(w))
+        L.check(self.lib.relux_mla_import_weights(self.h, C.byref(args)))
+
+    def selftest_wait(self, polls):
+        """Runs the bounded-wait self test (a wait nobody answers, `polls` polls): afterwards status() reports ERR_TIMEOUT."""
+        L.check(self.lib.relux_pool_selftest_wait(self.h, int(polls)))
+
+    def kernel_ms_list(self, last_n):
+        """Device times (ms) of the attention kernel of the most recent `last_n` decode / verify calls, oldest first."""
+        out = np.zeros(int(last_n), np.float32)
+        n = C.c_int32()
+        L.check(self.lib.relux_pool_kernel_ms_list(self.h, int(last_n), out.ctypes.data, C.byref(n)))
+        return out[:n.value]
 
     def _append_args(self, layer, a, b, n_seqs, seq_ids, n_new, layout, advance, dtype):
         ids = None if seq_ids is None else np.ascontiguousarray(seq_ids, dtype=np.int32)
@@ -409,13 +462,14 @@ class KVCache:
     """NewKVCacheSized(numLayers, maxLen, numKVHeads, headDim, BFloat16)   kvcache.go:66-93.
     One sequence, every layer; tensors follow the reference's shapes: K/V [1, numKVHeads, newLen, headDim]."""
 
-    def __init__(self, dev, num_layers, max_len, num_kv_heads, head_dim, page_tokens=64):
+    def __init__(self, dev, num_layers, max_len, num_kv_heads, head_dim, page_tokens=64, reference_compat=False):
         if num_layers <= 0:
             raise ValueError("NewKVCacheSized: numLayers=%d, must be > 0" % num_layers)
         if max_len <= 0:
             raise ValueError("NewKVCacheSized: maxLen=%d, must be > 0" % max_len)
         pages = (max_len + page_tokens - 1) // page_tokens
-        self.pool = Pool(dev, L.POOL_GQA, num_layers, pages, page_tokens, 1, pages, num_kv_heads=num_kv_heads, head_dim=head_dim)
+        self.pool = Pool(dev, L.POOL_GQA, num_layers, pages, page_tokens, 1, pages, num_kv_heads=num_kv_heads, head_dim=head_dim,
+                         reference_compat=reference_compat)
         self.seq = self.pool.seq_alloc(max_len)
         self.num_layers, self.max_len, self.num_kv_heads, self.head_dim = num_layers, max_len, num_kv_heads, head_dim
 
@@ -472,13 +526,13 @@ class KVCache:
 class MLACache:
     """NewMLACache(numLayers, maxLen, dC, dHR)   mla_cache.go:38-59 (rows are stored as bf16 here)."""
 
-    def __init__(self, dev, num_layers, max_len, dC, dHR, page_tokens=64):
+    def __init__(self, dev, num_layers, max_len, dC, dHR, page_tokens=64, reference_compat=False):
         if num_layers <= 0:
             raise ValueError("NewMLACache: numLayers=%d, must be > 0" % num_layers)
         if max_len <= 0:
             raise ValueError("NewMLACache: maxLen=%d, must be > 0" % max_len)
         pages = (max_len + page_tokens - 1) // page_tokens
-        self.pool = Pool(dev, L.POOL_MLA, num_layers, pages, page_tokens, 1, pages, dC=dC, dHR=dHR)
+        self.pool = Pool(dev, L.POOL_MLA, num_layers, pages, page_tokens, 1, pages, dC=dC, dHR=dHR, reference_compat=reference_compat)
         self.seq = self.pool.seq_alloc(max_len)
         self.num_layers, self.max_len, self.dC, self.dHR = num_layers, max_len, dC, dHR
 

@@ -53,9 +53,11 @@ __device__ __forceinline__ void advance_lengths_by_last_block(const AppendGeom& 
 
 // grid (n_seqs, row_slices).  One sequence's new rows are spread over blockIdx.y.
 // MLA row = [dC | dHR] fused, dC and dHR multiples of 8.
+// `shadow` (reference-compat pools only, else null): this layer's float32 copy of the rows, [page][token][dC + dHR] -- the
+// reference's MLA cache holds float32 (mla_cache.go:46-52, 171-176).
 template <bool kF32>
 __global__ void mla_append_kernel(AppendGeom g, uint16_t* __restrict__ layer_base, const void* __restrict__ ckv,
-                                  const void* __restrict__ kr, int dC, int dHR, int blocked) {
+                                  const void* __restrict__ kr, int dC, int dHR, int blocked, float* __restrict__ shadow) {
   const int i = blockIdx.x;
   const int seq = g.seq_ids ? g.seq_ids[i] : i;
   const int r0 = g.row_off ? g.row_off[i] : i;
@@ -75,6 +77,14 @@ __global__ void mla_append_kernel(AppendGeom g, uint16_t* __restrict__ layer_bas
       uint4 w = (v < vc) ? load8_as_bf16<kF32>(ckv, (size_t)(r0 + r) * dC + (size_t)v * 8)
                          : load8_as_bf16<kF32>(kr, (size_t)(r0 + r) * dHR + (size_t)(v - vc) * 8);
       *reinterpret_cast<uint4*>(page + mla_page_off(blocked != 0, g.page_tokens, row_elems, pos % g.page_tokens, v * 8)) = w;
+      if (shadow) {
+        float* srow = shadow + ((size_t)pg * g.page_tokens + pos % g.page_tokens) * row_elems + v * 8;
+        const void* sp = (v < vc) ? ckv : kr;
+        const size_t so = (v < vc) ? (size_t)(r0 + r) * dC + (size_t)v * 8 : (size_t)(r0 + r) * dHR + (size_t)(v - vc) * 8;
+#pragma unroll
+        for (int e = 0; e < 8; e++)
+          srow[e] = kF32 ? reinterpret_cast<const float*>(sp)[so + e] : f32_from_bf16_bits(reinterpret_cast<const uint16_t*>(sp)[so + e]);
+      }
     }
   }
   advance_lengths_by_last_block(g);
@@ -146,10 +156,11 @@ int32_t launch_mla_append(Pool* p, const SeqBatch& sb, int layer, const void* ck
   uint16_t* base = p->storage + (size_t)layer * p->layer_elems;
   dim3 grid(sb.n_seqs, std::min(std::max(sb.max_rows, 1), 64));
   int threads = 96;  // 72 vectors per 576-element row
+  float* shadow = p->shadow_f32 ? p->shadow_f32 + (size_t)layer * p->layer_elems : nullptr;
   if (dtype == RELUX_DTYPE_F32)
-    mla_append_kernel<true><<<grid, threads, 0, p->dev->stream>>>(g, base, ckv, kr, p->prm.mla_dc, p->prm.mla_dhr, p->mla_blocked);
+    mla_append_kernel<true><<<grid, threads, 0, p->dev->stream>>>(g, base, ckv, kr, p->prm.mla_dc, p->prm.mla_dhr, p->mla_blocked, shadow);
   else
-    mla_append_kernel<false><<<grid, threads, 0, p->dev->stream>>>(g, base, ckv, kr, p->prm.mla_dc, p->prm.mla_dhr, p->mla_blocked);
+    mla_append_kernel<false><<<grid, threads, 0, p->dev->stream>>>(g, base, ckv, kr, p->prm.mla_dc, p->prm.mla_dhr, p->mla_blocked, shadow);
   return finish_append(p);
 }
 

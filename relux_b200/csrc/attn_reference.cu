@@ -8,6 +8,19 @@
 //   * MLA decompresses each latent row with W_UK / W_UV first (mla.go:323-326) instead of absorbing.
 // One CTA per (head, sequence); the score rows live in shared memory, which bounds q_tokens * T.
 // Meant for the small models where greedy token ids are compared, not for speed.
+//
+// RELUX_ATTN_REFERENCE_FAITHFUL adds the reference's own indexing on top of the same arithmetic:
+//   GQA  the cache stream is written chunk by chunk (one chunk per Append, head-major inside the chunk,
+//        kvcache.go:407-438) and read as [numKVHeads][T][headDim] (mha.go:299-312): logical (kv head h, position j)
+//        is stream row r = h*T + j, which lies in the chunk c with Hkv*P_c <= r < Hkv*P_(c+1) and holds the row that
+//        chunk's head (r - Hkv*P_c) / len_c wrote for token P_c + (r - Hkv*P_c) % len_c;
+//   MLA  kcAll / vAll are [T][H][headDim] but indexed as [H][T][headDim] (mla.go:323-326 vs :348, 351): logical
+//        (head h, position j) reads token (h*T + j) / H with the up-projection columns of head (h*T + j) % H; the
+//        rope part is indexed correctly (mla.go:329-336); latent rows are the float32 values that were appended;
+//   mask only when q_tokens == T (mha.go:340, mla.go:368).
+#include <algorithm>
+#include <vector>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -23,7 +36,20 @@ struct RefGeom {
   int32_t S, extra, causal, H;
   float scale;
   int32_t blocked;   // MLA page layout (see mla_page_off)
+  // RELUX_ATTN_REFERENCE_FAITHFUL
+  int32_t faithful;
+  const int32_t* chunk_tab;   // GQA: per sequence of the call [count, P_0 .. P_(count-1)]
+  int32_t chunk_stride;
+  const float* shadow;        // MLA: float32 rows of this layer, [page][token][dC + dHR]
 };
+
+// Masked under the intended rule (row s of the S new rows sees positions <= T - S + s); the reference's own rule applies
+// that mask only when the call covers the whole cache (S == T).
+__device__ __forceinline__ bool ref_masked(const RefGeom& g, int T, int S, int s, int j) {
+  if (!g.causal) return false;
+  if (g.faithful && S != T) return false;
+  return j > T - S + s;
+}
 
 // Shared tail: softmaxRows over w[S][T] and nothing else; all threads of the CTA call it.
 __device__ void softmax_rows_ref(float* w, int S, int T, float* red) {
@@ -70,17 +96,38 @@ __global__ void gqa_reference_kernel(RefGeom g, const uint16_t* __restrict__ k_b
   const int T = g.len[seq] + g.extra;
   const int S = g.S, kvh = h / (g.H / Hkv);
   float* w = smem;  // [S][T]
+  int32_t* src = reinterpret_cast<int32_t*>(smem + (size_t)S * T);   // [T] physical (kv head << 20 | token) of logical position j
   const int tid = threadIdx.x, nt = blockDim.x;
   for (int j = tid; j < T; j += nt) {
+    int ph = kvh, pt = j;
+    if (g.faithful) {
+      const int32_t* ct = g.chunk_tab + (size_t)i * g.chunk_stride;
+      const int nc = ct[0];
+      const int r = kvh * T + j;
+      int lo = 0, hi = nc - 1;   // last chunk whose first stream row Hkv * P_c is <= r
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (Hkv * ct[1 + mid] <= r) lo = mid; else hi = mid - 1;
+      }
+      const int P = ct[1 + lo], len = ((lo + 1 < nc) ? ct[2 + lo] : T) - P;
+      const int rr = r - Hkv * P;
+      ph = rr / len;
+      pt = P + rr % len;
+    }
+    src[j] = (ph << 20) | pt;
+  }
+  __syncthreads();
+  for (int j = tid; j < T; j += nt) {
+    const int ph = src[j] >> 20, pt = src[j] & 0xFFFFF;
     int32_t pg;
-    bool ok = page_of(g.table, g.table_stride, seq, j / g.page_tokens, g.num_pages, g.status, &pg);
-    const uint16_t* kr = k_base + (size_t)(ok ? pg : 0) * Hkv * g.page_tokens * D + ((size_t)kvh * g.page_tokens + (j % g.page_tokens)) * D;
+    bool ok = page_of(g.table, g.table_stride, seq, pt / g.page_tokens, g.num_pages, g.status, &pg);
+    const uint16_t* kr = k_base + (size_t)(ok ? pg : 0) * Hkv * g.page_tokens * D + ((size_t)ph * g.page_tokens + (pt % g.page_tokens)) * D;
     for (int s = 0; s < S; s++) {
       const float* qv = q + (((size_t)i * S + s) * g.H + h) * D;
       float sum = 0.0f;
       for (int d = 0; d < D; d++) sum = __fadd_rn(sum, __fmul_rn(qv[d], f32_from_bf16_bits(kr[d])));
       float v = __fmul_rn(sum, g.scale);
-      if (g.causal && j > T - S + s) v = -INFINITY;
+      if (ref_masked(g, T, S, s, j)) v = -INFINITY;
       w[(size_t)s * T + j] = ok ? v : -INFINITY;
     }
   }
@@ -90,9 +137,10 @@ __global__ void gqa_reference_kernel(RefGeom g, const uint16_t* __restrict__ k_b
     const int s = e / D, d = e % D;
     float o = 0.0f;
     for (int j = 0; j < T; j++) {
-      int32_t pg = g.table[(size_t)seq * g.table_stride + j / g.page_tokens];
+      const int ph = src[j] >> 20, pt = src[j] & 0xFFFFF;
+      int32_t pg = g.table[(size_t)seq * g.table_stride + pt / g.page_tokens];
       if (pg < 0 || pg >= g.num_pages) continue;
-      const uint16_t* vr = v_base + (size_t)pg * Hkv * g.page_tokens * D + ((size_t)kvh * g.page_tokens + (j % g.page_tokens)) * D;
+      const uint16_t* vr = v_base + (size_t)pg * Hkv * g.page_tokens * D + ((size_t)ph * g.page_tokens + (pt % g.page_tokens)) * D;
       o = __fadd_rn(o, __fmul_rn(w[(size_t)s * T + j], f32_from_bf16_bits(vr[d])));
     }
     out[(((size_t)i * S + s) * g.H + h) * D + d] = o;
@@ -112,12 +160,21 @@ __global__ void mla_reference_kernel(RefGeom g, const uint16_t* __restrict__ bas
   float* w = smem;  // [S][T]
   const int tid = threadIdx.x, nt = blockDim.x;
   const size_t wstride = (size_t)H * Dh;
+  const bool blk = g.blocked != 0;
+  // value of column c of the cached row of token t: the bf16 page, or the float32 copy in faithful mode
+  auto cached = [&](int32_t pg, int t, int c) -> float {
+    const int tk = t % g.page_tokens;
+    if (g.shadow) return g.shadow[((size_t)pg * g.page_tokens + tk) * row + c];
+    return f32_from_bf16_bits(base[(size_t)pg * g.page_tokens * row + mla_page_off(blk, g.page_tokens, row, tk, c)]);
+  };
   for (int j = tid; j < T; j += nt) {
-    int32_t pg;
+    // content part: logical (h, j) -> physical (token tp, head hp)
+    const int r = h * T + j;
+    const int tp = g.faithful ? r / H : j, hp = g.faithful ? r % H : h;
+    int32_t pg, pgc;
     bool ok = page_of(g.table, g.table_stride, seq, j / g.page_tokens, g.num_pages, g.status, &pg);
-    const uint16_t* page = base + (size_t)(ok ? pg : 0) * g.page_tokens * row;
-    const int tk = j % g.page_tokens;
-    const bool blk = g.blocked != 0;
+    ok = page_of(g.table, g.table_stride, seq, tp / g.page_tokens, g.num_pages, g.status, &pgc) && ok;
+    if (!ok) pg = pgc = 0;
     for (int s = 0; s < S; s++) {
       const float* qcv = qc + (((size_t)i * S + s) * H + h) * Dh;
       const float* qrv = qr + (((size_t)i * S + s) * H + h) * dHR;
@@ -126,15 +183,13 @@ __global__ void mla_reference_kernel(RefGeom g, const uint16_t* __restrict__ bas
       for (int d = 0; d < Dh; d++) {
         float kc = 0.0f;
         for (int c = 0; c < dC; c++)
-          kc = __fadd_rn(kc, __fmul_rn(f32_from_bf16_bits(page[mla_page_off(blk, g.page_tokens, row, tk, c)]),
-                                       f32_from_bf16_bits(W_UK[(size_t)c * wstride + (size_t)h * Dh + d])));
+          kc = __fadd_rn(kc, __fmul_rn(cached(pgc, tp, c), f32_from_bf16_bits(W_UK[(size_t)c * wstride + (size_t)hp * Dh + d])));
         a = __fadd_rn(a, __fmul_rn(qcv[d], kc));
       }
-      float r = 0.0f;
-      for (int d = 0; d < dHR; d++)
-        r = __fadd_rn(r, __fmul_rn(qrv[d], f32_from_bf16_bits(page[mla_page_off(blk, g.page_tokens, row, tk, dC + d)])));
-      float v = __fmul_rn(__fadd_rn(a, r), g.scale);
-      if (g.causal && j > T - S + s) v = -INFINITY;
+      float rsum = 0.0f;
+      for (int d = 0; d < dHR; d++) rsum = __fadd_rn(rsum, __fmul_rn(qrv[d], cached(pg, j, dC + d)));
+      float v = __fmul_rn(__fadd_rn(a, rsum), g.scale);
+      if (ref_masked(g, T, S, s, j)) v = -INFINITY;
       w[(size_t)s * T + j] = ok ? v : -INFINITY;
     }
   }
@@ -144,14 +199,13 @@ __global__ void mla_reference_kernel(RefGeom g, const uint16_t* __restrict__ bas
     const int s = e / Dh, d = e % Dh;
     float o = 0.0f;
     for (int j = 0; j < T; j++) {
-      int32_t pg = g.table[(size_t)seq * g.table_stride + j / g.page_tokens];
+      const int r = h * T + j;
+      const int tp = g.faithful ? r / H : j, hp = g.faithful ? r % H : h;
+      int32_t pg = g.table[(size_t)seq * g.table_stride + tp / g.page_tokens];
       if (pg < 0 || pg >= g.num_pages) continue;
-      const uint16_t* page = base + (size_t)pg * g.page_tokens * row;
-      const int tk = j % g.page_tokens;
       float vv = 0.0f;
       for (int c = 0; c < dC; c++)
-        vv = __fadd_rn(vv, __fmul_rn(f32_from_bf16_bits(page[mla_page_off(g.blocked != 0, g.page_tokens, row, tk, c)]),
-                                     f32_from_bf16_bits(W_UV[(size_t)c * wstride + (size_t)h * Dh + d])));
+        vv = __fadd_rn(vv, __fmul_rn(cached(pg, tp, c), f32_from_bf16_bits(W_UV[(size_t)c * wstride + (size_t)hp * Dh + d])));
       o = __fadd_rn(o, __fmul_rn(w[(size_t)s * T + j], vv));
     }
     out[(((size_t)i * S + s) * H + h) * Dh + d] = o;
@@ -162,7 +216,7 @@ static int32_t ref_geom(Pool* p, const SeqBatch& sb, const relux_attn_args& a, R
   const relux_pool_params& prm = p->prm;
   int maxT = 0;
   for (int i = 0; i < sb.n_seqs; i++) maxT = std::max(maxT, p->h_len[(size_t)a.layer * prm.max_seqs + sb.seq[i]] + a.extra_tokens);
-  size_t need = (size_t)a.q_tokens * maxT * sizeof(float);
+  size_t need = ((size_t)a.q_tokens + 1) * maxT * sizeof(float);   // scores, and one index per position (GQA)
   if (need > 200 * 1024) {
     set_error("RELUX_ATTN_REFERENCE keeps q_tokens*T=%d*%d scores in shared memory; the limit is 51200", a.q_tokens, maxT);
     return RELUX_ERR_UNSUPPORTED;
@@ -181,6 +235,35 @@ static int32_t ref_geom(Pool* p, const SeqBatch& sb, const relux_attn_args& a, R
   g->H = a.num_heads;
   g->scale = a.scale;
   g->blocked = p->mla_blocked ? 1 : 0;
+  g->faithful = a.mode == RELUX_ATTN_REFERENCE_FAITHFUL ? 1 : 0;
+  g->chunk_tab = nullptr;
+  g->chunk_stride = 0;
+  g->shadow = nullptr;
+  return RELUX_OK;
+}
+
+// Chunk starts of the call's sequences -> device, [n_seqs][1 + max chunks]: count, then P_0 .. P_(count-1).
+static int32_t stage_chunks(Pool* p, const SeqBatch& sb, int layer, RefGeom* g) {
+  size_t most = 1;
+  for (int i = 0; i < sb.n_seqs; i++) most = std::max(most, p->chunks[(size_t)layer * p->prm.max_seqs + sb.seq[i]].size());
+  const size_t stride = most + 1;
+  std::vector<int32_t> tab((size_t)sb.n_seqs * stride, 0);
+  for (int i = 0; i < sb.n_seqs; i++) {
+    const std::vector<int32_t>& c = p->chunks[(size_t)layer * p->prm.max_seqs + sb.seq[i]];
+    if (c.empty() || c[0] != 0) {
+      set_error("sequence %d has cached rows that no Append call of this pool wrote; the chunk history needed by "
+                "RELUX_ATTN_REFERENCE_FAITHFUL is incomplete", sb.seq[i]);
+      return RELUX_ERR_INVALID_ARG;
+    }
+    tab[i * stride] = (int32_t)c.size();
+    std::copy(c.begin(), c.end(), tab.begin() + i * stride + 1);
+  }
+  int32_t rc = grow(p->dev, p->chunk_tab, tab.size() * 4);
+  if (rc) return rc;
+  RELUX_CUDA_TRY(cudaMemcpyAsync(p->chunk_tab.p, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, p->dev->stream));
+  RELUX_CUDA_TRY(cudaStreamSynchronize(p->dev->stream));   // `tab` is pageable and goes out of scope
+  g->chunk_tab = (const int32_t*)p->chunk_tab.p;
+  g->chunk_stride = (int32_t)stride;
   return RELUX_OK;
 }
 
@@ -189,6 +272,7 @@ int32_t launch_attn_reference_gqa(Pool* p, const SeqBatch& sb, const relux_attn_
   size_t smem;
   int32_t rc = ref_geom(p, sb, a, &g, &smem);
   if (rc) return rc;
+  if (g.faithful && (rc = stage_chunks(p, sb, a.layer, &g))) return rc;
   const uint16_t* kb = p->storage + (size_t)a.layer * p->layer_elems;
   const uint16_t* vb = kb + p->page_elems * p->prm.num_pages;
   if (smem > 48 * 1024) RELUX_CUDA_TRY(cudaFuncSetAttribute(gqa_reference_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -209,6 +293,7 @@ int32_t launch_attn_reference_mla(Pool* p, const SeqBatch& sb, const relux_attn_
   int32_t rc = ref_geom(p, sb, a, &g, &smem);
   if (rc) return rc;
   const uint16_t* base = p->storage + (size_t)a.layer * p->layer_elems;
+  if (g.faithful) g.shadow = p->shadow_f32 + (size_t)a.layer * p->layer_elems;
   if (smem > 48 * 1024) RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_reference_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(a.num_heads, sb.n_seqs);
   RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), p->dev->stream));

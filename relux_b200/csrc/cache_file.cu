@@ -48,7 +48,9 @@ extern "C" __attribute__((visibility("default"))) int32_t relux_seq_save_file(re
     a.assign((size_t)n * wa, 0);
     b.assign((size_t)n * wb, 0);
     if (n > 0) {
-      int32_t rc = relux_pool_read_rows(h, l, seq, 0, n, a.data(), b.data());
+      relux_read_rows_args rr{};
+      rr.layer = l; rr.seq_id = seq; rr.tok0 = 0; rr.n_tokens = n; rr.dst_a = a.data(); rr.dst_b = b.data();
+      int32_t rc = relux_pool_read_rows(h, &rr);
       if (rc) return rc;
     }
     if (mla) {

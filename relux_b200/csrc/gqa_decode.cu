@@ -385,8 +385,7 @@ static int32_t launch_gqa_prompt(Pool* p, const SeqBatch& sb, const relux_attn_a
   const int rows_total = per_group * a.num_heads;
   const size_t group_rows = (size_t)plan.num_items * rows_total;
   const size_t group_bytes = group_rows * kD * sizeof(float);
-  size_t budget = (size_t)256 << 20;
-  if (const char* e = getenv("RELUX_GQA_PROMPT_PARTIAL_MB")) budget = (size_t)std::max(1, atoi(e)) << 20;   // tuning / test aid
+  const size_t budget = (size_t)std::max(1, p->tune.get(RELUX_TUNE_GQA_PROMPT_PARTIAL_MB)) << 20;   // tuning / test knob
   const int zmax = (int)std::max<size_t>(1, std::min<size_t>({(size_t)groups, (size_t)65535, budget / std::max<size_t>(1, group_bytes)}));
   rc = grow(p->dev, p->part_o, (size_t)zmax * group_bytes);
   if (rc) return rc;
@@ -458,13 +457,6 @@ int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   // (a prompt) are cut into groups of tokens that run as the z slices of one grid
   const int per_group = std::max(1, 32 / g);
   if (a.q_tokens <= per_group) return launch_gqa_group(p, sb, a, d_q, d_out, 0, a.q_tokens);
-  if (getenv("RELUX_GQA_PROMPT_SERIAL")) {   // measurement aid: one launch per group, as before the grouped launch existed
-    for (int s0 = 0; s0 < a.q_tokens; s0 += per_group) {
-      int32_t rc = launch_gqa_group(p, sb, a, d_q, d_out, s0, std::min(per_group, a.q_tokens - s0));
-      if (rc) return rc;
-    }
-    return RELUX_OK;
-  }
   return launch_gqa_prompt(p, sb, a, d_q, d_out, per_group);
 }
 
@@ -521,6 +513,10 @@ extern "C" __attribute__((visibility("default"))) int32_t relux_gqa_decode_noall
       (a->q_tokens > 1 && (a->q_layout != RELUX_LAYOUT_TOKEN_MAJOR || a->out_layout != RELUX_LAYOUT_TOKEN_MAJOR))) {
     set_error("relux_gqa_decode_noalloc takes device-resident token-major q (f32 or bf16) and writes device-resident f32 output, FAST mode only");
     return RELUX_ERR_UNSUPPORTED;
+  }
+  {
+    int32_t rca;
+    if ((rca = check_dev_align(a->q, "q")) || (rca = check_dev_align(a->out, "out"))) return rca;
   }
   const int g = a->num_heads / prm.gqa_num_kv_heads, R = g * a->q_tokens;
   if (!p->has_tmap || prm.page_tokens != kPageTok || prm.gqa_head_dim != kD || R > 32) {

@@ -50,10 +50,20 @@ struct GrowBuf {
   size_t cap = 0;
 };
 
+// Tuning knobs of a pool.  Defaults come from the environment ONCE, when the pool is created (RELUX_MLA_GENERIC,
+// RELUX_MLA_WORKERS, RELUX_CHUNK_PAGES, RELUX_GEMM_GENERIC, RELUX_GEMM_SPLIT, RELUX_GQA_PROMPT_PARTIAL_MB,
+// RELUX_SEL_CLUSTER, RELUX_SEL_LOOKAHEAD, RELUX_SEL_BATCHED); relux_pool_tune changes them afterwards.  No launch path
+// reads the environment.
+struct Tuning {
+  int32_t v[RELUX_TUNE_COUNT];
+  int32_t get(int knob) const { return v[knob]; }
+};
+
 struct Pool {
   uint32_t magic = kPoolMagic;
   Device* dev = nullptr;
   relux_pool_params prm{};
+  Tuning tune{};
   int row_elems_a = 0;  // MLA: dC + dHR (one fused row); GQA: head_dim
   size_t page_elems = 0;    // elements per page per tensor (MLA: P*(dC+dHR); GQA: Hkv*P*D for K, same for V)
   size_t layer_elems = 0;   // elements per layer (GQA: K then V)
@@ -64,7 +74,17 @@ struct Pool {
   std::vector<int32_t> h_table, h_len;
   std::vector<int32_t> seq_pages;  // pages reserved per sequence (capacity), 0 = slot not live
   std::vector<uint8_t> seq_owned;  // 1 = table rows were filled by relux_seq_alloc
+  bool caller_tables = false;      // relux_pool_set_tables filled the tables: the free list stays unused until a reset
   std::vector<int32_t> free_pages;
+  std::vector<uint32_t> seq_stamp;  // duplicate-id detection of stage_batch: call number that last named the sequence
+  uint32_t stamp = 0;
+  // reference-compat pools (RELUX_POOL_FLAG_REFERENCE_COMPAT): what the quirk-faithful attention mode needs
+  bool compat = false;
+  float* shadow_f32 = nullptr;   // MLA: float32 copy of every appended row, [layer][page][token][dC + dHR] (the reference's cache
+                                 // is float32, mla_cache.go:46-52)
+  std::vector<std::vector<int32_t>> chunks;   // GQA: per (layer, sequence) the first row of every Append call (kvcache.go:407-438
+                                              // writes chunk-linear; mha.go:299-312 reads head-major)
+  GrowBuf chunk_tab;             // device staging of the chunk starts of one call's sequences
   // per-call staging of small host arrays (seq ids, row offsets)
   int32_t* d_seq_ids = nullptr;  // [max_seqs]
   int32_t* d_row_off = nullptr;  // [max_seqs + 1]
@@ -94,14 +114,20 @@ struct Pool {
   int rope_dim = 0, rope_positions = 0;
   float rope_base = 0.f;
   // timing of the dominant kernel: a ring of event pairs, one pair per attention call, so that a caller can read
-  // the device times of its last kTimeRing calls after the fact without a synchronisation between them
-  static constexpr int kTimeRing = 256;
+  // the device times of its last kTimeRing calls after the fact without a synchronisation between them.  The events
+  // of a slot are created the first time the slot is used.
+  static constexpr int kTimeRing = 8192;
   cudaEvent_t ev_ring[kTimeRing][2] = {};
   uint64_t timed_calls = 0;
   cudaEvent_t proj_ring[kTimeRing][2] = {};   // same, around the input-projection GEMM of the layer step
   uint64_t proj_calls = 0;
-  cudaEvent_t ev_begin() const { return ev_ring[timed_calls % kTimeRing][0]; }
-  cudaEvent_t ev_end() const { return ev_ring[timed_calls % kTimeRing][1]; }
+  static cudaEvent_t ring_event(cudaEvent_t (*ring)[2], uint64_t call, int which) {
+    cudaEvent_t& e = ring[call % kTimeRing][which];
+    if (!e && cudaEventCreate(&e) != cudaSuccess) { (void)cudaGetLastError(); e = nullptr; }
+    return e;
+  }
+  cudaEvent_t ev_begin() { return ring_event(ev_ring, timed_calls, 0); }
+  cudaEvent_t ev_end() { return ring_event(ev_ring, timed_calls, 1); }
 };
 
 inline Device* as_device(relux_device_t h) {
@@ -148,7 +174,15 @@ int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a);
 int32_t do_gqa_layer(Pool* p, const relux_gqa_layer_args* a);
 int32_t do_spec_accept(Pool* p, const relux_spec_accept_args* a);
 int32_t do_sample(Pool* p, const relux_sample_args* a);
+int32_t do_matmul(Pool* p, const relux_matmul_args* a);
+int32_t do_import_mla(Pool* p, const relux_mla_import_args* a);
+int32_t do_selftest_wait(Pool* p, int32_t polls);
 int32_t seq_set_len(Pool* p, int32_t layer, int32_t n_seqs, const int32_t* seq_ids, const int32_t* new_len);
+// Chunk bookkeeping of reference-compat pools (no-ops otherwise): an append of n rows at old_len, a length change.
+void note_append(Pool* p, int layer, int seq, int old_len, int n);
+void note_set_len(Pool* p, int layer, int seq, int old_len, int new_len);
+// Host pointers handed over as device memory must be 16-byte aligned: the kernels read them with vector loads.
+int32_t check_dev_align(const void* ptr, const char* what);
 
 inline void count_launch(Device* d, int n = 1) { d->launches += n; }
 

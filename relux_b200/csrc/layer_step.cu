@@ -215,6 +215,7 @@ struct FinishParams {
   const float* rope_cos;           // [positions][rope_dim / 2]
   const float* rope_sin;
   int32_t rope_positions;
+  int32_t same_pos;                // the reference's own rule (rope.go:151-158): on a non-empty cache every new row takes position len
   int32_t* status;
 };
 __global__ void proj_finish_kernel(const FinishParams p) {
@@ -236,7 +237,8 @@ __global__ void proj_finish_kernel(const FinishParams p) {
   if (sg.rope_dim > 0) {
     const int i = m / p.S, s = m % p.S;
     const int seq = p.seq_ids ? p.seq_ids[i] : i;
-    const int pos = p.len[seq] + s;
+    const int len0 = p.len[seq];
+    const int pos = (p.same_pos && len0 > 0) ? len0 : len0 + s;
     if (pos >= p.rope_positions) {
       set_status(p.status, RELUX_ERR_OVERFLOW);   // the reference panics: position >= maxSeqLen (rope.go:160-162)
     } else {
@@ -312,7 +314,7 @@ int32_t launch_skinny_gemm(Pool* p, const uint16_t* a_bf16, int M, int K, const 
       best = s;
     }
   }
-  if (const char* ov = getenv("RELUX_GEMM_SPLIT")) best = std::max(1, std::min(max_split, atoi(ov)));   // tuning aid
+  if (const int ov = p->tune.get(RELUX_TUNE_GEMM_SPLIT)) best = std::max(1, std::min(max_split, ov));   // tuning knob
   g.split_k = best;
   g.part = part;
   g.status = p->d_status;
@@ -326,7 +328,6 @@ int32_t launch_skinny_gemm(Pool* p, const uint16_t* a_bf16, int M, int K, const 
 }
 
 bool gemm_sm100_eligible(int K, const WeightRef* ws, int nw) {
-  if (getenv("RELUX_GEMM_GENERIC")) return false;
   if (K % 8 != 0 || nw > kMaxWeights) return false;
   for (int j = 0; j < nw; j++)
     if (ws[j].n % 8 != 0 || ((uintptr_t)ws[j].w & 15) != 0) return false;
@@ -371,12 +372,12 @@ int32_t ensure_rope_table(Pool* p, int dHR, float base, int positions) {
 // x [M][K] f32 -> every segment's buffer: cast + split-K tensor-core GEMM (or the reference-order GEMM), then the
 // finish kernel.  `proj_timing` records the event pair of the GEMM launch in the pool's projection ring.
 int32_t project_and_finish(Pool* p, const SeqBatch& sb, int layer, const float* dx, int M, int K, int S, const WeightRef* ws,
-                           const ProjSeg* segs, int nw, bool mma, uint16_t* a_bf16, float* part, size_t part_cap) {
+                           const ProjSeg* segs, int nw, bool mma, uint16_t* a_bf16, float* part, size_t part_cap, bool same_pos = false) {
   cudaStream_t st = p->dev->stream;
   int n_total = 0;
   for (int j = 0; j < nw; j++) n_total += ws[j].n;
   int split = 1;
-  cudaEvent_t* evs = p->proj_ring[p->proj_calls % Pool::kTimeRing];
+  cudaEvent_t evs[2] = {Pool::ring_event(p->proj_ring, p->proj_calls, 0), Pool::ring_event(p->proj_ring, p->proj_calls, 1)};
   if (mma) {
     const size_t n8 = (size_t)M * K / 8;
     cast_bf16_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, st>>>(dx, a_bf16, n8);
@@ -412,6 +413,7 @@ int32_t project_and_finish(Pool* p, const SeqBatch& sb, int layer, const float* 
   f.rope_cos = (const float*)p->rope_tab.p;
   f.rope_sin = f.rope_cos ? f.rope_cos + (size_t)p->rope_positions * (rope_dim / 2) : nullptr;
   f.rope_positions = p->rope_positions;
+  f.same_pos = same_pos ? 1 : 0;
   f.status = p->d_status;
   dim3 grid((n_total / 2 + 255) / 256, M);
   proj_finish_kernel<<<grid, 256, 0, st>>>(f);
@@ -520,7 +522,9 @@ int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a) {
     return RELUX_ERR_INVALID_ARG;
   }
   if (dHR % 2 != 0) { set_error("NewMLA: dHR=%d must be even for paired RoPE rotation", dHR); return RELUX_ERR_INVALID_ARG; }
-  if (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE) { set_error("bad mode"); return RELUX_ERR_INVALID_ARG; }
+  if (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE && a->mode != RELUX_ATTN_REFERENCE_FAITHFUL) { set_error("bad mode"); return RELUX_ERR_INVALID_ARG; }
+  const bool faithful = a->mode == RELUX_ATTN_REFERENCE_FAITHFUL;
+  if (faithful && !p->compat) { set_error("RELUX_ATTN_REFERENCE_FAITHFUL needs a pool created with RELUX_POOL_FLAG_REFERENCE_COMPAT"); return RELUX_ERR_INVALID_ARG; }
   if (a->x_dtype != RELUX_DTYPE_F32) { set_error("x must be float32"); return RELUX_ERR_UNSUPPORTED; }
   const int Dh = D / H;
   const float rope_base = a->rope_base == 0.f ? 10000.f : a->rope_base;   // NewMLA, mla.go:78-80
@@ -538,7 +542,7 @@ int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a) {
   const WeightRef outp[1] = {{w.w_o, D}};
   const int n_total = H * Dh + H * dHR + dC + dHR;
   const bool fast = a->mode == RELUX_ATTN_FAST;
-  const bool mma = fast && gemm_sm100_eligible(D, proj, 4) && gemm_sm100_eligible(H * Dh, outp, 1);
+  const bool mma = fast && !p->tune.get(RELUX_TUNE_GEMM_GENERIC) && gemm_sm100_eligible(D, proj, 4) && gemm_sm100_eligible(H * Dh, outp, 1);
   const size_t q_es = fast ? 2 : 4;
   const size_t b_qc = pad256((size_t)M * H * Dh * q_es), b_qr = pad256((size_t)M * H * dHR * q_es), b_c = pad256((size_t)M * dC * 4),
                b_kr = pad256((size_t)M * dHR * 4);
@@ -552,12 +556,16 @@ int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a) {
   float* d_attn = (float*)(sc.rest + b_qc + b_qr + b_c + b_kr);
   // 1 + 2. projections, RoPE on q^R and k^R
   const ProjSeg segs[4] = {{H * Dh, 0, d_qc, fast ? 1 : 0}, {H * dHR, dHR, d_qr, fast ? 1 : 0}, {dC, 0, d_c, 0}, {dHR, dHR, d_kr, 0}};
-  rc = project_and_finish(p, sb, a->layer, (const float*)dx, M, D, S, proj, segs, 4, mma, sc.a_bf16, sc.part, sc.part_cap);
+  rc = project_and_finish(p, sb, a->layer, (const float*)dx, M, D, S, proj, segs, 4, mma, sc.a_bf16, sc.part, sc.part_cap, faithful);
   if (rc) return rc;
   // 3. append (advances the cursors)
   rc = launch_mla_append(p, sb, a->layer, d_c, d_kr, RELUX_DTYPE_F32, 1);
   if (rc) return rc;
-  for (int i = 0; i < sb.n_seqs; i++) p->h_len[(size_t)a->layer * prm.max_seqs + sb.seq[i]] += S;
+  for (int i = 0; i < sb.n_seqs; i++) {
+    int32_t& len = p->h_len[(size_t)a->layer * prm.max_seqs + sb.seq[i]];
+    note_append(p, a->layer, sb.seq[i], len, S);
+    len += S;
+  }
   // 4. attention over the cache, the S new rows included
   relux_attn_args aa;
   memset(&aa, 0, sizeof(aa));
@@ -599,7 +607,9 @@ int32_t do_gqa_layer(Pool* p, const relux_gqa_layer_args* a) {
     return RELUX_ERR_INVALID_ARG;
   }
   if (a->rope && hd % 2 != 0) { set_error("NewRotaryEmbedding: headDim=%d, must be even and > 0", hd); return RELUX_ERR_INVALID_ARG; }
-  if (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE) { set_error("bad mode"); return RELUX_ERR_INVALID_ARG; }
+  if (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE && a->mode != RELUX_ATTN_REFERENCE_FAITHFUL) { set_error("bad mode"); return RELUX_ERR_INVALID_ARG; }
+  const bool faithful = a->mode == RELUX_ATTN_REFERENCE_FAITHFUL;
+  if (faithful && (!p->compat || !a->advance)) { set_error("RELUX_ATTN_REFERENCE_FAITHFUL needs a pool created with RELUX_POOL_FLAG_REFERENCE_COMPAT and advance != 0"); return RELUX_ERR_INVALID_ARG; }
   if (a->x_dtype != RELUX_DTYPE_F32) { set_error("x must be float32"); return RELUX_ERR_UNSUPPORTED; }
   if (a->mode == RELUX_ATTN_FAST && (!p->has_tmap || prm.page_tokens != 64 || hd != 128 || H / Hkv > 32)) {
     // checked before anything is written to the cache
@@ -623,7 +633,7 @@ int32_t do_gqa_layer(Pool* p, const relux_gqa_layer_args* a) {
   const WeightRef outp[1] = {{w.w_o, D}};
   const int n_total = (H + 2 * Hkv) * hd;
   const bool fast = a->mode == RELUX_ATTN_FAST;
-  const bool mma = fast && gemm_sm100_eligible(D, proj, 3) && gemm_sm100_eligible(H * hd, outp, 1);
+  const bool mma = fast && !p->tune.get(RELUX_TUNE_GEMM_GENERIC) && gemm_sm100_eligible(D, proj, 3) && gemm_sm100_eligible(H * hd, outp, 1);
   const size_t q_es = fast ? 2 : 4;
   const size_t b_q = pad256((size_t)M * H * hd * q_es), b_kv = pad256((size_t)M * Hkv * hd * 4);
   LayerScratch sc;
@@ -635,13 +645,17 @@ int32_t do_gqa_layer(Pool* p, const relux_gqa_layer_args* a) {
   float* d_attn = (float*)(sc.rest + b_q + 2 * b_kv);
   const int rd = a->rope ? hd : 0;
   const ProjSeg segs[3] = {{H * hd, rd, d_q, fast ? 1 : 0}, {Hkv * hd, rd, d_k, 0}, {Hkv * hd, 0, d_v, 0}};
-  rc = project_and_finish(p, sb, a->layer, (const float*)dx, M, D, S, proj, segs, 3, mma, sc.a_bf16, sc.part, sc.part_cap);
+  rc = project_and_finish(p, sb, a->layer, (const float*)dx, M, D, S, proj, segs, 3, mma, sc.a_bf16, sc.part, sc.part_cap, faithful);
   if (rc) return rc;
   // append: the GEMM rows are token-major [row][Hkv][hd]; advance = 0 leaves the rows past the cursor (verify)
   rc = launch_gqa_append(p, sb, a->layer, d_k, d_v, RELUX_DTYPE_F32, RELUX_LAYOUT_TOKEN_MAJOR, a->advance);
   if (rc) return rc;
   if (a->advance)
-    for (int i = 0; i < sb.n_seqs; i++) p->h_len[(size_t)a->layer * prm.max_seqs + sb.seq[i]] += S;
+    for (int i = 0; i < sb.n_seqs; i++) {
+      int32_t& len = p->h_len[(size_t)a->layer * prm.max_seqs + sb.seq[i]];
+      note_append(p, a->layer, sb.seq[i], len, S);
+      len += S;
+    }
   relux_attn_args aa;
   memset(&aa, 0, sizeof(aa));
   aa.layer = a->layer;
@@ -659,6 +673,34 @@ int32_t do_gqa_layer(Pool* p, const relux_gqa_layer_args* a) {
   rc = fast ? launch_gqa_decode_fast(p, sb, aa, d_q, d_attn) : launch_attn_reference_gqa(p, sb, aa, (const float*)d_q, d_attn);
   if (rc) return rc;
   return output_projection(p, d_attn, M, H * hd, w.w_o, D, mma, sc.a_bf16, sc.part, sc.part_cap, a->out, a->out_mem);
+}
+
+// ComputeBackend.MatMulFloat32 as matmulBatched3D uses it (interface.go:25-29, mha.go:759-785): C = A x B with A, C float32
+// and B a bf16 weight matrix [K][N] on the device.
+int32_t do_matmul(Pool* p, const relux_matmul_args* a) {
+  if (!a || !a->a || !a->b || !a->c) { set_error("nil argument"); return RELUX_ERR_INVALID_ARG; }
+  const int M = a->m, K = a->k, N = a->n;
+  if (M <= 0 || K <= 0 || N <= 0) { set_error("MatMulFloat32: M=%d K=%d N=%d must be positive", M, K, N); return RELUX_ERR_INVALID_ARG; }
+  if (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE) { set_error("bad mode"); return RELUX_ERR_INVALID_ARG; }
+  for (int i = 0; i < 4; i++)
+    if (a->reserved[i]) { set_error("reserved fields must be zero"); return RELUX_ERR_INVALID_ARG; }
+  int32_t rc;
+  if ((rc = check_dev_align(a->b, "B"))) return rc;
+  if (a->a_mem == RELUX_MEM_DEVICE && (rc = check_dev_align(a->a, "A"))) return rc;
+  if (a->c_mem == RELUX_MEM_DEVICE && (rc = check_dev_align(a->c, "C"))) return rc;
+  const WeightRef w[1] = {{a->b, N}};
+  const bool fast = a->mode == RELUX_ATTN_FAST;
+  if (fast && (p->tune.get(RELUX_TUNE_GEMM_GENERIC) || !gemm_sm100_eligible(K, w, 1) || N % 4 != 0)) {
+    set_error("MatMulFloat32 FAST needs K and N multiples of 8 (got K=%d N=%d); use RELUX_ATTN_REFERENCE", K, N);
+    return RELUX_ERR_UNSUPPORTED;
+  }
+  const void* dA = nullptr;
+  rc = stage_in(p, p->in_a, a->a, (size_t)M * K * 4, a->a_mem, &dA);
+  if (rc) return rc;
+  LayerScratch sc;
+  rc = layer_scratch(p, M, K, N, 0, &sc);
+  if (rc) return rc;
+  return output_projection(p, (const float*)dA, M, K, a->b, N, fast, sc.a_bf16, sc.part, sc.part_cap, a->c, a->c_mem);
 }
 
 }  // namespace relux

@@ -20,7 +20,6 @@ namespace relux {
 int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const SplitPlan& plan, const uint16_t* q_abs);
 bool mla_sm100_eligible(const Pool* p, const relux_attn_args& a);
 int mla_sm100_workers(Pool* p, int q_tokens);
-int32_t launch_mla_decode_sm100_t256(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const SplitPlan& plan, const uint16_t* q_abs);
 bool mla_proj_mma_eligible(int Dh, int dC);
 int32_t launch_mla_absorb_mma(Device* dev, const void* q_nope, const void* q_rope, int q_bf16, const uint16_t* W_UK, uint16_t* q_abs,
                               int rows, int H, int dC, int dHR);
@@ -252,15 +251,11 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   int32_t rc = grow(p->dev, p->q_abs, (size_t)rows * H * roww * 2);
   if (rc) return rc;
   const bool sm100 = mla_sm100_eligible(p, a);
-  // two tensor-core variants: 128-token tiles (default) and 256-token tiles (RELUX_MLA_TILE=256; fewer tensor
-  // cycles per token but too little shared memory left to cover the load latency, measured 12 % slower)
-  const char* tile_env = getenv("RELUX_MLA_TILE");
-  const bool t256 = sm100 && tile_env && atoi(tile_env) == 256;
   SplitPlan plan;
   // The stream partition depends on the cached lengths only, the absorb on the queries only: the one-block builder
   // runs on the side stream next to the absorb kernel and is joined before the decode kernel.
   cudaStream_t side = p->dev->side_stream;
-  const bool fork = sm100 && !t256 && side != nullptr && !getenv("RELUX_NO_SIDE_STREAM");
+  const bool fork = sm100 && side != nullptr;
   if (fork) {
     RELUX_CUDA_TRY(cudaEventRecord(p->dev->ev_fork, st));
     RELUX_CUDA_TRY(cudaStreamWaitEvent(side, p->dev->ev_fork, 0));
@@ -284,24 +279,23 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   }
   if (fork)
     RELUX_CUDA_TRY(cudaStreamWaitEvent(st, p->dev->ev_join, 0));
-  else if (sm100 && !t256)   // persistent CTA pairs over a stream partition; ranges are whole 128-token tiles
+  else if (sm100)   // persistent CTA pairs over a stream partition; ranges are whole 128-token tiles
     rc = plan_stream(p, sb, a.layer, a.extra_tokens, mla_sm100_workers(p, S), 2, &plan, st);
   else
-    rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, t256 ? 2 * S : std::max(1, rows_total / 16), t256 ? 4 : 1, t256 ? 4 : 1, t256 ? 320 : 0, &plan);
+    rc = plan_splitkv(p, sb, a.layer, a.extra_tokens, std::max(1, rows_total / 16), 1, 1, 0, &plan);
   if (rc) return rc;
   rc = grow(p->dev, p->part_o, (size_t)plan.num_items * rows_total * dC * sizeof(float));
   if (rc) return rc;
   rc = grow(p->dev, p->part_ml, (size_t)plan.num_items * rows_total * 2 * sizeof(float));
   if (rc) return rc;
-  const bool fused_merge = proj_mma && dC <= 512 && !getenv("RELUX_MLA_UNFUSED_MERGE");
+  const bool fused_merge = proj_mma && dC <= 512;
   if (!fused_merge) {   // the unfused paths hand the merged latent output to the up-projection through this buffer
     rc = grow(p->dev, p->o_lat, (size_t)rows * H * dC * sizeof(float));
     if (rc) return rc;
   }
   RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), st));
   if (sm100) {
-    rc = t256 ? launch_mla_decode_sm100_t256(p, sb, a, plan, (const uint16_t*)p->q_abs.p)
-              : launch_mla_decode_sm100(p, sb, a, plan, (const uint16_t*)p->q_abs.p);
+    rc = launch_mla_decode_sm100(p, sb, a, plan, (const uint16_t*)p->q_abs.p);
     if (rc) return rc;
   } else {
     MlaGenParams k;

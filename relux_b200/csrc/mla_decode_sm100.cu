@@ -478,7 +478,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 
 bool mla_sm100_eligible(const Pool* p, const relux_attn_args& a) {
   const relux_pool_params& prm = p->prm;
-  if (getenv("RELUX_MLA_GENERIC")) return false;
+  if (p->tune.get(RELUX_TUNE_MLA_GENERIC)) return false;
   // fewer than 128 heads run on the same M = 128 tile (padded); below 16 heads the CUDA-core kernel is the better fit
   return p->has_tmap && p->mla_blocked && prm.page_tokens == kPage && prm.mla_dc == kDC && prm.mla_dhr == kDR && a.num_heads <= kMaxHeads &&
          a.num_heads >= 16;
@@ -510,16 +510,17 @@ int mla_sm100_workers(Pool* p, int q_tokens) {
       (void)cudaGetLastError();
       n = std::max(1, p->dev->sm_count / 2);
     }
-    if (const char* ov = getenv("RELUX_MLA_WORKERS")) n = std::max(1, atoi(ov));   // tuning aid
     max_clusters = n;
   }
+  int mc = max_clusters;
+  if (const int ov = p->tune.get(RELUX_TUNE_MLA_WORKERS)) mc = std::max(1, ov);   // tuning knob
   if (q_tokens > kMaxInterleavedQ) {
     // A long multi-token call (a prompt) has one row of workers per query token: the rows already fill the device, so a
     // row needs only enough workers for about two waves in total, and each worker walks a long piece of the stream
     // (2048 tokens, one sequence: 3.2 ms with a full row of workers per token, 0.94 ms with one).
-    return std::min(max_clusters, std::max(1, (2 * max_clusters + q_tokens - 1) / q_tokens));
+    return std::min(mc, std::max(1, (2 * mc + q_tokens - 1) / q_tokens));
   }
-  return std::max(1, max_clusters / q_tokens);
+  return std::max(1, mc / q_tokens);
 }
 
 int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const SplitPlan& plan, const uint16_t* q_abs) {

@@ -86,13 +86,18 @@ int32_t stage_batch(Pool* p, int32_t n_seqs, const int32_t* seq_ids, const int32
     out->total_rows += r;
     out->max_rows = std::max(out->max_rows, r);
   }
-  if (seq_ids) {
-    for (int i = 0; i < n_seqs; i++)
-      for (int j = i + 1; j < n_seqs && n_seqs <= 64; j++)
-        if (out->seq[i] == out->seq[j]) {
-          set_error("sequence id %d appears twice in one call", out->seq[i]);
-          return RELUX_ERR_INVALID_ARG;
-        }
+  if (seq_ids) {   // a sequence named twice would be written by two blocks and advanced twice
+    if (++p->stamp == 0) {   // the call counter wrapped: forget every stamp
+      std::fill(p->seq_stamp.begin(), p->seq_stamp.end(), 0u);
+      p->stamp = 1;
+    }
+    for (int i = 0; i < n_seqs; i++) {
+      if (p->seq_stamp[out->seq[i]] == p->stamp) {
+        set_error("sequence id %d appears twice in one call", out->seq[i]);
+        return RELUX_ERR_INVALID_ARG;
+      }
+      p->seq_stamp[out->seq[i]] = p->stamp;
+    }
   }
   out->d_seq_ids = nullptr;
   out->d_row_off = nullptr;
@@ -160,11 +165,13 @@ bool make_tmap_2d(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint
   return r == CUDA_SUCCESS;
 }
 
+void tuning_defaults(Tuning* t);
+
 static void pool_free_all(Pool* p) {
   auto fr = [](void* q) { if (q) cudaFree(q); };
   fr(p->storage); fr(p->d_table); fr(p->d_len); fr(p->d_status); fr(p->d_seq_ids); fr(p->d_row_off);
   fr(p->in_a.p); fr(p->in_b.p); fr(p->out_buf.p); fr(p->q_abs.p); fr(p->part_o.p); fr(p->part_ml.p); fr(p->work.p);
-  fr(p->o_lat.p); fr(p->q_conv.p); fr(p->rope_tab.p); fr(p->layer_buf.p);
+  fr(p->o_lat.p); fr(p->q_conv.p); fr(p->rope_tab.p); fr(p->layer_buf.p); fr(p->shadow_f32); fr(p->chunk_tab.p);
   if (p->h_stage) cudaFreeHost(p->h_stage);
   for (cudaEvent_t ev : p->stage_ev)
     if (ev) cudaEventDestroy(ev);
@@ -201,6 +208,28 @@ int32_t stage_in(Pool* p, GrowBuf& buf, const void* src, size_t bytes, int mem, 
 
 static size_t dtype_size(int dt) { return dt == RELUX_DTYPE_BF16 ? 2 : 4; }
 
+int32_t check_dev_align(const void* ptr, const char* what) {
+  if (((uintptr_t)ptr & 15u) != 0) {
+    set_error("%s: device pointer %p is not 16-byte aligned (the kernels read it with 16-byte vector loads)", what, ptr);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  return RELUX_OK;
+}
+
+void note_append(Pool* p, int layer, int seq, int old_len, int n) {
+  if (!p->compat || n <= 0) return;
+  p->chunks[(size_t)layer * p->prm.max_seqs + seq].push_back(old_len);
+}
+void note_set_len(Pool* p, int layer, int seq, int old_len, int new_len) {
+  if (!p->compat || new_len == old_len) return;
+  std::vector<int32_t>& c = p->chunks[(size_t)layer * p->prm.max_seqs + seq];
+  if (new_len < old_len) {
+    while (!c.empty() && c.back() >= new_len) c.pop_back();   // a chunk cut in the middle keeps its start
+  } else {
+    c.push_back(old_len);   // rows made visible without an Append of their own (a committed draft) form one chunk
+  }
+}
+
 static int32_t do_append(Pool* p, const relux_append_args* a, int kind) {
   if (!a) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
   if (p->prm.kind != kind) { set_error("pool kind does not match this append call"); return RELUX_ERR_INVALID_ARG; }
@@ -226,6 +255,9 @@ static int32_t do_append(Pool* p, const relux_append_args* a, int kind) {
     }
   }
   if (sb.total_rows == 0) return RELUX_OK;
+  if (a->mem == RELUX_MEM_DEVICE) {
+    if ((rc = check_dev_align(a->a, "append input a")) || (rc = check_dev_align(a->b, "append input b"))) return rc;
+  }
   size_t es = dtype_size(a->dtype);
   const void *da = nullptr, *db = nullptr;
   if (kind == RELUX_POOL_MLA) {
@@ -244,7 +276,11 @@ static int32_t do_append(Pool* p, const relux_append_args* a, int kind) {
   }
   if (rc) return rc;
   if (a->advance)
-    for (int i = 0; i < sb.n_seqs; i++) p->h_len[(size_t)a->layer * prm.max_seqs + sb.seq[i]] += sb.rows[i];
+    for (int i = 0; i < sb.n_seqs; i++) {
+      int32_t& len = p->h_len[(size_t)a->layer * prm.max_seqs + sb.seq[i]];
+      note_append(p, a->layer, sb.seq[i], len, sb.rows[i]);
+      len += sb.rows[i];
+    }
   return RELUX_OK;
 }
 
@@ -271,8 +307,21 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
               a->num_heads, prm.gqa_num_kv_heads);
     return RELUX_ERR_INVALID_ARG;
   }
-  if (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE) { set_error("bad mode"); return RELUX_ERR_INVALID_ARG; }
+  if (a->mode != RELUX_ATTN_FAST && a->mode != RELUX_ATTN_REFERENCE && a->mode != RELUX_ATTN_REFERENCE_FAITHFUL) {
+    set_error("bad mode");
+    return RELUX_ERR_INVALID_ARG;
+  }
+  if (a->mode == RELUX_ATTN_REFERENCE_FAITHFUL && (!p->compat || a->extra_tokens != 0)) {
+    set_error("RELUX_ATTN_REFERENCE_FAITHFUL needs a pool created with RELUX_POOL_FLAG_REFERENCE_COMPAT and extra_tokens = 0");
+    return RELUX_ERR_INVALID_ARG;
+  }
   if (!(a->scale > 0.f)) { set_error("scale=%g, must be > 0", (double)a->scale); return RELUX_ERR_INVALID_ARG; }
+  if (a->q_mem == RELUX_MEM_DEVICE) {
+    if ((rc = check_dev_align(a->q, "q"))) return rc;
+    if (kind == RELUX_POOL_MLA && (rc = check_dev_align(a->q_rope, "q_rope"))) return rc;
+  }
+  if (a->out_mem == RELUX_MEM_DEVICE && (rc = check_dev_align(a->out, "out"))) return rc;
+  if (kind == RELUX_POOL_MLA && ((rc = check_dev_align(a->w_uk, "w_uk")) || (rc = check_dev_align(a->w_uv, "w_uv")))) return rc;
   SeqBatch sb;
   rc = stage_batch(p, a->n_seqs, a->seq_ids, nullptr, a->q_tokens, &sb);
   if (rc) return rc;
@@ -295,7 +344,7 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
     if (rc) return rc;
   }
   // canonical kernel input: token-major; f32 for REFERENCE, caller's dtype for FAST
-  const int want_dtype = (a->mode == RELUX_ATTN_REFERENCE) ? RELUX_DTYPE_F32 : a->q_dtype;
+  const int want_dtype = (a->mode != RELUX_ATTN_FAST) ? RELUX_DTYPE_F32 : a->q_dtype;
   const bool relayout_q = (a->q_layout == RELUX_LAYOUT_HEAD_MAJOR && S > 1) || want_dtype != a->q_dtype;
   if (relayout_q) {
     size_t need = (q_elems + qr_elems) * dtype_size(want_dtype);
@@ -326,7 +375,7 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
   relux_attn_args aa = *a;
   aa.q_dtype = want_dtype;
   aa.q_layout = RELUX_LAYOUT_TOKEN_MAJOR;
-  if (a->mode == RELUX_ATTN_REFERENCE) {
+  if (a->mode != RELUX_ATTN_FAST) {
     rc = (kind == RELUX_POOL_MLA) ? launch_attn_reference_mla(p, sb, aa, (const float*)dq, (const float*)dqr, kout)
                                   : launch_attn_reference_gqa(p, sb, aa, (const float*)dq, kout);
   } else {
@@ -349,6 +398,18 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
     }
   }
   return RELUX_OK;
+}
+
+// Built-in defaults of the tuning knobs, then the environment (read here, once per pool, never on a launch path).
+static const int32_t kTuneDefault[RELUX_TUNE_COUNT] = {0, 0, 0, 0, 0, 256, 0, -1, -1};
+static const char* const kTuneEnv[RELUX_TUNE_COUNT] = {"RELUX_MLA_GENERIC", "RELUX_MLA_WORKERS", "RELUX_CHUNK_PAGES", "RELUX_GEMM_GENERIC",
+                                                       "RELUX_GEMM_SPLIT", "RELUX_GQA_PROMPT_PARTIAL_MB", "RELUX_SEL_CLUSTER",
+                                                       "RELUX_SEL_LOOKAHEAD", "RELUX_SEL_BATCHED"};
+void tuning_defaults(Tuning* t) {
+  for (int i = 0; i < RELUX_TUNE_COUNT; i++) {
+    t->v[i] = kTuneDefault[i];
+    if (const char* e = getenv(kTuneEnv[i])) t->v[i] = atoi(e);
+  }
 }
 
 }  // namespace relux
@@ -570,8 +631,9 @@ API int32_t relux_pool_create(relux_device_t h, const relux_pool_params* prm, re
     set_error("NewCache: num_pages, page_tokens, max_seqs, max_pages_per_seq must all be > 0");
     return RELUX_ERR_INVALID_ARG;
   }
-  for (int i = 0; i < 6; i++)
+  for (int i = 0; i < 5; i++)
     if (prm->reserved[i]) { set_error("reserved fields must be zero"); return RELUX_ERR_INVALID_ARG; }
+  if (prm->flags & ~RELUX_POOL_FLAG_REFERENCE_COMPAT) { set_error("unknown pool flags 0x%x", prm->flags); return RELUX_ERR_INVALID_ARG; }
   Pool* p = new (std::nothrow) Pool();
   if (!p) return RELUX_ERR_OUT_OF_MEMORY;
   p->dev = dev;
@@ -609,15 +671,15 @@ API int32_t relux_pool_create(relux_device_t h, const relux_pool_params* prm, re
   A((void**)&p->d_status, 8);   // [0] status word, [1] block counter of the append kernels
   A((void**)&p->d_seq_ids, (size_t)prm->max_seqs * 4);
   A((void**)&p->d_row_off, ((size_t)prm->max_seqs + 1) * 4);
+  p->compat = (prm->flags & RELUX_POOL_FLAG_REFERENCE_COMPAT) != 0;
+  if (p->compat && prm->kind == RELUX_POOL_MLA) {
+    const size_t shadow_bytes = p->layer_elems * prm->num_layers * sizeof(float);
+    A((void**)&p->shadow_f32, shadow_bytes);
+    if (e == cudaSuccess) e = cudaMemsetAsync(p->shadow_f32, 0, shadow_bytes, dev->stream);
+  }
   if (e == cudaSuccess) e = cudaMallocHost((void**)&p->h_stage, Pool::kStageSlots * (2 * (size_t)prm->max_seqs + 1) * 4);
   for (cudaEvent_t& ev : p->stage_ev)
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
-  for (auto& pair : p->ev_ring)
-    for (cudaEvent_t& ev : pair)
-      if (e == cudaSuccess) e = cudaEventCreate(&ev);
-  for (auto& pair : p->proj_ring)
-    for (cudaEvent_t& ev : pair)
-      if (e == cudaSuccess) e = cudaEventCreate(&ev);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_table, 0xFF, table_n * 4, dev->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_len, 0, len_n * 4, dev->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(p->d_status, 0, 8, dev->stream);
@@ -632,6 +694,9 @@ API int32_t relux_pool_create(relux_device_t h, const relux_pool_params* prm, re
   p->h_len.assign(len_n, 0);
   p->seq_pages.assign(prm->max_seqs, 0);
   p->seq_owned.assign(prm->max_seqs, 0);
+  p->seq_stamp.assign(prm->max_seqs, 0u);
+  if (p->compat) p->chunks.assign(len_n, std::vector<int32_t>());
+  tuning_defaults(&p->tune);
   p->free_pages.resize(prm->num_pages);
   for (int i = 0; i < prm->num_pages; i++) p->free_pages[i] = prm->num_pages - 1 - i;
   // TMA views of the storage: all layers form one 2-D array of 64-row page slabs
@@ -662,6 +727,7 @@ API int32_t relux_pool_reset(relux_pool_t h) {
   GET_POOL(h);
   const relux_pool_params& prm = p->prm;
   std::fill(p->h_len.begin(), p->h_len.end(), 0);
+  for (auto& c : p->chunks) c.clear();
   for (int s = 0; s < prm.max_seqs; s++)
     if (p->seq_owned[s]) {
       for (int i = 0; i < p->seq_pages[s]; i++) p->free_pages.push_back(p->h_table[(size_t)s * prm.max_pages_per_seq + i]);
@@ -680,14 +746,23 @@ API int32_t relux_pool_set_tables(relux_pool_t h, const int32_t* table, int32_t 
     set_error("set_tables: n_seqs=%d (max %d), stride=%d (max %d)", n_seqs, prm.max_seqs, stride, prm.max_pages_per_seq);
     return RELUX_ERR_INVALID_ARG;
   }
+  // One pool has one owner of its pages: either the caller's tables or the library's free list.  Mixing them would
+  // let relux_seq_alloc hand out a page that a caller-made table still maps.
+  for (int s = 0; s < prm.max_seqs; s++)
+    if (p->seq_owned[s]) { set_error("set_tables: sequence %d is owned by relux_seq_alloc; a pool uses either caller tables or the library's free list", s); return RELUX_ERR_INVALID_ARG; }
+  std::vector<uint8_t> seen((size_t)prm.num_pages, 0);
   for (int s = 0; s < n_seqs; s++) {
-    if (p->seq_owned[s]) { set_error("sequence %d is owned by relux_seq_alloc", s); return RELUX_ERR_INVALID_ARG; }
     for (int i = 0; i < stride; i++) {
       int pg = table[(size_t)s * stride + i];
       if (pg < 0 || pg >= prm.num_pages) {
         set_error("page table entry [%d][%d]=%d outside [0,%d)", s, i, pg, prm.num_pages);
         return RELUX_ERR_BAD_PAGE;
       }
+      if (seen[pg]) {
+        set_error("page %d is mapped twice (second time at [%d][%d]): two sequences would share cache rows", pg, s, i);
+        return RELUX_ERR_BAD_PAGE;
+      }
+      seen[pg] = 1;
     }
     if (ctx_len && (ctx_len[s] < 0 || ctx_len[s] > stride * prm.page_tokens)) {
       set_error("ctx_len[%d]=%d exceeds the %d tokens its pages hold", s, ctx_len[s], stride * prm.page_tokens);
@@ -698,10 +773,20 @@ API int32_t relux_pool_set_tables(relux_pool_t h, const int32_t* table, int32_t 
   for (int s = 0; s < n_seqs; s++) {
     for (int i = 0; i < stride; i++) p->h_table[(size_t)s * prm.max_pages_per_seq + i] = table[(size_t)s * stride + i];
     p->seq_pages[s] = stride;
-    for (int l = 0; l < prm.num_layers; l++) p->h_len[(size_t)l * prm.max_seqs + s] = ctx_len ? ctx_len[s] : 0;
+    for (int l = 0; l < prm.num_layers; l++) {
+      p->h_len[(size_t)l * prm.max_seqs + s] = ctx_len ? ctx_len[s] : 0;
+      if (p->compat) {
+        std::vector<int32_t>& c = p->chunks[(size_t)l * prm.max_seqs + s];
+        c.clear();
+        if (ctx_len && ctx_len[s] > 0) c.push_back(0);
+      }
+    }
   }
-  RELUX_CUDA_TRY(cudaMemcpy(p->d_table, p->h_table.data(), p->h_table.size() * 4, cudaMemcpyHostToDevice));
-  RELUX_CUDA_TRY(cudaMemcpy(p->d_len, p->h_len.data(), p->h_len.size() * 4, cudaMemcpyHostToDevice));
+  // on the handle's stream (it does not synchronise with the legacy default stream), then waited for: the shadows are pageable
+  RELUX_CUDA_TRY(cudaMemcpyAsync(p->d_table, p->h_table.data(), p->h_table.size() * 4, cudaMemcpyHostToDevice, dev->stream));
+  RELUX_CUDA_TRY(cudaMemcpyAsync(p->d_len, p->h_len.data(), p->h_len.size() * 4, cudaMemcpyHostToDevice, dev->stream));
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  p->caller_tables = true;
   return RELUX_OK;
 }
 
@@ -711,6 +796,7 @@ API int32_t relux_seq_alloc(relux_pool_t h, int32_t max_tokens, int32_t* seq_id)
   if (!seq_id || max_tokens <= 0) { set_error("seq_alloc: maxLen=%d, must be > 0", max_tokens); return RELUX_ERR_INVALID_ARG; }
   int need = (max_tokens + prm.page_tokens - 1) / prm.page_tokens;
   if (need > prm.max_pages_per_seq) { set_error("seq_alloc: %d tokens need %d pages, max_pages_per_seq=%d", max_tokens, need, prm.max_pages_per_seq); return RELUX_ERR_OVERFLOW; }
+  if (p->caller_tables) { set_error("seq_alloc: this pool's page tables were set by relux_pool_set_tables; a pool uses either caller tables or the library's free list"); return RELUX_ERR_INVALID_ARG; }
   int s = -1;
   for (int i = 0; i < prm.max_seqs; i++)
     if (p->seq_pages[i] == 0) { s = i; break; }
@@ -721,10 +807,15 @@ API int32_t relux_seq_alloc(relux_pool_t h, int32_t max_tokens, int32_t* seq_id)
   }
   p->seq_pages[s] = need;
   p->seq_owned[s] = 1;
-  for (int l = 0; l < prm.num_layers; l++) p->h_len[(size_t)l * prm.max_seqs + s] = 0;
-  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
-  RELUX_CUDA_TRY(cudaMemcpy(p->d_table + (size_t)s * prm.max_pages_per_seq, &p->h_table[(size_t)s * prm.max_pages_per_seq], (size_t)need * 4, cudaMemcpyHostToDevice));
-  for (int l = 0; l < prm.num_layers; l++) RELUX_CUDA_TRY(cudaMemset(p->d_len + (size_t)l * prm.max_seqs + s, 0, 4));
+  for (int l = 0; l < prm.num_layers; l++) {
+    p->h_len[(size_t)l * prm.max_seqs + s] = 0;
+    if (p->compat) p->chunks[(size_t)l * prm.max_seqs + s].clear();
+  }
+  // every update goes through the handle's stream, so that it is ordered with the kernels queued there
+  RELUX_CUDA_TRY(cudaMemcpyAsync(p->d_table + (size_t)s * prm.max_pages_per_seq, &p->h_table[(size_t)s * prm.max_pages_per_seq], (size_t)need * 4,
+                                 cudaMemcpyHostToDevice, dev->stream));
+  for (int l = 0; l < prm.num_layers; l++) RELUX_CUDA_TRY(cudaMemsetAsync(p->d_len + (size_t)l * prm.max_seqs + s, 0, 4, dev->stream));
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));   // h_table is pageable host memory
   *seq_id = s;
   return RELUX_OK;
 }
@@ -761,7 +852,8 @@ API int32_t relux_seq_free(relux_pool_t h, int32_t s) {
   p->seq_owned[s] = 0;
   for (int l = 0; l < prm.num_layers; l++) {
     p->h_len[(size_t)l * prm.max_seqs + s] = 0;
-    RELUX_CUDA_TRY(cudaMemset(p->d_len + (size_t)l * prm.max_seqs + s, 0, 4));
+    if (p->compat) p->chunks[(size_t)l * prm.max_seqs + s].clear();
+    RELUX_CUDA_TRY(cudaMemsetAsync(p->d_len + (size_t)l * prm.max_seqs + s, 0, 4, dev->stream));
   }
   return RELUX_OK;
 }
@@ -806,7 +898,11 @@ int32_t relux::seq_set_len(Pool* p, int32_t layer, int32_t n_seqs, const int32_t
   for (int l = l0; l < l1; l++) {
     rc = launch_set_len(p, sb, l, p->d_row_off);
     if (rc) return rc;
-    for (int i = 0; i < n_seqs; i++) p->h_len[(size_t)l * prm.max_seqs + sb.seq[i]] = new_len[i];
+    for (int i = 0; i < n_seqs; i++) {
+      int32_t& len = p->h_len[(size_t)l * prm.max_seqs + sb.seq[i]];
+      note_set_len(p, l, sb.seq[i], len, new_len[i]);
+      len = new_len[i];
+    }
   }
   return RELUX_OK;
 }
@@ -814,15 +910,17 @@ int32_t relux::seq_set_len(Pool* p, int32_t layer, int32_t n_seqs, const int32_t
 API int32_t relux_pool_status(relux_pool_t h, int32_t* status) {
   GET_POOL(h);
   if (!status) return RELUX_ERR_INVALID_ARG;
+  RELUX_CUDA_TRY(cudaMemcpyAsync(status, p->d_status, 4, cudaMemcpyDeviceToHost, dev->stream));
   RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
-  RELUX_CUDA_TRY(cudaMemcpy(status, p->d_status, 4, cudaMemcpyDeviceToHost));
-  if (*status) RELUX_CUDA_TRY(cudaMemset(p->d_status, 0, 4));
+  if (*status) RELUX_CUDA_TRY(cudaMemsetAsync(p->d_status, 0, 4, dev->stream));
   return RELUX_OK;
 }
 
-API int32_t relux_pool_read_rows(relux_pool_t h, int32_t layer, int32_t s, int32_t tok0, int32_t n, void* dst_a, void* dst_b) {
+API int32_t relux_pool_read_rows(relux_pool_t h, const relux_read_rows_args* a) {
   GET_POOL(h);
+  if (!a) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
   const relux_pool_params& prm = p->prm;
+  const int32_t layer = a->layer, s = a->seq_id, tok0 = a->tok0, n = a->n_tokens;
   int32_t rc = check_layer(p, layer);
   if (rc) return rc;
   if (s < 0 || s >= prm.max_seqs || p->seq_pages[s] == 0 || tok0 < 0 || n < 0 || tok0 + n > p->seq_pages[s] * prm.page_tokens) {
@@ -839,9 +937,16 @@ API int32_t relux_pool_read_rows(relux_pool_t h, int32_t layer, int32_t s, int32
   uint16_t* db = da + ea;
   rc = launch_gather_rows(p, layer, s, tok0, n, da, db);
   if (rc) return rc;
-  if (dst_a) RELUX_CUDA_TRY(cudaMemcpyAsync(dst_a, da, ea * 2, cudaMemcpyDeviceToHost, dev->stream));
-  if (dst_b) RELUX_CUDA_TRY(cudaMemcpyAsync(dst_b, db, eb * 2, cudaMemcpyDeviceToHost, dev->stream));
+  if (a->dst_a) RELUX_CUDA_TRY(cudaMemcpyAsync(a->dst_a, da, ea * 2, cudaMemcpyDeviceToHost, dev->stream));
+  if (a->dst_b) RELUX_CUDA_TRY(cudaMemcpyAsync(a->dst_b, db, eb * 2, cudaMemcpyDeviceToHost, dev->stream));
   RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  return RELUX_OK;
+}
+
+API int32_t relux_pool_tune(relux_pool_t h, int32_t knob, int32_t value) {
+  GET_POOL(h);
+  if (knob < 0 || knob >= RELUX_TUNE_COUNT) { set_error("unknown tuning knob %d", knob); return RELUX_ERR_INVALID_ARG; }
+  p->tune.v[knob] = value < 0 ? kTuneDefault[knob] : value;
   return RELUX_OK;
 }
 
@@ -900,29 +1005,63 @@ API int32_t relux_sampler_sample(relux_pool_t h, const relux_sample_args* a) {
   return do_sample(p, a);
 }
 
+API int32_t relux_matmul_f32_bf16(relux_pool_t h, const relux_matmul_args* a) {
+  GET_POOL(h);
+  return do_matmul(p, a);
+}
+
+API int32_t relux_mla_import_weights(relux_pool_t h, const relux_mla_import_args* a) {
+  GET_POOL(h);
+  return do_import_mla(p, a);
+}
+
+API int32_t relux_pool_selftest_wait(relux_pool_t h, int32_t polls) {
+  GET_POOL(h);
+  return do_selftest_wait(p, polls);
+}
+
 API int32_t relux_pool_last_kernel_ms(relux_pool_t h, float* ms) {
   GET_POOL(h);
   if (!ms) return RELUX_ERR_INVALID_ARG;
   if (!p->timed_calls) { set_error("no attention kernel has been timed on this pool yet"); return RELUX_ERR_INVALID_ARG; }
   const auto& pair = p->ev_ring[(p->timed_calls - 1) % Pool::kTimeRing];
+  if (!pair[0] || !pair[1]) { set_error("the last call recorded no timing events"); return RELUX_ERR_CUDA; }
   RELUX_CUDA_TRY(cudaEventSynchronize(pair[1]));
   RELUX_CUDA_TRY(cudaEventElapsedTime(ms, pair[0], pair[1]));
   return RELUX_OK;
 }
 
-static int32_t ring_mean(cudaEvent_t (*ring)[2], uint64_t calls, int32_t last_n, float* mean_ms, int32_t* counted) {
+// Times of the last n calls of a ring, oldest first; slots whose events were never recorded are skipped.
+static int32_t ring_list(cudaEvent_t (*ring)[2], uint64_t calls, int32_t last_n, float* out, int32_t* counted) {
   const uint64_t n = std::min<uint64_t>(std::min<uint64_t>((uint64_t)last_n, calls), Pool::kTimeRing);
-  double sum = 0.0;
-  for (uint64_t i = 0; i < n; i++) {
+  int32_t k = 0;
+  for (uint64_t i = n; i-- > 0;) {
     cudaEvent_t* pair = ring[(calls - 1 - i) % Pool::kTimeRing];
+    if (!pair[0] || !pair[1]) continue;
     float ms = 0.f;
     RELUX_CUDA_TRY(cudaEventSynchronize(pair[1]));
     RELUX_CUDA_TRY(cudaEventElapsedTime(&ms, pair[0], pair[1]));
-    sum += ms;
+    out[k++] = ms;
   }
-  *mean_ms = (float)(sum / (double)n);
-  if (counted) *counted = (int32_t)n;
+  *counted = k;
   return RELUX_OK;
+}
+static int32_t ring_mean(cudaEvent_t (*ring)[2], uint64_t calls, int32_t last_n, float* mean_ms, int32_t* counted) {
+  std::vector<float> ms((size_t)std::min<int64_t>(last_n, Pool::kTimeRing));
+  int32_t n = 0;
+  int32_t rc = ring_list(ring, calls, last_n, ms.data(), &n);
+  if (rc) return rc;
+  double sum = 0.0;
+  for (int i = 0; i < n; i++) sum += ms[i];
+  *mean_ms = n ? (float)(sum / (double)n) : 0.f;
+  if (counted) *counted = n;
+  return RELUX_OK;
+}
+
+API int32_t relux_pool_kernel_ms_list(relux_pool_t h, int32_t last_n, float* ms_out, int32_t* counted) {
+  GET_POOL(h);
+  if (!ms_out || !counted || last_n <= 0) return RELUX_ERR_INVALID_ARG;
+  return ring_list(p->ev_ring, p->timed_calls, last_n, ms_out, counted);
 }
 
 API int32_t relux_pool_kernel_ms_mean(relux_pool_t h, int32_t last_n, float* mean_ms, int32_t* counted) {

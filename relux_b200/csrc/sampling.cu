@@ -1023,9 +1023,9 @@ static int32_t launch_selection(Pool* p, SelParams& prm, int n, const relux_samp
   prm.top_p = sp.top_p;
   prm.min_p = sp.min_p;
   prm.batched = n <= 16 ? 1 : 0;
-  if (const char* e = getenv("RELUX_SEL_BATCHED")) prm.batched = atoi(e) ? 1 : 0;       // tuning override
+  if (p->tune.get(RELUX_TUNE_SEL_BATCHED) >= 0) prm.batched = p->tune.get(RELUX_TUNE_SEL_BATCHED) ? 1 : 0;       // tuning knob
   prm.lookahead = n <= 32 ? 1 : 0;   // measured: 6 % faster at 4-16 sequences, even at 32, 1 % slower at 64
-  if (const char* e = getenv("RELUX_SEL_LOOKAHEAD")) prm.lookahead = atoi(e) ? 1 : 0;   // tuning override
+  if (p->tune.get(RELUX_TUNE_SEL_LOOKAHEAD) >= 0) prm.lookahead = p->tune.get(RELUX_TUNE_SEL_LOOKAHEAD) ? 1 : 0;   // tuning knob
   if (mode == RELUX_ATTN_REFERENCE) {
     // One thread per sequence repeats the reference's selection sorts: quadratic in the vocabulary for the nucleus cut,
     // top_k x vocabulary for kthLargest.  Refuse sizes that would keep the device busy for many seconds.
@@ -1073,8 +1073,8 @@ static int32_t launch_selection(Pool* p, SelParams& prm, int n, const relux_samp
       const double cost = (double)((n + have - 1) / have) / cs;   // waves x slice length
       if (cost <= best) { best = cost; csize = cs; }   // on a tie the smaller cluster: fewer waves, fewer remote reads
     }
-    if (const char* e = getenv("RELUX_SEL_CLUSTER")) {   // tuning override: 1, 2, 4 or 8
-      const int v = atoi(e);
+    {   // tuning knob: 1, 2, 4 or 8
+      const int v = p->tune.get(RELUX_TUNE_SEL_CLUSTER);
       if (v == 1 || v == 2 || v == 4 || v == 8) csize = v;
     }
     cudaLaunchConfig_t cfg{};
@@ -1112,7 +1112,23 @@ int32_t do_spec_accept(Pool* p, const relux_spec_accept_args* a) {
     set_error("spec_accept: bad arguments");
     return RELUX_ERR_INVALID_ARG;
   }
-  if (a->commit && n > p->prm.max_seqs) { set_error("spec_accept: more sequences than the pool holds"); return RELUX_ERR_INVALID_ARG; }
+  if (a->commit) {
+    // checked before anything is launched, so that a commit is all or nothing: every sequence live and named once, and
+    // room on every layer for the longest possible result (k + 1 rows)
+    if (n > p->prm.max_seqs) { set_error("spec_accept: more sequences than the pool holds"); return RELUX_ERR_INVALID_ARG; }
+    SeqBatch chk;
+    int32_t rc0 = stage_batch(p, n, a->seq_ids, nullptr, 1, &chk);
+    if (rc0) return rc0;
+    for (int l = 0; l < p->prm.num_layers; l++)
+      for (int i = 0; i < n; i++) {
+        const int s = chk.seq[i];
+        const int len = p->h_len[(size_t)l * p->prm.max_seqs + s], cap = p->seq_pages[s] * p->prm.page_tokens;
+        if (len + k + 1 > cap) {
+          set_error("spec_accept: committing up to %d rows would pass the capacity %d of sequence %d on layer %d (length %d)", k + 1, cap, s, l, len);
+          return RELUX_ERR_OVERFLOW;
+        }
+      }
+  }
   if (a->mem == RELUX_MEM_HOST)
     for (size_t i = 0; i < (size_t)n * k; i++)
       if (a->draft_tokens[i] < 0 || a->draft_tokens[i] >= V) {

@@ -95,8 +95,8 @@ int32_t plan_splitkv(Pool* p, const SeqBatch& sb, int layer, int extra, int ctas
       chunk = c;
     }
   }
-  if (const char* ov = getenv("RELUX_CHUNK_PAGES")) {  // tuning aid
-    chunk = std::max(1, atoi(ov));
+  if (const int ov = p->tune.get(RELUX_TUNE_CHUNK_PAGES)) {  // tuning knob
+    chunk = std::max(1, ov);
     chunk = (chunk + mult - 1) / mult * mult;
     if (max_chunk_pages > 0) chunk = std::min(chunk, max_chunk_pages / mult * mult);
   }
@@ -214,8 +214,7 @@ int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int worke
   }
   long G = 0;
   int items = 0;
-  const char* ov = getenv("RELUX_CHUNK_PAGES");   // tuning aid
-  stream_partition_shape(pages.data(), sb.n_seqs, workers, page_multiple, ov ? atol(ov) : 0, &G, &workers, &items);
+  stream_partition_shape(pages.data(), sb.n_seqs, workers, page_multiple, (long)p->tune.get(RELUX_TUNE_CHUNK_PAGES), &G, &workers, &items);
   plan->chunk_pages = (int)G;
   plan->num_items = items;
   plan->num_workers = workers;
@@ -241,10 +240,12 @@ int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int worke
 // kernel's planner produces for sequences of pages[i] pages.  items_out receives n_items x {seq_index, page_begin,
 // page_end, worker}; worker_first [workers_out + 1]; chunk_off [n_seqs + 1].  Returns the number of items, or -1 when
 // `cap` items are not enough.  Scheduling aid for callers and tests; no counterpart in the reference.
-extern "C" __attribute__((visibility("default"))) int32_t relux_stream_partition(const int32_t* pages, int32_t n_seqs, int32_t workers,
-                                                                               int32_t page_multiple, int32_t* range_pages_out,
-                                                                               int32_t* workers_out, int32_t* items_out, int32_t cap,
-                                                                               int32_t* worker_first, int32_t* chunk_off) {
+extern "C" __attribute__((visibility("default"))) int32_t relux_stream_partition(const relux_stream_partition_args* args) {
+  if (!args) return -1;
+  const int32_t* pages = args->pages;
+  const int32_t n_seqs = args->n_seqs, workers = args->workers, page_multiple = args->page_multiple, cap = args->cap;
+  int32_t *range_pages_out = args->range_pages_out, *workers_out = args->workers_out, *items_out = args->items_out;
+  int32_t *worker_first = args->worker_first, *chunk_off = args->chunk_off;
   if (!pages || n_seqs <= 0 || !range_pages_out || !workers_out) return -1;
   long G = 0;
   int W = 0, items = 0;

@@ -19,7 +19,10 @@ DTYPE_F32, DTYPE_BF16 = 0, 1
 MEM_HOST, MEM_DEVICE = 0, 1
 LAYOUT_TOKEN_MAJOR, LAYOUT_HEAD_MAJOR = 0, 1
 POOL_MLA, POOL_GQA = 0, 1
-ATTN_FAST, ATTN_REFERENCE = 0, 1
+ATTN_FAST, ATTN_REFERENCE, ATTN_REFERENCE_FAITHFUL = 0, 1, 2
+POOL_FLAG_REFERENCE_COMPAT = 1
+(TUNE_MLA_GENERIC, TUNE_MLA_WORKERS, TUNE_CHUNK_PAGES, TUNE_GEMM_GENERIC, TUNE_GEMM_SPLIT, TUNE_GQA_PROMPT_PARTIAL_MB, TUNE_SEL_CLUSTER,
+ TUNE_SEL_LOOKAHEAD, TUNE_SEL_BATCHED) = range(9)
 
 # Every symbol include/relux_cuda.h declares; tests check that the library exports each one.
 EXPORTS = [
@@ -31,14 +34,31 @@ EXPORTS = [
     "relux_pool_set_tables", "relux_seq_alloc", "relux_seq_free", "relux_seq_extend", "relux_seq_len", "relux_seq_set_len", "relux_pool_status",
     "relux_pool_read_rows", "relux_mla_append", "relux_gqa_append", "relux_mla_decode", "relux_gqa_decode", "relux_gqa_verify",
     "relux_mla_verify", "relux_pool_last_kernel_ms", "relux_pool_kernel_ms_mean", "relux_mla_forward_cached", "relux_gqa_forward_cached", "relux_stream_partition", "relux_seq_save_file", "relux_seq_load_file", "relux_pool_projection_ms_mean", "relux_gqa_decode_noalloc",
-    "relux_spec_accept", "relux_sampler_sample",
+    "relux_spec_accept", "relux_sampler_sample", "relux_pool_tune", "relux_pool_kernel_ms_list", "relux_matmul_f32_bf16",
+    "relux_mla_import_weights", "relux_pool_selftest_wait",
 ]
 
 
 class PoolParams(C.Structure):
     _fields_ = [("kind", C.c_int32), ("num_layers", C.c_int32), ("num_pages", C.c_int32), ("page_tokens", C.c_int32),
                 ("max_seqs", C.c_int32), ("max_pages_per_seq", C.c_int32), ("mla_dc", C.c_int32), ("mla_dhr", C.c_int32),
-                ("gqa_num_kv_heads", C.c_int32), ("gqa_head_dim", C.c_int32), ("reserved", C.c_int32 * 6)]
+                ("gqa_num_kv_heads", C.c_int32), ("gqa_head_dim", C.c_int32), ("flags", C.c_int32), ("reserved", C.c_int32 * 5)]
+
+
+class ReadRowsArgs(C.Structure):
+    _fields_ = [("layer", C.c_int32), ("seq_id", C.c_int32), ("tok0", C.c_int32), ("n_tokens", C.c_int32), ("dst_a", C.c_void_p),
+                ("dst_b", C.c_void_p), ("reserved", C.c_int32 * 4)]
+
+
+class StreamPartitionArgs(C.Structure):
+    _fields_ = [("pages", C.c_void_p), ("n_seqs", C.c_int32), ("workers", C.c_int32), ("page_multiple", C.c_int32), ("cap", C.c_int32),
+                ("range_pages_out", C.c_void_p), ("workers_out", C.c_void_p), ("items_out", C.c_void_p), ("worker_first", C.c_void_p),
+                ("chunk_off", C.c_void_p)]
+
+
+class MatmulArgs(C.Structure):
+    _fields_ = [("m", C.c_int32), ("k", C.c_int32), ("n", C.c_int32), ("mode", C.c_int32), ("a", C.c_void_p), ("a_mem", C.c_int32),
+                ("c_mem", C.c_int32), ("b", C.c_void_p), ("c", C.c_void_p), ("reserved", C.c_int32 * 4)]
 
 
 class AppendArgs(C.Structure):
@@ -66,6 +86,13 @@ class MlaLayerArgs(C.Structure):
                 ("causal", C.c_int32), ("d_model", C.c_int32), ("num_heads", C.c_int32), ("rope_base", C.c_float),
                 ("mode", C.c_int32), ("x", C.c_void_p), ("x_dtype", C.c_int32), ("x_mem", C.c_int32), ("out", C.c_void_p),
                 ("out_mem", C.c_int32), ("reserved", C.c_int32 * 3), ("w", C.POINTER(MlaLayerWeights))]
+
+
+class MlaImportArgs(C.Structure):
+    _fields_ = [("d_model", C.c_int32), ("num_heads", C.c_int32), ("nope_dim", C.c_int32), ("rope_dim", C.c_int32), ("v_dim", C.c_int32),
+                ("dc", C.c_int32), ("src_dtype", C.c_int32), ("src_mem", C.c_int32), ("fused_rope", C.c_int32),
+                ("reserved", C.c_int32 * 3), ("q_proj", C.c_void_p), ("kv_a_proj_with_mqa", C.c_void_p), ("kv_b_proj", C.c_void_p),
+                ("o_proj", C.c_void_p), ("q_pe_proj", C.c_void_p), ("k_pe_proj", C.c_void_p), ("dst", C.POINTER(MlaLayerWeights))]
 
 
 class GqaLayerWeights(C.Structure):
@@ -150,7 +177,12 @@ def load():
         L.relux_seq_len.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int32)]
         L.relux_seq_set_len.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
         L.relux_pool_status.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
-        L.relux_pool_read_rows.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+        L.relux_pool_read_rows.argtypes = [C.c_void_p, C.POINTER(ReadRowsArgs)]
+        L.relux_pool_tune.argtypes = [C.c_void_p, C.c_int32, C.c_int32]
+        L.relux_pool_kernel_ms_list.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.POINTER(C.c_int32)]
+        L.relux_matmul_f32_bf16.argtypes = [C.c_void_p, C.POINTER(MatmulArgs)]
+        L.relux_mla_import_weights.argtypes = [C.c_void_p, C.POINTER(MlaImportArgs)]
+        L.relux_pool_selftest_wait.argtypes = [C.c_void_p, C.c_int32]
         for n in ("relux_mla_append", "relux_gqa_append"):
             getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AppendArgs)]
         for n in ("relux_mla_decode", "relux_gqa_decode", "relux_gqa_decode_noalloc"):
@@ -158,8 +190,7 @@ def load():
         for n in ("relux_gqa_verify", "relux_mla_verify"):
             getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AttnArgs), C.POINTER(AppendArgs)]
         L.relux_pool_projection_ms_mean.argtypes = [C.c_void_p, C.c_int32, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
-        L.relux_stream_partition.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_int32),
-                                             C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p]
+        L.relux_stream_partition.argtypes = [C.POINTER(StreamPartitionArgs)]
         L.relux_seq_save_file.argtypes = [C.c_void_p, C.c_int32, C.c_char_p, C.c_int32]
         L.relux_seq_load_file.argtypes = [C.c_void_p, C.c_int32, C.c_char_p, C.c_int32, C.c_void_p]
         L.relux_gqa_forward_cached.argtypes = [C.c_void_p, C.POINTER(GqaLayerArgs)]

@@ -49,8 +49,10 @@ def stream_partition(pages, workers, page_multiple=2):
     wf = np.empty(cap + 2, np.int32)
     co = np.empty(len(pg) + 1, np.int32)
     G, W = C.c_int32(), C.c_int32()
-    n = lib.relux_stream_partition(pg.ctypes.data, len(pg), int(workers), int(page_multiple), C.byref(G), C.byref(W), items.ctypes.data,
-                                   cap, wf.ctypes.data, co.ctypes.data)
+    args = L.StreamPartitionArgs(pages=pg.ctypes.data, n_seqs=len(pg), workers=int(workers), page_multiple=int(page_multiple), cap=cap,
+                                 range_pages_out=C.addressof(G), workers_out=C.addressof(W), items_out=items.ctypes.data,
+                                 worker_first=wf.ctypes.data, chunk_off=co.ctypes.data)
+    n = lib.relux_stream_partition(C.byref(args))
     if n < 0:
         raise ValueError("stream_partition: bad arguments")
     return G.value, W.value, items[:n].copy(), wf[:W.value + 1].copy(), co

@@ -109,15 +109,17 @@ class GpuAttention:
     def __init__(self, dev, cfg, weights, mode):
         import ctypes as C
         import relux_b200 as rb
+        from relux_b200 import lib as L
         self.C, self.cfg, self.mode, self.dev = C, cfg, mode, dev
         self.hd = cfg.dModel // cfg.numHeads
+        compat = mode == L.ATTN_REFERENCE_FAITHFUL
         if cfg.mla:
-            self.cache = rb.MLACache(dev, cfg.numLayers, cfg.maxSeqLen, cfg.dC, cfg.dHR)
+            self.cache = rb.MLACache(dev, cfg.numLayers, cfg.maxSeqLen, cfg.dC, cfg.dHR, reference_compat=compat)
             self.w = [(dev.upload(weights[a:a + cfg.dC * cfg.numHeads * self.hd]), dev.upload(weights[b:b + cfg.dC * cfg.numHeads * self.hd]))
                       for a, b in layer_weight_offsets(cfg)]
             self.scale = float(np.float32(1.0 / np.sqrt(np.float64(self.hd + cfg.dHR))))
         else:
-            self.cache = rb.KVCache(dev, cfg.numLayers, cfg.maxSeqLen, cfg.numKVHeads, self.hd)
+            self.cache = rb.KVCache(dev, cfg.numLayers, cfg.maxSeqLen, cfg.numKVHeads, self.hd, reference_compat=compat)
             self.scale = float(np.float32(1.0 / np.sqrt(np.float64(self.hd))))
 
     def reset(self):
@@ -195,10 +197,12 @@ class GpuLayer:
         self.cfg, self.mode, self.dev, self.error = cfg, mode, dev, None
         pages = (cfg.maxSeqLen + page_tokens - 1) // page_tokens
         hd = cfg.dModel // cfg.numHeads
+        compat = mode == L.ATTN_REFERENCE_FAITHFUL
         if cfg.mla:
-            self.pool = rb.Pool(dev, L.POOL_MLA, cfg.numLayers, pages, page_tokens, 1, pages, dC=cfg.dC, dHR=cfg.dHR)
+            self.pool = rb.Pool(dev, L.POOL_MLA, cfg.numLayers, pages, page_tokens, 1, pages, dC=cfg.dC, dHR=cfg.dHR, reference_compat=compat)
         else:
-            self.pool = rb.Pool(dev, L.POOL_GQA, cfg.numLayers, pages, page_tokens, 1, pages, num_kv_heads=cfg.numKVHeads, head_dim=hd)
+            self.pool = rb.Pool(dev, L.POOL_GQA, cfg.numLayers, pages, page_tokens, 1, pages, num_kv_heads=cfg.numKVHeads, head_dim=hd,
+                                reference_compat=compat)
         self.pool.set_tables(np.arange(pages, dtype=np.int32)[::-1].copy().reshape(1, pages))
         self.w = [{k: dev.upload(np.ascontiguousarray(v)) for k, v in d.items()} for d in layer_weight_arrays(cfg, weights)]
 

@@ -56,7 +56,11 @@ def test_struct_sizes_match_the_header(so):
         #include <stdio.h>
         #include "relux_cuda.h"
         #include <stddef.h>
-        int main(void){ printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(relux_pool_params), sizeof(relux_append_args),
+        int main(void){ printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(relux_read_rows_args), offsetof(relux_read_rows_args, dst_b),
+                               sizeof(relux_stream_partition_args), offsetof(relux_stream_partition_args, chunk_off),
+                               sizeof(relux_matmul_args), offsetof(relux_matmul_args, b), offsetof(relux_matmul_args, c),
+                               sizeof(relux_mla_import_args), offsetof(relux_mla_import_args, q_proj), offsetof(relux_mla_import_args, dst));
+                        printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(relux_pool_params), sizeof(relux_append_args),
                                sizeof(relux_attn_args), sizeof(relux_mla_layer_weights), sizeof(relux_mla_layer_args),
                                sizeof(relux_gqa_layer_weights), sizeof(relux_gqa_layer_args),
                                offsetof(relux_mla_layer_args, w), offsetof(relux_gqa_layer_args, w),
@@ -70,6 +74,11 @@ def test_struct_sizes_match_the_header(so):
         exe = os.path.join(d, "s")
         subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
         sizes = [int(x) for x in subprocess.check_output([exe]).split()]
+    assert sizes[:10] == [C.sizeof(so.ReadRowsArgs), so.ReadRowsArgs.dst_b.offset, C.sizeof(so.StreamPartitionArgs),
+                          so.StreamPartitionArgs.chunk_off.offset, C.sizeof(so.MatmulArgs), so.MatmulArgs.b.offset, so.MatmulArgs.c.offset,
+                          C.sizeof(so.MlaImportArgs), so.MlaImportArgs.q_proj.offset, so.MlaImportArgs.dst.offset]
+    sizes = sizes[10:]
+    assert so.PoolParams.flags.offset == 40
     assert sizes == [C.sizeof(so.PoolParams), C.sizeof(so.AppendArgs), C.sizeof(so.AttnArgs), C.sizeof(so.MlaLayerWeights),
                      C.sizeof(so.MlaLayerArgs), C.sizeof(so.GqaLayerWeights), C.sizeof(so.GqaLayerArgs), so.MlaLayerArgs.w.offset,
                      so.GqaLayerArgs.w.offset, C.sizeof(so.SamplerParams), C.sizeof(so.SpecAcceptArgs),

@@ -221,3 +221,84 @@ def test_sequence_grows_page_by_page(dev, oracle):
     assert e.value.code == L.ERR_OVERFLOW
     assert pool.status() == 0
     pool.destroy()
+
+
+def test_a_sequence_named_twice_is_refused_whatever_the_batch_size(dev):
+    """Two blocks of one append would write the same rows and the cursor would move twice: refused on the host, for
+    small batches and for batches of hundreds of sequences alike."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    n = 300
+    pool = rb.Pool(dev, L.POOL_MLA, 1, n, 64, n, 1, dC=64, dHR=16)
+    pool.set_tables(np.arange(n, dtype=np.int32).reshape(n, 1))
+    c = np.ones((n, 64), np.float32); r = np.ones((n, 16), np.float32)
+    for ids in ([0, 1, 1], list(range(n - 1)) + [17]):
+        with pytest.raises(L.ReluxCudaError) as e:
+            pool.append(0, c[:len(ids)], r[:len(ids)], len(ids), seq_ids=ids)
+        assert e.value.code == L.ERR_INVALID_ARG and "twice" in str(e.value)
+    assert all(pool.seq_len(0, s) == 0 for s in (0, 1, 17))
+    pool.append(0, c, r, n, seq_ids=list(range(n))[::-1])   # a permutation is fine
+    assert pool.seq_len(0, 17) == 1 and pool.status() == 0
+    pool.destroy()
+
+
+def test_misaligned_device_pointers_are_refused_before_any_launch(dev):
+    """The kernels read device inputs with 16-byte vector loads; an offset pointer would fault.  It is refused."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    pool = rb.Pool(dev, L.POOL_MLA, 1, 2, 64, 1, 2, dC=64, dHR=16)
+    pool.set_tables(np.arange(2, dtype=np.int32).reshape(1, 2))
+    buf = dev.alloc(4096, L.DTYPE_BF16)
+    n0 = dev.launch_count()
+    with pytest.raises(L.ReluxCudaError) as e:
+        pool.append(0, buf.ptr + 2, buf.ptr + 1024, 1, dtype=L.DTYPE_BF16)
+    assert e.value.code == L.ERR_INVALID_ARG and "aligned" in str(e.value)
+    assert dev.launch_count() == n0 and pool.seq_len(0, 0) == 0
+    pool.append(0, buf.ptr + 16, buf.ptr + 1024, 1, dtype=L.DTYPE_BF16)   # 16-byte aligned offsets are fine
+    w = dev.alloc(64 * 2 * 32 * 2 + 64, L.DTYPE_BF16)
+    q = dev.alloc(8192, L.DTYPE_F32)
+    with pytest.raises(L.ReluxCudaError) as e:
+        pool.decode(0, 1, q.ptr + 4, q.ptr + 4096, 2, 32, 0.1, q_rope=q.ptr + 2048, w_uk=w, w_uv=w, q_dtype=L.DTYPE_F32, out_dtype=L.DTYPE_F32)
+    assert e.value.code == L.ERR_INVALID_ARG
+    assert pool.status() == 0
+    for b in (buf, w, q):
+        b.free()
+    pool.destroy()
+
+
+def test_a_wait_that_nobody_answers_gives_up_and_reports(dev):
+    """Every device-side wait of the library is bounded.  The self test runs the same polling loop on a barrier nobody
+    arrives at, with a limit of a few thousand polls: the kernel returns, the status word says RELUX_ERR_TIMEOUT, and the
+    context is as usable afterwards as before."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    pool = rb.Pool(dev, L.POOL_MLA, 1, 2, 64, 1, 2, dC=64, dHR=16)
+    pool.set_tables(np.arange(2, dtype=np.int32).reshape(1, 2))
+    assert pool.status() == 0
+    pool.selftest_wait(3000)
+    assert pool.status() == L.ERR_TIMEOUT
+    assert pool.status() == 0   # reading clears it
+    pool.append(0, np.ones((1, 64), np.float32), np.ones((1, 16), np.float32), 1)
+    assert pool.seq_len(0, 0) == 1 and pool.status() == 0
+    pool.destroy()
+
+
+def test_one_owner_of_the_pages_per_pool(dev):
+    """Caller-made page tables and the library's free list do not mix on one pool, and a page may be mapped once."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    pool = rb.Pool(dev, L.POOL_MLA, 1, 4, 64, 2, 2, dC=64, dHR=16)
+    with pytest.raises(L.ReluxCudaError) as e:
+        pool.set_tables(np.array([[0, 1], [1, 2]], np.int32))
+    assert e.value.code == L.ERR_BAD_PAGE and "twice" in str(e.value)
+    pool.set_tables(np.array([[0, 1], [3, 2]], np.int32))
+    with pytest.raises(L.ReluxCudaError) as e:
+        pool.seq_alloc(10)
+    assert e.value.code == L.ERR_INVALID_ARG
+    pool.destroy()
+    pool = rb.Pool(dev, L.POOL_MLA, 1, 4, 64, 2, 2, dC=64, dHR=16)
+    pool.seq_alloc(10)
+    with pytest.raises(L.ReluxCudaError) as e:
+        pool.set_tables(np.array([[0, 1], [3, 2]], np.int32))
+    assert e.value.code == L.ERR_INVALID_ARG
+    pool.destroy()

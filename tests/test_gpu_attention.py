@@ -338,10 +338,10 @@ def test_gqa_fast_prompt_longer_than_one_group(dev, oracle, causal):
 
 
 @pytest.mark.parametrize("budget_mb", [None, 1])
-def test_gqa_fast_long_prompt_as_grid_slices(dev, oracle, budget_mb, monkeypatch):
+def test_gqa_fast_long_prompt_as_grid_slices(dev, oracle, budget_mb):
     """A prompt of 203 tokens (26 groups of 8, the last one short) on three sequences of different cached lengths: the
-    groups run as z slices of one grid over one work list; with a partial budget of 1 MiB the same call is cut into
-    several launches.  Both must match the restatement, and so must the one-launch-per-group path kept for comparison."""
+    groups run as z slices of one grid over one work list; with a partial budget of 1 MiB (a tuning knob of the pool)
+    the same call is cut into several launches.  Both must match the restatement."""
     rng = np.random.default_rng(52)
     H, Hkv, D, S = 32, 8, 128, 203
     ctx = [S, 300 + S, 1000]
@@ -351,15 +351,12 @@ def test_gqa_fast_long_prompt_as_grid_slices(dev, oracle, budget_mb, monkeypatch
     out = np.empty_like(q)
     scale = float(1.0 / np.sqrt(D))
     if budget_mb is not None:
-        monkeypatch.setenv("RELUX_GQA_PROMPT_PARTIAL_MB", str(budget_mb))
+        from relux_b200 import lib as L
+        pool.tune(L.TUNE_GQA_PROMPT_PARTIAL_MB, budget_mb)
     pool.decode(0, B, q, out, H, D, scale, q_tokens=S, causal=True)
     with oracle.exact_exp():
         ref = oracle.gqa_attend(Kl, Vl, ctx, q, scale, causal=True)
     check_attention(out, ref, "gqa long prompt", max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
-    monkeypatch.setenv("RELUX_GQA_PROMPT_SERIAL", "1")
-    serial = np.empty_like(q)
-    pool.decode(0, B, q, serial, H, D, scale, q_tokens=S, causal=True)
-    check_attention(serial, ref, "gqa long prompt, one launch per group", max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
     assert pool.status() == 0
     pool.destroy()
 

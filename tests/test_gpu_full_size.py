@@ -64,12 +64,10 @@ def test_config3_full_batch_properties(dev, oracle):
             pool.decode(0, B, qc, out2, H, Dh, scale, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv2)
             assert np.array_equal(out2, out * 2.0)
             # split-KV invariance: another chunk length changes only float32 association
-            os.environ["RELUX_CHUNK_PAGES"] = "6"
-            try:
-                out3 = np.empty_like(out)
-                pool.decode(0, B, qc, out3, H, Dh, scale, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv)
-            finally:
-                del os.environ["RELUX_CHUNK_PAGES"]
+            pool.tune(L.TUNE_CHUNK_PAGES, 6)
+            out3 = np.empty_like(out)
+            pool.decode(0, B, qc, out3, H, Dh, scale, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv)
+            pool.tune(L.TUNE_CHUNK_PAGES, -1)
             assert np.abs(out3 - out).max() <= 1e-3
         assert pool.status() == 0
         pool.destroy()
@@ -87,7 +85,9 @@ def test_config3_full_batch_properties(dev, oracle):
 
 def test_config4_ragged_long_context_sample(dev, oracle):
     """config 4 shapes on one GPU's share: 16 sequences with lengths uniform in [1024, 32768] (seed 11), random page
-    permutation, a few append + decode steps; sampled sequences checked against the oracle at every step."""
+    permutation, 70 append + decode steps, so that EVERY sequence crosses a page boundary (64-token pages) inside the run;
+    the shortest and the longest sequence are checked against the oracle on the first steps, around step 64 and at the
+    end, and the rows appended during the run are read back bit for bit for every sequence."""
     from relux_b200 import lib as L
     rng = np.random.default_rng(11)
     all_len = rng.integers(1024, 32769, 128)
@@ -106,7 +106,9 @@ def test_config4_ragged_long_context_sample(dev, oracle):
     shortest, longest = int(np.argmin(ctx)), int(np.argmax(ctx))
     rows_c = {b: [c[off[b]:off[b + 1]]] for b in (shortest, longest)}
     rows_r = {b: [r[off[b]:off[b + 1]]] for b in (shortest, longest)}
-    for step in range(3):
+    n_steps, checked = 70, (0, 1, 63, 64, 69)
+    new_c, new_r = [], []
+    for step in range(n_steps):
         nc = rng.standard_normal((B, dC), dtype=np.float32)
         nr = rng.standard_normal((B, dHR), dtype=np.float32)
         qc = rng.standard_normal((B, 1, H, Dh), dtype=np.float32)
@@ -115,12 +117,20 @@ def test_config4_ragged_long_context_sample(dev, oracle):
         out = np.empty((B, 1, H, Dh), np.float32)
         pool.decode(0, B, qc, out, H, Dh, scale, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv)
         assert np.isfinite(out).all()
+        new_c.append(oracle.bf16_from_f32(nc)); new_r.append(oracle.bf16_from_f32(nr))
         for b in (shortest, longest):
             rows_c[b].append(oracle.bf16_from_f32(nc[b])[None]); rows_r[b].append(oracle.bf16_from_f32(nr[b])[None])
+            if step not in checked:
+                continue
             cl, rl = np.concatenate(rows_c[b])[None], np.concatenate(rows_r[b])[None]
             assert pool.seq_len(0, b) == cl.shape[1]
             ref = oracle.mla_attend(cl, rl, [cl.shape[1]], qc[b:b + 1], qr[b:b + 1], wuk, wuv, scale, absorbed=True)
             check_attention(out[b:b + 1], ref, "config 4 step %d seq %d (ctx %d)" % (step, b, cl.shape[1]))
+    new_c, new_r = np.stack(new_c, 1), np.stack(new_r, 1)   # [B, steps, ...]
+    for b in range(B):   # every sequence crossed a page boundary: the appended rows are where a reader expects them
+        assert (int(ctx[b]) // 64) != ((int(ctx[b]) + n_steps) // 64)
+        gc, gr = pool.read_rows(0, b, int(ctx[b]), n_steps)
+        assert np.array_equal(gc, new_c[b]) and np.array_equal(gr, new_r[b])
     assert pool.status() == 0
     pool.destroy(); d_wuk.free(); d_wuv.free()
 

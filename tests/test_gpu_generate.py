@@ -1,5 +1,10 @@
 """Greedy-decoded token ids on the two CPU-runnable configurations with the CUDA library plugged in at the
-reference's cache / attention seam (RELUX_ATTN_REFERENCE arithmetic): ids must be IDENTICAL to the oracle's."""
+reference's cache / attention seam: ids must be IDENTICAL to the oracle's.
+
+Two targets.  RELUX_ATTN_REFERENCE_FAITHFUL against the restatement of relux AS IT IS (golden `runs.faithful`: the GQA
+cache read head-major over a chunk-linear stream, cached MLA reading token-major K/V as head-major, float32 MLA rows, no
+mask inside a multi-token cached call) -- the ids relux itself emits.  RELUX_ATTN_REFERENCE against the restatement with
+textbook indexing (`runs.intended`), the semantics of the batched kernels."""
 import json
 import os
 
@@ -21,11 +26,13 @@ def dev():
 
 
 def _generate(oracle, dev, name, prompt, n_new, mode):
+    from relux_b200 import lib as L
     cfg = model_config(name)
     w = model_weights(cfg)
     att = GpuAttention(dev, cfg, w, mode)
     m = oracle.Model(cfg, w)
-    m.set_mode(oracle.INTENDED)
+    # the restatement's own switch decides what stays on the CPU side of the seam: RoPE positions of the rows it hands over
+    m.set_mode(oracle.FAITHFUL if mode == L.ATTN_REFERENCE_FAITHFUL else oracle.INTENDED)
     if cfg.mla:
         m.set_hooks(mla=att.mla_hook)
     else:
@@ -59,6 +66,30 @@ def test_config2_greedy_ids_identical(oracle, dev):
         assert first is None, "sequence %d diverges at position %d" % (s, first)
 
 
+def test_config1_greedy_ids_identical_to_the_reference_as_it_is(oracle, dev):
+    """Config 1 (GQA, 2 kv heads): after the first decode step the reference reads other rows than the textbook ones
+    (chunk-linear write, head-major read).  With the compat pool and RELUX_ATTN_REFERENCE_FAITHFUL the library reads the
+    same rows: all 56 ids equal the faithful restatement's, which differ from the intended ones."""
+    from relux_b200 import lib as L
+    g = json.load(open(os.path.join(GOLD, "config1_generate.json")))
+    p = prompts_for("config1")[0]
+    ids, _ = _generate(oracle, dev, "config1", p, 56, L.ATTN_REFERENCE_FAITHFUL)
+    assert ids.tolist() == g["runs"]["faithful"]["ids"][0]
+    assert g["runs"]["faithful"]["ids"][0] != g["runs"]["intended"]["ids"][0]
+
+
+def test_config2_greedy_ids_identical_to_the_reference_as_it_is(oracle, dev):
+    """Config 2 (MLA, 8 heads): 4 prompts of 32 tokens decoded to 512; the compat pool keeps float32 latent rows like the
+    reference's MLACache, so the target is the faithful restatement with its float32 cache."""
+    from relux_b200 import lib as L
+    g = json.load(open(os.path.join(GOLD, "config2_generate.json")))
+    for s, p in enumerate(prompts_for("config2")):
+        ids, _ = _generate(oracle, dev, "config2", p, 480, L.ATTN_REFERENCE_FAITHFUL)
+        gold = g["runs"]["faithful"]["ids"][s]
+        first = next((i for i in range(len(gold)) if ids[i] != gold[i]), None)
+        assert first is None, "sequence %d diverges at position %d" % (s, first)
+
+
 def test_config2_fast_mode_first_tokens(oracle, dev):
     """FAST arithmetic (bf16 tensor-core style contractions, exact exp2) is not bit-compatible with the reference's
     fastexp32; ids agree until a near-tie in the logits.  The test pins the prefill + first decoded tokens and reports
@@ -74,11 +105,12 @@ def test_config2_fast_mode_first_tokens(oracle, dev):
 
 
 def _generate_layer_level(oracle, dev, name, prompt, n_new, mode):
+    from relux_b200 import lib as L
     cfg = model_config(name)
     w = model_weights(cfg)
     lay = GpuLayer(dev, cfg, w, mode)
     m = oracle.Model(cfg, w)
-    m.set_mode(oracle.INTENDED)
+    m.set_mode(oracle.FAITHFUL if mode == L.ATTN_REFERENCE_FAITHFUL else oracle.INTENDED)
     m.set_layer_hook(lay.hook)
     try:
         ids, margins, ties = m.generate(prompt, n_new)
@@ -104,5 +136,23 @@ def test_config2_greedy_ids_identical_with_the_whole_layer_on_the_gpu(oracle, de
     g = json.load(open(os.path.join(GOLD, "config2_generate.json")))
     ids = _generate_layer_level(oracle, dev, "config2", prompts_for("config2")[0], 480, L.ATTN_REFERENCE)
     gold = g["runs"]["intended_bf16_cache"]["ids"][0]
+    first = next((i for i in range(len(gold)) if ids[i] != gold[i]), None)
+    assert first is None, "diverges at position %d" % first
+
+
+def test_config1_faithful_ids_with_the_whole_layer_on_the_gpu(oracle, dev):
+    """relux_gqa_forward_cached in RELUX_ATTN_REFERENCE_FAITHFUL mode (the reference's RoPE position rule and cache
+    indexing inside the library): the 56 ids equal the faithful restatement's."""
+    from relux_b200 import lib as L
+    g = json.load(open(os.path.join(GOLD, "config1_generate.json")))
+    ids = _generate_layer_level(oracle, dev, "config1", prompts_for("config1")[0], 56, L.ATTN_REFERENCE_FAITHFUL)
+    assert ids.tolist() == g["runs"]["faithful"]["ids"][0]
+
+
+def test_config2_faithful_ids_with_the_whole_layer_on_the_gpu(oracle, dev):
+    from relux_b200 import lib as L
+    g = json.load(open(os.path.join(GOLD, "config2_generate.json")))
+    ids = _generate_layer_level(oracle, dev, "config2", prompts_for("config2")[1], 480, L.ATTN_REFERENCE_FAITHFUL)
+    gold = g["runs"]["faithful"]["ids"][1]
     first = next((i for i in range(len(gold)) if ids[i] != gold[i]), None)
     assert first is None, "diverges at position %d" % first
