@@ -215,6 +215,21 @@ int32_t relux_pool_read_rows(relux_pool_t pool, const relux_read_rows_args* args
  * built-in default.  Tuning aid: no counterpart in the reference. */
 int32_t relux_pool_tune(relux_pool_t pool, int32_t knob, int32_t value);
 
+/* ---- call flags (relux_append_args.flags, relux_attn_args.flags) -----------------------------------
+ * RELUX_CALL_PIPELINED: inputs and outputs that live in HOST memory travel on two copy streams of their own instead of
+ * the handle's compute stream: inputs into one of two staging slots on the device, outputs from one of two result
+ * slots, with events between the streams.  The call returns as soon as its work is queued, so the copies of the next
+ * call overlap the kernels of this one.  Rules for the caller: pass page-locked buffers (relux_cuda_host_alloc) --
+ * pageable ones make the copies synchronous --; leave an input buffer unchanged, and an output buffer unread, until
+ * relux_pool_wait_output (or relux_cuda_sync) has returned for that call; give calls that may be in flight together
+ * different output buffers.  relux_cuda_sync and relux_cuda_event_record cover the copy streams.  The reference has no
+ * counterpart: its tensors never leave host memory (internal/alloc/alloc.go:15-18). */
+#define RELUX_CALL_PIPELINED 1
+/* Blocks until the host-memory output of a pipelined attention call has landed: calls_back = 0 the most recent such
+ * call on this pool, 1 the one before it (two result slots exist; a third call in flight waits on the device for the
+ * first one's copy).  No counterpart in the reference. */
+int32_t relux_pool_wait_output(relux_pool_t pool, int32_t calls_back);
+
 /* ---- append -------------------------------------------------------------------------------
  * MLACache.Append (mla_cache.go:152-182) fed by MLA.forwardCached step 4 (mla.go:309-312):
  * the latent c^KV and the already rotated shared key k^R of n_new[i] tokens per sequence.
@@ -235,7 +250,8 @@ typedef struct relux_append_args {
   int32_t layout;           /* GQA only: TOKEN_MAJOR [tok][Hkv][D] or HEAD_MAJOR [Hkv][n_new_i][D] per sequence */
   int32_t advance;          /* 1: lengths grow by n_new.  0: rows are written past the cursor, lengths unchanged
                                (draft rows of a speculative verify; commit with relux_seq_set_len) */
-  int32_t reserved[4];
+  int32_t flags;            /* RELUX_CALL_* */
+  int32_t reserved[3];
 } relux_append_args;
 int32_t relux_mla_append(relux_pool_t pool, const relux_append_args* args);
 int32_t relux_gqa_append(relux_pool_t pool, const relux_append_args* args);
@@ -268,8 +284,9 @@ typedef struct relux_attn_args {
   const void* w_uv;
   void* out;                /* [n][S][H][head_dim] */
   int32_t out_dtype, out_mem, out_layout;
-  int32_t mode;             /* RELUX_ATTN_FAST | RELUX_ATTN_REFERENCE */
-  int32_t reserved[5];
+  int32_t mode;             /* RELUX_ATTN_FAST | RELUX_ATTN_REFERENCE | RELUX_ATTN_REFERENCE_FAITHFUL */
+  int32_t flags;            /* RELUX_CALL_* */
+  int32_t reserved[4];
 } relux_attn_args;
 int32_t relux_mla_decode(relux_pool_t pool, const relux_attn_args* args);
 int32_t relux_gqa_decode(relux_pool_t pool, const relux_attn_args* args);

@@ -236,6 +236,10 @@ class Pool:
         L.check(self.lib.relux_pool_read_rows(self.h, C.byref(args)))
         return a, b
 
+    def wait_output(self, calls_back=0):
+        """Blocks until the host output of a pipelined attention call has landed (0: the latest call, 1: the one before)."""
+        L.check(self.lib.relux_pool_wait_output(self.h, int(calls_back)))
+
     def tune(self, knob, value):
         """Sets one tuning knob (L.TUNE_*); a negative value restores the built-in default."""
         L.check(self.lib.relux_pool_tune(self.h, int(knob), int(value)))
@@ -288,33 +292,37 @@ class Pool:
         L.check(self.lib.relux_pool_kernel_ms_list(self.h, int(last_n), out.ctypes.data, C.byref(n)))
         return out[:n.value]
 
-    def _append_args(self, layer, a, b, n_seqs, seq_ids, n_new, layout, advance, dtype):
+    def _append_args(self, layer, a, b, n_seqs, seq_ids, n_new, layout, advance, dtype, pipelined=False):
         ids = None if seq_ids is None else np.ascontiguousarray(seq_ids, dtype=np.int32)
         nn = None if n_new is None else np.ascontiguousarray(n_new, dtype=np.int32)
         self._keep = [ids, nn, a, b]
         return L.AppendArgs(layer=layer, n_seqs=n_seqs, seq_ids=_ptr(ids), n_new=_ptr(nn), a=_ptr(a), b=_ptr(b),
-                            dtype=_dtype_flag(a, dtype), mem=_mem(a), layout=layout, advance=int(advance))
+                            dtype=_dtype_flag(a, dtype), mem=_mem(a), layout=layout, advance=int(advance),
+                            flags=L.CALL_PIPELINED if pipelined else 0)
 
-    def append(self, layer, a, b, n_seqs, seq_ids=None, n_new=None, layout=L.LAYOUT_TOKEN_MAJOR, advance=True, dtype=None):
-        """MLA: a = c_kv [rows, dC], b = k_rope [rows, dHR].  GQA: a = K, b = V."""
-        args = self._append_args(layer, a, b, n_seqs, seq_ids, n_new, layout, advance, dtype)
+    def append(self, layer, a, b, n_seqs, seq_ids=None, n_new=None, layout=L.LAYOUT_TOKEN_MAJOR, advance=True, dtype=None,
+               pipelined=False):
+        """MLA: a = c_kv [rows, dC], b = k_rope [rows, dHR].  GQA: a = K, b = V.  pipelined: host inputs travel on the copy
+        stream and the call returns once queued (see RELUX_CALL_PIPELINED in include/relux_cuda.h)."""
+        args = self._append_args(layer, a, b, n_seqs, seq_ids, n_new, layout, advance, dtype, pipelined)
         fn = self.lib.relux_mla_append if self.kind == L.POOL_MLA else self.lib.relux_gqa_append
         L.check(fn(self.h, C.byref(args)))
 
     def _attn_args(self, layer, n_seqs, q, q_rope, out, num_heads, head_dim, scale, q_tokens, extra_tokens, causal, mode,
-                   w_uk, w_uv, seq_ids, q_layout, out_layout, q_dtype, out_dtype):
+                   w_uk, w_uv, seq_ids, q_layout, out_layout, q_dtype, out_dtype, pipelined=False):
         ids = None if seq_ids is None else np.ascontiguousarray(seq_ids, dtype=np.int32)
         self._keep2 = [ids, q, q_rope, out]
         return L.AttnArgs(layer=layer, n_seqs=n_seqs, seq_ids=_ptr(ids), q_tokens=q_tokens, extra_tokens=extra_tokens,
                           causal=int(causal), num_heads=num_heads, head_dim=head_dim, scale=scale, q=_ptr(q), q_rope=_ptr(q_rope),
                           q_dtype=_dtype_flag(q, q_dtype), q_mem=_mem(q), q_layout=q_layout, w_uk=_ptr(w_uk), w_uv=_ptr(w_uv),
-                          out=_ptr(out), out_dtype=_dtype_flag(out, out_dtype), out_mem=_mem(out), out_layout=out_layout, mode=mode)
+                          out=_ptr(out), out_dtype=_dtype_flag(out, out_dtype), out_mem=_mem(out), out_layout=out_layout, mode=mode,
+                          flags=L.CALL_PIPELINED if pipelined else 0)
 
     def decode(self, layer, n_seqs, q, out, num_heads, head_dim, scale, q_rope=None, w_uk=None, w_uv=None, q_tokens=1,
                extra_tokens=0, causal=True, mode=L.ATTN_FAST, seq_ids=None, q_layout=L.LAYOUT_TOKEN_MAJOR,
-               out_layout=L.LAYOUT_TOKEN_MAJOR, q_dtype=None, out_dtype=None):
+               out_layout=L.LAYOUT_TOKEN_MAJOR, q_dtype=None, out_dtype=None, pipelined=False):
         args = self._attn_args(layer, n_seqs, q, q_rope, out, num_heads, head_dim, scale, q_tokens, extra_tokens, causal, mode,
-                               w_uk, w_uv, seq_ids, q_layout, out_layout, q_dtype, out_dtype)
+                               w_uk, w_uv, seq_ids, q_layout, out_layout, q_dtype, out_dtype, pipelined)
         fn = self.lib.relux_mla_decode if self.kind == L.POOL_MLA else self.lib.relux_gqa_decode
         L.check(fn(self.h, C.byref(args)))
 
@@ -328,12 +336,12 @@ class Pool:
 
     def verify(self, layer, n_seqs, q, out, draft_a, draft_b, num_heads, head_dim, scale, q_tokens, q_rope=None, w_uk=None,
                w_uv=None, mode=L.ATTN_FAST, seq_ids=None, kv_layout=L.LAYOUT_TOKEN_MAJOR, q_dtype=None, out_dtype=None,
-               kv_dtype=None):
+               kv_dtype=None, pipelined=False):
         """Speculative verify: draft rows are written past the cursor, q_tokens rows attend causally."""
         n_new = np.full(n_seqs, q_tokens, np.int32)
-        ap = self._append_args(layer, draft_a, draft_b, n_seqs, seq_ids, n_new, kv_layout, False, kv_dtype)
+        ap = self._append_args(layer, draft_a, draft_b, n_seqs, seq_ids, n_new, kv_layout, False, kv_dtype, pipelined)
         at = self._attn_args(layer, n_seqs, q, q_rope, out, num_heads, head_dim, scale, q_tokens, q_tokens, True, mode, w_uk, w_uv,
-                             seq_ids, L.LAYOUT_TOKEN_MAJOR, L.LAYOUT_TOKEN_MAJOR, q_dtype, out_dtype)
+                             seq_ids, L.LAYOUT_TOKEN_MAJOR, L.LAYOUT_TOKEN_MAJOR, q_dtype, out_dtype, pipelined)
         fn = self.lib.relux_mla_verify if self.kind == L.POOL_MLA else self.lib.relux_gqa_verify
         L.check(fn(self.h, C.byref(at), C.byref(ap)))
 

@@ -37,6 +37,10 @@ struct Device {
   // side stream for small kernels that do not depend on their predecessor (forked from / joined to `stream` by events)
   cudaStream_t side_stream = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  // copy streams of pipelined calls (RELUX_CALL_PIPELINED): host -> device inputs, device -> host outputs
+  cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
+  cudaEvent_t ev_copy_join = nullptr;
+  bool copies_in_flight = false;
   std::mutex mu;
   int64_t launches = 0;
   void* flush_buf = nullptr;
@@ -57,6 +61,16 @@ struct GrowBuf {
 struct Tuning {
   int32_t v[RELUX_TUNE_COUNT];
   int32_t get(int knob) const { return v[knob]; }
+};
+
+// Two device buffers used in turn by pipelined calls.  `ready`: the copy into (inputs) or the kernels writing (outputs)
+// the slot are done; `freed`: whoever read the slot is done with it, so it may be overwritten.
+struct PipeSlots {
+  static constexpr int kSlots = 2;
+  GrowBuf buf[kSlots];
+  cudaEvent_t ready[kSlots] = {}, freed[kSlots] = {};
+  bool used[kSlots] = {};
+  uint64_t next = 0;
 };
 
 struct Pool {
@@ -98,6 +112,7 @@ struct Pool {
   size_t stage_slot_ints() const { return 2 * (size_t)prm.max_seqs + 1; }
   // staging of activations that arrive in host memory, and outputs that leave to it
   GrowBuf in_a, in_b, out_buf, q_conv;
+  PipeSlots pipe_in_a, pipe_in_b, pipe_app_a, pipe_app_b, pipe_out;   // the same for pipelined calls
   // attention scratch
   GrowBuf q_abs;     // MLA absorbed queries, bf16 [n][S][H][dC+dHR]
   GrowBuf part_o;    // split-KV partial accumulators, f32
@@ -140,6 +155,10 @@ inline Pool* as_pool(relux_pool_t h) {
 }
 
 int32_t grow(Device* dev, GrowBuf& b, size_t bytes);
+// Pipelined staging: copies a host input into the next slot on the copy stream and makes the compute stream wait for it;
+// pipe_release is called once the kernels that read the slot have been queued.
+int32_t pipe_stage_in(Pool* p, PipeSlots& ps, const void* src, size_t bytes, const void** dptr, int* slot);
+int32_t pipe_release(Pool* p, PipeSlots& ps, int slot);
 // Next staging slot (waits for the copy that last used it); call stage_release after the copies are enqueued.
 int32_t stage_acquire(Pool* p, int32_t** slot, int* slot_index);
 int32_t stage_release(Pool* p, int slot_index);

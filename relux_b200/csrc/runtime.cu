@@ -169,6 +169,14 @@ void tuning_defaults(Tuning* t);
 
 static void pool_free_all(Pool* p) {
   auto fr = [](void* q) { if (q) cudaFree(q); };
+  for (cudaStream_t st : {p->dev->h2d_stream, p->dev->d2h_stream})
+    if (st) cudaStreamSynchronize(st);
+  for (PipeSlots* ps : {&p->pipe_in_a, &p->pipe_in_b, &p->pipe_app_a, &p->pipe_app_b, &p->pipe_out})
+    for (int i = 0; i < PipeSlots::kSlots; i++) {
+      fr(ps->buf[i].p);
+      if (ps->ready[i]) cudaEventDestroy(ps->ready[i]);
+      if (ps->freed[i]) cudaEventDestroy(ps->freed[i]);
+    }
   fr(p->storage); fr(p->d_table); fr(p->d_len); fr(p->d_status); fr(p->d_seq_ids); fr(p->d_row_off);
   fr(p->in_a.p); fr(p->in_b.p); fr(p->out_buf.p); fr(p->q_abs.p); fr(p->part_o.p); fr(p->part_ml.p); fr(p->work.p);
   fr(p->o_lat.p); fr(p->q_conv.p); fr(p->rope_tab.p); fr(p->layer_buf.p); fr(p->shadow_f32); fr(p->chunk_tab.p);
@@ -208,6 +216,54 @@ int32_t stage_in(Pool* p, GrowBuf& buf, const void* src, size_t bytes, int mem, 
 
 static size_t dtype_size(int dt) { return dt == RELUX_DTYPE_BF16 ? 2 : 4; }
 
+static int32_t pipe_events(PipeSlots& ps, int slot) {
+  if (!ps.ready[slot]) RELUX_CUDA_TRY(cudaEventCreateWithFlags(&ps.ready[slot], cudaEventDisableTiming));
+  if (!ps.freed[slot]) RELUX_CUDA_TRY(cudaEventCreateWithFlags(&ps.freed[slot], cudaEventDisableTiming));
+  return RELUX_OK;
+}
+// A slot's buffer may be replaced only when nothing queued on any stream still uses it.
+static int32_t pipe_grow(Pool* p, GrowBuf& b, size_t bytes) {
+  if (bytes <= b.cap) return RELUX_OK;
+  Device* dev = p->dev;
+  if (dev->h2d_stream) RELUX_CUDA_TRY(cudaStreamSynchronize(dev->h2d_stream));
+  if (dev->d2h_stream) RELUX_CUDA_TRY(cudaStreamSynchronize(dev->d2h_stream));
+  return grow(dev, b, bytes);
+}
+int32_t pipe_stage_in(Pool* p, PipeSlots& ps, const void* src, size_t bytes, const void** dptr, int* slot) {
+  Device* dev = p->dev;
+  const int s = (int)(ps.next++ % PipeSlots::kSlots);
+  int32_t rc = pipe_events(ps, s);
+  if (rc) return rc;
+  rc = pipe_grow(p, ps.buf[s], bytes);
+  if (rc) return rc;
+  // the kernels that read this slot two calls ago must be done before the copy overwrites it
+  if (ps.used[s]) RELUX_CUDA_TRY(cudaStreamWaitEvent(dev->h2d_stream, ps.freed[s], 0));
+  RELUX_CUDA_TRY(cudaMemcpyAsync(ps.buf[s].p, src, bytes, cudaMemcpyHostToDevice, dev->h2d_stream));
+  RELUX_CUDA_TRY(cudaEventRecord(ps.ready[s], dev->h2d_stream));
+  RELUX_CUDA_TRY(cudaStreamWaitEvent(dev->stream, ps.ready[s], 0));
+  dev->copies_in_flight = true;
+  *dptr = ps.buf[s].p;
+  *slot = s;
+  return RELUX_OK;
+}
+int32_t pipe_release(Pool* p, PipeSlots& ps, int slot) {
+  if (slot < 0) return RELUX_OK;
+  RELUX_CUDA_TRY(cudaEventRecord(ps.freed[slot], p->dev->stream));
+  ps.used[slot] = true;
+  return RELUX_OK;
+}
+// Orders the compute stream after everything queued on the copy streams (used where a caller's event or a full
+// synchronisation must cover the copies of pipelined calls).
+static int32_t join_copy_streams(Device* dev) {
+  if (!dev->copies_in_flight || !dev->ev_copy_join) return RELUX_OK;
+  for (cudaStream_t st : {dev->h2d_stream, dev->d2h_stream}) {
+    if (!st) continue;
+    RELUX_CUDA_TRY(cudaEventRecord(dev->ev_copy_join, st));
+    RELUX_CUDA_TRY(cudaStreamWaitEvent(dev->stream, dev->ev_copy_join, 0));
+  }
+  return RELUX_OK;
+}
+
 int32_t check_dev_align(const void* ptr, const char* what) {
   if (((uintptr_t)ptr & 15u) != 0) {
     set_error("%s: device pointer %p is not 16-byte aligned (the kernels read it with 16-byte vector loads)", what, ptr);
@@ -240,6 +296,7 @@ static int32_t do_append(Pool* p, const relux_append_args* a, int kind) {
     set_error("bad dtype/mem flag");
     return RELUX_ERR_INVALID_ARG;
   }
+  if (a->flags & ~RELUX_CALL_PIPELINED) { set_error("unknown call flags 0x%x", a->flags); return RELUX_ERR_INVALID_ARG; }
   SeqBatch sb;
   rc = stage_batch(p, a->n_seqs, a->seq_ids, a->n_new, 1, &sb);
   if (rc) return rc;
@@ -260,20 +317,22 @@ static int32_t do_append(Pool* p, const relux_append_args* a, int kind) {
   }
   size_t es = dtype_size(a->dtype);
   const void *da = nullptr, *db = nullptr;
-  if (kind == RELUX_POOL_MLA) {
-    rc = stage_in(p, p->in_a, a->a, (size_t)sb.total_rows * prm.mla_dc * es, a->mem, &da);
-    if (rc) return rc;
-    rc = stage_in(p, p->in_b, a->b, (size_t)sb.total_rows * prm.mla_dhr * es, a->mem, &db);
-    if (rc) return rc;
-    rc = launch_mla_append(p, sb, a->layer, da, db, a->dtype, a->advance);
+  const bool piped = (a->flags & RELUX_CALL_PIPELINED) && a->mem == RELUX_MEM_HOST && p->dev->h2d_stream;
+  int slot_a = -1, slot_b = -1;
+  const size_t bytes_a = (kind == RELUX_POOL_MLA) ? (size_t)sb.total_rows * prm.mla_dc * es
+                                                  : (size_t)sb.total_rows * prm.gqa_num_kv_heads * prm.gqa_head_dim * es;
+  const size_t bytes_b = (kind == RELUX_POOL_MLA) ? (size_t)sb.total_rows * prm.mla_dhr * es : bytes_a;
+  if (piped) {
+    if ((rc = pipe_stage_in(p, p->pipe_app_a, a->a, bytes_a, &da, &slot_a))) return rc;
+    if ((rc = pipe_stage_in(p, p->pipe_app_b, a->b, bytes_b, &db, &slot_b))) return rc;
   } else {
-    size_t bytes = (size_t)sb.total_rows * prm.gqa_num_kv_heads * prm.gqa_head_dim * es;
-    rc = stage_in(p, p->in_a, a->a, bytes, a->mem, &da);
-    if (rc) return rc;
-    rc = stage_in(p, p->in_b, a->b, bytes, a->mem, &db);
-    if (rc) return rc;
-    rc = launch_gqa_append(p, sb, a->layer, da, db, a->dtype, a->layout, a->advance);
+    if ((rc = stage_in(p, p->in_a, a->a, bytes_a, a->mem, &da))) return rc;
+    if ((rc = stage_in(p, p->in_b, a->b, bytes_b, a->mem, &db))) return rc;
   }
+  if (kind == RELUX_POOL_MLA) rc = launch_mla_append(p, sb, a->layer, da, db, a->dtype, a->advance);
+  else rc = launch_gqa_append(p, sb, a->layer, da, db, a->dtype, a->layout, a->advance);
+  if (rc) return rc;
+  if ((rc = pipe_release(p, p->pipe_app_a, slot_a)) || (rc = pipe_release(p, p->pipe_app_b, slot_b))) return rc;
   if (rc) return rc;
   if (a->advance)
     for (int i = 0; i < sb.n_seqs; i++) {
@@ -316,6 +375,7 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
     return RELUX_ERR_INVALID_ARG;
   }
   if (!(a->scale > 0.f)) { set_error("scale=%g, must be > 0", (double)a->scale); return RELUX_ERR_INVALID_ARG; }
+  if (a->flags & ~RELUX_CALL_PIPELINED) { set_error("unknown call flags 0x%x", a->flags); return RELUX_ERR_INVALID_ARG; }
   if (a->q_mem == RELUX_MEM_DEVICE) {
     if ((rc = check_dev_align(a->q, "q"))) return rc;
     if (kind == RELUX_POOL_MLA && (rc = check_dev_align(a->q_rope, "q_rope"))) return rc;
@@ -337,11 +397,19 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
   const int n = sb.n_seqs, S = a->q_tokens, H = a->num_heads, D = a->head_dim, R = prm.mla_dhr;
   const size_t q_elems = (size_t)n * S * H * D, qr_elems = (size_t)n * S * H * R;
   const void *dq = nullptr, *dqr = nullptr;
-  rc = stage_in(p, p->in_a, a->q, q_elems * dtype_size(a->q_dtype), a->q_mem, &dq);
-  if (rc) return rc;
-  if (kind == RELUX_POOL_MLA) {
-    rc = stage_in(p, p->in_b, a->q_rope, qr_elems * dtype_size(a->q_dtype), a->q_mem, &dqr);
+  const bool piped = (a->flags & RELUX_CALL_PIPELINED) != 0 && p->dev->h2d_stream && p->dev->d2h_stream;
+  const bool piped_in = piped && a->q_mem == RELUX_MEM_HOST;
+  int slot_q = -1, slot_qr = -1;
+  if (piped_in) {
+    if ((rc = pipe_stage_in(p, p->pipe_in_a, a->q, q_elems * dtype_size(a->q_dtype), &dq, &slot_q))) return rc;
+    if (kind == RELUX_POOL_MLA && (rc = pipe_stage_in(p, p->pipe_in_b, a->q_rope, qr_elems * dtype_size(a->q_dtype), &dqr, &slot_qr))) return rc;
+  } else {
+    rc = stage_in(p, p->in_a, a->q, q_elems * dtype_size(a->q_dtype), a->q_mem, &dq);
     if (rc) return rc;
+    if (kind == RELUX_POOL_MLA) {
+      rc = stage_in(p, p->in_b, a->q_rope, qr_elems * dtype_size(a->q_dtype), a->q_mem, &dqr);
+      if (rc) return rc;
+    }
   }
   // canonical kernel input: token-major; f32 for REFERENCE, caller's dtype for FAST
   const int want_dtype = (a->mode != RELUX_ATTN_FAST) ? RELUX_DTYPE_F32 : a->q_dtype;
@@ -366,11 +434,24 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
   const bool direct = a->out_mem == RELUX_MEM_DEVICE && a->out_dtype == RELUX_DTYPE_F32 &&
                       (a->out_layout == RELUX_LAYOUT_TOKEN_MAJOR || S == 1);
   float* kout;
+  const bool piped_out = piped && a->out_mem == RELUX_MEM_HOST;
+  int slot_out = -1;
+  char* out_block = nullptr;   // [kernel output f32 | converted output]
   if (direct) kout = (float*)a->out;
-  else {
+  else if (piped_out) {
+    PipeSlots& po = p->pipe_out;
+    slot_out = (int)(po.next++ % PipeSlots::kSlots);
+    if ((rc = pipe_events(po, slot_out))) return rc;
+    if ((rc = pipe_grow(p, po.buf[slot_out], out_elems * 4 + out_elems * dtype_size(a->out_dtype)))) return rc;
+    // the copy that last read this slot (two pipelined calls ago) must have finished before the kernels overwrite it
+    if (po.used[slot_out]) RELUX_CUDA_TRY(cudaStreamWaitEvent(p->dev->stream, po.freed[slot_out], 0));
+    out_block = (char*)po.buf[slot_out].p;
+    kout = (float*)out_block;
+  } else {
     rc = grow(p->dev, p->out_buf, out_elems * 4 + out_elems * dtype_size(a->out_dtype));
     if (rc) return rc;
-    kout = (float*)p->out_buf.p;
+    out_block = (char*)p->out_buf.p;
+    kout = (float*)out_block;
   }
   relux_attn_args aa = *a;
   aa.q_dtype = want_dtype;
@@ -382,8 +463,9 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
     rc = (kind == RELUX_POOL_MLA) ? launch_mla_decode_fast(p, sb, aa, dq, dqr, kout) : launch_gqa_decode_fast(p, sb, aa, dq, kout);
   }
   if (rc) return rc;
+  if ((rc = pipe_release(p, p->pipe_in_a, slot_q)) || (rc = pipe_release(p, p->pipe_in_b, slot_qr))) return rc;
   if (!direct) {
-    void* conv = (char*)p->out_buf.p + out_elems * 4;
+    void* conv = out_block + out_elems * 4;
     const bool need_conv = a->out_dtype != RELUX_DTYPE_F32 || (a->out_layout == RELUX_LAYOUT_HEAD_MAJOR && S > 1);
     const void* src = kout;
     if (need_conv) {
@@ -392,7 +474,16 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
       if (rc) return rc;
       src = dst;
     }
-    if (a->out_mem == RELUX_MEM_HOST) {
+    if (piped_out) {
+      PipeSlots& po = p->pipe_out;
+      Device* dev = p->dev;
+      RELUX_CUDA_TRY(cudaEventRecord(po.ready[slot_out], dev->stream));
+      RELUX_CUDA_TRY(cudaStreamWaitEvent(dev->d2h_stream, po.ready[slot_out], 0));
+      RELUX_CUDA_TRY(cudaMemcpyAsync(a->out, src, out_elems * dtype_size(a->out_dtype), cudaMemcpyDeviceToHost, dev->d2h_stream));
+      RELUX_CUDA_TRY(cudaEventRecord(po.freed[slot_out], dev->d2h_stream));
+      po.used[slot_out] = true;
+      dev->copies_in_flight = true;
+    } else if (a->out_mem == RELUX_MEM_HOST) {
       RELUX_CUDA_TRY(cudaMemcpyAsync(a->out, src, out_elems * dtype_size(a->out_dtype), cudaMemcpyDeviceToHost, p->dev->stream));
       RELUX_CUDA_TRY(cudaStreamSynchronize(p->dev->stream));
     }
@@ -478,6 +569,12 @@ API int32_t relux_cuda_device_open(int32_t device_index, relux_device_t* out) {
     (void)cudaGetLastError();   // the side stream is an optimisation: without it the kernels stay on the main stream
     d->side_stream = nullptr;
   }
+  if (cudaStreamCreateWithFlags(&d->h2d_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&d->d2h_stream, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&d->ev_copy_join, cudaEventDisableTiming) != cudaSuccess) {
+    (void)cudaGetLastError();   // without copy streams pipelined calls behave like ordinary ones
+    d->h2d_stream = d->d2h_stream = nullptr;
+  }
   *out = d;
   return RELUX_OK;
 }
@@ -493,6 +590,9 @@ API int32_t relux_cuda_device_close(relux_device_t h) {
     if (dev->side_stream) { cudaStreamSynchronize(dev->side_stream); cudaStreamDestroy(dev->side_stream); }
     if (dev->ev_fork) cudaEventDestroy(dev->ev_fork);
     if (dev->ev_join) cudaEventDestroy(dev->ev_join);
+    for (cudaStream_t st : {dev->h2d_stream, dev->d2h_stream})
+      if (st) { cudaStreamSynchronize(st); cudaStreamDestroy(st); }
+    if (dev->ev_copy_join) cudaEventDestroy(dev->ev_copy_join);
     cudaStreamDestroy(dev->stream);
     dev->magic = 0;
   }
@@ -503,6 +603,12 @@ API int32_t relux_cuda_device_close(relux_device_t h) {
 API int32_t relux_cuda_sync(relux_device_t h) {
   GET_DEV(h);
   RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  if (dev->copies_in_flight) {
+    if (dev->h2d_stream) RELUX_CUDA_TRY(cudaStreamSynchronize(dev->h2d_stream));
+    if (dev->d2h_stream) RELUX_CUDA_TRY(cudaStreamSynchronize(dev->d2h_stream));
+    RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+    dev->copies_in_flight = false;
+  }
   return RELUX_OK;
 }
 
@@ -592,6 +698,8 @@ API int32_t relux_cuda_event_create(relux_device_t h, relux_event_t* ev) {
 API int32_t relux_cuda_event_record(relux_device_t h, relux_event_t ev) {
   GET_DEV(h);
   if (!ev) return RELUX_ERR_INVALID_ARG;
+  int32_t rcj = join_copy_streams(dev);   // the event also covers the copies of pipelined calls
+  if (rcj) return rcj;
   RELUX_CUDA_TRY(cudaEventRecord((cudaEvent_t)ev, dev->stream));
   return RELUX_OK;
 }
@@ -940,6 +1048,18 @@ API int32_t relux_pool_read_rows(relux_pool_t h, const relux_read_rows_args* a) 
   if (a->dst_a) RELUX_CUDA_TRY(cudaMemcpyAsync(a->dst_a, da, ea * 2, cudaMemcpyDeviceToHost, dev->stream));
   if (a->dst_b) RELUX_CUDA_TRY(cudaMemcpyAsync(a->dst_b, db, eb * 2, cudaMemcpyDeviceToHost, dev->stream));
   RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  return RELUX_OK;
+}
+
+API int32_t relux_pool_wait_output(relux_pool_t h, int32_t calls_back) {
+  GET_POOL(h);
+  PipeSlots& po = p->pipe_out;
+  if (calls_back < 0 || calls_back >= PipeSlots::kSlots || (uint64_t)calls_back >= po.next) {
+    set_error("wait_output: calls_back=%d, but %llu pipelined outputs exist (two are kept)", calls_back, (unsigned long long)po.next);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  const int slot = (int)((po.next - 1 - (uint64_t)calls_back) % PipeSlots::kSlots);
+  if (po.used[slot]) RELUX_CUDA_TRY(cudaEventSynchronize(po.freed[slot]));
   return RELUX_OK;
 }
 

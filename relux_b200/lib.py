@@ -21,6 +21,7 @@ LAYOUT_TOKEN_MAJOR, LAYOUT_HEAD_MAJOR = 0, 1
 POOL_MLA, POOL_GQA = 0, 1
 ATTN_FAST, ATTN_REFERENCE, ATTN_REFERENCE_FAITHFUL = 0, 1, 2
 POOL_FLAG_REFERENCE_COMPAT = 1
+CALL_PIPELINED = 1
 (TUNE_MLA_GENERIC, TUNE_MLA_WORKERS, TUNE_CHUNK_PAGES, TUNE_GEMM_GENERIC, TUNE_GEMM_SPLIT, TUNE_GQA_PROMPT_PARTIAL_MB, TUNE_SEL_CLUSTER,
  TUNE_SEL_LOOKAHEAD, TUNE_SEL_BATCHED) = range(9)
 
@@ -35,7 +36,7 @@ EXPORTS = [
     "relux_pool_read_rows", "relux_mla_append", "relux_gqa_append", "relux_mla_decode", "relux_gqa_decode", "relux_gqa_verify",
     "relux_mla_verify", "relux_pool_last_kernel_ms", "relux_pool_kernel_ms_mean", "relux_mla_forward_cached", "relux_gqa_forward_cached", "relux_stream_partition", "relux_seq_save_file", "relux_seq_load_file", "relux_pool_projection_ms_mean", "relux_gqa_decode_noalloc",
     "relux_spec_accept", "relux_sampler_sample", "relux_pool_tune", "relux_pool_kernel_ms_list", "relux_matmul_f32_bf16",
-    "relux_mla_import_weights", "relux_pool_selftest_wait",
+    "relux_mla_import_weights", "relux_pool_selftest_wait", "relux_pool_wait_output",
 ]
 
 
@@ -64,7 +65,7 @@ class MatmulArgs(C.Structure):
 class AppendArgs(C.Structure):
     _fields_ = [("layer", C.c_int32), ("n_seqs", C.c_int32), ("seq_ids", C.c_void_p), ("n_new", C.c_void_p),
                 ("a", C.c_void_p), ("b", C.c_void_p), ("dtype", C.c_int32), ("mem", C.c_int32), ("layout", C.c_int32),
-                ("advance", C.c_int32), ("reserved", C.c_int32 * 4)]
+                ("advance", C.c_int32), ("flags", C.c_int32), ("reserved", C.c_int32 * 3)]
 
 
 class AttnArgs(C.Structure):
@@ -73,7 +74,7 @@ class AttnArgs(C.Structure):
                 ("scale", C.c_float), ("q", C.c_void_p), ("q_rope", C.c_void_p), ("q_dtype", C.c_int32), ("q_mem", C.c_int32),
                 ("q_layout", C.c_int32), ("w_uk", C.c_void_p), ("w_uv", C.c_void_p), ("out", C.c_void_p),
                 ("out_dtype", C.c_int32), ("out_mem", C.c_int32), ("out_layout", C.c_int32), ("mode", C.c_int32),
-                ("reserved", C.c_int32 * 5)]
+                ("flags", C.c_int32), ("reserved", C.c_int32 * 4)]
 
 
 class MlaLayerWeights(C.Structure):
@@ -179,6 +180,7 @@ def load():
         L.relux_pool_status.argtypes = [C.c_void_p, C.POINTER(C.c_int32)]
         L.relux_pool_read_rows.argtypes = [C.c_void_p, C.POINTER(ReadRowsArgs)]
         L.relux_pool_tune.argtypes = [C.c_void_p, C.c_int32, C.c_int32]
+        L.relux_pool_wait_output.argtypes = [C.c_void_p, C.c_int32]
         L.relux_pool_kernel_ms_list.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.POINTER(C.c_int32)]
         L.relux_matmul_f32_bf16.argtypes = [C.c_void_p, C.POINTER(MatmulArgs)]
         L.relux_mla_import_weights.argtypes = [C.c_void_p, C.POINTER(MlaImportArgs)]

@@ -369,3 +369,60 @@ def test_mla_fewer_than_128_heads_on_the_tensor_path(dev, oracle, H):
     check_attention(out, ref, "mla H=%d" % H, max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
     out, ref = _mla_v2_case(dev, oracle, 61 + H, [2, 200], 2, H=H)
     check_attention(out, ref, "mla H=%d S=2" % H, max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+
+
+def test_pipelined_calls_give_the_same_bits_as_ordinary_ones(dev, oracle):
+    """RELUX_CALL_PIPELINED moves the host copies to streams of their own and returns at once; the numbers must not
+    change.  Six append + decode steps with pinned bf16 queries and outputs, two output buffers in turn, each output
+    read after relux_pool_wait_output, against the same steps made with ordinary calls on a second pool."""
+    from relux_b200 import lib as L
+    H, Dh, dC, dHR = 128, 128, 512, 64
+    ctx = [130, 700, 64, 1]
+    B = len(ctx)
+    scale = float(1.0 / np.sqrt(Dh + dHR))
+    pools = [build_mla(dev, oracle, np.random.default_rng(77), ctx, dC, dHR, extra_pages=2)[0] for _ in range(2)]
+    rng = np.random.default_rng(78)
+    wuk = dev.upload(oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02))
+    wuv = dev.upload(oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02))
+    steps = 6
+    qs = [oracle.bf16_from_f32(rng.standard_normal((B, 1, H, Dh)).astype(np.float32)) for _ in range(steps)]
+    qrs = [oracle.bf16_from_f32(rng.standard_normal((B, 1, H, dHR)).astype(np.float32)) for _ in range(steps)]
+    rows_c = [rng.standard_normal((B, dC)).astype(np.float32) for _ in range(steps)]
+    rows_r = [rng.standard_normal((B, dHR)).astype(np.float32) for _ in range(steps)]
+    want = []
+    for i in range(steps):
+        pools[0].append(0, rows_c[i], rows_r[i], B)
+        o = np.empty((B, 1, H, Dh), np.uint16)
+        pools[0].decode(0, B, qs[i], o, H, Dh, scale, q_rope=qrs[i], w_uk=wuk, w_uv=wuv)
+        want.append(o)
+    # pinned copies of every step's inputs (a pipelined call may still be reading them when the next one is made)
+    pin = lambda a: dev.pinned(a.shape, a.dtype)
+    p_q, p_qr, p_c, p_r = [], [], [], []
+    for i in range(steps):
+        for lst, a in ((p_q, qs[i]), (p_qr, qrs[i]), (p_c, rows_c[i]), (p_r, rows_r[i])):
+            h = pin(a)
+            h.array[...] = a
+            lst.append(h)
+    outs = [dev.pinned((B, 1, H, Dh), np.uint16) for _ in range(2)]
+    got = []
+    for i in range(steps):
+        pools[1].append(0, p_c[i].array, p_r[i].array, B, pipelined=True)
+        pools[1].decode(0, B, p_q[i].array, outs[i % 2].array, H, Dh, scale, q_rope=p_qr[i].array, w_uk=wuk, w_uv=wuv, pipelined=True)
+        if i >= 1:
+            pools[1].wait_output(1)
+            got.append(outs[(i - 1) % 2].array.copy())
+    pools[1].wait_output(0)
+    got.append(outs[(steps - 1) % 2].array.copy())
+    for i in range(steps):
+        assert np.array_equal(got[i], want[i]), "step %d differs" % i
+    # the cache rows went in the same way
+    a0, b0 = pools[0].read_rows(0, 1, 700, steps)
+    a1, b1 = pools[1].read_rows(0, 1, 700, steps)
+    assert np.array_equal(a0, a1) and np.array_equal(b0, b1)
+    dev.sync()
+    assert pools[0].status() == 0 and pools[1].status() == 0
+    for h in p_q + p_qr + p_c + p_r + outs:
+        h.close()
+    for p in pools:
+        p.destroy()
+    wuk.free(); wuv.free()
