@@ -209,7 +209,9 @@ int32_t relux_pool_read_rows(relux_pool_t pool, const relux_read_rows_args* args
 #define RELUX_TUNE_SEL_CLUSTER 6        /* RELUX_SEL_CLUSTER: cluster size of the selection kernel, 1/2/4/8 (0 = per call) */
 #define RELUX_TUNE_SEL_LOOKAHEAD 7      /* RELUX_SEL_LOOKAHEAD: 0/1 (-1 = per call)                                         */
 #define RELUX_TUNE_SEL_BATCHED 8        /* RELUX_SEL_BATCHED: 0/1 (-1 = per call)                                           */
-#define RELUX_TUNE_COUNT 9
+#define RELUX_TUNE_GQA_PROMPT_SLICES 9  /* RELUX_GQA_PROMPT_SLICES: 1 = GQA prompts as grid slices of the decode kernel instead
+                                           of the tcgen05 prefill kernel                                                  */
+#define RELUX_TUNE_COUNT 10
 /* Changes one tuning knob of a pool (see RELUX_TUNE_*).  A pool takes its defaults once, when it is created, from the
  * environment variables named beside the knobs; no call reads the environment afterwards.  value < 0 restores the
  * built-in default.  Tuning aid: no counterpart in the reference. */

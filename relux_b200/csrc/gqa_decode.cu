@@ -444,6 +444,14 @@ static int32_t launch_gqa_prompt(Pool* p, const SeqBatch& sb, const relux_attn_a
   return RELUX_OK;
 }
 
+bool gqa_prefill_eligible(const Pool* p, const relux_attn_args& a);
+int32_t launch_gqa_prefill_sm100(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const uint16_t* d_q, float* d_out);
+
+bool gqa_prompt_wants_bf16(const Pool* p, const relux_attn_args& a) {
+  const int g = a.num_heads / std::max(1, p->prm.gqa_num_kv_heads);
+  return g >= 1 && a.q_tokens > std::max(1, 32 / g) && !p->tune.get(RELUX_TUNE_GQA_PROMPT_SLICES) && gqa_prefill_eligible(p, a);
+}
+
 int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, void* d_out) {
   const relux_pool_params& prm = p->prm;
   const int g = a.num_heads / prm.gqa_num_kv_heads;
@@ -457,6 +465,9 @@ int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   // (a prompt) are cut into groups of tokens that run as the z slices of one grid
   const int per_group = std::max(1, 32 / g);
   if (a.q_tokens <= per_group) return launch_gqa_group(p, sb, a, d_q, d_out, 0, a.q_tokens);
+  // a prompt: 128 query rows per CTA on the tcgen05 prefill kernel; the grid slices of the decode kernel serve the
+  // group sizes that do not tile 128 rows, and stay selectable as a tuning knob
+  if (a.q_dtype == RELUX_DTYPE_BF16 && gqa_prompt_wants_bf16(p, a)) return launch_gqa_prefill_sm100(p, sb, a, (const uint16_t*)d_q, (float*)d_out);
   return launch_gqa_prompt(p, sb, a, d_q, d_out, per_group);
 }
 

@@ -56,8 +56,8 @@ struct GrowBuf {
 
 // Tuning knobs of a pool.  Defaults come from the environment ONCE, when the pool is created (RELUX_MLA_GENERIC,
 // RELUX_MLA_WORKERS, RELUX_CHUNK_PAGES, RELUX_GEMM_GENERIC, RELUX_GEMM_SPLIT, RELUX_GQA_PROMPT_PARTIAL_MB,
-// RELUX_SEL_CLUSTER, RELUX_SEL_LOOKAHEAD, RELUX_SEL_BATCHED); relux_pool_tune changes them afterwards.  No launch path
-// reads the environment.
+// RELUX_SEL_CLUSTER, RELUX_SEL_LOOKAHEAD, RELUX_SEL_BATCHED, RELUX_GQA_PROMPT_SLICES); relux_pool_tune changes them
+// afterwards.  No launch path reads the environment.
 struct Tuning {
   int32_t v[RELUX_TUNE_COUNT];
   int32_t get(int knob) const { return v[knob]; }
@@ -186,6 +186,8 @@ int32_t launch_attn_reference_gqa(Pool* p, const SeqBatch& sb, const relux_attn_
 int32_t launch_attn_reference_mla(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const float* d_q, const float* d_qr,
                                   float* d_out);
 int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, void* d_out);
+// True when this call is a multi-token call that the tcgen05 prefill kernel serves (it takes bf16 queries).
+bool gqa_prompt_wants_bf16(const Pool* p, const relux_attn_args& a);
 int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, const void* d_qr,
                                void* d_out);
 

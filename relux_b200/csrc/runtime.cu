@@ -412,7 +412,9 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
     }
   }
   // canonical kernel input: token-major; f32 for REFERENCE, caller's dtype for FAST
-  const int want_dtype = (a->mode != RELUX_ATTN_FAST) ? RELUX_DTYPE_F32 : a->q_dtype;
+  int want_dtype = (a->mode != RELUX_ATTN_FAST) ? RELUX_DTYPE_F32 : a->q_dtype;
+  // a GQA prompt goes to the tcgen05 prefill kernel, whose Q tile is a TMA load of bf16 rows
+  if (kind == RELUX_POOL_GQA && a->mode == RELUX_ATTN_FAST && gqa_prompt_wants_bf16(p, *a)) want_dtype = RELUX_DTYPE_BF16;
   const bool relayout_q = (a->q_layout == RELUX_LAYOUT_HEAD_MAJOR && S > 1) || want_dtype != a->q_dtype;
   if (relayout_q) {
     size_t need = (q_elems + qr_elems) * dtype_size(want_dtype);
@@ -492,10 +494,10 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
 }
 
 // Built-in defaults of the tuning knobs, then the environment (read here, once per pool, never on a launch path).
-static const int32_t kTuneDefault[RELUX_TUNE_COUNT] = {0, 0, 0, 0, 0, 256, 0, -1, -1};
+static const int32_t kTuneDefault[RELUX_TUNE_COUNT] = {0, 0, 0, 0, 0, 256, 0, -1, -1, 0};
 static const char* const kTuneEnv[RELUX_TUNE_COUNT] = {"RELUX_MLA_GENERIC", "RELUX_MLA_WORKERS", "RELUX_CHUNK_PAGES", "RELUX_GEMM_GENERIC",
                                                        "RELUX_GEMM_SPLIT", "RELUX_GQA_PROMPT_PARTIAL_MB", "RELUX_SEL_CLUSTER",
-                                                       "RELUX_SEL_LOOKAHEAD", "RELUX_SEL_BATCHED"};
+                                                       "RELUX_SEL_LOOKAHEAD", "RELUX_SEL_BATCHED", "RELUX_GQA_PROMPT_SLICES"};
 void tuning_defaults(Tuning* t) {
   for (int i = 0; i < RELUX_TUNE_COUNT; i++) {
     t->v[i] = kTuneDefault[i];

@@ -350,8 +350,9 @@ def test_gqa_fast_long_prompt_as_grid_slices(dev, oracle, budget_mb):
     q = rng.standard_normal((B, S, H, D)).astype(np.float32)
     out = np.empty_like(q)
     scale = float(1.0 / np.sqrt(D))
+    from relux_b200 import lib as L
+    pool.tune(L.TUNE_GQA_PROMPT_SLICES, 1)   # this test is about the grid-slice path (the default is the prefill kernel)
     if budget_mb is not None:
-        from relux_b200 import lib as L
         pool.tune(L.TUNE_GQA_PROMPT_PARTIAL_MB, budget_mb)
     pool.decode(0, B, q, out, H, D, scale, q_tokens=S, causal=True)
     with oracle.exact_exp():
@@ -426,3 +427,53 @@ def test_pipelined_calls_give_the_same_bits_as_ordinary_ones(dev, oracle):
     for p in pools:
         p.destroy()
     wuk.free(); wuv.free()
+
+
+@pytest.mark.parametrize("S,cached", [(33, 0), (63, 0), (64, 0), (65, 0), (203, 0), (203, 517), (129, 64), (1024, 0)])
+def test_gqa_prefill_kernel_prompts(dev, oracle, S, cached):
+    """The tcgen05 prefill kernel (128 query rows per CTA) on prompts of odd and page-aligned lengths, on an empty cache
+    and after `cached` rows, causal inside the prompt; three sequences whose earlier rows differ in number."""
+    rng = np.random.default_rng(300 + S + cached)
+    H, Hkv, D = 32, 8, 128
+    ctx = [cached + S, cached + S + 70, S] if cached else [S, S, S]
+    if S == 1024:
+        ctx = [S]
+    pool, Kl, Vl = build_gqa(dev, oracle, rng, ctx, Hkv, D)
+    B = len(ctx)
+    q = rng.standard_normal((B, S, H, D)).astype(np.float32)
+    out = np.full_like(q, np.nan)
+    scale = float(1.0 / np.sqrt(D))
+    n0 = dev.launch_count()
+    pool.decode(0, B, q, out, H, D, scale, q_tokens=S, causal=True)
+    assert dev.launch_count() - n0 <= 2   # one conversion of q to bf16 + one attention launch: no split-KV, no merge
+    with oracle.exact_exp():
+        ref = oracle.gqa_attend(Kl, Vl, ctx, q, scale, causal=True)
+    check_attention(out, ref, "gqa prefill S=%d cached=%d" % (S, cached), max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+    assert pool.status() == 0
+    pool.destroy()
+
+
+@pytest.mark.parametrize("H,Hkv,causal", [(8, 8, True), (16, 8, True), (64, 8, True), (32, 2, True), (32, 8, False)])
+def test_gqa_prefill_kernel_group_sizes(dev, oracle, H, Hkv, causal):
+    """Group sizes 1, 2, 8 and 16 query heads per kv head (128, 64, 16 and 8 tokens per CTA), and the unmasked variant
+    (every query row sees the whole cache), on ragged caches, against the restatement."""
+    rng = np.random.default_rng(400 + H + Hkv)
+    D, S = 128, 77
+    ctx = [S, 150, 1000]
+    pool, Kl, Vl = build_gqa(dev, oracle, rng, ctx, Hkv, D)
+    B = len(ctx)
+    q = oracle.bf16_from_f32(rng.standard_normal((B, S, H, D)).astype(np.float32))
+    out = np.empty((B, S, H, D), np.float32)
+    scale = float(1.0 / np.sqrt(D))
+    pool.decode(0, B, q, out, H, D, scale, q_tokens=S, causal=causal)
+    with oracle.exact_exp():
+        ref = oracle.gqa_attend(Kl, Vl, ctx, oracle.f32_from_bf16(q), scale, causal=causal)
+    check_attention(out, ref, "gqa prefill H=%d Hkv=%d causal=%s" % (H, Hkv, causal), max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+    # the grid-slice path gives the same numbers within float32 re-association and the bf16 rounding of P
+    from relux_b200 import lib as L
+    pool.tune(L.TUNE_GQA_PROMPT_SLICES, 1)
+    out2 = np.empty_like(out)
+    pool.decode(0, B, q, out2, H, D, scale, q_tokens=S, causal=causal)
+    assert np.abs(out2 - out).max() <= 5e-3
+    assert pool.status() == 0
+    pool.destroy()
