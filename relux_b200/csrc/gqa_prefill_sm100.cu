@@ -98,8 +98,8 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
 
 __global__ void __launch_bounds__(192, 1)
     gqa_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid_constant__ CUtensorMap tmap_q, const PrefillParams prm) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // the swizzled layouts need a 1024-byte aligned base
   Bars* bars = reinterpret_cast<Bars*>(smem + kSmemBar);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qb = prm.n_qblocks - 1 - (int)blockIdx.x;   // the blocks that see the most keys start first
@@ -134,13 +134,18 @@ __global__ void __launch_bounds__(192, 1)
 
   if (warp == 4) {
     // =============================== producer ===============================
-    if (lane == 0 && ntiles > 0) {
-      tma_prefetch_desc(&tmap_kv);
-      tma_prefetch_desc(&tmap_q);
-      mbar_expect_tx(&bars->q_full, 2 * kHalf);
-      // box = [64 dims][g heads][bq tokens]: rows land as token_in_block * g + head_in_group
-      tma_load_3d(smem + kSmemQ, &tmap_q, 0, hk * prm.g, bi * prm.S + t0, &bars->q_full);
-      tma_load_3d(smem + kSmemQ + kHalf, &tmap_q, 64, hk * prm.g, bi * prm.S + t0, &bars->q_full);
+    // The whole warp stays converged and one elected lane issues (operands stay in uniform registers).
+    const bool el = elect_one();
+    if (ntiles > 0) {
+      if (el) {
+        tma_prefetch_desc(&tmap_kv);
+        tma_prefetch_desc(&tmap_q);
+        mbar_expect_tx(&bars->q_full, 2 * kHalf);
+        // box = [64 dims][g heads][bq tokens]: rows land as token_in_block * g + head_in_group
+        tma_load_3d(smem + kSmemQ, &tmap_q, 0, hk * prm.g, bi * prm.S + t0, &bars->q_full);
+        tma_load_3d(smem + kSmemQ + kHalf, &tmap_q, 64, hk * prm.g, bi * prm.S + t0, &bars->q_full);
+      }
+      __syncwarp();
       for (int j = 0; j < ntiles; j++) {
         int32_t y[2];
 #pragma unroll
@@ -158,19 +163,23 @@ __global__ void __launch_bounds__(192, 1)
         for (int kv = 0; kv < 2; kv++) {
           const int st = (j & 1) * 2 + kv;
           if (u > 0) wait_bar(&bars->kv_empty[st], (u - 1) & 1, bars, prm.status);
-          uint8_t* dst = smem + kSmemRing + st * kStageBytes;
-          const int32_t row0 = kv ? prm.vrow0 : prm.krow0;
-          mbar_expect_tx(&bars->kv_full[st], kStageBytes);
+          if (el) {
+            uint8_t* dst = smem + kSmemRing + st * kStageBytes;
+            const int32_t row0 = kv ? prm.vrow0 : prm.krow0;
+            mbar_expect_tx(&bars->kv_full[st], kStageBytes);
 #pragma unroll
-          for (int cb = 0; cb < 2; cb++)
+            for (int cb = 0; cb < 2; cb++)
 #pragma unroll
-            for (int h2 = 0; h2 < 2; h2++) tma_load_2d(dst + cb * kHalf + h2 * kBlk, &tmap_kv, cb * 64, row0 + y[h2], &bars->kv_full[st]);
+              for (int h2 = 0; h2 < 2; h2++) tma_load_2d(dst + cb * kHalf + h2 * kBlk, &tmap_kv, cb * 64, row0 + y[h2], &bars->kv_full[st]);
+          }
+          __syncwarp();
         }
       }
     }
   } else if (warp == 5) {
-    // =============================== MMA issuer ===============================
-    if (lane == 0 && ntiles > 0) {
+    // =============================== MMA issuer (converged warp + elected lane) ===============================
+    const bool el = elect_one();
+    if (ntiles > 0) {
       const uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
       const uint32_t idesc_pv = make_idesc_bf16(128, 128, false, true);
       const uint64_t dQ = make_desc_kmajor_sw128(smem_u32(smem + kSmemQ));
@@ -179,30 +188,36 @@ __global__ void __launch_bounds__(192, 1)
         const int st = (j & 1) * 2;
         wait_bar(&bars->kv_full[st], (j >> 1) & 1, bars, prm.status);
         tc_fence_after();
-        const uint64_t dK = make_desc_kmajor_sw128(smem_u32(smem + kSmemRing + st * kStageBytes));
-        const uint32_t d = tmem + kTmemS + (j & 1) * 128;
+        if (el) {
+          const uint64_t dK = make_desc_kmajor_sw128(smem_u32(smem + kSmemRing + st * kStageBytes));
+          const uint32_t d = tmem + kTmemS + (j & 1) * 128;
 #pragma unroll
-        for (int ks = 0; ks < 8; ks++) {
-          const uint32_t off = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
-          umma_ss<1>(d, dQ + off, dK + off, idesc_qk, ks != 0);
+          for (int ks = 0; ks < 8; ks++) {
+            const uint32_t off = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
+            umma_ss<1>(d, dQ + off, dK + off, idesc_qk, ks != 0);
+          }
+          umma_commit<1>(&bars->kv_empty[st]);
+          umma_commit<1>(&bars->s_full[j & 1]);
         }
-        umma_commit<1>(&bars->kv_empty[st]);
-        umma_commit<1>(&bars->s_full[j & 1]);
+        __syncwarp();
       };
       auto issue_pv = [&](int j) {
         const int st = (j & 1) * 2 + 1;
         wait_bar(&bars->p_full, j & 1, bars, prm.status);
         wait_bar(&bars->kv_full[st], (j >> 1) & 1, bars, prm.status);
         tc_fence_after();   // P rows and a possible O rescale were done by the softmax warps
-        const uint32_t vbase = smem_u32(smem + kSmemRing + st * kStageBytes);
+        if (el) {
+          const uint64_t dV = make_desc_mnmajor_sw128(smem_u32(smem + kSmemRing + st * kStageBytes), kHalf);
+          const uint64_t dPj = dP + ((uint32_t)((j & 1) * kPBytes) >> 4);
 #pragma unroll
-        for (int ks = 0; ks < 8; ks++) {
-          const uint32_t aoff = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
-          umma_ss<1>(tmem + kTmemO, dP + (uint32_t)(((j & 1) * kPBytes) >> 4) + aoff, make_desc_mnmajor_sw128(vbase + ks * 2048, kHalf), idesc_pv,
-                     j > 0 || ks != 0);
+          for (int ks = 0; ks < 8; ks++) {
+            const uint32_t aoff = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
+            umma_ss<1>(tmem + kTmemO, dPj + aoff, dV + ((uint32_t)(ks * 2048) >> 4), idesc_pv, j > 0 || ks != 0);
+          }
+          umma_commit<1>(&bars->kv_empty[st]);
+          umma_commit<1>(&bars->pv_done);
         }
-        umma_commit<1>(&bars->kv_empty[st]);
-        umma_commit<1>(&bars->pv_done);
+        __syncwarp();
       };
       wait_bar(&bars->q_full, 0, bars, prm.status);
       issue_qk(0);
@@ -222,6 +237,7 @@ __global__ void __launch_bounds__(192, 1)
     float m_used = -INFINITY, l_run = 0.f;
     for (int j = 0; j < ntiles; j++) {
       wait_bar(&bars->s_full[j & 1], (j >> 1) & 1, bars, prm.status);
+      __syncwarp();   // the TMEM loads below are warp-collective
       tc_fence_after();
       uint32_t sv[128];
 #pragma unroll
@@ -268,7 +284,11 @@ __global__ void __launch_bounds__(192, 1)
       l_run = l_run * alpha + psum;
       // O may be rescaled only after PV(j-1) has completed
       if (j > 0) wait_bar(&bars->pv_done, (j - 1) & 1, bars, prm.status);
-      if (rescale && j > 0) {
+      __syncwarp();
+      // The TMEM loads and stores are warp-collective: the decision is taken for the whole warp, and the rows that keep
+      // their maximum multiply by one.
+      if (j > 0 && __any_sync(0xffffffffu, rescale)) {
+        const float a_row = rescale ? alpha : 1.f;
         tc_fence_after();
 #pragma unroll 1
         for (int c = 0; c < 128; c += 32) {
@@ -276,7 +296,7 @@ __global__ void __launch_bounds__(192, 1)
           tmem_ld_32x32b_x32(tmem + lane_addr + kTmemO + c, ov);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+          for (int i = 0; i < 32; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * a_row);
           tmem_st_32x32b_x32(tmem + lane_addr + kTmemO + c, ov);
         }
         tmem_st_wait();
@@ -289,35 +309,29 @@ __global__ void __launch_bounds__(192, 1)
     // ---- epilogue: O / l -> out ----
     if (ntiles > 0) {
       wait_bar(&bars->pv_done, (ntiles - 1) & 1, bars, prm.status);
+      __syncwarp();
       tc_fence_after();
     }
-    const bool ok = !bars->abort_flag && ntiles > 0 && l_run > 0.f;
-    const float inv = ok ? 1.f / l_run : 0.f;
-    if (real) {
-      float* orow = prm.out + (((size_t)bi * prm.S + t0 + tq) * prm.H + (size_t)hk * prm.g + hq) * kD;
+    // warp-uniform: the TMEM loads below are warp-collective
+    const bool ok = ntiles > 0 && !__any_sync(0xffffffffu, bars->abort_flag != 0);
+    const float inv = (ok && l_run > 0.f) ? 1.f / l_run : 0.f;
+    float* orow = prm.out + (((size_t)bi * prm.S + t0 + (real ? tq : 0)) * prm.H + (size_t)hk * prm.g + hq) * kD;
 #pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t ov[32];
-        if (ok) {
-          tmem_ld_32x32b_x32(tmem + lane_addr + kTmemO + c, ov);
-          tmem_ld_wait();
-        } else {
+    for (int c = 0; c < 128; c += 32) {
+      uint32_t ov[32];
+      if (ok) {
+        tmem_ld_32x32b_x32(tmem + lane_addr + kTmemO + c, ov);
+        tmem_ld_wait();
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; i++) ov[i] = 0u;
-        }
+        for (int i = 0; i < 32; i++) ov[i] = 0u;
+      }
+      if (real) {   // rows past the prompt's last token are padding: computed, never written
         float4* dst = reinterpret_cast<float4*>(orow + c);
 #pragma unroll
         for (int i = 0; i < 8; i++)
           dst[i] = make_float4(__uint_as_float(ov[4 * i]) * inv, __uint_as_float(ov[4 * i + 1]) * inv, __uint_as_float(ov[4 * i + 2]) * inv,
                                __uint_as_float(ov[4 * i + 3]) * inv);
-      }
-    } else if (ok) {
-      // the warp-collective TMEM load must be executed by every lane of the warp
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t ov[32];
-        tmem_ld_32x32b_x32(tmem + lane_addr + kTmemO + c, ov);
-        tmem_ld_wait();
       }
     }
   }
