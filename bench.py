@@ -51,6 +51,7 @@ WORKLOADS = {
     "spec_accept_b32_k4_v128k": dict(kind="accept", B=32, k=4, V=131072),
     # prompt processing through the decode kernels (a multi-token cached call on an empty cache): 8 sequences x 2048 tokens
     "gqa_prompt_b8_2k": dict(kind="prompt", pool="gqa", B=8, S=2048, H=32, Hkv=8, D=128),
+    "gqa_prompt_b2_2k": dict(kind="prompt", pool="gqa", B=2, S=2048, H=32, Hkv=8, D=128),   # small case for profiler captures
     "mla_prompt_b4_1k": dict(kind="prompt", pool="mla", B=4, S=1024, H=128, Dh=128, dC=512, dHR=64),
     "gqa_layer_verify_b128_ctx8k": dict(kind="gqa", B=128, ctx=8192, H=32, Hkv=8, D=128, S=4, layer=True),
 }
@@ -165,10 +166,31 @@ class ClockSampler(threading.Thread):
                 "reason_masks": sorted(masks), "source": "nvidia-smi -lms 50"}
 
 
+def bind_rank_to_cores(local, world):
+    """Gives every rank of a node its own slice of the host cores this process may use (affinity only; nothing of the
+    GPU is touched): eight single-threaded ranks that share one affinity mask otherwise migrate over each other while
+    they feed their copy streams.  Returns the cores chosen (for the JSON line)."""
+    if not hasattr(os, "sched_getaffinity") or world <= 1:
+        return None
+    try:
+        cores = sorted(os.sched_getaffinity(0))
+        per = max(1, len(cores) // world)
+        mine = cores[local * per:(local + 1) * per] or cores
+        os.sched_setaffinity(0, mine)
+        return [mine[0], mine[-1]]
+    except OSError:
+        return None
+
+
+HOST_CORES = None
+
+
 def dist_setup(n_gpus):
+    global HOST_CORES
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    HOST_CORES = bind_rank_to_cores(local, world)
     if world > 1:
         import torch
         import torch.distributed as dist
@@ -458,7 +480,9 @@ def run_mla(args, w, world, rank, local, dist):
                                 "frac_of_sustained": tflops / pk.get("bf16_tflops_sustained", 1400.0)}},
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": ms_e2e / K, "burst_value": (e2e * ms_e2e / ms_e2e_burst),
-                "h2d_d2h_gbs_per_rank": (h2d + d2h) / (ms_e2e / K * 1e-3) / 1e9},
+                "h2d_d2h_gbs_per_rank": (h2d + d2h) / (ms_e2e / K * 1e-3) / 1e9, "host_cores_rank0": HOST_CORES,
+                "how": "pipelined calls (copies on their own streams, two steps in flight), page-locked host buffers; q and out "
+                       "travel as bf16, the new rows as float32"},
         "gpu_launches": int(round(launches / float(len(ms_list)))), "clocks": clocks,
         "kv_read_gbs_whole_step": alg_bytes * world / (ms_res / K * 1e-3) / 1e9,
     }
@@ -627,9 +651,9 @@ _CPU_INPUTS = {}   # inputs of the CPU legs, kept between steps of the reference
 
 def run_prompt(args, w, world, rank, local, dist):
     """Prompt processing: every step empties the sequences, appends the S prompt rows and runs one causal multi-token
-    attention call over them (device-resident inputs).  There is no dedicated prefill kernel: the decode kernels take
-    the prompt in groups of query tokens, so the bound reported is the tensor pipe (2 * 2 * S^2 / 2 * H * D flop per
-    sequence for GQA, 2 * S^2 / 2 * H * (2 dC + dHR) for absorbed MLA), not HBM."""
+    attention call over them (device-resident inputs).  GQA prompts run on the tcgen05 prefill kernel (128 query rows per
+    CTA); MLA prompts go through the decode kernel, one row of workers per query token.  The bound reported is the
+    tensor pipe (2 * 2 * S^2 / 2 * H * D flop per sequence for GQA, 2 * S^2 / 2 * H * (2 dC + dHR) for absorbed MLA)."""
     import relux_b200 as rb
     from relux_b200 import lib as L
 
@@ -703,7 +727,7 @@ def run_prompt(args, w, world, rank, local, dist):
         "data": "synthetic",
         "config": workload_config(args.workload, w),
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
-                     "peak_source": "measured" if peaks else "fallback", "kernel": "mla_decode_sm100_kernel" if mla else "gqa_decode_kernel",
+                     "peak_source": "measured" if peaks else "fallback", "kernel": "mla_decode_sm100_kernel" if mla else "gqa_prefill_sm100_kernel",
                      "kernel_ms": kernel_ms, "launches_timed": counted, "algorithmic_flops_per_launch": flops},
         "e2e": None, "gpu_launches": launches, "clocks": clocks,
     }
