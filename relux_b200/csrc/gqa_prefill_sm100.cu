@@ -17,7 +17,9 @@
 //     O[128 x 128] += P V             8 MMAs M128 N128 K16, B = the V pages as they lie (MN-major by descriptor)
 // TMEM: S double-buffered (2 x 128 columns), O 128 columns.  Issue order QK(j+1), PV(j): the softmax of tile j
 // overlaps QK(j+1), the softmax of tile j+1 overlaps PV(j).
-// Warp roles: 4 softmax / epilogue warps (one TMEM lane = one query row per thread), 1 TMA producer, 1 MMA issuer.
+// Warp roles: 8 softmax / epilogue warps -- a query row (TMEM lane) is shared by two threads, 64 keys (and 64 output
+// dims) each, because four warps alone, one per scheduler, leave the exponentials and their dependent chains exposed
+// (measured: tensor pipe 26 % busy with four, the softmax being the period of the pipeline) --, 1 TMA producer, 1 MMA issuer.
 // No split-KV: a prompt has (tokens x kv heads x sequences) / (128 / g) CTAs, which fills the device; the output is
 // normalised in the epilogue and written once.  Blocks are numbered so that the longest (last) blocks start first.
 // Every wait is bounded (status RELUX_ERR_TIMEOUT, shared abort flag, all warps still reach the end and free TMEM).
@@ -41,8 +43,9 @@ constexpr int kPBytes = 2 * kHalf;
 constexpr int kStages = 4;                 // K(j), V(j), K(j+1), V(j+1)
 constexpr int kStageBytes = 2 * kHalf;     // 32 KB: [dims 0-63: page 0 | page 1][dims 64-127: page 0 | page 1]
 constexpr int kSmemRing = kSmemP + 2 * kPBytes;
-constexpr int kSmemBar = kSmemRing + kStages * kStageBytes;
-constexpr int kSmemTotal = kSmemBar + 256 + 1024;   // + slack for the 1024-byte alignment of the base
+constexpr int kSmemBar = kSmemRing + kStages * kStageBytes;   // 229376
+constexpr int kSmemTotal = kSmemBar + 3072;                   // 232448: all a CTA may use
+constexpr int kSoftmaxThreads = 256, kThreads = kSoftmaxThreads + 64;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemS = 0, kTmemO = 256;
 constexpr float kRescaleThreshold = 8.0f;
@@ -51,8 +54,10 @@ struct Bars {
   uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], p_full, pv_done;
   uint32_t tmem_base;
   volatile int32_t abort_flag;
+  float rowmax[2][2][128];   // [tile parity][key half][row]
+  float lsum[128];           // row sums of the second key half, for the epilogue
 };
-static_assert(sizeof(Bars) <= 256, "barrier block too large");
+static_assert(sizeof(Bars) <= 3072, "barrier block too large");
 
 struct PrefillParams {
   const int32_t* table;
@@ -96,10 +101,9 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kThreads, 1)
     gqa_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid_constant__ CUtensorMap tmap_q, const PrefillParams prm) {
-  extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // the swizzled layouts need a 1024-byte aligned base
+  extern __shared__ __align__(1024) uint8_t smem[];
   Bars* bars = reinterpret_cast<Bars*>(smem + kSmemBar);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qb = prm.n_qblocks - 1 - (int)blockIdx.x;   // the blocks that see the most keys start first
@@ -113,12 +117,16 @@ __global__ void __launch_bounds__(192, 1)
   const int ntiles = (kmax + kTile - 1) / kTile;
   const int last_slot = (T + kPage - 1) / kPage - 1;           // last page slot of the sequence that holds a row
 
+  if ((smem_u32(smem) & 1023u) != 0) {   // the swizzled layouts need a 1024-byte aligned base
+    if (threadIdx.x == 0) set_status(prm.status, RELUX_ERR_UNSUPPORTED);
+    return;
+  }
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
     for (int s = 0; s < kStages; s++) { mbar_init(&bars->kv_full[s], 1); mbar_init(&bars->kv_empty[s], 1); }
     mbar_init(&bars->s_full[0], 1);
     mbar_init(&bars->s_full[1], 1);
-    mbar_init(&bars->p_full, 4);   // one arrival per softmax warp
+    mbar_init(&bars->p_full, 8);   // one arrival per softmax warp
     mbar_init(&bars->pv_done, 1);
     bars->abort_flag = 0;
     fence_mbar_init();
@@ -132,7 +140,7 @@ __global__ void __launch_bounds__(192, 1)
   tc_fence_after();
   const uint32_t tmem = bars->tmem_base;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // =============================== producer ===============================
     // The whole warp stays converged and one elected lane issues (operands stay in uniform registers).
     const bool el = elect_one();
@@ -176,7 +184,7 @@ __global__ void __launch_bounds__(192, 1)
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // =============================== MMA issuer (converged warp + elected lane) ===============================
     const bool el = elect_one();
     if (ntiles > 0) {
@@ -227,11 +235,14 @@ __global__ void __launch_bounds__(192, 1)
       }
     }
   } else {
-    // =============================== softmax / correction / epilogue (warps 0-3) ===============================
-    const int r = warp * 32 + lane;                 // TMEM lane = query row
+    // =============================== softmax / correction / epilogue (warps 0-7) ===============================
+    // Warp w reads TMEM lanes 32 (w & 3) .. +31 (the hardware's rule); warps 0-3 take keys / output dims 0-63 of
+    // their rows, warps 4-7 take 64-127.
+    const int wq = warp & 3, hb = warp >> 2;
+    const int r = wq * 32 + lane;                   // TMEM lane = query row
     const int tq = r / prm.g, hq = r % prm.g;       // token in block, head in group
     const bool real = tq < ntok;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = ((uint32_t)(wq * 32) << 16) + (uint32_t)(hb * 64);
     // keys [0, t_eff) are visible to this row
     const int t_eff = prm.causal ? min(T, T - prm.S + t0 + tq + 1) : T;
     float m_used = -INFINITY, l_run = 0.f;
@@ -239,20 +250,27 @@ __global__ void __launch_bounds__(192, 1)
       wait_bar(&bars->s_full[j & 1], (j >> 1) & 1, bars, prm.status);
       __syncwarp();   // the TMEM loads below are warp-collective
       tc_fence_after();
-      uint32_t sv[128];
-#pragma unroll
-      for (int c = 0; c < 4; c++) tmem_ld_32x32b_x32(tmem + lane_addr + kTmemS + (j & 1) * 128 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
+      uint32_t sv[64];
+      tmem_ld_32x32b_x32(tmem + lane_addr + kTmemS + (j & 1) * 128, *reinterpret_cast<uint32_t(*)[32]>(&sv[0]));
+      tmem_ld_32x32b_x32(tmem + lane_addr + kTmemS + (j & 1) * 128 + 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[32]));
       tmem_ld_wait();
-      const int nvalid = max(0, min(kTile, t_eff - j * kTile));
-      if (nvalid < kTile) {
+      const int nvalid = max(0, min(64, t_eff - j * kTile - hb * 64));
+      if (nvalid < 64) {
 #pragma unroll
-        for (int c = 0; c < 128; c++)
+        for (int c = 0; c < 64; c++)
           if (c >= nvalid) sv[c] = 0xFF800000u;   // -inf
       }
-      float mx = -INFINITY;
+      // row max of the raw scores (the softmax scale is positive, so it commutes with max); four chains, not one
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 128; c++) mx = fmaxf(mx, __uint_as_float(sv[c]));
-      mx *= prm.scale_log2;
+      for (int c = 0; c < 64; c += 4)
+#pragma unroll
+        for (int k = 0; k < 4; k++) mx4[k] = fmaxf(mx4[k], __uint_as_float(sv[c + k]));
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * prm.scale_log2;
+      bars->rowmax[j & 1][hb][r] = mx;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mx = fmaxf(mx, bars->rowmax[j & 1][hb ^ 1][r]);
+      // lazily updated running max: both threads of a row take the same decision
       float alpha = 1.f;
       bool rescale = false;
       if (mx > m_used + kRescaleThreshold) {   // also true on the first tile with a visible key (m_used = -inf)
@@ -261,37 +279,37 @@ __global__ void __launch_bounds__(192, 1)
         m_used = mx;
       }
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-      float psum = 0.f;
-      // P(j) goes to buffer j & 1, which PV(j-2) has finished reading (PV(j-1) was issued after it and is awaited below).
-      // 32 keys at a time: one FFMA + one MUFU.EX2 per score, packed to bf16, four 16-byte stores into the swizzled row.
-      uint8_t* pbuf = smem + kSmemP + (j & 1) * kPBytes;
+      float ps[2] = {0.f, 0.f};
+      // P(j) goes to buffer j & 1, which PV(j-2) has finished reading (QK(j) was issued after it).  32 keys at a time:
+      // one FFMA + one MUFU.EX2 per score, packed to bf16, four 16-byte stores into the swizzled row of key half hb.
+      uint8_t* prow = smem + kSmemP + (j & 1) * kPBytes + hb * kHalf + r * 128;
 #pragma unroll
-      for (int q4 = 0; q4 < 4; q4++) {
+      for (int q2 = 0; q2 < 2; q2++) {
         uint32_t pk[16];
 #pragma unroll
         for (int c = 0; c < 32; c += 2) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(sv[q4 * 32 + c]), prm.scale_log2, neg_m));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(sv[q4 * 32 + c + 1]), prm.scale_log2, neg_m));
-          psum += p0 + p1;
+          const float p0 = ex2_approx(fmaf(__uint_as_float(sv[q2 * 32 + c]), prm.scale_log2, neg_m));
+          const float p1 = ex2_approx(fmaf(__uint_as_float(sv[q2 * 32 + c + 1]), prm.scale_log2, neg_m));
+          ps[0] += p0;
+          ps[1] += p1;
           __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
           pk[c >> 1] = *reinterpret_cast<uint32_t*>(&b2);
         }
-        uint8_t* prow = pbuf + (q4 >> 1) * kHalf + r * 128;
 #pragma unroll
         for (int c = 0; c < 4; c++)
-          *reinterpret_cast<uint4*>(prow + ((((q4 & 1) * 4 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+          *reinterpret_cast<uint4*>(prow + (((q2 * 4 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
       }
-      l_run = l_run * alpha + psum;
+      l_run = l_run * alpha + (ps[0] + ps[1]);
       // O may be rescaled only after PV(j-1) has completed
       if (j > 0) wait_bar(&bars->pv_done, (j - 1) & 1, bars, prm.status);
       __syncwarp();
       // The TMEM loads and stores are warp-collective: the decision is taken for the whole warp, and the rows that keep
-      // their maximum multiply by one.
+      // their maximum multiply by one.  This thread's half of the row: output dims 64 hb .. +63.
       if (j > 0 && __any_sync(0xffffffffu, rescale)) {
         const float a_row = rescale ? alpha : 1.f;
         tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < 128; c += 32) {
+        for (int c = 0; c < 64; c += 32) {
           uint32_t ov[32];
           tmem_ld_32x32b_x32(tmem + lane_addr + kTmemO + c, ov);
           tmem_ld_wait();
@@ -312,12 +330,18 @@ __global__ void __launch_bounds__(192, 1)
       __syncwarp();
       tc_fence_after();
     }
+    // the row sum is the sum of its two key halves
+    if (hb == 1) bars->lsum[r] = l_run;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (hb == 0) bars->lsum[r] = l_run + bars->lsum[r];
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l_run = bars->lsum[r];
     // warp-uniform: the TMEM loads below are warp-collective
     const bool ok = ntiles > 0 && !__any_sync(0xffffffffu, bars->abort_flag != 0);
     const float inv = (ok && l_run > 0.f) ? 1.f / l_run : 0.f;
-    float* orow = prm.out + (((size_t)bi * prm.S + t0 + (real ? tq : 0)) * prm.H + (size_t)hk * prm.g + hq) * kD;
+    float* orow = prm.out + (((size_t)bi * prm.S + t0 + (real ? tq : 0)) * prm.H + (size_t)hk * prm.g + hq) * kD + hb * 64;
 #pragma unroll 1
-    for (int c = 0; c < 128; c += 32) {
+    for (int c = 0; c < 64; c += 32) {
       uint32_t ov[32];
       if (ok) {
         tmem_ld_32x32b_x32(tmem + lane_addr + kTmemO + c, ov);
@@ -405,7 +429,7 @@ int32_t launch_gqa_prefill_sm100(Pool* p, const SeqBatch& sb, const relux_attn_a
   RELUX_CUDA_TRY(cudaFuncSetAttribute(gqa_prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
   dim3 grid(k.n_qblocks, prm.gqa_num_kv_heads, sb.n_seqs);
   RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), st));
-  gqa_prefill_sm100_kernel<<<grid, 192, kSmemTotal, st>>>(p->tmap_gqa, tq, k);
+  gqa_prefill_sm100_kernel<<<grid, kThreads, kSmemTotal, st>>>(p->tmap_gqa, tq, k);
   RELUX_CUDA_TRY(cudaGetLastError());
   RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), st));
   p->timed_calls++;
