@@ -335,17 +335,17 @@ def run_mla(args, w, world, rank, local, dist):
         rows_now[0] = float(lens0.sum())
 
     def step_resident():
-        pool.append(0, d_new_c, d_new_r, B)
+        # one call per decode step: append of the new rows + attention over the cache that now holds them
         rows_now[0] += B
         rows_log.append(rows_now[0])
-        pool.decode(0, B, d_qc, d_out, H, Dh, scale, q_rope=d_qr, w_uk=d_wuk, w_uv=d_wuv)
+        pool.step(0, B, d_new_c, d_new_r, d_qc, d_out, H, Dh, scale, q_rope=d_qr, w_uk=d_wuk, w_uv=d_wuv)
 
     def step_e2e():
         # pipelined calls: this step's host -> device copies overlap the previous step's kernels; the previous step's
         # output is read (one value of it) once its copy has landed
         i = e2e_calls[0]
-        pool.append(0, pins[0].array, pins[1].array, B, pipelined=True)
-        pool.decode(0, B, pins[2].array, pin_outs[i % 2].array, H, Dh, scale, q_rope=pins[3].array, w_uk=d_wuk, w_uv=d_wuv, pipelined=True)
+        pool.step(0, B, pins[0].array, pins[1].array, pins[2].array, pin_outs[i % 2].array, H, Dh, scale, q_rope=pins[3].array,
+                  w_uk=d_wuk, w_uv=d_wuv, pipelined=True)
         if i >= 1:
             pool.wait_output(1)
             e2e_checksum[0] ^= int(pin_outs[(i - 1) % 2].array[0, 0, 0, 0])

@@ -293,6 +293,14 @@ typedef struct relux_attn_args {
 int32_t relux_mla_decode(relux_pool_t pool, const relux_attn_args* args);
 int32_t relux_gqa_decode(relux_pool_t pool, const relux_attn_args* args);
 
+/* One decode step in one call: append the new rows (append->advance must be 1), then attend over the cache that now
+ * includes them -- MLA.forwardCached steps 4-6 (mla.go:309-377), MHA.forwardCached steps 5-8 (mha.go:283-348).  Same
+ * results as relux_*_append followed by relux_*_decode.  On the MLA tensor-core path the append and the stream partition
+ * ride in the launch that absorbs W_UK into the queries (one kernel instead of three); other shapes and modes run the two
+ * calls one after the other.  Both argument structs must name the same layer and sequences. */
+int32_t relux_mla_step(relux_pool_t pool, const relux_append_args* append, const relux_attn_args* attn);
+int32_t relux_gqa_step(relux_pool_t pool, const relux_append_args* append, const relux_attn_args* attn);
+
 /* Speculative verify in one call (speculative.go:189-207 -> mha.go:245-369 with seqQ = k+1): writes the
  * q_tokens draft K/V rows of every sequence past its cursor (append with advance = 0), then attends with
  * extra_tokens = q_tokens.  Commit the accepted prefix with relux_seq_set_len afterwards. */

@@ -345,6 +345,15 @@ class Pool:
         fn = self.lib.relux_mla_verify if self.kind == L.POOL_MLA else self.lib.relux_gqa_verify
         L.check(fn(self.h, C.byref(at), C.byref(ap)))
 
+    def step(self, layer, n_seqs, new_a, new_b, q, out, num_heads, head_dim, scale, q_rope=None, w_uk=None, w_uv=None, n_new=None,
+             mode=L.ATTN_FAST, seq_ids=None, kv_layout=L.LAYOUT_TOKEN_MAJOR, q_dtype=None, out_dtype=None, kv_dtype=None, pipelined=False):
+        """One decode step in one call: append the new rows, then attend (relux_mla_step / relux_gqa_step)."""
+        ap = self._append_args(layer, new_a, new_b, n_seqs, seq_ids, n_new, kv_layout, True, kv_dtype, pipelined)
+        at = self._attn_args(layer, n_seqs, q, q_rope, out, num_heads, head_dim, scale, 1, 0, True, mode, w_uk, w_uv, seq_ids,
+                             L.LAYOUT_TOKEN_MAJOR, L.LAYOUT_TOKEN_MAJOR, q_dtype, out_dtype, pipelined)
+        fn = self.lib.relux_mla_step if self.kind == L.POOL_MLA else self.lib.relux_gqa_step
+        L.check(fn(self.h, C.byref(ap), C.byref(at)))
+
     def spec_accept(self, n_seqs, k, vocab, draft_tokens, draft_logits, target_logits, draws, temperature=1.0, top_k=0,
                     top_p=1.0, min_p=0.0, mode=L.ATTN_FAST, commit=False, seq_ids=None):
         """acceptPhase + resampleRejected (speculative.go:211-295) for n_seqs sequences, ending in Sampler.Sample

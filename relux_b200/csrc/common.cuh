@@ -97,7 +97,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Every wait is bounded: after kSpinLimit failed polls the caller gets `false`, records
 // RELUX_ERR_TIMEOUT and leaves its loop, so a protocol bug cannot hang the GPU.
-constexpr uint32_t kSpinLimit = 20u * 1000u * 1000u;
+constexpr uint32_t kSpinLimit = 4u * 1000u * 1000u;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t i = 0; i < kSpinLimit; i++) {
     if (mbar_try_wait(bar, parity)) return true;

@@ -112,6 +112,7 @@ struct Pool {
   size_t stage_slot_ints() const { return 2 * (size_t)prm.max_seqs + 1; }
   // staging of activations that arrive in host memory, and outputs that leave to it
   GrowBuf in_a, in_b, out_buf, q_conv;
+  GrowBuf step_rows;   // host-resident new rows of a fused decode step (the attention call uses in_a / in_b for the queries)
   PipeSlots pipe_in_a, pipe_in_b, pipe_app_a, pipe_app_b, pipe_out;   // the same for pipelined calls
   // attention scratch
   GrowBuf q_abs;     // MLA absorbed queries, bf16 [n][S][H][dC+dHR]
@@ -188,8 +189,18 @@ int32_t launch_attn_reference_mla(Pool* p, const SeqBatch& sb, const relux_attn_
 int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, void* d_out);
 // True when this call is a multi-token call that the tcgen05 prefill kernel serves (it takes bf16 queries).
 bool gqa_prompt_wants_bf16(const Pool* p, const relux_attn_args& a);
+// The new rows of a decode step handed to the attention call, for the fused preparation (one launch for absorb + append +
+// stream partition); the host lengths already include them.
+struct StepAppend {
+  const void* ckv;
+  const void* kr;
+  int dtype;
+  const int32_t* d_row_off;   // device row offsets of the append batch (nullptr = one row per sequence)
+};
 int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, const void* d_qr,
-                               void* d_out);
+                               void* d_out, const StepAppend* step = nullptr);
+// True when launch_mla_decode_fast can take the step's append into its preparation launch.
+bool mla_step_fusable(Pool* p, const relux_attn_args& a, int n_seqs);
 
 int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a);
 int32_t do_gqa_layer(Pool* p, const relux_gqa_layer_args* a);

@@ -14,6 +14,7 @@
 #include "common.cuh"
 #include "internal.h"
 #include "splitkv.h"
+#include "prep_parts.cuh"
 
 namespace relux {
 
@@ -21,6 +22,9 @@ int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_ar
 bool mla_sm100_eligible(const Pool* p, const relux_attn_args& a);
 int mla_sm100_workers(Pool* p, int q_tokens);
 bool mla_proj_mma_eligible(int Dh, int dC);
+bool mla_prep_fits(int n_seqs, int H, int dC);
+int32_t launch_mla_prep(Device* dev, const void* q_nope, const void* q_rope, int q_bf16, const uint16_t* W_UK, uint16_t* q_abs, int rows,
+                        int H, int dC, int dHR, const PrepAppend& ap, const PrepPlan& pl);
 int32_t launch_mla_absorb_mma(Device* dev, const void* q_nope, const void* q_rope, int q_bf16, const uint16_t* W_UK, uint16_t* q_abs,
                               int rows, int H, int dC, int dHR);
 int32_t launch_mla_vup_mma(Device* dev, const uint16_t* o_lat, const uint16_t* W_UV, float* out, int rows, int H, int dC);
@@ -238,8 +242,14 @@ int32_t launch_generic(Pool* p, const MlaGenParams& k, int items, cudaStream_t s
 
 }  // namespace
 
+bool mla_step_fusable(Pool* p, const relux_attn_args& a, int n_seqs) {
+  const relux_pool_params& prm = p->prm;
+  return !p->compat && a.mode == RELUX_ATTN_FAST && a.extra_tokens == 0 && mla_sm100_eligible(p, a) &&
+         mla_proj_mma_eligible(a.head_dim, prm.mla_dc) && mla_prep_fits(n_seqs, a.num_heads, prm.mla_dc);
+}
+
 int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, const void* d_qr,
-                               void* d_out) {
+                               void* d_out, const StepAppend* step) {
   const relux_pool_params& prm = p->prm;
   const int H = a.num_heads, Dh = a.head_dim, dC = prm.mla_dc, dHR = prm.mla_dhr, S = a.q_tokens;
   const int rows = sb.n_seqs * S, rows_total = S * H, roww = dC + dHR;
@@ -255,7 +265,42 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   // The stream partition depends on the cached lengths only, the absorb on the queries only: the one-block builder
   // runs on the side stream next to the absorb kernel and is joined before the decode kernel.
   cudaStream_t side = p->dev->side_stream;
-  const bool fork = sm100 && side != nullptr;
+  const bool fused_prep = step != nullptr;   // the caller checked mla_step_fusable
+  const bool fork = sm100 && side != nullptr && !fused_prep;
+  if (fused_prep) {
+    // one launch: absorb + the step's append + the stream partition (the host lengths already count the new rows)
+    rc = plan_stream(p, sb, a.layer, a.extra_tokens, mla_sm100_workers(p, S), 2, &plan, st, false);
+    if (rc) return rc;
+    PrepAppend ap;
+    ap.table = p->d_table;
+    ap.table_stride = prm.max_pages_per_seq;
+    ap.len = p->d_len + (size_t)a.layer * prm.max_seqs;
+    ap.seq_ids = sb.d_seq_ids;
+    ap.row_off = step->d_row_off;
+    ap.num_pages = prm.num_pages;
+    ap.page_tokens = prm.page_tokens;
+    ap.max_pages_per_seq = prm.max_pages_per_seq;
+    ap.n_seqs = sb.n_seqs;
+    ap.status = p->d_status;
+    ap.done = reinterpret_cast<uint32_t*>(p->d_status + 1);
+    ap.layer_base = p->storage + (size_t)a.layer * p->layer_elems;
+    ap.ckv = step->ckv;
+    ap.kr = step->kr;
+    ap.f32 = step->dtype == RELUX_DTYPE_F32;
+    ap.dC = dC;
+    ap.dHR = dHR;
+    ap.blocked = p->mla_blocked ? 1 : 0;
+    PrepPlan pl;
+    pl.extra = a.extra_tokens;
+    pl.G = plan.chunk_pages;
+    pl.workers = plan.num_workers;
+    pl.items = plan.stream_items;
+    pl.chunk_off = plan.chunk_off;
+    pl.worker_first = plan.worker_first;
+    rc = launch_mla_prep(p->dev, d_q, d_qr, a.q_dtype == RELUX_DTYPE_BF16, (const uint16_t*)a.w_uk, (uint16_t*)p->q_abs.p, rows, H, dC, dHR, ap,
+                         pl);
+    if (rc) return rc;
+  }
   if (fork) {
     RELUX_CUDA_TRY(cudaEventRecord(p->dev->ev_fork, st));
     RELUX_CUDA_TRY(cudaStreamWaitEvent(side, p->dev->ev_fork, 0));
@@ -264,7 +309,9 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
     RELUX_CUDA_TRY(cudaEventRecord(p->dev->ev_join, side));
   }
   const bool proj_mma = mla_proj_mma_eligible(Dh, dC);
-  if (proj_mma) {
+  if (fused_prep) {
+    // absorbed queries, appended rows and the partition are already queued
+  } else if (proj_mma) {
     rc = launch_mla_absorb_mma(p->dev, d_q, d_qr, a.q_dtype == RELUX_DTYPE_BF16, (const uint16_t*)a.w_uk, (uint16_t*)p->q_abs.p, rows, H, dC,
                                dHR);
     if (rc) return rc;
@@ -277,7 +324,8 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
     RELUX_CUDA_TRY(cudaGetLastError());
     count_launch(p->dev);
   }
-  if (fork)
+  if (fused_prep) {
+  } else if (fork)
     RELUX_CUDA_TRY(cudaStreamWaitEvent(st, p->dev->ev_join, 0));
   else if (sm100)   // persistent CTA pairs over a stream partition; ranges are whole 128-token tiles
     rc = plan_stream(p, sb, a.layer, a.extra_tokens, mla_sm100_workers(p, S), 2, &plan, st);

@@ -10,6 +10,7 @@
 // Shapes: Dh = 128, dC a multiple of 128.  Other shapes use the scalar kernels in mla_decode.cu.
 #include "common.cuh"
 #include "internal.h"
+#include "prep_parts.cuh"
 
 namespace relux {
 
@@ -60,13 +61,12 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 // grid (H, dC/128, ceil(rows/64)), 128 threads.  Every load of the CTA is in flight at once (cp.async for bf16
 // sources), the result leaves through shared memory as 16-byte row-contiguous stores.
-__global__ void __launch_bounds__(128) mla_absorb_mma_kernel(const void* __restrict__ q_nope, const void* __restrict__ q_rope, int q_bf16,
-                                                             const uint16_t* __restrict__ W_UK, uint16_t* __restrict__ q_abs, int rows,
-                                                             int H, int dC, int dHR) {
-  extern __shared__ __align__(16) uint16_t sm[];
+__device__ __forceinline__ void absorb_block(uint16_t* sm, const void* __restrict__ q_nope, const void* __restrict__ q_rope, int q_bf16,
+                                             const uint16_t* __restrict__ W_UK, uint16_t* __restrict__ q_abs, int rows, int H, int dC,
+                                             int dHR, int bx, int by, int bz) {
   uint16_t* As = sm;                  // [64][kStride]
   uint16_t* Bs = sm + 64 * kStride;   // [128][kStride]   rows = latent index c, cols = d
-  const int h = blockIdx.x, c0 = blockIdx.y * 128, r0 = blockIdx.z * 64;
+  const int h = bx, c0 = by * 128, r0 = bz * 64;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll 4
   for (int e = threadIdx.x; e < 128 * (kDh / 8); e += blockDim.x) {
@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(128) mla_absorb_mma_kernel(const void* __restr
   }
   cp_async_commit();
   const int roww = dC + dHR;
-  if (blockIdx.y == 0) {   // the rope part of q~ is a copy (with the same rounding when the source is float32)
+  if (by == 0) {   // the rope part of q~ is a copy (with the same rounding when the source is float32)
     const int vecs = dHR / 8;
     for (int e = threadIdx.x; e < 64 * vecs; e += blockDim.x) {
       const int r = e / vecs, v = e % vecs;
@@ -132,6 +132,32 @@ __global__ void __launch_bounds__(128) mla_absorb_mma_kernel(const void* __restr
     if (r0 + r >= rows) continue;
     *reinterpret_cast<uint4*>(q_abs + ((size_t)(r0 + r) * H + h) * roww + c0 + v * 8) = *reinterpret_cast<const uint4*>(Os + r * kStride + v * 8);
   }
+}
+
+__global__ void __launch_bounds__(128) mla_absorb_mma_kernel(const void* __restrict__ q_nope, const void* __restrict__ q_rope, int q_bf16,
+                                                             const uint16_t* __restrict__ W_UK, uint16_t* __restrict__ q_abs, int rows,
+                                                             int H, int dC, int dHR) {
+  extern __shared__ __align__(16) uint16_t sm[];
+  absorb_block(sm, q_nope, q_rope, q_bf16, W_UK, q_abs, rows, H, dC, dHR, blockIdx.x, blockIdx.y, blockIdx.z);
+}
+
+// The preparation of one MLA decode step in ONE launch: the absorb grid (H, dC/128, ceil(rows/64)) plus one extra z
+// slice whose blocks append the step's new rows (block e < n_seqs: sequence e) and build the stream partition (block
+// e == n_seqs).  The three jobs are independent of one another: the append reads the lengths before it writes, the
+// partition counts every sequence's new rows itself, and the last of those blocks to finish advances the lengths.
+__global__ void __launch_bounds__(128) mla_prep_kernel(const void* __restrict__ q_nope, const void* __restrict__ q_rope, int q_bf16,
+                                                       const uint16_t* __restrict__ W_UK, uint16_t* __restrict__ q_abs, int rows, int H,
+                                                       int dC, int dHR, int z_absorb, const PrepAppend ap, const PrepPlan pl) {
+  extern __shared__ __align__(16) uint16_t sm[];
+  if ((int)blockIdx.z < z_absorb) {
+    absorb_block(sm, q_nope, q_rope, q_bf16, W_UK, q_abs, rows, H, dC, dHR, blockIdx.x, blockIdx.y, blockIdx.z);
+    return;
+  }
+  const int e = blockIdx.y * gridDim.x + blockIdx.x;
+  if (e > ap.n_seqs) return;
+  if (e < ap.n_seqs) prep_append_seq(ap, e);
+  else prep_build_stream(ap, pl);
+  prep_arrive_and_advance(ap, (uint32_t)ap.n_seqs + 1u);
 }
 
 // grid (H, ceil(rows/64)), 128 threads.  o_lat bf16 [rows][H][dC]; out f32 [rows][H][128].
@@ -356,6 +382,21 @@ int32_t launch_mla_absorb_mma(Device* dev, const void* q_nope, const void* q_rop
   const size_t smem = (size_t)(64 + 128) * kStride * 2;
   RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_absorb_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   mla_absorb_mma_kernel<<<grid, 128, smem, dev->stream>>>(q_nope, q_rope, q_bf16, W_UK, q_abs, rows, H, dC, dHR);
+  RELUX_CUDA_TRY(cudaGetLastError());
+  count_launch(dev);
+  return RELUX_OK;
+}
+
+// One launch: absorb + append of the step's rows + stream partition (see mla_prep_kernel).  n_seqs + 1 extra blocks
+// must fit one z slice of the absorb grid.
+bool mla_prep_fits(int n_seqs, int H, int dC) { return n_seqs + 1 <= H * (dC / 128); }
+int32_t launch_mla_prep(Device* dev, const void* q_nope, const void* q_rope, int q_bf16, const uint16_t* W_UK, uint16_t* q_abs, int rows,
+                        int H, int dC, int dHR, const PrepAppend& ap, const PrepPlan& pl) {
+  const int z_absorb = (rows + 63) / 64;
+  dim3 grid(H, dC / 128, z_absorb + 1);
+  const size_t smem = (size_t)(64 + 128) * kStride * 2;
+  RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  mla_prep_kernel<<<grid, 128, smem, dev->stream>>>(q_nope, q_rope, q_bf16, W_UK, q_abs, rows, H, dC, dHR, z_absorb, ap, pl);
   RELUX_CUDA_TRY(cudaGetLastError());
   count_launch(dev);
   return RELUX_OK;

@@ -179,7 +179,7 @@ static void pool_free_all(Pool* p) {
     }
   fr(p->storage); fr(p->d_table); fr(p->d_len); fr(p->d_status); fr(p->d_seq_ids); fr(p->d_row_off);
   fr(p->in_a.p); fr(p->in_b.p); fr(p->out_buf.p); fr(p->q_abs.p); fr(p->part_o.p); fr(p->part_ml.p); fr(p->work.p);
-  fr(p->o_lat.p); fr(p->q_conv.p); fr(p->rope_tab.p); fr(p->layer_buf.p); fr(p->shadow_f32); fr(p->chunk_tab.p);
+  fr(p->o_lat.p); fr(p->q_conv.p); fr(p->rope_tab.p); fr(p->layer_buf.p); fr(p->shadow_f32); fr(p->chunk_tab.p); fr(p->step_rows.p);
   if (p->h_stage) cudaFreeHost(p->h_stage);
   for (cudaEvent_t ev : p->stage_ev)
     if (ev) cudaEventDestroy(ev);
@@ -347,7 +347,7 @@ static int32_t do_append(Pool* p, const relux_append_args* a, int kind) {
 int32_t convert_layout(Device* dev, const void* src, void* dst, int n, int S, int H, int D, int src_dtype, int dst_dtype,
                        int src_layout, int dst_layout);
 
-static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
+static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind, const StepAppend* step = nullptr) {
   if (!a) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
   if (p->prm.kind != kind) { set_error("pool kind does not match this attention call"); return RELUX_ERR_INVALID_ARG; }
   int32_t rc = check_layer(p, a->layer);
@@ -462,7 +462,7 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind) {
     rc = (kind == RELUX_POOL_MLA) ? launch_attn_reference_mla(p, sb, aa, (const float*)dq, (const float*)dqr, kout)
                                   : launch_attn_reference_gqa(p, sb, aa, (const float*)dq, kout);
   } else {
-    rc = (kind == RELUX_POOL_MLA) ? launch_mla_decode_fast(p, sb, aa, dq, dqr, kout) : launch_gqa_decode_fast(p, sb, aa, dq, kout);
+    rc = (kind == RELUX_POOL_MLA) ? launch_mla_decode_fast(p, sb, aa, dq, dqr, kout, step) : launch_gqa_decode_fast(p, sb, aa, dq, kout);
   }
   if (rc) return rc;
   if ((rc = pipe_release(p, p->pipe_in_a, slot_q)) || (rc = pipe_release(p, p->pipe_in_b, slot_qr))) return rc;
@@ -1098,6 +1098,81 @@ static int32_t do_verify(Pool* p, const relux_attn_args* attn, const relux_appen
   if (rc) return rc;
   return do_attention(p, attn, kind);
 }
+// One decode step: append the new rows (advance = 1), then attend over the cache that now includes them
+// (MLA.forwardCached steps 4-6, mla.go:309-377; MHA.forwardCached steps 5-8, mha.go:283-348).  For the MLA tensor-core
+// path the append rides in the attention call's preparation launch (absorb + append + stream partition: one kernel
+// instead of three); every other case is the two calls one after the other.
+static int32_t do_step(Pool* p, const relux_append_args* kv, const relux_attn_args* attn, int kind) {
+  if (!attn || !kv) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
+  if (kv->advance != 1) { set_error("step: the new rows must be appended with advance=1 (use relux_*_verify for draft rows)"); return RELUX_ERR_INVALID_ARG; }
+  if (kv->layer != attn->layer || kv->n_seqs != attn->n_seqs) { set_error("step: append and attention arguments disagree"); return RELUX_ERR_INVALID_ARG; }
+  const bool same_ids = (!kv->seq_ids && !attn->seq_ids) ||
+                        (kv->seq_ids && attn->seq_ids && memcmp(kv->seq_ids, attn->seq_ids, sizeof(int32_t) * (size_t)std::max(0, kv->n_seqs)) == 0);
+  const bool fuse = kind == RELUX_POOL_MLA && p->prm.kind == RELUX_POOL_MLA && same_ids && kv->n_seqs > 0 && kv->n_seqs <= p->prm.max_seqs &&
+                    kv->a && kv->b && attn->num_heads > 0 && attn->head_dim > 0 && mla_step_fusable(p, *attn, kv->n_seqs) &&
+                    (kv->dtype == RELUX_DTYPE_F32 || kv->dtype == RELUX_DTYPE_BF16) && (kv->mem == RELUX_MEM_HOST || kv->mem == RELUX_MEM_DEVICE) &&
+                    !(kv->flags & ~RELUX_CALL_PIPELINED) && kv->layer >= 0 && kv->layer < p->prm.num_layers;
+  if (!fuse) {
+    int32_t rc = do_append(p, kv, kind);
+    if (rc) return rc;
+    return do_attention(p, attn, kind);
+  }
+  // --- fused: validate and stage the append exactly as do_append does, but leave the launch to the attention call ---
+  const relux_pool_params& prm = p->prm;
+  SeqBatch sb;
+  int32_t rc = stage_batch(p, kv->n_seqs, kv->seq_ids, kv->n_new, 1, &sb);
+  if (rc) return rc;
+  for (int i = 0; i < sb.n_seqs; i++) {
+    const int s = sb.seq[i];
+    const int len = p->h_len[(size_t)kv->layer * prm.max_seqs + s], cap = p->seq_pages[s] * prm.page_tokens;
+    if (len + sb.rows[i] > cap) {
+      set_error("Append: layer %d overflow: total=%d + newLen=%d > capacity=%d (sequence %d)", kv->layer, len, sb.rows[i], cap, s);
+      return RELUX_ERR_OVERFLOW;
+    }
+  }
+  if (sb.total_rows == 0) return do_attention(p, attn, kind);
+  if (kv->mem == RELUX_MEM_DEVICE && ((rc = check_dev_align(kv->a, "append input a")) || (rc = check_dev_align(kv->b, "append input b")))) return rc;
+  const size_t es = dtype_size(kv->dtype);
+  const size_t bytes_a = (size_t)sb.total_rows * prm.mla_dc * es, bytes_b = (size_t)sb.total_rows * prm.mla_dhr * es;
+  const bool piped = (kv->flags & RELUX_CALL_PIPELINED) && kv->mem == RELUX_MEM_HOST && p->dev->h2d_stream;
+  const void *da = nullptr, *db = nullptr;
+  int slot_a = -1, slot_b = -1;
+  if (piped) {
+    if ((rc = pipe_stage_in(p, p->pipe_app_a, kv->a, bytes_a, &da, &slot_a))) return rc;
+    if ((rc = pipe_stage_in(p, p->pipe_app_b, kv->b, bytes_b, &db, &slot_b))) return rc;
+  } else if (kv->mem == RELUX_MEM_HOST) {
+    // the attention call stages q / q_rope in in_a / in_b: the step's rows get a block of their own
+    if ((rc = grow(p->dev, p->step_rows, bytes_a + bytes_b + 256))) return rc;
+    char* base = (char*)p->step_rows.p;
+    const size_t off_b = (bytes_a + 255) & ~(size_t)255;
+    RELUX_CUDA_TRY(cudaMemcpyAsync(base, kv->a, bytes_a, cudaMemcpyHostToDevice, p->dev->stream));
+    RELUX_CUDA_TRY(cudaMemcpyAsync(base + off_b, kv->b, bytes_b, cudaMemcpyHostToDevice, p->dev->stream));
+    da = base;
+    db = base + off_b;
+  } else {
+    da = kv->a;
+    db = kv->b;
+  }
+  // the host lengths count the new rows from here on: the attention call plans with them
+  for (int i = 0; i < sb.n_seqs; i++) p->h_len[(size_t)kv->layer * prm.max_seqs + sb.seq[i]] += sb.rows[i];
+  StepAppend step{da, db, kv->dtype, sb.d_row_off};
+  rc = do_attention(p, attn, kind, &step);
+  if (rc) {   // nothing was launched for the append: take the rows back
+    for (int i = 0; i < sb.n_seqs; i++) p->h_len[(size_t)kv->layer * prm.max_seqs + sb.seq[i]] -= sb.rows[i];
+    return rc;
+  }
+  if ((rc = pipe_release(p, p->pipe_app_a, slot_a)) || (rc = pipe_release(p, p->pipe_app_b, slot_b))) return rc;
+  return RELUX_OK;
+}
+API int32_t relux_mla_step(relux_pool_t h, const relux_append_args* kv, const relux_attn_args* attn) {
+  GET_POOL(h);
+  return do_step(p, kv, attn, RELUX_POOL_MLA);
+}
+API int32_t relux_gqa_step(relux_pool_t h, const relux_append_args* kv, const relux_attn_args* attn) {
+  GET_POOL(h);
+  return do_step(p, kv, attn, RELUX_POOL_GQA);
+}
+
 API int32_t relux_gqa_verify(relux_pool_t h, const relux_attn_args* attn, const relux_append_args* kv) {
   GET_POOL(h);
   return do_verify(p, attn, kv, RELUX_POOL_GQA);

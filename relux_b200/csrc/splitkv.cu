@@ -205,7 +205,8 @@ void stream_partition_shape(const int* pages, int n_seqs, int workers, int page_
   *items_out = items;
 }
 
-int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int workers, int page_multiple, SplitPlan* plan, cudaStream_t st) {
+int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int workers, int page_multiple, SplitPlan* plan, cudaStream_t st,
+                    bool launch_builder) {
   const relux_pool_params& prm = p->prm;
   std::vector<int> pages(sb.n_seqs);
   for (int i = 0; i < sb.n_seqs; i++) {
@@ -226,6 +227,7 @@ int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int worke
   plan->stream_items = (StreamItem*)p->work.p;
   plan->chunk_off = (int32_t*)((char*)p->work.p + off_chunk);
   plan->worker_first = (int32_t*)((char*)p->work.p + off_worker);
+  if (!launch_builder) return RELUX_OK;
   const int32_t* len = p->d_len + (size_t)layer * prm.max_seqs;
   build_stream_kernel<<<1, 256, 0, st>>>(len, sb.d_seq_ids, sb.n_seqs, extra, prm.page_tokens, (int)G, workers,
                                                      plan->stream_items, plan->chunk_off, plan->worker_first);

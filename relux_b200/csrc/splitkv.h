@@ -42,7 +42,10 @@ int32_t plan_splitkv(Pool* p, const SeqBatch& sb, int layer, int extra, int ctas
 // `workers` equal ranges of `chunk_pages` pages (a multiple of `page_multiple`); one item = the part of one sequence
 // inside one range, so a worker meets an item boundary only where a sequence ends inside its range.
 // `st`: the stream the builder kernel is launched on (the pool's main stream, or the device's side stream).
-int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int workers, int page_multiple, SplitPlan* plan, cudaStream_t st);
+// launch_builder = false: only the host half (counts, buffers); the caller builds the lists itself (the fused decode-step
+// preparation of mla_proj.cu does it inside its own launch).
+int32_t plan_stream(Pool* p, const SeqBatch& sb, int layer, int extra, int workers, int page_multiple, SplitPlan* plan, cudaStream_t st,
+                    bool launch_builder = true);
 int32_t launch_build_worklist_raw(cudaStream_t st, const int32_t* len, const int32_t* seq_ids, int n_seqs, int extra, int page_tokens,
                                   int chunk_pages, WorkItem* items, int32_t* chunk_off);
 int32_t launch_merge_raw(cudaStream_t st, const float* part_o, const float* part_ml, const int32_t* chunk_off, int n_seqs, int rows,

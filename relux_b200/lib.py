@@ -36,7 +36,7 @@ EXPORTS = [
     "relux_pool_read_rows", "relux_mla_append", "relux_gqa_append", "relux_mla_decode", "relux_gqa_decode", "relux_gqa_verify",
     "relux_mla_verify", "relux_pool_last_kernel_ms", "relux_pool_kernel_ms_mean", "relux_mla_forward_cached", "relux_gqa_forward_cached", "relux_stream_partition", "relux_seq_save_file", "relux_seq_load_file", "relux_pool_projection_ms_mean", "relux_gqa_decode_noalloc",
     "relux_spec_accept", "relux_sampler_sample", "relux_pool_tune", "relux_pool_kernel_ms_list", "relux_matmul_f32_bf16",
-    "relux_mla_import_weights", "relux_pool_selftest_wait", "relux_pool_wait_output",
+    "relux_mla_import_weights", "relux_pool_selftest_wait", "relux_pool_wait_output", "relux_mla_step", "relux_gqa_step",
 ]
 
 
@@ -191,6 +191,8 @@ def load():
             getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AttnArgs)]
         for n in ("relux_gqa_verify", "relux_mla_verify"):
             getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AttnArgs), C.POINTER(AppendArgs)]
+        for n in ("relux_gqa_step", "relux_mla_step"):
+            getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AppendArgs), C.POINTER(AttnArgs)]
         L.relux_pool_projection_ms_mean.argtypes = [C.c_void_p, C.c_int32, C.POINTER(C.c_float), C.POINTER(C.c_int32)]
         L.relux_stream_partition.argtypes = [C.POINTER(StreamPartitionArgs)]
         L.relux_seq_save_file.argtypes = [C.c_void_p, C.c_int32, C.c_char_p, C.c_int32]

@@ -477,3 +477,121 @@ def test_gqa_prefill_kernel_group_sizes(dev, oracle, H, Hkv, causal):
     assert np.abs(out2 - out).max() <= 5e-3
     assert pool.status() == 0
     pool.destroy()
+
+
+@pytest.mark.parametrize("variant", ["host_f32", "pipelined_bf16", "ragged_ids"])
+def test_mla_step_is_append_then_decode_in_one_call(dev, oracle, variant):
+    """relux_mla_step (append + decode; on this shape the append and the stream partition ride in the absorb launch)
+    against relux_mla_append followed by relux_mla_decode on a second pool with the same contents: the same output bits,
+    the same cache rows, the same lengths; fewer launches.  Variants: float32 host rows; pinned bf16 rows through the
+    pipelined copies; sequences named in another order with 0, 1, 2 and 3 new rows."""
+    H, Dh, dC, dHR = 128, 128, 512, 64
+    ctx = [130, 700, 63, 1, 255]
+    B = len(ctx)
+    scale = float(1.0 / np.sqrt(Dh + dHR))
+    pools = [build_mla(dev, oracle, np.random.default_rng(91), ctx, dC, dHR, extra_pages=2)[0] for _ in range(2)]
+    rng = np.random.default_rng(92)
+    wuk = dev.upload(oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02))
+    wuv = dev.upload(oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02))
+    ids = np.array([3, 0, 4, 1, 2], np.int32) if variant == "ragged_ids" else None
+    steps = 5
+    piped = variant == "pipelined_bf16"
+    held = []
+    fused_launches = plain_launches = 0
+    for i in range(steps):
+        n_new = np.array([(i + j) % 4 for j in range(B)], np.int32) if variant == "ragged_ids" else None
+        rows = int(n_new.sum()) if n_new is not None else B
+        c = rng.standard_normal((rows, dC)).astype(np.float32)
+        r = rng.standard_normal((rows, dHR)).astype(np.float32)
+        q = oracle.bf16_from_f32(rng.standard_normal((B, 1, H, Dh)).astype(np.float32))
+        qr = oracle.bf16_from_f32(rng.standard_normal((B, 1, H, dHR)).astype(np.float32))
+        if piped:
+            c, r = oracle.bf16_from_f32(c), oracle.bf16_from_f32(r)
+        want = np.empty((B, 1, H, Dh), np.float32)
+        n0 = dev.launch_count()
+        pools[0].append(0, c, r, B, seq_ids=ids, n_new=n_new)
+        pools[0].decode(0, B, q, want, H, Dh, scale, q_rope=qr, w_uk=wuk, w_uv=wuv, seq_ids=ids)
+        plain_launches += dev.launch_count() - n0
+        if piped:
+            bufs = []
+            for a in (c, r, q, qr):
+                h = dev.pinned(a.shape, a.dtype)
+                h.array[...] = a
+                bufs.append(h)
+            o = dev.pinned((B, 1, H, Dh), np.float32)
+            held += bufs + [o]
+            n0 = dev.launch_count()
+            pools[1].step(0, B, bufs[0].array, bufs[1].array, bufs[2].array, o.array, H, Dh, scale, q_rope=bufs[3].array, w_uk=wuk,
+                          w_uv=wuv, pipelined=True)
+            fused_launches += dev.launch_count() - n0
+            pools[1].wait_output(0)
+            got = o.array.copy()
+        else:
+            got = np.full((B, 1, H, Dh), np.nan, np.float32)
+            n0 = dev.launch_count()
+            pools[1].step(0, B, c, r, q, got, H, Dh, scale, q_rope=qr, w_uk=wuk, w_uv=wuv, n_new=n_new, seq_ids=ids)
+            fused_launches += dev.launch_count() - n0
+        assert np.array_equal(got, want), "step %d differs" % i
+    assert fused_launches == plain_launches - 2 * steps   # append and partition builder folded into the absorb launch
+    for s in range(B):
+        n = pools[0].seq_len(0, s)
+        assert pools[1].seq_len(0, s) == n
+        a0, b0 = pools[0].read_rows(0, s, max(0, n - 12), min(n, 12))
+        a1, b1 = pools[1].read_rows(0, s, max(0, n - 12), min(n, 12))
+        assert np.array_equal(a0, a1) and np.array_equal(b0, b1)
+    dev.sync()
+    assert pools[0].status() == 0 and pools[1].status() == 0
+    for h in held:
+        h.close()
+    for p in pools:
+        p.destroy()
+    wuk.free(); wuv.free()
+
+
+def test_step_falls_back_to_two_calls_where_the_fused_launch_does_not_apply(dev, oracle):
+    """relux_gqa_step, and relux_mla_step in RELUX_ATTN_REFERENCE mode, run the append and the attention one after the
+    other: results equal the two separate calls; mismatched arguments are refused before anything is written."""
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(95)
+    H, Hkv, D = 32, 8, 128
+    ctx = [100, 64, 7]
+    B = len(ctx)
+    pools = [build_gqa(dev, oracle, np.random.default_rng(96), ctx, Hkv, D, extra_pages=2)[0] for _ in range(2)]
+    k = rng.standard_normal((B, Hkv, D)).astype(np.float32)
+    v = rng.standard_normal((B, Hkv, D)).astype(np.float32)
+    q = rng.standard_normal((B, 1, H, D)).astype(np.float32)
+    want = np.empty_like(q)
+    got = np.empty_like(q)
+    scale = float(1.0 / np.sqrt(D))
+    pools[0].append(0, k, v, B)
+    pools[0].decode(0, B, q, want, H, D, scale)
+    pools[1].step(0, B, k, v, q, got, H, D, scale)
+    assert np.array_equal(got, want)
+    assert [pools[1].seq_len(0, s) for s in range(B)] == [c + 1 for c in ctx]
+    for p in pools:
+        p.destroy()
+    # MLA, reference arithmetic
+    dC, dHR, Hm, Dh = 512, 64, 16, 128
+    pools = [build_mla(dev, oracle, np.random.default_rng(97), ctx, dC, dHR, extra_pages=2)[0] for _ in range(2)]
+    wuk = dev.upload(oracle.bf16_from_f32(rng.standard_normal((dC, Hm * Dh)).astype(np.float32) * 0.02))
+    wuv = dev.upload(oracle.bf16_from_f32(rng.standard_normal((dC, Hm * Dh)).astype(np.float32) * 0.02))
+    c = rng.standard_normal((B, dC)).astype(np.float32)
+    r = rng.standard_normal((B, dHR)).astype(np.float32)
+    q = rng.standard_normal((B, 1, Hm, Dh)).astype(np.float32)
+    qr = rng.standard_normal((B, 1, Hm, dHR)).astype(np.float32)
+    want = np.empty_like(q)
+    got = np.empty_like(q)
+    pools[0].append(0, c, r, B)
+    pools[0].decode(0, B, q, want, Hm, Dh, 0.07, q_rope=qr, w_uk=wuk, w_uv=wuv, mode=L.ATTN_REFERENCE)
+    pools[1].step(0, B, c, r, q, got, Hm, Dh, 0.07, q_rope=qr, w_uk=wuk, w_uv=wuv, mode=L.ATTN_REFERENCE)
+    assert np.array_equal(got, want)
+    # the two argument structs must name the same sequences
+    ap = pools[1]._append_args(0, c, r, B, None, None, L.LAYOUT_TOKEN_MAJOR, True, None)
+    at = pools[1]._attn_args(0, B - 1, q, qr, got, Hm, Dh, 0.07, 1, 0, True, L.ATTN_FAST, wuk, wuv, None, L.LAYOUT_TOKEN_MAJOR,
+                             L.LAYOUT_TOKEN_MAJOR, None, None)
+    import ctypes as C
+    assert pools[1].lib.relux_mla_step(pools[1].h, C.byref(ap), C.byref(at)) == L.ERR_INVALID_ARG
+    assert [pools[1].seq_len(0, s) for s in range(B)] == [c_ + 1 for c_ in ctx]
+    for p in pools:
+        p.destroy()
+    wuk.free(); wuv.free()
