@@ -34,6 +34,15 @@
 // barriers live in each CTA and are armed by tcgen05.commit with mbarrier multicast (not a TMA load); p_full lives in
 // the leader and counts the softmax warps of both CTAs.  No TMA multicast anywhere.
 // No split-KV: the output is normalised in the epilogue and written once.
+//
+// The same kernel serves MLA prompts (template parameter kMla): MLA.forwardCached for seqQ > 1 expands every cached
+// latent row into per-head keys and values first (internal/transformer/mla.go:323-326; here mla_expand_sm100.cu, bf16
+// rows in a dense scratch array) and then runs ordinary attention with 128 + 64 score dims (mla.go:328-377).  For this
+// kernel that is the group size 1 case with three changes: the Q tile and every K stage carry a third 64-column block
+// (the RoPE part: of the query from its own array, of the key from the pool's pages, shared by all heads), QK^T is 12
+// K-steps instead of 8, and the expanded keys / values are addressed densely (head * Ttot + first row of the sequence +
+// token) instead of through the page table.  192-wide tiles leave room for one Q buffer only: the next item's Q is
+// requested when the current item's last QK^T has completed and lands behind its last softmax and PV.
 // Every wait is bounded (status RELUX_ERR_TIMEOUT, shared abort flag, all warps still reach the end and free TMEM).
 #include <algorithm>
 #include <cuda_bf16.h>
@@ -49,16 +58,32 @@ namespace {
 constexpr int kD = 128, kPage = 64, kTile = 128;
 constexpr int kBlk = 8192;                 // one [64 rows x 64 cols] bf16 box, 128-byte swizzled
 constexpr int kHalf = 2 * kBlk;            // [128 rows x 64 cols]
-constexpr int kQBytes = 2 * kHalf;         // one Q tile: [dims 0-63 | dims 64-127], each 128 rows x 128 B
-constexpr int kSmemQ = 0;                  // two Q tiles (items in turn)
-constexpr int kSmemP = kSmemQ + 2 * kQBytes;   // two P tiles (tiles in turn) of [keys 0-63 | keys 64-127]
-constexpr int kPBytes = 2 * kHalf;
-constexpr int kDepth = 3;                  // K / V tiles in flight
-constexpr int kStages = 2 * kDepth;        // K(g), V(g), K(g+1), V(g+1), ...
-constexpr int kStageBytes = 2 * kBlk;      // 16 KB per CTA.  K: own page [dims 0-63 | dims 64-127]; V: own 64 dims [page 0 | page 1]
-constexpr int kSmemRing = kSmemP + 2 * kPBytes;
-constexpr int kSmemBar = kSmemRing + kStages * kStageBytes;   // 229376
-constexpr int kSmemTotal = kSmemBar + 3072;                   // 232448: all a CTA may use
+constexpr int kPBytes = 2 * kHalf;         // one P tile: [keys 0-63 | keys 64-127], each 128 rows x 128 B
+constexpr int kVBytes = 2 * kBlk;          // V stage, 16 KB per CTA: own 64 output dims of [keys 0-63 | keys 64-127]
+constexpr int kMaxDepth = 3;
+
+// Shared-memory plan of the two variants.
+//   GQA (kMla = false): score width 128.  Q tile [dims 0-63 | dims 64-127] x 2 buffers (items in turn), K stage = own
+//     page [dims 0-63 | dims 64-127] (16 KB), three K and three V stages: 64 + 64 + 48 + 48 = 224 KB.
+//   MLA (kMla = true): score width 192 = 128 expanded key dims + 64 shared RoPE dims.  Q tile [nope 0-63 | nope 64-127 |
+//     rope] (48 KB) in ONE buffer, K stage = own 64 keys [nope 0-63 | nope 64-127 | rope] (24 KB), three K and two V
+//     stages: 48 + 64 + 72 + 32 = 216 KB.
+template <bool kMla>
+struct Plan {
+  static constexpr int kQHalves = kMla ? 3 : 2;
+  static constexpr int kQBytes = kQHalves * kHalf;
+  static constexpr int kQBufs = kMla ? 1 : 2;
+  static constexpr int kKBytes = (kMla ? 3 : 2) * kBlk;
+  static constexpr int kDepthK = 3, kDepthV = kMla ? 2 : 3;
+  static constexpr int kKSteps = kMla ? 12 : 8;            // K = 16 slices of the score contraction
+  static constexpr int kSmemQ = 0;
+  static constexpr int kSmemP = kSmemQ + kQBufs * kQBytes;  // two P tiles (tiles in turn)
+  static constexpr int kSmemK = kSmemP + 2 * kPBytes;
+  static constexpr int kSmemV = kSmemK + kDepthK * kKBytes;
+  static constexpr int kSmemBar = kSmemV + kDepthV * kVBytes;
+  static constexpr int kSmemTotal = kSmemBar + 3072;
+  static_assert(kSmemTotal <= 232448, "more shared memory than a CTA may use");
+};
 constexpr int kSplit = 2;                                     // threads per query row: each takes 128 / kSplit keys and output dims
 constexpr int kCols = 128 / kSplit;
 constexpr int kSoftmaxWarps = 4 * kSplit;
@@ -68,7 +93,7 @@ constexpr uint32_t kTmemS = 0, kTmemO = 256;
 constexpr float kRescaleThreshold = 8.0f;
 
 struct Bars {
-  uint64_t q_full[2], q_empty[2], kv_full[kStages], kv_empty[kStages], s_full[2], p_full, pv_done;
+  uint64_t q_full[2], q_empty[2], k_full[kMaxDepth], k_empty[kMaxDepth], v_full[kMaxDepth], v_empty[kMaxDepth], s_full[2], p_full, pv_done;
   uint32_t tmem_base;
   volatile int32_t abort_flag;
   float rowmax[2][kSplit][128];   // [tile parity][key slice][row]; an item's epilogue borrows the buffer of the tile that follows
@@ -85,7 +110,12 @@ struct PrefillParams {
   int32_t bq;                 // query tokens per block = 128 / g
   int32_t n_qblocks, n_pairs; // blocks and block pairs per (sequence, kv head)
   int32_t n_seqs, n_items;    // items = n_pairs * Hkv * n_seqs
-  int32_t krow0, vrow0;       // first TMA row of this layer's K block / V block
+  int32_t krow0, vrow0;       // first TMA row of this layer's K block / V block (MLA: of the expanded keys / values)
+  // MLA only: expanded rows are dense, row = head * Ttot + seq_base[sequence] + token; the RoPE part of a key is read from
+  // the pool's pages (block rope_block of blocks_per_page 64-column blocks per page, first row of the layer pool_row0)
+  const int32_t* seq_base;
+  int32_t Ttot, rope_block, blocks_per_page;
+  int64_t pool_row0;
   float scale_log2;
   float* out;                 // [n][S][H][128] f32
   int32_t* status;
@@ -95,8 +125,9 @@ struct PrefillParams {
 // keys under the causal mask) to the first, and inside a pair index over (sequence, kv head).
 struct Item {
   int32_t bi, seq, hk, pair;
-  int32_t T, ntiles, last_slot;
+  int32_t T, ntiles, last_slot, base;
 };
+template <bool kMla>
 __device__ __forceinline__ Item item_of(const PrefillParams& prm, int idx) {
   Item it;
   const int per = prm.Hkv * prm.n_seqs;
@@ -111,6 +142,8 @@ __device__ __forceinline__ Item item_of(const PrefillParams& prm, int idx) {
   const int kmax = prm.causal ? (it.T - prm.S + last_tok + 1) : it.T;
   it.ntiles = (kmax + kTile - 1) / kTile;
   it.last_slot = (it.T + kPage - 1) / kPage - 1;   // last page slot of the sequence that holds a row
+  it.base = 0;
+  if constexpr (kMla) it.base = __ldg(prm.seq_base + it.bi);
   return it;
 }
 
@@ -143,10 +176,17 @@ __device__ __forceinline__ void tma_load_3d_2sm(void* smem_dst, const CUtensorMa
       : "memory");
 }
 
+// tmap_kv: GQA the pool's K / V rows; MLA the expanded keys / values.  tmap_q: the queries (MLA: their nope part).
+// tmap_qr, tmap_rope (MLA only): the queries' RoPE part, and the pool's 64-column blocks.
+template <bool kMla>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-    gqa_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid_constant__ CUtensorMap tmap_q, const PrefillParams prm) {
+    prefill_sm100_kernel(const __grid_constant__ CUtensorMap tmap_kv, const __grid_constant__ CUtensorMap tmap_q,
+                         const __grid_constant__ CUtensorMap tmap_qr, const __grid_constant__ CUtensorMap tmap_rope, const PrefillParams prm) {
+  using PL = Plan<kMla>;
+  constexpr int kQBytes = PL::kQBytes, kQBufs = PL::kQBufs, kKBytes = PL::kKBytes, kDepthK = PL::kDepthK, kDepthV = PL::kDepthV;
+  constexpr int kSmemQ = PL::kSmemQ, kSmemP = PL::kSmemP, kSmemK = PL::kSmemK, kSmemV = PL::kSmemV;
   extern __shared__ __align__(1024) uint8_t smem[];
-  Bars* bars = reinterpret_cast<Bars*>(smem + kSmemBar);
+  Bars* bars = reinterpret_cast<Bars*>(smem + PL::kSmemBar);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const int worker = blockIdx.x >> 1, n_workers = gridDim.x >> 1;
@@ -158,7 +198,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   }
   if (threadIdx.x == 0) {
     for (int s = 0; s < 2; s++) { mbar_init(&bars->q_full[s], 1); mbar_init(&bars->q_empty[s], 1); }
-    for (int s = 0; s < kStages; s++) { mbar_init(&bars->kv_full[s], 1); mbar_init(&bars->kv_empty[s], 1); }
+    for (int s = 0; s < kMaxDepth; s++) {
+      mbar_init(&bars->k_full[s], 1);
+      mbar_init(&bars->k_empty[s], 1);
+      mbar_init(&bars->v_full[s], 1);
+      mbar_init(&bars->v_empty[s], 1);
+    }
     mbar_init(&bars->s_full[0], 1);
     mbar_init(&bars->s_full[1], 1);
     mbar_init(&bars->p_full, 2 * kSoftmaxWarps);   // one arrival per softmax warp of each CTA of the pair
@@ -182,60 +227,86 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     if (el) {
       tma_prefetch_desc(&tmap_kv);
       tma_prefetch_desc(&tmap_q);
+      if constexpr (kMla) {
+        tma_prefetch_desc(&tmap_qr);
+        tma_prefetch_desc(&tmap_rope);
+      }
     }
     auto load_q = [&](const Item& it, int n) {
-      // item n of this worker uses Q buffer n & 1, free again once the last QK^T of item n - 2 has completed
-      if (n >= 2) wait_bar(&bars->q_empty[n & 1], ((n >> 1) - 1) & 1, bars, prm.status);
-      const uint32_t lead_q = mapa_u32(smem_u32(&bars->q_full[n & 1]), 0);
+      // item n of this worker uses Q buffer n % kQBufs, free again once the last QK^T of item n - kQBufs has completed
+      const int qb = n % kQBufs, use = n / kQBufs;
+      if (use > 0) wait_bar(&bars->q_empty[qb], (use - 1) & 1, bars, prm.status);
+      const uint32_t lead_q = mapa_u32(smem_u32(&bars->q_full[qb]), 0);
       if (el) {
         const int t0 = (2 * it.pair + (int)rank) * prm.bq;
-        uint8_t* dst = smem + kSmemQ + (n & 1) * kQBytes;
-        if (rank == 0) mbar_expect_tx(&bars->q_full[n & 1], 2 * kQBytes);   // the Q tiles of both CTAs
+        uint8_t* dst = smem + kSmemQ + qb * kQBytes;
+        if (rank == 0) mbar_expect_tx(&bars->q_full[qb], 2 * kQBytes);   // the Q tiles of both CTAs
         // box = [64 dims][g heads][bq tokens]: rows land as token_in_block * g + head_in_group
         tma_load_3d_2sm(dst, &tmap_q, 0, it.hk * prm.g, it.bi * prm.S + t0, lead_q);
         tma_load_3d_2sm(dst + kHalf, &tmap_q, 64, it.hk * prm.g, it.bi * prm.S + t0, lead_q);
+        if constexpr (kMla) tma_load_3d_2sm(dst + 2 * kHalf, &tmap_qr, 0, it.hk, it.bi * prm.S + t0, lead_q);
       }
       __syncwarp();
     };
     int g = 0, n = 0;
-    Item cur = item_of(prm, worker);
+    Item cur = item_of<kMla>(prm, worker);
     load_q(cur, 0);
     for (int idx = worker; idx < prm.n_items; idx += n_workers, n++) {
       for (int j = 0; j < cur.ntiles; j++, g++) {
-        int32_t y[2];
-#pragma unroll
-        for (int h2 = 0; h2 < 2; h2++) {
-          const int slot = min(2 * j + h2, cur.last_slot);   // a tile's second page may lie past the sequence: its keys are masked
+        // rows of the tile's two 64-key halves in tmap_kv (relative to krow0 / vrow0), and for MLA the pool row of the
+        // RoPE block of this CTA's half
+        int32_t y[2], y_rope = 0;
+        if constexpr (kMla) {
+          y[0] = cur.hk * prm.Ttot + cur.base + j * kTile;
+          y[1] = y[0] + kPage;
+          const int slot = min(2 * j + (int)rank, cur.last_slot);
           int32_t pg = __ldg(prm.table + (size_t)cur.seq * prm.table_stride + slot);
-          if (pg < 0 || pg >= prm.num_pages) {               // reported, and replaced by page 0 so that no load leaves the pool
+          if (pg < 0 || pg >= prm.num_pages) {
             set_status(prm.status, RELUX_ERR_BAD_PAGE);
             pg = 0;
           }
-          y[h2] = (pg * prm.Hkv + cur.hk) * kPage;
+          y_rope = (int32_t)(prm.pool_row0 + ((int64_t)pg * prm.blocks_per_page + prm.rope_block) * kPage);
+        } else {
+#pragma unroll
+          for (int h2 = 0; h2 < 2; h2++) {
+            const int slot = min(2 * j + h2, cur.last_slot);   // a tile's second page may lie past the sequence: its keys are masked
+            int32_t pg = __ldg(prm.table + (size_t)cur.seq * prm.table_stride + slot);
+            if (pg < 0 || pg >= prm.num_pages) {               // reported, and replaced by page 0 so that no load leaves the pool
+              set_status(prm.status, RELUX_ERR_BAD_PAGE);
+              pg = 0;
+            }
+            y[h2] = (pg * prm.Hkv + cur.hk) * kPage;
+          }
         }
         const int32_t y_own = rank ? y[1] : y[0];
-        const int u = g / kDepth;
-#pragma unroll
-        for (int kv = 0; kv < 2; kv++) {
-          const int st = (g % kDepth) * 2 + kv;
-          if (u > 0) wait_bar(&bars->kv_empty[st], (u - 1) & 1, bars, prm.status);
-          const uint32_t lead = mapa_u32(smem_u32(&bars->kv_full[st]), 0);
+        {   // K: this CTA's 64 keys of the tile, every 64-dim block of the score contraction
+          const int st = g % kDepthK, u = g / kDepthK;
+          if (u > 0) wait_bar(&bars->k_empty[st], (u - 1) & 1, bars, prm.status);
+          const uint32_t lead = mapa_u32(smem_u32(&bars->k_full[st]), 0);
           if (el) {
-            uint8_t* dst = smem + kSmemRing + st * kStageBytes;
-            if (rank == 0) mbar_expect_tx(&bars->kv_full[st], 2 * kStageBytes);   // the halves of both CTAs
-            if (kv == 0) {   // K: this CTA's page of the tile, both 64-dim halves
-              tma_load_2d_2sm(dst, &tmap_kv, 0, prm.krow0 + y_own, lead);
-              tma_load_2d_2sm(dst + kBlk, &tmap_kv, 64, prm.krow0 + y_own, lead);
-            } else {         // V: this CTA's 64 output dims of both pages
-              tma_load_2d_2sm(dst, &tmap_kv, 64 * (int)rank, prm.vrow0 + y[0], lead);
-              tma_load_2d_2sm(dst + kBlk, &tmap_kv, 64 * (int)rank, prm.vrow0 + y[1], lead);
-            }
+            uint8_t* dst = smem + kSmemK + st * kKBytes;
+            if (rank == 0) mbar_expect_tx(&bars->k_full[st], 2 * kKBytes);   // the halves of both CTAs
+            tma_load_2d_2sm(dst, &tmap_kv, 0, prm.krow0 + y_own, lead);
+            tma_load_2d_2sm(dst + kBlk, &tmap_kv, 64, prm.krow0 + y_own, lead);
+            if constexpr (kMla) tma_load_2d_2sm(dst + 2 * kBlk, &tmap_rope, 0, y_rope, lead);
+          }
+          __syncwarp();
+        }
+        {   // V: this CTA's 64 output dims of both halves
+          const int st = g % kDepthV, u = g / kDepthV;
+          if (u > 0) wait_bar(&bars->v_empty[st], (u - 1) & 1, bars, prm.status);
+          const uint32_t lead = mapa_u32(smem_u32(&bars->v_full[st]), 0);
+          if (el) {
+            uint8_t* dst = smem + kSmemV + st * kVBytes;
+            if (rank == 0) mbar_expect_tx(&bars->v_full[st], 2 * kVBytes);
+            tma_load_2d_2sm(dst, &tmap_kv, 64 * (int)rank, prm.vrow0 + y[0], lead);
+            tma_load_2d_2sm(dst + kBlk, &tmap_kv, 64 * (int)rank, prm.vrow0 + y[1], lead);
           }
           __syncwarp();
         }
       }
       if (idx + n_workers < prm.n_items) {   // the next item's Q, while this item's last tiles are still in flight
-        cur = item_of(prm, idx + n_workers);
+        cur = item_of<kMla>(prm, idx + n_workers);
         load_q(cur, n + 1);
       }
     }
@@ -250,54 +321,64 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       // QK^T of tile g (worker-wide index) of item n; `first`: the item's first tile (its Q must have landed);
       // `last`: its last tile, after which the Q buffer is free
       auto issue_qk = [&](int g, int n, bool first, bool last) {
-        if (first) wait_bar(&bars->q_full[n & 1], (n >> 1) & 1, bars, prm.status);
-        const int st = (g % kDepth) * 2;
-        wait_bar(&bars->kv_full[st], (g / kDepth) & 1, bars, prm.status);
+        const int qb = n % kQBufs;
+        if (first) wait_bar(&bars->q_full[qb], (n / kQBufs) & 1, bars, prm.status);
+        const int st = g % kDepthK;
+        wait_bar(&bars->k_full[st], (g / kDepthK) & 1, bars, prm.status);
         tc_fence_after();
         if (el) {
-          const uint64_t dK = make_desc_kmajor_sw128(smem_u32(smem + kSmemRing + st * kStageBytes));
-          const uint64_t dQn = dQ + ((uint32_t)((n & 1) * kQBytes) >> 4);
+          const uint64_t dK = make_desc_kmajor_sw128(smem_u32(smem + kSmemK + st * kKBytes));
+          const uint64_t dQn = dQ + ((uint32_t)(qb * kQBytes) >> 4);
           const uint32_t d = tmem + kTmemS + (g & 1) * 128;
 #pragma unroll
-          for (int ks = 0; ks < 8; ks++) {
-            const uint32_t aoff = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;   // Q: 128 rows per 64-dim half
-            const uint32_t boff = (uint32_t)((ks >> 2) * kBlk + (ks & 3) * 32) >> 4;    // K: 64 rows per 64-dim half
+          for (int ks = 0; ks < PL::kKSteps; ks++) {
+            const uint32_t aoff = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;   // Q: 128 rows per 64-dim block
+            const uint32_t boff = (uint32_t)((ks >> 2) * kBlk + (ks & 3) * 32) >> 4;    // K: 64 rows per 64-dim block
             umma_ss<2>(d, dQn + aoff, dK + boff, idesc_qk, ks != 0);
           }
-          umma_commit_mc<2>(&bars->kv_empty[st], 0x3);
-          if (last) umma_commit_mc<2>(&bars->q_empty[n & 1], 0x3);
+          umma_commit_mc<2>(&bars->k_empty[st], 0x3);
+          if (last) umma_commit_mc<2>(&bars->q_empty[qb], 0x3);
           umma_commit_mc<2>(&bars->s_full[g & 1], 0x3);
         }
         __syncwarp();
       };
       auto issue_pv = [&](int g, bool first) {
-        const int st = (g % kDepth) * 2 + 1;
+        const int st = g % kDepthV;
         wait_bar(&bars->p_full, g & 1, bars, prm.status);
-        wait_bar(&bars->kv_full[st], (g / kDepth) & 1, bars, prm.status);
+        wait_bar(&bars->v_full[st], (g / kDepthV) & 1, bars, prm.status);
         tc_fence_after();   // P rows, a possible O rescale and the previous item's O read-out were done by the softmax warps of both CTAs
         if (el) {
-          const uint64_t dV = make_desc_mnmajor_sw128(smem_u32(smem + kSmemRing + st * kStageBytes), kBlk);
+          const uint64_t dV = make_desc_mnmajor_sw128(smem_u32(smem + kSmemV + st * kVBytes), kBlk);
           const uint64_t dPg = dP + ((uint32_t)((g & 1) * kPBytes) >> 4);
 #pragma unroll
           for (int ks = 0; ks < 8; ks++) {
             const uint32_t aoff = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
             umma_ss<2>(tmem + kTmemO, dPg + aoff, dV + ((uint32_t)(ks * 2048) >> 4), idesc_pv, !first || ks != 0);
           }
-          umma_commit_mc<2>(&bars->kv_empty[st], 0x3);
+          umma_commit_mc<2>(&bars->v_empty[st], 0x3);
           umma_commit_mc<2>(&bars->pv_done, 0x3);
         }
         __syncwarp();
       };
       int g = 0, n = 0;
-      int ntiles = item_of(prm, worker).ntiles;
+      int ntiles = item_of<kMla>(prm, worker).ntiles;
       issue_qk(0, 0, true, ntiles == 1);
       for (int idx = worker; idx < prm.n_items; idx += n_workers, n++) {
         const bool has_next = idx + n_workers < prm.n_items;
-        const int next_tiles = has_next ? item_of(prm, idx + n_workers).ntiles : 0;
+        const int next_tiles = has_next ? item_of<kMla>(prm, idx + n_workers).ntiles : 0;
         for (int i = 0; i < ntiles; i++, g++) {
-          if (i + 1 < ntiles) issue_qk(g + 1, n, false, i + 2 == ntiles);
-          else if (has_next) issue_qk(g + 1, n + 1, true, next_tiles == 1);
-          issue_pv(g, i == 0);
+          if (i + 1 < ntiles) {
+            issue_qk(g + 1, n, false, i + 2 == ntiles);
+            issue_pv(g, i == 0);
+          } else if (has_next && kQBufs > 1) {
+            issue_qk(g + 1, n + 1, true, next_tiles == 1);
+            issue_pv(g, i == 0);
+          } else {
+            // one Q buffer: the next item's Q is requested when this item's last QK^T has completed, so its first QK^T
+            // goes behind this item's last PV instead of waiting for the load in front of it
+            issue_pv(g, i == 0);
+            if (has_next) issue_qk(g + 1, n + 1, true, next_tiles == 1);
+          }
         }
         ntiles = next_tiles;
       }
@@ -313,7 +394,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     const uint32_t p_full_lead = mapa_u32(smem_u32(&bars->p_full), 0);
     int g = 0;
     for (int idx = worker; idx < prm.n_items; idx += n_workers) {
-      const Item it = item_of(prm, idx);
+      const Item it = item_of<kMla>(prm, idx);
       const int t0 = (2 * it.pair + (int)rank) * prm.bq;          // first query token of this CTA's block
       const int ntok = max(0, min(prm.bq, prm.S - t0));           // its real tokens (0: the odd block of the last pair)
       const bool real = tq < ntok;
@@ -454,9 +535,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+}  // namespace
+bool make_tmap_2d(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows);
+namespace {
+
 // CTA pairs that can be resident at the same time (one CTA per SM: the kernel uses all of its shared memory).
+template <bool kMla>
 int prefill_workers(Pool* p) {
   static int max_clusters = 0;
+  constexpr int kSmemTotal = Plan<kMla>::kSmemTotal;
+  auto gqa_prefill_sm100_kernel = prefill_sm100_kernel<kMla>;
   if (!max_clusters) {
     int n = 0;
     cudaLaunchConfig_t cfg = {};
@@ -542,11 +630,120 @@ int32_t launch_gqa_prefill_sm100(Pool* p, const SeqBatch& sb, const relux_attn_a
   k.out = d_out;
   k.status = p->d_status;
   cudaStream_t st = p->dev->stream;
-  const int workers = (int)std::min<int64_t>(prefill_workers(p), items);
-  RELUX_CUDA_TRY(cudaFuncSetAttribute(gqa_prefill_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+  const int workers = (int)std::min<int64_t>(prefill_workers<false>(p), items);
+  constexpr int kSmemTotal = Plan<false>::kSmemTotal;
+  RELUX_CUDA_TRY(cudaFuncSetAttribute(prefill_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
   dim3 grid(2 * workers, 1, 1);   // CTA pairs
   RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), st));
-  gqa_prefill_sm100_kernel<<<grid, kThreads, kSmemTotal, st>>>(p->tmap_gqa, tq, k);
+  prefill_sm100_kernel<false><<<grid, kThreads, kSmemTotal, st>>>(p->tmap_gqa, tq, tq, p->tmap_gqa, k);
+  RELUX_CUDA_TRY(cudaGetLastError());
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), st));
+  p->timed_calls++;
+  count_launch(p->dev);
+  return RELUX_OK;
+}
+
+// ---- MLA prompts ---------------------------------------------------------------------------------------------------
+bool mla_expand_eligible(const Pool* p, int num_heads, int head_dim);
+int64_t mla_expand_rows(const Pool* p, const SeqBatch& sb, int layer, int extra);
+int32_t launch_mla_expand_sm100(Pool* p, const SeqBatch& sb, int layer, int extra, int H, const uint16_t* w_uk, const uint16_t* w_uv,
+                                int64_t Ttot, uint16_t* kx, uint16_t* vx, int32_t* seq_base);
+
+// Bytes of scratch the expanded keys and values of this batch take: 2 x H x Ttot rows of 128 bf16.
+static int64_t mla_prefill_scratch_bytes(int64_t Ttot, int H) { return 2 * (int64_t)H * Ttot * 128 * 2; }
+
+// A prompt goes to the expand + prefill pair when the calls' shapes fit the kernels, the prompt is long enough for the
+// expansion to pay (its cost is per cached row, the saving per query row), and the scratch stays within the limit.
+bool mla_prefill_eligible(const Pool* p, const SeqBatch& sb, const relux_attn_args& a) {
+  const relux_pool_params& prm = p->prm;
+  if (p->compat || a.mode != RELUX_ATTN_FAST || !mla_expand_eligible(p, a.num_heads, a.head_dim) || prm.mla_dhr != 64) return false;
+  const int min_tokens = p->tune.get(RELUX_TUNE_MLA_PROMPT_MIN_TOKENS);
+  if (min_tokens < 0 || a.q_tokens < std::max(2, min_tokens)) return false;
+  const int64_t Ttot = mla_expand_rows(p, sb, a.layer, a.extra_tokens);
+  if (2 * (int64_t)a.num_heads * Ttot >= ((int64_t)1 << 31)) return false;   // TMA row coordinates are 32-bit
+  // absorbed scores cost 1088 multiply-adds per (query row, key), expanded ones 320 plus 512 * 256 per key and head
+  // for the expansion: the expansion pays from about 170 query tokens per sequence
+  const int64_t limit = (int64_t)p->tune.get(RELUX_TUNE_MLA_PROMPT_SCRATCH_MB) << 20;
+  return mla_prefill_scratch_bytes(Ttot, a.num_heads) <= limit;
+}
+
+// q: device bf16 [n][S][H][128], q_rope: device bf16 [n][S][H][64], token-major.  out: device f32 [n][S][H][128].
+int32_t launch_mla_prefill_sm100(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const uint16_t* d_q, const uint16_t* d_qr, float* d_out) {
+  const relux_pool_params& prm = p->prm;
+  static EncodeTiledFn enc = nullptr;
+  if (!enc) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+      set_error("cuTensorMapEncodeTiled is not available");
+      return RELUX_ERR_CUDA;
+    }
+    enc = (EncodeTiledFn)sym;
+  }
+  const int S = a.q_tokens, H = a.num_heads;
+  const int64_t Ttot = mla_expand_rows(p, sb, a.layer, a.extra_tokens);
+  const size_t x_bytes = (size_t)mla_prefill_scratch_bytes(Ttot, H);
+  int32_t rc = grow(p->dev, p->expand_buf, x_bytes + sizeof(int32_t) * ((size_t)sb.n_seqs + 1) + 256);
+  if (rc) return rc;
+  uint16_t* kx = (uint16_t*)p->expand_buf.p;
+  uint16_t* vx = kx + (size_t)H * Ttot * 128;
+  int32_t* seq_base = (int32_t*)((char*)p->expand_buf.p + ((x_bytes + 255) & ~(size_t)255));
+  rc = launch_mla_expand_sm100(p, sb, a.layer, a.extra_tokens, H, (const uint16_t*)a.w_uk, (const uint16_t*)a.w_uv, Ttot, kx, vx, seq_base);
+  if (rc) return rc;
+  CUtensorMap tq, tqr, tx;
+  for (int which = 0; which < 2; which++) {
+    const int cols = which ? 64 : kD;
+    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)H, (cuuint64_t)sb.n_seqs * S};
+    cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)H * cols * 2};
+    cuuint32_t box[3] = {64, 1, 128};
+    cuuint32_t es[3] = {1, 1, 1};
+    if (enc(which ? &tqr : &tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)(which ? d_qr : d_q), dims, strides, box, es,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+      set_error("tensor map for the prompt's queries could not be encoded");
+      return RELUX_ERR_CUDA;
+    }
+  }
+  if (!make_tmap_2d(&tx, kx, (uint64_t)2 * H * Ttot, kD, 64, 64)) {
+    set_error("tensor map for the expanded keys / values could not be encoded");
+    return RELUX_ERR_CUDA;
+  }
+  PrefillParams k{};
+  k.table = p->d_table;
+  k.table_stride = prm.max_pages_per_seq;
+  k.len = p->d_len + (size_t)a.layer * prm.max_seqs;
+  k.seq_ids = sb.d_seq_ids;
+  k.num_pages = prm.num_pages;
+  k.Hkv = H;
+  k.H = H;
+  k.g = 1;
+  k.S = S;
+  k.extra = a.extra_tokens;
+  k.causal = a.causal;
+  k.bq = 128;
+  k.n_qblocks = (S + 127) / 128;
+  k.n_pairs = (k.n_qblocks + 1) / 2;
+  k.n_seqs = sb.n_seqs;
+  const int64_t items = (int64_t)k.n_pairs * H * sb.n_seqs;
+  if (items > ((int64_t)1 << 30)) { set_error("prompt too long for one prefill launch"); return RELUX_ERR_UNSUPPORTED; }
+  k.n_items = (int32_t)items;
+  k.krow0 = 0;
+  k.vrow0 = (int32_t)((int64_t)H * Ttot);
+  k.seq_base = seq_base;
+  k.Ttot = (int32_t)Ttot;
+  k.blocks_per_page = p->row_elems_a / 64;
+  k.rope_block = prm.mla_dc / 64;
+  k.pool_row0 = (int64_t)a.layer * prm.num_pages * k.blocks_per_page * kPage;
+  k.scale_log2 = a.scale * 1.4426950408889634f;
+  k.out = d_out;
+  k.status = p->d_status;
+  cudaStream_t st = p->dev->stream;
+  const int workers = (int)std::min<int64_t>(prefill_workers<true>(p), items);
+  constexpr int kSmemTotal = Plan<true>::kSmemTotal;
+  RELUX_CUDA_TRY(cudaFuncSetAttribute(prefill_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
+  dim3 grid(2 * workers, 1, 1);   // CTA pairs
+  RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), st));
+  prefill_sm100_kernel<true><<<grid, kThreads, kSmemTotal, st>>>(tx, tq, tqr, p->tmap_mla, k);
   RELUX_CUDA_TRY(cudaGetLastError());
   RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), st));
   p->timed_calls++;

@@ -112,6 +112,7 @@ struct Pool {
   size_t stage_slot_ints() const { return 2 * (size_t)prm.max_seqs + 1; }
   // staging of activations that arrive in host memory, and outputs that leave to it
   GrowBuf in_a, in_b, out_buf, q_conv;
+  GrowBuf expand_buf;  // expanded keys / values of an MLA prompt (+ the sequences' first rows)
   GrowBuf step_rows;   // host-resident new rows of a fused decode step (the attention call uses in_a / in_b for the queries)
   PipeSlots pipe_in_a, pipe_in_b, pipe_app_a, pipe_app_b, pipe_out;   // the same for pipelined calls
   // attention scratch
@@ -188,6 +189,7 @@ int32_t launch_attn_reference_mla(Pool* p, const SeqBatch& sb, const relux_attn_
                                   float* d_out);
 int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, void* d_out);
 // True when this call is a multi-token call that the tcgen05 prefill kernel serves (it takes bf16 queries).
+bool mla_prefill_eligible(const Pool* p, const SeqBatch& sb, const relux_attn_args& a);
 bool gqa_prompt_wants_bf16(const Pool* p, const relux_attn_args& a);
 // The new rows of a decode step handed to the attention call, for the fused preparation (one launch for absorb + append +
 // stream partition); the host lengths already include them.

@@ -23,6 +23,7 @@ bool mla_sm100_eligible(const Pool* p, const relux_attn_args& a);
 int mla_sm100_workers(Pool* p, int q_tokens);
 bool mla_proj_mma_eligible(int Dh, int dC);
 bool mla_prep_fits(int n_seqs, int H, int dC);
+int32_t launch_mla_prefill_sm100(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const uint16_t* d_q, const uint16_t* d_qr, float* d_out);
 int32_t launch_mla_prep(Device* dev, const void* q_nope, const void* q_rope, int q_bf16, const uint16_t* W_UK, uint16_t* q_abs, int rows,
                         int H, int dC, int dHR, const PrepAppend& ap, const PrepPlan& pl);
 int32_t launch_mla_absorb_mma(Device* dev, const void* q_nope, const void* q_rope, int q_bf16, const uint16_t* W_UK, uint16_t* q_abs,
@@ -257,6 +258,9 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
     set_error("MLA FAST kernels cover dC in {64,128,256,512} (got %d); use RELUX_ATTN_REFERENCE", dC);
     return RELUX_ERR_UNSUPPORTED;
   }
+  // a prompt: expand the cached latents into per-head keys / values once, then ordinary attention on the prefill kernel
+  if (!step && a.q_dtype == RELUX_DTYPE_BF16 && mla_prefill_eligible(p, sb, a))
+    return launch_mla_prefill_sm100(p, sb, a, (const uint16_t*)d_q, (const uint16_t*)d_qr, (float*)d_out);
   cudaStream_t st = p->dev->stream;
   int32_t rc = grow(p->dev, p->q_abs, (size_t)rows * H * roww * 2);
   if (rc) return rc;

@@ -179,7 +179,7 @@ static void pool_free_all(Pool* p) {
     }
   fr(p->storage); fr(p->d_table); fr(p->d_len); fr(p->d_status); fr(p->d_seq_ids); fr(p->d_row_off);
   fr(p->in_a.p); fr(p->in_b.p); fr(p->out_buf.p); fr(p->q_abs.p); fr(p->part_o.p); fr(p->part_ml.p); fr(p->work.p);
-  fr(p->o_lat.p); fr(p->q_conv.p); fr(p->rope_tab.p); fr(p->layer_buf.p); fr(p->shadow_f32); fr(p->chunk_tab.p); fr(p->step_rows.p);
+  fr(p->o_lat.p); fr(p->q_conv.p); fr(p->rope_tab.p); fr(p->layer_buf.p); fr(p->shadow_f32); fr(p->chunk_tab.p); fr(p->step_rows.p); fr(p->expand_buf.p);
   if (p->h_stage) cudaFreeHost(p->h_stage);
   for (cudaEvent_t ev : p->stage_ev)
     if (ev) cudaEventDestroy(ev);
@@ -415,6 +415,8 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind, const S
   int want_dtype = (a->mode != RELUX_ATTN_FAST) ? RELUX_DTYPE_F32 : a->q_dtype;
   // a GQA prompt goes to the tcgen05 prefill kernel, whose Q tile is a TMA load of bf16 rows
   if (kind == RELUX_POOL_GQA && a->mode == RELUX_ATTN_FAST && gqa_prompt_wants_bf16(p, *a)) want_dtype = RELUX_DTYPE_BF16;
+  // so does an MLA prompt (expanded keys / values + the same kernel)
+  if (kind == RELUX_POOL_MLA && a->mode == RELUX_ATTN_FAST && mla_prefill_eligible(p, sb, *a)) want_dtype = RELUX_DTYPE_BF16;
   const bool relayout_q = (a->q_layout == RELUX_LAYOUT_HEAD_MAJOR && S > 1) || want_dtype != a->q_dtype;
   if (relayout_q) {
     size_t need = (q_elems + qr_elems) * dtype_size(want_dtype);
@@ -494,10 +496,11 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind, const S
 }
 
 // Built-in defaults of the tuning knobs, then the environment (read here, once per pool, never on a launch path).
-static const int32_t kTuneDefault[RELUX_TUNE_COUNT] = {0, 0, 0, 0, 0, 256, 0, -1, -1, 0};
+static const int32_t kTuneDefault[RELUX_TUNE_COUNT] = {0, 0, 0, 0, 0, 256, 0, -1, -1, 0, 128, 16384};
 static const char* const kTuneEnv[RELUX_TUNE_COUNT] = {"RELUX_MLA_GENERIC", "RELUX_MLA_WORKERS", "RELUX_CHUNK_PAGES", "RELUX_GEMM_GENERIC",
                                                        "RELUX_GEMM_SPLIT", "RELUX_GQA_PROMPT_PARTIAL_MB", "RELUX_SEL_CLUSTER",
-                                                       "RELUX_SEL_LOOKAHEAD", "RELUX_SEL_BATCHED", "RELUX_GQA_PROMPT_SLICES"};
+                                                       "RELUX_SEL_LOOKAHEAD", "RELUX_SEL_BATCHED", "RELUX_GQA_PROMPT_SLICES",
+                                                       "RELUX_MLA_PROMPT_MIN_TOKENS", "RELUX_MLA_PROMPT_SCRATCH_MB"};
 void tuning_defaults(Tuning* t) {
   for (int i = 0; i < RELUX_TUNE_COUNT; i++) {
     t->v[i] = kTuneDefault[i];

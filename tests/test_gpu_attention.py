@@ -595,3 +595,74 @@ def test_step_falls_back_to_two_calls_where_the_fused_launch_does_not_apply(dev,
     for p in pools:
         p.destroy()
     wuk.free(); wuv.free()
+
+
+@pytest.mark.parametrize("S,cached,H", [(128, 0, 16), (129, 0, 16), (203, 0, 128), (300, 517, 16), (256, 64, 32), (1024, 0, 16)])
+def test_mla_prefill_kernel_prompts(dev, oracle, S, cached, H):
+    """MLA prompts on the expand + tcgen05 prefill pair: cached latents expanded to per-head keys / values (the
+    reference's order for seqQ > 1, mla.go:323-326), then 192-wide scores; odd and tile-aligned prompt lengths, on an empty
+    cache and after `cached` rows, sequences of different lengths, against the decompress-order restatement."""
+    rng = np.random.default_rng(500 + S + cached + H)
+    Dh, dC, dHR = 128, 512, 64
+    ctx = [cached + S, cached + S + 70, S] if cached else [S, S, S]
+    if S == 1024:
+        ctx = [S]
+    B = len(ctx)
+    pool, cl, rl = build_mla(dev, oracle, rng, ctx, dC, dHR)
+    wuk = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02)
+    wuv = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02)
+    d_wuk, d_wuv = dev.upload(wuk), dev.upload(wuv)
+    qc = oracle.bf16_from_f32(rng.standard_normal((B, S, H, Dh)).astype(np.float32))
+    qr = oracle.bf16_from_f32(rng.standard_normal((B, S, H, dHR)).astype(np.float32))
+    out = np.full((B, S, H, Dh), np.nan, np.float32)
+    scale = float(1.0 / np.sqrt(Dh + dHR))
+    n0 = dev.launch_count()
+    pool.decode(0, B, qc, out, H, Dh, scale, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv, q_tokens=S, causal=True)
+    assert dev.launch_count() - n0 == 3   # first rows of the sequences, expansion, attention: no absorb, no split-KV, no merge
+    with oracle.exact_exp():
+        ref = oracle.mla_attend(cl, rl, ctx, oracle.f32_from_bf16(qc), oracle.f32_from_bf16(qr), wuk, wuv, scale, causal=True, absorbed=False)
+    check_attention(out, ref, "mla prefill S=%d cached=%d H=%d" % (S, cached, H), max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+    assert pool.status() == 0
+    # the same call through the absorbed decode kernels (the knob turns the prompt path off): same numbers within tolerance
+    from relux_b200 import lib as L
+    if S <= 203:
+        pool.tune(L.TUNE_MLA_PROMPT_MIN_TOKENS, 1 << 30)
+        out2 = np.full((B, S, H, Dh), np.nan, np.float32)
+        pool.decode(0, B, qc, out2, H, Dh, scale, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv, q_tokens=S, causal=True)
+        check_attention(out2, ref, "mla prompt on the decode kernels", max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+    pool.destroy(); d_wuk.free(); d_wuv.free()
+
+
+def test_mla_prefill_float32_queries_unmasked_and_named_sequences(dev, oracle):
+    """float32 queries (converted on the device), no causal mask (every query row sees the whole cache), sequences
+    named in another order, and two layers (the second layer's pages start further down the pool)."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(611)
+    H, Dh, dC, dHR, S, P = 16, 128, 512, 64, 150, 64
+    ctx = [150, 421, 260]
+    B = len(ctx)
+    pages_per = (max(ctx) + P - 1) // P + 1
+    pool = rb.Pool(dev, L.POOL_MLA, 2, B * pages_per, P, B, pages_per, dC=dC, dHR=dHR)
+    pool.set_tables(permuted_tables(rng, B, pages_per))
+    c = rng.standard_normal((int(np.sum(ctx)), dC)).astype(np.float32)
+    r = rng.standard_normal((int(np.sum(ctx)), dHR)).astype(np.float32)
+    pool.append(0, rng.standard_normal(c.shape).astype(np.float32), r, B, n_new=np.asarray(ctx, np.int32))
+    pool.append(1, c, r, B, n_new=np.asarray(ctx, np.int32))
+    cl = ragged_to_padded(oracle.bf16_from_f32(c), ctx, (dC,))
+    rl = ragged_to_padded(oracle.bf16_from_f32(r), ctx, (dHR,))
+    wuk = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02)
+    wuv = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02)
+    d_wuk, d_wuv = dev.upload(wuk), dev.upload(wuv)
+    ids = np.array([2, 0, 1], np.int32)
+    qc = rng.standard_normal((B, S, H, Dh)).astype(np.float32)
+    qr = rng.standard_normal((B, S, H, dHR)).astype(np.float32)
+    out = np.full((B, S, H, Dh), np.nan, np.float32)
+    scale = float(1.0 / np.sqrt(Dh + dHR))
+    pool.decode(1, B, qc, out, H, Dh, scale, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv, q_tokens=S, causal=False, seq_ids=ids)
+    qcb, qrb = oracle.f32_from_bf16(oracle.bf16_from_f32(qc)), oracle.f32_from_bf16(oracle.bf16_from_f32(qr))
+    with oracle.exact_exp():
+        ref = oracle.mla_attend(cl[ids], rl[ids], [ctx[i] for i in ids], qcb, qrb, wuk, wuv, scale, causal=False, absorbed=False)
+    check_attention(out, ref, "mla prefill unmasked", max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+    assert pool.status() == 0
+    pool.destroy(); d_wuk.free(); d_wuv.free()
