@@ -54,6 +54,8 @@ WORKLOADS = {
     "gqa_prompt_b2_2k": dict(kind="prompt", pool="gqa", B=2, S=2048, H=32, Hkv=8, D=128),   # small case for profiler captures
     "gqa_prompt_b2_8k": dict(kind="prompt", pool="gqa", B=2, S=8192, H=32, Hkv=8, D=128),   # a long prompt: 32 tiles per block on average
     "mla_prompt_b4_1k": dict(kind="prompt", pool="mla", B=4, S=1024, H=128, Dh=128, dC=512, dHR=64),
+    "mla_prompt_b8_2k": dict(kind="prompt", pool="mla", B=8, S=2048, H=128, Dh=128, dC=512, dHR=64),
+    "mla_prompt_b2_8k": dict(kind="prompt", pool="mla", B=2, S=8192, H=128, Dh=128, dC=512, dHR=64),
     "gqa_layer_verify_b128_ctx8k": dict(kind="gqa", B=128, ctx=8192, H=32, Hkv=8, D=128, S=4, layer=True),
 }
 DEFAULT_WORKLOAD = "mla_decode_b64_ctx32k"
@@ -653,8 +655,10 @@ _CPU_INPUTS = {}   # inputs of the CPU legs, kept between steps of the reference
 def run_prompt(args, w, world, rank, local, dist):
     """Prompt processing: every step empties the sequences, appends the S prompt rows and runs one causal multi-token
     attention call over them (device-resident inputs).  GQA prompts run on the tcgen05 prefill kernel (128 query rows per
-    CTA); MLA prompts go through the decode kernel, one row of workers per query token.  The bound reported is the
-    tensor pipe (2 * 2 * S^2 / 2 * H * D flop per sequence for GQA, 2 * S^2 / 2 * H * (2 dC + dHR) for absorbed MLA)."""
+    CTA); MLA prompts expand the cached latents into per-head keys / values (one tcgen05 GEMM) and run the same kernel
+    with 192-wide scores.  The bound reported is the tensor pipe, for the attention kernel alone: 2 * S^2 / 2 * H * (Dqk +
+    Dv) flop per sequence (GQA 128 + 128, MLA 192 + 128); the MLA line also carries the expansion's flops
+    (2 * S * dC * 2 * H * 128 per sequence) and the time of the step outside the attention kernel."""
     import relux_b200 as rb
     from relux_b200 import lib as L
 
@@ -674,7 +678,8 @@ def run_prompt(args, w, world, rank, local, dist):
         wuv = dev.upload(bf16_bits(rng.standard_normal((dC, H * Dh), dtype=np.float32) * np.float32(0.02)))
         out = dev.alloc(B * S * H * Dh * 4, L.DTYPE_F32)
         scale = float(1.0 / np.sqrt(Dh + dHR))
-        flops = B * (S * (S + 1) / 2) * H * 2 * (2 * dC + dHR)
+        flops = B * (S * (S + 1) / 2) * H * 2 * (Dh + dHR + Dh)
+        expand_flops = B * S * 2.0 * dC * 2 * H * Dh
         kw = dict(q_rope=qr, w_uk=wuk, w_uv=wuv)
         head_dim = Dh
     else:
@@ -728,10 +733,16 @@ def run_prompt(args, w, world, rank, local, dist):
         "data": "synthetic",
         "config": workload_config(args.workload, w),
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
-                     "peak_source": "measured" if peaks else "fallback", "kernel": "mla_decode_sm100_kernel" if mla else "gqa_prefill_sm100_kernel",
+                     "peak_source": "measured" if peaks else "fallback", "kernel": "prefill_sm100_kernel<mla>" if mla else "prefill_sm100_kernel<gqa>",
                      "kernel_ms": kernel_ms, "launches_timed": counted, "algorithmic_flops_per_launch": flops},
         "e2e": None, "gpu_launches": launches, "clocks": clocks,
     }
+    if mla:
+        # everything of the step that is not the attention kernel: set_len, append, the expansion GEMM and its plan
+        rest_ms = ms / steps - kernel_ms
+        line["roofline"]["expansion"] = {"kernel": "mla_expand_sm100_kernel", "flops_per_launch": expand_flops,
+                                         "step_ms_outside_attention": rest_ms,
+                                         "whole_step_tflops": (flops + expand_flops) / (ms / steps * 1e-3) / 1e12}
     if rank == 0 and world == 1 and not args.skip_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_prompt(w)
     pool.destroy()

@@ -87,17 +87,21 @@ struct Plan {
 constexpr int kSplit = 2;                                     // threads per query row: each takes 128 / kSplit keys and output dims
 constexpr int kCols = 128 / kSplit;
 constexpr int kSoftmaxWarps = 4 * kSplit;
-constexpr int kSoftmaxThreads = 32 * kSoftmaxWarps, kThreads = kSoftmaxThreads + 64;
+constexpr int kEpiWarps = 4;                                  // read-out warps: one per TMEM lane quarter
+constexpr int kSoftmaxThreads = 32 * kSoftmaxWarps, kThreads = kSoftmaxThreads + 64 + 32 * kEpiWarps;
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kTmemS = 0, kTmemO = 256;
+constexpr uint32_t kTmemS = 0, kTmemO = 256;                  // S(g) at kTmemS + 128 (g & 1); O of item n at kTmemO + 128 (n & 1)
 constexpr float kRescaleThreshold = 8.0f;
+constexpr int kPolyPairsOf8 = 3;   // score pairs out of every eight whose exponential runs on the FMA pipe
 
 struct Bars {
   uint64_t q_full[2], q_empty[2], k_full[kMaxDepth], k_empty[kMaxDepth], v_full[kMaxDepth], v_empty[kMaxDepth], s_full[2], p_full, pv_done;
+  uint64_t o_full[2], o_empty[2], l_full, l_empty;
   uint32_t tmem_base;
   volatile int32_t abort_flag;
-  float rowmax[2][kSplit][128];   // [tile parity][key slice][row]; an item's epilogue borrows the buffer of the tile that follows
-                                  // for the row sums of the key slices
+  float rowmax[2][kSplit][128];   // [tile parity][key slice][row]; at the end of an item the buffer of the tile that follows
+                                  // carries the row sums of the key slices from one slice's thread to the other's
+  float lsum[128];                // an item's row sums, handed to the read-out warps
 };
 static_assert(sizeof(Bars) <= 3072, "barrier block too large");
 
@@ -140,7 +144,7 @@ __device__ __forceinline__ Item item_of(const PrefillParams& prm, int idx) {
   // keys the PAIR needs: all T without the mask, else up to the position of its last real token
   const int last_tok = min(prm.S, (2 * it.pair + 2) * prm.bq) - 1;
   const int kmax = prm.causal ? (it.T - prm.S + last_tok + 1) : it.T;
-  it.ntiles = (kmax + kTile - 1) / kTile;
+  it.ntiles = max(1, (kmax + kTile - 1) / kTile);
   it.last_slot = (it.T + kPage - 1) / kPage - 1;   // last page slot of the sequence that holds a row
   it.base = 0;
   if constexpr (kMla) it.base = __ldg(prm.seq_base + it.bi);
@@ -151,6 +155,78 @@ __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// ---- two float32 lanes per instruction (add / fma on a 64-bit register pair) ----
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+// 2^x for two arguments on the FMA pipe instead of the special-function unit (which delivers 16 exponentials per clock
+// and SM: 1024 clocks for the 128 x 128 scores of a tile, as long as the tile's MMAs).  x = n + f with n the nearest
+// integer (magic-number rounding) and f in [-1/2, 1/2]; 2^f by a cubic (relative error 7.5e-5, well inside the bf16
+// rounding of P); n goes into the exponent field.  x is clamped to [-126, ..): results stay normal numbers.
+__device__ __forceinline__ uint64_t ex2_poly2(uint64_t x2) {
+  float x0, x1;
+  unpack2(x2, x0, x1);
+  x2 = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+  const uint64_t magic = pack2(12582912.f, 12582912.f), neg_magic = pack2(-12582912.f, -12582912.f), neg_one = pack2(-1.f, -1.f);
+  const uint64_t t2 = add2(x2, magic);            // low mantissa bits = n (two's complement)
+  const uint64_t n2 = add2(t2, neg_magic);
+  const uint64_t f2 = fma2(n2, neg_one, x2);
+  uint64_t p2 = fma2(pack2(0.0551716648f, 0.0551716648f), f2, pack2(0.2426111251f, 0.2426111251f));
+  p2 = fma2(p2, f2, pack2(0.6932609677f, 0.6932609677f));
+  p2 = fma2(p2, f2, pack2(0.9999280572f, 0.9999280572f));
+  float t0, t1, p0, p1;
+  unpack2(t2, t0, t1);
+  unpack2(p2, p0, p1);
+  p0 = __int_as_float(__float_as_int(p0) + (__float_as_int(t0) << 23));
+  p1 = __int_as_float(__float_as_int(p1) + (__float_as_int(t1) << 23));
+  return pack2(p0, p1);
+}
+
+// exp2(score * scale - max) for this thread's kCols scores of one row: bf16 P values into the swizzled shared row
+// (16-byte chunk index chunk0 + ..., XOR row & 7), returns the two partial row sums.
+template <bool kPoly>
+__device__ __forceinline__ uint64_t exp_rows(const uint32_t (&sv)[kCols], uint64_t scale2, uint64_t neg_m2, uint8_t* pbuf, int chunk0, int r) {
+  uint64_t ps2 = pack2(0.f, 0.f);
+#pragma unroll
+  for (int q2 = 0; q2 < kCols / 32; q2++) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int c = 0; c < 32; c += 2) {
+      const uint64_t x2 = fma2(pack2(__uint_as_float(sv[q2 * 32 + c]), __uint_as_float(sv[q2 * 32 + c + 1])), scale2, neg_m2);
+      uint64_t p2;
+      if (kPoly && ((c >> 1) & 7) < kPolyPairsOf8) {
+        p2 = ex2_poly2(x2);
+      } else {
+        float x0, x1;
+        unpack2(x2, x0, x1);
+        p2 = pack2(ex2_approx(x0), ex2_approx(x1));
+      }
+      ps2 = add2(ps2, p2);
+      float p0, p1;
+      unpack2(p2, p0, p1);
+      __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+      pk[c >> 1] = *reinterpret_cast<uint32_t*>(&b2);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; c++)
+      *reinterpret_cast<uint4*>(pbuf + (((chunk0 + q2 * 4 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
+  }
+  return ps2;
 }
 
 __device__ __noinline__ void wait_slow(uint64_t* bar, uint32_t parity, Bars* b, int32_t* status) {
@@ -208,6 +284,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     mbar_init(&bars->s_full[1], 1);
     mbar_init(&bars->p_full, 2 * kSoftmaxWarps);   // one arrival per softmax warp of each CTA of the pair
     mbar_init(&bars->pv_done, 1);
+    for (int s = 0; s < 2; s++) {
+      mbar_init(&bars->o_full[s], 1);
+      mbar_init(&bars->o_empty[s], 2 * kEpiWarps);   // the read-out warps of both CTAs (leader's copy is the one waited on)
+    }
+    mbar_init(&bars->l_full, kSoftmaxWarps / kSplit);
+    mbar_init(&bars->l_empty, kEpiWarps);
     bars->abort_flag = 0;
     fence_mbar_init();
   }
@@ -342,8 +424,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         }
         __syncwarp();
       };
-      auto issue_pv = [&](int g, bool first) {
+      // PV of tile g of item n; `first`: the item's first tile (O is overwritten: the read-out of item n - 2 must have left
+      // the buffer); `last`: its last tile, after which the read-out warps take the buffer
+      auto issue_pv = [&](int g, int n, bool first, bool last) {
         const int st = g % kDepthV;
+        if (first && n >= 2) wait_bar(&bars->o_empty[n & 1], ((n >> 1) - 1) & 1, bars, prm.status);
         wait_bar(&bars->p_full, g & 1, bars, prm.status);
         wait_bar(&bars->v_full[st], (g / kDepthV) & 1, bars, prm.status);
         tc_fence_after();   // P rows, a possible O rescale and the previous item's O read-out were done by the softmax warps of both CTAs
@@ -353,10 +438,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int ks = 0; ks < 8; ks++) {
             const uint32_t aoff = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
-            umma_ss<2>(tmem + kTmemO, dPg + aoff, dV + ((uint32_t)(ks * 2048) >> 4), idesc_pv, !first || ks != 0);
+            umma_ss<2>(tmem + kTmemO + (n & 1) * 128, dPg + aoff, dV + ((uint32_t)(ks * 2048) >> 4), idesc_pv, !first || ks != 0);
           }
           umma_commit_mc<2>(&bars->v_empty[st], 0x3);
           umma_commit_mc<2>(&bars->pv_done, 0x3);
+          if (last) umma_commit_mc<2>(&bars->o_full[n & 1], 0x3);
         }
         __syncwarp();
       };
@@ -369,37 +455,36 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         for (int i = 0; i < ntiles; i++, g++) {
           if (i + 1 < ntiles) {
             issue_qk(g + 1, n, false, i + 2 == ntiles);
-            issue_pv(g, i == 0);
+            issue_pv(g, n, i == 0, false);
           } else if (has_next && kQBufs > 1) {
             issue_qk(g + 1, n + 1, true, next_tiles == 1);
-            issue_pv(g, i == 0);
+            issue_pv(g, n, i == 0, true);
           } else {
             // one Q buffer: the next item's Q is requested when this item's last QK^T has completed, so its first QK^T
             // goes behind this item's last PV instead of waiting for the load in front of it
-            issue_pv(g, i == 0);
+            issue_pv(g, n, i == 0, true);
             if (has_next) issue_qk(g + 1, n + 1, true, next_tiles == 1);
           }
         }
         ntiles = next_tiles;
       }
     }
-  } else {
-    // =============================== softmax / correction / epilogue ===============================
+  } else if (warp < kSoftmaxWarps) {
+    // =============================== softmax / correction ===============================
     // Warp w reads TMEM lanes 32 (w & 3) .. +31 (the hardware's rule); the kSplit warps that share a lane quarter take
     // one slice of kCols keys (and output dims) each.
     const int wq = warp & 3, hb = warp >> 2;
     const int r = wq * 32 + lane;                   // TMEM lane = query row
-    const int tq = r / prm.g, hq = r % prm.g;       // token in block, head in group
+    const int tq = r / prm.g;                       // token in block
     const uint32_t lane_addr = ((uint32_t)(wq * 32) << 16) + (uint32_t)(hb * kCols);
     const uint32_t p_full_lead = mapa_u32(smem_u32(&bars->p_full), 0);
-    int g = 0;
-    for (int idx = worker; idx < prm.n_items; idx += n_workers) {
+    int g = 0, n = 0;
+    for (int idx = worker; idx < prm.n_items; idx += n_workers, n++) {
       const Item it = item_of<kMla>(prm, idx);
       const int t0 = (2 * it.pair + (int)rank) * prm.bq;          // first query token of this CTA's block
-      const int ntok = max(0, min(prm.bq, prm.S - t0));           // its real tokens (0: the odd block of the last pair)
-      const bool real = tq < ntok;
       // keys [0, t_eff) are visible to this row
       const int t_eff = prm.causal ? min(it.T, it.T - prm.S + t0 + tq + 1) : it.T;
+      const uint32_t tmem_o = tmem + lane_addr + kTmemO + (n & 1) * 128;
       float m_used = -INFINITY, l_run = 0.f;
       for (int j = 0; j < it.ntiles; j++, g++) {
         wait_bar(&bars->s_full[g & 1], (g >> 1) & 1, bars, prm.status);
@@ -436,29 +521,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           m_used = mx;
         }
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-        float ps[2] = {0.f, 0.f};
-        // P(g) goes to buffer g & 1, which PV(g-2) has finished reading (QK(g) was issued after it).  32 keys at a time: one
-        // FFMA + one MUFU.EX2 per score, packed to bf16, four 16-byte stores into the swizzled row of this slice's 64-key half.
-        uint8_t* pbuf = smem + kSmemP + (g & 1) * kPBytes + r * 128;
-#pragma unroll
-        for (int q2 = 0; q2 < kCols / 32; q2++) {
-          uint32_t pk[16];
-#pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            const float p0 = ex2_approx(fmaf(__uint_as_float(sv[q2 * 32 + c]), prm.scale_log2, neg_m));
-            const float p1 = ex2_approx(fmaf(__uint_as_float(sv[q2 * 32 + c + 1]), prm.scale_log2, neg_m));
-            ps[0] += p0;
-            ps[1] += p1;
-            __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
-            pk[c >> 1] = *reinterpret_cast<uint32_t*>(&b2);
-          }
-          const int key0 = hb * kCols + q2 * 32;   // first key of these 32 inside the tile
-          uint8_t* prow = pbuf + (key0 >> 6) * kHalf;
-#pragma unroll
-          for (int c = 0; c < 4; c++)
-            *reinterpret_cast<uint4*>(prow + (((((key0 & 63) >> 3) + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-        }
-        l_run = l_run * alpha + (ps[0] + ps[1]);
+        const uint64_t scale2 = pack2(prm.scale_log2, prm.scale_log2), neg_m2 = pack2(neg_m, neg_m);
+        // Three pairs of eight take the polynomial; a thread with a masked key in its slice (the diagonal tiles only)
+        // keeps to the exact-zero path of ex2(-inf).
+        // P(g) goes to buffer g & 1, which PV(g-2) has finished reading (QK(g) was issued after it).  32 keys at a time,
+        // packed to bf16, four 16-byte stores into the swizzled row of this slice's 64-key half.  kPolyPairsOf8 pairs of
+        // every eight take the polynomial; a thread with a masked key in its slice (the diagonal tiles only) keeps to
+        // ex2(-inf) = 0 exactly.
+        uint8_t* pbuf = smem + kSmemP + (g & 1) * kPBytes + r * 128 + ((hb * kCols) >> 6) * kHalf;
+        const int chunk0 = ((hb * kCols) & 63) >> 3;   // first 16-byte chunk of this slice inside its 64-key half
+        uint64_t ps2;
+        if (nvalid == kCols) ps2 = exp_rows<true>(sv, scale2, neg_m2, pbuf, chunk0, r);
+        else ps2 = exp_rows<false>(sv, scale2, neg_m2, pbuf, chunk0, r);
+        float ps0, ps1;
+        unpack2(ps2, ps0, ps1);
+        l_run = l_run * alpha + (ps0 + ps1);
         // O may be rescaled only after PV(g-1) has completed
         if (j > 0) wait_bar(&bars->pv_done, (g - 1) & 1, bars, prm.status);
         __syncwarp();
@@ -470,11 +547,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 #pragma unroll 1
           for (int c = 0; c < kCols; c += 32) {
             uint32_t ov[32];
-            tmem_ld_32x32b_x32(tmem + lane_addr + kTmemO + c, ov);
+            tmem_ld_32x32b_x32(tmem_o + c, ov);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * a_row);
-            tmem_st_32x32b_x32(tmem + lane_addr + kTmemO + c, ov);
+            tmem_st_32x32b_x32(tmem_o + c, ov);
           }
           tmem_st_wait();
         }
@@ -483,35 +560,53 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(p_full_lead);
       }
-      // ---- item epilogue: O / l -> out ----
-      if (it.ntiles > 0) {
-        wait_bar(&bars->pv_done, (g - 1) & 1, bars, prm.status);
-        __syncwarp();
-        tc_fence_after();
-      }
-      // the row sum is the sum of its key slices (exchanged through the row-maximum buffer of the tile that follows, which
-      // nobody touches before the barrier at the end of this epilogue)
-      float(*lsum)[128] = bars->rowmax[g & 1];
-      lsum[hb][r] = l_run;
+      // ---- end of the item: the row sum (the sum of its key slices) goes to the read-out warps ----
+      // The slices meet in the row-maximum buffer of the tile that follows; nobody writes it before the second barrier.
+      float(*lx)[128] = bars->rowmax[g & 1];
+      lx[hb][r] = l_run;
       asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
-      l_run = 0.f;
+      if (hb == 0) {
+        float l = 0.f;
 #pragma unroll
-      for (int k = 0; k < kSplit; k++) l_run += lsum[k][r];
-      // warp-uniform: the TMEM loads below are warp-collective
-      const bool ok = it.ntiles > 0 && !__any_sync(0xffffffffu, bars->abort_flag != 0);
-      const float inv = (ok && l_run > 0.f) ? 1.f / l_run : 0.f;
-      float* orow = prm.out + (((size_t)it.bi * prm.S + t0 + (real ? tq : 0)) * prm.H + (size_t)it.hk * prm.g + hq) * kD + hb * kCols;
+        for (int k = 0; k < kSplit; k++) l += lx[k][r];
+        if (n > 0) wait_bar(&bars->l_empty, (n - 1) & 1, bars, prm.status);   // the read-out of the previous item has taken its sums
+        bars->lsum[r] = l;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->l_full);
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+    }
+  } else {
+    // =============================== read-out: O / l -> out ===============================
+    // One warp per TMEM lane quarter; item n's accumulator is O buffer n & 1, handed over by the commit behind the
+    // item's last PV and handed back (to the first PV of item n + 2) when the row has been read.
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;
+    const int tq = r / prm.g, hq = r % prm.g;       // token in block, head in group
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    const uint32_t o_empty_lead[2] = {mapa_u32(smem_u32(&bars->o_empty[0]), 0), mapa_u32(smem_u32(&bars->o_empty[1]), 0)};
+    int n = 0;
+    for (int idx = worker; idx < prm.n_items; idx += n_workers, n++) {
+      const Item it = item_of<kMla>(prm, idx);
+      const int t0 = (2 * it.pair + (int)rank) * prm.bq;          // first query token of this CTA's block
+      const int ntok = max(0, min(prm.bq, prm.S - t0));           // its real tokens (0: the odd block of the last pair)
+      const bool real = tq < ntok;                                 // rows past the prompt's last token are padding: computed, never written
+      wait_bar(&bars->l_full, n & 1, bars, prm.status);
+      const float l_row = bars->lsum[r];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->l_empty);
+      wait_bar(&bars->o_full[n & 1], (n >> 1) & 1, bars, prm.status);
+      __syncwarp();   // the TMEM loads below are warp-collective
+      tc_fence_after();
+      const bool ok = !__any_sync(0xffffffffu, bars->abort_flag != 0);
+      const float inv = (ok && l_row > 0.f) ? 1.f / l_row : 0.f;
+      float* orow = prm.out + (((size_t)it.bi * prm.S + t0 + (real ? tq : 0)) * prm.H + (size_t)it.hk * prm.g + hq) * kD;
 #pragma unroll 1
-      for (int c = 0; c < kCols; c += 32) {
+      for (int c = 0; c < kD; c += 32) {
         uint32_t ov[32];
-        if (ok) {
-          tmem_ld_32x32b_x32(tmem + lane_addr + kTmemO + c, ov);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i++) ov[i] = 0u;
-        }
-        if (real) {   // rows past the prompt's last token are padding: computed, never written
+        tmem_ld_32x32b_x32(tmem + lane_addr + kTmemO + (n & 1) * 128 + c, ov);
+        tmem_ld_wait();
+        if (real) {
           float4* dst = reinterpret_cast<float4*>(orow + c);
 #pragma unroll
           for (int i = 0; i < 8; i++)
@@ -519,10 +614,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                                  __uint_as_float(ov[4 * i + 3]) * inv);
         }
       }
-      // the O read-out is ordered before this thread's next p_full arrival, which releases the first PV of the next
-      // item; the row sums are read by every thread before the barrier of the next tile's row maxima
       tc_fence_before();
-      asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster((n & 1) ? o_empty_lead[1] : o_empty_lead[0]);
     }
   }
   __syncwarp();
