@@ -54,6 +54,7 @@ WORKLOADS = {
     "gqa_prompt_b2_2k": dict(kind="prompt", pool="gqa", B=2, S=2048, H=32, Hkv=8, D=128),   # small case for profiler captures
     "gqa_prompt_b2_8k": dict(kind="prompt", pool="gqa", B=2, S=8192, H=32, Hkv=8, D=128),   # a long prompt: 32 tiles per block on average
     "mla_prompt_b4_1k": dict(kind="prompt", pool="mla", B=4, S=1024, H=128, Dh=128, dC=512, dHR=64),
+    "mla_prompt_b1_2k": dict(kind="prompt", pool="mla", B=1, S=2048, H=128, Dh=128, dC=512, dHR=64),   # small case for profiler captures
     "mla_prompt_b8_2k": dict(kind="prompt", pool="mla", B=8, S=2048, H=128, Dh=128, dC=512, dHR=64),
     "mla_prompt_b2_8k": dict(kind="prompt", pool="mla", B=2, S=8192, H=128, Dh=128, dC=512, dHR=64),
     "gqa_layer_verify_b128_ctx8k": dict(kind="gqa", B=128, ctx=8192, H=32, Hkv=8, D=128, S=4, layer=True),

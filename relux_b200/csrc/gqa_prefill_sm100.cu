@@ -114,6 +114,7 @@ struct PrefillParams {
   int32_t bq;                 // query tokens per block = 128 / g
   int32_t n_qblocks, n_pairs; // blocks and block pairs per (sequence, kv head)
   int32_t n_seqs, n_items;    // items = n_pairs * Hkv * n_seqs
+  int32_t n_half, n_couples;  // couples per (sequence, kv head) = ceil(n_pairs / 2), and in all
   int32_t krow0, vrow0;       // first TMA row of this layer's K block / V block (MLA: of the expanded keys / values)
   // MLA only: expanded rows are dense, row = head * Ttot + seq_base[sequence] + token; the RoPE part of a key is read from
   // the pool's pages (block rope_block of blocks_per_page 64-column blocks per page, first row of the layer pool_row0)
@@ -125,20 +126,33 @@ struct PrefillParams {
   int32_t* status;
 };
 
-// One item as every warp of the pair derives it from its index: the list runs over block pairs from the last (most
-// keys under the causal mask) to the first, and inside a pair index over (sequence, kv head).
+// The order of the work.  Under the causal mask block pair p of a stream (a sequence's kv head) needs 2 (p + 1) key tiles:
+// pairs p and n_pairs - 1 - p together always need the same number, so the unit handed to a worker is that COUPLE, the
+// long member first.  Couples are numbered stream by stream and worker w takes couples w, w + W, ...: every worker gets
+// the same amount of work, and the workers that run at the same time read the keys and values of a few streams only,
+// which then come out of L2 (with 128 heads and long prompts the streams of one call are far larger than L2 together).
+struct Cursor {
+  int32_t c, m;   // couple, member (0: pair n_pairs - 1 - k, 1: pair k, for couple k of its stream)
+};
+__device__ __forceinline__ bool cursor_valid(const PrefillParams& prm, Cursor u) { return u.c < prm.n_couples; }
+__device__ __forceinline__ Cursor cursor_next(const PrefillParams& prm, Cursor u, int n_workers) {
+  const int k = u.c % prm.n_half;
+  if (u.m == 0 && prm.n_pairs - 1 - k != k) return Cursor{u.c, 1};
+  return Cursor{u.c + n_workers, 0};
+}
+
+// One item as every warp of the pair derives it from the cursor.
 struct Item {
   int32_t bi, seq, hk, pair;
   int32_t T, ntiles, last_slot, base;
 };
 template <bool kMla>
-__device__ __forceinline__ Item item_of(const PrefillParams& prm, int idx) {
+__device__ __forceinline__ Item item_of(const PrefillParams& prm, Cursor u) {
   Item it;
-  const int per = prm.Hkv * prm.n_seqs;
-  it.pair = prm.n_pairs - 1 - idx / per;
-  const int rem = idx % per;
-  it.hk = rem % prm.Hkv;
-  it.bi = rem / prm.Hkv;
+  const int stream = u.c / prm.n_half, k = u.c % prm.n_half;
+  it.pair = u.m ? k : prm.n_pairs - 1 - k;
+  it.hk = stream % prm.Hkv;
+  it.bi = stream / prm.Hkv;
   it.seq = prm.seq_ids ? __ldg(prm.seq_ids + it.bi) : it.bi;
   it.T = __ldg(prm.len + it.seq) + prm.extra;
   // keys the PAIR needs: all T without the mask, else up to the position of its last real token
@@ -266,7 +280,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const int worker = blockIdx.x >> 1, n_workers = gridDim.x >> 1;
-  if (worker >= prm.n_items) return;   // both CTAs of the pair leave before any pair-wide step
+  if (worker >= prm.n_couples) return;   // both CTAs of the pair leave before any pair-wide step
 
   if ((smem_u32(smem) & 1023u) != 0) {   // the swizzled layouts need a 1024-byte aligned base (same in both CTAs of the pair)
     if (threadIdx.x == 0) set_status(prm.status, RELUX_ERR_UNSUPPORTED);
@@ -331,9 +345,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       __syncwarp();
     };
     int g = 0, n = 0;
-    Item cur = item_of<kMla>(prm, worker);
+    Cursor cu{worker, 0};
+    Item cur = item_of<kMla>(prm, cu);
     load_q(cur, 0);
-    for (int idx = worker; idx < prm.n_items; idx += n_workers, n++) {
+    for (; cursor_valid(prm, cu); n++) {
       for (int j = 0; j < cur.ntiles; j++, g++) {
         // rows of the tile's two 64-key halves in tmap_kv (relative to krow0 / vrow0), and for MLA the pool row of the
         // RoPE block of this CTA's half
@@ -387,8 +402,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           __syncwarp();
         }
       }
-      if (idx + n_workers < prm.n_items) {   // the next item's Q, while this item's last tiles are still in flight
-        cur = item_of<kMla>(prm, idx + n_workers);
+      cu = cursor_next(prm, cu, n_workers);
+      if (cursor_valid(prm, cu)) {   // the next item's Q, while this item's last tiles are still in flight
+        cur = item_of<kMla>(prm, cu);
         load_q(cur, n + 1);
       }
     }
@@ -447,11 +463,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         __syncwarp();
       };
       int g = 0, n = 0;
-      int ntiles = item_of<kMla>(prm, worker).ntiles;
+      Cursor cu{worker, 0};
+      int ntiles = item_of<kMla>(prm, cu).ntiles;
       issue_qk(0, 0, true, ntiles == 1);
-      for (int idx = worker; idx < prm.n_items; idx += n_workers, n++) {
-        const bool has_next = idx + n_workers < prm.n_items;
-        const int next_tiles = has_next ? item_of<kMla>(prm, idx + n_workers).ntiles : 0;
+      for (; cursor_valid(prm, cu); n++) {
+        cu = cursor_next(prm, cu, n_workers);
+        const bool has_next = cursor_valid(prm, cu);
+        const int next_tiles = has_next ? item_of<kMla>(prm, cu).ntiles : 0;
         for (int i = 0; i < ntiles; i++, g++) {
           if (i + 1 < ntiles) {
             issue_qk(g + 1, n, false, i + 2 == ntiles);
@@ -479,8 +497,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     const uint32_t lane_addr = ((uint32_t)(wq * 32) << 16) + (uint32_t)(hb * kCols);
     const uint32_t p_full_lead = mapa_u32(smem_u32(&bars->p_full), 0);
     int g = 0, n = 0;
-    for (int idx = worker; idx < prm.n_items; idx += n_workers, n++) {
-      const Item it = item_of<kMla>(prm, idx);
+    for (Cursor cu{worker, 0}; cursor_valid(prm, cu); cu = cursor_next(prm, cu, n_workers), n++) {
+      const Item it = item_of<kMla>(prm, cu);
       const int t0 = (2 * it.pair + (int)rank) * prm.bq;          // first query token of this CTA's block
       // keys [0, t_eff) are visible to this row
       const int t_eff = prm.causal ? min(it.T, it.T - prm.S + t0 + tq + 1) : it.T;
@@ -586,8 +604,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
     const uint32_t o_empty_lead[2] = {mapa_u32(smem_u32(&bars->o_empty[0]), 0), mapa_u32(smem_u32(&bars->o_empty[1]), 0)};
     int n = 0;
-    for (int idx = worker; idx < prm.n_items; idx += n_workers, n++) {
-      const Item it = item_of<kMla>(prm, idx);
+    for (Cursor cu{worker, 0}; cursor_valid(prm, cu); cu = cursor_next(prm, cu, n_workers), n++) {
+      const Item it = item_of<kMla>(prm, cu);
       const int t0 = (2 * it.pair + (int)rank) * prm.bq;          // first query token of this CTA's block
       const int ntok = max(0, min(prm.bq, prm.S - t0));           // its real tokens (0: the odd block of the last pair)
       const bool real = tq < ntok;                                 // rows past the prompt's last token are padding: computed, never written
@@ -717,6 +735,8 @@ int32_t launch_gqa_prefill_sm100(Pool* p, const SeqBatch& sb, const relux_attn_a
   const int64_t items = (int64_t)k.n_pairs * prm.gqa_num_kv_heads * sb.n_seqs;
   if (items > ((int64_t)1 << 30)) { set_error("prompt too long for one prefill launch"); return RELUX_ERR_UNSUPPORTED; }
   k.n_items = (int32_t)items;
+  k.n_half = (k.n_pairs + 1) / 2;
+  k.n_couples = k.n_half * prm.gqa_num_kv_heads * sb.n_seqs;
   const int64_t rows_per_block = (int64_t)prm.num_pages * prm.gqa_num_kv_heads * kPage;
   k.krow0 = (int32_t)((int64_t)a.layer * 2 * rows_per_block);
   k.vrow0 = (int32_t)((int64_t)a.layer * 2 * rows_per_block + rows_per_block);
@@ -724,7 +744,7 @@ int32_t launch_gqa_prefill_sm100(Pool* p, const SeqBatch& sb, const relux_attn_a
   k.out = d_out;
   k.status = p->d_status;
   cudaStream_t st = p->dev->stream;
-  const int workers = (int)std::min<int64_t>(prefill_workers<false>(p), items);
+  const int workers = std::min(prefill_workers<false>(p), k.n_couples);
   constexpr int kSmemTotal = Plan<false>::kSmemTotal;
   RELUX_CUDA_TRY(cudaFuncSetAttribute(prefill_sm100_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
   dim3 grid(2 * workers, 1, 1);   // CTA pairs
@@ -821,6 +841,8 @@ int32_t launch_mla_prefill_sm100(Pool* p, const SeqBatch& sb, const relux_attn_a
   const int64_t items = (int64_t)k.n_pairs * H * sb.n_seqs;
   if (items > ((int64_t)1 << 30)) { set_error("prompt too long for one prefill launch"); return RELUX_ERR_UNSUPPORTED; }
   k.n_items = (int32_t)items;
+  k.n_half = (k.n_pairs + 1) / 2;
+  k.n_couples = k.n_half * H * sb.n_seqs;
   k.krow0 = 0;
   k.vrow0 = (int32_t)((int64_t)H * Ttot);
   k.seq_base = seq_base;
@@ -832,7 +854,7 @@ int32_t launch_mla_prefill_sm100(Pool* p, const SeqBatch& sb, const relux_attn_a
   k.out = d_out;
   k.status = p->d_status;
   cudaStream_t st = p->dev->stream;
-  const int workers = (int)std::min<int64_t>(prefill_workers<true>(p), items);
+  const int workers = std::min(prefill_workers<true>(p), k.n_couples);
   constexpr int kSmemTotal = Plan<true>::kSmemTotal;
   RELUX_CUDA_TRY(cudaFuncSetAttribute(prefill_sm100_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
   dim3 grid(2 * workers, 1, 1);   // CTA pairs
