@@ -58,27 +58,27 @@ namespace {
 constexpr int kD = 128, kPage = 64, kTile = 128;
 constexpr int kBlk = 8192;                 // one [64 rows x 64 cols] bf16 box, 128-byte swizzled
 constexpr int kHalf = 2 * kBlk;            // [128 rows x 64 cols]
-constexpr int kPBytes = 2 * kHalf;         // one P tile: [keys 0-63 | keys 64-127], each 128 rows x 128 B
 constexpr int kVBytes = 2 * kBlk;          // V stage, 16 KB per CTA: own 64 output dims of [keys 0-63 | keys 64-127]
-constexpr int kMaxDepth = 3;
+constexpr int kMaxDepth = 4;
 
 // Shared-memory plan of the two variants.
 //   GQA (kMla = false): score width 128.  Q tile [dims 0-63 | dims 64-127] x 2 buffers (items in turn), K stage = own
-//     page [dims 0-63 | dims 64-127] (16 KB), three K and three V stages: 64 + 64 + 48 + 48 = 224 KB.
+//     page [dims 0-63 | dims 64-127] (16 KB), four K and four V stages: 64 + 64 + 64 = 192 KB.
 //   MLA (kMla = true): score width 192 = 128 expanded key dims + 64 shared RoPE dims.  Q tile [nope 0-63 | nope 64-127 |
-//     rope] (48 KB) in ONE buffer, K stage = own 64 keys [nope 0-63 | nope 64-127 | rope] (24 KB), three K and two V
-//     stages: 48 + 64 + 72 + 32 = 216 KB.
+//     rope] (48 KB) x 2 buffers, K stage = own 64 keys [nope 0-63 | nope 64-127 | rope] (24 KB), four K and three V
+//     stages: 96 + 96 + 48 = 240 KB is too much: three K and three V stages, 96 + 72 + 48 = 216 KB.
+// P never touches shared memory: the softmax warps write it, packed to bf16, over the first 64 columns of the S tile they
+// have just read, and PV takes its A operand from tensor memory.
 template <bool kMla>
 struct Plan {
   static constexpr int kQHalves = kMla ? 3 : 2;
   static constexpr int kQBytes = kQHalves * kHalf;
-  static constexpr int kQBufs = kMla ? 1 : 2;
+  static constexpr int kQBufs = 2;
   static constexpr int kKBytes = (kMla ? 3 : 2) * kBlk;
-  static constexpr int kDepthK = 3, kDepthV = kMla ? 2 : 3;
+  static constexpr int kDepthK = kMla ? 3 : 4, kDepthV = kMla ? 3 : 4;
   static constexpr int kKSteps = kMla ? 12 : 8;            // K = 16 slices of the score contraction
   static constexpr int kSmemQ = 0;
-  static constexpr int kSmemP = kSmemQ + kQBufs * kQBytes;  // two P tiles (tiles in turn)
-  static constexpr int kSmemK = kSmemP + 2 * kPBytes;
+  static constexpr int kSmemK = kSmemQ + kQBufs * kQBytes;
   static constexpr int kSmemV = kSmemK + kDepthK * kKBytes;
   static constexpr int kSmemBar = kSmemV + kDepthV * kVBytes;
   static constexpr int kSmemTotal = kSmemBar + 3072;
@@ -211,14 +211,16 @@ __device__ __forceinline__ uint64_t ex2_poly2(uint64_t x2) {
   return pack2(p0, p1);
 }
 
-// exp2(score * scale - max) for this thread's kCols scores of one row: bf16 P values into the swizzled shared row
-// (16-byte chunk index chunk0 + ..., XOR row & 7), returns the two partial row sums.
+// exp2(score * scale - max) for this thread's kCols scores of one row: bf16 P values, two per 32-bit word in key order,
+// into pw; returns the two partial row sums.  (The caller stores pw to tensor memory: that store is warp-collective and
+// this function is called under a per-row condition.)
 template <bool kPoly>
-__device__ __forceinline__ uint64_t exp_rows(const uint32_t (&sv)[kCols], uint64_t scale2, uint64_t neg_m2, uint8_t* pbuf, int chunk0, int r) {
+__device__ __forceinline__ uint64_t exp_rows(const uint32_t (&sv)[kCols], uint64_t scale2, uint64_t neg_m2, uint32_t (&pw)[kCols / 2]) {
+  static_assert(kCols == 64, "one 32-column store per thread");
   uint64_t ps2 = pack2(0.f, 0.f);
 #pragma unroll
   for (int q2 = 0; q2 < kCols / 32; q2++) {
-    uint32_t pk[16];
+    uint32_t* pk = pw + 16 * q2;
 #pragma unroll
     for (int c = 0; c < 32; c += 2) {
       const uint64_t x2 = fma2(pack2(__uint_as_float(sv[q2 * 32 + c]), __uint_as_float(sv[q2 * 32 + c + 1])), scale2, neg_m2);
@@ -236,9 +238,6 @@ __device__ __forceinline__ uint64_t exp_rows(const uint32_t (&sv)[kCols], uint64
       __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
       pk[c >> 1] = *reinterpret_cast<uint32_t*>(&b2);
     }
-#pragma unroll
-    for (int c = 0; c < 4; c++)
-      *reinterpret_cast<uint4*>(pbuf + (((chunk0 + q2 * 4 + c) ^ (r & 7)) << 4)) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
   }
   return ps2;
 }
@@ -274,7 +273,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                          const __grid_constant__ CUtensorMap tmap_qr, const __grid_constant__ CUtensorMap tmap_rope, const PrefillParams prm) {
   using PL = Plan<kMla>;
   constexpr int kQBytes = PL::kQBytes, kQBufs = PL::kQBufs, kKBytes = PL::kKBytes, kDepthK = PL::kDepthK, kDepthV = PL::kDepthV;
-  constexpr int kSmemQ = PL::kSmemQ, kSmemP = PL::kSmemP, kSmemK = PL::kSmemK, kSmemV = PL::kSmemV;
+  constexpr int kSmemQ = PL::kSmemQ, kSmemK = PL::kSmemK, kSmemV = PL::kSmemV;
   extern __shared__ __align__(1024) uint8_t smem[];
   Bars* bars = reinterpret_cast<Bars*>(smem + PL::kSmemBar);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -415,7 +414,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       const uint32_t idesc_qk = make_idesc_bf16(256, 128, false, false);
       const uint32_t idesc_pv = make_idesc_bf16(256, 128, false, true);
       const uint64_t dQ = make_desc_kmajor_sw128(smem_u32(smem + kSmemQ));
-      const uint64_t dP = make_desc_kmajor_sw128(smem_u32(smem + kSmemP));
       // QK^T of tile g (worker-wide index) of item n; `first`: the item's first tile (its Q must have landed);
       // `last`: its last tile, after which the Q buffer is free
       auto issue_qk = [&](int g, int n, bool first, bool last) {
@@ -450,12 +448,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         tc_fence_after();   // P rows, a possible O rescale and the previous item's O read-out were done by the softmax warps of both CTAs
         if (el) {
           const uint64_t dV = make_desc_mnmajor_sw128(smem_u32(smem + kSmemV + st * kVBytes), kBlk);
-          const uint64_t dPg = dP + ((uint32_t)((g & 1) * kPBytes) >> 4);
+          const uint32_t tP = tmem + kTmemS + (g & 1) * 128;   // P(g) lies over the first 64 columns of S(g)
 #pragma unroll
-          for (int ks = 0; ks < 8; ks++) {
-            const uint32_t aoff = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 32) >> 4;
-            umma_ss<2>(tmem + kTmemO + (n & 1) * 128, dPg + aoff, dV + ((uint32_t)(ks * 2048) >> 4), idesc_pv, !first || ks != 0);
-          }
+          for (int ks = 0; ks < 8; ks++)
+            umma_ts<2>(tmem + kTmemO + (n & 1) * 128, tP + ks * 8, dV + ((uint32_t)(ks * 2048) >> 4), idesc_pv, !first || ks != 0);
           umma_commit_mc<2>(&bars->v_empty[st], 0x3);
           umma_commit_mc<2>(&bars->pv_done, 0x3);
           if (last) umma_commit_mc<2>(&bars->o_full[n & 1], 0x3);
@@ -540,17 +536,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         }
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
         const uint64_t scale2 = pack2(prm.scale_log2, prm.scale_log2), neg_m2 = pack2(neg_m, neg_m);
-        // Three pairs of eight take the polynomial; a thread with a masked key in its slice (the diagonal tiles only)
-        // keeps to the exact-zero path of ex2(-inf).
-        // P(g) goes to buffer g & 1, which PV(g-2) has finished reading (QK(g) was issued after it).  32 keys at a time,
-        // packed to bf16, four 16-byte stores into the swizzled row of this slice's 64-key half.  kPolyPairsOf8 pairs of
-        // every eight take the polynomial; a thread with a masked key in its slice (the diagonal tiles only) keeps to
-        // ex2(-inf) = 0 exactly.
-        uint8_t* pbuf = smem + kSmemP + (g & 1) * kPBytes + r * 128 + ((hb * kCols) >> 6) * kHalf;
-        const int chunk0 = ((hb * kCols) & 63) >> 3;   // first 16-byte chunk of this slice inside its 64-key half
+        // P(g), packed to bf16, goes over the first 64 columns of S(g): every slice of the row has read its S columns (the
+        // barrier above came after the loads), and QK(g+2), which writes this S buffer again, is issued behind PV(g).
+        // kPolyPairsOf8 pairs of every eight take the polynomial; a thread with a masked key in its slice (the diagonal
+        // tiles only) keeps to ex2(-inf) = 0 exactly.
+        uint32_t pw[kCols / 2];
         uint64_t ps2;
-        if (nvalid == kCols) ps2 = exp_rows<true>(sv, scale2, neg_m2, pbuf, chunk0, r);
-        else ps2 = exp_rows<false>(sv, scale2, neg_m2, pbuf, chunk0, r);
+        if (nvalid == kCols) ps2 = exp_rows<true>(sv, scale2, neg_m2, pw);
+        else ps2 = exp_rows<false>(sv, scale2, neg_m2, pw);
+        __syncwarp();   // the store is warp-collective
+        tmem_st_32x32b_x32(tmem + ((uint32_t)(wq * 32) << 16) + kTmemS + (g & 1) * 128 + hb * (kCols / 2), pw);
         float ps0, ps1;
         unpack2(ps2, ps0, ps1);
         l_run = l_run * alpha + (ps0 + ps1);
@@ -573,7 +568,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           }
           tmem_st_wait();
         }
-        fence_proxy_async();
+        tmem_st_wait();   // P, and a rescaled O
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(p_full_lead);
