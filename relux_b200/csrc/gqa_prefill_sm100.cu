@@ -171,6 +171,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+
 // ---- two float32 lanes per instruction (add / fma on a 64-bit register pair) ----
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
   uint64_t r;
@@ -515,12 +521,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           for (int c = 0; c < kCols; c++)
             if (c >= nvalid) sv[c] = 0xFF800000u;   // -inf
         }
-        // row max of the raw scores (the softmax scale is positive, so it commutes with max); four chains, not one
+        // row max of the raw scores (the softmax scale is positive, so it commutes with max); four chains of three-input
+        // maxima, two scores per instruction
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int c = 0; c < kCols; c += 4)
+        for (int c = 0; c < kCols; c += 8)
 #pragma unroll
-          for (int k = 0; k < 4; k++) mx4[k] = fmaxf(mx4[k], __uint_as_float(sv[c + k]));
+          for (int k = 0; k < 4; k++) mx4[k] = max3(mx4[k], __uint_as_float(sv[c + 2 * k]), __uint_as_float(sv[c + 2 * k + 1]));
         float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * prm.scale_log2;
         bars->rowmax[g & 1][hb][r] = mx;
         asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory");
