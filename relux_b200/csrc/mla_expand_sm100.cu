@@ -16,8 +16,13 @@
 // [64 r, 64 r + 64) of every weight stage ([128 latent rows x 64 columns], MN-major as the weights lie).  Worker w takes a
 // contiguous run of (token tile, output tile) units in token-tile-major order, so the latent tile is loaded once per run
 // (twice when the run crosses a token tile) and the 32 MB of weights stream from L2 through a six-stage ring.
+// The latent tile is the A operand of every MMA of a run: it is copied once from shared memory into tensor memory (lane =
+// token, two latents per 32-bit column, 256 columns), so that the MMAs read only the weight stages from shared memory.
+// With both operands there, an M256 N128 K16 step reads 4 KB of A + 2 KB of B per CTA and serves 2 KB of B to its
+// peer: 8 KB per 64 clocks, the whole shared-memory bandwidth, and the tensor pipe measured 52 % busy.
 // The accumulator is double-buffered in tensor memory: four epilogue warps convert and store unit n while the MMAs of
-// unit n + 1 run.  Warp roles per CTA: 4 epilogue warps, 1 TMA producer, 1 MMA issuer (leader CTA only).
+// unit n + 1 run (they also make the copy of the latent tile, between two runs of units).
+// Warp roles per CTA: 4 epilogue warps, 1 TMA producer, 1 MMA issuer (leader CTA only).
 // No TMA multicast; full barriers live in the leader and count both CTAs' bytes; every wait is bounded.
 #include <algorithm>
 #include <cuda_bf16.h>
@@ -40,10 +45,11 @@ constexpr int kSmemRing = kABytes;
 constexpr int kSmemBar = kSmemRing + kStages * kStageBytes;   // 229376
 constexpr int kSmemTotal = kSmemBar + 1024;
 constexpr int kEpiWarps = 4, kThreads = 32 * (kEpiWarps + 2);
-constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kTmemCols = 512;
+constexpr uint32_t kTmemA = 256;                    // accumulators at columns [0, 256), the latent tile at [256, 512)
 
 struct Bars {
-  uint64_t a_full, a_empty, b_full[kStages], b_empty[kStages], acc_full[2], acc_empty[2];
+  uint64_t a_full, a_empty, a_ready, b_full[kStages], b_empty[kStages], acc_full[2], acc_empty[2], drain;
   uint32_t tmem_base;
   volatile int32_t abort_flag;
 };
@@ -96,7 +102,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   }
   if (threadIdx.x == 0) {
     mbar_init(&bars->a_full, 1);
-    mbar_init(&bars->a_empty, 1);
+    mbar_init(&bars->drain, 1);
+    mbar_init(&bars->a_empty, kEpiWarps);       // this CTA's copy has left the shared tile
+    mbar_init(&bars->a_ready, 2 * kEpiWarps);   // both CTAs' latent tiles are in tensor memory (the leader's copy is waited on)
     for (int s = 0; s < kStages; s++) { mbar_init(&bars->b_full[s], 1); mbar_init(&bars->b_empty[s], 1); }
     for (int s = 0; s < 2; s++) { mbar_init(&bars->acc_full[s], 1); mbar_init(&bars->acc_empty[s], 2 * kEpiWarps); }
     bars->abort_flag = 0;
@@ -146,9 +154,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           y[h2] = prm.row0 + (int64_t)pg * prm.blocks_per_page * kPage;
         }
         if (na > 0) wait_bar(&bars->a_empty, (na - 1) & 1, bars, prm.status);
-        const uint32_t lead = mapa_u32(smem_u32(&bars->a_full), 0);
+        // every CTA's latent tile reports to its OWN barrier: its epilogue warps copy it to tensor memory
+        const uint32_t lead = mapa_u32(smem_u32(&bars->a_full), rank);
         if (el) {
-          if (rank == 0) mbar_expect_tx(&bars->a_full, 2 * kABytes);   // the latent tiles of both CTAs
+          mbar_expect_tx(&bars->a_full, kABytes);
 #pragma unroll 1
           for (int kb = 0; kb < kDC / 64; kb++) {
             tma_load_2d_2sm(smem + kb * kABlock, &tmap_pool, 0, (int32_t)(y[0] + kb * kPage), lead);
@@ -178,12 +187,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     const bool el = elect_one();
     if (rank == 0) {
       const uint32_t idesc = make_idesc_bf16(256, 128, false, true);
-      const uint64_t dA = make_desc_kmajor_sw128(smem_u32(smem));
       int cur_tt = -1, na = 0, gs = 0, n = 0;
       for (int u = u0; u < u1; u++, n++) {
         const int tt = u / prm.n_out;
         if (tt != cur_tt) {
-          wait_bar(&bars->a_full, na & 1, bars, prm.status);
+          wait_bar(&bars->a_ready, na & 1, bars, prm.status);
           na++;
           cur_tt = tt;
         }
@@ -198,28 +206,59 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             const uint64_t dB = make_desc_mnmajor_sw128(smem_u32(smem + kSmemRing + st * kStageBytes), kBlk);
 #pragma unroll
             for (int ks = 0; ks < 8; ks++) {
-              const uint32_t aoff = (uint32_t)((2 * s + (ks >> 2)) * kABlock + (ks & 3) * 32) >> 4;
-              umma_ss<2>(tmem + buf * 128, dA + aoff, dB + ((uint32_t)(ks * 2048) >> 4), idesc, (s | ks) != 0);
+              umma_ts<2>(tmem + buf * 128, tmem + kTmemA + (8 * s + ks) * 8, dB + ((uint32_t)(ks * 2048) >> 4), idesc, (s | ks) != 0);
             }
             umma_commit_mc<2>(&bars->b_empty[st], 0x3);
           }
           __syncwarp();
         }
-        const bool last_of_tile = (u + 1 == u1) || ((u + 1) / prm.n_out != tt);
-        if (el) {
-          umma_commit_mc<2>(&bars->acc_full[buf], 0x3);
-          if (last_of_tile) umma_commit_mc<2>(&bars->a_empty, 0x3);
-        }
+        if (el) umma_commit_mc<2>(&bars->acc_full[buf], 0x3);
         __syncwarp();
       }
+      // Nothing of this pair may be freed while an MMA is in flight.  On the ordinary path the epilogue's last wait says
+      // so already; after a wait that gave up it does not, so the issuer itself sees its last MMA complete.
+      if (el) umma_commit<2>(&bars->drain);
+      __syncwarp();
+      mbar_wait(&bars->drain, 0);
     }
   } else {
     // =============================== epilogue: accumulator -> bf16 rows ===============================
     const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
     const uint32_t lead_empty0 = mapa_u32(smem_u32(&bars->acc_empty[0]), 0), lead_empty1 = mapa_u32(smem_u32(&bars->acc_empty[1]), 0);
-    int n = 0;
+    const uint32_t lead_ready = mapa_u32(smem_u32(&bars->a_ready), 0);
+    const int row = warp * 32 + lane;
+    int n = 0, na = 0, cur_tt = -1;
     for (int u = u0; u < u1; u++, n++) {
       const int tt = u / prm.n_out, nt = u % prm.n_out;
+      if (tt != cur_tt) {
+        // A new latent tile.  The MMAs that read the previous one have completed (this warp has seen acc_full of the last
+        // unit that used it).  Row `row` of every 64-column block -> 32 columns of this thread's lane.
+        wait_bar(&bars->a_full, na & 1, bars, prm.status);
+        __syncwarp();
+#pragma unroll 1
+        for (int kb = 0; kb < kDC / 64; kb++) {
+          uint32_t w[32];
+          const uint8_t* src = smem + kb * kABlock + row * 128;
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const uint4 v = *reinterpret_cast<const uint4*>(src + ((j ^ (row & 7)) << 4));
+            w[4 * j] = v.x;
+            w[4 * j + 1] = v.y;
+            w[4 * j + 2] = v.z;
+            w[4 * j + 3] = v.w;
+          }
+          tmem_st_32x32b_x32(tmem + lane_addr + kTmemA + kb * 32, w);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bars->a_empty);        // the producer may fetch the next token tile into the shared tile
+          mbar_arrive_cluster(lead_ready);
+        }
+        na++;
+        cur_tt = tt;
+      }
       const int buf = n & 1;
       wait_bar(&bars->acc_full[buf], (n >> 1) & 1, bars, prm.status);
       __syncwarp();   // the TMEM loads below are warp-collective
