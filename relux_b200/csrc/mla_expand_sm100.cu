@@ -15,13 +15,15 @@
 // token tile -- 8 latent blocks of [128 tokens x 64 columns], 128 KB, straight out of the blocked pages -- and columns
 // [64 r, 64 r + 64) of every weight stage ([128 latent rows x 64 columns], MN-major as the weights lie).  Worker w takes a
 // contiguous run of (token tile, output tile) units in token-tile-major order, so the latent tile is loaded once per run
-// (twice when the run crosses a token tile) and the 32 MB of weights stream from L2 through a six-stage ring.
+// (twice when the run crosses a token tile) and the 32 MB of weights stream from L2 through a four-stage ring.
 // The latent tile is the A operand of every MMA of a run: it is copied once from shared memory into tensor memory (lane =
 // token, two latents per 32-bit column, 256 columns), so that the MMAs read only the weight stages from shared memory.
 // With both operands there, an M256 N128 K16 step reads 4 KB of A + 2 KB of B per CTA and serves 2 KB of B to its
 // peer: 8 KB per 64 clocks, the whole shared-memory bandwidth, and the tensor pipe measured 52 % busy.
-// The accumulator is double-buffered in tensor memory: four epilogue warps convert and store unit n while the MMAs of
-// unit n + 1 run (they also make the copy of the latent tile, between two runs of units).
+// The accumulator is double-buffered in tensor memory: four epilogue warps convert unit n while the MMAs of unit n + 1
+// run (they also make the copy of the latent tile, between two runs of units).  The bf16 rows leave through a swizzled
+// shared tile and TMA stores: written straight from the row-per-thread registers, 16 bytes per lane at a 256-byte pitch,
+// they took twice the time of the unit's MMAs.
 // Warp roles per CTA: 4 epilogue warps, 1 TMA producer, 1 MMA issuer (leader CTA only).
 // No TMA multicast; full barriers live in the leader and count both CTAs' bytes; every wait is bounded.
 #include <algorithm>
@@ -40,9 +42,11 @@ constexpr int kBlk = 8192;                          // one [64 rows x 64 cols] b
 constexpr int kABlock = 2 * kBlk;                   // [128 tokens x 64 latent columns]
 constexpr int kABytes = (kDC / 64) * kABlock;       // 131072
 constexpr int kStageBytes = 2 * kBlk;               // [128 latent rows x 64 output columns]
-constexpr int kStages = 6, kStagesPerUnit = kDC / 128;
+constexpr int kStages = 4, kStagesPerUnit = kDC / 128;
 constexpr int kSmemRing = kABytes;
-constexpr int kSmemBar = kSmemRing + kStages * kStageBytes;   // 229376
+constexpr int kSmemOut = kSmemRing + kStages * kStageBytes;   // one output tile [128 tokens x (cols 0-63 | cols 64-127)] bf16, swizzled
+constexpr int kOutBytes = 4 * kBlk;
+constexpr int kSmemBar = kSmemOut + kOutBytes;                // 229376
 constexpr int kSmemTotal = kSmemBar + 1024;
 constexpr int kEpiWarps = 4, kThreads = 32 * (kEpiWarps + 2);
 constexpr uint32_t kTmemCols = 512;
@@ -87,7 +91,8 @@ __device__ __forceinline__ void wait_bar(uint64_t* bar, uint32_t parity, Bars* b
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     mla_expand_sm100_kernel(const __grid_constant__ CUtensorMap tmap_pool, const __grid_constant__ CUtensorMap tmap_wuk,
-                            const __grid_constant__ CUtensorMap tmap_wuv, const ExpandParams prm) {
+                            const __grid_constant__ CUtensorMap tmap_wuv, const __grid_constant__ CUtensorMap tmap_out,
+                            const ExpandParams prm) {
   extern __shared__ __align__(1024) uint8_t smem[];
   Bars* bars = reinterpret_cast<Bars*>(smem + kSmemBar);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -263,8 +268,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
       wait_bar(&bars->acc_full[buf], (n >> 1) & 1, bars, prm.status);
       __syncwarp();   // the TMEM loads below are warp-collective
       tc_fence_after();
-      const int64_t row = (int64_t)tt * kTokTile + 128 * (int)rank + warp * 32 + lane;
-      uint16_t* dst = (nt < prm.H ? prm.kx + (int64_t)nt * prm.Ttot * 128 : prm.vx + (int64_t)(nt - prm.H) * prm.Ttot * 128) + row * 128;
+      // the stores of the previous unit have read the shared tile
+      if (threadIdx.x == 0) tma_store_wait_read();
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
+      uint8_t* orow = smem + kSmemOut + row * 128;
 #pragma unroll 1
       for (int c = 0; c < 128; c += 32) {
         uint32_t v[32];
@@ -273,15 +280,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) pk[i] = pack_bf16x2(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+        // columns c .. c + 31 = 16-byte chunks (c & 63) / 8 .. + 3 of the 64-column half c / 64
 #pragma unroll
         for (int i = 0; i < 4; i++)
-          *reinterpret_cast<uint4*>(dst + c + 8 * i) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+          *reinterpret_cast<uint4*>(orow + (c >> 6) * 2 * kBlk + (((((c & 63) >> 3) + i) ^ (row & 7)) << 4)) =
+              make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(buf ? lead_empty1 : lead_empty0);
+      if (lane == 0) mbar_arrive_cluster(buf ? lead_empty1 : lead_empty0);   // the accumulator is free again
+      fence_proxy_async();
+      asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpiWarps) : "memory");
+      if (threadIdx.x == 0) {
+        // first row of this CTA's 128 tokens in the [2 H Ttot][128] array of expanded keys and values
+        const int32_t y = (int32_t)((int64_t)nt * prm.Ttot + (int64_t)tt * kTokTile + 128 * (int)rank);
+#pragma unroll
+        for (int h2 = 0; h2 < 2; h2++)
+#pragma unroll
+          for (int r2 = 0; r2 < 2; r2++) tma_store_2d(&tmap_out, 64 * h2, y + 64 * r2, smem + kSmemOut + h2 * 2 * kBlk + r2 * kBlk);
+        tma_store_commit();
+      }
     }
   }
+  if (threadIdx.x == 0) tma_store_wait_all();
   __syncwarp();
   tc_fence_before();
   cluster_sync();
@@ -351,9 +372,14 @@ int32_t launch_mla_expand_sm100(Pool* p, const SeqBatch& sb, int layer, int extr
                                 int64_t Ttot, uint16_t* kx, uint16_t* vx, int32_t* seq_base) {
   const relux_pool_params& prm = p->prm;
   cudaStream_t st = p->dev->stream;
-  CUtensorMap t_uk, t_uv;
+  CUtensorMap t_uk, t_uv, t_out;
   if (!make_tmap_2d(&t_uk, (void*)w_uk, kDC, (uint64_t)H * 128, 64, 128) || !make_tmap_2d(&t_uv, (void*)w_uv, kDC, (uint64_t)H * 128, 64, 128)) {
     set_error("tensor maps for W_UK / W_UV could not be encoded");
+    return RELUX_ERR_CUDA;
+  }
+  // keys and values are one array: vx must follow kx directly (row = (K: head | V: H + head) * Ttot + dense token row)
+  if (vx != kx + (size_t)H * Ttot * 128 || !make_tmap_2d(&t_out, kx, (uint64_t)2 * H * Ttot, 128, 64, 64)) {
+    set_error("tensor map for the expanded keys / values could not be encoded");
     return RELUX_ERR_CUDA;
   }
   const int32_t* len = p->d_len + (size_t)layer * prm.max_seqs;
@@ -385,7 +411,7 @@ int32_t launch_mla_expand_sm100(Pool* p, const SeqBatch& sb, int layer, int extr
   k.status = p->d_status;
   RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_expand_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
   const int launched = (int)((units + k.span - 1) / k.span);
-  mla_expand_sm100_kernel<<<dim3(2 * launched), kThreads, kSmemTotal, st>>>(p->tmap_mla, t_uk, t_uv, k);
+  mla_expand_sm100_kernel<<<dim3(2 * launched), kThreads, kSmemTotal, st>>>(p->tmap_mla, t_uk, t_uv, t_out, k);
   RELUX_CUDA_TRY(cudaGetLastError());
   count_launch(p->dev);
   return RELUX_OK;
