@@ -14,26 +14,33 @@
 //   Q tile  : own 128 rows x 128 dims bf16 (32 KB), one 3-D TMA box per 64-dim half; row = token_in_block * g + head
 //   per 128-key tile (two pages of the kv head):
 //     S[256 x 128] = Q K^T      8 MMAs M256 N128 K16; B = K, split by keys: CTA r holds page 2j + r (16 KB)
-//     softmax warps: S from TMEM -> exp2 with a lazily updated running max -> P bf16 into a swizzled shared tile
-//                    (two P tiles in turn, so the exponentials of tile j+1 run while PV(j) still reads P(j))
-//     O[256 x 128] += P V       8 MMAs M256 N128 K16; B = V as it lies (MN-major), split by output dims: CTA r holds
-//                               dims [64 r, 64 r + 64) of both pages (16 KB)
-// Persistent workers.  As many CTA pairs as fit on the GPU are launched once; worker w takes items w, w + W, ... of a
-// list ordered longest first.  One launch per block measured 16k cycles (8 us) of fixed cost per CTA pair -- launch,
+//     softmax warps: S from TMEM -> exp2 with a lazily updated running max -> P packed to bf16 and written back to
+//                    tensor memory over the first 64 columns of the S tile just read (P never touches shared memory)
+//     O[256 x 128] += P V       8 MMAs M256 N128 K16; A = P from tensor memory; B = V as it lies (MN-major), split by
+//                               output dims: CTA r holds dims [64 r, 64 r + 64) of both pages (16 KB)
+// Persistent workers.  As many CTA pairs as fit on the GPU are launched once and walk a static list of items (see
+// Cursor below for its order).  One launch per block measured 16k cycles (8 us) of fixed cost per CTA pair -- launch,
 // tensor-memory allocation, the latency of the first Q / K loads, pipeline fill, drain and the epilogue -- against
 // 2.1k cycles per tile: at 2048-token prompts (9 tiles per item on average) that was half of the kernel.  Here the tile
 // pipeline does not drain at an item boundary: tiles are numbered over the worker's whole life, Q has two buffers (the
 // next item's Q is requested while the current item's last tiles are in flight), the first QK^T of the next item is
-// issued ahead of the last PV of the current one like any other tile, and an item's epilogue (O read-out, normalise,
-// store) overlaps the next item's first QK^T and softmax: it is ordered before the thread's next p_full arrival, which
-// is what releases the next item's first PV.
-// TMEM per CTA: S double-buffered (2 x 128 columns), O 128 columns; rows = TMEM lanes.  Issue order QK(g+1), PV(g).
-// Warp roles per CTA: 8 softmax / epilogue warps -- a query row (TMEM lane) is shared by two threads, 64 keys (and 64
-// output dims) each --, 1 TMA producer, 1 MMA issuer (leader CTA only), both converged with one elected lane.
-// Barriers: full barriers live in the leader CTA and count the bytes of both CTAs' loads; empty / s_full / pv_done
-// barriers live in each CTA and are armed by tcgen05.commit with mbarrier multicast (not a TMA load); p_full lives in
-// the leader and counts the softmax warps of both CTAs.  No TMA multicast anywhere.
-// No split-KV: the output is normalised in the epilogue and written once.
+// issued ahead of the last PV of the current one like any other tile, O has two accumulators (items in turn), and an
+// item's read-out (O / row sum -> out) is the work of four warps of its own while the softmax warps are already on the
+// next item.
+// TMEM per CTA: S double-buffered (2 x 128 columns, P over the first 64 of each), O double-buffered (2 x 128 columns);
+// rows = TMEM lanes.  Issue order QK(g+1), PV(g): QK(g+2), which overwrites the S / P buffer of tile g, is issued behind
+// PV(g), and the tensor pipe executes in issue order.
+// Warp roles per CTA: 8 softmax warps -- a query row (TMEM lane) is shared by two threads, 64 keys (and 64 output dims
+// of a rescale) each --, 1 TMA producer, 1 MMA issuer (leader CTA only), both converged with one elected lane, 4 read-out
+// warps.  The softmax warps are the busiest part: per tile and SM 16384 scores through max, scale, exp2, sum and pack.
+// The special-function unit delivers 16 exponentials per clock and SM (1024 clocks per tile, as long as the tile's
+// MMAs), so three pairs of every eight take a cubic on the FMA pipe instead, arithmetic runs two lanes per instruction
+// (fma.f32x2, add.f32x2) and the row maximum takes two scores per instruction (three-input max).
+// Barriers: full barriers live in the leader CTA and count the bytes of both CTAs' loads; empty / s_full / pv_done /
+// o_full barriers live in each CTA and are armed by tcgen05.commit with mbarrier multicast (not a TMA load); p_full and
+// o_empty live in the leader and count warps of both CTAs.  No TMA multicast anywhere.
+// No split-KV: the output is normalised in the read-out and written once.
+// Every wait is bounded (status RELUX_ERR_TIMEOUT, shared abort flag, all warps still reach the end and free TMEM).
 //
 // The same kernel serves MLA prompts (template parameter kMla): MLA.forwardCached for seqQ > 1 expands every cached
 // latent row into per-head keys and values first (internal/transformer/mla.go:323-326; here mla_expand_sm100.cu, bf16
@@ -41,8 +48,7 @@
 // kernel that is the group size 1 case with three changes: the Q tile and every K stage carry a third 64-column block
 // (the RoPE part: of the query from its own array, of the key from the pool's pages, shared by all heads), QK^T is 12
 // K-steps instead of 8, and the expanded keys / values are addressed densely (head * Ttot + first row of the sequence +
-// token) instead of through the page table.  192-wide tiles leave room for one Q buffer only: the next item's Q is
-// requested when the current item's last QK^T has completed and lands behind its last softmax and PV.
+// token) instead of through the page table.
 // Every wait is bounded (status RELUX_ERR_TIMEOUT, shared abort flag, all warps still reach the end and free TMEM).
 #include <algorithm>
 #include <cuda_bf16.h>
@@ -96,7 +102,7 @@ constexpr int kPolyPairsOf8 = 3;   // score pairs out of every eight whose expon
 
 struct Bars {
   uint64_t q_full[2], q_empty[2], k_full[kMaxDepth], k_empty[kMaxDepth], v_full[kMaxDepth], v_empty[kMaxDepth], s_full[2], p_full, pv_done;
-  uint64_t o_full[2], o_empty[2], l_full, l_empty;
+  uint64_t o_full[2], o_empty[2], l_full, l_empty, drain;
   uint32_t tmem_base;
   volatile int32_t abort_flag;
   float rowmax[2][kSplit][128];   // [tile parity][key slice][row]; at the end of an item the buffer of the tile that follows
@@ -309,6 +315,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     }
     mbar_init(&bars->l_full, kSoftmaxWarps / kSplit);
     mbar_init(&bars->l_empty, kEpiWarps);
+    mbar_init(&bars->drain, 1);
     bars->abort_flag = 0;
     fence_mbar_init();
   }
@@ -488,6 +495,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         }
         ntiles = next_tiles;
       }
+      // Nothing of this pair may be freed while an MMA is in flight.  On the ordinary path the read-out's last wait says
+      // so already; after a wait that gave up it does not, so the issuer itself sees its last MMA complete.
+      if (el) umma_commit<2>(&bars->drain);
+      __syncwarp();
+      mbar_wait(&bars->drain, 0);
     }
   } else if (warp < kSoftmaxWarps) {
     // =============================== softmax / correction ===============================

@@ -225,69 +225,79 @@ __device__ __forceinline__ void tile_mma_64x64x128_bt(const uint16_t* As, const 
   }
 }
 
-// Merges the split-KV partials of the tile's rows into the bf16 A operand.  COLS = columns of every 128-column chunk
-// one thread owns; 128 / COLS threads share a row, 256 * COLS / 128 rows are covered (the rest of the 64-row tile is
-// zeroed).  Two items are in flight per thread at a time: their loads do not depend on each other.
-template <int COLS>
-__device__ __forceinline__ void merge_rows(uint16_t* As, const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                           const int32_t* sC0, const int32_t* sC1, const float* sM, const float* sInv, int r0, int rows,
-                                           int S, int H, int h, int dC, int nk, int rows_total) {
-  constexpr int TPR = 128 / COLS, ROWS = 256 / TPR;
-  const int row = threadIdx.x / TPR, qt = threadIdx.x % TPR;
-  for (int e = threadIdx.x; e < (64 - ROWS) * 16 * nk; e += 256) {   // rows of the MMA tile nobody merges into
-    const int k = e / ((64 - ROWS) * 16), rem = e % ((64 - ROWS) * 16);
-    *reinterpret_cast<uint4*>(As + ((size_t)k * 64 + ROWS + rem / 16) * kStride + (rem % 16) * 8) = make_uint4(0, 0, 0, 0);
-  }
-  const int r = r0 + row;
-  const int c0 = sC0[row], c1 = sC1[row];
-  const float M = sM[row], inv = sInv[row];
-  const size_t prow = (r < rows) ? (size_t)(r % S) * H + h : 0;
-  float acc[kMaxChunks][COLS];
+// Merges the split-KV partials of the tile's rows into the bf16 A operand, one warp per row at a time: a lane owns the
+// same 4 of every 128 latent columns, so every load instruction of a warp is 512 contiguous bytes of one partial row
+// (four threads per row with 128 bytes each, the first layout, put 32 different cache lines into every load
+// instruction: the kernel spent most of its time in the load unit's address stage).  The weights of a row's items come
+// from one round trip: lane j reads (max, sum) of item j, the warp reduces.  Four items are in flight per lane.
+// Rows past the batch are zero rows of the MMA tile.
+constexpr int kMergeWarps = 16;
+__device__ __forceinline__ void merge_rows_warp(uint16_t* As, const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                                const int32_t* __restrict__ chunk_off, int r0, int rows, int S, int H, int h, int dC, int nk,
+                                                int rows_total) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int row = warp; row < 64; row += kMergeWarps) {
+    const int r = r0 + row;
+    float4 acc[kMaxChunks];
 #pragma unroll
-  for (int k = 0; k < kMaxChunks; k++)
+    for (int k = 0; k < kMaxChunks; k++) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < rows) {
+      const int i = r / S;
+      const int c0 = __ldg(chunk_off + i), c1 = __ldg(chunk_off + i + 1);
+      const size_t prow = (size_t)(r % S) * H + h;
+      // global maximum and normaliser over all items of the sequence
+      float M = -INFINITY;
+      for (int c = c0 + lane; c < c1; c += 32) M = fmaxf(M, __ldg(part_ml + ((size_t)c * rows_total + prow) * 2));
 #pragma unroll
-    for (int j = 0; j < COLS; j++) acc[k][j] = 0.f;
-  for (int c = c0; c < c1; c += 2) {
-    const bool two = c + 1 < c1;
-    const size_t pr0 = (size_t)c * rows_total + prow, pr1 = (size_t)(two ? c + 1 : c) * rows_total + prow;
-    const float m0 = __ldg(part_ml + pr0 * 2), m1 = __ldg(part_ml + pr1 * 2);
-    const float w0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - M) * inv;
-    const float w1 = (!two || m1 == -INFINITY) ? 0.f : exp2f(m1 - M) * inv;
-    const float4* s0 = reinterpret_cast<const float4*>(part_o + pr0 * dC + qt * COLS);
-    const float4* s1 = reinterpret_cast<const float4*>(part_o + pr1 * dC + qt * COLS);
+      for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+      float L = 0.f;
+      for (int c = c0 + lane; c < c1; c += 32) {
+        const float2 ml = __ldg(reinterpret_cast<const float2*>(part_ml + ((size_t)c * rows_total + prow) * 2));
+        if (ml.x != -INFINITY) L += ml.y * exp2f(ml.x - M);
+      }
 #pragma unroll
-    for (int k = 0; k < kMaxChunks; k++) {
-      if (k < nk) {
-        float4 x0[COLS / 4], x1[COLS / 4];
-#pragma unroll
-        for (int j = 0; j < COLS / 4; j++) {
-          x0[j] = __ldg(s0 + k * 32 + j);
-          x1[j] = __ldg(s1 + k * 32 + j);
+      for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+      const float inv = (L > 0.f) ? 1.0f / L : 0.f;
+      for (int cb = c0; cb < c1; cb += 32) {
+        // this lane's item of the group of 32: its weight; then four items at a time, weights by shuffle
+        const int cm = cb + lane;
+        float w_mine = 0.f;
+        if (cm < c1) {
+          const float m = __ldg(part_ml + ((size_t)cm * rows_total + prow) * 2);
+          w_mine = (m == -INFINITY) ? 0.f : exp2f(m - M) * inv;
         }
+        const int ng = min(32, c1 - cb);
+        for (int j = 0; j < ng; j += 4) {
+          float4 x[4][kMaxChunks];
 #pragma unroll
-        for (int j = 0; j < COLS / 4; j++) {
-          acc[k][4 * j] = fmaf(x1[j].x, w1, fmaf(x0[j].x, w0, acc[k][4 * j]));
-          acc[k][4 * j + 1] = fmaf(x1[j].y, w1, fmaf(x0[j].y, w0, acc[k][4 * j + 1]));
-          acc[k][4 * j + 2] = fmaf(x1[j].z, w1, fmaf(x0[j].z, w0, acc[k][4 * j + 2]));
-          acc[k][4 * j + 3] = fmaf(x1[j].w, w1, fmaf(x0[j].w, w0, acc[k][4 * j + 3]));
+          for (int u = 0; u < 4; u++) {
+            const int c = cb + min(j + u, ng - 1);   // a short group re-reads its last item with weight 0
+            const float4* src = reinterpret_cast<const float4*>(part_o + ((size_t)c * rows_total + prow) * dC) + lane;
+#pragma unroll
+            for (int k = 0; k < kMaxChunks; k++)
+              if (k < nk) x[u][k] = __ldg(src + k * 32);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; u++) {
+            float w = __shfl_sync(0xffffffffu, w_mine, min(j + u, 31));
+            if (j + u >= ng) w = 0.f;
+#pragma unroll
+            for (int k = 0; k < kMaxChunks; k++)
+              if (k < nk) {
+                acc[k].x = fmaf(x[u][k].x, w, acc[k].x);
+                acc[k].y = fmaf(x[u][k].y, w, acc[k].y);
+                acc[k].z = fmaf(x[u][k].z, w, acc[k].z);
+                acc[k].w = fmaf(x[u][k].w, w, acc[k].w);
+              }
+          }
         }
       }
     }
-  }
 #pragma unroll
-  for (int k = 0; k < kMaxChunks; k++) {
-    if (k < nk) {
-      uint16_t* dst = As + ((size_t)k * 64 + row) * kStride + qt * COLS;
-      if constexpr (COLS >= 8) {
-#pragma unroll
-        for (int j = 0; j < COLS / 8; j++)
-          *reinterpret_cast<uint4*>(dst + j * 8) =
-              make_uint4(pack_bf16x2(acc[k][8 * j], acc[k][8 * j + 1]), pack_bf16x2(acc[k][8 * j + 2], acc[k][8 * j + 3]),
-                         pack_bf16x2(acc[k][8 * j + 4], acc[k][8 * j + 5]), pack_bf16x2(acc[k][8 * j + 6], acc[k][8 * j + 7]));
-      } else {
-        *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(acc[k][0], acc[k][1]), pack_bf16x2(acc[k][2], acc[k][3]));
-      }
-    }
+    for (int k = 0; k < kMaxChunks; k++)
+      if (k < nk)
+        *reinterpret_cast<uint2*>(As + ((size_t)k * 64 + row) * kStride + lane * 4) =
+            make_uint2(pack_bf16x2(acc[k].x, acc[k].y), pack_bf16x2(acc[k].z, acc[k].w));
   }
 }
 
@@ -295,18 +305,16 @@ __device__ __forceinline__ void merge_rows(uint16_t* As, const float* __restrict
 // 64 rows of one head, as bf16) is built straight from the per-item partials
 //   part_o [item][S * H][dC] f32 (unnormalised), part_ml [item][S * H][2] = (max in the log2 domain, sum),
 // items of sequence i = [chunk_off[i], chunk_off[i + 1]).  All of W_UV's slice for this head (dC x 128 bf16) streams
-// into shared memory with cp.async while the partials are combined; four threads per row keep 32 independent
-// 16-byte loads in flight per item, so the merge costs about one memory round trip per item of a sequence.
-// grid (H, ceil(rows/64)), 256 threads, row = seq_index * S + query token.  dC = 128 * nk, nk <= 4.
-__global__ void __launch_bounds__(256) mla_merge_vup_mma_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+// into shared memory with cp.async while the partials are combined by 16 warps (merge_rows_warp); the first 8 warps
+// then run the MMAs.
+// grid (H, ceil(rows/64)), 512 threads, row = seq_index * S + query token.  dC = 128 * nk, nk <= 4.
+__global__ void __launch_bounds__(32 * kMergeWarps) mla_merge_vup_mma_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                                 const int32_t* __restrict__ chunk_off, const uint16_t* __restrict__ W_UV,
                                                                 float* __restrict__ out, int rows, int S, int H, int dC) {
   extern __shared__ __align__(16) uint16_t sm[];
   const int nk = dC / 128;
   uint16_t* As = sm;                             // [nk][64][kStride]
   uint16_t* Bs = sm + (size_t)nk * 64 * kStride;  // [nk][128][kStride]
-  __shared__ float sM[64], sInv[64];
-  __shared__ int32_t sC0[64], sC1[64];
   const int h = blockIdx.x, r0 = blockIdx.y * 64;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rows_total = S * H;
@@ -318,33 +326,7 @@ __global__ void __launch_bounds__(256) mla_merge_vup_mma_kernel(const float* __r
     }
     cp_async_commit();
   }
-  if (threadIdx.x < 64) {
-    const int r = r0 + threadIdx.x;
-    int c0 = 0, c1 = 0;
-    float M = -INFINITY, L = 0.f;
-    if (r < rows) {
-      const int i = r / S, sq = r % S;
-      c0 = chunk_off[i];
-      c1 = chunk_off[i + 1];
-      const size_t prow = (size_t)sq * H + h;
-      for (int c = c0; c < c1; c++) M = fmaxf(M, part_ml[((size_t)c * rows_total + prow) * 2]);
-      for (int c = c0; c < c1; c++) {
-        const float* ml = part_ml + ((size_t)c * rows_total + prow) * 2;
-        if (ml[0] != -INFINITY) L += ml[1] * exp2f(ml[0] - M);
-      }
-    }
-    sM[threadIdx.x] = M;
-    sInv[threadIdx.x] = (L > 0.f) ? 1.0f / L : 0.f;
-    sC0[threadIdx.x] = c0;
-    sC1[threadIdx.x] = c1;
-  }
-  __syncthreads();
-  // fewer real rows in the tile -> more threads per row, so that a short batch still keeps every thread loading
-  const int rows_here = min(64, rows - r0);
-  if (rows_here > 32) merge_rows<32>(As, part_o, part_ml, sC0, sC1, sM, sInv, r0, rows, S, H, h, dC, nk, rows_total);
-  else if (rows_here > 16) merge_rows<16>(As, part_o, part_ml, sC0, sC1, sM, sInv, r0, rows, S, H, h, dC, nk, rows_total);
-  else if (rows_here > 8) merge_rows<8>(As, part_o, part_ml, sC0, sC1, sM, sInv, r0, rows, S, H, h, dC, nk, rows_total);
-  else merge_rows<4>(As, part_o, part_ml, sC0, sC1, sM, sInv, r0, rows, S, H, h, dC, nk, rows_total);
+  merge_rows_warp(As, part_o, part_ml, chunk_off, r0, rows, S, H, h, dC, nk, rows_total);
   float acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; i++)
@@ -359,8 +341,9 @@ __global__ void __launch_bounds__(256) mla_merge_vup_mma_kernel(const float* __r
       default: cp_async_wait<0>(); break;
     }
     __syncthreads();   // also publishes the merged A tiles (first iteration)
-    tile_mma_64x64x128_bt(As + (size_t)k * 64 * kStride, Bs + (size_t)k * 128 * kStride, acc, warp, lane);
+    if (warp < 8) tile_mma_64x64x128_bt(As + (size_t)k * 64 * kStride, Bs + (size_t)k * 128 * kStride, acc, warp, lane);
   }
+  if (warp >= 8) return;
 #pragma unroll
   for (int hf = 0; hf < 2; hf++) {
     const int r = r0 + (warp & 3) * 16 + hf * 8 + (lane >> 2);
@@ -417,7 +400,7 @@ int32_t launch_mla_merge_vup_mma(Device* dev, const float* part_o, const float* 
   dim3 grid(H, (rows + 63) / 64);
   const size_t smem = (size_t)(dC / 128) * (64 + 128) * kStride * 2;
   RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_merge_vup_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  mla_merge_vup_mma_kernel<<<grid, 256, smem, dev->stream>>>(part_o, part_ml, chunk_off, W_UV, out, rows, S, H, dC);
+  mla_merge_vup_mma_kernel<<<grid, 32 * kMergeWarps, smem, dev->stream>>>(part_o, part_ml, chunk_off, W_UV, out, rows, S, H, dC);
   RELUX_CUDA_TRY(cudaGetLastError());
   count_launch(dev);
   return RELUX_OK;
