@@ -666,3 +666,34 @@ def test_mla_prefill_float32_queries_unmasked_and_named_sequences(dev, oracle):
     check_attention(out, ref, "mla prefill unmasked", max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
     assert pool.status() == 0
     pool.destroy(); d_wuk.free(); d_wuv.free()
+
+
+def test_mla_prefill_with_rows_past_the_cursor(dev, oracle):
+    """A verify call long enough for the prompt path: 130 draft rows written past the cursor (extra_tokens = 130), expanded
+    and attended causally; the committed lengths stay where they were.  Against the restatement on the cache + drafts."""
+    rng = np.random.default_rng(702)
+    H, Dh, dC, dHR, S = 16, 128, 512, 64, 130
+    ctx = [70, 200]
+    B = len(ctx)
+    pool, cl, rl = build_mla(dev, oracle, rng, ctx, dC, dHR, extra_pages=4)
+    wuk = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02)
+    wuv = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02)
+    d_wuk, d_wuv = dev.upload(wuk), dev.upload(wuv)
+    dc = rng.standard_normal((B * S, dC)).astype(np.float32)
+    dr = rng.standard_normal((B * S, dHR)).astype(np.float32)
+    qc = oracle.bf16_from_f32(rng.standard_normal((B, S, H, Dh)).astype(np.float32))
+    qr = oracle.bf16_from_f32(rng.standard_normal((B, S, H, dHR)).astype(np.float32))
+    out = np.full((B, S, H, Dh), np.nan, np.float32)
+    scale = float(1.0 / np.sqrt(Dh + dHR))
+    pool.verify(0, B, qc, out, dc, dr, H, Dh, scale, S, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv)
+    assert [pool.seq_len(0, b) for b in range(B)] == ctx
+    full = [c + S for c in ctx]
+    C_ = [np.concatenate([cl[b, :ctx[b]], oracle.bf16_from_f32(dc[b * S:(b + 1) * S])]) for b in range(B)]
+    R_ = [np.concatenate([rl[b, :ctx[b]], oracle.bf16_from_f32(dr[b * S:(b + 1) * S])]) for b in range(B)]
+    Cl = ragged_to_padded(np.concatenate(C_), full, (dC,))
+    Rl = ragged_to_padded(np.concatenate(R_), full, (dHR,))
+    with oracle.exact_exp():
+        ref = oracle.mla_attend(Cl, Rl, full, oracle.f32_from_bf16(qc), oracle.f32_from_bf16(qr), wuk, wuv, scale, causal=True, absorbed=False)
+    check_attention(out, ref, "mla prefill over draft rows", max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+    assert pool.status() == 0
+    pool.destroy(); d_wuk.free(); d_wuv.free()

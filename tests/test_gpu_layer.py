@@ -181,6 +181,17 @@ def test_layer_fast_mode_tcgen05_shapes(dev, oracle):
         _close(oracle, got, ref, "step %d" % i)
 
 
+def test_layer_fast_mode_prompt_on_the_prefill_kernels(dev, oracle):
+    """128 heads x 128, latent 512, rope 64 over dModel 1024, a 150-token prompt after 70 and 0 cached rows: inside relux_mla_forward_cached the attention
+    of a prompt expands the cached latents and runs the tcgen05 prefill kernel; a decode step follows on the rows the
+    prompt appended."""
+    from relux_b200 import lib as L
+    with oracle.exact_exp():
+        results, _ = run_steps(dev, oracle, 15, 1024, 128, 512, 64, [70, 0], [150, 1], L.ATTN_FAST, capacity=512)
+    for i, (got, ref) in enumerate(results):
+        _close(oracle, got, ref, "step %d" % i)
+
+
 def test_layer_errors(dev, oracle):
     import relux_b200 as rb
     from relux_b200 import lib as L
