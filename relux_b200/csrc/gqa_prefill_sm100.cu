@@ -98,7 +98,10 @@ constexpr int kSoftmaxThreads = 32 * kSoftmaxWarps, kThreads = kSoftmaxThreads +
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kTmemS = 0, kTmemO = 256;                  // S(g) at kTmemS + 128 (g & 1); O of item n at kTmemO + 128 (n & 1)
 constexpr float kRescaleThreshold = 8.0f;
-constexpr int kPolyPairsOf8 = 3;   // score pairs out of every eight whose exponential runs on the FMA pipe
+#ifndef RELUX_PREFILL_POLY_PAIRS
+#define RELUX_PREFILL_POLY_PAIRS 3
+#endif
+constexpr int kPolyPairsOf8 = RELUX_PREFILL_POLY_PAIRS;   // score pairs out of every eight whose exponential runs on the FMA pipe
 
 struct Bars {
   uint64_t q_full[2], q_empty[2], k_full[kMaxDepth], k_empty[kMaxDepth], v_full[kMaxDepth], v_empty[kMaxDepth], s_full[2], p_full, pv_done;
