@@ -214,7 +214,9 @@ int32_t relux_pool_read_rows(relux_pool_t pool, const relux_read_rows_args* args
 #define RELUX_TUNE_MLA_PROMPT_MIN_TOKENS 10 /* RELUX_MLA_PROMPT_MIN_TOKENS: query tokens per sequence from which an MLA call expands
                                            K / V and runs the tcgen05 prefill kernel (128; a huge value turns the path off) */
 #define RELUX_TUNE_MLA_PROMPT_SCRATCH_MB 11 /* RELUX_MLA_PROMPT_SCRATCH_MB: most device memory the expanded K / V may take (16384) */
-#define RELUX_TUNE_COUNT 12
+#define RELUX_TUNE_KERNEL_TIMING_STRIDE 12 /* RELUX_KERNEL_TIMING_STRIDE: the MLA decode kernel's event pair is recorded on every
+                                           Nth call (1); the pairs are what relux_pool_kernel_ms_* read */
+#define RELUX_TUNE_COUNT 13
 /* Changes one tuning knob of a pool (see RELUX_TUNE_*).  A pool takes its defaults once, when it is created, from the
  * environment variables named beside the knobs; no call reads the environment afterwards.  value < 0 restores the
  * built-in default.  Tuning aid: no counterpart in the reference. */

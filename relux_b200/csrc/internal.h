@@ -136,6 +136,7 @@ struct Pool {
   static constexpr int kTimeRing = 8192;
   cudaEvent_t ev_ring[kTimeRing][2] = {};
   uint64_t timed_calls = 0;
+  uint64_t attn_calls = 0;   // MLA decode calls, timed or not (RELUX_TUNE_KERNEL_TIMING_STRIDE)
   cudaEvent_t proj_ring[kTimeRing][2] = {};   // same, around the input-projection GEMM of the layer step
   uint64_t proj_calls = 0;
   static cudaEvent_t ring_event(cudaEvent_t (*ring)[2], uint64_t call, int which) {

@@ -345,7 +345,11 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
     rc = grow(p->dev, p->o_lat, (size_t)rows * H * dC * sizeof(float));
     if (rc) return rc;
   }
-  RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), st));
+  // the event pair around the decode kernel: on every call, or on every Nth (the records are not free: they sit
+  // between this launch and its neighbours)
+  const int stride = std::max(1, p->tune.get(RELUX_TUNE_KERNEL_TIMING_STRIDE));
+  const bool timed = (p->attn_calls++ % (uint64_t)stride) == 0;
+  if (timed) RELUX_CUDA_TRY(cudaEventRecord(p->ev_begin(), st));
   if (sm100) {
     rc = launch_mla_decode_sm100(p, sb, a, plan, (const uint16_t*)p->q_abs.p);
     if (rc) return rc;
@@ -378,8 +382,10 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
     }
     if (rc) return rc;
   }
-  RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), st));
-  p->timed_calls++;
+  if (timed) {
+    RELUX_CUDA_TRY(cudaEventRecord(p->ev_end(), st));
+    p->timed_calls++;
+  }
   count_launch(p->dev);
   if (fused_merge) {
     // split-KV merge fused into the up-projection: the merged latent output never touches HBM

@@ -245,37 +245,55 @@ __device__ __forceinline__ void merge_rows_warp(uint16_t* As, const float* __res
       const int i = r / S;
       const int c0 = __ldg(chunk_off + i), c1 = __ldg(chunk_off + i + 1);
       const size_t prow = (size_t)(r % S) * H + h;
+      // (max, sum) of this lane's item of every group of 32, and at the same time the partial rows of the first four
+      // items: one memory round trip serves the common case of a sequence cut into a handful of items
+      const int n_items = c1 - c0;
+      if (n_items <= 0) goto store_row;   // no partial to merge: a zero row
+      float2 ml = make_float2(-INFINITY, 0.f);
+      if (lane < n_items) ml = __ldg(reinterpret_cast<const float2*>(part_ml + ((size_t)(c0 + lane) * rows_total + prow) * 2));
+      float4 x[4][kMaxChunks];
+      const int ng0 = min(32, n_items);
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        const int c = c0 + min(u, ng0 - 1);   // a short group re-reads its last item with weight 0
+        const float4* src = reinterpret_cast<const float4*>(part_o + ((size_t)c * rows_total + prow) * dC) + lane;
+#pragma unroll
+        for (int k = 0; k < kMaxChunks; k++)
+          if (k < nk) x[u][k] = __ldg(src + k * 32);
+      }
       // global maximum and normaliser over all items of the sequence
-      float M = -INFINITY;
-      for (int c = c0 + lane; c < c1; c += 32) M = fmaxf(M, __ldg(part_ml + ((size_t)c * rows_total + prow) * 2));
+      float M = ml.x;
+      for (int c = c0 + 32 + lane; c < c1; c += 32) M = fmaxf(M, __ldg(part_ml + ((size_t)c * rows_total + prow) * 2));
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-      float L = 0.f;
-      for (int c = c0 + lane; c < c1; c += 32) {
-        const float2 ml = __ldg(reinterpret_cast<const float2*>(part_ml + ((size_t)c * rows_total + prow) * 2));
-        if (ml.x != -INFINITY) L += ml.y * exp2f(ml.x - M);
+      float L = (ml.x != -INFINITY) ? ml.y * exp2f(ml.x - M) : 0.f;
+      for (int c = c0 + 32 + lane; c < c1; c += 32) {
+        const float2 t = __ldg(reinterpret_cast<const float2*>(part_ml + ((size_t)c * rows_total + prow) * 2));
+        if (t.x != -INFINITY) L += t.y * exp2f(t.x - M);
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
       const float inv = (L > 0.f) ? 1.0f / L : 0.f;
       for (int cb = c0; cb < c1; cb += 32) {
         // this lane's item of the group of 32: its weight; then four items at a time, weights by shuffle
-        const int cm = cb + lane;
         float w_mine = 0.f;
-        if (cm < c1) {
-          const float m = __ldg(part_ml + ((size_t)cm * rows_total + prow) * 2);
+        if (cb == c0) {
+          w_mine = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - M) * inv;
+        } else if (cb + lane < c1) {
+          const float m = __ldg(part_ml + ((size_t)(cb + lane) * rows_total + prow) * 2);
           w_mine = (m == -INFINITY) ? 0.f : exp2f(m - M) * inv;
         }
         const int ng = min(32, c1 - cb);
         for (int j = 0; j < ng; j += 4) {
-          float4 x[4][kMaxChunks];
+          if (cb != c0 || j != 0) {   // the first four items of the row are in flight already
 #pragma unroll
-          for (int u = 0; u < 4; u++) {
-            const int c = cb + min(j + u, ng - 1);   // a short group re-reads its last item with weight 0
-            const float4* src = reinterpret_cast<const float4*>(part_o + ((size_t)c * rows_total + prow) * dC) + lane;
+            for (int u = 0; u < 4; u++) {
+              const int c = cb + min(j + u, ng - 1);
+              const float4* src = reinterpret_cast<const float4*>(part_o + ((size_t)c * rows_total + prow) * dC) + lane;
 #pragma unroll
-            for (int k = 0; k < kMaxChunks; k++)
-              if (k < nk) x[u][k] = __ldg(src + k * 32);
+              for (int k = 0; k < kMaxChunks; k++)
+                if (k < nk) x[u][k] = __ldg(src + k * 32);
+            }
           }
 #pragma unroll
           for (int u = 0; u < 4; u++) {
@@ -293,6 +311,7 @@ __device__ __forceinline__ void merge_rows_warp(uint16_t* As, const float* __res
         }
       }
     }
+  store_row:
 #pragma unroll
     for (int k = 0; k < kMaxChunks; k++)
       if (k < nk)
