@@ -177,3 +177,102 @@ def test_config5_full_batch_properties(dev, oracle):
     Vl = np.stack([np.concatenate([np.tile(Vb[b * blk:(b + 1) * blk], (T0 // blk, 1, 1)), oracle.bf16_from_f32(dV[b * S:(b + 1) * S])]) for b in sample])
     ref = oracle.gqa_attend(Kl, Vl, [T0 + S] * len(sample), q[sample], scale, causal=True)
     check_attention(outs[0][sample], ref, "config 5 sample")
+
+
+def test_mla_prompt_full_size_properties(dev, oracle):
+    """An MLA prompt at the benchmark's widths (128 heads, 2 sequences x 2048 tokens, the second after 300 cached rows)
+    on the expansion + prefill kernels, through properties that need no full CPU run: the result does not depend on the
+    page permutation (bit for bit), agrees with the absorbed decode kernels on the same inputs (two different
+    algorithms: expanded 192-wide scores against 576-wide latent scores), and the last query token of every sequence,
+    which sees the whole cache like a decode step, agrees with the restatement's one-token call."""
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(31)
+    H, Dh, dC, dHR, S = 128, 128, 512, 64, 2048
+    ctx = [S, 300 + S]
+    B = len(ctx)
+    c = oracle.bf16_from_f32(rng.standard_normal((int(np.sum(ctx)), dC), dtype=np.float32))
+    r = oracle.bf16_from_f32(rng.standard_normal((int(np.sum(ctx)), dHR), dtype=np.float32))
+    wuk = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh), dtype=np.float32) * 0.02)
+    wuv = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh), dtype=np.float32) * 0.02)
+    d_wuk, d_wuv = dev.upload(wuk), dev.upload(wuv)
+    qc = oracle.bf16_from_f32(rng.standard_normal((B, S, H, Dh), dtype=np.float32))
+    qr = oracle.bf16_from_f32(rng.standard_normal((B, S, H, dHR), dtype=np.float32))
+    scale = float(1.0 / np.sqrt(Dh + dHR))
+    outs = []
+    for perm_seed in (1, 2):
+        pool = _mla_full(dev, oracle, rng, B, ctx, perm_seed)
+        pool.append(0, c, r, B, n_new=np.asarray(ctx, np.int32))
+        out = np.full((B, S, H, Dh), np.nan, np.float32)
+        n0 = dev.launch_count()
+        pool.decode(0, B, qc, out, H, Dh, scale, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv, q_tokens=S, causal=True)
+        assert dev.launch_count() - n0 == 3
+        assert pool.status() == 0
+        outs.append(out)
+        if perm_seed == 2:
+            pool.tune(L.TUNE_MLA_PROMPT_MIN_TOKENS, 1 << 30)   # the same call on the absorbed decode kernels
+            out_abs = np.full((B, S, H, Dh), np.nan, np.float32)
+            pool.decode(0, B, qc, out_abs, H, Dh, scale, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv, q_tokens=S, causal=True)
+            assert pool.status() == 0
+        pool.destroy()
+    assert np.array_equal(outs[0], outs[1]), "the result depends on the page permutation"
+    check_attention(outs[0], out_abs, "mla prompt: prefill kernels against the absorbed decode kernels")
+    # the last query token of every sequence against the restatement (one token over the whole cache)
+    Tm = max(ctx)
+    cl = np.zeros((B, Tm, dC), np.uint16)
+    rl = np.zeros((B, Tm, dHR), np.uint16)
+    o = 0
+    for b in range(B):
+        cl[b, :ctx[b]] = c[o:o + ctx[b]]
+        rl[b, :ctx[b]] = r[o:o + ctx[b]]
+        o += ctx[b]
+    with oracle.exact_exp():
+        ref = oracle.mla_attend(cl, rl, ctx, oracle.f32_from_bf16(qc[:, -1:]), oracle.f32_from_bf16(qr[:, -1:]), wuk, wuv, scale, causal=True,
+                                absorbed=False)
+    check_attention(outs[0][:, -1:], ref, "mla prompt: last token against the restatement")
+    d_wuk.free(); d_wuv.free()
+
+
+def test_gqa_prompt_full_size_properties(dev, oracle):
+    """A GQA prompt at the benchmark's widths (32 heads / 8 kv heads, 2 sequences x 4096 tokens, the second after 500
+    cached rows) on the prefill kernel: independent of the page permutation bit for bit, equal within tolerance to the
+    grid slices of the decode kernel (another algorithm: split-KV partials and a merge), last token against the
+    restatement."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(32)
+    H, Hkv, D, S, P = 32, 8, 128, 4096, 64
+    ctx = [S, 500 + S]
+    B = len(ctx)
+    K = oracle.bf16_from_f32(rng.standard_normal((int(np.sum(ctx)), Hkv, D), dtype=np.float32))
+    V = oracle.bf16_from_f32(rng.standard_normal((int(np.sum(ctx)), Hkv, D), dtype=np.float32))
+    q = oracle.bf16_from_f32(rng.standard_normal((B, S, H, D), dtype=np.float32))
+    scale = float(1.0 / np.sqrt(D))
+    pages_per = (max(ctx) + P - 1) // P + 1
+    outs = []
+    for perm_seed in (1, 2):
+        pool = rb.Pool(dev, L.POOL_GQA, 1, B * pages_per, P, B, pages_per, num_kv_heads=Hkv, head_dim=D)
+        pool.set_tables(np.random.default_rng(perm_seed).permutation(B * pages_per).astype(np.int32).reshape(B, pages_per))
+        pool.append(0, K, V, B, n_new=np.asarray(ctx, np.int32))
+        out = np.full((B, S, H, D), np.nan, np.float32)
+        pool.decode(0, B, q, out, H, D, scale, q_tokens=S, causal=True)
+        assert pool.status() == 0
+        outs.append(out)
+        if perm_seed == 2:
+            pool.tune(L.TUNE_GQA_PROMPT_SLICES, 1)
+            out_sl = np.full((B, S, H, D), np.nan, np.float32)
+            pool.decode(0, B, q, out_sl, H, D, scale, q_tokens=S, causal=True)
+            assert pool.status() == 0
+        pool.destroy()
+    assert np.array_equal(outs[0], outs[1]), "the result depends on the page permutation"
+    check_attention(outs[0], out_sl, "gqa prompt: prefill kernel against the decode kernel's grid slices")
+    Tm = max(ctx)
+    Kl = np.zeros((B, Tm, Hkv, D), np.uint16)
+    Vl = np.zeros((B, Tm, Hkv, D), np.uint16)
+    o = 0
+    for b in range(B):
+        Kl[b, :ctx[b]] = K[o:o + ctx[b]]
+        Vl[b, :ctx[b]] = V[o:o + ctx[b]]
+        o += ctx[b]
+    with oracle.exact_exp():
+        ref = oracle.gqa_attend(Kl, Vl, ctx, oracle.f32_from_bf16(q[:, -1:]), scale, causal=True)
+    check_attention(outs[0][:, -1:], ref, "gqa prompt: last token against the restatement")
