@@ -551,6 +551,31 @@ typedef struct relux_matmul_args {
 } relux_matmul_args;
 int32_t relux_matmul_f32_bf16(relux_pool_t pool, const relux_matmul_args* args);
 
+/* ---- expansion of the cached MLA latents --------------------------------------------------------
+ * What MLA.forwardCached does before it scores a multi-token call: every cached latent row times W_UK and W_UV
+ * (internal/transformer/mla.go:323-326), here as one tensor-core GEMM with bf16 results.  The library's own prompt path
+ * (relux_mla_decode with 128 or more query tokens) runs it into an internal scratch array; this entry point runs it
+ * into the caller's memory.
+ *   kv_out     device bf16 [2 * num_heads][rows_total][128]: keys of head h at block h, values at block num_heads + h;
+ *              row = seq_base[i] + token for the i-th named sequence
+ *   seq_base   device int32 [n_seqs + 1], written by the call: first row of every sequence (lengths rounded up to 256;
+ *              rows past a sequence's end hold values computed from whatever its last page holds)
+ *   rows_total as returned by a first call with kv_out == NULL (host value; nothing is launched then)
+ * Shapes: latent 512, 64-token pages, head width 128, FAST arithmetic; other pools get RELUX_ERR_UNSUPPORTED. */
+typedef struct relux_mla_expand_args {
+  int32_t layer, n_seqs;
+  const int32_t* seq_ids;      /* host, or NULL = 0..n_seqs-1 */
+  int32_t extra_tokens, num_heads;
+  const void* w_uk;            /* device bf16 [dC][num_heads * 128] */
+  const void* w_uv;            /* device bf16 [dC][num_heads * 128] */
+  void* kv_out;                /* device, or NULL to ask for rows_total only */
+  int32_t* seq_base;           /* device */
+  int64_t rows_total;          /* in (when kv_out != NULL) */
+  int64_t* rows_total_out;     /* host, may be NULL */
+  int32_t reserved[4];
+} relux_mla_expand_args;
+int32_t relux_mla_expand_kv(relux_pool_t pool, const relux_mla_expand_args* args);
+
 /* ---- weight import -------------------------------------------------------------------------------
  * Brings the attention weights of one MLA layer from checkpoint layout into the device layout the layer calls take.
  * The reference's DeepSeek mapper names the checkpoint tensors (internal/loader/mapper.go:139-180): q_proj -> mla.W_Q,

@@ -281,6 +281,26 @@ class Pool:
                                q_pe_proj=src(q_pe_proj), k_pe_proj=src(k_pe_proj), dst=C.pointer(w))
         L.check(self.lib.relux_mla_import_weights(self.h, C.byref(args)))
 
+    def expand_kv(self, layer, n_seqs, num_heads, w_uk, w_uv, seq_ids=None, extra_tokens=0):
+        """Cached MLA latents times W_UK / W_UV (relux_mla_expand_kv).  Returns (k, v, seq_base): k, v uint16 (bf16 bits)
+        [num_heads][rows_total][128] host arrays, seq_base int32 [n_seqs + 1] (first row of every sequence)."""
+        ids = None if seq_ids is None else np.ascontiguousarray(seq_ids, dtype=np.int32)
+        rows = C.c_int64()
+        args = L.MlaExpandArgs(layer=layer, n_seqs=n_seqs, seq_ids=_ptr(ids), extra_tokens=extra_tokens, num_heads=num_heads,
+                               w_uk=_ptr(w_uk), w_uv=_ptr(w_uv), kv_out=None, seq_base=None, rows_total=0,
+                               rows_total_out=C.pointer(rows))
+        L.check(self.lib.relux_mla_expand_kv(self.h, C.byref(args)))
+        n = int(rows.value)
+        kv = self.dev.alloc(2 * num_heads * n * 128 * 2, L.DTYPE_BF16)
+        L.check(self.lib.relux_cuda_memset(self.dev.h, kv.ptr, 0xFF, kv.nbytes))   # NaN bit patterns: a row the kernel misses shows
+        base = self.dev.alloc((n_seqs + 1) * 4, L.DTYPE_F32)
+        args.kv_out, args.seq_base, args.rows_total = kv.ptr, base.ptr, n
+        L.check(self.lib.relux_mla_expand_kv(self.h, C.byref(args)))
+        out = kv.download((2, num_heads, n, 128), np.uint16)
+        sb = base.download((n_seqs + 1,), np.int32)
+        kv.free(); base.free()
+        return out[0], out[1], sb
+
     def selftest_wait(self, polls):
         """Runs the bounded-wait self test (a wait nobody answers, `polls` polls): afterwards status() reports ERR_TIMEOUT."""
         L.check(self.lib.relux_pool_selftest_wait(self.h, int(polls)))

@@ -571,8 +571,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         float ps0, ps1;
         unpack2(ps2, ps0, ps1);
         l_run = l_run * alpha + (ps0 + ps1);
-        // O may be rescaled only after PV(g-1) has completed
-        if (j > 0) wait_bar(&bars->pv_done, (g - 1) & 1, bars, prm.status);
+        // O may be rescaled only after PV(g-1) has completed.  The wait is made on an item's first tile too (PV(g-1) is then
+        // the previous item's last one): PV(g-1) was issued behind the completion of p_full's phase g-1, so no warp arrives
+        // for tile g before every warp OF BOTH CTAs has arrived for tile g-1.  Without it the softmax warps of one CTA,
+        // which after an item's last tile wait for nothing but S of the next item's first tile (computed ahead), could
+        // arrive twice while a warp of the other CTA was still writing P(g-1): p_full's phase g-1 completed early and the
+        // item's last PV read an unfinished P.
+        if (g > 0) wait_bar(&bars->pv_done, (g - 1) & 1, bars, prm.status);
         __syncwarp();
         // The TMEM loads and stores are warp-collective: the decision is taken for the whole warp, and the rows that keep
         // their maximum multiply by one.  This thread's slice of the row: output dims kCols hb .. +kCols-1.

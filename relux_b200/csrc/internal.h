@@ -190,6 +190,10 @@ int32_t launch_attn_reference_mla(Pool* p, const SeqBatch& sb, const relux_attn_
                                   float* d_out);
 int32_t launch_gqa_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const void* d_q, void* d_out);
 // True when this call is a multi-token call that the tcgen05 prefill kernel serves (it takes bf16 queries).
+bool mla_expand_eligible(const Pool* p, int num_heads, int head_dim);
+int64_t mla_expand_rows(const Pool* p, const SeqBatch& sb, int layer, int extra);
+int32_t launch_mla_expand_sm100(Pool* p, const SeqBatch& sb, int layer, int extra, int H, const uint16_t* w_uk, const uint16_t* w_uv,
+                                int64_t Ttot, uint16_t* kx, uint16_t* vx, int32_t* seq_base);
 bool mla_prefill_eligible(const Pool* p, const SeqBatch& sb, const relux_attn_args& a);
 bool gqa_prompt_wants_bf16(const Pool* p, const relux_attn_args& a);
 // The new rows of a decode step handed to the attention call, for the fused preparation (one launch for absorb + append +

@@ -1176,6 +1176,38 @@ API int32_t relux_gqa_step(relux_pool_t h, const relux_append_args* kv, const re
   return do_step(p, kv, attn, RELUX_POOL_GQA);
 }
 
+API int32_t relux_mla_expand_kv(relux_pool_t h, const relux_mla_expand_args* a) {
+  GET_POOL(h);
+  if (!a) { set_error("nil argument struct"); return RELUX_ERR_INVALID_ARG; }
+  if (p->prm.kind != RELUX_POOL_MLA) { set_error("pool kind does not match this call (MLA pool needed)"); return RELUX_ERR_INVALID_ARG; }
+  int32_t rc = check_layer(p, a->layer);
+  if (rc) return rc;
+  if (a->num_heads <= 0 || a->extra_tokens < 0) { set_error("bad expansion arguments"); return RELUX_ERR_INVALID_ARG; }
+  if (p->compat || !mla_expand_eligible(p, a->num_heads, 128)) {
+    set_error("the expansion kernel covers latent 512, 64-token pages and 128-wide heads on an ordinary pool");
+    return RELUX_ERR_UNSUPPORTED;
+  }
+  SeqBatch sb;
+  rc = stage_batch(p, a->n_seqs, a->seq_ids, nullptr, 1, &sb);
+  if (rc) return rc;
+  const int64_t rows = mla_expand_rows(p, sb, a->layer, a->extra_tokens);
+  if (a->rows_total_out) *a->rows_total_out = rows;
+  if (!a->kv_out) return RELUX_OK;
+  if (!a->w_uk || !a->w_uv || !a->seq_base || a->rows_total != rows) {
+    set_error("expansion: nil weights / seq_base, or rows_total=%lld does not match the cached lengths (%lld)", (long long)a->rows_total,
+              (long long)rows);
+    return RELUX_ERR_INVALID_ARG;
+  }
+  if (2 * (int64_t)a->num_heads * rows >= ((int64_t)1 << 31)) { set_error("expansion: more rows than one launch addresses"); return RELUX_ERR_UNSUPPORTED; }
+  if ((rc = check_dev_align(a->w_uk, "w_uk")) || (rc = check_dev_align(a->w_uv, "w_uv")) || (rc = check_dev_align(a->kv_out, "kv_out"))) return rc;
+  uint16_t* kx = (uint16_t*)a->kv_out;
+  rc = launch_mla_expand_sm100(p, sb, a->layer, a->extra_tokens, a->num_heads, (const uint16_t*)a->w_uk, (const uint16_t*)a->w_uv, rows, kx,
+                               kx + (size_t)a->num_heads * rows * 128, a->seq_base);
+  if (rc) return rc;
+  RELUX_CUDA_TRY(cudaStreamSynchronize(dev->stream));
+  return RELUX_OK;
+}
+
 API int32_t relux_gqa_verify(relux_pool_t h, const relux_attn_args* attn, const relux_append_args* kv) {
   GET_POOL(h);
   return do_verify(p, attn, kv, RELUX_POOL_GQA);

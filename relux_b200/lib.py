@@ -37,7 +37,7 @@ EXPORTS = [
     "relux_pool_read_rows", "relux_mla_append", "relux_gqa_append", "relux_mla_decode", "relux_gqa_decode", "relux_gqa_verify",
     "relux_mla_verify", "relux_pool_last_kernel_ms", "relux_pool_kernel_ms_mean", "relux_mla_forward_cached", "relux_gqa_forward_cached", "relux_stream_partition", "relux_seq_save_file", "relux_seq_load_file", "relux_pool_projection_ms_mean", "relux_gqa_decode_noalloc",
     "relux_spec_accept", "relux_sampler_sample", "relux_pool_tune", "relux_pool_kernel_ms_list", "relux_matmul_f32_bf16",
-    "relux_mla_import_weights", "relux_pool_selftest_wait", "relux_pool_wait_output", "relux_mla_step", "relux_gqa_step",
+    "relux_mla_import_weights", "relux_pool_selftest_wait", "relux_pool_wait_output", "relux_mla_step", "relux_gqa_step", "relux_mla_expand_kv",
 ]
 
 
@@ -95,6 +95,12 @@ class MlaImportArgs(C.Structure):
                 ("dc", C.c_int32), ("src_dtype", C.c_int32), ("src_mem", C.c_int32), ("fused_rope", C.c_int32),
                 ("reserved", C.c_int32 * 3), ("q_proj", C.c_void_p), ("kv_a_proj_with_mqa", C.c_void_p), ("kv_b_proj", C.c_void_p),
                 ("o_proj", C.c_void_p), ("q_pe_proj", C.c_void_p), ("k_pe_proj", C.c_void_p), ("dst", C.POINTER(MlaLayerWeights))]
+
+
+class MlaExpandArgs(C.Structure):
+    _fields_ = [("layer", C.c_int32), ("n_seqs", C.c_int32), ("seq_ids", C.c_void_p), ("extra_tokens", C.c_int32), ("num_heads", C.c_int32),
+                ("w_uk", C.c_void_p), ("w_uv", C.c_void_p), ("kv_out", C.c_void_p), ("seq_base", C.c_void_p), ("rows_total", C.c_int64),
+                ("rows_total_out", C.POINTER(C.c_int64)), ("reserved", C.c_int32 * 4)]
 
 
 class GqaLayerWeights(C.Structure):
@@ -185,6 +191,7 @@ def load():
         L.relux_pool_kernel_ms_list.argtypes = [C.c_void_p, C.c_int32, C.c_void_p, C.POINTER(C.c_int32)]
         L.relux_matmul_f32_bf16.argtypes = [C.c_void_p, C.POINTER(MatmulArgs)]
         L.relux_mla_import_weights.argtypes = [C.c_void_p, C.POINTER(MlaImportArgs)]
+        L.relux_mla_expand_kv.argtypes = [C.c_void_p, C.POINTER(MlaExpandArgs)]
         L.relux_pool_selftest_wait.argtypes = [C.c_void_p, C.c_int32]
         for n in ("relux_mla_append", "relux_gqa_append"):
             getattr(L, n).argtypes = [C.c_void_p, C.POINTER(AppendArgs)]
