@@ -697,3 +697,118 @@ def test_mla_prefill_with_rows_past_the_cursor(dev, oracle):
     check_attention(out, ref, "mla prefill over draft rows", max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
     assert pool.status() == 0
     pool.destroy(); d_wuk.free(); d_wuv.free()
+
+
+def test_prefill_short_items_followed_by_other_items(dev, oracle):
+    """Items of two tiles whose second tile holds a single key (129 cached rows), several of them per worker (128 heads):
+    the last PV of such an item must not start before both CTAs of the pair have written its P.  A build in which the
+    softmax warps of one CTA could run one tile ahead across an item boundary failed this case in about half of the
+    runs; it is repeated here on fresh pools with other page permutations."""
+    rng = np.random.default_rng(5)
+    B, S, H, Dh, dC, dHR, P = 2, 129, 128, 128, 512, 64, 64
+    ctx = [200 + S, S]
+    pages_per = (max(ctx) + P - 1) // P + 1
+    c = rng.standard_normal((sum(ctx), dC)).astype(np.float32)
+    r = rng.standard_normal((sum(ctx), dHR)).astype(np.float32)
+    wuk = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02)
+    wuv = oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02)
+    d_wuk, d_wuv = dev.upload(wuk), dev.upload(wuv)
+    q = oracle.bf16_from_f32(rng.standard_normal((B, S, H, Dh)).astype(np.float32))
+    qr = oracle.bf16_from_f32(rng.standard_normal((B, S, H, dHR)).astype(np.float32))
+    scale = float(1.0 / np.sqrt(Dh + dHR))
+    cl = ragged_to_padded(oracle.bf16_from_f32(c), ctx, (dC,))
+    rl = ragged_to_padded(oracle.bf16_from_f32(r), ctx, (dHR,))
+    with oracle.exact_exp():
+        ref = oracle.mla_attend(cl, rl, ctx, oracle.f32_from_bf16(q), oracle.f32_from_bf16(qr), wuk, wuv, scale, causal=False, absorbed=False)
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    for it in range(12):
+        pool = rb.Pool(dev, L.POOL_MLA, 1, B * pages_per, P, B, pages_per, dC=dC, dHR=dHR)
+        pool.set_tables(np.random.default_rng(it).permutation(B * pages_per).astype(np.int32).reshape(B, pages_per))
+        pool.append(0, c, r, B, n_new=np.asarray(ctx, np.int32))
+        out = np.full((B, S, H, Dh), np.nan, np.float32)
+        pool.decode(0, B, q, out, H, Dh, scale, q_rope=qr, w_uk=d_wuk, w_uv=d_wuv, q_tokens=S, causal=False)
+        check_attention(out, ref, "run %d" % it, max_tol=EDGE_MAX, mean_tol=EDGE_MEAN)
+        assert pool.status() == 0
+        pool.destroy()
+    d_wuk.free(); d_wuv.free()
+
+
+def test_mla_expand_kv_against_a_plain_product(dev, oracle):
+    """relux_mla_expand_kv: cached latents times W_UK / W_UV into the caller's memory (pre-filled with NaN patterns by
+    the binding), against a float32 product of the same bf16 operands; every row up to the rounded lengths is written."""
+    rng = np.random.default_rng(77)
+    H, dC, dHR = 24, 512, 64
+    ctx = [87, 417, 57, 256]
+    B = len(ctx)
+    pool, cl, rl = build_mla(dev, oracle, rng, ctx, dC, dHR)
+    wuk = oracle.bf16_from_f32(rng.standard_normal((dC, H * 128)).astype(np.float32) * 0.02)
+    wuv = oracle.bf16_from_f32(rng.standard_normal((dC, H * 128)).astype(np.float32) * 0.02)
+    d_wuk, d_wuv = dev.upload(wuk), dev.upload(wuv)
+    ids = np.array([2, 0, 3, 1], np.int32)
+    k, v, base = pool.expand_kv(0, B, H, d_wuk, d_wuv, seq_ids=ids)
+    assert base.tolist() == [0, 256, 512, 768, 1280]   # lengths 57, 87, 256, 417 rounded up to 256
+    assert np.isfinite(oracle.f32_from_bf16(k)).all() and np.isfinite(oracle.f32_from_bf16(v)).all()
+    for i, b in enumerate(ids):
+        lat = oracle.f32_from_bf16(cl[b, :ctx[b]])
+        for got, w in ((k, wuk), (v, wuv)):
+            ref = lat @ oracle.f32_from_bf16(w)
+            g = oracle.f32_from_bf16(got[:, base[i]:base[i] + ctx[b]]).transpose(1, 0, 2).reshape(ctx[b], H * 128)
+            assert np.abs(g - ref).max() <= 0.01 + 0.008 * np.abs(ref).max()
+    pool.destroy(); d_wuk.free(); d_wuv.free()
+
+
+def test_prefill_paths_agree_with_the_decode_paths_on_random_shapes(dev, oracle):
+    """A seeded sweep over shapes (MLA and GQA; 1-6 sequences; prompt lengths around the 128-row block and 256-row pair
+    boundaries; cached prefixes around the page boundary; causal or not; named sequences): the prefill kernels against
+    the decode-kernel paths of the same call (tuning knobs), both validated against the restatement at single shapes."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    P = 64
+    for case in range(24):
+        rng = np.random.default_rng(9000 + case)
+        mla = bool(rng.integers(0, 2))
+        B = int(rng.integers(1, 7))
+        S = int(rng.choice([128, 129, 191, 255, 256, 257, 300, 383, 384, 385, 511, 513]))
+        cached = [int(rng.choice([0, 0, 1, 63, 64, 65, 200, 511])) for _ in range(B)]
+        ctx = [c + S for c in cached]
+        causal = bool(rng.integers(0, 4) > 0)
+        pages_per = (max(ctx) + P - 1) // P + 1
+        ids = rng.permutation(B).astype(np.int32) if rng.integers(0, 2) else None
+        if mla:
+            H = int(rng.choice([1, 3, 16, 24, 128]))
+            Dh, dC, dHR = 128, 512, 64
+            pool = rb.Pool(dev, L.POOL_MLA, 1, B * pages_per, P, B, pages_per, dC=dC, dHR=dHR)
+            pool.set_tables(rng.permutation(B * pages_per).astype(np.int32).reshape(B, pages_per))
+            pool.append(0, rng.standard_normal((sum(ctx), dC)).astype(np.float32), rng.standard_normal((sum(ctx), dHR)).astype(np.float32), B,
+                        n_new=np.asarray(ctx, np.int32))
+            wuk = dev.upload(oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02))
+            wuv = dev.upload(oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02))
+            q = oracle.bf16_from_f32(rng.standard_normal((B, S, H, Dh)).astype(np.float32))
+            qr = oracle.bf16_from_f32(rng.standard_normal((B, S, H, dHR)).astype(np.float32))
+            kw = dict(q_rope=qr, w_uk=wuk, w_uv=wuv)
+            shape, scale, knob, launches = (B, S, H, Dh), float(1 / np.sqrt(Dh + dHR)), L.TUNE_MLA_PROMPT_MIN_TOKENS, 3
+        else:
+            Hkv, g = int(rng.choice([1, 2, 8])), int(rng.choice([1, 2, 4, 8, 16]))
+            H, D = Hkv * g, 128
+            pool = rb.Pool(dev, L.POOL_GQA, 1, B * pages_per, P, B, pages_per, num_kv_heads=Hkv, head_dim=D)
+            pool.set_tables(rng.permutation(B * pages_per).astype(np.int32).reshape(B, pages_per))
+            pool.append(0, rng.standard_normal((sum(ctx), Hkv, D)).astype(np.float32), rng.standard_normal((sum(ctx), Hkv, D)).astype(np.float32), B,
+                        n_new=np.asarray(ctx, np.int32))
+            q = oracle.bf16_from_f32(rng.standard_normal((B, S, H, D)).astype(np.float32))
+            kw = {}
+            shape, scale, knob, launches = (B, S, H, D), float(1 / np.sqrt(D)), L.TUNE_GQA_PROMPT_SLICES, 1
+        out = np.full(shape, np.nan, np.float32)
+        n0 = dev.launch_count()
+        pool.decode(0, B, q, out, shape[2], 128, scale, q_tokens=S, causal=causal, seq_ids=ids, **kw)
+        assert dev.launch_count() - n0 == launches, "case %d did not take the prefill path" % case
+        pool.tune(knob, 1 << 30 if mla else 1)
+        out2 = np.full(shape, np.nan, np.float32)
+        pool.decode(0, B, q, out2, shape[2], 128, scale, q_tokens=S, causal=causal, seq_ids=ids, **kw)
+        assert pool.status() == 0
+        assert np.isfinite(out).all() and np.isfinite(out2).all(), "case %d" % case
+        assert np.abs(out - out2).max() <= 1.5e-2, "case %d (%s B=%d S=%d cached=%s causal=%s): %g" % (
+            case, "mla" if mla else "gqa", B, S, cached, causal, np.abs(out - out2).max())
+        pool.destroy()
+        if mla:
+            wuk.free(); wuv.free()
