@@ -56,7 +56,9 @@ def test_struct_sizes_match_the_header(so):
         #include <stdio.h>
         #include "relux_cuda.h"
         #include <stddef.h>
-        int main(void){ printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(relux_read_rows_args), offsetof(relux_read_rows_args, dst_b),
+        int main(void){ printf("%zu %zu %zu %zu\\n", sizeof(relux_mla_expand_args), offsetof(relux_mla_expand_args, w_uk),
+                               offsetof(relux_mla_expand_args, rows_total), offsetof(relux_mla_expand_args, rows_total_out));
+                        printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(relux_read_rows_args), offsetof(relux_read_rows_args, dst_b),
                                sizeof(relux_stream_partition_args), offsetof(relux_stream_partition_args, chunk_off),
                                sizeof(relux_matmul_args), offsetof(relux_matmul_args, b), offsetof(relux_matmul_args, c),
                                sizeof(relux_mla_import_args), offsetof(relux_mla_import_args, q_proj), offsetof(relux_mla_import_args, dst));
@@ -74,6 +76,9 @@ def test_struct_sizes_match_the_header(so):
         exe = os.path.join(d, "s")
         subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
         sizes = [int(x) for x in subprocess.check_output([exe]).split()]
+    assert sizes[:4] == [C.sizeof(so.MlaExpandArgs), so.MlaExpandArgs.w_uk.offset, so.MlaExpandArgs.rows_total.offset,
+                         so.MlaExpandArgs.rows_total_out.offset]
+    sizes = sizes[4:]
     assert sizes[:10] == [C.sizeof(so.ReadRowsArgs), so.ReadRowsArgs.dst_b.offset, C.sizeof(so.StreamPartitionArgs),
                           so.StreamPartitionArgs.chunk_off.offset, C.sizeof(so.MatmulArgs), so.MatmulArgs.b.offset, so.MatmulArgs.c.offset,
                           C.sizeof(so.MlaImportArgs), so.MlaImportArgs.q_proj.offset, so.MlaImportArgs.dst.offset]
