@@ -71,8 +71,8 @@ constexpr int kMaxDepth = 4;
 //   GQA (kMla = false): score width 128.  Q tile [dims 0-63 | dims 64-127] x 2 buffers (items in turn), K stage = own
 //     page [dims 0-63 | dims 64-127] (16 KB), four K and four V stages: 64 + 64 + 64 = 192 KB.
 //   MLA (kMla = true): score width 192 = 128 expanded key dims + 64 shared RoPE dims.  Q tile [nope 0-63 | nope 64-127 |
-//     rope] (48 KB) x 2 buffers, K stage = own 64 keys [nope 0-63 | nope 64-127 | rope] (24 KB), four K and three V
-//     stages: 96 + 96 + 48 = 240 KB is too much: three K and three V stages, 96 + 72 + 48 = 216 KB.
+//     rope] (48 KB) x 2 buffers, K stage = own 64 keys [nope 0-63 | nope 64-127 | rope] (24 KB), three K and three V
+//     stages: 96 + 72 + 48 = 216 KB.
 // P never touches shared memory: the softmax warps write it, packed to bf16, over the first 64 columns of the S tile they
 // have just read, and PV takes its A operand from tensor memory.
 template <bool kMla>

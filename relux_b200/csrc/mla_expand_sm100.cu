@@ -18,14 +18,16 @@
 // (twice when the run crosses a token tile) and the 32 MB of weights stream from L2 through a four-stage ring.
 // The latent tile is the A operand of every MMA of a run: it is copied once from shared memory into tensor memory (lane =
 // token, two latents per 32-bit column, 256 columns), so that the MMAs read only the weight stages from shared memory.
-// With both operands there, an M256 N128 K16 step reads 4 KB of A + 2 KB of B per CTA and serves 2 KB of B to its
-// peer: 8 KB per 64 clocks, the whole shared-memory bandwidth, and the tensor pipe measured 52 % busy.
 // The accumulator is double-buffered in tensor memory: four epilogue warps convert unit n while the MMAs of unit n + 1
-// run (they also make the copy of the latent tile, between two runs of units).  The bf16 rows leave through a swizzled
-// shared tile and TMA stores: written straight from the row-per-thread registers, 16 bytes per lane at a 256-byte pitch,
-// they took twice the time of the unit's MMAs.
+// run (they also make the copy of the latent tile, between two runs of units), and the bf16 rows leave through a
+// swizzled shared tile and TMA stores (whole 128-byte lines instead of 16 bytes per lane at a 256-byte pitch).
+// What bounds the kernel is neither of those: every token tile streams all of W_UK and W_UV (32 MB at 128 heads), 256
+// flop per weight byte at 256 tokens per pair, and the L2 -> SM traffic measured 4.2 TB/s: 1.0-1.06 PFLOP/s with the latent
+// tile in shared or in tensor memory, with rows stored from registers or by TMA alike.
 // Warp roles per CTA: 4 epilogue warps, 1 TMA producer, 1 MMA issuer (leader CTA only).
-// No TMA multicast; full barriers live in the leader and count both CTAs' bytes; every wait is bounded.
+// No TMA multicast.  The weight stages' full barriers live in the leader and count both CTAs' bytes; the latent tile's
+// full barrier is each CTA's own (its epilogue warps wait on it).  Every wait is bounded, and the MMA issuer sees its
+// last MMA complete before the pair frees its tensor memory.
 #include <algorithm>
 #include <cuda_bf16.h>
 
@@ -71,8 +73,6 @@ struct ExpandParams {
   int32_t blocks_per_page;     // 64-column blocks of one page (latent + rope)
   int64_t row0;                // first TMA row of this layer in the pool's block array
   int64_t Ttot;
-  uint16_t* kx;
-  uint16_t* vx;
   int32_t* status;
 };
 
@@ -406,8 +406,6 @@ int32_t launch_mla_expand_sm100(Pool* p, const SeqBatch& sb, int layer, int extr
   k.blocks_per_page = p->row_elems_a / 64;
   k.row0 = (int64_t)layer * prm.num_pages * k.blocks_per_page * kPage;
   k.Ttot = Ttot;
-  k.kx = kx;
-  k.vx = vx;
   k.status = p->d_status;
   RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_expand_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
   const int launched = (int)((units + k.span - 1) / k.span);
