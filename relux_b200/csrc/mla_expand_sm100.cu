@@ -34,6 +34,7 @@
 #include "common.cuh"
 #include "internal.h"
 #include "umma.cuh"
+#include "prep_parts.cuh"
 
 namespace relux {
 
@@ -309,17 +310,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   if (warp == 0) tmem_dealloc<2>(tmem, kTmemCols);
 }
 
-// seq_base[i] = dense row of sequence i's first token: running sum of the cached lengths rounded up to 256.
+// seq_base[i] = dense row of sequence i's first token: running sum of the cached lengths rounded up to 256 (one block,
+// a block-wide scan per 256 sequences).
 __global__ void mla_expand_plan_kernel(const int32_t* __restrict__ len, const int32_t* __restrict__ seq_ids, int n_seqs, int extra,
                                        int32_t* __restrict__ seq_base) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  int acc = 0;
-  for (int i = 0; i < n_seqs; i++) {
-    seq_base[i] = acc;
-    const int T = len[seq_ids ? seq_ids[i] : i] + extra;
-    acc += (T + kTokTile - 1) / kTokTile * kTokTile;
+  __shared__ int32_t s_warp[32];
+  int base = 0;
+  for (int i0 = 0; i0 < n_seqs; i0 += blockDim.x) {
+    const int i = i0 + threadIdx.x;
+    int rows = 0;
+    if (i < n_seqs) {
+      const int T = len[seq_ids ? seq_ids[i] : i] + extra;
+      rows = (T + kTokTile - 1) / kTokTile * kTokTile;
+    }
+    int total;
+    const int before = prep_block_excl_scan(rows, s_warp, &total);
+    if (i < n_seqs) seq_base[i] = base + before;
+    base += total;
   }
-  seq_base[n_seqs] = acc;
+  if (threadIdx.x == 0) seq_base[n_seqs] = base;
 }
 
 int expand_workers(Pool* p) {
@@ -383,7 +392,7 @@ int32_t launch_mla_expand_sm100(Pool* p, const SeqBatch& sb, int layer, int extr
     return RELUX_ERR_CUDA;
   }
   const int32_t* len = p->d_len + (size_t)layer * prm.max_seqs;
-  mla_expand_plan_kernel<<<1, 32, 0, st>>>(len, sb.d_seq_ids, sb.n_seqs, extra, seq_base);
+  mla_expand_plan_kernel<<<1, 256, 0, st>>>(len, sb.d_seq_ids, sb.n_seqs, extra, seq_base);
   RELUX_CUDA_TRY(cudaGetLastError());
   count_launch(p->dev);
   ExpandParams k{};

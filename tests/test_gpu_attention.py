@@ -812,3 +812,33 @@ def test_prefill_paths_agree_with_the_decode_paths_on_random_shapes(dev, oracle)
         pool.destroy()
         if mla:
             wuk.free(); wuv.free()
+
+
+def test_mla_prefill_many_sequences(dev, oracle):
+    """300 sequences in one prompt call (more than one 256-thread pass of the kernel that lays out the expanded rows, more
+    couples than workers, sequences of different cached lengths): the prefill kernels against the decode kernels."""
+    import relux_b200 as rb
+    from relux_b200 import lib as L
+    rng = np.random.default_rng(811)
+    B, S, H, Dh, dC, dHR, P = 300, 128, 2, 128, 512, 64, 64
+    ctx = [int(c) + S for c in rng.integers(0, 130, B)]
+    pages_per = (max(ctx) + P - 1) // P + 1
+    pool = rb.Pool(dev, L.POOL_MLA, 1, B * pages_per, P, B, pages_per, dC=dC, dHR=dHR)
+    pool.set_tables(rng.permutation(B * pages_per).astype(np.int32).reshape(B, pages_per))
+    pool.append(0, rng.standard_normal((sum(ctx), dC)).astype(np.float32), rng.standard_normal((sum(ctx), dHR)).astype(np.float32), B,
+                n_new=np.asarray(ctx, np.int32))
+    wuk = dev.upload(oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02))
+    wuv = dev.upload(oracle.bf16_from_f32(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02))
+    q = oracle.bf16_from_f32(rng.standard_normal((B, S, H, Dh)).astype(np.float32))
+    qr = oracle.bf16_from_f32(rng.standard_normal((B, S, H, dHR)).astype(np.float32))
+    scale = float(1 / np.sqrt(Dh + dHR))
+    out = np.full((B, S, H, Dh), np.nan, np.float32)
+    n0 = dev.launch_count()
+    pool.decode(0, B, q, out, H, Dh, scale, q_rope=qr, w_uk=wuk, w_uv=wuv, q_tokens=S, causal=True)
+    assert dev.launch_count() - n0 == 3
+    pool.tune(L.TUNE_MLA_PROMPT_MIN_TOKENS, 1 << 30)
+    out2 = np.full((B, S, H, Dh), np.nan, np.float32)
+    pool.decode(0, B, q, out2, H, Dh, scale, q_rope=qr, w_uk=wuk, w_uv=wuv, q_tokens=S, causal=True)
+    assert pool.status() == 0
+    assert np.isfinite(out).all() and np.abs(out - out2).max() <= 1.5e-2
+    pool.destroy(); wuk.free(); wuv.free()
