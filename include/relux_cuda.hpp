@@ -318,6 +318,41 @@ class MLACache {
     a.mode = mode;
     check(relux_mla_decode(pool_, &a));
   }
+  // One decode step in one call: Append of one row, then Attend with one query token (relux_mla_step; mla.go:309-377).
+  void Step(int layerIdx, const float* newC, const float* newKR, const float* qc, const float* qr, const void* wUK, const void* wUV,
+            float* out, int numHeads, int headDim, float scale, int mode = RELUX_ATTN_FAST) {
+    relux_append_args ap{};
+    ap.layer = layerIdx;
+    ap.n_seqs = 1;
+    ap.seq_ids = &seq_;
+    ap.a = newC;
+    ap.b = newKR;
+    ap.dtype = RELUX_DTYPE_F32;
+    ap.mem = RELUX_MEM_HOST;
+    ap.advance = 1;
+    relux_attn_args a{};
+    a.layer = layerIdx;
+    a.n_seqs = 1;
+    a.seq_ids = &seq_;
+    a.q_tokens = 1;
+    a.causal = 1;
+    a.num_heads = numHeads;
+    a.head_dim = headDim;
+    a.scale = scale;
+    a.q = qc;
+    a.q_rope = qr;
+    a.q_dtype = RELUX_DTYPE_F32;
+    a.q_mem = RELUX_MEM_HOST;
+    a.q_layout = RELUX_LAYOUT_HEAD_MAJOR;
+    a.w_uk = wUK;
+    a.w_uv = wUV;
+    a.out = out;
+    a.out_dtype = RELUX_DTYPE_F32;
+    a.out_mem = RELUX_MEM_HOST;
+    a.out_layout = RELUX_LAYOUT_HEAD_MAJOR;
+    a.mode = mode;
+    check(relux_mla_step(pool_, &ap, &a));
+  }
   // MLA.forwardCached (mla.go:272-397): x, out [1, seqQ, dModel] float32; w = device copies of the seven matrices.
   void ForwardCached(int layerIdx, const float* x, float* out, const relux_mla_layer_weights& w, int dModel, int numHeads, int seqQ,
                      bool causal, float ropeBase = 10000.f, int mode = RELUX_ATTN_FAST) {

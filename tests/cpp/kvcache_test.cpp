@@ -14,6 +14,12 @@ static int failures = 0;
     if (!(cond)) { printf("FAIL %s: %s\n", name, #cond); failures++; } \
   } while (0)
 
+static uint16_t bf16_from_f32(float f) {   // round to nearest even (dtype_convert.go:15-24)
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  u += 0x7FFFu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
 static float f32_from_bf16(uint16_t b) {
   uint32_t u = (uint32_t)b << 16;
   float f;
@@ -99,6 +105,37 @@ int main() {
     EXPECT(same, "MLACache data");
     c.Reset();
     EXPECT(c.TotalLen(1) == 0, "MLACache reset");
+  }
+  {  // MLACache.Step = Append + Attend: the same bits from two caches fed the same rows (16 heads x 128, latent 512, rope 64)
+    const int H = 16, Dh = 128, dC = 512, dHR = 64;
+    relux::MLACache c1(dev, 1, 256, dC, dHR), c2(dev, 1, 256, dC, dHR);
+    uint32_t state = 777u;
+    auto next = [&]() { state = state * 1664525u + 1013904223u; return (float)(state >> 8) / 16777216.0f - 0.5f; };
+    std::vector<uint16_t> wuk((size_t)dC * H * Dh), wuv((size_t)dC * H * Dh);
+    for (auto& v : wuk) v = bf16_from_f32(next() * 0.05f);
+    for (auto& v : wuv) v = bf16_from_f32(next() * 0.05f);
+    void* d_uk = dev.Upload(wuk.data(), wuk.size() * 2);
+    void* d_uv = dev.Upload(wuv.data(), wuv.size() * 2);
+    std::vector<float> rows_c((size_t)70 * dC), rows_r((size_t)70 * dHR);
+    for (auto& v : rows_c) v = next();
+    for (auto& v : rows_r) v = next();
+    c1.Append(0, rows_c.data(), rows_r.data(), 70);
+    c2.Append(0, rows_c.data(), rows_r.data(), 70);
+    bool same = true;
+    for (int step = 0; step < 3 && same; step++) {
+      std::vector<float> nc(dC), nr(dHR), qc((size_t)H * Dh), qr((size_t)H * dHR), o1((size_t)H * Dh, -1.f), o2((size_t)H * Dh, -2.f);
+      for (auto& v : nc) v = next();
+      for (auto& v : nr) v = next();
+      for (auto& v : qc) v = next();
+      for (auto& v : qr) v = next();
+      c1.Append(0, nc.data(), nr.data(), 1);
+      c1.Attend(0, qc.data(), qr.data(), d_uk, d_uv, o1.data(), H, Dh, 1, 0.0722f, true);
+      c2.Step(0, nc.data(), nr.data(), qc.data(), qr.data(), d_uk, d_uv, o2.data(), H, Dh, 0.0722f);
+      for (size_t i = 0; same && i < o1.size(); i++) same = o1[i] == o2[i];
+      same = same && c1.TotalLen(0) == c2.TotalLen(0);
+    }
+    EXPECT(same, "MLACache Step equals Append + Attend");
+    dev.Free(d_uk); dev.Free(d_uv);
   }
   {  // attention through the mirror: one cached row -> the output is that V row (softmax of one score = 1)
     relux::KVCache c(dev, 1, 64, 1, 128);
