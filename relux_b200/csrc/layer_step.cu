@@ -558,9 +558,19 @@ int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a) {
   const ProjSeg segs[4] = {{H * Dh, 0, d_qc, fast ? 1 : 0}, {H * dHR, dHR, d_qr, fast ? 1 : 0}, {dC, 0, d_c, 0}, {dHR, dHR, d_kr, 0}};
   rc = project_and_finish(p, sb, a->layer, (const float*)dx, M, D, S, proj, segs, 4, mma, sc.a_bf16, sc.part, sc.part_cap, faithful);
   if (rc) return rc;
-  // 3. append (advances the cursors)
-  rc = launch_mla_append(p, sb, a->layer, d_c, d_kr, RELUX_DTYPE_F32, 1);
-  if (rc) return rc;
+  // 3. append (advances the cursors).  A one-token step on the tensor-core path leaves the append to the attention's
+  //    preparation launch (absorb + append + stream partition in one kernel, as relux_mla_step does).
+  relux_attn_args probe;
+  memset(&probe, 0, sizeof(probe));
+  probe.mode = a->mode;
+  probe.num_heads = H;
+  probe.head_dim = Dh;
+  probe.q_tokens = S;
+  const bool fused_append = fast && S == 1 && mla_step_fusable(p, probe, sb.n_seqs);
+  if (!fused_append) {
+    rc = launch_mla_append(p, sb, a->layer, d_c, d_kr, RELUX_DTYPE_F32, 1);
+    if (rc) return rc;
+  }
   for (int i = 0; i < sb.n_seqs; i++) {
     int32_t& len = p->h_len[(size_t)a->layer * prm.max_seqs + sb.seq[i]];
     note_append(p, a->layer, sb.seq[i], len, S);
@@ -583,7 +593,8 @@ int32_t do_mla_layer(Pool* p, const relux_mla_layer_args* a) {
   aa.w_uk = w.w_uk;
   aa.w_uv = w.w_uv;
   aa.mode = a->mode;
-  rc = fast ? launch_mla_decode_fast(p, sb, aa, d_qc, d_qr, d_attn)
+  const StepAppend step{d_c, d_kr, RELUX_DTYPE_F32, nullptr};   // one row per sequence
+  rc = fast ? launch_mla_decode_fast(p, sb, aa, d_qc, d_qr, d_attn, fused_append ? &step : nullptr)
             : launch_attn_reference_mla(p, sb, aa, (const float*)d_qc, (const float*)d_qr, d_attn);
   if (rc) return rc;
   // 5. output projection
