@@ -60,8 +60,9 @@ WORKLOADS = {
     "gqa_layer_verify_b128_ctx8k": dict(kind="gqa", B=128, ctx=8192, H=32, Hkv=8, D=128, S=4, layer=True),
 }
 DEFAULT_WORKLOAD = "mla_decode_b64_ctx32k"
-# config 3, config 4 (one GPU's share) and config 5 of the benchmark definition: run after the headline workload
-ALSO_WORKLOADS = ("mla_decode_b64_ctx4k", "mla_decode_ragged_b16", "gqa_verify_b128_ctx8k")
+# config 3, config 4 (one GPU's share) and config 5 of the benchmark definition, then the two prompt workloads (the
+# prefill kernels): run after the headline workload
+ALSO_WORKLOADS = ("mla_decode_b64_ctx4k", "mla_decode_ragged_b16", "gqa_verify_b128_ctx8k", "gqa_prompt_b8_2k", "mla_prompt_b4_1k")
 # dram__bytes_read + dram__bytes_write of the dominant kernel divided by its algorithmic bytes, from the ncu captures
 # summarised under profiles/ (small case, traffic grows in proportion to the cached tokens read).
 TRAFFIC_RATIO = {"mla": 1.04, "gqa": 1.015, "accept": 1.08}
