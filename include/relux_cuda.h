@@ -216,7 +216,10 @@ int32_t relux_pool_read_rows(relux_pool_t pool, const relux_read_rows_args* args
 #define RELUX_TUNE_MLA_PROMPT_SCRATCH_MB 11 /* RELUX_MLA_PROMPT_SCRATCH_MB: most device memory the expanded K / V may take (16384) */
 #define RELUX_TUNE_KERNEL_TIMING_STRIDE 12 /* RELUX_KERNEL_TIMING_STRIDE: the MLA decode kernel's event pair is recorded on every
                                            Nth call (1); the pairs are what relux_pool_kernel_ms_* read */
-#define RELUX_TUNE_COUNT 13
+#define RELUX_TUNE_CHAINED_LAUNCHES 13 /* RELUX_CHAINED_LAUNCHES: 1 = the kernels of an MLA decode step are launched with
+                                           programmatic stream serialization, so each is scheduled while the one before it
+                                           still runs and waits on the device for its results (1); 0 = plain launches */
+#define RELUX_TUNE_COUNT 14
 /* Changes one tuning knob of a pool (see RELUX_TUNE_*).  A pool takes its defaults once, when it is created, from the
  * environment variables named beside the knobs; no call reads the environment afterwards.  value < 0 restores the
  * built-in default.  Tuning aid: no counterpart in the reference. */

@@ -132,6 +132,13 @@ __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.b
 // All committed stores of this thread are complete.
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// Programmatic dependent launch.  A kernel launched with the stream-serialization attribute may be scheduled while the
+// kernel before it in the stream still runs; chain_wait() returns once that kernel has completed and its writes are
+// visible, so it stands before the first access to global memory.  chain_release() lets the kernel after this one be
+// scheduled (it blocks in its own chain_wait() until this grid is complete).  Both are no-ops in a plain launch.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }

@@ -9,6 +9,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "relux_cuda.h"
@@ -224,5 +225,24 @@ void note_set_len(Pool* p, int layer, int seq, int old_len, int new_len);
 int32_t check_dev_align(const void* ptr, const char* what);
 
 inline void count_launch(Device* d, int n = 1) { d->launches += n; }
+
+// Launches `kern`; with `chained` the launch carries the programmatic stream-serialization attribute, so the grid may be
+// scheduled while the kernel before it in the stream still runs.  Such a kernel calls chain_wait() (common.cuh) before
+// its first access to global memory, which is what keeps the stream's order of results.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(bool chained, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at;
+  at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at.val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = &at;
+  cfg.numAttrs = chained ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
 
 }  // namespace relux

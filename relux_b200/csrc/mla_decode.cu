@@ -25,12 +25,12 @@ bool mla_proj_mma_eligible(int Dh, int dC);
 bool mla_prep_fits(int n_seqs, int H, int dC);
 int32_t launch_mla_prefill_sm100(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const uint16_t* d_q, const uint16_t* d_qr, float* d_out);
 int32_t launch_mla_prep(Device* dev, const void* q_nope, const void* q_rope, int q_bf16, const uint16_t* W_UK, uint16_t* q_abs, int rows,
-                        int H, int dC, int dHR, const PrepAppend& ap, const PrepPlan& pl);
+                        int H, int dC, int dHR, const PrepAppend& ap, const PrepPlan& pl, bool chained);
 int32_t launch_mla_absorb_mma(Device* dev, const void* q_nope, const void* q_rope, int q_bf16, const uint16_t* W_UK, uint16_t* q_abs,
                               int rows, int H, int dC, int dHR);
 int32_t launch_mla_vup_mma(Device* dev, const uint16_t* o_lat, const uint16_t* W_UV, float* out, int rows, int H, int dC);
 int32_t launch_mla_merge_vup_mma(Device* dev, const float* part_o, const float* part_ml, const int32_t* chunk_off, const uint16_t* W_UV,
-                                 float* out, int rows, int S, int H, int dC);
+                                 float* out, int rows, int S, int H, int dC, bool chained);
 
 namespace {
 
@@ -302,7 +302,7 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
     pl.chunk_off = plan.chunk_off;
     pl.worker_first = plan.worker_first;
     rc = launch_mla_prep(p->dev, d_q, d_qr, a.q_dtype == RELUX_DTYPE_BF16, (const uint16_t*)a.w_uk, (uint16_t*)p->q_abs.p, rows, H, dC, dHR, ap,
-                         pl);
+                         pl, p->tune.get(RELUX_TUNE_CHAINED_LAUNCHES) != 0);
     if (rc) return rc;
   }
   if (fork) {
@@ -390,7 +390,7 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   if (fused_merge) {
     // split-KV merge fused into the up-projection: the merged latent output never touches HBM
     rc = launch_mla_merge_vup_mma(p->dev, (const float*)p->part_o.p, (const float*)p->part_ml.p, plan.chunk_off, (const uint16_t*)a.w_uv,
-                                  (float*)d_out, rows, S, H, dC);
+                                  (float*)d_out, rows, S, H, dC, p->tune.get(RELUX_TUNE_CHAINED_LAUNCHES) != 0);
     if (rc) return rc;
   } else if (proj_mma) {
     // merged latent output goes to the up-projection as bf16 (tensor-core operand)

@@ -136,6 +136,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
   const int cluster = blockIdx.x >> 1;
   const int worker = cluster / prm.sx;
   const int sq = blockIdx.y * prm.sx + cluster % prm.sx;   // query token of this worker
+  chain_release();
+  chain_wait();   // the ranges, the absorbed queries and the step's new rows come from the kernel before this one
   const int it0 = prm.worker_first[worker], it1 = prm.worker_first[worker + 1];
   if (it0 >= it1 || sq >= prm.S) return;   // an empty range: both CTAs of the pair leave before any pair-wide step
 
@@ -568,8 +570,8 @@ int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_ar
   k.status = p->d_status;
   RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_decode_sm100_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemTotal));
   dim3 grid(2 * plan.num_workers * sx, a.q_tokens / sx);
-  mla_decode_sm100_kernel<<<grid, 192, kSmemTotal, p->dev->stream>>>(p->tmap_mla, tq, k);
-  RELUX_CUDA_TRY(cudaGetLastError());
+  RELUX_CUDA_TRY(launch_chained(p->tune.get(RELUX_TUNE_CHAINED_LAUNCHES) != 0, mla_decode_sm100_kernel, grid, dim3(192), (size_t)kSmemTotal,
+                                p->dev->stream, p->tmap_mla, tq, k));
   return RELUX_OK;
 }
 

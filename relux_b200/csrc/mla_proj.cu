@@ -149,6 +149,8 @@ __global__ void __launch_bounds__(128) mla_prep_kernel(const void* __restrict__ 
                                                        const uint16_t* __restrict__ W_UK, uint16_t* __restrict__ q_abs, int rows, int H,
                                                        int dC, int dHR, int z_absorb, const PrepAppend ap, const PrepPlan pl) {
   extern __shared__ __align__(16) uint16_t sm[];
+  chain_release();
+  chain_wait();   // the kernel before this one in the stream may still be reading what this one overwrites
   if ((int)blockIdx.z < z_absorb) {
     absorb_block(sm, q_nope, q_rope, q_bf16, W_UK, q_abs, rows, H, dC, dHR, blockIdx.x, blockIdx.y, blockIdx.z);
     return;
@@ -337,6 +339,8 @@ __global__ void __launch_bounds__(32 * kMergeWarps) mla_merge_vup_mma_kernel(con
   const int h = blockIdx.x, r0 = blockIdx.y * 64;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rows_total = S * H;
+  chain_release();
+  chain_wait();   // the partial results come from the kernel before this one
   for (int k = 0; k < nk; k++) {
 #pragma unroll 4
     for (int e = threadIdx.x; e < 128 * 16; e += blockDim.x) {
@@ -393,13 +397,13 @@ int32_t launch_mla_absorb_mma(Device* dev, const void* q_nope, const void* q_rop
 // must fit one z slice of the absorb grid.
 bool mla_prep_fits(int n_seqs, int H, int dC) { return n_seqs + 1 <= H * (dC / 128); }
 int32_t launch_mla_prep(Device* dev, const void* q_nope, const void* q_rope, int q_bf16, const uint16_t* W_UK, uint16_t* q_abs, int rows,
-                        int H, int dC, int dHR, const PrepAppend& ap, const PrepPlan& pl) {
+                        int H, int dC, int dHR, const PrepAppend& ap, const PrepPlan& pl, bool chained) {
   const int z_absorb = (rows + 63) / 64;
   dim3 grid(H, dC / 128, z_absorb + 1);
   const size_t smem = (size_t)(64 + 128) * kStride * 2;
   RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  mla_prep_kernel<<<grid, 128, smem, dev->stream>>>(q_nope, q_rope, q_bf16, W_UK, q_abs, rows, H, dC, dHR, z_absorb, ap, pl);
-  RELUX_CUDA_TRY(cudaGetLastError());
+  RELUX_CUDA_TRY(launch_chained(chained, mla_prep_kernel, grid, dim3(128), smem, dev->stream, q_nope, q_rope, q_bf16, W_UK, q_abs, rows, H, dC,
+                                dHR, z_absorb, ap, pl));
   count_launch(dev);
   return RELUX_OK;
 }
@@ -415,12 +419,12 @@ int32_t launch_mla_vup_mma(Device* dev, const uint16_t* o_lat, const uint16_t* W
 }
 
 int32_t launch_mla_merge_vup_mma(Device* dev, const float* part_o, const float* part_ml, const int32_t* chunk_off, const uint16_t* W_UV,
-                                 float* out, int rows, int S, int H, int dC) {
+                                 float* out, int rows, int S, int H, int dC, bool chained) {
   dim3 grid(H, (rows + 63) / 64);
   const size_t smem = (size_t)(dC / 128) * (64 + 128) * kStride * 2;
   RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_merge_vup_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  mla_merge_vup_mma_kernel<<<grid, 32 * kMergeWarps, smem, dev->stream>>>(part_o, part_ml, chunk_off, W_UV, out, rows, S, H, dC);
-  RELUX_CUDA_TRY(cudaGetLastError());
+  RELUX_CUDA_TRY(launch_chained(chained, mla_merge_vup_mma_kernel, grid, dim3(32 * kMergeWarps), smem, dev->stream, part_o, part_ml, chunk_off,
+                                W_UV, out, rows, S, H, dC));
   count_launch(dev);
   return RELUX_OK;
 }

@@ -496,11 +496,12 @@ static int32_t do_attention(Pool* p, const relux_attn_args* a, int kind, const S
 }
 
 // Built-in defaults of the tuning knobs, then the environment (read here, once per pool, never on a launch path).
-static const int32_t kTuneDefault[RELUX_TUNE_COUNT] = {0, 0, 0, 0, 0, 256, 0, -1, -1, 0, 128, 16384, 1};
+static const int32_t kTuneDefault[RELUX_TUNE_COUNT] = {0, 0, 0, 0, 0, 256, 0, -1, -1, 0, 128, 16384, 1, 1};
 static const char* const kTuneEnv[RELUX_TUNE_COUNT] = {"RELUX_MLA_GENERIC", "RELUX_MLA_WORKERS", "RELUX_CHUNK_PAGES", "RELUX_GEMM_GENERIC",
                                                        "RELUX_GEMM_SPLIT", "RELUX_GQA_PROMPT_PARTIAL_MB", "RELUX_SEL_CLUSTER",
                                                        "RELUX_SEL_LOOKAHEAD", "RELUX_SEL_BATCHED", "RELUX_GQA_PROMPT_SLICES",
-                                                       "RELUX_MLA_PROMPT_MIN_TOKENS", "RELUX_MLA_PROMPT_SCRATCH_MB", "RELUX_KERNEL_TIMING_STRIDE"};
+                                                       "RELUX_MLA_PROMPT_MIN_TOKENS", "RELUX_MLA_PROMPT_SCRATCH_MB", "RELUX_KERNEL_TIMING_STRIDE",
+                                                       "RELUX_CHAINED_LAUNCHES"};
 void tuning_defaults(Tuning* t) {
   for (int i = 0; i < RELUX_TUNE_COUNT; i++) {
     t->v[i] = kTuneDefault[i];

@@ -24,7 +24,7 @@ POOL_FLAG_REFERENCE_COMPAT = 1
 CALL_PIPELINED = 1
 (TUNE_MLA_GENERIC, TUNE_MLA_WORKERS, TUNE_CHUNK_PAGES, TUNE_GEMM_GENERIC, TUNE_GEMM_SPLIT, TUNE_GQA_PROMPT_PARTIAL_MB, TUNE_SEL_CLUSTER,
  TUNE_SEL_LOOKAHEAD, TUNE_SEL_BATCHED, TUNE_GQA_PROMPT_SLICES, TUNE_MLA_PROMPT_MIN_TOKENS, TUNE_MLA_PROMPT_SCRATCH_MB,
- TUNE_KERNEL_TIMING_STRIDE) = range(13)
+ TUNE_KERNEL_TIMING_STRIDE, TUNE_CHAINED_LAUNCHES) = range(14)
 
 # Every symbol include/relux_cuda.h declares; tests check that the library exports each one.
 EXPORTS = [
