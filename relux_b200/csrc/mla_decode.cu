@@ -30,7 +30,7 @@ int32_t launch_mla_absorb_mma(Device* dev, const void* q_nope, const void* q_rop
                               int rows, int H, int dC, int dHR);
 int32_t launch_mla_vup_mma(Device* dev, const uint16_t* o_lat, const uint16_t* W_UV, float* out, int rows, int H, int dC);
 int32_t launch_mla_merge_vup_mma(Device* dev, const float* part_o, const float* part_ml, const int32_t* chunk_off, const uint16_t* W_UV,
-                                 float* out, int rows, int S, int H, int dC, bool chained);
+                                 float* out, int rows, int S, int H, int dC, int32_t* status, bool chained);
 
 namespace {
 
@@ -390,7 +390,7 @@ int32_t launch_mla_decode_fast(Pool* p, const SeqBatch& sb, const relux_attn_arg
   if (fused_merge) {
     // split-KV merge fused into the up-projection: the merged latent output never touches HBM
     rc = launch_mla_merge_vup_mma(p->dev, (const float*)p->part_o.p, (const float*)p->part_ml.p, plan.chunk_off, (const uint16_t*)a.w_uv,
-                                  (float*)d_out, rows, S, H, dC, p->tune.get(RELUX_TUNE_CHAINED_LAUNCHES) != 0);
+                                  (float*)d_out, rows, S, H, dC, p->d_status, p->tune.get(RELUX_TUNE_CHAINED_LAUNCHES) != 0);
     if (rc) return rc;
   } else if (proj_mma) {
     // merged latent output goes to the up-projection as bf16 (tensor-core operand)

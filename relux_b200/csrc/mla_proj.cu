@@ -238,14 +238,26 @@ __device__ __forceinline__ void merge_rows_warp(uint16_t* As, const float* __res
                                                 const int32_t* __restrict__ chunk_off, int r0, int rows, int S, int H, int h, int dC, int nk,
                                                 int rows_total) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The item range of a row is the first of two dependent round trips to L2, so it is requested one row ahead.
+  int c0_next = 0, c1_next = 0;
+  if (r0 + warp < rows) {
+    const int i = (r0 + warp) / S;
+    c0_next = __ldg(chunk_off + i);
+    c1_next = __ldg(chunk_off + i + 1);
+  }
   for (int row = warp; row < 64; row += kMergeWarps) {
     const int r = r0 + row;
+    const int c0 = c0_next, c1 = c1_next;
+    c0_next = c1_next = 0;
+    if (row + kMergeWarps < 64 && r + kMergeWarps < rows) {
+      const int i = (r + kMergeWarps) / S;
+      c0_next = __ldg(chunk_off + i);
+      c1_next = __ldg(chunk_off + i + 1);
+    }
     float4 acc[kMaxChunks];
 #pragma unroll
     for (int k = 0; k < kMaxChunks; k++) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (r < rows) {
-      const int i = r / S;
-      const int c0 = __ldg(chunk_off + i), c1 = __ldg(chunk_off + i + 1);
       const size_t prow = (size_t)(r % S) * H + h;
       // (max, sum) of this lane's item of every group of 32, and at the same time the partial rows of the first four
       // items: one memory round trip serves the common case of a sequence cut into a handful of items
@@ -326,13 +338,15 @@ __device__ __forceinline__ void merge_rows_warp(uint16_t* As, const float* __res
 // 64 rows of one head, as bf16) is built straight from the per-item partials
 //   part_o [item][S * H][dC] f32 (unnormalised), part_ml [item][S * H][2] = (max in the log2 domain, sum),
 // items of sequence i = [chunk_off[i], chunk_off[i + 1]).  All of W_UV's slice for this head (dC x 128 bf16) streams
-// into shared memory with cp.async while the partials are combined by 16 warps (merge_rows_warp); the first 8 warps
-// then run the MMAs.
+// into shared memory as bulk copies while the partials are combined by 16 warps (merge_rows_warp); the first 8 warps
+// then run the MMAs, chunk by chunk as the copies land.
 // grid (H, ceil(rows/64)), 512 threads, row = seq_index * S + query token.  dC = 128 * nk, nk <= 4.
 __global__ void __launch_bounds__(32 * kMergeWarps) mla_merge_vup_mma_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                                 const int32_t* __restrict__ chunk_off, const uint16_t* __restrict__ W_UV,
-                                                                float* __restrict__ out, int rows, int S, int H, int dC) {
+                                                                float* __restrict__ out, int rows, int S, int H, int dC,
+                                                                int32_t* __restrict__ status) {
   extern __shared__ __align__(16) uint16_t sm[];
+  __shared__ __align__(8) uint64_t w_full[kMaxChunks];   // chunk k of W_UV has landed (bytes counted by the bulk copies)
   const int nk = dC / 128;
   uint16_t* As = sm;                             // [nk][64][kStride]
   uint16_t* Bs = sm + (size_t)nk * 64 * kStride;  // [nk][128][kStride]
@@ -341,32 +355,30 @@ __global__ void __launch_bounds__(32 * kMergeWarps) mla_merge_vup_mma_kernel(con
   const int rows_total = S * H;
   chain_release();
   chain_wait();   // the partial results come from the kernel before this one
-  for (int k = 0; k < nk; k++) {
-#pragma unroll 4
-    for (int e = threadIdx.x; e < 128 * 16; e += blockDim.x) {
-      const int c = e / 16, v = e % 16;
-      cp_async16(Bs + ((size_t)k * 128 + c) * kStride + v * 8, W_UV + (size_t)(k * 128 + c) * H * kDh + (size_t)h * kDh + (size_t)v * 8);
-    }
-    cp_async_commit();
+  // W_UV's slice comes in as one 256-byte bulk copy per latent row, through the TMA unit: as 16-byte cp.async requests
+  // the same 128 KB sat in the load/store unit's queue ahead of the merge's own loads, whose round trips then took
+  // 1.0-1.6 us each.
+  if (threadIdx.x == 0) {
+    for (int k = 0; k < nk; k++) mbar_init(&w_full[k], 1);
+    fence_mbar_init();
   }
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int k = 0; k < nk; k++) mbar_expect_tx(&w_full[k], 128u * kDh * 2u);
+  for (int e = threadIdx.x; e < nk * 128; e += blockDim.x)
+    bulk_load_1d(Bs + (size_t)e * kStride, W_UV + (size_t)e * H * kDh + (size_t)h * kDh, kDh * 2, &w_full[e >> 7]);
   merge_rows_warp(As, part_o, part_ml, chunk_off, r0, rows, S, H, h, dC, nk, rows_total);
   float acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; i++)
 #pragma unroll
     for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
-  for (int k = 0; k < nk; k++) {
-    // chunk k of W_UV has landed once at most nk - 1 - k younger groups are still in flight
-    switch (nk - 1 - k) {
-      case 3: cp_async_wait<3>(); break;
-      case 2: cp_async_wait<2>(); break;
-      case 1: cp_async_wait<1>(); break;
-      default: cp_async_wait<0>(); break;
-    }
-    __syncthreads();   // also publishes the merged A tiles (first iteration)
-    if (warp < 8) tile_mma_64x64x128_bt(As + (size_t)k * 64 * kStride, Bs + (size_t)k * 128 * kStride, acc, warp, lane);
-  }
+  __syncthreads();   // the merged A tiles are complete
   if (warp >= 8) return;
+  for (int k = 0; k < nk; k++) {
+    if (!mbar_wait(&w_full[k], 0)) set_status(status, RELUX_ERR_TIMEOUT);   // bounded: a copy that never lands is reported, not waited for
+    tile_mma_64x64x128_bt(As + (size_t)k * 64 * kStride, Bs + (size_t)k * 128 * kStride, acc, warp, lane);
+  }
 #pragma unroll
   for (int hf = 0; hf < 2; hf++) {
     const int r = r0 + (warp & 3) * 16 + hf * 8 + (lane >> 2);
@@ -419,12 +431,12 @@ int32_t launch_mla_vup_mma(Device* dev, const uint16_t* o_lat, const uint16_t* W
 }
 
 int32_t launch_mla_merge_vup_mma(Device* dev, const float* part_o, const float* part_ml, const int32_t* chunk_off, const uint16_t* W_UV,
-                                 float* out, int rows, int S, int H, int dC, bool chained) {
+                                 float* out, int rows, int S, int H, int dC, int32_t* status, bool chained) {
   dim3 grid(H, (rows + 63) / 64);
   const size_t smem = (size_t)(dC / 128) * (64 + 128) * kStride * 2;
   RELUX_CUDA_TRY(cudaFuncSetAttribute(mla_merge_vup_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   RELUX_CUDA_TRY(launch_chained(chained, mla_merge_vup_mma_kernel, grid, dim3(32 * kMergeWarps), smem, dev->stream, part_o, part_ml, chunk_off,
-                                W_UV, out, rows, S, H, dC));
+                                W_UV, out, rows, S, H, dC, status));
   count_launch(dev);
   return RELUX_OK;
 }
