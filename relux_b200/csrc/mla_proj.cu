@@ -234,10 +234,14 @@ __device__ __forceinline__ void tile_mma_64x64x128_bt(const uint16_t* As, const 
 // from one round trip: lane j reads (max, sum) of item j, the warp reduces.  Four items are in flight per lane.
 // Rows past the batch are zero rows of the MMA tile.
 constexpr int kMergeWarps = 16;
+// `after_first_requests` runs once per thread, after the loads of the warp's first row have been issued: work that
+// stalls the thread for its own reasons goes there, under the shadow of that round trip.
+template <typename Hook>
 __device__ __forceinline__ void merge_rows_warp(uint16_t* As, const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                 const int32_t* __restrict__ chunk_off, int r0, int rows, int S, int H, int h, int dC, int nk,
-                                                int rows_total) {
+                                                int rows_total, Hook&& after_first_requests) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  bool hook_due = true;
   // The item range of a row is the first of two dependent round trips to L2, so it is requested one row ahead.
   int c0_next = 0, c1_next = 0;
   if (r0 + warp < rows) {
@@ -274,6 +278,10 @@ __device__ __forceinline__ void merge_rows_warp(uint16_t* As, const float* __res
 #pragma unroll
         for (int k = 0; k < kMaxChunks; k++)
           if (k < nk) x[u][k] = __ldg(src + k * 32);
+      }
+      if (hook_due) {
+        after_first_requests();
+        hook_due = false;
       }
       // global maximum and normaliser over all items of the sequence
       float M = ml.x;
@@ -326,6 +334,10 @@ __device__ __forceinline__ void merge_rows_warp(uint16_t* As, const float* __res
       }
     }
   store_row:
+    if (hook_due) {
+      after_first_requests();
+      hook_due = false;
+    }
 #pragma unroll
     for (int k = 0; k < kMaxChunks; k++)
       if (k < nk)
@@ -365,9 +377,12 @@ __global__ void __launch_bounds__(32 * kMergeWarps) mla_merge_vup_mma_kernel(con
   __syncthreads();
   if (threadIdx.x == 0)
     for (int k = 0; k < nk; k++) mbar_expect_tx(&w_full[k], 128u * kDh * 2u);
-  for (int e = threadIdx.x; e < nk * 128; e += blockDim.x)
-    bulk_load_1d(Bs + (size_t)e * kStride, W_UV + (size_t)e * H * kDh + (size_t)h * kDh, kDh * 2, &w_full[e >> 7]);
-  merge_rows_warp(As, part_o, part_ml, chunk_off, r0, rows, S, H, h, dC, nk, rows_total);
+  // 512 bulk copies queue up in the TMA unit (2-3 us until the last is accepted), so each thread issues its own after the
+  // loads of its first row are on their way
+  merge_rows_warp(As, part_o, part_ml, chunk_off, r0, rows, S, H, h, dC, nk, rows_total, [&]() {
+    for (int e = threadIdx.x; e < nk * 128; e += blockDim.x)
+      bulk_load_1d(Bs + (size_t)e * kStride, W_UV + (size_t)e * H * kDh + (size_t)h * kDh, kDh * 2, &w_full[e >> 7]);
+  });
   float acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; i++)
