@@ -273,11 +273,12 @@ __device__ __forceinline__ void merge_rows_warp(uint16_t* As, const float* __res
       const int ng0 = min(32, n_items);
 #pragma unroll
       for (int u = 0; u < 4; u++) {
-        const int c = c0 + min(u, ng0 - 1);   // a short group re-reads its last item with weight 0
-        const float4* src = reinterpret_cast<const float4*>(part_o + ((size_t)c * rows_total + prow) * dC) + lane;
+        // a slot past the group's last item stays zero (its weight is zero too): the load unit's data path, 128 bytes
+        // per clock for all 16 warps, is what a row's requests queue on, so no load is spent on padding
+        const float4* src = reinterpret_cast<const float4*>(part_o + ((size_t)(c0 + u) * rows_total + prow) * dC) + lane;
 #pragma unroll
         for (int k = 0; k < kMaxChunks; k++)
-          if (k < nk) x[u][k] = __ldg(src + k * 32);
+          if (k < nk) x[u][k] = (u < ng0) ? __ldg(src + k * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
       }
       if (hook_due) {
         after_first_requests();
@@ -310,11 +311,10 @@ __device__ __forceinline__ void merge_rows_warp(uint16_t* As, const float* __res
           if (cb != c0 || j != 0) {   // the first four items of the row are in flight already
 #pragma unroll
             for (int u = 0; u < 4; u++) {
-              const int c = cb + min(j + u, ng - 1);
-              const float4* src = reinterpret_cast<const float4*>(part_o + ((size_t)c * rows_total + prow) * dC) + lane;
+              const float4* src = reinterpret_cast<const float4*>(part_o + ((size_t)(cb + j + u) * rows_total + prow) * dC) + lane;
 #pragma unroll
               for (int k = 0; k < kMaxChunks; k++)
-                if (k < nk) x[u][k] = __ldg(src + k * 32);
+                if (k < nk) x[u][k] = (j + u < ng) ? __ldg(src + k * 32) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
           }
 #pragma unroll
