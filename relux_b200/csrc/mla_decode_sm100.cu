@@ -14,7 +14,7 @@
 // the part of one sequence inside one range, so a worker changes item (new Q~, new accumulator, one split-KV
 // partial written) only where a sequence ends inside its range.  The tile pipeline does not drain at an item
 // boundary: Q~ of the next item is loaded as soon as the last QK^T of the current one has completed, and the
-// first QK^T of the next item is issued ahead of the last PV of the current one like any other tile.
+// first QK^T of the next item is issued right behind the last PV of the current one.
 //
 // Per 128-token tile (two pages; page r of the tile belongs to CTA r):
 //   S[128 x 128]  = Q~[128 x 576] . K[128 tok x 576]^T      36 MMAs M128 N128 K16, K-major A and B
@@ -256,10 +256,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         if (i + 1 < ntiles) {
           load_k(w, i + 1, g + 1);
         } else if (has_next) {
-          // Q~ may be replaced once the last QK^T of this item (tile g) has completed
+          // the next item's first K tile goes group by group behind QK^T(g) like any other tile; Q~ may be replaced once
+          // the last QK^T of this item (tile g) has completed, which the last group's slot being free says
+          load_k(wn, 0, g + 1);
           wait_bar(&bars->k_empty[kKGroups - 1], g & 1, bars, prm.status);
           load_q(nxt);
-          load_k(wn, 0, g + 1);
         }
         load_v(w, i, g);
         if (((2 * i + 2) >> 5) > w.blk) {
@@ -333,11 +334,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
         for (int i = 0; i < ntiles; i++, g++) {
           if (i + 1 < ntiles) {
             issue_qk(g + 1);
-          } else if (has_next) {
+          }
+          issue_pv(g, i == 0);
+          if (i + 1 == ntiles && has_next) {
+            // at an item end PV(g) goes first: the next Q~ lands a memory latency after QK^T(g), later than P(g) is ready,
+            // and the softmax warps can start writing the item out as soon as PV(g) has completed
             wait_bar(&bars->q_full, (n + 1) & 1, bars, prm.status);
             issue_qk(g + 1);
           }
-          issue_pv(g, i == 0);
         }
         ntiles = next_tiles;
       }
