@@ -548,6 +548,58 @@ def test_mla_step_is_append_then_decode_in_one_call(dev, oracle, variant):
     wuk.free(); wuv.free()
 
 
+def test_mla_steps_back_to_back_with_chained_and_with_plain_launches(dev, oracle):
+    """Twelve decode steps queued without a host wait in between, inputs and outputs resident on the device, so the
+    three kernels of every step follow one another in the stream with nothing between them: launched with programmatic
+    stream serialization (the default) and with plain launches they must leave the same output bits after every step
+    and the same cache."""
+    from relux_b200 import lib as L
+    H, Dh, dC, dHR = 128, 128, 512, 64
+    ctx = [700, 64, 129, 1, 255, 1000, 63, 320]
+    B = len(ctx)
+    steps = 12
+    scale = float(1.0 / np.sqrt(Dh + dHR))
+    pools = [build_mla(dev, oracle, np.random.default_rng(191), ctx, dC, dHR, extra_pages=2)[0] for _ in range(2)]
+    pools[1].tune(L.TUNE_CHAINED_LAUNCHES, 0)
+    rng = np.random.default_rng(192)
+    bf = oracle.bf16_from_f32
+    wuk = dev.upload(bf(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02))
+    wuv = dev.upload(bf(rng.standard_normal((dC, H * Dh)).astype(np.float32) * 0.02))
+    bufs = []
+    for i in range(steps):
+        bufs.append([dev.upload(bf(rng.standard_normal((B, dC)).astype(np.float32))),
+                     dev.upload(bf(rng.standard_normal((B, dHR)).astype(np.float32))),
+                     dev.upload(bf(rng.standard_normal((B, 1, H, Dh)).astype(np.float32))),
+                     dev.upload(bf(rng.standard_normal((B, 1, H, dHR)).astype(np.float32)))])
+    outs = [[dev.alloc(B * H * Dh * 4, L.DTYPE_F32) for _ in range(steps)] for _ in range(2)]
+    for k in range(2):
+        for i in range(steps):
+            c, r, q, qr = bufs[i]
+            pools[k].step(0, B, c, r, q, outs[k][i], H, Dh, scale, q_rope=qr, w_uk=wuk, w_uv=wuv)
+    dev.sync()
+    for i in range(steps):
+        a = outs[0][i].download((B, 1, H, Dh), np.float32)
+        b = outs[1][i].download((B, 1, H, Dh), np.float32)
+        assert np.isfinite(a).all()
+        assert np.array_equal(a, b), "step %d differs between chained and plain launches" % i
+    for s in range(B):
+        n = pools[0].seq_len(0, s)
+        assert n == ctx[s] + steps and pools[1].seq_len(0, s) == n
+        a0, b0 = pools[0].read_rows(0, s, max(0, n - steps), min(n, steps))
+        a1, b1 = pools[1].read_rows(0, s, max(0, n - steps), min(n, steps))
+        assert np.array_equal(a0, a1) and np.array_equal(b0, b1)
+    assert pools[0].status() == 0 and pools[1].status() == 0
+    for p in pools:
+        p.destroy()
+    for bs in bufs:
+        for b in bs:
+            b.free()
+    for k in range(2):
+        for o in outs[k]:
+            o.free()
+    wuk.free(); wuv.free()
+
+
 def test_step_falls_back_to_two_calls_where_the_fused_launch_does_not_apply(dev, oracle):
     """relux_gqa_step, and relux_mla_step in RELUX_ATTN_REFERENCE mode, run the append and the attention one after the
     other: results equal the two separate calls; mismatched arguments are refused before anything is written."""
