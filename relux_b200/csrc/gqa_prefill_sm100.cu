@@ -614,12 +614,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   if (warp == 0) tmem_dealloc<2>(tmem, kTmemCols);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 }  // namespace
-bool make_tmap_2d(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows);
 namespace {
 
 // CTA pairs that can be resident at the same time (one CTA per SM: the kernel uses all of its shared memory).
@@ -664,28 +660,11 @@ bool gqa_prefill_eligible(const Pool* p, const relux_attn_args& a) {
 // q: device bf16 [n][S][H][128] token-major.  out: device f32, same shape.
 int32_t launch_gqa_prefill_sm100(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const uint16_t* d_q, float* d_out) {
   const relux_pool_params& prm = p->prm;
-  static EncodeTiledFn enc = nullptr;
-  if (!enc) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
-      set_error("cuTensorMapEncodeTiled is not available");
-      return RELUX_ERR_CUDA;
-    }
-    enc = (EncodeTiledFn)sym;
-  }
   const int g = a.num_heads / prm.gqa_num_kv_heads, bq = 128 / g, S = a.q_tokens, H = a.num_heads;
-  CUtensorMap tq;
-  {
-    cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)H, (cuuint64_t)sb.n_seqs * S};
-    cuuint64_t strides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)H * kD * 2};
-    cuuint32_t box[3] = {64, (cuuint32_t)g, (cuuint32_t)bq};
-    cuuint32_t es[3] = {1, 1, 1};
-    if (enc(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)d_q, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-      set_error("tensor map for the prompt's queries could not be encoded");
-      return RELUX_ERR_CUDA;
-    }
+  CUtensorMap tq;   // queries [n * S][H][128]: a box is the g heads of one KV head for bq tokens
+  if (!make_tmap_3d(&tq, (void*)d_q, (uint64_t)sb.n_seqs * S, (uint64_t)H, kD, 64, (uint32_t)g, (uint32_t)bq)) {
+    set_error("tensor map for the prompt's queries could not be encoded");
+    return RELUX_ERR_CUDA;
   }
   PrefillParams k{};
   k.table = p->d_table;
@@ -755,16 +734,6 @@ bool mla_prefill_eligible(const Pool* p, const SeqBatch& sb, const relux_attn_ar
 // q: device bf16 [n][S][H][128], q_rope: device bf16 [n][S][H][64], token-major.  out: device f32 [n][S][H][128].
 int32_t launch_mla_prefill_sm100(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const uint16_t* d_q, const uint16_t* d_qr, float* d_out) {
   const relux_pool_params& prm = p->prm;
-  static EncodeTiledFn enc = nullptr;
-  if (!enc) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
-      set_error("cuTensorMapEncodeTiled is not available");
-      return RELUX_ERR_CUDA;
-    }
-    enc = (EncodeTiledFn)sym;
-  }
   const int S = a.q_tokens, H = a.num_heads;
   const int64_t Ttot = mla_expand_rows(p, sb, a.layer, a.extra_tokens);
   const size_t x_bytes = (size_t)mla_prefill_scratch_bytes(Ttot, H);
@@ -776,18 +745,11 @@ int32_t launch_mla_prefill_sm100(Pool* p, const SeqBatch& sb, const relux_attn_a
   rc = launch_mla_expand_sm100(p, sb, a.layer, a.extra_tokens, H, (const uint16_t*)a.w_uk, (const uint16_t*)a.w_uv, Ttot, kx, vx, seq_base);
   if (rc) return rc;
   CUtensorMap tq, tqr, tx;
-  for (int which = 0; which < 2; which++) {
-    const int cols = which ? 64 : kD;
-    cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)H, (cuuint64_t)sb.n_seqs * S};
-    cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)H * cols * 2};
-    cuuint32_t box[3] = {64, 1, 128};
-    cuuint32_t es[3] = {1, 1, 1};
-    if (enc(which ? &tqr : &tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)(which ? d_qr : d_q), dims, strides, box, es,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-      set_error("tensor map for the prompt's queries could not be encoded");
-      return RELUX_ERR_CUDA;
-    }
+  // queries [n * S][H][128] and their rope parts [n * S][H][64]: a box is one head for 128 tokens
+  if (!make_tmap_3d(&tq, (void*)d_q, (uint64_t)sb.n_seqs * S, (uint64_t)H, kD, 64, 1, 128) ||
+      !make_tmap_3d(&tqr, (void*)d_qr, (uint64_t)sb.n_seqs * S, (uint64_t)H, 64, 64, 1, 128)) {
+    set_error("tensor map for the prompt's queries could not be encoded");
+    return RELUX_ERR_CUDA;
   }
   if (!make_tmap_2d(&tx, kx, (uint64_t)2 * H * Ttot, kD, 64, 64)) {
     set_error("tensor map for the expanded keys / values could not be encoded");

@@ -224,6 +224,14 @@ void note_set_len(Pool* p, int layer, int seq, int old_len, int new_len);
 // Host pointers handed over as device memory must be 16-byte aligned: the kernels read them with vector loads.
 int32_t check_dev_align(const void* ptr, const char* what);
 
+// Tensor maps (runtime.cu).  bf16 elements, 128-byte swizzle, no out-of-bounds fill value (zeros); false when the driver
+// entry point is missing or refuses the map.
+//   2-D: [rows][cols], cols contiguous, box = box_cols x box_rows.
+//   3-D: [outer][mid][cols], cols contiguous and mid rows adjacent, box = box_cols x box_mid x box_outer.
+bool make_tmap_2d(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows);
+bool make_tmap_3d(CUtensorMap* m, void* base, uint64_t outer, uint64_t mid, uint64_t cols, uint32_t box_cols, uint32_t box_mid,
+                  uint32_t box_outer);
+
 inline void count_launch(Device* d, int n = 1) { d->launches += n; }
 
 // Launches `kern`; with `chained` the launch carries the programmatic stream-serialization attribute, so the grid may be

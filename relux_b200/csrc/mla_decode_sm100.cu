@@ -500,9 +500,6 @@ bool mla_sm100_eligible(const Pool* p, const relux_attn_args& a) {
          a.num_heads >= 16;
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // Number of ranges the stream of pages is cut into: one per CTA pair that can be resident at the same time,
 // divided among the query tokens that run side by side.
@@ -542,28 +539,10 @@ int mla_sm100_workers(Pool* p, int q_tokens) {
 int32_t launch_mla_decode_sm100(Pool* p, const SeqBatch& sb, const relux_attn_args& a, const SplitPlan& plan, const uint16_t* q_abs) {
   const relux_pool_params& prm = p->prm;
   if (plan.num_items == 0) return RELUX_OK;   // every sequence is empty: the merge writes zeros
-  static EncodeTiledFn enc = nullptr;
-  if (!enc) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
-      set_error("cuTensorMapEncodeTiled is not available");
-      return RELUX_ERR_CUDA;
-    }
-    enc = (EncodeTiledFn)sym;
-  }
-  CUtensorMap tq;
-  {
-    const uint64_t rows = (uint64_t)sb.n_seqs * a.q_tokens * a.num_heads;
-    cuuint64_t dims[2] = {kRow, rows};
-    cuuint64_t strides[1] = {kRow * 2};
-    cuuint32_t box[2] = {64, 64};
-    cuuint32_t es[2] = {1, 1};
-    if (enc(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)q_abs, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
-      set_error("tensor map for the absorbed queries could not be encoded");
-      return RELUX_ERR_CUDA;
-    }
+  CUtensorMap tq;   // the absorbed queries [rows][576], 64 x 64 boxes
+  if (!make_tmap_2d(&tq, (void*)q_abs, (uint64_t)sb.n_seqs * a.q_tokens * a.num_heads, kRow, 64, 64)) {
+    set_error("tensor map for the absorbed queries could not be encoded");
+    return RELUX_ERR_CUDA;
   }
   const int sx = a.q_tokens <= kMaxInterleavedQ ? a.q_tokens : 1;
   MlaSm100Params k;

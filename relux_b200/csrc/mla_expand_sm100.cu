@@ -358,7 +358,6 @@ int expand_workers(Pool* p) {
 
 }  // namespace
 
-bool make_tmap_2d(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint32_t box_cols, uint32_t box_rows);
 
 bool mla_expand_eligible(const Pool* p, int num_heads, int head_dim) {
   const relux_pool_params& prm = p->prm;

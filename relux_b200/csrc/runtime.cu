@@ -164,6 +164,18 @@ bool make_tmap_2d(CUtensorMap* m, void* base, uint64_t rows, uint64_t cols, uint
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
+bool make_tmap_3d(CUtensorMap* m, void* base, uint64_t outer, uint64_t mid, uint64_t cols, uint32_t box_cols, uint32_t box_mid,
+                  uint32_t box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {cols, mid, outer};
+  cuuint64_t strides[2] = {cols * 2, mid * cols * 2};
+  cuuint32_t box[3] = {box_cols, box_mid, box_outer};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
 
 void tuning_defaults(Tuning* t);
 
